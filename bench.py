@@ -1,0 +1,423 @@
+#!/usr/bin/env python
+"""Benchmark of the batch navigation step + rollout returns.
+
+One bench "step" is one rollout window: T = 32 simulator steps over all N environments of this GPU
+(action -> move/turn on the navmesh -> GPS/compass -> A* + funnel geodesic -> reward / done /
+info -> on-device episode reset), each step's reward and mask stored into rollout-storage tensors,
+followed by one fused GAE + advantage normalisation over the [T+1, N] window.  The metric is
+environment steps per second = N * T * windows / time, whole job (all ranks).
+
+Default workload: benchmark config 1 -- one 50x50 m synthetic floor plan with 60 box obstacles
+(Recast single-tile build: 446 polygons), 4096 environments per GPU, i.i.d. uniform actions over
+{stop, forward, left, right}.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Lines printed (rank 0, one JSON object):
+  value     device-resident arm: actions already in HBM, results stay in HBM, CUDA-event timed
+  e2e       same metric through the reference-shaped host API: numpy actions in, numpy
+            reward / mask / info / polar out every step (pinned-memory H2D + D2H inside the timed
+            region)
+  roofline  for the kernel with the largest share of step time, from CUDA events recorded around
+            every launch in a separate pass
+  cpu_baseline  the CPU oracle (the reference's compiled PathFinder driven by the simulator
+            restatement, all host cores) on a bounded sample of the same workload
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+T_ROLLOUT = 32
+GAMMA, TAU = 0.99, 0.95
+# algorithmic bytes (state columns read + written, outputs written) per unit of each launch
+BYTES_PER_ENV_STEP = 177          # move + sensor + reward path, per environment step
+BYTES_PER_GEO_QUERY = 44          # list entry 4, scene 4, two points 24, two refs 8 -> distance 4
+BYTES_PER_GAE_ELEM = 25.2         # scan 17.2 + normalise 8 per (t, env)
+L2_FLUSH_BYTES = 256 << 20
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--envs", type=int, default=4096, help="environments per GPU")
+    ap.add_argument("--scene", default="c1")
+    ap.add_argument("--mix", default="uniform", choices=["uniform", "policy"])
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def scene_files(name):
+    d = os.path.join(ROOT, "tests", "golden", "scenes")
+    return os.path.join(d, f"{name}.navmesh"), os.path.join(d, f"{name}.episodes.npy")
+
+
+def draw_actions(shape, mix, seed):
+    rng = np.random.default_rng(seed)
+    if mix == "uniform":
+        return rng.integers(0, 4, size=shape, dtype=np.int64)
+    u = rng.random(shape)
+    a = np.full(shape, 3, np.int64)
+    a[u < 0.8025] = 2
+    a[u < 0.605] = 1
+    a[u < 0.005] = 0
+    return a
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu):
+        self.gpu = gpu
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.Q}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                "sw_power_cap"), f[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": float(np.max(mx)) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback 6.65 TB/s (MEASURED_PEAKS.json absent)"
+
+
+# ------------------------------------------------------------------------------------ CPU arm
+
+def cpu_arm(args, seconds, steps_cap=None):
+    """Times the CPU oracle on the bench workload; returns (env_steps_per_s, details)."""
+    from oracle import pyoracle
+    if not pyoracle.available():
+        raise RuntimeError("oracle libraries missing (oracle/_ref, oracle/_build)")
+    nav, epf = scene_files(args.scene)
+    eps = np.load(epf)
+    cores = len(os.sched_getaffinity(0))
+    n = args.envs
+    sim = pyoracle.OracleSim([(nav, eps)], n, seed=1, threads=cores)
+    sim.reset()
+    chunk = T_ROLLOUT
+    rewards = np.zeros((T_ROLLOUT + 1, n), np.float32)
+    masks = np.ones((T_ROLLOUT + 1, n), bool)
+    values = np.random.default_rng(0).standard_normal((T_ROLLOUT + 1, n)).astype(np.float32)
+    sim.run(draw_actions((8, n), args.mix, 99))  # warm-up
+    done_steps = 0
+    t0 = time.perf_counter()
+    k = 0
+    while True:
+        acts = draw_actions((chunk, n), args.mix, 1000 + k)
+        ta = time.perf_counter()
+        for t in range(chunk):
+            sim.step(acts[t])
+            rewards[t] = sim.rewards
+            masks[t + 1] = sim.masks != 0
+        pyoracle.gae_reference(rewards, values, masks, values[T_ROLLOUT], GAMMA, TAU, normalize=True)
+        tb = time.perf_counter()
+        k += 1
+        done_steps += chunk
+        if k == 1:
+            t0 = ta  # exclude the first action draw
+            busy = 0.0
+        busy += tb - ta
+        if busy >= seconds or (steps_cap and k >= steps_cap):
+            break
+    sim.close()
+    rate = done_steps * n / busy
+    return rate, {"cores": cores, "windows": k, "seconds": busy,
+                  "sample": f"{k} windows of {T_ROLLOUT} steps x {n} envs on scene {args.scene} "
+                            f"({args.mix} actions) + numpy GAE per window; simulator control flow = "
+                            "oracle/oracle_sim.cpp restatement, every navmesh query = the "
+                            "reference's compiled PathFinder (oracle/_ref/libref_nav.so), one "
+                            "PathFinder replica per thread"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    t_start = time.perf_counter()
+    per_window_budget = max(args.cpu_seconds, 5.0)
+    rate, d = cpu_arm(args, per_window_budget, steps_cap=args.steps + args.warmup)
+    ms = 1000.0 * d["seconds"] / max(d["windows"], 1)
+    line = {
+        "impl": "reference", "metric": "env_steps_per_sec", "value": rate, "unit": "env-steps/s",
+        "n_gpus": args.gpus, "steps": d["windows"], "warmup": 0, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": f"config1: scene {args.scene}, {args.envs} envs, T={T_ROLLOUT} "
+                               f"rollout + GAE, {args.mix} actions", "l2": "n/a (CPU)"},
+        "cpu_baseline": {"value": rate, "unit": "env-steps/s", "cores": d["cores"],
+                         "kind": "reference", "sample": d["sample"]},
+        "e2e": {"value": rate, "unit": "env-steps/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0, "wall_s": time.perf_counter() - t_start,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------ GPU arm
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from bps_nav_b200 import bps_sim, rollout
+    from bps_nav_b200.dataset import Scene
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    nav, epf = scene_files(args.scene)
+    scene = Scene(nav, np.load(epf), f"{args.scene}.glb")
+    N, T, K, W = args.envs, T_ROLLOUT, args.steps, max(args.warmup, 3)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if world > 1:
+            t = torch.tensor([x], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        return x
+
+    rewards = torch.zeros(T + 1, N, 1, device=dev)
+    values = torch.randn(T + 1, N, 1, device=dev)
+    next_value = torch.randn(N, 1, device=dev)
+    masks = torch.ones(T + 1, N, 1, dtype=torch.bool, device=dev)
+    returns = torch.zeros(T + 1, N, 1, device=dev)
+    adv = torch.empty(T, N, 1, device=dev)
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+
+    # ---------------- device-resident arm
+    gen = bps_sim.PointNavRolloutGenerator.from_scenes([scene], N, gpu_id=local,
+                                                       seed=1000 + rank, host_mirrors=False)
+    info = gen.scene_info(0)
+    gen.reset(0)
+    acts = torch.from_numpy(draw_actions(((W + K) * T, N), args.mix, 7 + rank)).to(dev)
+    r_view = gen.tensor(0, "reward")
+    m_view = gen.tensor(0, "mask")
+
+    def window(k):
+        base = k * T
+        for t in range(T):
+            gen.step_start(0, acts[base + t])
+            gen.step_end(0)
+            rewards[t, :, 0].copy_(r_view)
+            masks[t + 1, :, 0].copy_(m_view)
+        rollout.compute_returns(rewards, values, masks, returns, next_value, T, GAMMA, TAU,
+                                advantages=adv, normalize=True)
+
+    for k in range(W):
+        window(k)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+          for _ in range(K)]
+    t_wall0 = time.perf_counter()
+    for k in range(K):
+        flush.fill_(k & 0xFF)  # evict L2 between timed windows (untimed)
+        ev[k][0].record()
+        window(W + k)
+        ev[k][1].record()
+    barrier()
+    wall = time.perf_counter() - t_wall0
+    clocks = sampler.stop() if rank == 0 else None
+    dev_ms = sum(a.elapsed_time(b) for a, b in ev)
+    dev_ms = max_over_ranks(dev_ms)
+    value = world * N * T * K / (dev_ms / 1000.0)
+    mean_return = float(returns[:T].mean().item())
+
+    # ---------------- per-kernel pass (roofline): CUDA events around every launch
+    gen.profile(0, True)
+    P = min(K, 5)
+    nres = 0.0
+    for k in range(P):
+        for t in range(T):
+            gen.step_start(0, acts[k * T + t])
+            gen.step_end(0)
+            nres += float((m_view == 0).sum().item())
+    kms, ksteps = gen.profile_read(0)
+    gen.profile(0, False)
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g0.record()
+    for _ in range(20):
+        rollout.compute_returns(rewards, values, masks, returns, next_value, T, GAMMA, TAU,
+                                advantages=adv, normalize=True)
+    g1.record()
+    torch.cuda.synchronize()
+    gae_ms = g0.elapsed_time(g1) / 20
+    kms = {k: v / max(ksteps, 1) for k, v in kms.items()}  # ms per launch
+    peak, peak_src = measured_peak()
+    top = max(kms, key=kms.get)
+    resets_per_step = nres / max(ksteps, 1)
+    if args.mix == "uniform":
+        q_step = N * 0.5  # moved (1/4) or stopped (1/4) -> one geodesic query
+    else:
+        q_step = N * 0.61
+    units = {"k_move": N, "k_finish": N, "k_geo[step]": q_step, "k_reset": resets_per_step,
+             "k_geo[reset]": resets_per_step}
+    per_unit = {"k_move": 96 + 56 + 8, "k_finish": 60 + 25, "k_geo[step]": BYTES_PER_GEO_QUERY,
+                "k_reset": 40 + 100, "k_geo[reset]": BYTES_PER_GEO_QUERY + 4}
+    alg_bytes = units[top] * per_unit[top]
+    achieved = alg_bytes / (kms[top] * 1e-3) / 1e9
+    step_ms = sum(kms.values())
+    roofline = {
+        "bound": "hbm", "kernel": top, "achieved": achieved, "peak": peak, "unit": "GB/s",
+        "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+        "ms_per_launch": kms[top],
+        "note": "A* is latency/divergence-bound: its algorithmic HBM bytes are tiny by design "
+                "(scratch is L2-resident); see kernels{} for every launch",
+    }
+    kernels = {k: {"ms_per_launch": v, "share": v / step_ms} for k, v in kms.items()}
+    kernels["gae(scan+normalise)"] = {"ms_per_launch": gae_ms,
+                                      "achieved_gbs": T * N * BYTES_PER_GAE_ELEM / (gae_ms * 1e-3) / 1e9}
+    step_roofline = {"achieved": N * BYTES_PER_ENV_STEP / (step_ms * 1e-3) / 1e9, "unit": "GB/s",
+                     "frac": N * BYTES_PER_ENV_STEP / (step_ms * 1e-3) / 1e9 / peak,
+                     "ms_per_step_all_launches": step_ms}
+    gen.close()
+
+    # ---------------- end-to-end arm through the reference-shaped host API
+    e2e = None
+    if not args.no_e2e:
+        gen2 = bps_sim.PointNavRolloutGenerator.from_scenes([scene], N, gpu_id=local,
+                                                           seed=1000 + rank, host_mirrors=True)
+        gen2.reset(0)
+        hacts = draw_actions(((W + K) * T, N), args.mix, 7 + rank)
+        h_rew = torch.from_numpy(gen2.get_rewards(0)).view(-1, 1)
+        h_mask = torch.from_numpy(gen2.get_masks(0)).view(-1, 1)
+        h_polar = gen2.get_polars(0)
+        h_info = gen2.get_infos(0)
+        sink = 0.0
+
+        def window_e2e(k):
+            nonlocal sink
+            base = k * T
+            for t in range(T):
+                gen2.step_start(0, hacts[base + t])
+                gen2.step_end(0)
+                rewards[t].copy_(h_rew, non_blocking=True)       # rollouts.insert: host -> device
+                masks[t + 1].copy_(h_mask.bool(), non_blocking=True)
+                sink += float(h_polar[0, 0]) + float(h_info["distanceToGoal"][0])
+            rollout.compute_returns(rewards, values, masks, returns, next_value, T, GAMMA, TAU,
+                                    advantages=adv, normalize=True)
+            return float(adv.mean().item())  # device -> host read of the window's result
+
+        for k in range(W):
+            window_e2e(k)
+        barrier()
+        t0 = time.perf_counter()
+        for k in range(K):
+            window_e2e(W + k)
+        barrier()
+        e2e_s = max_over_ranks(time.perf_counter() - t0)
+        h2d = T * (N * 8 + N * 4 + N)            # actions, then reward + mask into the rollout
+        d2h = T * (N * 4 + N + N * 12 + N * 8) + 4
+        e2e = {"value": world * N * T * K / e2e_s, "unit": "env-steps/s",
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "ms_per_step": 1000 * e2e_s / K,
+               "how": "host wall clock, barrier + synchronize on both sides, max over ranks"}
+        gen2.close()
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        try:
+            rate, d = cpu_arm(args, args.cpu_seconds)
+            cpu = {"value": rate, "unit": "env-steps/s", "cores": d["cores"], "kind": "reference",
+                   "sample": d["sample"], "seconds": d["seconds"]}
+        except Exception as e:  # the baseline is a reported figure, not a dependency
+            cpu = {"value": None, "unit": "env-steps/s", "cores": 0, "kind": "reference",
+                   "sample": f"unavailable: {e}"}
+
+    if rank == 0:
+        line = {
+            "metric": "env_steps_per_sec", "value": value, "unit": "env-steps/s", "n_gpus": world,
+            "steps": K, "warmup": W, "ms_per_step": dev_ms / K, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"config1: scene {args.scene} ({info['num_polys']} polys, "
+                                   f"{info['num_islands']} islands), {N} envs/GPU, one step = "
+                                   f"T={T} sim steps + fused GAE/normalise, {args.mix} actions",
+                       "envs_per_gpu": N, "rollout_T": T, "polys": info["num_polys"],
+                       "l2": f"flushed between timed windows ({L2_FLUSH_BYTES >> 20} MiB write)",
+                       "timing": "CUDA events per window on the launch stream, summed, max over ranks"},
+            "clocks": clocks, "e2e": e2e, "roofline": roofline, "roofline_step": step_roofline,
+            "kernels": kernels, "cpu_baseline": cpu,
+            "gpu_launches": K * (T * 5 + 2), "resets_per_step": resets_per_step,
+            "mean_return": mean_return, "wall_s_device_arm": wall,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

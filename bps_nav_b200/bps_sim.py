@@ -1,0 +1,346 @@
+"""Drop-in for the reference's ``bps_sim`` extension module (PointGoal navigation).
+
+Class and method names, argument order and meaning follow the pybind11 bindings at
+``simulator/simulator.cpp:1785-1823`` (``RolloutGenerator`` at ``:1332-1460``).  The work that the
+reference fans out over CPU threads (``:1619-1653``) is done by CUDA kernels behind the C ABI of
+``include/bpsn.h``.
+
+Kept from the reference:
+
+* constructor signature, and ``step / step_start / step_end / render / reset / rgba / depth /
+  get_rewards / get_masks / get_infos / get_polars / wait_for_frame / swap_stats``;
+* ``get_*`` return numpy arrays that alias fixed host buffers for the life of the generator
+  (``makeFlatNumpyArray``, ``:1001-1009``) and are up to date when ``step_end`` returns;
+* environment order: group-major, then ``num_environments / num_active_scenes`` consecutive
+  environments per scene (``:1205-1221, 1581-1592``);
+* after a finished episode the environment is reset inside the same step: reward / mask / info
+  describe the terminal transition, polar the first state of the new episode (``:1636-1642``).
+
+Added (not in the reference): device-resident views of every result and state array
+(``tensor(group, name)``), and ``step_start`` accepting a CUDA int64 tensor of actions, so a
+trainer can keep the whole rollout on the GPU.
+
+Not reproduced: rendering (``render`` / ``wait_for_frame`` only order the stream; ``rgba`` /
+``depth`` expose zero-filled device buffers) and active-scene swapping (``swap_stats`` reports no
+swaps).
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import _lib as L
+from . import dataset as _dataset
+
+INFO_DTYPE = np.dtype([("success", "<f4"), ("spl", "<f4"), ("distanceToGoal", "<f4")])
+
+_FIELDS = {
+    # name: (field id, numpy dtype, shape as function of B)
+    "reward": (L.FIELD_REWARD, np.float32, lambda B: (B,)),
+    "mask": (L.FIELD_MASK, np.uint8, lambda B: (B,)),
+    "info": (L.FIELD_INFO, np.float32, lambda B: (B, 3)),
+    "polar": (L.FIELD_POLAR, np.float32, lambda B: (B, 2)),
+    "position": (L.FIELD_POSITION, np.float32, lambda B: (3, B)),
+    "rotation": (L.FIELD_ROTATION, np.float32, lambda B: (4, B)),
+    "goal": (L.FIELD_GOAL, np.float32, lambda B: (3, B)),
+    "nav_position": (L.FIELD_NAV_POSITION, np.float32, lambda B: (3, B)),
+    "nav_poly": (L.FIELD_NAV_POLY, np.uint32, lambda B: (B,)),
+    "goal_poly": (L.FIELD_GOAL_POLY, np.uint32, lambda B: (B,)),
+    "step": (L.FIELD_STEP, np.uint32, lambda B: (B,)),
+    "episode": (L.FIELD_EPISODE, np.uint32, lambda B: (B,)),
+    "reset_count": (L.FIELD_RESET_COUNT, np.uint32, lambda B: (B,)),
+    "status": (L.FIELD_STATUS, np.uint32, lambda B: (B,)),
+    "prev_dist": (L.FIELD_PREV_DIST, np.float32, lambda B: (B,)),
+    "cum_travel": (L.FIELD_CUM_TRAVEL, np.float32, lambda B: (B,)),
+    "init_dist": (L.FIELD_INIT_DIST, np.float32, lambda B: (B,)),
+    "scene": (L.FIELD_SCENE, np.uint32, lambda B: (B,)),
+}
+
+
+class _DeviceArray:
+    """Minimal ``__cuda_array_interface__`` carrier for a raw device pointer (non-owning)."""
+
+    def __init__(self, ptr, shape, dtype):
+        self.__cuda_array_interface__ = {
+            "shape": tuple(shape), "typestr": np.dtype(dtype).str, "data": (int(ptr), False),
+            "version": 3, "strides": None,
+        }
+
+
+def _new_capsule(ptr):
+    f = C.pythonapi.PyCapsule_New
+    f.restype = C.py_object
+    f.argtypes = [C.c_void_p, C.c_char_p, C.c_void_p]
+    return f(ptr, None, None)
+
+
+class _RolloutGenerator:
+    _task = None
+
+    def __init__(self, dataset_path, asset_path, num_environments, num_active_scenes, num_workers,
+                 gpu_id, render_resolution, color, depth, double_buffered, seed,
+                 should_set_affinity=True):
+        # num_workers / should_set_affinity configure the reference's CPU worker pool; a kernel
+        # launch replaces that pool, so they are accepted and ignored.
+        del num_workers, should_set_affinity
+        scenes = _dataset.load_dataset(dataset_path, asset_path)
+        self._setup(scenes, num_environments, num_active_scenes, gpu_id, render_resolution, color,
+                    depth, double_buffered, seed, host_mirrors=True)
+
+    @classmethod
+    def from_scenes(cls, scenes, num_environments, num_active_scenes=None, gpu_id=0,
+                    render_resolution=(64, 64), color=False, depth=False, double_buffered=False,
+                    seed=0, host_mirrors=True):
+        """Builds a generator from in-memory ``dataset.Scene`` objects (no JSON involved)."""
+        self = cls.__new__(cls)
+        if num_active_scenes is None:
+            num_active_scenes = len(scenes)
+        self._setup(list(scenes), num_environments, num_active_scenes, gpu_id, render_resolution,
+                    color, depth, double_buffered, seed, host_mirrors)
+        return self
+
+    def _setup(self, scenes, num_environments, num_active_scenes, gpu_id, render_resolution, color,
+               depth, double_buffered, seed, host_mirrors):
+        if self._task != "pointnav":
+            raise NotImplementedError(
+                f"{type(self).__name__}: only the PointGoal navigation task is implemented")
+        self._lib = L.load()
+        self._h = C.c_void_p()
+        num_groups = 2 if double_buffered else 1
+        if num_active_scenes > len(scenes):
+            raise RuntimeError("num_active_scenes exceeds the number of scenes in the dataset")
+        active, inactive = _dataset.select_active_scenes(len(scenes), num_active_scenes, seed)
+        self._active_scenes = active
+        self._inactive_scenes = inactive
+        self._scenes = [scenes[i] for i in active]
+        self.num_environments = int(num_environments)
+        self.num_groups = num_groups
+        self.gpu_id = int(gpu_id)
+        self._color = bool(color)
+        self._depth = bool(depth)
+        self._res = (int(render_resolution[0]), int(render_resolution[1]))
+        self._host_mirrors = bool(host_mirrors)
+        cfg = L.Config(gpu_id=self.gpu_id, num_envs=self.num_environments, num_groups=num_groups,
+                       num_scenes=len(self._scenes), seed=int(seed) & (2**64 - 1),
+                       flags=L.FLAG_HOST_MIRRORS if host_mirrors else 0, reserved=0)
+        L.check(self._lib.bpsn_create(C.byref(cfg), C.byref(self._h)))
+        try:
+            for i, sc in enumerate(self._scenes):
+                L.check(self._lib.bpsn_set_navmesh_file(self._h, i, sc.navmesh_path.encode()),
+                        self._h)
+                eps = np.ascontiguousarray(sc.episodes)
+                L.check(self._lib.bpsn_set_episodes(self._h, i, eps.ctypes.data, len(eps)),
+                        self._h)
+            L.check(self._lib.bpsn_finalize(self._h), self._h)
+        except Exception:
+            self._lib.bpsn_destroy(self._h)
+            self._h = C.c_void_p()
+            raise
+        self.envs_per_group = self.num_environments // num_groups
+        self.envs_per_scene = self.num_environments // len(self._scenes)
+        self._num_steps_taken = 0
+        self._host_views = {}
+        self._dev_tensors = {}
+        self._render_bufs = {}
+        self._keepalive = []
+
+    # ------------------------------------------------------------------ lifecycle
+    def close(self):
+        h = getattr(self, "_h", None)
+        if h is not None and h.value:
+            self._lib.bpsn_destroy(h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ------------------------------------------------------------------ stepping
+    def _stream(self):
+        import torch
+        return C.c_void_p(torch.cuda.current_stream(self.gpu_id).cuda_stream)
+
+    def reset(self, group_idx):
+        L.check(self._lib.bpsn_reset(self._h, group_idx, self._stream()), self._h)
+
+    def step_start(self, group_idx, actions):
+        """``actions``: C-contiguous int64 numpy array of length ``envs_per_group`` (reference
+        signature), or a CUDA int64 tensor of the same length (device-resident fast path)."""
+        if isinstance(actions, np.ndarray):
+            if actions.dtype != np.int64 or not actions.flags.c_contiguous:
+                actions = np.ascontiguousarray(actions, dtype=np.int64)
+            if actions.shape[0] != self.envs_per_group:
+                raise RuntimeError("actions length must equal the number of envs in the group")
+            self._keepalive = [actions]
+            L.check(self._lib.bpsn_step_start(self._h, group_idx, actions.ctypes.data, L.MEM_HOST,
+                                              self._stream()), self._h)
+        else:
+            import torch
+            if not (isinstance(actions, torch.Tensor) and actions.is_cuda and
+                    actions.dtype == torch.int64 and actions.is_contiguous()):
+                raise RuntimeError("actions must be an int64 numpy array or a contiguous CUDA "
+                                   "int64 tensor")
+            if actions.numel() != self.envs_per_group:
+                raise RuntimeError("actions length must equal the number of envs in the group")
+            self._keepalive = [actions]
+            L.check(self._lib.bpsn_step_start(self._h, group_idx, actions.data_ptr(),
+                                              L.MEM_DEVICE, self._stream()), self._h)
+        self._num_steps_taken += self.envs_per_group
+
+    def step_end(self, group_idx):
+        L.check(self._lib.bpsn_step_end(self._h, group_idx), self._h)
+
+    def render(self, group_idx):
+        """No renderer on this path; kept so call sites need no change."""
+        del group_idx
+
+    def step(self, group_idx, actions):
+        self.step_start(group_idx, actions)
+        self.step_end(group_idx)
+        self.render(group_idx)
+
+    def wait_for_frame(self, group_idx):
+        import torch
+        del group_idx
+        torch.cuda.current_stream(self.gpu_id).synchronize()
+
+    # ------------------------------------------------------------------ result views (host)
+    def _host_array(self, group_idx, name):
+        key = (group_idx, name)
+        if key not in self._host_views:
+            fid, dt, shape = _FIELDS[name]
+            p, n = C.c_void_p(), C.c_size_t()
+            L.check(self._lib.bpsn_get_ptr(self._h, group_idx, fid, L.MEM_HOST, C.byref(p),
+                                           C.byref(n)), self._h)
+            buf = (C.c_uint8 * n.value).from_address(p.value)
+            arr = np.frombuffer(buf, dtype=dt).reshape(shape(self.envs_per_group))
+            self._host_views[key] = arr
+        return self._host_views[key]
+
+    def get_rewards(self, group_idx):
+        return self._host_array(group_idx, "reward")
+
+    def get_masks(self, group_idx):
+        return self._host_array(group_idx, "mask")
+
+    def get_infos(self, group_idx):
+        return self._host_array(group_idx, "info").view(INFO_DTYPE).reshape(-1)
+
+    def get_polars(self, group_idx):
+        return self._host_array(group_idx, "polar")
+
+    # ------------------------------------------------------------------ device views (added)
+    def tensor(self, group_idx, name):
+        """Zero-copy CUDA tensor over a per-group array; names are the keys of ``_FIELDS``
+        (``reward mask info polar position rotation goal nav_position nav_poly goal_poly step
+        episode reset_count status prev_dist cum_travel init_dist scene``).  uint32 arrays are
+        exposed as int32 tensors (same bits)."""
+        import torch
+        key = (group_idx, name)
+        if key not in self._dev_tensors:
+            fid, dt, shape = _FIELDS[name]
+            p, n = C.c_void_p(), C.c_size_t()
+            L.check(self._lib.bpsn_get_ptr(self._h, group_idx, fid, L.MEM_DEVICE, C.byref(p),
+                                           C.byref(n)), self._h)
+            if dt == np.uint32:
+                dt = np.int32
+            carrier = _DeviceArray(p.value, shape(self.envs_per_group), dt)
+            self._dev_tensors[key] = torch.as_tensor(carrier, device=f"cuda:{self.gpu_id}")
+        return self._dev_tensors[key]
+
+    # ------------------------------------------------------------------ image buffers (stubs)
+    def _render_buffer(self, group_idx, kind):
+        import torch
+        key = (group_idx, kind)
+        if key not in self._render_bufs:
+            B = self.envs_per_group
+            H, W = self._res[1], self._res[0]
+            if kind == "rgba":
+                t = torch.zeros(B, H, W, 4, dtype=torch.uint8, device=f"cuda:{self.gpu_id}")
+            else:
+                t = torch.zeros(B, H, W, dtype=torch.float32, device=f"cuda:{self.gpu_id}")
+            self._render_bufs[key] = t
+        return self._render_bufs[key]
+
+    def rgba(self, group_idx):
+        return _new_capsule(self._render_buffer(group_idx, "rgba").data_ptr())
+
+    def depth(self, group_idx):
+        return _new_capsule(self._render_buffer(group_idx, "depth").data_ptr())
+
+    # ------------------------------------------------------------------ misc
+    @property
+    def swap_stats(self):
+        # (% of steps that swapped a scene, scenes in use, mean envs per scene) summed over
+        # groups as RolloutGenerator::swapStats does (simulator.cpp:1412-1424); no swapping here.
+        return (0.0, float(len(self._scenes)), float(self.envs_per_scene * self.num_groups))
+
+    KERNEL_NAMES = ("k_move", "k_geo[step]", "k_finish", "k_reset", "k_geo[reset]")
+
+    def profile(self, group_idx, enable=True):
+        """Turns per-kernel CUDA-event timing of the step on or off (totals are cleared)."""
+        L.check(self._lib.bpsn_profile_enable(self._h, group_idx, 1 if enable else 0), self._h)
+
+    def profile_read(self, group_idx):
+        """Returns ({kernel name: total ms}, steps) accumulated since ``profile(.., True)``."""
+        ms = (C.c_double * 5)()
+        n = C.c_uint64()
+        L.check(self._lib.bpsn_profile_read(self._h, group_idx, ms, C.byref(n)), self._h)
+        return dict(zip(self.KERNEL_NAMES, list(ms))), int(n.value)
+
+    def scene_info(self, scene_idx):
+        a, b, c = C.c_int32(), C.c_int32(), C.c_int32()
+        L.check(self._lib.bpsn_scene_info(self._h, scene_idx, C.byref(a), C.byref(b), C.byref(c)),
+                self._h)
+        return {"num_polys": a.value, "num_disabled": b.value, "num_islands": c.value}
+
+    # batched navmesh queries on device tensors (PathFinder API in batch form)
+    def query_snap(self, scene_idx, points):
+        import torch
+        pts = points.contiguous().float()
+        n = pts.shape[0]
+        out = torch.empty_like(pts)
+        refs = torch.empty(n, dtype=torch.int32, device=pts.device)
+        L.check(self._lib.bpsn_query_snap(self._h, scene_idx, n, pts.data_ptr(), out.data_ptr(),
+                                          refs.data_ptr(), self._stream()), self._h)
+        return out, refs
+
+    def query_try_step(self, scene_idx, start, start_refs, end):
+        import torch
+        s, e = start.contiguous().float(), end.contiguous().float()
+        r = start_refs.contiguous().to(torch.int32)
+        n = s.shape[0]
+        out = torch.empty_like(s)
+        refs = torch.empty(n, dtype=torch.int32, device=s.device)
+        L.check(self._lib.bpsn_query_try_step(self._h, scene_idx, n, s.data_ptr(), r.data_ptr(),
+                                              e.data_ptr(), out.data_ptr(), refs.data_ptr(),
+                                              self._stream()), self._h)
+        return out, refs
+
+    def query_geodesic(self, scene_idx, start, start_refs, end, end_refs):
+        import torch
+        s, e = start.contiguous().float(), end.contiguous().float()
+        sr = start_refs.contiguous().to(torch.int32)
+        er = end_refs.contiguous().to(torch.int32)
+        n = s.shape[0]
+        out = torch.empty(n, dtype=torch.float32, device=s.device)
+        status = torch.empty(n, dtype=torch.int32, device=s.device)
+        L.check(self._lib.bpsn_query_geodesic(self._h, scene_idx, n, s.data_ptr(), sr.data_ptr(),
+                                              e.data_ptr(), er.data_ptr(), out.data_ptr(),
+                                              status.data_ptr(), self._stream()), self._h)
+        return out, status
+
+
+class PointNavRolloutGenerator(_RolloutGenerator):
+    _task = "pointnav"
+
+
+class FleeRolloutGenerator(_RolloutGenerator):
+    """Present in the reference module (``simulator/simulator.cpp:1818-1819``); not implemented."""
+    _task = "flee"
+
+
+class ExplorationRolloutGenerator(_RolloutGenerator):
+    """Present in the reference module (``simulator/simulator.cpp:1821-1822``); not implemented."""
+    _task = "exploration"

@@ -1,0 +1,54 @@
+"""Builds the CUDA shared library in-tree (``bps_nav_b200/libbpsn.so``) with nvcc for sm_100a.
+
+Run as ``python -m bps_nav_b200.build``.  nvcc cross-compiles without a GPU.
+FMA contraction is disabled (``-fmad=false``): the navigation-mesh queries and
+the GAE scan must round every operation like the scalar CPU reference does.
+"""
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIB = os.path.join(HERE, "libbpsn.so")
+SOURCES = ["bpsn.cu", "navmesh_host.cpp"]
+HEADERS = ["nav_types.h", "nav_query.cuh", "sim_kernels.cuh", "gae_kernels.cuh", "navmesh_host.h"]
+
+
+def _nvcc():
+    cand = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(cand):
+        raise RuntimeError("nvcc not found; cannot build libbpsn.so")
+    return cand
+
+
+def needs_build():
+    if not os.path.exists(LIB):
+        return True
+    t = os.path.getmtime(LIB)
+    deps = [os.path.join(CSRC, f) for f in SOURCES + HEADERS]
+    deps.append(os.path.join(HERE, "..", "include", "bpsn.h"))
+    return any(os.path.getmtime(d) > t for d in deps)
+
+
+def build(force=False, verbose=False):
+    if not force and not needs_build():
+        return LIB
+    cmd = [
+        _nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+        "-fmad=false", "-Xcompiler", "-fPIC", "-shared",
+    ]
+    if verbose:
+        cmd += ["-Xptxas", "-v"]
+    cmd += [os.path.join(CSRC, s) for s in SOURCES] + ["-o", LIB]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose:
+        sys.stderr.write(res.stderr)
+    if res.returncode != 0:
+        raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

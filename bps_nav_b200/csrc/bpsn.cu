@@ -1,0 +1,724 @@
+// C-ABI implementation (see include/bpsn.h).  Host-side bookkeeping only: it
+// owns device buffers, uploads flattened navmeshes and episodes, and launches
+// the kernels of sim_kernels.cuh / gae_kernels.cuh.  There is no CPU
+// execution path: every compute entry point launches CUDA kernels or fails.
+
+#include "../../include/bpsn.h"
+
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <string>
+#include <vector>
+
+#include "gae_kernels.cuh"
+#include "navmesh_host.h"
+#include "sim_kernels.cuh"
+
+using namespace bpsn;
+
+namespace {
+
+thread_local std::string g_lastError;
+
+struct DeviceScene {
+  HostScene host;
+  bool loaded = false;
+  void* blob = nullptr;  // one device allocation holding every array
+  NavScene dev{};
+  std::vector<bpsn_episode> episodes;
+};
+
+struct Group {
+  GroupDev dev{};
+  void* stateBlob = nullptr;
+  size_t stateBytes = 0;
+  // pinned host mirrors of the four result arrays
+  float* hReward = nullptr;
+  uint8_t* hMask = nullptr;
+  float* hInfo = nullptr;
+  float* hPolar = nullptr;
+  int64_t* hActions = nullptr;  // pinned staging
+  int64_t* dActions = nullptr;
+  AStarScratch* scratch = nullptr;
+  cudaEvent_t done = nullptr;
+  bool inFlight = false;
+  // optional per-kernel timing (bpsn_profile_enable)
+  bool profiling = false;
+  cudaEvent_t prof[6] = {};
+  double profMs[5] = {0, 0, 0, 0, 0};
+  uint64_t profSteps = 0;
+  // offsets of each field inside stateBlob (for bpsn_get_ptr)
+  void* fieldPtr[BPSN_FIELD_COUNT] = {};
+  size_t fieldBytes[BPSN_FIELD_COUNT] = {};
+};
+
+}  // namespace
+
+struct bpsn_sim {
+  bpsn_config cfg{};
+  std::vector<DeviceScene> scenes;
+  std::vector<uint32_t> envScene;
+  std::vector<Group> groups;
+  bool finalized = false;
+  std::string lastError;
+  // device tables
+  NavScene* dScenes = nullptr;
+  float* dEpisodes = nullptr;
+  uint32_t* dEpOffset = nullptr;
+  uint32_t* dEpCount = nullptr;
+  SceneTable table{};
+  TurnConsts turn{};
+  // scratch for the bpsn_query_* entry points
+  AStarScratch* queryScratch = nullptr;
+  uint32_t querySlots = 0;
+};
+
+namespace {
+
+int32_t fail(bpsn_sim* sim, int32_t code, const std::string& msg) {
+  if (sim)
+    sim->lastError = msg;
+  g_lastError = msg;
+  return code;
+}
+
+#define BPSN_CUDA(sim, expr)                                                              \
+  do {                                                                                    \
+    cudaError_t _e = (expr);                                                              \
+    if (_e != cudaSuccess)                                                                \
+      return fail(sim, BPSN_ERR_CUDA,                                                     \
+                  std::string(#expr) + ": " + cudaGetErrorString(_e));                    \
+  } while (0)
+
+inline size_t alignUp(size_t x, size_t a) {
+  return (x + a - 1) / a * a;
+}
+
+int32_t uploadScene(bpsn_sim* sim, DeviceScene& ds) {
+  const HostScene& h = ds.host;
+  size_t off = 0;
+  auto place = [&](size_t bytes) {
+    size_t o = off;
+    off = alignUp(off + bytes, 256);
+    return o;
+  };
+  const size_t oVerts = place(h.verts.size() * sizeof(float));
+  const size_t oPolys = place(h.polys.size() * sizeof(NavPoly));
+  const size_t oDetail = place(h.detail.size() * sizeof(NavDetail));
+  const size_t oDverts = place(h.dverts.size() * sizeof(float) + 16);
+  const size_t oDtris = place(h.dtris.size());
+  const size_t oBv = place(h.bv.size() * sizeof(NavBVNode) + 16);
+  const size_t oIsland = place(h.island.size() * sizeof(int32_t));
+  BPSN_CUDA(sim, cudaMalloc(&ds.blob, off));
+  uint8_t* base = static_cast<uint8_t*>(ds.blob);
+  auto up = [&](size_t o, const void* src, size_t bytes) -> cudaError_t {
+    if (!bytes)
+      return cudaSuccess;
+    return cudaMemcpy(base + o, src, bytes, cudaMemcpyHostToDevice);
+  };
+  BPSN_CUDA(sim, up(oVerts, h.verts.data(), h.verts.size() * sizeof(float)));
+  BPSN_CUDA(sim, up(oPolys, h.polys.data(), h.polys.size() * sizeof(NavPoly)));
+  BPSN_CUDA(sim, up(oDetail, h.detail.data(), h.detail.size() * sizeof(NavDetail)));
+  BPSN_CUDA(sim, up(oDverts, h.dverts.data(), h.dverts.size() * sizeof(float)));
+  BPSN_CUDA(sim, up(oDtris, h.dtris.data(), h.dtris.size()));
+  BPSN_CUDA(sim, up(oBv, h.bv.data(), h.bv.size() * sizeof(NavBVNode)));
+  BPSN_CUDA(sim, up(oIsland, h.island.data(), h.island.size() * sizeof(int32_t)));
+  NavScene s = h.view();
+  s.verts = reinterpret_cast<const float*>(base + oVerts);
+  s.polys = reinterpret_cast<const NavPoly*>(base + oPolys);
+  s.detail = reinterpret_cast<const NavDetail*>(base + oDetail);
+  s.dverts = reinterpret_cast<const float*>(base + oDverts);
+  s.dtris = reinterpret_cast<const uint8_t*>(base + oDtris);
+  s.bv = reinterpret_cast<const NavBVNode*>(base + oBv);
+  s.island = reinterpret_cast<const int32_t*>(base + oIsland);
+  ds.dev = s;
+  return BPSN_OK;
+}
+
+int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase) {
+  size_t off = 0;
+  auto place = [&](size_t bytes) {
+    size_t o = off;
+    off = alignUp(off + bytes, 256);
+    return o;
+  };
+  const size_t f = sizeof(float), u = sizeof(uint32_t);
+  const size_t oPos = place(3 * B * f), oRot = place(4 * B * f), oGoal = place(3 * B * f);
+  const size_t oNavPos = place(3 * B * f), oNavGoal = place(3 * B * f),
+               oPrevPos = place(3 * B * f);
+  const size_t oPrevDist = place(B * f), oCum = place(B * f), oInit = place(B * f),
+               oTmp = place(B * f);
+  const size_t oNavRef = place(B * u), oGoalRef = place(B * u), oStep = place(B * u),
+               oEpisode = place(B * u), oResetCount = place(B * u), oStatus = place(B * u),
+               oScene = place(B * u), oFlags = place(B * u);
+  const size_t oReward = place(B * f), oMask = place(B), oInfo = place(3 * B * f),
+               oPolar = place(2 * B * f);
+  const size_t oGeoList = place(B * u), oResetList = place(B * u), oCounts = place(4 * u);
+  g.stateBytes = off;
+  BPSN_CUDA(sim, cudaMalloc(&g.stateBlob, off));
+  BPSN_CUDA(sim, cudaMemset(g.stateBlob, 0, off));
+  uint8_t* b = static_cast<uint8_t*>(g.stateBlob);
+  GroupDev& d = g.dev;
+  d.B = B;
+  d.envBase = envBase;
+  d.pos = reinterpret_cast<float*>(b + oPos);
+  d.rot = reinterpret_cast<float*>(b + oRot);
+  d.goal = reinterpret_cast<float*>(b + oGoal);
+  d.navPos = reinterpret_cast<float*>(b + oNavPos);
+  d.navGoal = reinterpret_cast<float*>(b + oNavGoal);
+  d.prevPos = reinterpret_cast<float*>(b + oPrevPos);
+  d.prevDist = reinterpret_cast<float*>(b + oPrevDist);
+  d.cumTravel = reinterpret_cast<float*>(b + oCum);
+  d.initDist = reinterpret_cast<float*>(b + oInit);
+  d.tmpDist = reinterpret_cast<float*>(b + oTmp);
+  d.navRef = reinterpret_cast<uint32_t*>(b + oNavRef);
+  d.goalRef = reinterpret_cast<uint32_t*>(b + oGoalRef);
+  d.step = reinterpret_cast<uint32_t*>(b + oStep);
+  d.episode = reinterpret_cast<uint32_t*>(b + oEpisode);
+  d.resetCount = reinterpret_cast<uint32_t*>(b + oResetCount);
+  d.status = reinterpret_cast<uint32_t*>(b + oStatus);
+  d.scene = reinterpret_cast<uint32_t*>(b + oScene);
+  d.flags = reinterpret_cast<uint32_t*>(b + oFlags);
+  d.reward = reinterpret_cast<float*>(b + oReward);
+  d.mask = reinterpret_cast<uint8_t*>(b + oMask);
+  d.info = reinterpret_cast<float*>(b + oInfo);
+  d.polar = reinterpret_cast<float*>(b + oPolar);
+  d.geoList = reinterpret_cast<uint32_t*>(b + oGeoList);
+  d.resetList = reinterpret_cast<uint32_t*>(b + oResetList);
+  d.counts = reinterpret_cast<uint32_t*>(b + oCounts);
+
+  auto setField = [&](int id, void* p, size_t bytes) {
+    g.fieldPtr[id] = p;
+    g.fieldBytes[id] = bytes;
+  };
+  setField(BPSN_FIELD_REWARD, d.reward, B * f);
+  setField(BPSN_FIELD_MASK, d.mask, B);
+  setField(BPSN_FIELD_INFO, d.info, 3 * B * f);
+  setField(BPSN_FIELD_POLAR, d.polar, 2 * B * f);
+  setField(BPSN_FIELD_POSITION, d.pos, 3 * B * f);
+  setField(BPSN_FIELD_ROTATION, d.rot, 4 * B * f);
+  setField(BPSN_FIELD_GOAL, d.goal, 3 * B * f);
+  setField(BPSN_FIELD_NAV_POSITION, d.navPos, 3 * B * f);
+  setField(BPSN_FIELD_NAV_POLY, d.navRef, B * u);
+  setField(BPSN_FIELD_GOAL_POLY, d.goalRef, B * u);
+  setField(BPSN_FIELD_STEP, d.step, B * u);
+  setField(BPSN_FIELD_EPISODE, d.episode, B * u);
+  setField(BPSN_FIELD_RESET_COUNT, d.resetCount, B * u);
+  setField(BPSN_FIELD_STATUS, d.status, B * u);
+  setField(BPSN_FIELD_PREV_DIST, d.prevDist, B * f);
+  setField(BPSN_FIELD_CUM_TRAVEL, d.cumTravel, B * f);
+  setField(BPSN_FIELD_INIT_DIST, d.initDist, B * f);
+  setField(BPSN_FIELD_SCENE, d.scene, B * u);
+
+  BPSN_CUDA(sim, cudaMalloc(&g.scratch, sizeof(AStarScratch) * static_cast<size_t>(B)));
+  BPSN_CUDA(sim, cudaMalloc(&g.dActions, sizeof(int64_t) * B));
+  BPSN_CUDA(sim, cudaMallocHost(&g.hActions, sizeof(int64_t) * B));
+  if (sim->cfg.flags & BPSN_FLAG_HOST_MIRRORS) {
+    BPSN_CUDA(sim, cudaMallocHost(&g.hReward, B * f));
+    BPSN_CUDA(sim, cudaMallocHost(&g.hMask, B));
+    BPSN_CUDA(sim, cudaMallocHost(&g.hInfo, 3 * B * f));
+    BPSN_CUDA(sim, cudaMallocHost(&g.hPolar, 2 * B * f));
+    memset(g.hReward, 0, B * f);
+    memset(g.hMask, 0, B);
+    memset(g.hInfo, 0, 3 * B * f);
+    memset(g.hPolar, 0, 2 * B * f);
+  }
+  BPSN_CUDA(sim, cudaEventCreateWithFlags(&g.done, cudaEventDisableTiming));
+  return BPSN_OK;
+}
+
+// D2H of the result arrays + completion event
+int32_t finishLaunch(bpsn_sim* sim, Group& g, cudaStream_t s, bool polarOnly) {
+  if (sim->cfg.flags & BPSN_FLAG_HOST_MIRRORS) {
+    const uint32_t B = g.dev.B;
+    if (!polarOnly) {
+      BPSN_CUDA(sim, cudaMemcpyAsync(g.hReward, g.dev.reward, B * sizeof(float),
+                                     cudaMemcpyDeviceToHost, s));
+      BPSN_CUDA(sim, cudaMemcpyAsync(g.hMask, g.dev.mask, B, cudaMemcpyDeviceToHost, s));
+      BPSN_CUDA(sim, cudaMemcpyAsync(g.hInfo, g.dev.info, 3 * B * sizeof(float),
+                                     cudaMemcpyDeviceToHost, s));
+    }
+    BPSN_CUDA(sim, cudaMemcpyAsync(g.hPolar, g.dev.polar, 2 * B * sizeof(float),
+                                   cudaMemcpyDeviceToHost, s));
+  }
+  BPSN_CUDA(sim, cudaEventRecord(g.done, s));
+  return BPSN_OK;
+}
+
+inline uint32_t blocksFor(uint32_t n, uint32_t bs) {
+  return (n + bs - 1) / bs;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* bpsn_version(void) {
+  return "bpsn 0.1 sm_100a";
+}
+
+const char* bpsn_last_error(const bpsn_sim* sim) {
+  if (sim)
+    return sim->lastError.c_str();
+  return g_lastError.c_str();
+}
+
+int32_t bpsn_create(const bpsn_config* cfg, bpsn_sim** out) {
+  if (!cfg || !out)
+    return fail(nullptr, BPSN_ERR_INVALID_ARG, "bpsn_create: null argument");
+  *out = nullptr;
+  if (cfg->num_envs == 0 || cfg->num_scenes == 0 || cfg->num_groups == 0 || cfg->num_groups > 2)
+    return fail(nullptr, BPSN_ERR_INVALID_ARG,
+                "bpsn_create: num_envs, num_scenes must be > 0 and num_groups 1 or 2");
+  // the reference aborts on these (simulator/simulator.cpp:1503-1508, 1536-1538)
+  if (cfg->num_envs % cfg->num_scenes != 0)
+    return fail(nullptr, BPSN_ERR_INVALID_ARG,
+                "Num environments is not a multiple of the number of active scenes");
+  if (cfg->num_envs % cfg->num_groups != 0 || cfg->num_scenes % cfg->num_groups != 0)
+    return fail(nullptr, BPSN_ERR_INVALID_ARG,
+                "num_envs and num_scenes must be multiples of num_groups");
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0)
+    return fail(nullptr, BPSN_ERR_NO_DEVICE, "bpsn_create: no CUDA device available");
+  if (cfg->gpu_id < 0 || cfg->gpu_id >= ndev)
+    return fail(nullptr, BPSN_ERR_INVALID_ARG, "bpsn_create: gpu_id out of range");
+  bpsn_sim* sim = new bpsn_sim();
+  sim->cfg = *cfg;
+  sim->scenes.resize(cfg->num_scenes);
+  sim->envScene.resize(cfg->num_envs);
+  const uint32_t perScene = cfg->num_envs / cfg->num_scenes;
+  for (uint32_t e = 0; e < cfg->num_envs; ++e)
+    sim->envScene[e] = e / perScene;
+  // glm::angleAxis(radians(+/-10), +Y) = (sin(a/2) * axis, cos(a/2)), on the
+  // host libm as the reference does at static-init time (simulator.cpp:52-60)
+  const float a = 10.f * 0.01745329251994329576923690768489f;
+  const float sl = sinf(a * 0.5f), cl = cosf(a * 0.5f);
+  const float na = -a;
+  const float sr = sinf(na * 0.5f), cr = cosf(na * 0.5f);
+  sim->turn = TurnConsts{0.f * sl, 1.f * sl, 0.f * sl, cl, 0.f * sr, 1.f * sr, 0.f * sr, cr};
+  *out = sim;
+  return BPSN_OK;
+}
+
+int32_t bpsn_destroy(bpsn_sim* sim) {
+  if (!sim)
+    return BPSN_OK;
+  cudaSetDevice(sim->cfg.gpu_id);
+  cudaDeviceSynchronize();
+  for (auto& g : sim->groups) {
+    cudaFree(g.stateBlob);
+    cudaFree(g.scratch);
+    cudaFree(g.dActions);
+    cudaFreeHost(g.hActions);
+    cudaFreeHost(g.hReward);
+    cudaFreeHost(g.hMask);
+    cudaFreeHost(g.hInfo);
+    cudaFreeHost(g.hPolar);
+    if (g.done)
+      cudaEventDestroy(g.done);
+    for (cudaEvent_t ev : g.prof)
+      if (ev)
+        cudaEventDestroy(ev);
+  }
+  for (auto& s : sim->scenes)
+    cudaFree(s.blob);
+  cudaFree(sim->dScenes);
+  cudaFree(sim->dEpisodes);
+  cudaFree(sim->dEpOffset);
+  cudaFree(sim->dEpCount);
+  cudaFree(sim->queryScratch);
+  delete sim;
+  return BPSN_OK;
+}
+
+int32_t bpsn_set_navmesh_blob(bpsn_sim* sim, uint32_t scene, const void* data, size_t size) {
+  if (!sim || !data)
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_set_navmesh_blob: null argument");
+  if (sim->finalized)
+    return fail(sim, BPSN_ERR_STATE, "bpsn_set_navmesh_blob: already finalized");
+  if (scene >= sim->scenes.size())
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_set_navmesh_blob: scene index out of range");
+  HostScene hs;
+  std::string err = parseNavmesh(data, size, &hs);
+  if (!err.empty())
+    return fail(sim, BPSN_ERR_BAD_NAVMESH, err);
+  sim->scenes[scene].host = std::move(hs);
+  sim->scenes[scene].loaded = true;
+  return BPSN_OK;
+}
+
+int32_t bpsn_set_navmesh_file(bpsn_sim* sim, uint32_t scene, const char* path) {
+  if (!sim || !path)
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_set_navmesh_file: null argument");
+  FILE* fp = fopen(path, "rb");
+  if (!fp)
+    return fail(sim, BPSN_ERR_IO, std::string("Failed to load navmesh: ") + path);
+  std::vector<uint8_t> buf;
+  fseek(fp, 0, SEEK_END);
+  long n = ftell(fp);
+  fseek(fp, 0, SEEK_SET);
+  if (n < 0) {
+    fclose(fp);
+    return fail(sim, BPSN_ERR_IO, std::string("Failed to load navmesh: ") + path);
+  }
+  buf.resize(static_cast<size_t>(n));
+  size_t got = n ? fread(buf.data(), 1, buf.size(), fp) : 0;
+  fclose(fp);
+  if (got != buf.size())
+    return fail(sim, BPSN_ERR_IO, std::string("Failed to load navmesh: ") + path);
+  return bpsn_set_navmesh_blob(sim, scene, buf.data(), buf.size());
+}
+
+int32_t bpsn_set_episodes(bpsn_sim* sim, uint32_t scene, const bpsn_episode* episodes,
+                          uint32_t count) {
+  if (!sim || !episodes || count == 0)
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_set_episodes: null or empty episode list");
+  if (sim->finalized)
+    return fail(sim, BPSN_ERR_STATE, "bpsn_set_episodes: already finalized");
+  if (scene >= sim->scenes.size())
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_set_episodes: scene index out of range");
+  sim->scenes[scene].episodes.assign(episodes, episodes + count);
+  return BPSN_OK;
+}
+
+int32_t bpsn_set_env_scenes(bpsn_sim* sim, const uint32_t* env_scene, uint32_t count) {
+  if (!sim || !env_scene)
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_set_env_scenes: null argument");
+  if (sim->finalized)
+    return fail(sim, BPSN_ERR_STATE, "bpsn_set_env_scenes: already finalized");
+  if (count != sim->cfg.num_envs)
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_set_env_scenes: count != num_envs");
+  for (uint32_t e = 0; e < count; ++e)
+    if (env_scene[e] >= sim->cfg.num_scenes)
+      return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_set_env_scenes: scene index out of range");
+  sim->envScene.assign(env_scene, env_scene + count);
+  return BPSN_OK;
+}
+
+int32_t bpsn_finalize(bpsn_sim* sim) {
+  if (!sim)
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_finalize: null handle");
+  if (sim->finalized)
+    return fail(sim, BPSN_ERR_STATE, "bpsn_finalize: already finalized");
+  for (size_t i = 0; i < sim->scenes.size(); ++i) {
+    if (!sim->scenes[i].loaded)
+      return fail(sim, BPSN_ERR_STATE, "bpsn_finalize: scene " + std::to_string(i) + " has no navmesh");
+    if (sim->scenes[i].episodes.empty())
+      return fail(sim, BPSN_ERR_STATE, "bpsn_finalize: scene " + std::to_string(i) + " has no episodes");
+  }
+  BPSN_CUDA(sim, cudaSetDevice(sim->cfg.gpu_id));
+  const uint32_t ns = sim->cfg.num_scenes;
+  std::vector<NavScene> table(ns);
+  std::vector<uint32_t> epOff(ns), epCnt(ns);
+  std::vector<float> eps;
+  for (uint32_t i = 0; i < ns; ++i) {
+    int32_t rc = uploadScene(sim, sim->scenes[i]);
+    if (rc)
+      return rc;
+    table[i] = sim->scenes[i].dev;
+    epOff[i] = static_cast<uint32_t>(eps.size() / 10);
+    epCnt[i] = static_cast<uint32_t>(sim->scenes[i].episodes.size());
+    for (const bpsn_episode& ep : sim->scenes[i].episodes) {
+      eps.insert(eps.end(), ep.start_position, ep.start_position + 3);
+      eps.insert(eps.end(), ep.start_rotation, ep.start_rotation + 4);
+      eps.insert(eps.end(), ep.goal, ep.goal + 3);
+    }
+  }
+  BPSN_CUDA(sim, cudaMalloc(&sim->dScenes, sizeof(NavScene) * ns));
+  BPSN_CUDA(sim, cudaMemcpy(sim->dScenes, table.data(), sizeof(NavScene) * ns,
+                            cudaMemcpyHostToDevice));
+  BPSN_CUDA(sim, cudaMalloc(&sim->dEpisodes, sizeof(float) * eps.size()));
+  BPSN_CUDA(sim, cudaMemcpy(sim->dEpisodes, eps.data(), sizeof(float) * eps.size(),
+                            cudaMemcpyHostToDevice));
+  BPSN_CUDA(sim, cudaMalloc(&sim->dEpOffset, sizeof(uint32_t) * ns));
+  BPSN_CUDA(sim, cudaMemcpy(sim->dEpOffset, epOff.data(), sizeof(uint32_t) * ns,
+                            cudaMemcpyHostToDevice));
+  BPSN_CUDA(sim, cudaMalloc(&sim->dEpCount, sizeof(uint32_t) * ns));
+  BPSN_CUDA(sim, cudaMemcpy(sim->dEpCount, epCnt.data(), sizeof(uint32_t) * ns,
+                            cudaMemcpyHostToDevice));
+  sim->table.scenes = sim->dScenes;
+  sim->table.episodes = sim->dEpisodes;
+  sim->table.epOffset = sim->dEpOffset;
+  sim->table.epCount = sim->dEpCount;
+
+  const uint32_t ng = sim->cfg.num_groups;
+  const uint32_t B = sim->cfg.num_envs / ng;
+  sim->groups.resize(ng);
+  for (uint32_t gi = 0; gi < ng; ++gi) {
+    int32_t rc = allocGroup(sim, sim->groups[gi], B, gi * B);
+    if (rc)
+      return rc;
+    BPSN_CUDA(sim, cudaMemcpy(sim->groups[gi].dev.scene, sim->envScene.data() + gi * B,
+                              sizeof(uint32_t) * B, cudaMemcpyHostToDevice));
+  }
+  sim->querySlots = 16384;
+  BPSN_CUDA(sim, cudaMalloc(&sim->queryScratch, sizeof(AStarScratch) * sim->querySlots));
+  sim->finalized = true;
+  return BPSN_OK;
+}
+
+int32_t bpsn_reset(bpsn_sim* sim, uint32_t group, void* stream) {
+  if (!sim || !sim->finalized)
+    return fail(sim, BPSN_ERR_STATE, "bpsn_reset: handle not finalized");
+  if (group >= sim->groups.size())
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_reset: group out of range");
+  Group& g = sim->groups[group];
+  if (g.inFlight)
+    return fail(sim, BPSN_ERR_STATE, "Not done with previous simulation");
+  BPSN_CUDA(sim, cudaSetDevice(sim->cfg.gpu_id));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const uint32_t B = g.dev.B;
+  k_reset<<<blocksFor(B, 128), 128, 0, s>>>(g.dev, sim->table,
+                                            static_cast<uint32_t>(sim->cfg.seed),
+                                            static_cast<uint32_t>(sim->cfg.seed >> 32), nullptr,
+                                            nullptr);
+  k_geo<<<blocksFor(B, 128), 128, 0, s>>>(g.dev, sim->table, g.scratch, nullptr, nullptr, 1);
+  BPSN_CUDA(sim, cudaGetLastError());
+  int32_t rc = finishLaunch(sim, g, s, /*polarOnly=*/true);
+  if (rc)
+    return rc;
+  if (sim->cfg.flags & BPSN_FLAG_HOST_MIRRORS)
+    BPSN_CUDA(sim, cudaEventSynchronize(g.done));
+  return BPSN_OK;
+}
+
+int32_t bpsn_step_start(bpsn_sim* sim, uint32_t group, const int64_t* actions,
+                        int32_t actions_mem, void* stream) {
+  if (!sim || !sim->finalized)
+    return fail(sim, BPSN_ERR_STATE, "bpsn_step_start: handle not finalized");
+  if (group >= sim->groups.size())
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_step_start: group out of range");
+  if (!actions)
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_step_start: null actions");
+  Group& g = sim->groups[group];
+  if (g.inFlight)
+    return fail(sim, BPSN_ERR_STATE, "Not done with previous simulation");
+  BPSN_CUDA(sim, cudaSetDevice(sim->cfg.gpu_id));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const uint32_t B = g.dev.B;
+  const int64_t* dAct = actions;
+  if (actions_mem == BPSN_MEM_HOST) {
+    for (uint32_t i = 0; i < B; ++i) {
+      const int64_t a = actions[i];
+      if (a < 0 || a > 3)
+        return fail(sim, BPSN_ERR_BAD_ACTION, "Unknown action: " + std::to_string(a));
+      g.hActions[i] = a;
+    }
+    BPSN_CUDA(sim, cudaMemcpyAsync(g.dActions, g.hActions, sizeof(int64_t) * B,
+                                   cudaMemcpyHostToDevice, s));
+    dAct = g.dActions;
+  } else if (actions_mem != BPSN_MEM_DEVICE) {
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_step_start: actions_mem must be host or device");
+  }
+  BPSN_CUDA(sim, cudaMemsetAsync(g.dev.counts, 0, 4 * sizeof(uint32_t), s));
+  const bool prof = g.profiling;
+  if (prof) cudaEventRecord(g.prof[0], s);
+  k_move<<<blocksFor(B, 128), 128, 0, s>>>(g.dev, sim->table, dAct, sim->turn);
+  if (prof) cudaEventRecord(g.prof[1], s);
+  k_geo<<<blocksFor(B, 128), 128, 0, s>>>(g.dev, sim->table, g.scratch, g.dev.geoList,
+                                          g.dev.counts + 0, 0);
+  if (prof) cudaEventRecord(g.prof[2], s);
+  k_finish<<<blocksFor(B, 256), 256, 0, s>>>(g.dev);
+  if (prof) cudaEventRecord(g.prof[3], s);
+  k_reset<<<blocksFor(B, 128), 128, 0, s>>>(g.dev, sim->table,
+                                            static_cast<uint32_t>(sim->cfg.seed),
+                                            static_cast<uint32_t>(sim->cfg.seed >> 32),
+                                            g.dev.resetList, g.dev.counts + 1);
+  if (prof) cudaEventRecord(g.prof[4], s);
+  k_geo<<<blocksFor(B, 128), 128, 0, s>>>(g.dev, sim->table, g.scratch, g.dev.resetList,
+                                          g.dev.counts + 1, 1);
+  if (prof) cudaEventRecord(g.prof[5], s);
+  BPSN_CUDA(sim, cudaGetLastError());
+  int32_t rc = finishLaunch(sim, g, s, /*polarOnly=*/false);
+  if (rc)
+    return rc;
+  g.inFlight = true;
+  return BPSN_OK;
+}
+
+int32_t bpsn_step_end(bpsn_sim* sim, uint32_t group) {
+  if (!sim || !sim->finalized)
+    return fail(sim, BPSN_ERR_STATE, "bpsn_step_end: handle not finalized");
+  if (group >= sim->groups.size())
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_step_end: group out of range");
+  Group& g = sim->groups[group];
+  if (!g.inFlight)
+    return fail(sim, BPSN_ERR_STATE, "Simulation already done");
+  g.inFlight = false;
+  if (sim->cfg.flags & BPSN_FLAG_HOST_MIRRORS)
+    BPSN_CUDA(sim, cudaEventSynchronize(g.done));
+  if (g.profiling) {
+    BPSN_CUDA(sim, cudaEventSynchronize(g.prof[5]));
+    for (int k = 0; k < 5; ++k) {
+      float ms = 0.f;
+      BPSN_CUDA(sim, cudaEventElapsedTime(&ms, g.prof[k], g.prof[k + 1]));
+      g.profMs[k] += ms;
+    }
+    g.profSteps++;
+  }
+  return BPSN_OK;
+}
+
+int32_t bpsn_profile_enable(bpsn_sim* sim, uint32_t group, int32_t enable) {
+  if (!sim || !sim->finalized)
+    return fail(sim, BPSN_ERR_STATE, "bpsn_profile_enable: handle not finalized");
+  if (group >= sim->groups.size())
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_profile_enable: group out of range");
+  Group& g = sim->groups[group];
+  if (g.inFlight)
+    return fail(sim, BPSN_ERR_STATE, "bpsn_profile_enable: a step is in flight");
+  BPSN_CUDA(sim, cudaSetDevice(sim->cfg.gpu_id));
+  if (enable && !g.prof[0])
+    for (cudaEvent_t& ev : g.prof)
+      BPSN_CUDA(sim, cudaEventCreate(&ev));
+  g.profiling = enable != 0;
+  for (double& v : g.profMs)
+    v = 0;
+  g.profSteps = 0;
+  return BPSN_OK;
+}
+
+int32_t bpsn_profile_read(bpsn_sim* sim, uint32_t group, double* ms5, uint64_t* steps) {
+  if (!sim || !sim->finalized || group >= sim->groups.size() || !ms5)
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_profile_read: bad argument");
+  Group& g = sim->groups[group];
+  for (int k = 0; k < 5; ++k)
+    ms5[k] = g.profMs[k];
+  if (steps)
+    *steps = g.profSteps;
+  return BPSN_OK;
+}
+
+int32_t bpsn_get_ptr(bpsn_sim* sim, uint32_t group, int32_t field, int32_t mem, void** ptr,
+                     size_t* bytes) {
+  if (!sim || !sim->finalized)
+    return fail(sim, BPSN_ERR_STATE, "bpsn_get_ptr: handle not finalized");
+  if (group >= sim->groups.size() || field < 0 || field >= BPSN_FIELD_COUNT || !ptr)
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_get_ptr: bad group, field or null output");
+  Group& g = sim->groups[group];
+  if (mem == BPSN_MEM_DEVICE) {
+    *ptr = g.fieldPtr[field];
+  } else if (mem == BPSN_MEM_HOST) {
+    if (!(sim->cfg.flags & BPSN_FLAG_HOST_MIRRORS))
+      return fail(sim, BPSN_ERR_STATE, "bpsn_get_ptr: host mirrors were not enabled at creation");
+    switch (field) {
+      case BPSN_FIELD_REWARD: *ptr = g.hReward; break;
+      case BPSN_FIELD_MASK: *ptr = g.hMask; break;
+      case BPSN_FIELD_INFO: *ptr = g.hInfo; break;
+      case BPSN_FIELD_POLAR: *ptr = g.hPolar; break;
+      default:
+        return fail(sim, BPSN_ERR_INVALID_ARG,
+                    "bpsn_get_ptr: only reward, mask, info and polar have host mirrors");
+    }
+  } else {
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_get_ptr: mem must be host or device");
+  }
+  if (bytes)
+    *bytes = g.fieldBytes[field];
+  return BPSN_OK;
+}
+
+int32_t bpsn_scene_info(bpsn_sim* sim, uint32_t scene, int32_t* num_polys, int32_t* num_disabled,
+                        int32_t* num_islands) {
+  if (!sim || scene >= sim->scenes.size() || !sim->scenes[scene].loaded)
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_scene_info: scene not loaded");
+  const HostScene& h = sim->scenes[scene].host;
+  if (num_polys)
+    *num_polys = static_cast<int32_t>(h.polys.size());
+  if (num_disabled)
+    *num_disabled = h.numDisabled;
+  if (num_islands)
+    *num_islands = h.numIslands;
+  return BPSN_OK;
+}
+
+int32_t bpsn_query_snap(bpsn_sim* sim, uint32_t scene, uint32_t n, const float* points,
+                        float* out_points, uint32_t* out_refs, void* stream) {
+  if (!sim || !sim->finalized)
+    return fail(sim, BPSN_ERR_STATE, "bpsn_query_snap: handle not finalized");
+  if (scene >= sim->scenes.size() || !points || !out_points || !out_refs)
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_query_snap: bad argument");
+  if (n == 0)
+    return BPSN_OK;
+  BPSN_CUDA(sim, cudaSetDevice(sim->cfg.gpu_id));
+  k_query_snap<<<blocksFor(n, 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      sim->dScenes + scene, n, points, out_points, out_refs);
+  BPSN_CUDA(sim, cudaGetLastError());
+  return BPSN_OK;
+}
+
+int32_t bpsn_query_try_step(bpsn_sim* sim, uint32_t scene, uint32_t n, const float* start,
+                            const uint32_t* start_refs, const float* end, float* out_points,
+                            uint32_t* out_refs, void* stream) {
+  if (!sim || !sim->finalized)
+    return fail(sim, BPSN_ERR_STATE, "bpsn_query_try_step: handle not finalized");
+  if (scene >= sim->scenes.size() || !start || !start_refs || !end || !out_points || !out_refs)
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_query_try_step: bad argument");
+  if (n == 0)
+    return BPSN_OK;
+  BPSN_CUDA(sim, cudaSetDevice(sim->cfg.gpu_id));
+  k_query_try_step<<<blocksFor(n, 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      sim->dScenes + scene, n, start, start_refs, end, out_points, out_refs);
+  BPSN_CUDA(sim, cudaGetLastError());
+  return BPSN_OK;
+}
+
+int32_t bpsn_query_geodesic(bpsn_sim* sim, uint32_t scene, uint32_t n, const float* start,
+                            const uint32_t* start_refs, const float* end,
+                            const uint32_t* end_refs, float* out_dist, uint32_t* out_status,
+                            void* stream) {
+  if (!sim || !sim->finalized)
+    return fail(sim, BPSN_ERR_STATE, "bpsn_query_geodesic: handle not finalized");
+  if (scene >= sim->scenes.size() || !start || !start_refs || !end || !end_refs || !out_dist)
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_query_geodesic: bad argument");
+  if (n == 0)
+    return BPSN_OK;
+  BPSN_CUDA(sim, cudaSetDevice(sim->cfg.gpu_id));
+  const uint32_t slots = n < sim->querySlots ? n : sim->querySlots;
+  k_query_geodesic<<<blocksFor(slots, 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      sim->dScenes + scene, sim->queryScratch, slots, n, start, start_refs, end, end_refs,
+      out_dist, out_status);
+  BPSN_CUDA(sim, cudaGetLastError());
+  return BPSN_OK;
+}
+
+size_t bpsn_gae_workspace_bytes(uint32_t N) {
+  return sizeof(GaeStat) * (static_cast<size_t>(blocksFor(N, kGaeBlock)) + 1);
+}
+
+int32_t bpsn_gae(const float* rewards, float* values, const uint8_t* masks,
+                 const float* next_value, float* returns, float* advantages, uint32_t T,
+                 uint32_t N, double gamma, double tau, int32_t normalize, float eps,
+                 void* workspace, void* stream) {
+  if (!rewards || !values || !masks || !returns)
+    return fail(nullptr, BPSN_ERR_INVALID_ARG, "bpsn_gae: null tensor");
+  if (T == 0 || N == 0)
+    return fail(nullptr, BPSN_ERR_INVALID_ARG, "bpsn_gae: T and N must be positive");
+  if (normalize && (!advantages || !workspace))
+    return fail(nullptr, BPSN_ERR_INVALID_ARG,
+                "bpsn_gae: normalisation needs the advantages output and a workspace");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const uint32_t blocks = blocksFor(N, kGaeBlock);
+  GaeStat* partials = normalize ? static_cast<GaeStat*>(workspace) : nullptr;
+  k_gae_scan<<<blocks, kGaeBlock, 0, s>>>(rewards, values, masks, next_value, returns, advantages,
+                                          T, N, static_cast<float>(gamma),
+                                          static_cast<float>(gamma * tau), partials);
+  if (normalize) {
+    const size_t total = static_cast<size_t>(T) * N;
+    uint32_t nb = static_cast<uint32_t>((total + 256 * 4 - 1) / (256 * 4));
+    if (nb > 148 * 8)
+      nb = 148 * 8;
+    if (nb == 0)
+      nb = 1;
+    k_gae_normalize<<<nb, 256, 0, s>>>(advantages, total, partials, blocks, eps);
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess)
+    return fail(nullptr, BPSN_ERR_CUDA, std::string("bpsn_gae launch: ") + cudaGetErrorString(e));
+  return BPSN_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,143 @@
+// Rollout returns: generalised advantage estimation as one reverse scan per
+// environment column, fused with the advantage (returns - values) and the
+// statistics for whole-batch normalisation.
+//
+// Follows RolloutStorage.compute_returns (bps_nav/common/rollout_storage.py:
+// 203-219) and PPO.get_advantages (bps_nav/rl/ppo/ppo.py:190-201).  The float
+// expression tree is the one PyTorch evaluates for those lines, each op
+// rounded to fp32 on its own (compile without FMA contraction):
+//     delta = (r[t] + (gamma * v[t+1]) * m[t+1]) - v[t]
+//     gae   = delta + ((gamma*tau) * gae) * m[t+1]      gamma*tau folded in double
+//     ret   = gae + v[t]
+//     adv   = ret - v[t]
+// Normalisation: (adv - mean) / (std + eps), std unbiased over T*N elements;
+// mean and M2 are accumulated per thread in double (Welford) and merged with
+// Chan's pairwise formula, so the statistics are at least as accurate as the
+// fp32 reductions of the reference.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace bpsn {
+
+struct GaeStat {  // running (count, mean, M2)
+  double n;
+  double mean;
+  double m2;
+};
+
+__device__ __forceinline__ GaeStat gaeMerge(const GaeStat& a, const GaeStat& b) {
+  if (b.n == 0.0)
+    return a;
+  if (a.n == 0.0)
+    return b;
+  GaeStat r;
+  r.n = a.n + b.n;
+  const double delta = b.mean - a.mean;
+  r.mean = a.mean + delta * (b.n / r.n);
+  r.m2 = a.m2 + b.m2 + delta * delta * (a.n * b.n / r.n);
+  return r;
+}
+
+__device__ __forceinline__ GaeStat gaeWarpReduce(GaeStat s) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    GaeStat o;
+    o.n = __shfl_down_sync(0xffffffffu, s.n, off);
+    o.mean = __shfl_down_sync(0xffffffffu, s.mean, off);
+    o.m2 = __shfl_down_sync(0xffffffffu, s.m2, off);
+    s = gaeMerge(s, o);
+  }
+  return s;
+}
+
+constexpr int kGaeBlock = 128;
+
+// One thread per environment column.  partials[blockIdx.x] receives the
+// block's advantage statistics when `partials` is non-null.
+__global__ void __launch_bounds__(kGaeBlock)
+k_gae_scan(const float* __restrict__ rewards, float* __restrict__ values,
+           const uint8_t* __restrict__ masks, const float* __restrict__ nextValue,
+           float* __restrict__ returns, float* __restrict__ adv, uint32_t T, uint32_t N,
+           float gamma, float gammaTau, GaeStat* __restrict__ partials) {
+  const uint32_t n = blockIdx.x * blockDim.x + threadIdx.x;
+  GaeStat st;
+  st.n = 0.0;
+  st.mean = 0.0;
+  st.m2 = 0.0;
+  if (n < N) {
+    float vnext;
+    if (nextValue) {
+      vnext = nextValue[n];
+      values[static_cast<size_t>(T) * N + n] = vnext;
+    } else {
+      vnext = values[static_cast<size_t>(T) * N + n];
+    }
+    float gae = 0.f;
+    for (int t = static_cast<int>(T) - 1; t >= 0; --t) {
+      const size_t i = static_cast<size_t>(t) * N + n;
+      const float m = masks[i + N] ? 1.f : 0.f;
+      const float v = values[i];
+      const float r = rewards[i];
+      const float delta = (r + (gamma * vnext) * m) - v;
+      gae = delta + (gammaTau * gae) * m;
+      const float ret = gae + v;
+      returns[i] = ret;
+      if (adv) {
+        const float a = ret - v;
+        adv[i] = a;
+        st.n += 1.0;
+        const double d = static_cast<double>(a) - st.mean;
+        st.mean += d / st.n;
+        st.m2 += d * (static_cast<double>(a) - st.mean);
+      }
+      vnext = v;
+    }
+  }
+  if (partials) {
+    __shared__ GaeStat sh[kGaeBlock / 32];
+    st = gaeWarpReduce(st);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0)
+      sh[warp] = st;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      GaeStat acc = sh[0];
+      for (int w = 1; w < kGaeBlock / 32; ++w)
+        acc = gaeMerge(acc, sh[w]);
+      partials[blockIdx.x] = acc;
+    }
+  }
+}
+
+// Every block merges the (few) partials itself, then normalises its slice.
+__global__ void __launch_bounds__(256)
+k_gae_normalize(float* __restrict__ adv, size_t total, const GaeStat* __restrict__ partials,
+                uint32_t numPartials, float eps) {
+  __shared__ float sMean, sInv;
+  if (threadIdx.x < 32) {
+    GaeStat st;
+    st.n = 0.0;
+    st.mean = 0.0;
+    st.m2 = 0.0;
+    for (uint32_t i = threadIdx.x; i < numPartials; i += 32)
+      st = gaeMerge(st, partials[i]);
+    st = gaeWarpReduce(st);
+    if (threadIdx.x == 0) {
+      const double var = st.n > 1.0 ? st.m2 / (st.n - 1.0) : __longlong_as_double(0x7ff8000000000000ll);
+      const float mean = static_cast<float>(st.mean);
+      const float sd = static_cast<float>(sqrt(var));
+      sMean = mean;
+      sInv = sd + eps;
+    }
+  }
+  __syncthreads();
+  const float mean = sMean, denom = sInv;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += stride)
+    adv[i] = (adv[i] - mean) / denom;
+}
+
+}  // namespace bpsn

@@ -10,6 +10,7 @@
 // neis[] array and recovers neighbour order by scanning edges 0..n-1.
 #pragma once
 
+#include <stddef.h>
 #include <stdint.h>
 
 #if defined(__CUDACC__)
@@ -107,11 +108,14 @@ struct alignas(8) HeapEntry {
 };
 
 // Per-query scratch slab (global memory; one per resident query slot).
-struct AStarScratch {
+struct alignas(16) AStarScratch {
   AStarNode nodes[kMaxAStarNodes];
-  HeapEntry heap[kMaxAStarNodes + 1];  // reused as the corridor after the search
-  uint16_t first[kHashBuckets];
+  uint16_t first[kHashBuckets];        // hash heads; cleared with 16-byte stores
+  HeapEntry heap[kMaxAStarNodes + 2];  // reused as the corridor after the search
 };
+static_assert(offsetof(AStarScratch, first) % 16 == 0, "hash heads must be 16-byte aligned");
+static_assert(offsetof(AStarScratch, heap) % 16 == 0, "heap must be 16-byte aligned");
+static_assert(sizeof(AStarScratch) % 16 == 0, "scratch slabs must tile with 16-byte alignment");
 
 // Per-query status bits (diagnostics only; they never change an output).
 enum QueryStatus : uint32_t {

@@ -1,0 +1,387 @@
+// Per-environment PointNav state machine as CUDA kernels.
+//
+// One environment step of the reference (BaseSimulator::step followed by the
+// in-loop auto-reset, simulator/simulator.cpp:620-641, 1626-1644) is split
+// into phases so that warps do uniform work:
+//
+//   k_move    every env : action -> turn / forward move (tryStep) -> GPS/compass
+//                         (handleMovement :680-710, updateObservationState :651-677);
+//                         envs that moved or finished are appended to the
+//                         geodesic work list
+//   k_geo     listed    : geodesic distance goal -> agent (InfoFunctor::step :758-790)
+//   k_finish  every env : success / SPL / distance, reward, mask
+//                         (InfoFunctor::step, RewardFunctor::step :808-822);
+//                         finished envs are appended to the reset list
+//   k_reset   listed    : new episode: pose from the episode record, snap start
+//                         and goal, GPS/compass (BaseSimulator::reset :601-618,
+//                         InfoFunctor::reset :744-756)
+//   k_geo     listed    : geodesic agent -> goal = initial distance (:750-752)
+//
+// State is structure-of-arrays per group so that each phase reads and writes
+// coalesced 4-byte columns.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "nav_query.cuh"
+
+namespace bpsn {
+
+struct GroupDev {
+  uint32_t B;        // environments in this group
+  uint32_t envBase;  // global index of the group's first environment
+  // pose / task state, each [B] (vectors are component-major: x[B] y[B] z[B])
+  float* pos;      // [3][B]  position_
+  float* rot;      // [4][B]  rotation_ (x y z w)
+  float* goal;     // [3][B]  goal_
+  float* navPos;   // [3][B]  navmeshPosition_.xyz
+  float* navGoal;  // [3][B]  navmeshGoal_.xyz
+  float* prevPos;  // [3][B]  prev_position_
+  float* prevDist;
+  float* cumTravel;
+  float* initDist;
+  float* tmpDist;  // geodesic result of the current step
+  uint32_t* navRef;
+  uint32_t* goalRef;
+  uint32_t* step;
+  uint32_t* episode;
+  uint32_t* resetCount;
+  uint32_t* status;
+  uint32_t* scene;
+  uint32_t* flags;  // per-step: bit0 done, bit1 moved
+  // outputs
+  float* reward;  // [B]
+  uint8_t* mask;  // [B]
+  float* info;    // [B][3]
+  float* polar;   // [B][2]
+  // work lists
+  uint32_t* geoList;    // [B]
+  uint32_t* resetList;  // [B]
+  uint32_t* counts;     // [0] geodesic queries, [1] resets
+};
+
+struct SceneTable {
+  const NavScene* scenes;
+  const float* episodes;      // 10 floats per record, all scenes concatenated
+  const uint32_t* epOffset;   // [numScenes]
+  const uint32_t* epCount;    // [numScenes]
+};
+
+struct TurnConsts {  // +/-10 degrees about +Y, evaluated once on the host
+  float lx, ly, lz, lw;
+  float rx, ry, rz, rw;
+};
+
+constexpr float kSuccessReward = 2.5f;    // simulator/simulator.cpp:47
+constexpr float kSlackReward = 1e-2f;     // :48
+constexpr float kSuccessDistance = 0.2f;  // :49
+constexpr float kMaxSteps = 500.f;        // :50
+constexpr float kForwardStep = 0.25f;     // :51
+
+// Philox-4x32-10 (Salmon et al., SC'11): the episode-selection stream.
+__device__ __forceinline__ uint32_t philoxFirst(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
+                                                uint32_t k0, uint32_t k1) {
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c0);
+    const uint32_t lo0 = 0xD2511F53u * c0;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2);
+    const uint32_t lo1 = 0xCD9E8D57u * c2;
+    const uint32_t n0 = hi1 ^ c1 ^ k0;
+    const uint32_t n2 = hi0 ^ c3 ^ k1;
+    c0 = n0;
+    c1 = lo1;
+    c2 = n2;
+    c3 = lo0;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  return c0;
+}
+
+// GPS/compass: polar coordinates of the goal in the agent frame.
+__device__ __forceinline__ void writePolar(const GroupDev& g, uint32_t e, float px, float py,
+                                           float pz, float qx, float qy, float qz, float qw,
+                                           float gx, float gy, float gz) {
+  const float qxx = qx * qx, qyy = qy * qy, qzz = qz * qz;
+  const float qxz = qx * qz, qxy = qx * qy, qyz = qy * qz;
+  const float qwx = qw * qx, qwy = qw * qy, qwz = qw * qz;
+  const float m00 = 1.f - 2.f * (qyy + qzz), m01 = 2.f * (qxy + qwz), m02 = 2.f * (qxz - qwy);
+  const float m20 = 2.f * (qxz + qwy), m21 = 2.f * (qyz - qwx), m22 = 1.f - 2.f * (qxx + qyy);
+  const float tx = gx - px, ty = gy - py, tz = gz - pz;
+  const float vx = m00 * tx + m01 * ty + m02 * tz;
+  const float vz = m20 * tx + m21 * ty + m22 * tz;
+  const float ax = -vz, ay = vx;
+  const float rho = sqrtf(ax * ax + ay * ay);
+  const float phi = atan2f(ay, ax);
+  reinterpret_cast<float2*>(g.polar)[e] = make_float2(rho, -phi);
+}
+
+__global__ void __launch_bounds__(128)
+k_move(GroupDev g, SceneTable st, const int64_t* __restrict__ actions, TurnConsts tc) {
+  const uint32_t e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= g.B)
+    return;
+  const uint32_t B = g.B;
+  const int64_t action = actions[e];
+  uint32_t step = g.step[e] + 1;
+  g.step[e] = step;
+  bool done = static_cast<float>(step) >= kMaxSteps;
+  bool moved = false;
+
+  if (action == 0) {
+    done = true;
+  } else {
+    float px = g.pos[e], py = g.pos[B + e], pz = g.pos[2 * B + e];
+    float qx = g.rot[e], qy = g.rot[B + e], qz = g.rot[2 * B + e], qw = g.rot[3 * B + e];
+    if (action == 1) {
+      // delta = rot * (0, 0, -0.25):  v + 2 * (w * (q x v) + q x (q x v))
+      const float vx = 0.f * kForwardStep, vy = 0.f * kForwardStep, vz = -1.f * kForwardStep;
+      const float uvx = qy * vz - vy * qz;
+      const float uvy = qz * vx - vz * qx;
+      const float uvz = qx * vy - vx * qy;
+      const float uuvx = qy * uvz - uvy * qz;
+      const float uuvy = qz * uvx - uvz * qx;
+      const float uuvz = qx * uvy - uvx * qy;
+      float endPos[3];
+      endPos[0] = px + (vx + ((uvx * qw) + uuvx) * 2.f);
+      endPos[1] = py + (vy + ((uvy * qw) + uuvy) * 2.f);
+      endPos[2] = pz + (vz + ((uvz * qw) + uuvz) * 2.f);
+      float np[3] = {g.navPos[e], g.navPos[B + e], g.navPos[2 * B + e]};
+      uint32_t ref = g.navRef[e];
+      const NavScene sc = st.scenes[g.scene[e]];
+      tryStep(sc, np, &ref, endPos);
+      g.navPos[e] = np[0];
+      g.navPos[B + e] = np[1];
+      g.navPos[2 * B + e] = np[2];
+      g.navRef[e] = ref;
+      px = np[0];
+      py = np[1];
+      pz = np[2];
+      g.pos[e] = px;
+      g.pos[B + e] = py;
+      g.pos[2 * B + e] = pz;
+      moved = true;
+    } else if (action == 2 || action == 3) {
+      const float ox = action == 2 ? tc.lx : tc.rx;
+      const float oy = action == 2 ? tc.ly : tc.ry;
+      const float oz = action == 2 ? tc.lz : tc.rz;
+      const float ow = action == 2 ? tc.lw : tc.rw;
+      const float rw = qw * ow - qx * ox - qy * oy - qz * oz;
+      const float rx = qw * ox + qx * ow + qy * oz - qz * oy;
+      const float ry = qw * oy + qy * ow + qz * ox - qx * oz;
+      const float rz = qw * oz + qz * ow + qx * oy - qy * ox;
+      qx = rx;
+      qy = ry;
+      qz = rz;
+      qw = rw;
+      g.rot[e] = qx;
+      g.rot[B + e] = qy;
+      g.rot[2 * B + e] = qz;
+      g.rot[3 * B + e] = qw;
+    } else {
+      // The reference aborts the process here; this implementation flags the
+      // environment and leaves its pose untouched.
+      g.status[e] |= kStatBadAction;
+    }
+    writePolar(g, e, px, py, pz, qx, qy, qz, qw, g.goal[e], g.goal[B + e], g.goal[2 * B + e]);
+  }
+
+  g.flags[e] = (done ? 1u : 0u) | (moved ? 2u : 0u);
+  if (done || moved) {
+    const uint32_t slot = atomicAdd(&g.counts[0], 1u);
+    g.geoList[slot] = e;
+  }
+}
+
+// mode 0: step query  goal -> agent, result to tmpDist
+// mode 1: reset query agent -> goal, result to initDist and prevDist
+__global__ void __launch_bounds__(128)
+k_geo(GroupDev g, SceneTable st, AStarScratch* __restrict__ scratch, const uint32_t* list,
+      const uint32_t* count, int mode) {
+  const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+  const uint32_t n = count ? min(*count, g.B) : g.B;
+  if (t >= n)
+    return;
+  const uint32_t e = list ? list[t] : t;
+  const uint32_t B = g.B;
+  const NavScene sc = st.scenes[g.scene[e]];
+  const float a[3] = {g.navPos[e], g.navPos[B + e], g.navPos[2 * B + e]};
+  const float b[3] = {g.navGoal[e], g.navGoal[B + e], g.navGoal[2 * B + e]};
+  const uint32_t aref = g.navRef[e];
+  const uint32_t bref = g.goalRef[e];
+  uint32_t status = 0;
+  float d;
+  if (mode == 0)
+    d = geodesic(sc, scratch + t, b, bref, a, aref, &status);
+  else
+    d = geodesic(sc, scratch + t, a, aref, b, bref, &status);
+  if (status)
+    g.status[e] |= status;
+  if (mode == 0) {
+    g.tmpDist[e] = d;
+  } else {
+    g.initDist[e] = d;
+    g.prevDist[e] = d;
+  }
+}
+
+__global__ void __launch_bounds__(256) k_finish(GroupDev g) {
+  const uint32_t e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= g.B)
+    return;
+  const uint32_t B = g.B;
+  const uint32_t f = g.flags[e];
+  const bool done = f & 1u;
+  const bool moved = f & 2u;
+  const float prev = g.prevDist[e];
+  float d = 0, success = 0, spl = 0;
+  if (done) {
+    d = g.tmpDist[e];
+    success = d < kSuccessDistance ? 1.f : 0.f;
+    const float init = g.initDist[e];
+    const float cum = g.cumTravel[e];
+    spl = success * init / fmaxf(init, cum);
+  } else if (moved) {
+    d = g.tmpDist[e];
+    const float px = g.pos[e], py = g.pos[B + e], pz = g.pos[2 * B + e];
+    const float dx = px - g.prevPos[e];
+    const float dy = py - g.prevPos[B + e];
+    const float dz = pz - g.prevPos[2 * B + e];
+    g.cumTravel[e] += sqrtf(dx * dx + dy * dy + dz * dz);
+    g.prevDist[e] = d;
+    g.prevPos[e] = px;
+    g.prevPos[B + e] = py;
+    g.prevPos[2 * B + e] = pz;
+  } else {
+    d = prev;
+  }
+  float reward = -kSlackReward;
+  if (done)
+    reward += kSuccessReward * spl;
+  else
+    reward += prev - d;
+  g.reward[e] = reward;
+  g.mask[e] = done ? 0 : 1;
+  g.info[3 * e + 0] = success;
+  g.info[3 * e + 1] = spl;
+  g.info[3 * e + 2] = d;
+  if (done) {
+    const uint32_t slot = atomicAdd(&g.counts[1], 1u);
+    g.resetList[slot] = e;
+  }
+}
+
+__global__ void __launch_bounds__(128)
+k_reset(GroupDev g, SceneTable st, uint32_t seedLo, uint32_t seedHi, const uint32_t* list,
+        const uint32_t* count) {
+  const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+  const uint32_t n = count ? min(*count, g.B) : g.B;
+  if (t >= n)
+    return;
+  const uint32_t e = list ? list[t] : t;
+  const uint32_t B = g.B;
+  const uint32_t sceneIdx = g.scene[e];
+  const NavScene sc = st.scenes[sceneIdx];
+  const uint32_t rc = g.resetCount[e];
+  const uint32_t r = philoxFirst(g.envBase + e, rc, 0u, 0u, seedLo, seedHi);
+  const uint32_t nEp = st.epCount[sceneIdx];
+  const uint32_t idx = __umulhi(r, nEp);
+  g.resetCount[e] = rc + 1;
+  g.episode[e] = idx;
+  g.step[e] = 1;
+  const float* ep = st.episodes + 10 * static_cast<size_t>(st.epOffset[sceneIdx] + idx);
+  const float start[3] = {ep[0], ep[1], ep[2]};
+  const float qx = ep[3], qy = ep[4], qz = ep[5], qw = ep[6];
+  const float goal[3] = {ep[7], ep[8], ep[9]};
+  g.pos[e] = start[0];
+  g.pos[B + e] = start[1];
+  g.pos[2 * B + e] = start[2];
+  g.rot[e] = qx;
+  g.rot[B + e] = qy;
+  g.rot[2 * B + e] = qz;
+  g.rot[3 * B + e] = qw;
+  g.goal[e] = goal[0];
+  g.goal[B + e] = goal[1];
+  g.goal[2 * B + e] = goal[2];
+  float np[3];
+  uint32_t nref;
+  snapPoint(sc, start, np, &nref);
+  g.navPos[e] = np[0];
+  g.navPos[B + e] = np[1];
+  g.navPos[2 * B + e] = np[2];
+  g.navRef[e] = nref;
+  writePolar(g, e, start[0], start[1], start[2], qx, qy, qz, qw, goal[0], goal[1], goal[2]);
+  float ng[3];
+  uint32_t gref;
+  snapPoint(sc, goal, ng, &gref);
+  g.navGoal[e] = ng[0];
+  g.navGoal[B + e] = ng[1];
+  g.navGoal[2 * B + e] = ng[2];
+  g.goalRef[e] = gref;
+  if (nref == 0 || gref == 0)
+    g.status[e] |= kStatSnapFailed;
+  g.cumTravel[e] = 0.f;
+  g.prevPos[e] = start[0];
+  g.prevPos[B + e] = start[1];
+  g.prevPos[2 * B + e] = start[2];
+}
+
+// ------------------------------------------------------------ query kernels
+
+__global__ void __launch_bounds__(128)
+k_query_snap(const NavScene* scene, uint32_t n, const float* __restrict__ pts, float* out,
+             uint32_t* outRef) {
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n)
+    return;
+  const NavScene sc = *scene;
+  const float p[3] = {pts[3 * i], pts[3 * i + 1], pts[3 * i + 2]};
+  float o[3];
+  uint32_t r;
+  snapPoint(sc, p, o, &r);
+  out[3 * i] = o[0];
+  out[3 * i + 1] = o[1];
+  out[3 * i + 2] = o[2];
+  outRef[i] = r;
+}
+
+__global__ void __launch_bounds__(128)
+k_query_try_step(const NavScene* scene, uint32_t n, const float* __restrict__ start,
+                 const uint32_t* __restrict__ startRef, const float* __restrict__ end, float* out,
+                 uint32_t* outRef) {
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n)
+    return;
+  const NavScene sc = *scene;
+  float p[3] = {start[3 * i], start[3 * i + 1], start[3 * i + 2]};
+  const float q[3] = {end[3 * i], end[3 * i + 1], end[3 * i + 2]};
+  uint32_t r = startRef[i];
+  tryStep(sc, p, &r, q);
+  out[3 * i] = p[0];
+  out[3 * i + 1] = p[1];
+  out[3 * i + 2] = p[2];
+  outRef[i] = r;
+}
+
+__global__ void __launch_bounds__(128)
+k_query_geodesic(const NavScene* scene, AStarScratch* __restrict__ scratch, uint32_t nslots,
+                 uint32_t n, const float* __restrict__ start,
+                 const uint32_t* __restrict__ startRef, const float* __restrict__ end,
+                 const uint32_t* __restrict__ endRef, float* out, uint32_t* outStatus) {
+  const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= nslots)
+    return;
+  const NavScene sc = *scene;
+  for (uint32_t i = t; i < n; i += nslots) {
+    const float a[3] = {start[3 * i], start[3 * i + 1], start[3 * i + 2]};
+    const float b[3] = {end[3 * i], end[3 * i + 1], end[3 * i + 2]};
+    uint32_t status = 0;
+    out[i] = geodesic(sc, scratch + t, a, startRef[i], b, endRef[i], &status);
+    if (outStatus)
+      outStatus[i] = status;
+  }
+}
+
+}  // namespace bpsn

@@ -1,0 +1,193 @@
+/*
+ * bpsn -- batch PointGoal-navigation environment step and rollout returns on
+ * one NVIDIA B200 (sm_100a).  Plain C ABI: opaque handle, pointers and sizes
+ * only.  Every entry point returns 0 on success or a BPSN_ERR_* code; none of
+ * them aborts the process or throws.  bpsn_last_error() gives a message for
+ * the most recent failure on a handle (or for handle-less calls, a
+ * thread-local message when called with NULL).
+ *
+ * What each group of entry points replaces in the reference (paths relative
+ * to the bps-nav tree):
+ *
+ *   bpsn_create / bpsn_destroy / bpsn_set_navmesh* / bpsn_set_episodes /
+ *   bpsn_finalize
+ *       RolloutGenerator construction: dataset + navmesh loading, environment
+ *       groups, per-thread PathFinder replicas.
+ *       simulator/simulator.cpp:1463-1617, 1712-1730; PathFinder::loadNavMesh,
+ *       simulator/external/habitat-sim-geodesic/habitat_sim_geodesic/csrc/PathFinder.cpp:330-408
+ *   bpsn_reset
+ *       RolloutGenerator::reset(group)          simulator/simulator.cpp:1377-1380, 601-618
+ *   bpsn_step_start / bpsn_step_end
+ *       RolloutGenerator::stepStart / stepEnd   simulator/simulator.cpp:1382-1399,
+ *       the work loop :1619-1653 and BaseSimulator::step :620-641
+ *   bpsn_get_ptr
+ *       getRewards / getMasks / getInfos / getPolars (zero-copy result views)
+ *                                               simulator/simulator.cpp:1242-1262, 1426-1445
+ *   bpsn_query_snap / bpsn_query_try_step / bpsn_query_geodesic
+ *       PathFinder::snapPoint / tryStep / findPath in batch form
+ *                                               .../csrc/PathFinder.h:99-227
+ *   bpsn_gae
+ *       RolloutStorage.compute_returns          bps_nav/common/rollout_storage.py:203-219
+ *       PPO.get_advantages                      bps_nav/rl/ppo/ppo.py:190-201
+ */
+#ifndef BPSN_H
+#define BPSN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct bpsn_sim bpsn_sim;
+
+enum {
+  BPSN_OK = 0,
+  BPSN_ERR_INVALID_ARG = 1,   /* null pointer, index out of range, bad size */
+  BPSN_ERR_BAD_NAVMESH = 2,   /* navmesh file/blob rejected; see bpsn_last_error */
+  BPSN_ERR_CUDA = 3,          /* a CUDA runtime call failed */
+  BPSN_ERR_STATE = 4,         /* call order violated (e.g. step_start twice) */
+  BPSN_ERR_BAD_ACTION = 5,    /* an action outside {0,1,2,3} */
+  BPSN_ERR_IO = 6,            /* file could not be read */
+  BPSN_ERR_NO_DEVICE = 7      /* no usable CUDA device */
+};
+
+/* Episode record: simulator/simulator.cpp:83-87 (rotation stored x, y, z, w). */
+typedef struct {
+  float start_position[3];
+  float start_rotation[4];
+  float goal[3];
+} bpsn_episode;
+
+typedef struct {
+  int32_t gpu_id;            /* CUDA device ordinal */
+  uint32_t num_envs;         /* environments over all groups */
+  uint32_t num_groups;       /* 1, or 2 for double buffering */
+  uint32_t num_scenes;       /* scenes resident on the device */
+  uint64_t seed;             /* seeds the episode-selection stream */
+  uint32_t flags;            /* BPSN_FLAG_* */
+  uint32_t reserved;
+} bpsn_config;
+
+enum {
+  /* keep pinned host copies of reward/mask/info/polar, refreshed by every
+     step/reset and complete when bpsn_step_end returns (reference behaviour:
+     the result arrays are host memory) */
+  BPSN_FLAG_HOST_MIRRORS = 1u << 0
+};
+
+/* Fields addressable through bpsn_get_ptr.  All arrays are indexed by the
+ * environment's position inside its group. */
+enum {
+  BPSN_FIELD_REWARD = 0,     /* float32 [B]                               */
+  BPSN_FIELD_MASK = 1,       /* uint8   [B]   1 = episode continues       */
+  BPSN_FIELD_INFO = 2,       /* float32 [B,3] success, spl, distanceToGoal*/
+  BPSN_FIELD_POLAR = 3,      /* float32 [B,2] rho, -phi                   */
+  BPSN_FIELD_POSITION = 4,   /* float32 [3,B] x | y | z                   */
+  BPSN_FIELD_ROTATION = 5,   /* float32 [4,B] x | y | z | w               */
+  BPSN_FIELD_GOAL = 6,       /* float32 [3,B]                             */
+  BPSN_FIELD_NAV_POSITION = 7, /* float32 [3,B] position on the navmesh   */
+  BPSN_FIELD_NAV_POLY = 8,   /* uint32  [B]   Detour polygon ref          */
+  BPSN_FIELD_GOAL_POLY = 9,  /* uint32  [B]                               */
+  BPSN_FIELD_STEP = 10,      /* uint32  [B]   step counter (starts at 1)  */
+  BPSN_FIELD_EPISODE = 11,   /* uint32  [B]   index of the current episode*/
+  BPSN_FIELD_RESET_COUNT = 12, /* uint32 [B]  episodes started so far     */
+  BPSN_FIELD_STATUS = 13,    /* uint32  [B]   sticky diagnostic bits      */
+  BPSN_FIELD_PREV_DIST = 14, /* float32 [B]                               */
+  BPSN_FIELD_CUM_TRAVEL = 15,/* float32 [B]                               */
+  BPSN_FIELD_INIT_DIST = 16, /* float32 [B]                               */
+  BPSN_FIELD_SCENE = 17,     /* uint32  [B]   scene index of the env      */
+  BPSN_FIELD_COUNT = 18
+};
+
+enum { BPSN_MEM_DEVICE = 0, BPSN_MEM_HOST = 1 };
+
+int32_t bpsn_create(const bpsn_config* cfg, bpsn_sim** out);
+int32_t bpsn_destroy(bpsn_sim* sim);
+
+/* Scene `scene` <- a `.navmesh` file (MSET container, one Detour tile). */
+int32_t bpsn_set_navmesh_file(bpsn_sim* sim, uint32_t scene, const char* path);
+int32_t bpsn_set_navmesh_blob(bpsn_sim* sim, uint32_t scene, const void* data, size_t size);
+/* Episode list of a scene (copied). */
+int32_t bpsn_set_episodes(bpsn_sim* sim, uint32_t scene, const bpsn_episode* episodes,
+                          uint32_t count);
+/* Optional: explicit scene per environment (default: num_envs / num_scenes
+ * consecutive environments per scene, group-major then scene-major, as in
+ * simulator/simulator.cpp:1205-1221, 1581-1592). */
+int32_t bpsn_set_env_scenes(bpsn_sim* sim, const uint32_t* env_scene, uint32_t count);
+/* Uploads scenes and episodes, allocates state, outputs and query scratch. */
+int32_t bpsn_finalize(bpsn_sim* sim);
+
+/* Starts a fresh episode in every environment of the group.  Asynchronous on
+ * `stream` (a cudaStream_t, NULL = default stream). */
+int32_t bpsn_reset(bpsn_sim* sim, uint32_t group, void* stream);
+
+/* actions: int64 [B], one of {0 stop, 1 forward, 2 left, 3 right}.
+ * actions_mem = BPSN_MEM_HOST: validated, staged and copied by the call;
+ * BPSN_MEM_DEVICE: read by the kernels as is (an out-of-range value sets the
+ * environment's BAD_ACTION status bit and that environment does not move).
+ * The step is enqueued on `stream`; bpsn_step_end waits for it when host
+ * mirrors are enabled and otherwise only closes the start/end pairing. */
+int32_t bpsn_step_start(bpsn_sim* sim, uint32_t group, const int64_t* actions,
+                        int32_t actions_mem, void* stream);
+int32_t bpsn_step_end(bpsn_sim* sim, uint32_t group);
+
+/* Pointer to a per-group array; mem selects device memory or (for the four
+ * result fields, when BPSN_FLAG_HOST_MIRRORS is set) the pinned host copy.
+ * Addresses are stable for the life of the handle. */
+int32_t bpsn_get_ptr(bpsn_sim* sim, uint32_t group, int32_t field, int32_t mem, void** ptr,
+                     size_t* bytes);
+
+/* Per-kernel device timing of the step (no counterpart in the reference; its
+ * Python side times phases with wall clocks, bps_nav/common/utils.py:387-436).
+ * While enabled, bpsn_step_end waits for the step and adds the CUDA-event
+ * duration of each of its five launches, in order: move, geodesic (step),
+ * finish, reset, geodesic (reset), to running totals in milliseconds. */
+int32_t bpsn_profile_enable(bpsn_sim* sim, uint32_t group, int32_t enable);
+int32_t bpsn_profile_read(bpsn_sim* sim, uint32_t group, double* ms5, uint64_t* steps);
+
+/* Number of polygons / disabled polygons / islands of a loaded scene. */
+int32_t bpsn_scene_info(bpsn_sim* sim, uint32_t scene, int32_t* num_polys, int32_t* num_disabled,
+                        int32_t* num_islands);
+
+/* Batched navigation queries on one scene.  All pointers are DEVICE pointers;
+ * positions are float32 [n,3], polygon refs uint32 [n]. */
+int32_t bpsn_query_snap(bpsn_sim* sim, uint32_t scene, uint32_t n, const float* points,
+                        float* out_points, uint32_t* out_refs, void* stream);
+int32_t bpsn_query_try_step(bpsn_sim* sim, uint32_t scene, uint32_t n, const float* start,
+                            const uint32_t* start_refs, const float* end, float* out_points,
+                            uint32_t* out_refs, void* stream);
+int32_t bpsn_query_geodesic(bpsn_sim* sim, uint32_t scene, uint32_t n, const float* start,
+                            const uint32_t* start_refs, const float* end,
+                            const uint32_t* end_refs, float* out_dist, uint32_t* out_status,
+                            void* stream);
+
+/* Generalised advantage estimation over a rollout of T steps and N
+ * environments; every pointer is a DEVICE pointer.
+ *   rewards, values, returns : float32 [T+1, N]   (row-major; trailing 1 dims ok)
+ *   masks                    : uint8/bool [T+1, N], masks[t+1] = not done after step t
+ *   next_value               : float32 [N] or NULL; when given it is stored to
+ *                              values[T] first (compute_returns does the same)
+ *   advantages               : float32 [T, N] or NULL; = returns[:T] - values[:T],
+ *                              then, if normalize != 0, (a - mean) / (std + eps)
+ *                              with the unbiased std over all T*N elements
+ *   gamma, tau               : doubles, because the reference folds gamma*tau in
+ *                              double before rounding to float32
+ *   workspace                : device scratch of at least bpsn_gae_workspace_bytes(N)
+ */
+size_t bpsn_gae_workspace_bytes(uint32_t N);
+int32_t bpsn_gae(const float* rewards, float* values, const uint8_t* masks,
+                 const float* next_value, float* returns, float* advantages, uint32_t T,
+                 uint32_t N, double gamma, double tau, int32_t normalize, float eps,
+                 void* workspace, void* stream);
+
+const char* bpsn_last_error(const bpsn_sim* sim);
+/* Library build identification, e.g. "bpsn sm_100a". */
+const char* bpsn_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* BPSN_H */
