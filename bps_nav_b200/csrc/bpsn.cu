@@ -47,8 +47,8 @@ struct Group {
   bool inFlight = false;
   // optional per-kernel timing (bpsn_profile_enable)
   bool profiling = false;
-  cudaEvent_t prof[6] = {};
-  double profMs[5] = {0, 0, 0, 0, 0};
+  cudaEvent_t prof[4] = {};
+  double profMs[3] = {0, 0, 0};
   uint64_t profSteps = 0;
   // offsets of each field inside stateBlob (for bpsn_get_ptr)
   void* fieldPtr[BPSN_FIELD_COUNT] = {};
@@ -67,6 +67,7 @@ struct bpsn_sim {
   // device tables
   NavScene* dScenes = nullptr;
   float* dEpisodes = nullptr;
+  EpisodeNav* dEpNav = nullptr;
   uint32_t* dEpOffset = nullptr;
   uint32_t* dEpCount = nullptr;
   SceneTable table{};
@@ -156,7 +157,7 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase) {
                oScene = place(B * u), oFlags = place(B * u);
   const size_t oReward = place(B * f), oMask = place(B), oInfo = place(3 * B * f),
                oPolar = place(2 * B * f);
-  const size_t oGeoList = place(B * u), oResetList = place(B * u), oCounts = place(4 * u);
+  const size_t oGeoList = place(B * u), oCounts = place(4 * u);
   g.stateBytes = off;
   BPSN_CUDA(sim, cudaMalloc(&g.stateBlob, off));
   BPSN_CUDA(sim, cudaMemset(g.stateBlob, 0, off));
@@ -187,7 +188,6 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase) {
   d.info = reinterpret_cast<float*>(b + oInfo);
   d.polar = reinterpret_cast<float*>(b + oPolar);
   d.geoList = reinterpret_cast<uint32_t*>(b + oGeoList);
-  d.resetList = reinterpret_cast<uint32_t*>(b + oResetList);
   d.counts = reinterpret_cast<uint32_t*>(b + oCounts);
 
   auto setField = [&](int id, void* p, size_t bytes) {
@@ -327,6 +327,7 @@ int32_t bpsn_destroy(bpsn_sim* sim) {
     cudaFree(s.blob);
   cudaFree(sim->dScenes);
   cudaFree(sim->dEpisodes);
+  cudaFree(sim->dEpNav);
   cudaFree(sim->dEpOffset);
   cudaFree(sim->dEpCount);
   cudaFree(sim->queryScratch);
@@ -439,8 +440,22 @@ int32_t bpsn_finalize(bpsn_sim* sim) {
   BPSN_CUDA(sim, cudaMalloc(&sim->dEpCount, sizeof(uint32_t) * ns));
   BPSN_CUDA(sim, cudaMemcpy(sim->dEpCount, epCnt.data(), sizeof(uint32_t) * ns,
                             cudaMemcpyHostToDevice));
+  sim->querySlots = 16384;
+  BPSN_CUDA(sim, cudaMalloc(&sim->queryScratch, sizeof(AStarScratch) * sim->querySlots));
+  const size_t totalEps = eps.size() / 10;
+  BPSN_CUDA(sim, cudaMalloc(&sim->dEpNav, sizeof(EpisodeNav) * totalEps));
+  for (uint32_t i = 0; i < ns; ++i) {
+    const uint32_t slots = epCnt[i] < sim->querySlots ? epCnt[i] : sim->querySlots;
+    k_episode_table<<<blocksFor(slots, 128), 128>>>(sim->dScenes + i,
+                                                    sim->dEpisodes + 10 * static_cast<size_t>(epOff[i]),
+                                                    epCnt[i], sim->queryScratch, slots,
+                                                    sim->dEpNav + epOff[i]);
+  }
+  BPSN_CUDA(sim, cudaGetLastError());
+  BPSN_CUDA(sim, cudaDeviceSynchronize());
   sim->table.scenes = sim->dScenes;
   sim->table.episodes = sim->dEpisodes;
+  sim->table.epNav = sim->dEpNav;
   sim->table.epOffset = sim->dEpOffset;
   sim->table.epCount = sim->dEpCount;
 
@@ -454,8 +469,6 @@ int32_t bpsn_finalize(bpsn_sim* sim) {
     BPSN_CUDA(sim, cudaMemcpy(sim->groups[gi].dev.scene, sim->envScene.data() + gi * B,
                               sizeof(uint32_t) * B, cudaMemcpyHostToDevice));
   }
-  sim->querySlots = 16384;
-  BPSN_CUDA(sim, cudaMalloc(&sim->queryScratch, sizeof(AStarScratch) * sim->querySlots));
   sim->finalized = true;
   return BPSN_OK;
 }
@@ -471,11 +484,9 @@ int32_t bpsn_reset(bpsn_sim* sim, uint32_t group, void* stream) {
   BPSN_CUDA(sim, cudaSetDevice(sim->cfg.gpu_id));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const uint32_t B = g.dev.B;
-  k_reset<<<blocksFor(B, 128), 128, 0, s>>>(g.dev, sim->table,
-                                            static_cast<uint32_t>(sim->cfg.seed),
-                                            static_cast<uint32_t>(sim->cfg.seed >> 32), nullptr,
-                                            nullptr);
-  k_geo<<<blocksFor(B, 128), 128, 0, s>>>(g.dev, sim->table, g.scratch, nullptr, nullptr, 1);
+  k_reset_all<<<blocksFor(B, 256), 256, 0, s>>>(g.dev, sim->table,
+                                                static_cast<uint32_t>(sim->cfg.seed),
+                                                static_cast<uint32_t>(sim->cfg.seed >> 32));
   BPSN_CUDA(sim, cudaGetLastError());
   int32_t rc = finishLaunch(sim, g, s, /*polarOnly=*/true);
   if (rc)
@@ -518,19 +529,12 @@ int32_t bpsn_step_start(bpsn_sim* sim, uint32_t group, const int64_t* actions,
   if (prof) cudaEventRecord(g.prof[0], s);
   k_move<<<blocksFor(B, 128), 128, 0, s>>>(g.dev, sim->table, dAct, sim->turn);
   if (prof) cudaEventRecord(g.prof[1], s);
-  k_geo<<<blocksFor(B, 128), 128, 0, s>>>(g.dev, sim->table, g.scratch, g.dev.geoList,
-                                          g.dev.counts + 0, 0);
+  k_geo<<<blocksFor(B, 128), 128, 0, s>>>(g.dev, sim->table, g.scratch);
   if (prof) cudaEventRecord(g.prof[2], s);
-  k_finish<<<blocksFor(B, 256), 256, 0, s>>>(g.dev);
+  k_finish<<<blocksFor(B, 256), 256, 0, s>>>(g.dev, sim->table,
+                                             static_cast<uint32_t>(sim->cfg.seed),
+                                             static_cast<uint32_t>(sim->cfg.seed >> 32));
   if (prof) cudaEventRecord(g.prof[3], s);
-  k_reset<<<blocksFor(B, 128), 128, 0, s>>>(g.dev, sim->table,
-                                            static_cast<uint32_t>(sim->cfg.seed),
-                                            static_cast<uint32_t>(sim->cfg.seed >> 32),
-                                            g.dev.resetList, g.dev.counts + 1);
-  if (prof) cudaEventRecord(g.prof[4], s);
-  k_geo<<<blocksFor(B, 128), 128, 0, s>>>(g.dev, sim->table, g.scratch, g.dev.resetList,
-                                          g.dev.counts + 1, 1);
-  if (prof) cudaEventRecord(g.prof[5], s);
   BPSN_CUDA(sim, cudaGetLastError());
   int32_t rc = finishLaunch(sim, g, s, /*polarOnly=*/false);
   if (rc)
@@ -551,8 +555,8 @@ int32_t bpsn_step_end(bpsn_sim* sim, uint32_t group) {
   if (sim->cfg.flags & BPSN_FLAG_HOST_MIRRORS)
     BPSN_CUDA(sim, cudaEventSynchronize(g.done));
   if (g.profiling) {
-    BPSN_CUDA(sim, cudaEventSynchronize(g.prof[5]));
-    for (int k = 0; k < 5; ++k) {
+    BPSN_CUDA(sim, cudaEventSynchronize(g.prof[3]));
+    for (int k = 0; k < 3; ++k) {
       float ms = 0.f;
       BPSN_CUDA(sim, cudaEventElapsedTime(&ms, g.prof[k], g.prof[k + 1]));
       g.profMs[k] += ms;
@@ -581,12 +585,12 @@ int32_t bpsn_profile_enable(bpsn_sim* sim, uint32_t group, int32_t enable) {
   return BPSN_OK;
 }
 
-int32_t bpsn_profile_read(bpsn_sim* sim, uint32_t group, double* ms5, uint64_t* steps) {
-  if (!sim || !sim->finalized || group >= sim->groups.size() || !ms5)
+int32_t bpsn_profile_read(bpsn_sim* sim, uint32_t group, double* ms3, uint64_t* steps) {
+  if (!sim || !sim->finalized || group >= sim->groups.size() || !ms3)
     return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_profile_read: bad argument");
   Group& g = sim->groups[group];
-  for (int k = 0; k < 5; ++k)
-    ms5[k] = g.profMs[k];
+  for (int k = 0; k < 3; ++k)
+    ms3[k] = g.profMs[k];
   if (steps)
     *steps = g.profSteps;
   return BPSN_OK;

@@ -11,11 +11,16 @@
 //   k_geo     listed    : geodesic distance goal -> agent (InfoFunctor::step :758-790)
 //   k_finish  every env : success / SPL / distance, reward, mask
 //                         (InfoFunctor::step, RewardFunctor::step :808-822);
-//                         finished envs are appended to the reset list
-//   k_reset   listed    : new episode: pose from the episode record, snap start
-//                         and goal, GPS/compass (BaseSimulator::reset :601-618,
-//                         InfoFunctor::reset :744-756)
-//   k_geo     listed    : geodesic agent -> goal = initial distance (:750-752)
+//                         finished envs start a new episode in the same thread
+//                         (BaseSimulator::reset :601-618, InfoFunctor::reset
+//                         :744-756, RewardFunctor::reset :801-806)
+//
+// Everything reset() derives from the chosen episode alone -- the snapped
+// start point, the snapped goal and the initial geodesic distance agent ->
+// goal (:611-612, :747-752) -- is a pure function of the episode record, so it
+// is evaluated once per episode when the scenes are uploaded (k_episode_table,
+// same device functions) and a reset becomes a table lookup.  The values are
+// bit-identical to evaluating them at every reset as the reference does.
 //
 // State is structure-of-arrays per group so that each phase reads and writes
 // coalesced 4-byte columns.
@@ -55,15 +60,27 @@ struct GroupDev {
   uint8_t* mask;  // [B]
   float* info;    // [B][3]
   float* polar;   // [B][2]
-  // work lists
-  uint32_t* geoList;    // [B]
-  uint32_t* resetList;  // [B]
-  uint32_t* counts;     // [0] geodesic queries, [1] resets
+  // work list
+  uint32_t* geoList;  // [B]
+  uint32_t* counts;   // [0] geodesic queries this step
 };
+
+// Per-episode results of reset()'s navmesh queries.
+struct alignas(16) EpisodeNav {
+  float navStart[3];
+  uint32_t startRef;
+  float navGoal[3];
+  uint32_t goalRef;
+  float initDist;
+  uint32_t status;
+  uint32_t pad[2];
+};
+static_assert(sizeof(EpisodeNav) == 48, "EpisodeNav is 48 bytes");
 
 struct SceneTable {
   const NavScene* scenes;
   const float* episodes;      // 10 floats per record, all scenes concatenated
+  const EpisodeNav* epNav;    // one per episode record
   const uint32_t* epOffset;   // [numScenes]
   const uint32_t* epCount;    // [numScenes]
 };
@@ -195,39 +212,77 @@ k_move(GroupDev g, SceneTable st, const int64_t* __restrict__ actions, TurnConst
   }
 }
 
-// mode 0: step query  goal -> agent, result to tmpDist
-// mode 1: reset query agent -> goal, result to initDist and prevDist
+// Geodesic distance goal -> agent for the listed environments (the reference
+// queries in that direction on every step, simulator.cpp:766-768, 775-777).
 __global__ void __launch_bounds__(128)
-k_geo(GroupDev g, SceneTable st, AStarScratch* __restrict__ scratch, const uint32_t* list,
-      const uint32_t* count, int mode) {
+k_geo(GroupDev g, SceneTable st, AStarScratch* __restrict__ scratch) {
   const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
-  const uint32_t n = count ? min(*count, g.B) : g.B;
+  const uint32_t n = min(g.counts[0], g.B);
   if (t >= n)
     return;
-  const uint32_t e = list ? list[t] : t;
+  const uint32_t e = g.geoList[t];
   const uint32_t B = g.B;
   const NavScene sc = st.scenes[g.scene[e]];
   const float a[3] = {g.navPos[e], g.navPos[B + e], g.navPos[2 * B + e]};
   const float b[3] = {g.navGoal[e], g.navGoal[B + e], g.navGoal[2 * B + e]};
-  const uint32_t aref = g.navRef[e];
-  const uint32_t bref = g.goalRef[e];
   uint32_t status = 0;
-  float d;
-  if (mode == 0)
-    d = geodesic(sc, scratch + t, b, bref, a, aref, &status);
-  else
-    d = geodesic(sc, scratch + t, a, aref, b, bref, &status);
+  const float d = geodesic(sc, scratch + t, b, g.goalRef[e], a, g.navRef[e], &status);
   if (status)
     g.status[e] |= status;
-  if (mode == 0) {
-    g.tmpDist[e] = d;
-  } else {
-    g.initDist[e] = d;
-    g.prevDist[e] = d;
-  }
+  g.tmpDist[e] = d;
 }
 
-__global__ void __launch_bounds__(256) k_finish(GroupDev g) {
+// BaseSimulator::reset + InfoFunctor::reset + RewardFunctor::reset for one env.
+__device__ __forceinline__ void resetEnv(const GroupDev& g, const SceneTable& st, uint32_t e,
+                                         uint32_t seedLo, uint32_t seedHi) {
+  const uint32_t B = g.B;
+  const uint32_t sceneIdx = g.scene[e];
+  const uint32_t rc = g.resetCount[e];
+  const uint32_t r = philoxFirst(g.envBase + e, rc, 0u, 0u, seedLo, seedHi);
+  const uint32_t nEp = st.epCount[sceneIdx];
+  const uint32_t idx = __umulhi(r, nEp);
+  g.resetCount[e] = rc + 1;
+  g.episode[e] = idx;
+  g.step[e] = 1;
+  const size_t rec = static_cast<size_t>(st.epOffset[sceneIdx]) + idx;
+  const float* ep = st.episodes + 10 * rec;
+  const float sx = ep[0], sy = ep[1], sz = ep[2];
+  const float qx = ep[3], qy = ep[4], qz = ep[5], qw = ep[6];
+  const float gx = ep[7], gy = ep[8], gz = ep[9];
+  const uint4* nv = reinterpret_cast<const uint4*>(st.epNav + rec);
+  const uint4 n0 = __ldg(nv), n1 = __ldg(nv + 1), n2 = __ldg(nv + 2);
+  g.pos[e] = sx;
+  g.pos[B + e] = sy;
+  g.pos[2 * B + e] = sz;
+  g.rot[e] = qx;
+  g.rot[B + e] = qy;
+  g.rot[2 * B + e] = qz;
+  g.rot[3 * B + e] = qw;
+  g.goal[e] = gx;
+  g.goal[B + e] = gy;
+  g.goal[2 * B + e] = gz;
+  g.navPos[e] = __uint_as_float(n0.x);
+  g.navPos[B + e] = __uint_as_float(n0.y);
+  g.navPos[2 * B + e] = __uint_as_float(n0.z);
+  g.navRef[e] = n0.w;
+  g.navGoal[e] = __uint_as_float(n1.x);
+  g.navGoal[B + e] = __uint_as_float(n1.y);
+  g.navGoal[2 * B + e] = __uint_as_float(n1.z);
+  g.goalRef[e] = n1.w;
+  const float init = __uint_as_float(n2.x);
+  g.initDist[e] = init;
+  g.prevDist[e] = init;
+  if (n2.y)
+    g.status[e] |= n2.y;
+  g.cumTravel[e] = 0.f;
+  g.prevPos[e] = sx;
+  g.prevPos[B + e] = sy;
+  g.prevPos[2 * B + e] = sz;
+  writePolar(g, e, sx, sy, sz, qx, qy, qz, qw, gx, gy, gz);
+}
+
+__global__ void __launch_bounds__(256)
+k_finish(GroupDev g, SceneTable st, uint32_t seedLo, uint32_t seedHi) {
   const uint32_t e = blockIdx.x * blockDim.x + threadIdx.x;
   if (e >= g.B)
     return;
@@ -267,65 +322,43 @@ __global__ void __launch_bounds__(256) k_finish(GroupDev g) {
   g.info[3 * e + 0] = success;
   g.info[3 * e + 1] = spl;
   g.info[3 * e + 2] = d;
-  if (done) {
-    const uint32_t slot = atomicAdd(&g.counts[1], 1u);
-    g.resetList[slot] = e;
-  }
+  if (done)
+    resetEnv(g, st, e, seedLo, seedHi);
 }
 
-__global__ void __launch_bounds__(128)
-k_reset(GroupDev g, SceneTable st, uint32_t seedLo, uint32_t seedHi, const uint32_t* list,
-        const uint32_t* count) {
-  const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
-  const uint32_t n = count ? min(*count, g.B) : g.B;
-  if (t >= n)
+__global__ void __launch_bounds__(256)
+k_reset_all(GroupDev g, SceneTable st, uint32_t seedLo, uint32_t seedHi) {
+  const uint32_t e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= g.B)
     return;
-  const uint32_t e = list ? list[t] : t;
-  const uint32_t B = g.B;
-  const uint32_t sceneIdx = g.scene[e];
-  const NavScene sc = st.scenes[sceneIdx];
-  const uint32_t rc = g.resetCount[e];
-  const uint32_t r = philoxFirst(g.envBase + e, rc, 0u, 0u, seedLo, seedHi);
-  const uint32_t nEp = st.epCount[sceneIdx];
-  const uint32_t idx = __umulhi(r, nEp);
-  g.resetCount[e] = rc + 1;
-  g.episode[e] = idx;
-  g.step[e] = 1;
-  const float* ep = st.episodes + 10 * static_cast<size_t>(st.epOffset[sceneIdx] + idx);
-  const float start[3] = {ep[0], ep[1], ep[2]};
-  const float qx = ep[3], qy = ep[4], qz = ep[5], qw = ep[6];
-  const float goal[3] = {ep[7], ep[8], ep[9]};
-  g.pos[e] = start[0];
-  g.pos[B + e] = start[1];
-  g.pos[2 * B + e] = start[2];
-  g.rot[e] = qx;
-  g.rot[B + e] = qy;
-  g.rot[2 * B + e] = qz;
-  g.rot[3 * B + e] = qw;
-  g.goal[e] = goal[0];
-  g.goal[B + e] = goal[1];
-  g.goal[2 * B + e] = goal[2];
-  float np[3];
-  uint32_t nref;
-  snapPoint(sc, start, np, &nref);
-  g.navPos[e] = np[0];
-  g.navPos[B + e] = np[1];
-  g.navPos[2 * B + e] = np[2];
-  g.navRef[e] = nref;
-  writePolar(g, e, start[0], start[1], start[2], qx, qy, qz, qw, goal[0], goal[1], goal[2]);
-  float ng[3];
-  uint32_t gref;
-  snapPoint(sc, goal, ng, &gref);
-  g.navGoal[e] = ng[0];
-  g.navGoal[B + e] = ng[1];
-  g.navGoal[2 * B + e] = ng[2];
-  g.goalRef[e] = gref;
-  if (nref == 0 || gref == 0)
-    g.status[e] |= kStatSnapFailed;
-  g.cumTravel[e] = 0.f;
-  g.prevPos[e] = start[0];
-  g.prevPos[B + e] = start[1];
-  g.prevPos[2 * B + e] = start[2];
+  resetEnv(g, st, e, seedLo, seedHi);
+}
+
+// One thread per episode record of one scene: snapPoint(start), snapPoint(goal)
+// and the geodesic distance start -> goal, exactly what reset() asks of the
+// navmesh (simulator.cpp:611-612, 747-752).
+__global__ void __launch_bounds__(128)
+k_episode_table(const NavScene* scene, const float* __restrict__ episodes, uint32_t count,
+                AStarScratch* __restrict__ scratch, uint32_t nslots, EpisodeNav* out) {
+  const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= nslots)
+    return;
+  const NavScene sc = *scene;
+  for (uint32_t i = t; i < count; i += nslots) {
+    const float* ep = episodes + 10 * static_cast<size_t>(i);
+    const float start[3] = {ep[0], ep[1], ep[2]};
+    const float goal[3] = {ep[7], ep[8], ep[9]};
+    EpisodeNav r;
+    snapPoint(sc, start, r.navStart, &r.startRef);
+    snapPoint(sc, goal, r.navGoal, &r.goalRef);
+    uint32_t status = 0;
+    if (r.startRef == 0 || r.goalRef == 0)
+      status |= kStatSnapFailed;
+    r.initDist = geodesic(sc, scratch + t, r.navStart, r.startRef, r.navGoal, r.goalRef, &status);
+    r.status = status;
+    r.pad[0] = r.pad[1] = 0;
+    out[i] = r;
+  }
 }
 
 // ------------------------------------------------------------ query kernels
