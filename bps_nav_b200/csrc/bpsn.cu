@@ -14,6 +14,7 @@
 #include <vector>
 
 #include "gae_kernels.cuh"
+#include "geo_warp.cuh"
 #include "navmesh_host.h"
 #include "sim_kernels.cuh"
 
@@ -43,6 +44,15 @@ struct Group {
   int64_t* hActions = nullptr;  // pinned staging
   int64_t* dActions = nullptr;
   AStarScratch* scratch = nullptr;
+  // launch plan of the geodesic phase
+  uint32_t numScenesUsed = 0;   // grid.y
+  uint32_t maxSceneEnvs = 0;    // largest per-scene list
+  bool warpGeo = false;         // shared-memory warp kernel usable for every scene of the group
+  int warpsPerBlock = 0;
+  int pcap = 0;
+  uint32_t geoGridX = 0;
+  size_t geoSmem = 0;
+  AStarScratch* fallbackScratch = nullptr;
   cudaEvent_t done = nullptr;
   bool inFlight = false;
   // optional per-kernel timing (bpsn_profile_enable)
@@ -139,7 +149,8 @@ int32_t uploadScene(bpsn_sim* sim, DeviceScene& ds) {
   return BPSN_OK;
 }
 
-int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase) {
+int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
+                   const uint32_t* envScene) {
   size_t off = 0;
   auto place = [&](size_t bytes) {
     size_t o = off;
@@ -157,7 +168,9 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase) {
                oScene = place(B * u), oFlags = place(B * u);
   const size_t oReward = place(B * f), oMask = place(B), oInfo = place(3 * B * f),
                oPolar = place(2 * B * f);
-  const size_t oGeoList = place(B * u), oCounts = place(4 * u);
+  const uint32_t ns = sim->cfg.num_scenes;
+  const size_t oGeoList = place(B * u), oCounts = place((ns + 4) * u),
+               oListBase = place((ns + 4) * u);
   g.stateBytes = off;
   BPSN_CUDA(sim, cudaMalloc(&g.stateBlob, off));
   BPSN_CUDA(sim, cudaMemset(g.stateBlob, 0, off));
@@ -189,6 +202,71 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase) {
   d.polar = reinterpret_cast<float*>(b + oPolar);
   d.geoList = reinterpret_cast<uint32_t*>(b + oGeoList);
   d.counts = reinterpret_cast<uint32_t*>(b + oCounts);
+  d.listBase = reinterpret_cast<const uint32_t*>(b + oListBase);
+  {
+    // per-scene segments of the geodesic work list, sized by the number of
+    // environments of this group that live in each scene
+    std::vector<uint32_t> perScene(ns, 0), base(ns + 4, 0);
+    for (uint32_t e = 0; e < B; ++e)
+      perScene[envScene[e]]++;
+    uint32_t acc = 0;
+    g.maxSceneEnvs = 0;
+    for (uint32_t s2 = 0; s2 < ns; ++s2) {
+      base[s2] = acc;
+      acc += perScene[s2];
+      if (perScene[s2] > g.maxSceneEnvs)
+        g.maxSceneEnvs = perScene[s2];
+    }
+    BPSN_CUDA(sim, cudaMemcpy(b + oListBase, base.data(), sizeof(uint32_t) * (ns + 4),
+                              cudaMemcpyHostToDevice));
+    BPSN_CUDA(sim, cudaMemcpy(d.scene, envScene, sizeof(uint32_t) * B, cudaMemcpyHostToDevice));
+    g.numScenesUsed = ns;
+    // Shared-memory plan: every scene used by the group must fit next to at
+    // least four warp slabs in one CTA's 227 KB.
+    const size_t kSmemMax = 227 * 1024;
+    size_t maxSceneBytes = 0;
+    int maxPolys = 0;
+    bool anyUsed = false;
+    for (uint32_t s2 = 0; s2 < ns; ++s2) {
+      if (!perScene[s2])
+        continue;
+      anyUsed = true;
+      const HostScene& h = sim->scenes[s2].host;
+      const size_t sb = warpGeoSceneBytes(static_cast<int>(h.verts.size() / 3),
+                                          static_cast<int>(h.polys.size()));
+      if (sb > maxSceneBytes)
+        maxSceneBytes = sb;
+      if (static_cast<int>(h.polys.size()) > maxPolys)
+        maxPolys = static_cast<int>(h.polys.size());
+    }
+    g.pcap = (maxPolys + 15) / 16 * 16;
+    const size_t slab = warpGeoSlabBytes(g.pcap);
+    int wpb = 0;
+    if (anyUsed && maxPolys < 65000 && maxSceneBytes + 4 * slab <= kSmemMax)
+      wpb = static_cast<int>((kSmemMax - maxSceneBytes) / slab);
+    if (wpb > 16)
+      wpb = 16;
+    g.warpGeo = wpb >= 4;
+    if (g.warpGeo) {
+      g.warpsPerBlock = wpb;
+      g.geoSmem = maxSceneBytes + static_cast<size_t>(wpb) * slab;
+      const int blocksPerSm = static_cast<int>(kSmemMax / g.geoSmem) > 0
+                                  ? static_cast<int>(kSmemMax / g.geoSmem) : 1;
+      int sms = 148;
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, sim->cfg.gpu_id);
+      uint32_t gx = (static_cast<uint32_t>(sms * blocksPerSm) + ns - 1) / ns;
+      const uint32_t need = (g.maxSceneEnvs + wpb - 1) / wpb;
+      if (gx > need)
+        gx = need;
+      if (gx == 0)
+        gx = 1;
+      g.geoGridX = gx;
+      BPSN_CUDA(sim, cudaFuncSetAttribute(k_geo_warp, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          static_cast<int>(kSmemMax)));
+      BPSN_CUDA(sim, cudaMalloc(&g.fallbackScratch,
+                                sizeof(AStarScratch) * static_cast<size_t>(gx) * ns * wpb));
+    }
+  }
 
   auto setField = [&](int id, void* p, size_t bytes) {
     g.fieldPtr[id] = p;
@@ -311,6 +389,7 @@ int32_t bpsn_destroy(bpsn_sim* sim) {
   for (auto& g : sim->groups) {
     cudaFree(g.stateBlob);
     cudaFree(g.scratch);
+    cudaFree(g.fallbackScratch);
     cudaFree(g.dActions);
     cudaFreeHost(g.hActions);
     cudaFreeHost(g.hReward);
@@ -463,11 +542,9 @@ int32_t bpsn_finalize(bpsn_sim* sim) {
   const uint32_t B = sim->cfg.num_envs / ng;
   sim->groups.resize(ng);
   for (uint32_t gi = 0; gi < ng; ++gi) {
-    int32_t rc = allocGroup(sim, sim->groups[gi], B, gi * B);
+    int32_t rc = allocGroup(sim, sim->groups[gi], B, gi * B, sim->envScene.data() + gi * B);
     if (rc)
       return rc;
-    BPSN_CUDA(sim, cudaMemcpy(sim->groups[gi].dev.scene, sim->envScene.data() + gi * B,
-                              sizeof(uint32_t) * B, cudaMemcpyHostToDevice));
   }
   sim->finalized = true;
   return BPSN_OK;
@@ -524,12 +601,18 @@ int32_t bpsn_step_start(bpsn_sim* sim, uint32_t group, const int64_t* actions,
   } else if (actions_mem != BPSN_MEM_DEVICE) {
     return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_step_start: actions_mem must be host or device");
   }
-  BPSN_CUDA(sim, cudaMemsetAsync(g.dev.counts, 0, 4 * sizeof(uint32_t), s));
+  BPSN_CUDA(sim, cudaMemsetAsync(g.dev.counts, 0, g.numScenesUsed * sizeof(uint32_t), s));
   const bool prof = g.profiling;
   if (prof) cudaEventRecord(g.prof[0], s);
   k_move<<<blocksFor(B, 128), 128, 0, s>>>(g.dev, sim->table, dAct, sim->turn);
   if (prof) cudaEventRecord(g.prof[1], s);
-  k_geo<<<blocksFor(B, 128), 128, 0, s>>>(g.dev, sim->table, g.scratch);
+  if (g.warpGeo) {
+    k_geo_warp<<<dim3(g.geoGridX, g.numScenesUsed), g.warpsPerBlock * 32, g.geoSmem, s>>>(
+        g.dev, sim->table, g.dev.listBase, g.pcap, g.fallbackScratch);
+  } else {
+    k_geo<<<dim3(blocksFor(g.maxSceneEnvs, 128), g.numScenesUsed), 128, 0, s>>>(g.dev, sim->table,
+                                                                               g.scratch);
+  }
   if (prof) cudaEventRecord(g.prof[2], s);
   k_finish<<<blocksFor(B, 256), 256, 0, s>>>(g.dev, sim->table,
                                              static_cast<uint32_t>(sim->cfg.seed),

@@ -127,6 +127,7 @@ enum QueryStatus : uint32_t {
   kStatIterCap = 1u << 5,       // a defensive loop bound was hit
   kStatNoIsland = 1u << 6,      // start/end on different components -> +inf
   kStatBadAction = 1u << 7,     // action outside {0,1,2,3}
+  kStatTieFallback = 1u << 8,   // open-list tie: query rerun with the exact heap emulation
 };
 
 }  // namespace bpsn

@@ -60,9 +60,11 @@ struct GroupDev {
   uint8_t* mask;  // [B]
   float* info;    // [B][3]
   float* polar;   // [B][2]
-  // work list
-  uint32_t* geoList;  // [B]
-  uint32_t* counts;   // [0] geodesic queries this step
+  // geodesic work list, segmented by scene: scene s owns geoList[listBase[s] ...],
+  // counts[s] entries are valid this step
+  uint32_t* geoList;         // [B]
+  uint32_t* counts;          // [numScenes]
+  const uint32_t* listBase;  // [numScenes]
 };
 
 // Per-episode results of reset()'s navmesh queries.
@@ -207,20 +209,28 @@ k_move(GroupDev g, SceneTable st, const int64_t* __restrict__ actions, TurnConst
 
   g.flags[e] = (done ? 1u : 0u) | (moved ? 2u : 0u);
   if (done || moved) {
-    const uint32_t slot = atomicAdd(&g.counts[0], 1u);
-    g.geoList[slot] = e;
+    const uint32_t sceneIdx = g.scene[e];
+    const uint32_t slot = atomicAdd(&g.counts[sceneIdx], 1u);
+    g.geoList[g.listBase[sceneIdx] + slot] = e;
   }
 }
 
 // Geodesic distance goal -> agent for the listed environments (the reference
 // queries in that direction on every step, simulator.cpp:766-768, 775-777).
+// Generic path: one thread per query, tables and scratch in global memory
+// (grid.y = scene).  Used when a scene does not fit the shared-memory kernel.
 __global__ void __launch_bounds__(128)
 k_geo(GroupDev g, SceneTable st, AStarScratch* __restrict__ scratch) {
   const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
-  const uint32_t n = min(g.counts[0], g.B);
+  const uint32_t sceneIdx = blockIdx.y;
+  const uint32_t n = g.counts[sceneIdx];
   if (t >= n)
     return;
-  const uint32_t e = g.geoList[t];
+  const uint32_t slot = g.listBase[sceneIdx] + t;
+  if (slot >= g.B)
+    return;
+  const uint32_t e = g.geoList[slot];
+  scratch += slot - t;
   const uint32_t B = g.B;
   const NavScene sc = st.scenes[g.scene[e]];
   const float a[3] = {g.navPos[e], g.navPos[B + e], g.navPos[2 * B + e]};
