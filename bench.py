@@ -316,8 +316,10 @@ def run_ours(args):
         q_step = N * 0.5  # moved (1/4) or stopped (1/4) -> one geodesic query
     else:
         q_step = N * 0.61
-    units = {"k_move": N, "k_finish": N, "k_geo": q_step}
-    per_unit = {"k_move": 96 + 56 + 8, "k_finish": 60 + 25, "k_geo": BYTES_PER_GEO_QUERY}
+    # k_pre touches action 8 + step 8 + rot 32 + pos 12 + goal 12 + polar 8 + outputs/state of
+    # the envs it finishes (~25 + 8); k_step is the per-env step path for listed envs
+    units = {"k_pre": N, "k_step": q_step}
+    per_unit = {"k_pre": 113, "k_step": BYTES_PER_ENV_STEP}
     alg_bytes = units[top] * per_unit[top]
     achieved = alg_bytes / (kms[top] * 1e-3) / 1e9
     step_ms = sum(kms.values())
@@ -401,7 +403,7 @@ def run_ours(args):
                        "timing": "CUDA events per window on the launch stream, summed, max over ranks"},
             "clocks": clocks, "e2e": e2e, "roofline": roofline, "roofline_step": step_roofline,
             "kernels": kernels, "cpu_baseline": cpu,
-            "gpu_launches": K * (T * 3 + 2), "resets_per_step": resets_per_step,
+            "gpu_launches": K * (T * 2 + 2), "resets_per_step": resets_per_step,
             "mean_return": mean_return, "wall_s_device_arm": wall,
         }
         print(json.dumps(line), flush=True)

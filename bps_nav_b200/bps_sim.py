@@ -276,7 +276,7 @@ class _RolloutGenerator:
         # groups as RolloutGenerator::swapStats does (simulator.cpp:1412-1424); no swapping here.
         return (0.0, float(len(self._scenes)), float(self.envs_per_scene * self.num_groups))
 
-    KERNEL_NAMES = ("k_move", "k_geo", "k_finish")
+    KERNEL_NAMES = ("k_pre", "k_step")
 
     def profile(self, group_idx, enable=True):
         """Turns per-kernel CUDA-event timing of the step on or off (totals are cleared)."""
@@ -284,7 +284,7 @@ class _RolloutGenerator:
 
     def profile_read(self, group_idx):
         """Returns ({kernel name: total ms}, steps) accumulated since ``profile(.., True)``."""
-        ms = (C.c_double * 3)()
+        ms = (C.c_double * 2)()
         n = C.c_uint64()
         L.check(self._lib.bpsn_profile_read(self._h, group_idx, ms, C.byref(n)), self._h)
         return dict(zip(self.KERNEL_NAMES, list(ms))), int(n.value)

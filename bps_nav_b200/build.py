@@ -13,7 +13,6 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libbpsn.so")
 SOURCES = ["bpsn.cu", "navmesh_host.cpp"]
-HEADERS = ["nav_types.h", "nav_query.cuh", "sim_kernels.cuh", "gae_kernels.cuh", "navmesh_host.h"]
 
 
 def _nvcc():
@@ -27,7 +26,8 @@ def needs_build():
     if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
-    deps = [os.path.join(CSRC, f) for f in SOURCES + HEADERS]
+    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)
+            if f.endswith((".cu", ".cuh", ".cpp", ".h"))]
     deps.append(os.path.join(HERE, "..", "include", "bpsn.h"))
     return any(os.path.getmtime(d) > t for d in deps)
 

@@ -52,13 +52,14 @@ struct Group {
   int pcap = 0;
   uint32_t geoGridX = 0;
   size_t geoSmem = 0;
+  size_t slabOffset = 0;
   AStarScratch* fallbackScratch = nullptr;
   cudaEvent_t done = nullptr;
   bool inFlight = false;
   // optional per-kernel timing (bpsn_profile_enable)
   bool profiling = false;
-  cudaEvent_t prof[4] = {};
-  double profMs[3] = {0, 0, 0};
+  cudaEvent_t prof[3] = {};
+  double profMs[2] = {0, 0};
   uint64_t profSteps = 0;
   // offsets of each field inside stateBlob (for bpsn_get_ptr)
   void* fieldPtr[BPSN_FIELD_COUNT] = {};
@@ -169,7 +170,7 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
   const size_t oReward = place(B * f), oMask = place(B), oInfo = place(3 * B * f),
                oPolar = place(2 * B * f);
   const uint32_t ns = sim->cfg.num_scenes;
-  const size_t oGeoList = place(B * u), oCounts = place((ns + 4) * u),
+  const size_t oGeoList = place(B * u), oCounts = place((2 * ns + 4) * u),
                oListBase = place((ns + 4) * u);
   g.stateBytes = off;
   BPSN_CUDA(sim, cudaMalloc(&g.stateBlob, off));
@@ -232,8 +233,10 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
         continue;
       anyUsed = true;
       const HostScene& h = sim->scenes[s2].host;
-      const size_t sb = warpGeoSceneBytes(static_cast<int>(h.verts.size() / 3),
-                                          static_cast<int>(h.polys.size()));
+      const NavScene hv = h.view();
+      // staged tables + the search's filtered polygon table
+      const size_t sb = stagedLayout(hv.nverts, hv.npolys, hv.ndtris, hv.ndverts).total +
+                        static_cast<size_t>(hv.npolys) * sizeof(NavPoly);
       if (sb > maxSceneBytes)
         maxSceneBytes = sb;
       if (static_cast<int>(h.polys.size()) > maxPolys)
@@ -249,6 +252,7 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
     g.warpGeo = wpb >= 4;
     if (g.warpGeo) {
       g.warpsPerBlock = wpb;
+      g.slabOffset = maxSceneBytes;
       g.geoSmem = maxSceneBytes + static_cast<size_t>(wpb) * slab;
       const int blocksPerSm = static_cast<int>(kSmemMax / g.geoSmem) > 0
                                   ? static_cast<int>(kSmemMax / g.geoSmem) : 1;
@@ -261,7 +265,7 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
       if (gx == 0)
         gx = 1;
       g.geoGridX = gx;
-      BPSN_CUDA(sim, cudaFuncSetAttribute(k_geo_warp, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      BPSN_CUDA(sim, cudaFuncSetAttribute(k_step_warp, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           static_cast<int>(kSmemMax)));
       BPSN_CUDA(sim, cudaMalloc(&g.fallbackScratch,
                                 sizeof(AStarScratch) * static_cast<size_t>(gx) * ns * wpb));
@@ -601,23 +605,21 @@ int32_t bpsn_step_start(bpsn_sim* sim, uint32_t group, const int64_t* actions,
   } else if (actions_mem != BPSN_MEM_DEVICE) {
     return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_step_start: actions_mem must be host or device");
   }
-  BPSN_CUDA(sim, cudaMemsetAsync(g.dev.counts, 0, g.numScenesUsed * sizeof(uint32_t), s));
+  BPSN_CUDA(sim, cudaMemsetAsync(g.dev.counts, 0, 2 * g.numScenesUsed * sizeof(uint32_t), s));
   const bool prof = g.profiling;
+  const uint32_t seedLo = static_cast<uint32_t>(sim->cfg.seed);
+  const uint32_t seedHi = static_cast<uint32_t>(sim->cfg.seed >> 32);
   if (prof) cudaEventRecord(g.prof[0], s);
-  k_move<<<blocksFor(B, 128), 128, 0, s>>>(g.dev, sim->table, dAct, sim->turn);
+  k_pre<<<blocksFor(B, 256), 256, 0, s>>>(g.dev, sim->table, dAct, sim->turn, seedLo, seedHi);
   if (prof) cudaEventRecord(g.prof[1], s);
   if (g.warpGeo) {
-    k_geo_warp<<<dim3(g.geoGridX, g.numScenesUsed), g.warpsPerBlock * 32, g.geoSmem, s>>>(
-        g.dev, sim->table, g.dev.listBase, g.pcap, g.fallbackScratch);
+    k_step_warp<<<dim3(g.geoGridX, g.numScenesUsed), g.warpsPerBlock * 32, g.geoSmem, s>>>(
+        g.dev, sim->table, g.pcap, g.slabOffset, g.fallbackScratch, seedLo, seedHi);
   } else {
-    k_geo<<<dim3(blocksFor(g.maxSceneEnvs, 128), g.numScenesUsed), 128, 0, s>>>(g.dev, sim->table,
-                                                                               g.scratch);
+    k_step_thread<<<dim3(blocksFor(g.maxSceneEnvs, 128), g.numScenesUsed), 128, 0, s>>>(
+        g.dev, sim->table, g.scratch, seedLo, seedHi);
   }
   if (prof) cudaEventRecord(g.prof[2], s);
-  k_finish<<<blocksFor(B, 256), 256, 0, s>>>(g.dev, sim->table,
-                                             static_cast<uint32_t>(sim->cfg.seed),
-                                             static_cast<uint32_t>(sim->cfg.seed >> 32));
-  if (prof) cudaEventRecord(g.prof[3], s);
   BPSN_CUDA(sim, cudaGetLastError());
   int32_t rc = finishLaunch(sim, g, s, /*polarOnly=*/false);
   if (rc)
@@ -638,8 +640,8 @@ int32_t bpsn_step_end(bpsn_sim* sim, uint32_t group) {
   if (sim->cfg.flags & BPSN_FLAG_HOST_MIRRORS)
     BPSN_CUDA(sim, cudaEventSynchronize(g.done));
   if (g.profiling) {
-    BPSN_CUDA(sim, cudaEventSynchronize(g.prof[3]));
-    for (int k = 0; k < 3; ++k) {
+    BPSN_CUDA(sim, cudaEventSynchronize(g.prof[2]));
+    for (int k = 0; k < 2; ++k) {
       float ms = 0.f;
       BPSN_CUDA(sim, cudaEventElapsedTime(&ms, g.prof[k], g.prof[k + 1]));
       g.profMs[k] += ms;
@@ -668,12 +670,12 @@ int32_t bpsn_profile_enable(bpsn_sim* sim, uint32_t group, int32_t enable) {
   return BPSN_OK;
 }
 
-int32_t bpsn_profile_read(bpsn_sim* sim, uint32_t group, double* ms3, uint64_t* steps) {
-  if (!sim || !sim->finalized || group >= sim->groups.size() || !ms3)
+int32_t bpsn_profile_read(bpsn_sim* sim, uint32_t group, double* ms2, uint64_t* steps) {
+  if (!sim || !sim->finalized || group >= sim->groups.size() || !ms2)
     return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_profile_read: bad argument");
   Group& g = sim->groups[group];
-  for (int k = 0; k < 3; ++k)
-    ms3[k] = g.profMs[k];
+  for (int k = 0; k < 2; ++k)
+    ms2[k] = g.profMs[k];
   if (steps)
     *steps = g.profSteps;
   return BPSN_OK;

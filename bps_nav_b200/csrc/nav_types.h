@@ -72,6 +72,8 @@ struct NavScene {
   int32_t npolys;
   int32_t nverts;
   int32_t nbv;
+  int32_t ndverts;
+  int32_t ndtris;
   uint32_t refBase;   // salt/tile bits of every polygon ref of this tile
   uint32_t polyMask;  // (1 << polyBits) - 1
   float bmin[3];

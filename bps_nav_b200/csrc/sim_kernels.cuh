@@ -1,19 +1,23 @@
 // Per-environment PointNav state machine as CUDA kernels.
 //
 // One environment step of the reference (BaseSimulator::step followed by the
-// in-loop auto-reset, simulator/simulator.cpp:620-641, 1626-1644) is split
-// into phases so that warps do uniform work:
+// in-loop auto-reset, simulator/simulator.cpp:620-641, 1626-1644) is two
+// launches:
 //
-//   k_move    every env : action -> turn / forward move (tryStep) -> GPS/compass
-//                         (handleMovement :680-710, updateObservationState :651-677);
-//                         envs that moved or finished are appended to the
-//                         geodesic work list
-//   k_geo     listed    : geodesic distance goal -> agent (InfoFunctor::step :758-790)
-//   k_finish  every env : success / SPL / distance, reward, mask
-//                         (InfoFunctor::step, RewardFunctor::step :808-822);
-//                         finished envs start a new episode in the same thread
-//                         (BaseSimulator::reset :601-618, InfoFunctor::reset
-//                         :744-756, RewardFunctor::reset :801-806)
+//   k_pre   one thread per env: decode the action, advance the step counter,
+//           apply a turn (handleMovement :696-703) and refresh the GPS/compass
+//           (updateObservationState :651-677).  An env that neither moved nor
+//           finished needs no navmesh query (InfoFunctor::step :784-786): its
+//           info / reward / mask are written here.  Envs that moved forward,
+//           stopped or timed out are appended to their scene's work list.
+//   k_step_warp / k_step_thread
+//           one warp (scene tables in shared memory, geo_warp.cuh) or one
+//           thread (tables in global memory) per listed env: forward move
+//           (PathFinder::tryStep, handleMovement :684-695), GPS/compass,
+//           geodesic goal -> agent (InfoFunctor::step :758-790), success / SPL /
+//           reward / mask (RewardFunctor::step :808-822) and, when the episode
+//           finished, the reset (BaseSimulator::reset :601-618,
+//           InfoFunctor::reset :744-756, RewardFunctor::reset :801-806).
 //
 // Everything reset() derives from the chosen episode alone -- the snapped
 // start point, the snapped goal and the initial geodesic distance agent ->
@@ -63,7 +67,7 @@ struct GroupDev {
   // geodesic work list, segmented by scene: scene s owns geoList[listBase[s] ...],
   // counts[s] entries are valid this step
   uint32_t* geoList;         // [B]
-  uint32_t* counts;          // [numScenes]
+  uint32_t* counts;          // [2 * numScenes]: list lengths, then work-queue cursors
   const uint32_t* listBase;  // [numScenes]
 };
 
@@ -137,111 +141,6 @@ __device__ __forceinline__ void writePolar(const GroupDev& g, uint32_t e, float 
   reinterpret_cast<float2*>(g.polar)[e] = make_float2(rho, -phi);
 }
 
-__global__ void __launch_bounds__(128)
-k_move(GroupDev g, SceneTable st, const int64_t* __restrict__ actions, TurnConsts tc) {
-  const uint32_t e = blockIdx.x * blockDim.x + threadIdx.x;
-  if (e >= g.B)
-    return;
-  const uint32_t B = g.B;
-  const int64_t action = actions[e];
-  uint32_t step = g.step[e] + 1;
-  g.step[e] = step;
-  bool done = static_cast<float>(step) >= kMaxSteps;
-  bool moved = false;
-
-  if (action == 0) {
-    done = true;
-  } else {
-    float px = g.pos[e], py = g.pos[B + e], pz = g.pos[2 * B + e];
-    float qx = g.rot[e], qy = g.rot[B + e], qz = g.rot[2 * B + e], qw = g.rot[3 * B + e];
-    if (action == 1) {
-      // delta = rot * (0, 0, -0.25):  v + 2 * (w * (q x v) + q x (q x v))
-      const float vx = 0.f * kForwardStep, vy = 0.f * kForwardStep, vz = -1.f * kForwardStep;
-      const float uvx = qy * vz - vy * qz;
-      const float uvy = qz * vx - vz * qx;
-      const float uvz = qx * vy - vx * qy;
-      const float uuvx = qy * uvz - uvy * qz;
-      const float uuvy = qz * uvx - uvz * qx;
-      const float uuvz = qx * uvy - uvx * qy;
-      float endPos[3];
-      endPos[0] = px + (vx + ((uvx * qw) + uuvx) * 2.f);
-      endPos[1] = py + (vy + ((uvy * qw) + uuvy) * 2.f);
-      endPos[2] = pz + (vz + ((uvz * qw) + uuvz) * 2.f);
-      float np[3] = {g.navPos[e], g.navPos[B + e], g.navPos[2 * B + e]};
-      uint32_t ref = g.navRef[e];
-      const NavScene sc = st.scenes[g.scene[e]];
-      tryStep(sc, np, &ref, endPos);
-      g.navPos[e] = np[0];
-      g.navPos[B + e] = np[1];
-      g.navPos[2 * B + e] = np[2];
-      g.navRef[e] = ref;
-      px = np[0];
-      py = np[1];
-      pz = np[2];
-      g.pos[e] = px;
-      g.pos[B + e] = py;
-      g.pos[2 * B + e] = pz;
-      moved = true;
-    } else if (action == 2 || action == 3) {
-      const float ox = action == 2 ? tc.lx : tc.rx;
-      const float oy = action == 2 ? tc.ly : tc.ry;
-      const float oz = action == 2 ? tc.lz : tc.rz;
-      const float ow = action == 2 ? tc.lw : tc.rw;
-      const float rw = qw * ow - qx * ox - qy * oy - qz * oz;
-      const float rx = qw * ox + qx * ow + qy * oz - qz * oy;
-      const float ry = qw * oy + qy * ow + qz * ox - qx * oz;
-      const float rz = qw * oz + qz * ow + qx * oy - qy * ox;
-      qx = rx;
-      qy = ry;
-      qz = rz;
-      qw = rw;
-      g.rot[e] = qx;
-      g.rot[B + e] = qy;
-      g.rot[2 * B + e] = qz;
-      g.rot[3 * B + e] = qw;
-    } else {
-      // The reference aborts the process here; this implementation flags the
-      // environment and leaves its pose untouched.
-      g.status[e] |= kStatBadAction;
-    }
-    writePolar(g, e, px, py, pz, qx, qy, qz, qw, g.goal[e], g.goal[B + e], g.goal[2 * B + e]);
-  }
-
-  g.flags[e] = (done ? 1u : 0u) | (moved ? 2u : 0u);
-  if (done || moved) {
-    const uint32_t sceneIdx = g.scene[e];
-    const uint32_t slot = atomicAdd(&g.counts[sceneIdx], 1u);
-    g.geoList[g.listBase[sceneIdx] + slot] = e;
-  }
-}
-
-// Geodesic distance goal -> agent for the listed environments (the reference
-// queries in that direction on every step, simulator.cpp:766-768, 775-777).
-// Generic path: one thread per query, tables and scratch in global memory
-// (grid.y = scene).  Used when a scene does not fit the shared-memory kernel.
-__global__ void __launch_bounds__(128)
-k_geo(GroupDev g, SceneTable st, AStarScratch* __restrict__ scratch) {
-  const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
-  const uint32_t sceneIdx = blockIdx.y;
-  const uint32_t n = g.counts[sceneIdx];
-  if (t >= n)
-    return;
-  const uint32_t slot = g.listBase[sceneIdx] + t;
-  if (slot >= g.B)
-    return;
-  const uint32_t e = g.geoList[slot];
-  scratch += slot - t;
-  const uint32_t B = g.B;
-  const NavScene sc = st.scenes[g.scene[e]];
-  const float a[3] = {g.navPos[e], g.navPos[B + e], g.navPos[2 * B + e]};
-  const float b[3] = {g.navGoal[e], g.navGoal[B + e], g.navGoal[2 * B + e]};
-  uint32_t status = 0;
-  const float d = geodesic(sc, scratch + t, b, g.goalRef[e], a, g.navRef[e], &status);
-  if (status)
-    g.status[e] |= status;
-  g.tmpDist[e] = d;
-}
-
 // BaseSimulator::reset + InfoFunctor::reset + RewardFunctor::reset for one env.
 __device__ __forceinline__ void resetEnv(const GroupDev& g, const SceneTable& st, uint32_t e,
                                          uint32_t seedLo, uint32_t seedHi) {
@@ -291,25 +190,22 @@ __device__ __forceinline__ void resetEnv(const GroupDev& g, const SceneTable& st
   writePolar(g, e, sx, sy, sz, qx, qy, qz, qw, gx, gy, gz);
 }
 
-__global__ void __launch_bounds__(256)
-k_finish(GroupDev g, SceneTable st, uint32_t seedLo, uint32_t seedHi) {
-  const uint32_t e = blockIdx.x * blockDim.x + threadIdx.x;
-  if (e >= g.B)
-    return;
+// InfoFunctor::step + RewardFunctor::step, then the in-loop reset when done.
+// `d` is the geodesic distance of this step (ignored when the env neither
+// moved nor finished).
+__device__ __forceinline__ void finishEnv(const GroupDev& g, const SceneTable& st, uint32_t e,
+                                          bool done, bool moved, float d, uint32_t seedLo,
+                                          uint32_t seedHi) {
   const uint32_t B = g.B;
-  const uint32_t f = g.flags[e];
-  const bool done = f & 1u;
-  const bool moved = f & 2u;
   const float prev = g.prevDist[e];
-  float d = 0, success = 0, spl = 0;
+  float success = 0, spl = 0;
   if (done) {
-    d = g.tmpDist[e];
     success = d < kSuccessDistance ? 1.f : 0.f;
     const float init = g.initDist[e];
     const float cum = g.cumTravel[e];
-    spl = success * init / fmaxf(init, cum);
+    const float mx = (init < cum) ? cum : init;  // std::max(init, cum)
+    spl = success * init / mx;
   } else if (moved) {
-    d = g.tmpDist[e];
     const float px = g.pos[e], py = g.pos[B + e], pz = g.pos[2 * B + e];
     const float dx = px - g.prevPos[e];
     const float dy = py - g.prevPos[B + e];
@@ -334,6 +230,122 @@ k_finish(GroupDev g, SceneTable st, uint32_t seedLo, uint32_t seedHi) {
   g.info[3 * e + 2] = d;
   if (done)
     resetEnv(g, st, e, seedLo, seedHi);
+}
+
+// MoveForward of handleMovement: target = position + rotation * (0, 0, -0.25),
+// PathFinder::tryStep from the navmesh position, then position = result and the
+// GPS/compass is refreshed.  `sc` may point at shared-memory tables.
+__device__ __forceinline__ void forwardMove(const GroupDev& g, const NavScene& sc, uint32_t e) {
+  const uint32_t B = g.B;
+  const float px = g.pos[e], py = g.pos[B + e], pz = g.pos[2 * B + e];
+  const float qx = g.rot[e], qy = g.rot[B + e], qz = g.rot[2 * B + e], qw = g.rot[3 * B + e];
+  // delta = rot * v :  v + 2 * (w * (q x v) + q x (q x v))
+  const float vx = 0.f * kForwardStep, vy = 0.f * kForwardStep, vz = -1.f * kForwardStep;
+  const float uvx = qy * vz - vy * qz;
+  const float uvy = qz * vx - vz * qx;
+  const float uvz = qx * vy - vx * qy;
+  const float uuvx = qy * uvz - uvy * qz;
+  const float uuvy = qz * uvx - uvz * qx;
+  const float uuvz = qx * uvy - uvx * qy;
+  float endPos[3];
+  endPos[0] = px + (vx + ((uvx * qw) + uuvx) * 2.f);
+  endPos[1] = py + (vy + ((uvy * qw) + uuvy) * 2.f);
+  endPos[2] = pz + (vz + ((uvz * qw) + uuvz) * 2.f);
+  float np[3] = {g.navPos[e], g.navPos[B + e], g.navPos[2 * B + e]};
+  uint32_t ref = g.navRef[e];
+  tryStep(sc, np, &ref, endPos);
+  g.navPos[e] = np[0];
+  g.navPos[B + e] = np[1];
+  g.navPos[2 * B + e] = np[2];
+  g.navRef[e] = ref;
+  g.pos[e] = np[0];
+  g.pos[B + e] = np[1];
+  g.pos[2 * B + e] = np[2];
+  writePolar(g, e, np[0], np[1], np[2], qx, qy, qz, qw, g.goal[e], g.goal[B + e],
+             g.goal[2 * B + e]);
+}
+
+__global__ void __launch_bounds__(256)
+k_pre(GroupDev g, SceneTable st, const int64_t* __restrict__ actions, TurnConsts tc,
+      uint32_t seedLo, uint32_t seedHi) {
+  const uint32_t e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= g.B)
+    return;
+  const uint32_t B = g.B;
+  const int64_t action = actions[e];
+  const uint32_t step = g.step[e] + 1;
+  g.step[e] = step;
+  bool done = static_cast<float>(step) >= kMaxSteps;
+  bool moved = false;
+  if (action == 0) {
+    done = true;
+  } else if (action == 1) {
+    moved = true;
+  } else {
+    float qx = g.rot[e], qy = g.rot[B + e], qz = g.rot[2 * B + e], qw = g.rot[3 * B + e];
+    if (action == 2 || action == 3) {
+      const float ox = action == 2 ? tc.lx : tc.rx;
+      const float oy = action == 2 ? tc.ly : tc.ry;
+      const float oz = action == 2 ? tc.lz : tc.rz;
+      const float ow = action == 2 ? tc.lw : tc.rw;
+      const float rw = qw * ow - qx * ox - qy * oy - qz * oz;
+      const float rx = qw * ox + qx * ow + qy * oz - qz * oy;
+      const float ry = qw * oy + qy * ow + qz * ox - qx * oz;
+      const float rz = qw * oz + qz * ow + qx * oy - qy * ox;
+      qx = rx;
+      qy = ry;
+      qz = rz;
+      qw = rw;
+      g.rot[e] = qx;
+      g.rot[B + e] = qy;
+      g.rot[2 * B + e] = qz;
+      g.rot[3 * B + e] = qw;
+    } else {
+      // The reference aborts the process here; this implementation flags the
+      // environment and leaves its pose untouched.
+      g.status[e] |= kStatBadAction;
+    }
+    writePolar(g, e, g.pos[e], g.pos[B + e], g.pos[2 * B + e], qx, qy, qz, qw, g.goal[e],
+               g.goal[B + e], g.goal[2 * B + e]);
+  }
+  if (done || moved) {
+    g.flags[e] = (done ? 1u : 0u) | (moved ? 2u : 0u);
+    const uint32_t sceneIdx = g.scene[e];
+    const uint32_t slot = atomicAdd(&g.counts[sceneIdx], 1u);
+    g.geoList[g.listBase[sceneIdx] + slot] = e;
+  } else {
+    finishEnv(g, st, e, false, false, 0.f, seedLo, seedHi);
+  }
+}
+
+// Generic path: one thread per listed env, tables and A* scratch in global
+// memory (grid.y = scene).  Used when a scene does not fit the shared-memory
+// kernel of geo_warp.cuh.
+__global__ void __launch_bounds__(128)
+k_step_thread(GroupDev g, SceneTable st, AStarScratch* __restrict__ scratch, uint32_t seedLo,
+              uint32_t seedHi) {
+  const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+  const uint32_t sceneIdx = blockIdx.y;
+  const uint32_t n = g.counts[sceneIdx];
+  if (t >= n)
+    return;
+  const uint32_t slot = g.listBase[sceneIdx] + t;
+  if (slot >= g.B)
+    return;
+  const uint32_t e = g.geoList[slot];
+  const uint32_t B = g.B;
+  const NavScene sc = st.scenes[sceneIdx];
+  const uint32_t f = g.flags[e];
+  const bool done = f & 1u, moved = f & 2u;
+  if (moved)
+    forwardMove(g, sc, e);
+  const float a[3] = {g.navPos[e], g.navPos[B + e], g.navPos[2 * B + e]};
+  const float b[3] = {g.navGoal[e], g.navGoal[B + e], g.navGoal[2 * B + e]};
+  uint32_t status = 0;
+  const float d = geodesic(sc, scratch + slot, b, g.goalRef[e], a, g.navRef[e], &status);
+  if (status)
+    g.status[e] |= status;
+  finishEnv(g, st, e, done, moved, d, seedLo, seedHi);
 }
 
 __global__ void __launch_bounds__(256)

@@ -142,10 +142,11 @@ int32_t bpsn_get_ptr(bpsn_sim* sim, uint32_t group, int32_t field, int32_t mem, 
 /* Per-kernel device timing of the step (no counterpart in the reference; its
  * Python side times phases with wall clocks, bps_nav/common/utils.py:387-436).
  * While enabled, bpsn_step_end waits for the step and adds the CUDA-event
- * duration of each of its three launches, in order: move, geodesic, finish
- * (+ reset), to running totals in milliseconds. */
+ * duration of each of its two launches, in order: pre (action decode, turns,
+ * sensor, envs that need no navmesh query) and step (forward move, geodesic,
+ * reward, reset), to running totals in milliseconds. */
 int32_t bpsn_profile_enable(bpsn_sim* sim, uint32_t group, int32_t enable);
-int32_t bpsn_profile_read(bpsn_sim* sim, uint32_t group, double* ms3, uint64_t* steps);
+int32_t bpsn_profile_read(bpsn_sim* sim, uint32_t group, double* ms2, uint64_t* steps);
 
 /* Number of polygons / disabled polygons / islands of a loaded scene. */
 int32_t bpsn_scene_info(bpsn_sim* sim, uint32_t scene, int32_t* num_polys, int32_t* num_disabled,

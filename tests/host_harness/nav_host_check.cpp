@@ -97,4 +97,8 @@ void hchk_geodesic_batch(void* p, int n, const float* s, const uint32_t* sref, c
   }
 }
 
+#if defined(BPSN_QUERY_STATS)
+long hchk_pops() { return bpsn::g_statPops; }
+#endif
+
 }  // extern "C"
