@@ -234,9 +234,7 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
       anyUsed = true;
       const HostScene& h = sim->scenes[s2].host;
       const NavScene hv = h.view();
-      // staged tables + the search's filtered polygon table
-      const size_t sb = stagedLayout(hv.nverts, hv.npolys, hv.ndtris, hv.ndverts).total +
-                        static_cast<size_t>(hv.npolys) * sizeof(NavPoly);
+      const size_t sb = stagedLayout(hv.nverts, hv.npolys, hv.ndtris, hv.ndverts).total;
       if (sb > maxSceneBytes)
         maxSceneBytes = sb;
       if (static_cast<int>(h.polys.size()) > maxPolys)
@@ -773,6 +771,20 @@ int32_t bpsn_query_geodesic(bpsn_sim* sim, uint32_t scene, uint32_t n, const flo
   BPSN_CUDA(sim, cudaGetLastError());
   return BPSN_OK;
 }
+
+#if defined(BPSN_PHASE_TIMING)
+// developer builds only (see geo_warp.cuh)
+int32_t bpsn_debug_phase_cycles(unsigned long long* out16, int32_t reset) {
+  cudaDeviceSynchronize();
+  if (out16)
+    cudaMemcpyFromSymbol(out16, g_phaseCycles, sizeof(unsigned long long) * 16);
+  if (reset) {
+    unsigned long long z[16] = {};
+    cudaMemcpyToSymbol(g_phaseCycles, z, sizeof(z));
+  }
+  return 0;
+}
+#endif
 
 size_t bpsn_gae_workspace_bytes(uint32_t N) {
   return sizeof(GaeStat) * (static_cast<size_t>(blocksFor(N, kGaeBlock)) + 1);

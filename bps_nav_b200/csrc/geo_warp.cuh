@@ -1,33 +1,39 @@
-// Warp-cooperative geodesic distance on a scene staged in shared memory.
+// Warp-cooperative simulator step on a scene staged in shared memory.
 //
-// Same function as geodesic() in nav_query.cuh (PathFinder::Impl::findPathInternal,
+// One warp takes one listed environment through forward move, geodesic
+// distance, reward and reset.  The geodesic is the same function as
+// geodesic() in nav_query.cuh (PathFinder::Impl::findPathInternal,
 // PathFinder.cpp:485-526: island check, dtNavMeshQuery::findPath A*,
 // findStraightPath funnel, polyline length) with the work of one query spread
-// over the 32 lanes of a warp and every table it touches held on chip:
+// over the 32 lanes and every table it touches held on chip:
 //
-//   * the scene's vertex and polygon tables are copied once per CTA into shared
-//     memory (plain 16-byte loads/stores; no multicast);
+//   * the scene's vertex (padded to 16 bytes each), polygon, detail-mesh and
+//     island tables are copied once per CTA into shared memory (plain loads and
+//     stores; no multicast).  In the staged polygon table links to neighbours
+//     the query filter rejects are cleared: for the search they do not exist
+//     and for moveAlongSurface they are walls either way
+//     (DetourNavMeshQuery.cpp:2118-2132);
 //   * A* nodes are direct-mapped, one slot per polygon (a single tile has one
 //     search node per polygon: dtNavMeshQuery::findPath only creates extra
-//     nodes per polygon for tile-border links, DetourNavMeshQuery.cpp:1040-1045),
-//     structure-of-arrays in the warp's private shared-memory slab;
-//   * the open list is an *unordered* array; "pop" is a warp-parallel arg-min.
-//     A binary heap and an arg-min return the same node whenever the minimum
-//     `total` is unique.  When two open nodes tie for the minimum the result
-//     would depend on the reference heap's internal order
-//     (dtNodeQueue, Detour/Source/DetourNode.cpp:172-200), so the warp abandons
-//     the fast path and lane 0 reruns the query with the exact sequential
-//     emulation (geodesic()) on a global-memory scratch slab.  Ties are rare
-//     (totals are sums of square roots of mesh coordinates);
+//     nodes per polygon for tile-border links, DetourNavMeshQuery.cpp:1040-1045)
+//     in the warp's private shared-memory slab;
+//   * the open list lives in registers, two (total, polygon) entries per lane;
+//     "pop" is one hardware warp min-reduction.  A binary heap and an arg-min
+//     return the same node whenever the minimum `total` is unique.  When two
+//     open nodes tie for the minimum the result would depend on the reference
+//     heap's internal order (dtNodeQueue, Detour/Source/DetourNode.cpp:172-200),
+//     so the warp abandons the fast path and lane 0 reruns the query with the
+//     exact sequential emulation (geodesic()) on a global-memory scratch slab.
+//     The same fallback is taken if more than 64 nodes are open at once;
 //   * the up-to-six neighbours of the popped polygon are evaluated by six
-//     lanes at once (portal midpoint, cost, heuristic, skip test, node update,
-//     open-list append).  Two edges leading to the same neighbour produce
-//     bit-identical candidates, of which the second can never pass the
-//     reference's `total >= node->total` test, so only the lowest edge acts;
+//     lanes at once (portal midpoint, cost, heuristic, skip test, node update).
+//     Two edges leading to the same neighbour produce bit-identical
+//     candidates, of which the second can never pass the reference's
+//     `total >= node->total` test, so only the lowest edge acts;
 //   * `lastBestNode` bookkeeping is dropped: it only matters for partial
-//     paths, which PathFinder turns into +inf anyway (PathFinder.cpp:506).
-//
-// The funnel runs on lane 0 against the shared-memory scene.
+//     paths, which PathFinder turns into +inf anyway (PathFinder.cpp:506);
+//   * the funnel's portal end points are extracted by all lanes, its
+//     sequential scan runs on lane 0.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -38,10 +44,34 @@
 
 namespace bpsn {
 
-// Shared-memory layout of a staged scene: vertices | polygons | detail bases |
-// detail triangles | detail vertices, each section padded to 16 bytes.
+#if defined(BPSN_PHASE_TIMING)
+// Developer instrumentation (not compiled into the shipped library): cycles
+// spent per phase of k_step_warp, summed over queries, and per-phase maxima.
+// [0] staging  [1] state load + forward move  [2] A*  [3] funnel  [4] finish
+// [5] queries  [6..10] per-phase max  [12] pop cycles [13] expand cycles [14] pops
+__device__ unsigned long long g_phaseCycles[16];
+#define BPSN_TICK(var) const long long var = clock64()
+#define BPSN_PHASE_ADD(idx, cycles)                                              \
+  do {                                                                           \
+    atomicAdd(&g_phaseCycles[idx], static_cast<unsigned long long>(cycles));     \
+    atomicMax(&g_phaseCycles[6 + idx], static_cast<unsigned long long>(cycles)); \
+  } while (0)
+#else
+#define BPSN_TICK(var)
+#define BPSN_PHASE_ADD(idx, cycles)
+#endif
+
+constexpr uint32_t kInfBits = 0x7f800000u;
+
+// Shared-memory layout of a staged scene (byte offsets, each 16-byte aligned).
 struct StagedLayout {
-  size_t verts, polys, detail, dtris, dverts, total;
+  size_t verts;   // float4 per vertex
+  size_t polys;   // NavPoly per polygon (links filtered)
+  size_t detail;  // NavDetail per polygon
+  size_t dtris;   // 4 bytes per detail triangle (+1 padding entry)
+  size_t dverts;  // 3 floats per extra detail vertex
+  size_t island;  // int32 per polygon
+  size_t total;
 };
 __host__ __device__ inline size_t pad16(size_t x) {
   return (x + 15) / 16 * 16;
@@ -50,48 +80,43 @@ __host__ __device__ inline StagedLayout stagedLayout(int nverts, int npolys, int
                                                      int ndverts) {
   StagedLayout l;
   l.verts = 0;
-  l.polys = pad16(static_cast<size_t>(nverts) * 12);
+  l.polys = static_cast<size_t>(nverts) * 16;
   l.detail = l.polys + static_cast<size_t>(npolys) * sizeof(NavPoly);
   l.dtris = l.detail + pad16(static_cast<size_t>(npolys) * sizeof(NavDetail));
   l.dverts = l.dtris + pad16(static_cast<size_t>(ndtris + 1) * 4);
-  l.total = l.dverts + pad16(static_cast<size_t>(ndverts) * 12);
+  l.island = l.dverts + pad16(static_cast<size_t>(ndverts) * 12);
+  l.total = l.island + pad16(static_cast<size_t>(npolys) * 4);
   return l;
 }
-// Per-warp slab for node capacity pcap (multiple of 16).
+
+// Per-warp slab for node capacity pcap (a multiple of 16):
+//   nodeA  float4 {x, y, z, cost}                      16 B / polygon
+//   nodeB  uint2  {total bits, parent | slot << 16}      8 B / polygon
+//   flags  uint8  0 unseen, 1 open, 2 closed             1 B / polygon
+//   path   uint16 corridor, at most 256 polygons       512 B
+// After the search the node arrays are reused for the corridor's portals.
 __host__ __device__ inline size_t warpGeoSlabBytes(int pcap) {
-  return static_cast<size_t>(pcap) * 31 + 1024;
+  return static_cast<size_t>(pcap) * 25 + 512;
 }
 
 struct WarpSlab {
-  float* px;
-  float* py;
-  float* pz;
-  float* cost;
-  float* total;
-  float* listTotal;
-  uint16_t* listPoly;
-  uint16_t* parent;
-  uint16_t* listPos;
+  float4* nodeA;
+  uint2* nodeB;
   uint8_t* flags;
-  uint32_t* path;  // [256]
+  uint16_t* path;
 };
 
 __device__ __forceinline__ WarpSlab carveSlab(uint8_t* base, int pcap) {
   WarpSlab s;
-  float* f = reinterpret_cast<float*>(base);
-  s.px = f;
-  s.py = f + pcap;
-  s.pz = f + 2 * pcap;
-  s.cost = f + 3 * pcap;
-  s.total = f + 4 * pcap;
-  s.listTotal = f + 5 * pcap;
-  uint16_t* h = reinterpret_cast<uint16_t*>(f + 6 * pcap);
-  s.listPoly = h;
-  s.parent = h + pcap;
-  s.listPos = h + 2 * pcap;
-  s.flags = reinterpret_cast<uint8_t*>(h + 3 * pcap);
-  s.path = reinterpret_cast<uint32_t*>(s.flags + pcap);
+  s.nodeA = reinterpret_cast<float4*>(base);
+  s.nodeB = reinterpret_cast<uint2*>(base + static_cast<size_t>(pcap) * 16);
+  s.flags = base + static_cast<size_t>(pcap) * 24;
+  s.path = reinterpret_cast<uint16_t*>(base + static_cast<size_t>(pcap) * 25);
   return s;
+}
+
+__device__ __forceinline__ float4 ldVert4(const NavScene& sc, uint32_t iv) {
+  return reinterpret_cast<const float4*>(sc.verts)[iv];
 }
 
 // closestPointOnPolyBoundary (DetourNavMeshQuery.cpp:538-586) for the first and
@@ -115,10 +140,10 @@ __device__ __forceinline__ void warpClosestOnBoundary(const NavScene& sc, int la
   float vj[3] = {0, 0, 0}, vi[3] = {0, 0, 0};
   if (act) {
     const int i = (j + 1 == nv) ? 0 : j + 1;
-    const float* a = sc.verts + 3 * static_cast<size_t>(p->verts[j]);
-    const float* b = sc.verts + 3 * static_cast<size_t>(p->verts[i]);
-    vj[0] = a[0]; vj[1] = a[1]; vj[2] = a[2];
-    vi[0] = b[0]; vi[1] = b[1]; vi[2] = b[2];
+    const float4 a = ldVert4(sc, p->verts[j]);
+    const float4 b = ldVert4(sc, p->verts[i]);
+    vj[0] = a.x; vj[1] = a.y; vj[2] = a.z;
+    vi[0] = b.x; vi[1] = b.y; vi[2] = b.z;
     const float pt[3] = {ptx, pty, ptz};
     cross = ((vi[2] > ptz) != (vj[2] > ptz)) &&
             (ptx < (vj[0] - vi[0]) * (ptz - vi[2]) / (vj[2] - vi[2]) + vi[0]);
@@ -153,7 +178,7 @@ __device__ __forceinline__ void warpClosestOnBoundary(const NavScene& sc, int la
 // findStraightPath (options = 0) + polyline length over the corridor in
 // w.path[0..pathSize), same decisions as funnelLength() in nav_query.cuh.
 // Portal end points of every corridor edge are extracted by all lanes first
-// (they only depend on the corridor), into the slab's node arrays, which the
+// (they only depend on the corridor) into the slab's node arrays, which the
 // finished search no longer needs; lane 0 then walks the funnel.
 __device__ __forceinline__ float warpFunnel(const NavScene& sc, const WarpSlab& w, int lane,
                                             const float* startPos, const float* endPos,
@@ -161,12 +186,6 @@ __device__ __forceinline__ float warpFunnel(const NavScene& sc, const WarpSlab& 
   float closestStart[3], closestEnd[3];
   warpClosestOnBoundary(sc, lane, w.path[0], startPos, w.path[pathSize - 1], endPos, closestStart,
                         closestEnd);
-  float* lx = w.px;
-  float* ly = w.py;
-  float* lz = w.pz;
-  float* rx = w.cost;
-  float* ry = w.total;
-  float* rz = w.listTotal;
   bool bad = false;
   for (int i = lane; i + 1 < pathSize; i += 32) {
     const NavPoly* from = &sc.polys[w.path[i]];
@@ -183,15 +202,11 @@ __device__ __forceinline__ float warpFunnel(const NavScene& sc, const WarpSlab& 
     if (e < 0) {
       bad = true;
     } else {
-      const float* l = sc.verts + 3 * static_cast<size_t>(from->verts[e]);
+      const float4 l = ldVert4(sc, from->verts[e]);
       const int e1 = (e + 1 == nv) ? 0 : e + 1;
-      const float* r = sc.verts + 3 * static_cast<size_t>(from->verts[e1]);
-      lx[i] = l[0];
-      ly[i] = l[1];
-      lz[i] = l[2];
-      rx[i] = r[0];
-      ry[i] = r[1];
-      rz[i] = r[2];
+      const float4 r = ldVert4(sc, from->verts[e1]);
+      w.nodeA[i] = make_float4(l.x, l.y, l.z, r.x);
+      w.nodeB[i] = make_uint2(__float_as_uint(r.y), __float_as_uint(r.z));
     }
   }
   if (__any_sync(0xffffffffu, bad)) {
@@ -227,8 +242,10 @@ __device__ __forceinline__ float warpFunnel(const NavScene& sc, const WarpSlab& 
         float left[3], right[3];
         const bool isPortal = i + 1 < pathSize;
         if (isPortal) {
-          left[0] = lx[i]; left[1] = ly[i]; left[2] = lz[i];
-          right[0] = rx[i]; right[1] = ry[i]; right[2] = rz[i];
+          const float4 pa = w.nodeA[i];
+          const uint2 pb = w.nodeB[i];
+          left[0] = pa.x; left[1] = pa.y; left[2] = pa.z;
+          right[0] = pa.w; right[1] = __uint_as_float(pb.x); right[2] = __uint_as_float(pb.y);
           if (i == 0) {
             float t;
             if (distPtSegSqr2D(apex, left, right, t) < (0.001f * 0.001f))
@@ -312,15 +329,17 @@ __device__ __forceinline__ float warpFunnel(const NavScene& sc, const WarpSlab& 
   return result;
 }
 
-// One query by one warp.  `sc` has verts/polys pointing into shared memory.
+// One query by one warp.  `sc` points at the staged (shared-memory) tables.
 // Returns the distance in every lane.  *needFallback is set (uniformly) when
-// the open list had a tie for the minimum.
+// the fast path cannot decide the pop order (tie for the minimum) or the
+// register open list is full.
 __device__ __forceinline__ float warpGeodesic(const NavScene& sc, const WarpSlab& w, int lane,
                                               const float* startPos, uint32_t startRef,
                                               const float* endPos, uint32_t endRef,
                                               uint32_t* status, bool* needFallback) {
   *needFallback = false;
-  // (i) trivial path
+  BPSN_TICK(tA0);
+  // (i) trivial path: Eigen isApprox with precision 1e-5
   {
     const float dx = startPos[0] - endPos[0];
     const float dy = startPos[1] - endPos[1];
@@ -351,12 +370,11 @@ __device__ __forceinline__ float warpGeodesic(const NavScene& sc, const WarpSlab
   int pathSize = 0;
   if (startIdx == endIdx) {
     if (lane == 0)
-      w.path[0] = startIdx;
+      w.path[0] = static_cast<uint16_t>(startIdx);
     pathSize = 1;
     __syncwarp();
   } else {
     const int P = sc.npolys;
-    // clear node flags
     {
       uint32_t* f32 = reinterpret_cast<uint32_t*>(w.flags);
       const int words = (P + 3) / 4;
@@ -364,172 +382,192 @@ __device__ __forceinline__ float warpGeodesic(const NavScene& sc, const WarpSlab
         f32[i] = 0u;
     }
     __syncwarp();
+    // open list: two register entries per lane, kInfBits = empty
+    uint32_t t0 = kInfBits, t1 = kInfBits;
+    uint32_t p0 = 0, p1 = 0;
     if (lane == 0) {
-      w.px[startIdx] = startPos[0];
-      w.py[startIdx] = startPos[1];
-      w.pz[startIdx] = startPos[2];
-      w.cost[startIdx] = 0.f;
-      const float t0 = vdist(startPos, endPos) * 0.999f;
-      w.total[startIdx] = t0;
-      w.parent[startIdx] = 0xffffu;
+      const float tot = vdist(startPos, endPos) * 0.999f;
+      w.nodeA[startIdx] = make_float4(startPos[0], startPos[1], startPos[2], 0.f);
+      w.nodeB[startIdx] = make_uint2(__float_as_uint(tot), 0xffffu);
       w.flags[startIdx] = 1;
-      w.listTotal[0] = t0;
-      w.listPoly[0] = static_cast<uint16_t>(startIdx);
-      w.listPos[startIdx] = 0;
+      t0 = __float_as_uint(tot);
+      p0 = startIdx;
     }
     __syncwarp();
-    int size = 1;
     int nodeCount = 1;
     bool reached = false;
     bool outOfNodes = false;
     int guard = 0;
 
-    while (size > 0) {
+    while (true) {
       if (++guard > 32 * kMaxAStarNodes) {
         *status |= kStatIterCap;
         return BPSN_INF;
       }
-      // ---- pop: warp arg-min over the open list, with tie detection
-      float lmin = BPSN_INF;
-      int lidx = -1;
-      int lcnt = 0;
-      for (int i = lane; i < size; i += 32) {
-        const float t = w.listTotal[i];
-        if (t < lmin) {
-          lmin = t;
-          lidx = i;
-          lcnt = 1;
-        } else if (t == lmin) {
-          lcnt++;
-        }
-      }
-      // totals are non-negative floats, so their bit patterns order like
-      // unsigned integers: one hardware warp reduction finds the minimum
-      const uint32_t mbits = __reduce_min_sync(0xffffffffu, __float_as_uint(lmin));
-      const uint32_t minMask =
-          __ballot_sync(0xffffffffu, __float_as_uint(lmin) == mbits && lidx >= 0);
-      if (minMask == 0u || __popc(minMask) > 1) {
+      BPSN_TICK(tP0);
+      // ---- pop: totals are non-negative floats, so their bit patterns order
+      // like unsigned integers and one warp reduction finds the minimum
+      const uint32_t lm = min(t0, t1);
+      const uint32_t gm = __reduce_min_sync(0xffffffffu, lm);
+      if (gm == kInfBits)
+        break;  // open list empty: the end polygon was not reached
+      const uint32_t b0 = __ballot_sync(0xffffffffu, t0 == gm);
+      const uint32_t b1 = __ballot_sync(0xffffffffu, t1 == gm);
+      if (__popc(b0) + __popc(b1) != 1) {
         *needFallback = true;
         return 0.f;
       }
-      const int winLane = __ffs(minMask) - 1;
-      const int winCnt = __shfl_sync(0xffffffffu, lcnt, winLane);
-      if (winCnt > 1) {
-        *needFallback = true;
-        return 0.f;
+      uint32_t best;
+      if (b0) {
+        const int wl = __ffs(b0) - 1;
+        best = __shfl_sync(0xffffffffu, p0, wl);
+        if (lane == wl)
+          t0 = kInfBits;
+      } else {
+        const int wl = __ffs(b1) - 1;
+        best = __shfl_sync(0xffffffffu, p1, wl);
+        if (lane == wl)
+          t1 = kInfBits;
       }
-      const int slot = __shfl_sync(0xffffffffu, lidx, winLane);
-      const uint32_t best = w.listPoly[slot];
-      __syncwarp();
-      if (lane == 0) {
-        const int last = size - 1;
-        if (slot != last) {
-          const uint16_t lp = w.listPoly[last];
-          w.listPoly[slot] = lp;
-          w.listTotal[slot] = w.listTotal[last];
-          w.listPos[lp] = static_cast<uint16_t>(slot);
-        }
-        w.flags[best] = 2;  // closed
-      }
-      size--;
-      __syncwarp();
-
       if (best == endIdx) {
         reached = true;
         break;
       }
+      if (lane == 0)
+        w.flags[best] = 2;  // closed
+      BPSN_TICK(tP1);
 
-      // ---- expand: one lane per edge of the popped polygon
+      // ---- expand: one lane per edge of the popped polygon.  All loads of a
+      // round are issued before any of them is used.
       const NavPoly* bp = &sc.polys[best];
+      const int li = lane < kVertsPerPoly ? lane : kVertsPerPoly - 1;
       const int nv = bp->vertCount;
-      const float bx = w.px[best], by = w.py[best], bz = w.pz[best];
-      const float bcost = w.cost[best];
-      const uint32_t parentPoly = w.parent[best] == 0xffffu ? 0xffffffffu : w.parent[best];
+      const uint32_t dupFlag = bp->pad;
+      const uint16_t ne = bp->neis[li];
+      const uint16_t va = bp->verts[li];
+      // verts[li + 1] stays inside the record (neis follows verts)
+      const uint16_t vbNext = (&bp->verts[0])[li + 1];
+      const uint16_t vbFirst = bp->verts[0];
+      const float4 bA = w.nodeA[best];
+      const uint32_t bpar = w.nodeB[best].y & 0xffffu;
 
-      bool act = false;
-      uint32_t nei = 0xffff0000u + lane;  // unique dummy for inactive lanes
-      if (lane < nv) {
-        // the staged copy keeps only links to walkable neighbours
-        const uint16_t ne = bp->neis[lane];
-        if (ne && !(ne & kExtLink)) {
-          const uint32_t idx = static_cast<uint32_t>(ne - 1);
-          if (idx != parentPoly) {
-            act = true;
-            nei = idx;
-          }
+      const uint16_t vb = (li + 1 == nv) ? vbFirst : vbNext;
+      bool act = lane < nv && ne != 0 && !(ne & kExtLink) &&
+                 static_cast<uint32_t>(ne - 1) != bpar;
+      uint32_t nei = act ? static_cast<uint32_t>(ne - 1) : best;
+      if (dupFlag & 1) {  // polygon shares more than one edge with some neighbour (rare)
+        const uint32_t grp = __match_any_sync(0xffffffffu, act ? nei : 0xffff0000u + lane);
+        if (act && (__ffs(grp) - 1) != lane) {
+          act = false;  // same neighbour through a lower edge: that lane acts
+          nei = best;
         }
       }
-      if (bp->pad & 1) {  // polygon shares more than one edge with some neighbour (rare)
-        const uint32_t grp = __match_any_sync(0xffffffffu, nei);
-        if (act && (__ffs(grp) - 1) != lane)
-          act = false;  // same neighbour through a lower edge: that lane acts
-      }
+      const float4 nA = w.nodeA[nei];
+      const uint2 nB = w.nodeB[nei];
+      const uint8_t nf = w.flags[nei];
+      const float4 V0 = ldVert4(sc, va);
+      const float4 V1 = ldVert4(sc, vb);
 
-      uint8_t nf = 0;
-      if (act)
-        nf = w.flags[nei];
       const bool isNew = act && nf == 0;
       const uint32_t newMask = __ballot_sync(0xffffffffu, isNew);
       if (nodeCount + __popc(newMask) > kMaxAStarNodes) {
-        outOfNodes = true;  // some getNode() would have failed: status gets DT_OUT_OF_NODES
+        outOfNodes = true;  // some getNode() would have failed: DT_OUT_OF_NODES
         break;
       }
       nodeCount += __popc(newMask);
 
-      bool upd = false;
-      float ntotal = 0.f;
-      if (act) {
-        float nx, ny, nz;
-        if (isNew) {
-          const float* l = sc.verts + 3 * static_cast<size_t>(bp->verts[lane]);
-          const int e1 = (lane + 1 == nv) ? 0 : lane + 1;
-          const float* r = sc.verts + 3 * static_cast<size_t>(bp->verts[e1]);
-          nx = (l[0] + r[0]) * 0.5f;
-          ny = (l[1] + r[1]) * 0.5f;
-          nz = (l[2] + r[2]) * 0.5f;
+      float nx, ny, nz;
+      if (isNew) {
+        nx = (V0.x + V1.x) * 0.5f;
+        ny = (V0.y + V1.y) * 0.5f;
+        nz = (V0.z + V1.z) * 0.5f;
+      } else {
+        nx = nA.x;
+        ny = nA.y;
+        nz = nA.z;
+      }
+      const float bpos[3] = {bA.x, bA.y, bA.z};
+      const float npos[3] = {nx, ny, nz};
+      const float curCost = vdist(bpos, npos) * 1.0f;
+      const float toEnd = vdist(npos, endPos);
+      float cost, heuristic;
+      if (nei == endIdx) {
+        cost = bA.w + curCost + toEnd * 1.0f;
+        heuristic = 0.f;
+      } else {
+        cost = bA.w + curCost;
+        heuristic = toEnd * 0.999f;
+      }
+      const float ntotal = cost + heuristic;
+      const uint32_t ntBits = __float_as_uint(ntotal);
+      const bool upd = act && (isNew || !(ntotal >= __uint_as_float(nB.x)));
+      const bool wasOpen = (nf & 1) != 0;
+
+      // ---- open-list bookkeeping
+      uint32_t mySlot = (nB.y >> 16) & 0xffu;
+      uint32_t am = __ballot_sync(0xffffffffu, upd && !wasOpen);
+      uint32_t f0 = __ballot_sync(0xffffffffu, t0 == kInfBits);
+      uint32_t f1 = __ballot_sync(0xffffffffu, t1 == kInfBits);
+      if (__popc(am) > __popc(f0) + __popc(f1)) {
+        *needFallback = true;
+        return 0.f;
+      }
+      while (am) {
+        const int src = __ffs(am) - 1;
+        am &= am - 1;
+        int dst, reg;
+        if (f0) {
+          dst = __ffs(f0) - 1;
+          f0 &= f0 - 1;
+          reg = 0;
         } else {
-          nx = w.px[nei];
-          ny = w.py[nei];
-          nz = w.pz[nei];
+          dst = __ffs(f1) - 1;
+          f1 &= f1 - 1;
+          reg = 1;
         }
-        const float bpos[3] = {bx, by, bz};
-        const float npos[3] = {nx, ny, nz};
-        const float curCost = vdist(bpos, npos) * 1.0f;
-        float cost, heuristic;
-        if (nei == endIdx) {
-          const float endCost = vdist(npos, endPos) * 1.0f;
-          cost = bcost + curCost + endCost;
-          heuristic = 0.f;
-        } else {
-          cost = bcost + curCost;
-          heuristic = vdist(npos, endPos) * 0.999f;
-        }
-        ntotal = cost + heuristic;
-        upd = isNew || !(ntotal >= w.total[nei]);
-        if (upd) {
-          if (isNew) {
-            w.px[nei] = nx;
-            w.py[nei] = ny;
-            w.pz[nei] = nz;
+        const uint32_t nt = __shfl_sync(0xffffffffu, ntBits, src);
+        const uint32_t np = __shfl_sync(0xffffffffu, nei, src);
+        if (lane == dst) {
+          if (reg == 0) {
+            t0 = nt;
+            p0 = np;
+          } else {
+            t1 = nt;
+            p1 = np;
           }
-          w.parent[nei] = static_cast<uint16_t>(best);
-          w.cost[nei] = cost;
-          w.total[nei] = ntotal;
-          w.flags[nei] = 1;  // open (closed bit cleared)
-          if (nf & 1)
-            w.listTotal[w.listPos[nei]] = ntotal;
+        }
+        if (lane == src)
+          mySlot = static_cast<uint32_t>(dst) | (static_cast<uint32_t>(reg) << 5);
+      }
+      uint32_t mm = __ballot_sync(0xffffffffu, upd && wasOpen);
+      while (mm) {
+        const int src = __ffs(mm) - 1;
+        mm &= mm - 1;
+        const uint32_t sl = __shfl_sync(0xffffffffu, mySlot, src);
+        const uint32_t nt = __shfl_sync(0xffffffffu, ntBits, src);
+        if (lane == static_cast<int>(sl & 31u)) {
+          if (sl >> 5)
+            t1 = nt;
+          else
+            t0 = nt;
         }
       }
-      const bool app = upd && !(nf & 1);
-      const uint32_t appMask = __ballot_sync(0xffffffffu, app);
-      if (app) {
-        const int s = size + __popc(appMask & ((1u << lane) - 1u));
-        w.listTotal[s] = ntotal;
-        w.listPoly[s] = static_cast<uint16_t>(nei);
-        w.listPos[nei] = static_cast<uint16_t>(s);
+      if (upd) {
+        w.nodeA[nei] = make_float4(nx, ny, nz, cost);
+        w.nodeB[nei] = make_uint2(ntBits, best | (mySlot << 16));
+        w.flags[nei] = 1;  // open (closed bit cleared)
       }
-      size += __popc(appMask);
       __syncwarp();
+#if defined(BPSN_PHASE_TIMING)
+      {
+        BPSN_TICK(tP2);
+        if (lane == 0) {
+          atomicAdd(&g_phaseCycles[12], static_cast<unsigned long long>(tP1 - tP0));
+          atomicAdd(&g_phaseCycles[13], static_cast<unsigned long long>(tP2 - tP1));
+          atomicAdd(&g_phaseCycles[14], 1ull);
+        }
+      }
+#endif
     }
 
     if (outOfNodes) {
@@ -546,13 +584,13 @@ __device__ __forceinline__ float warpGeodesic(const NavScene& sc, const WarpSlab
       uint32_t cur = endIdx;
       while (cur != 0xffffu && length <= kMaxAStarNodes) {
         length++;
-        cur = w.parent[cur];
+        cur = w.nodeB[cur].y & 0xffffu;
       }
       if (length <= kMaxPathPolys) {
         cur = endIdx;
         for (int i = length - 1; i >= 0; --i) {
-          w.path[i] = cur;
-          cur = w.parent[cur];
+          w.path[i] = static_cast<uint16_t>(cur);
+          cur = w.nodeB[cur].y & 0xffffu;
         }
       }
     }
@@ -565,7 +603,14 @@ __device__ __forceinline__ float warpGeodesic(const NavScene& sc, const WarpSlab
     pathSize = length;
   }
 
-  return warpFunnel(sc, w, lane, startPos, endPos, pathSize, status);
+  BPSN_TICK(tA1);
+  const float dres = warpFunnel(sc, w, lane, startPos, endPos, pathSize, status);
+  BPSN_TICK(tA2);
+  if (lane == 0) {
+    BPSN_PHASE_ADD(2, tA1 - tA0);
+    BPSN_PHASE_ADD(3, tA2 - tA1);
+  }
+  return dres;
 }
 
 // One simulator step for the environments listed per scene (see sim_kernels.cuh
@@ -586,10 +631,16 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
   if (static_cast<uint32_t>(blockIdx.x) * warpsPerBlock >= n)
     return;
 
-  NavScene sc = st.scenes[sceneIdx];
-  const NavScene scGlobal = sc;
+  BPSN_TICK(tS0);
+  const NavScene scGlobal = st.scenes[sceneIdx];
+  NavScene sc = scGlobal;
   const StagedLayout lay = stagedLayout(sc.nverts, sc.npolys, sc.ndtris, sc.ndverts);
   {
+    float4* dv = reinterpret_cast<float4*>(smem + lay.verts);
+    for (int i = threadIdx.x; i < sc.nverts; i += blockDim.x) {
+      const float* v = scGlobal.verts + 3 * static_cast<size_t>(i);
+      dv[i] = make_float4(v[0], v[1], v[2], 0.f);
+    }
     auto copy16 = [&](size_t dstOff, const void* srcPtr, size_t bytes) {
       const uint4* src = reinterpret_cast<const uint4*>(srcPtr);
       uint4* dst = reinterpret_cast<uint4*>(smem + dstOff);
@@ -599,44 +650,52 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
     };
     // every source array is followed by at least 16 bytes of padding in the
     // scene's device allocation, so the rounded-up 16-byte reads stay inside it
-    copy16(lay.verts, scGlobal.verts, static_cast<size_t>(sc.nverts) * 12);
     copy16(lay.polys, scGlobal.polys, static_cast<size_t>(sc.npolys) * sizeof(NavPoly));
     copy16(lay.detail, scGlobal.detail, static_cast<size_t>(sc.npolys) * sizeof(NavDetail));
     copy16(lay.dtris, scGlobal.dtris, static_cast<size_t>(sc.ndtris + 1) * 4);
     copy16(lay.dverts, scGlobal.dverts, static_cast<size_t>(sc.ndverts) * 12);
+    copy16(lay.island, scGlobal.island, static_cast<size_t>(sc.npolys) * 4);
   }
   __syncthreads();
-  // tables for the forward move: an unmodified copy (wall tests look at links
-  // to non-walkable neighbours through the neighbour's flags)
+  {
+    // drop links to neighbours the filter rejects; flag polygons that reach one
+    // neighbour through two edges (each thread edits only its own records'
+    // neis/pad and reads other records' flags)
+    NavPoly* sp = reinterpret_cast<NavPoly*>(smem + lay.polys);
+    for (int i = threadIdx.x; i < sc.npolys; i += blockDim.x) {
+      uint16_t ne[kVertsPerPoly];
+      const int nvp = sp[i].vertCount;
+#pragma unroll
+      for (int j = 0; j < kVertsPerPoly; ++j) {
+        uint16_t v = j < nvp ? sp[i].neis[j] : 0;
+        if (v && !(v & kExtLink) && (sp[v - 1].flags & kFlagWalk) == 0)
+          v = 0;
+        ne[j] = v;
+      }
+      bool dup = false;
+#pragma unroll
+      for (int j = 1; j < kVertsPerPoly; ++j)
+#pragma unroll
+        for (int k = 0; k < j; ++k)
+          if (ne[j] && !(ne[j] & kExtLink) && ne[j] == ne[k])
+            dup = true;
+#pragma unroll
+      for (int j = 0; j < kVertsPerPoly; ++j)
+        sp[i].neis[j] = ne[j];
+      sp[i].pad = dup ? 1 : 0;
+    }
+  }
+  __syncthreads();
   sc.verts = reinterpret_cast<const float*>(smem + lay.verts);
+  sc.vstride = 4;
   sc.polys = reinterpret_cast<const NavPoly*>(smem + lay.polys);
   sc.detail = reinterpret_cast<const NavDetail*>(smem + lay.detail);
   sc.dtris = smem + lay.dtris;
   sc.dverts = reinterpret_cast<const float*>(smem + lay.dverts);
-  // a second polygon table for the search: links to neighbours the filter
-  // rejects are dropped (the search and the funnel never cross them) and
-  // polygons that reach one neighbour through two edges are flagged
-  NavPoly* sp = reinterpret_cast<NavPoly*>(smem + lay.total);
-  for (int i = threadIdx.x; i < sc.npolys; i += blockDim.x) {
-    NavPoly q = sc.polys[i];
-    const int nvp = q.vertCount;
-    for (int j = 0; j < kVertsPerPoly; ++j) {
-      uint16_t v = j < nvp ? q.neis[j] : 0;
-      if (v && !(v & kExtLink) && (sc.polys[v - 1].flags & kFlagWalk) == 0)
-        v = 0;
-      q.neis[j] = v;
-    }
-    bool dup = false;
-    for (int j = 1; j < kVertsPerPoly; ++j)
-      for (int k = 0; k < j; ++k)
-        if (q.neis[j] && !(q.neis[j] & kExtLink) && q.neis[j] == q.neis[k])
-          dup = true;
-    q.pad = dup ? 1 : 0;
-    sp[i] = q;
-  }
-  __syncthreads();
-  NavScene scSearch = sc;
-  scSearch.polys = sp;
+  sc.island = reinterpret_cast<const int32_t*>(smem + lay.island);
+  BPSN_TICK(tS1);
+  if (threadIdx.x == 0)
+    BPSN_PHASE_ADD(0, tS1 - tS0);
 
   uint8_t* slabBase = smem + slabOffset + static_cast<size_t>(warp) * warpGeoSlabBytes(pcap);
   const WarpSlab w = carveSlab(slabBase, pcap);
@@ -651,6 +710,7 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
     q = __shfl_sync(0xffffffffu, q, 0);
     if (q >= n)
       break;
+    BPSN_TICK(tQ0);
     const uint32_t e = g.geoList[base + q];
     const uint32_t f = g.flags[e];
     const bool done = f & 1u, moved = f & 2u;
@@ -658,7 +718,6 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
       if (lane == 0)
         forwardMove(g, sc, e);
       __syncwarp();
-      __threadfence_block();
     }
     const float a[3] = {g.navPos[e], g.navPos[B + e], g.navPos[2 * B + e]};
     const float b[3] = {g.navGoal[e], g.navGoal[B + e], g.navGoal[2 * B + e]};
@@ -666,7 +725,9 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
     const uint32_t bref = g.goalRef[e];
     uint32_t status = 0;
     bool fallback = false;
-    float d = warpGeodesic(scSearch, w, lane, b, bref, a, aref, &status, &fallback);
+    BPSN_TICK(tQ1);
+    float d = warpGeodesic(sc, w, lane, b, bref, a, aref, &status, &fallback);
+    BPSN_TICK(tQ2);
     if (lane == 0) {
       if (fallback) {
         status = 0;
@@ -678,6 +739,12 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
       if (status)
         g.status[e] |= status;
       finishEnv(g, st, e, done, moved, d, seedLo, seedHi);
+      BPSN_TICK(tQ3);
+      BPSN_PHASE_ADD(1, tQ1 - tQ0);
+      BPSN_PHASE_ADD(4, tQ3 - tQ2);
+#if defined(BPSN_PHASE_TIMING)
+      atomicAdd(&g_phaseCycles[5], 1ull);
+#endif
     }
     __syncwarp();
   }

@@ -74,6 +74,7 @@ struct NavScene {
   int32_t nbv;
   int32_t ndverts;
   int32_t ndtris;
+  int32_t vstride;  // floats between consecutive vertices in `verts` (3, or 4 when staged)
   uint32_t refBase;   // salt/tile bits of every polygon ref of this tile
   uint32_t polyMask;  // (1 << polyBits) - 1
   float bmin[3];

@@ -129,6 +129,7 @@ NavScene HostScene::view() const {
   s.nbv = static_cast<int32_t>(bv.size());
   s.ndverts = static_cast<int32_t>(dverts.size() / 3);
   s.ndtris = static_cast<int32_t>(dtris.size() / 4) - 1;  // the array carries one padding entry
+  s.vstride = 3;
   s.refBase = refBase;
   s.polyMask = polyMask;
   for (int k = 0; k < 3; ++k) {
