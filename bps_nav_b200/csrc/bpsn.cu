@@ -10,6 +10,7 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -819,6 +820,84 @@ int32_t bpsn_gae(const float* rewards, float* values, const uint8_t* masks,
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess)
     return fail(nullptr, BPSN_ERR_CUDA, std::string("bpsn_gae launch: ") + cudaGetErrorString(e));
+  return BPSN_OK;
+}
+
+// ---------------------------------------------------------------------------
+// bpsn_gae_static: the same two GAE launches as bpsn_gae, for callers that are
+// not able to provide a device workspace.  The per-block advantage statistics
+// go to a fixed array that is part of the library image, so the call performs
+// no device or host allocation of any kind.
+
+constexpr uint32_t kGaeStaticMaxEnvs = 262144;  // environments per call
+constexpr uint32_t kGaeStaticMaxBlocks = kGaeStaticMaxEnvs / kGaeBlock;
+
+// 2048 x 24 bytes = 48 KB, resident on every GPU that loads this library.
+static __device__ __align__(256) GaeStat g_gaeStaticPartials[kGaeStaticMaxBlocks];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_gaeStaticMutex;
+GaeStat* g_gaeStaticPtr[kMaxDevices] = {};
+}  // namespace
+
+int32_t bpsn_gae_static(const float* rewards, float* values, const uint8_t* masks,
+                        const float* next_value, float* returns, float* advantages, uint32_t T,
+                        uint32_t N, double gamma, double tau, int32_t normalize, float eps,
+                        void* stream) {
+  if (!rewards || !values || !masks || !returns)
+    return fail(nullptr, BPSN_ERR_INVALID_ARG, "bpsn_gae_static: null tensor");
+  if (T == 0 || N == 0)
+    return fail(nullptr, BPSN_ERR_INVALID_ARG, "bpsn_gae_static: T and N must be positive");
+  if (N > kGaeStaticMaxEnvs)
+    return fail(nullptr, BPSN_ERR_INVALID_ARG,
+                "bpsn_gae_static: N = " + std::to_string(N) + " exceeds the built-in scratch (" +
+                    std::to_string(kGaeStaticMaxEnvs) +
+                    " environments per call); use bpsn_gae with a caller-provided workspace");
+  if (normalize && !advantages)
+    return fail(nullptr, BPSN_ERR_INVALID_ARG,
+                "bpsn_gae_static: normalisation needs the advantages output");
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+    return fail(nullptr, BPSN_ERR_CUDA, "bpsn_gae_static: cannot identify the current device");
+  GaeStat* partials = nullptr;
+  {
+    // Once per device, with that device current: turn the array's host-side
+    // symbol into the device address kernels can use.  The symbol itself is
+    // not a device pointer and must never be handed to a kernel.
+    std::lock_guard<std::mutex> lock(g_gaeStaticMutex);
+    if (!g_gaeStaticPtr[dev]) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_gaeStaticPartials);
+      if (e != cudaSuccess || !p)
+        return fail(nullptr, BPSN_ERR_CUDA,
+                    std::string("bpsn_gae_static: cudaGetSymbolAddress: ") + cudaGetErrorString(e));
+      g_gaeStaticPtr[dev] = static_cast<GaeStat*>(p);
+    }
+    partials = g_gaeStaticPtr[dev];
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const uint32_t blocks = blocksFor(N, kGaeBlock);
+  // Every block overwrites its own slot before the second launch reads slots
+  // [0, blocks): nothing in the array has to start at zero.
+  k_gae_scan<<<blocks, kGaeBlock, 0, s>>>(rewards, values, masks, next_value, returns, advantages,
+                                          T, N, static_cast<float>(gamma),
+                                          static_cast<float>(gamma * tau),
+                                          normalize ? partials : nullptr);
+  if (normalize) {
+    const size_t total = static_cast<size_t>(T) * N;
+    uint32_t nb = static_cast<uint32_t>((total + 256 * 4 - 1) / (256 * 4));
+    if (nb > 148 * 8)
+      nb = 148 * 8;
+    if (nb == 0)
+      nb = 1;
+    k_gae_normalize<<<nb, 256, 0, s>>>(advantages, total, partials, blocks, eps);
+  }
+  e = cudaGetLastError();
+  if (e != cudaSuccess)
+    return fail(nullptr, BPSN_ERR_CUDA,
+                std::string("bpsn_gae_static launch: ") + cudaGetErrorString(e));
   return BPSN_OK;
 }
 

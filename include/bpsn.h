@@ -183,6 +183,32 @@ int32_t bpsn_gae(const float* rewards, float* values, const uint8_t* masks,
                  uint32_t N, double gamma, double tau, int32_t normalize, float eps,
                  void* workspace, void* stream);
 
+/* bpsn_gae without any allocation.  No counterpart in the reference.
+ *
+ * Some hosts of this library may not allocate GPU memory at the moment they
+ * need returns computed: a trainer that sized its memory pool up front and
+ * treats any later cudaMalloc as a bug, an embedding process whose allocator
+ * is owned by another runtime, or code running between two phases that must
+ * not disturb the allocator's state.  bpsn_gae asks such a caller for a device
+ * workspace; this variant does not.  Its per-block scratch is a fixed 48 KB
+ * array inside the library image (every GPU that loads the library carries it
+ * until the process exits), and the call itself performs no cudaMalloc /
+ * cudaFree / host allocation.  Inputs and outputs are still the caller's.
+ *
+ *   - Limit: N <= 262144 environments per call; larger N is rejected with
+ *     BPSN_ERR_INVALID_ARG (use bpsn_gae with your own workspace).
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current).  Make that first call
+ *     outside any stream capture.
+ *   - All calls on a device share the one array.  Two calls whose kernels can
+ *     overlap on the GPU (different streams, no ordering between them) race on
+ *     it; serialise them.  Nothing in the array needs clearing between calls.
+ * Arguments and results are those of bpsn_gae, minus `workspace`. */
+int32_t bpsn_gae_static(const float* rewards, float* values, const uint8_t* masks,
+                        const float* next_value, float* returns, float* advantages, uint32_t T,
+                        uint32_t N, double gamma, double tau, int32_t normalize, float eps,
+                        void* stream);
+
 const char* bpsn_last_error(const bpsn_sim* sim);
 /* Library build identification, e.g. "bpsn sm_100a". */
 const char* bpsn_version(void);
