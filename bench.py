@@ -211,12 +211,10 @@ def run_ours(args):
     import torch
     import torch.distributed as dist
 
-    from bps_nav_b200 import bps_sim, rollout
+    from bps_nav_b200 import bps_sim, dist_utils, rollout
     from bps_nav_b200.dataset import Scene
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
+    rank, world, local = dist_utils.rank_info()
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py needs a CUDA device: the library has no CPU path")
     torch.cuda.set_device(local)
@@ -234,11 +232,7 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     def max_over_ranks(x):
-        if world > 1:
-            t = torch.tensor([x], dtype=torch.float64, device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            return float(t.item())
-        return x
+        return dist_utils.max_over_ranks(x, dev)
 
     rewards = torch.zeros(T + 1, N, 1, device=dev)
     values = torch.randn(T + 1, N, 1, device=dev)
@@ -250,7 +244,8 @@ def run_ours(args):
 
     # ---------------- device-resident arm
     gen = bps_sim.PointNavRolloutGenerator.from_scenes([scene], N, gpu_id=local,
-                                                       seed=1000 + rank, host_mirrors=False)
+                                                       seed=dist_utils.shard_seed(1000, rank, N),
+                                                       host_mirrors=False)
     info = gen.scene_info(0)
     gen.reset(0)
     acts = torch.from_numpy(draw_actions(((W + K) * T, N), args.mix, 7 + rank)).to(dev)
@@ -342,7 +337,8 @@ def run_ours(args):
     e2e = None
     if not args.no_e2e:
         gen2 = bps_sim.PointNavRolloutGenerator.from_scenes([scene], N, gpu_id=local,
-                                                           seed=1000 + rank, host_mirrors=True)
+                                                           seed=dist_utils.shard_seed(1000, rank, N),
+                                                           host_mirrors=True)
         gen2.reset(0)
         hacts = draw_actions(((W + K) * T, N), args.mix, 7 + rank)
         h_rew = torch.from_numpy(gen2.get_rewards(0)).view(-1, 1)

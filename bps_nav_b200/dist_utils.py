@@ -1,0 +1,40 @@
+"""Multi-GPU plumbing for the environment shards: one process per GPU, no data-path collective.
+
+Environments never interact (reference: ``simulator/simulator.cpp:1626-1644`` touches one env per
+work item; DD-PPO runs one generator per rank with a rank-offset seed,
+``bps_nav/rl/ddppo/algo/ddppo_trainer.py:354-359``), so ranks only meet for a start barrier and to
+agree on the slowest rank's time.
+"""
+import os
+
+
+def rank_info():
+    """(rank, world_size, local_rank) from the torchrun environment (defaults: single process)."""
+    return (int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")),
+            int(os.environ.get("LOCAL_RANK", "0")))
+
+
+def shard_seed(base_seed, rank, envs_per_rank):
+    """Seed of a rank's generator: ``base + rank * envs_per_rank`` as the reference offsets it."""
+    return int(base_seed) + int(rank) * int(envs_per_rank)
+
+
+def max_over_ranks(value, device=None):
+    """Maximum of a python float over all ranks (identity when not distributed)."""
+    import torch
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return float(value)
+    t = torch.tensor([float(value)], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def sum_over_ranks(value, device=None):
+    import torch
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return float(value)
+    t = torch.tensor([float(value)], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())

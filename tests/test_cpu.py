@@ -1,0 +1,326 @@
+"""CPU-only tests (no GPU): the oracle against the golden vectors, host-side logic, and that the
+C-ABI library loads and exports every declared symbol."""
+import ctypes as C
+import os
+import re
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from conftest import GOLD, ROOT, SCENES, scene_path
+
+from oracle import pyoracle
+
+needs_oracle = pytest.mark.skipif(not pyoracle.available(),
+                                  reason="oracle/_ref not built (needs the reference sources)")
+
+HARNESS_DIR = os.path.join(ROOT, "tests", "host_harness")
+HARNESS_LIB = os.path.join(HARNESS_DIR, "_build", "libnav_host_check.so")
+
+
+@pytest.fixture(scope="session")
+def harness():
+    """nav_query.cuh compiled for the host (test harness only)."""
+    src = [os.path.join(HARNESS_DIR, "nav_host_check.cpp"),
+           os.path.join(ROOT, "bps_nav_b200", "csrc", "navmesh_host.cpp")]
+    deps = src + [os.path.join(ROOT, "bps_nav_b200", "csrc", f)
+                  for f in ("nav_query.cuh", "nav_types.h", "navmesh_host.h")]
+    if (not os.path.exists(HARNESS_LIB) or
+            any(os.path.getmtime(d) > os.path.getmtime(HARNESS_LIB) for d in deps)):
+        os.makedirs(os.path.dirname(HARNESS_LIB), exist_ok=True)
+        subprocess.run(["g++", "-O2", "-std=c++17", "-fPIC", "-ffp-contract=off", "-shared"] + src +
+                       ["-o", HARNESS_LIB], check=True)
+    lib = C.CDLL(HARNESS_LIB)
+    lib.hchk_load.restype = C.c_void_p
+    lib.hchk_load.argtypes = [C.c_char_p, C.c_char_p, C.c_int]
+    lib.hchk_free.argtypes = [C.c_void_p]
+    lib.hchk_info.argtypes = [C.c_void_p, C.POINTER(C.c_int)]
+    return lib
+
+
+def _p(a, t):
+    return a.ctypes.data_as(C.POINTER(t))
+
+
+def _same(a, b):
+    return ((a == b) | (np.isnan(a) & np.isnan(b))).all()
+
+
+# ------------------------------------------------------------------ oracle vs golden vectors
+
+@needs_oracle
+@pytest.mark.parametrize("name", ["c0", "c1", "m03"])
+def test_reference_pathfinder_reproduces_golden_queries(name):
+    q = np.load(os.path.join(GOLD, f"queries_{name}.npz"))
+    nav = pyoracle.RefNav(scene_path(name))
+    xyz, ref = nav.snap(q["snap_in"])
+    assert np.array_equal(ref.astype(np.uint32), q["snap_ref"]) and _same(xyz, q["snap_xyz"])
+    xyz, ref = nav.try_step(q["step_start"], q["step_start_ref"].astype(np.uint64), q["step_end"])
+    assert np.array_equal(ref.astype(np.uint32), q["step_ref"]) and _same(xyz, q["step_xyz"])
+    d = nav.geodesic(q["geo_a"], q["geo_a_ref"].astype(np.uint64), q["geo_b"],
+                     q["geo_b_ref"].astype(np.uint64))
+    assert _same(d, q["geo_dist"])
+    nav.close()
+
+
+@needs_oracle
+@pytest.mark.parametrize("fname,mix", [("c0_traj.npz", "uniform"), ("c0_policy_traj.npz", "policy")])
+def test_oracle_simulator_reproduces_golden_trajectory(fname, mix):
+    g = np.load(os.path.join(GOLD, fname))
+    eps = np.load(os.path.join(SCENES, "c0.episodes.npy"))
+    steps, n = g["actions"].shape
+    # the action stream is a pure function of (seed, env, t)
+    acts = pyoracle.philox_actions(steps, n, int(g["act_seed"]), mix)
+    assert np.array_equal(acts, g["actions"].astype(np.int64))
+    sim = pyoracle.OracleSim([(scene_path("c0"), eps)], n, int(g["seed"]), threads=2)
+    sim.reset()
+    assert _same(sim.polars, g["polar0"])
+    for t in range(steps):
+        assert sim.step(acts[t]) == 0
+        assert np.array_equal(sim.masks, g["mask"][t])
+        assert _same(sim.rewards, g["reward"][t]) and _same(sim.infos, g["info"][t])
+        assert _same(sim.polars, g["polar"][t])
+    st = sim.state()
+    for k in ("nav_poly", "goal_poly", "step", "episode", "reset_count"):
+        assert np.array_equal(st[k], g[f"s{steps}_{k}"])
+    sim.close()
+
+
+@needs_oracle
+def test_oracle_rejects_unknown_action():
+    eps = np.load(os.path.join(SCENES, "c0.episodes.npy"))
+    sim = pyoracle.OracleSim([(scene_path("c0"), eps)], 4, 1)
+    sim.reset()
+    assert sim.step(np.array([0, 1, 7, 2], np.int64)) == -1
+    sim.close()
+
+
+def test_gae_restatement_matches_reference_python_fixture():
+    g = np.load(os.path.join(GOLD, "gae_ref.npz"))
+    for tag in ("small", "c2"):
+        r, v, m = g[f"{tag}_rewards"][..., 0], g[f"{tag}_values"][..., 0], g[f"{tag}_masks"][..., 0]
+        T = r.shape[0] - 1
+        ret, adv, _ = pyoracle.gae_reference(r, v, m, g[f"{tag}_next_value"][:, 0], 0.99, 0.95)
+        assert np.array_equal(ret[:T], g[f"{tag}_returns"][:T, :, 0])  # bit-exact
+        assert np.array_equal(adv, g[f"{tag}_adv"][..., 0])
+        _, advn, _ = pyoracle.gae_reference(r, v, m, g[f"{tag}_next_value"][:, 0], 0.99, 0.95,
+                                            normalize=True)
+        assert np.allclose(advn, g[f"{tag}_adv_norm"][..., 0], rtol=1e-5, atol=2e-6)
+
+
+def test_philox_known_answers():
+    # Random123 known-answer vectors for philox4x32-10
+    out = pyoracle._philox4x32(0, 0, 0, 0, 0, 0)
+    assert [int(x) for x in out] == [0x6627e8d5, 0xe169c58d, 0xbc57ac4c, 0x9b00dbd8]
+    out = pyoracle._philox4x32(0xffffffff, 0xffffffff, 0xffffffff, 0xffffffff, 0xffffffff, 0xffffffff)
+    assert [int(x) for x in out] == [0x408f276d, 0x41c83b0e, 0xa20bc7c6, 0x6d5451fd]
+    if pyoracle.available():
+        lib = pyoracle.sim_lib()
+        o = (C.c_uint32 * 4)()
+        lib.osim_philox(0x243f6a88, 0x85a308d3, 0x13198a2e, 0x03707344, 0xa4093822, 0x299f31d0, o)
+        assert list(o) == [0xd16cfe09, 0x94fdcceb, 0x5001e420, 0x24126ea1]
+
+
+# ------------------------------------------------------------------ host-compiled device functions
+
+@needs_oracle
+@pytest.mark.parametrize("name", ["c0", "c1", "m03"])
+def test_query_functions_bit_exact_on_host(harness, name):
+    q = np.load(os.path.join(GOLD, f"queries_{name}.npz"))
+    err = C.create_string_buffer(256)
+    h = C.c_void_p(harness.hchk_load(scene_path(name).encode(), err, 256))
+    assert h.value, err.value
+    n = len(q["snap_in"])
+    xyz = np.zeros((n, 3), np.float32)
+    ref = np.zeros(n, np.uint32)
+    harness.hchk_snap_batch(h, n, _p(np.ascontiguousarray(q["snap_in"]), C.c_float),
+                            _p(xyz, C.c_float), _p(ref, C.c_uint32))
+    assert np.array_equal(ref, q["snap_ref"]) and _same(xyz, q["snap_xyz"])
+    m = len(q["step_start"])
+    xyz = np.zeros((m, 3), np.float32)
+    ref = np.zeros(m, np.uint32)
+    harness.hchk_try_step_batch(h, m, _p(np.ascontiguousarray(q["step_start"]), C.c_float),
+                                _p(np.ascontiguousarray(q["step_start_ref"]), C.c_uint32),
+                                _p(np.ascontiguousarray(q["step_end"]), C.c_float),
+                                _p(xyz, C.c_float), _p(ref, C.c_uint32))
+    assert np.array_equal(ref, q["step_ref"]) and _same(xyz, q["step_xyz"])
+    d = np.zeros(m, np.float32)
+    st = np.zeros(m, np.uint32)
+    harness.hchk_geodesic_batch(h, m, _p(np.ascontiguousarray(q["geo_a"]), C.c_float),
+                                _p(np.ascontiguousarray(q["geo_a_ref"]), C.c_uint32),
+                                _p(np.ascontiguousarray(q["geo_b"]), C.c_float),
+                                _p(np.ascontiguousarray(q["geo_b_ref"]), C.c_uint32),
+                                _p(d, C.c_float), _p(st, C.c_uint32))
+    assert _same(d, q["geo_dist"])
+    harness.hchk_free(h)
+
+
+def test_navmesh_parser_rejects_bad_input(harness, tmp_path):
+    good = open(scene_path("c0"), "rb").read()
+    cases = {
+        "short": good[:20],
+        "magic": b"XXXX" + good[4:],
+        "version": good[:4] + (2).to_bytes(4, "little") + good[8:],
+        "truncated_tile": good[:len(good) // 2],
+        "tile_magic": good[:48] + b"\0\0\0\0" + good[52:],
+        "two_tiles": good[:8] + (2).to_bytes(4, "little") + good[12:] + good[40:],
+    }
+    for name, blob in cases.items():
+        p = tmp_path / f"{name}.navmesh"
+        p.write_bytes(blob)
+        err = C.create_string_buffer(256)
+        h = harness.hchk_load(str(p).encode(), err, 256)
+        assert not h, name
+        assert err.value.startswith(b"navmesh:"), (name, err.value)
+    err = C.create_string_buffer(256)
+    h = C.c_void_p(harness.hchk_load(scene_path("c0").encode(), err, 256))
+    info = (C.c_int * 6)()
+    harness.hchk_info(h, info)
+    assert info[0] == 87 and info[3] == 0 and info[4] == 23  # polys, disabled, islands
+    harness.hchk_free(h)
+
+
+# ------------------------------------------------------------------ C ABI
+
+def test_library_exports_every_declared_symbol():
+    from bps_nav_b200 import _lib
+    hdr = open(os.path.join(ROOT, "include", "bpsn.h")).read()
+    declared = set(re.findall(r"\b(bpsn_[a-z_0-9]+)\s*\(", hdr))
+    declared -= {"bpsn_sim"}
+    assert declared == set(_lib.SYMBOLS), declared ^ set(_lib.SYMBOLS)
+    lib = _lib.load()
+    for name in declared:
+        assert getattr(lib, name) is not None
+    assert b"sm_100a" in lib.bpsn_version()
+
+
+def test_create_validates_arguments_and_needs_a_gpu():
+    import torch
+    from bps_nav_b200 import _lib as L
+    lib = L.load()
+    h = C.c_void_p()
+    bad = L.Config(gpu_id=0, num_envs=10, num_groups=1, num_scenes=3, seed=0, flags=0, reserved=0)
+    assert lib.bpsn_create(C.byref(bad), C.byref(h)) == L.ERR_INVALID_ARG
+    assert b"multiple" in lib.bpsn_last_error(None)
+    assert lib.bpsn_create(None, C.byref(h)) == L.ERR_INVALID_ARG
+    if not torch.cuda.is_available():
+        ok = L.Config(gpu_id=0, num_envs=8, num_groups=1, num_scenes=1, seed=0, flags=0, reserved=0)
+        assert lib.bpsn_create(C.byref(ok), C.byref(h)) == L.ERR_NO_DEVICE
+        # the Python mirror surfaces it as an exception: no silent CPU fallback
+        from bps_nav_b200 import bps_sim
+        from conftest import load_scene
+        with pytest.raises(RuntimeError, match="BPSN_ERR_NO_DEVICE"):
+            bps_sim.PointNavRolloutGenerator.from_scenes([load_scene("c0")], 8)
+        from bps_nav_b200 import rollout
+        t = torch.zeros(3, 4, 1)
+        with pytest.raises(RuntimeError, match="CUDA"):
+            rollout.compute_returns(t, t, t.bool(), t, None, 2, 0.99, 0.95)
+    assert lib.bpsn_gae(None, None, None, None, None, None, 1, 1, 0.99, 0.95, 0, 1e-5, None,
+                        None) == L.ERR_INVALID_ARG
+
+
+def test_unimplemented_tasks_raise():
+    from bps_nav_b200 import bps_sim
+    from conftest import load_scene
+    for cls in (bps_sim.FleeRolloutGenerator, bps_sim.ExplorationRolloutGenerator):
+        with pytest.raises(NotImplementedError):
+            cls.from_scenes([load_scene("c0")], 8)
+
+
+# ------------------------------------------------------------------ dataset / host logic
+
+def test_dataset_round_trip(tmp_path):
+    from bps_nav_b200 import dataset
+    from conftest import load_scene
+    scenes = [load_scene("c0"), load_scene("m15")]
+    scenes[0].episodes = scenes[0].episodes[:17]
+    scenes[1].episodes = scenes[1].episodes[:5]
+    dataset.write_dataset(scenes, str(tmp_path / "eps"), str(tmp_path / "assets"))
+    back = dataset.load_dataset(str(tmp_path / "eps"), str(tmp_path / "assets"))
+    assert [len(s.episodes) for s in back] == [17, 5]
+    for a, b in zip(scenes, back):
+        assert os.path.exists(b.navmesh_path)
+        for f in ("start_position", "start_rotation", "goal"):
+            assert np.array_equal(a.episodes[f], b.episodes[f])
+    with pytest.raises(RuntimeError):
+        dataset.load_dataset(str(tmp_path / "assets"), str(tmp_path / "assets"))
+
+
+def test_active_scene_selection_matches_std_mt19937(tmp_path):
+    """Selection sampling of simulator.cpp:1518-1534 against the C++ standard library itself."""
+    from bps_nav_b200 import dataset
+    src = tmp_path / "sel.cpp"
+    src.write_text(r'''
+#include <cstdio>
+#include <cstdlib>
+#include <random>
+#include <vector>
+int main(int argc, char** argv) {
+  unsigned long long seed = strtoull(argv[1], 0, 10); unsigned n = atoi(argv[2]), k = atoi(argv[3]);
+  std::mt19937 rgen(seed); std::uniform_real_distribution<> d(0.f, 1.f); std::vector<unsigned> act;
+  for (unsigned i = 0; i < n && act.size() < k; i++) {
+    float w = d(rgen);
+    if (w * float(n - i) < float(k - act.size())) act.push_back(i);
+  }
+  for (unsigned a : act) printf("%u ", a);
+  return 0;
+}''')
+    exe = tmp_path / "sel"
+    subprocess.run(["g++", "-O1", "-o", str(exe), str(src)], check=True)
+    for seed, n, k in [(0, 10, 3), (5, 72, 16), (12345, 64, 64), (7, 100, 1)]:
+        out = subprocess.run([str(exe), str(seed), str(n), str(k)], capture_output=True, text=True,
+                             check=True).stdout.split()
+        active, inactive = dataset.select_active_scenes(n, k, seed)
+        assert active == [int(x) for x in out]
+        assert sorted(active + inactive) == list(range(n))
+
+
+def test_bench_reference_arm_prints_contract_line():
+    if not pyoracle.available():
+        pytest.skip("oracle not built")
+    import json
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference",
+                          "--steps", "1", "--warmup", "0", "--envs", "256", "--cpu-seconds", "0.2"],
+                         capture_output=True, text=True, check=True).stdout.strip().splitlines()[-1]
+    line = json.loads(out)
+    assert line["impl"] == "reference" and line["value"] > 0
+    assert line["cpu_baseline"]["cores"] >= 1 and line["e2e"]["h2d_bytes_per_step"] == 0
+
+
+# ------------------------------------------------------------------ N > 1 plumbing (gloo, CPU)
+
+def _dist_worker(rank, world, port, q):
+    import torch.distributed as dist
+    from bps_nav_b200 import dist_utils
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank),
+                      WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    assert dist_utils.rank_info() == (rank, world, rank)
+    dist.barrier()
+    mx = dist_utils.max_over_ranks(10.0 + rank)
+    sm = dist_utils.sum_over_ranks(4096)
+    seed = dist_utils.shard_seed(1000, rank, 4096)
+    # each rank's episode stream is its own: same env index, different key
+    r = pyoracle._philox4x32(np.arange(8), 0, 0, 0, seed & 0xffffffff, seed >> 32)[0]
+    q.put((rank, mx, sm, seed, r.tolist()))
+    dist.destroy_process_group()
+
+
+def test_two_rank_sharding_gloo():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + os.getpid() % 2000
+    procs = [ctx.Process(target=_dist_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    assert [r[1] for r in res] == [11.0, 11.0]          # max over ranks, same on every rank
+    assert [r[2] for r in res] == [8192.0, 8192.0]      # whole-job env count
+    assert res[0][3] == 1000 and res[1][3] == 1000 + 4096
+    assert res[0][4] != res[1][4]
