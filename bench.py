@@ -255,10 +255,9 @@ def run_ours(args):
     def window(k):
         base = k * T
         for t in range(T):
-            gen.step_start(0, acts[base + t])
+            # reward / mask of step t land directly in rows t / t+1 of the rollout tensors
+            gen.step_start(0, acts[base + t], reward_out=rewards[t], mask_out=masks[t + 1])
             gen.step_end(0)
-            rewards[t, :, 0].copy_(r_view)
-            masks[t + 1, :, 0].copy_(m_view)
         rollout.compute_returns(rewards, values, masks, returns, next_value, T, GAMMA, TAU,
                                 advantages=adv, normalize=True)
 
@@ -341,8 +340,8 @@ def run_ours(args):
                                                            host_mirrors=True)
         gen2.reset(0)
         hacts = draw_actions(((W + K) * T, N), args.mix, 7 + rank)
-        h_rew = torch.from_numpy(gen2.get_rewards(0)).view(-1, 1)
-        h_mask = torch.from_numpy(gen2.get_masks(0)).view(-1, 1)
+        h_rew = gen2.get_rewards(0)
+        h_mask = gen2.get_masks(0)
         h_polar = gen2.get_polars(0)
         h_info = gen2.get_infos(0)
         sink = 0.0
@@ -351,11 +350,12 @@ def run_ours(args):
             nonlocal sink
             base = k * T
             for t in range(T):
-                gen2.step_start(0, hacts[base + t])
+                # numpy actions in (H2D), numpy reward / mask / info / polar out (D2H) every
+                # step; the rollout rows are filled on the device by the same launch
+                gen2.step_start(0, hacts[base + t], reward_out=rewards[t], mask_out=masks[t + 1])
                 gen2.step_end(0)
-                rewards[t].copy_(h_rew, non_blocking=True)       # rollouts.insert: host -> device
-                masks[t + 1].copy_(h_mask.bool(), non_blocking=True)
-                sink += float(h_polar[0, 0]) + float(h_info["distanceToGoal"][0])
+                sink += (float(h_polar[0, 0]) + float(h_info["distanceToGoal"][0]) +
+                         float(h_rew[0]) + float(h_mask[0]))
             rollout.compute_returns(rewards, values, masks, returns, next_value, T, GAMMA, TAU,
                                     advantages=adv, normalize=True)
             return float(adv.mean().item())  # device -> host read of the window's result
@@ -368,8 +368,8 @@ def run_ours(args):
             window_e2e(W + k)
         barrier()
         e2e_s = max_over_ranks(time.perf_counter() - t0)
-        h2d = T * (N * 8 + N * 4 + N)            # actions, then reward + mask into the rollout
-        d2h = T * (N * 4 + N + N * 12 + N * 8) + 4
+        h2d = T * (N * 8)                         # int64 actions
+        d2h = T * (N * 4 + N + N * 12 + N * 8) + 4  # reward, mask, info, polar (+ window result)
         e2e = {"value": world * N * T * K / e2e_s, "unit": "env-steps/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                "ms_per_step": 1000 * e2e_s / K,

@@ -164,17 +164,31 @@ class _RolloutGenerator:
     def reset(self, group_idx):
         L.check(self._lib.bpsn_reset(self._h, group_idx, self._stream()), self._h)
 
-    def step_start(self, group_idx, actions):
+    def step_start(self, group_idx, actions, reward_out=None, mask_out=None):
         """``actions``: C-contiguous int64 numpy array of length ``envs_per_group`` (reference
-        signature), or a CUDA int64 tensor of the same length (device-resident fast path)."""
+        signature), or a CUDA int64 tensor of the same length (device-resident fast path).
+
+        ``reward_out`` / ``mask_out`` (added): contiguous CUDA tensors of ``envs_per_group``
+        float32 / 1-byte elements that also receive this step's reward and mask, e.g.
+        ``rollouts.rewards[t]`` and ``rollouts.masks[t + 1]``."""
+        ro = reward_out.data_ptr() if reward_out is not None else None
+        mo = mask_out.data_ptr() if mask_out is not None else None
+        if reward_out is not None and (reward_out.numel() != self.envs_per_group or
+                                       reward_out.element_size() != 4 or
+                                       not reward_out.is_contiguous() or not reward_out.is_cuda):
+            raise RuntimeError("reward_out must be a contiguous CUDA float32 tensor of B elements")
+        if mask_out is not None and (mask_out.numel() != self.envs_per_group or
+                                     mask_out.element_size() != 1 or
+                                     not mask_out.is_contiguous() or not mask_out.is_cuda):
+            raise RuntimeError("mask_out must be a contiguous CUDA 1-byte tensor of B elements")
         if isinstance(actions, np.ndarray):
             if actions.dtype != np.int64 or not actions.flags.c_contiguous:
                 actions = np.ascontiguousarray(actions, dtype=np.int64)
             if actions.shape[0] != self.envs_per_group:
                 raise RuntimeError("actions length must equal the number of envs in the group")
-            self._keepalive = [actions]
-            L.check(self._lib.bpsn_step_start(self._h, group_idx, actions.ctypes.data, L.MEM_HOST,
-                                              self._stream()), self._h)
+            self._keepalive = [actions, reward_out, mask_out]
+            L.check(self._lib.bpsn_step_start_ex(self._h, group_idx, actions.ctypes.data,
+                                                 L.MEM_HOST, self._stream(), ro, mo), self._h)
         else:
             import torch
             if not (isinstance(actions, torch.Tensor) and actions.is_cuda and
@@ -184,8 +198,8 @@ class _RolloutGenerator:
             if actions.numel() != self.envs_per_group:
                 raise RuntimeError("actions length must equal the number of envs in the group")
             self._keepalive = [actions]
-            L.check(self._lib.bpsn_step_start(self._h, group_idx, actions.data_ptr(),
-                                              L.MEM_DEVICE, self._stream()), self._h)
+            L.check(self._lib.bpsn_step_start_ex(self._h, group_idx, actions.data_ptr(),
+                                                 L.MEM_DEVICE, self._stream(), ro, mo), self._h)
         self._num_steps_taken += self.envs_per_group
 
     def step_end(self, group_idx):

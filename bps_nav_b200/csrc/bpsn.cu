@@ -38,7 +38,9 @@ struct Group {
   void* stateBlob = nullptr;
   size_t stateBytes = 0;
   // pinned host mirrors of the four result arrays
-  float* hReward = nullptr;
+  uint8_t* hOut = nullptr;   // one pinned block mirroring [reward | mask | info | polar]
+  size_t outBytes = 0;       // bytes from d.reward to the end of d.polar
+  float* hReward = nullptr;  // views into hOut
   uint8_t* hMask = nullptr;
   float* hInfo = nullptr;
   float* hPolar = nullptr;
@@ -125,6 +127,44 @@ int32_t uploadScene(bpsn_sim* sim, DeviceScene& ds) {
   const size_t oDtris = place(h.dtris.size());
   const size_t oBv = place(h.bv.size() * sizeof(NavBVNode) + 16);
   const size_t oIsland = place(h.island.size() * sizeof(int32_t));
+  // shared-memory image for k_step_warp (layout = stagedLayout())
+  const NavScene hv = h.view();
+  const StagedLayout lay = stagedLayout(hv.nverts, hv.npolys, hv.ndtris, hv.ndverts);
+  std::vector<uint8_t> img(lay.total, 0);
+  {
+    float* v4 = reinterpret_cast<float*>(img.data() + lay.verts);
+    for (int i = 0; i < hv.nverts; ++i) {
+      v4[4 * i + 0] = h.verts[3 * i + 0];
+      v4[4 * i + 1] = h.verts[3 * i + 1];
+      v4[4 * i + 2] = h.verts[3 * i + 2];
+      v4[4 * i + 3] = 0.f;
+    }
+    NavPoly* sp = reinterpret_cast<NavPoly*>(img.data() + lay.polys);
+    for (int i = 0; i < hv.npolys; ++i) {
+      NavPoly q = h.polys[i];
+      // links to neighbours the filter rejects do not exist for the search and are
+      // walls for moveAlongSurface either way
+      for (int j = 0; j < kVertsPerPoly; ++j) {
+        uint16_t v = j < q.vertCount ? q.neis[j] : 0;
+        if (v && !(v & kExtLink) && (h.polys[v - 1].flags & kFlagWalk) == 0)
+          v = 0;
+        q.neis[j] = v;
+      }
+      bool dup = false;
+      for (int j = 1; j < kVertsPerPoly; ++j)
+        for (int k = 0; k < j; ++k)
+          if (q.neis[j] && !(q.neis[j] & kExtLink) && q.neis[j] == q.neis[k])
+            dup = true;
+      q.pad = dup ? 1 : 0;
+      sp[i] = q;
+    }
+    memcpy(img.data() + lay.detail, h.detail.data(), h.detail.size() * sizeof(NavDetail));
+    memcpy(img.data() + lay.dtris, h.dtris.data(), h.dtris.size());
+    if (!h.dverts.empty())
+      memcpy(img.data() + lay.dverts, h.dverts.data(), h.dverts.size() * sizeof(float));
+    memcpy(img.data() + lay.island, h.island.data(), h.island.size() * sizeof(int32_t));
+  }
+  const size_t oStaged = place(img.size());
   BPSN_CUDA(sim, cudaMalloc(&ds.blob, off));
   uint8_t* base = static_cast<uint8_t*>(ds.blob);
   auto up = [&](size_t o, const void* src, size_t bytes) -> cudaError_t {
@@ -139,6 +179,7 @@ int32_t uploadScene(bpsn_sim* sim, DeviceScene& ds) {
   BPSN_CUDA(sim, up(oDtris, h.dtris.data(), h.dtris.size()));
   BPSN_CUDA(sim, up(oBv, h.bv.data(), h.bv.size() * sizeof(NavBVNode)));
   BPSN_CUDA(sim, up(oIsland, h.island.data(), h.island.size() * sizeof(int32_t)));
+  BPSN_CUDA(sim, up(oStaged, img.data(), img.size()));
   NavScene s = h.view();
   s.verts = reinterpret_cast<const float*>(base + oVerts);
   s.polys = reinterpret_cast<const NavPoly*>(base + oPolys);
@@ -147,6 +188,8 @@ int32_t uploadScene(bpsn_sim* sim, DeviceScene& ds) {
   s.dtris = reinterpret_cast<const uint8_t*>(base + oDtris);
   s.bv = reinterpret_cast<const NavBVNode*>(base + oBv);
   s.island = reinterpret_cast<const int32_t*>(base + oIsland);
+  s.staged = base + oStaged;
+  s.stagedBytes = static_cast<uint32_t>(img.size());
   ds.dev = s;
   return BPSN_OK;
 }
@@ -294,18 +337,20 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
   setField(BPSN_FIELD_INIT_DIST, d.initDist, B * f);
   setField(BPSN_FIELD_SCENE, d.scene, B * u);
 
-  BPSN_CUDA(sim, cudaMalloc(&g.scratch, sizeof(AStarScratch) * static_cast<size_t>(B)));
+  if (!g.warpGeo)  // per-slot A* scratch is only used by the generic (global-memory) kernel
+    BPSN_CUDA(sim, cudaMalloc(&g.scratch, sizeof(AStarScratch) * static_cast<size_t>(B)));
   BPSN_CUDA(sim, cudaMalloc(&g.dActions, sizeof(int64_t) * B));
   BPSN_CUDA(sim, cudaMallocHost(&g.hActions, sizeof(int64_t) * B));
   if (sim->cfg.flags & BPSN_FLAG_HOST_MIRRORS) {
-    BPSN_CUDA(sim, cudaMallocHost(&g.hReward, B * f));
-    BPSN_CUDA(sim, cudaMallocHost(&g.hMask, B));
-    BPSN_CUDA(sim, cudaMallocHost(&g.hInfo, 3 * B * f));
-    BPSN_CUDA(sim, cudaMallocHost(&g.hPolar, 2 * B * f));
-    memset(g.hReward, 0, B * f);
-    memset(g.hMask, 0, B);
-    memset(g.hInfo, 0, 3 * B * f);
-    memset(g.hPolar, 0, 2 * B * f);
+    // the four result arrays are adjacent in the state block: one pinned
+    // block with the same relative layout lets a step publish them in one copy
+    g.outBytes = (oPolar + 2 * B * f) - oReward;
+    BPSN_CUDA(sim, cudaMallocHost(&g.hOut, g.outBytes));
+    memset(g.hOut, 0, g.outBytes);
+    g.hReward = reinterpret_cast<float*>(g.hOut);
+    g.hMask = g.hOut + (oMask - oReward);
+    g.hInfo = reinterpret_cast<float*>(g.hOut + (oInfo - oReward));
+    g.hPolar = reinterpret_cast<float*>(g.hOut + (oPolar - oReward));
   }
   BPSN_CUDA(sim, cudaEventCreateWithFlags(&g.done, cudaEventDisableTiming));
   return BPSN_OK;
@@ -316,14 +361,11 @@ int32_t finishLaunch(bpsn_sim* sim, Group& g, cudaStream_t s, bool polarOnly) {
   if (sim->cfg.flags & BPSN_FLAG_HOST_MIRRORS) {
     const uint32_t B = g.dev.B;
     if (!polarOnly) {
-      BPSN_CUDA(sim, cudaMemcpyAsync(g.hReward, g.dev.reward, B * sizeof(float),
-                                     cudaMemcpyDeviceToHost, s));
-      BPSN_CUDA(sim, cudaMemcpyAsync(g.hMask, g.dev.mask, B, cudaMemcpyDeviceToHost, s));
-      BPSN_CUDA(sim, cudaMemcpyAsync(g.hInfo, g.dev.info, 3 * B * sizeof(float),
+      BPSN_CUDA(sim, cudaMemcpyAsync(g.hOut, g.dev.reward, g.outBytes, cudaMemcpyDeviceToHost, s));
+    } else {
+      BPSN_CUDA(sim, cudaMemcpyAsync(g.hPolar, g.dev.polar, 2 * B * sizeof(float),
                                      cudaMemcpyDeviceToHost, s));
     }
-    BPSN_CUDA(sim, cudaMemcpyAsync(g.hPolar, g.dev.polar, 2 * B * sizeof(float),
-                                   cudaMemcpyDeviceToHost, s));
   }
   BPSN_CUDA(sim, cudaEventRecord(g.done, s));
   return BPSN_OK;
@@ -395,10 +437,7 @@ int32_t bpsn_destroy(bpsn_sim* sim) {
     cudaFree(g.fallbackScratch);
     cudaFree(g.dActions);
     cudaFreeHost(g.hActions);
-    cudaFreeHost(g.hReward);
-    cudaFreeHost(g.hMask);
-    cudaFreeHost(g.hInfo);
-    cudaFreeHost(g.hPolar);
+    cudaFreeHost(g.hOut);
     if (g.done)
       cudaEventDestroy(g.done);
     for (cudaEvent_t ev : g.prof)
@@ -578,6 +617,12 @@ int32_t bpsn_reset(bpsn_sim* sim, uint32_t group, void* stream) {
 
 int32_t bpsn_step_start(bpsn_sim* sim, uint32_t group, const int64_t* actions,
                         int32_t actions_mem, void* stream) {
+  return bpsn_step_start_ex(sim, group, actions, actions_mem, stream, nullptr, nullptr);
+}
+
+int32_t bpsn_step_start_ex(bpsn_sim* sim, uint32_t group, const int64_t* actions,
+                           int32_t actions_mem, void* stream, float* reward_out,
+                           uint8_t* mask_out) {
   if (!sim || !sim->finalized)
     return fail(sim, BPSN_ERR_STATE, "bpsn_step_start: handle not finalized");
   if (group >= sim->groups.size())
@@ -606,17 +651,20 @@ int32_t bpsn_step_start(bpsn_sim* sim, uint32_t group, const int64_t* actions,
   }
   BPSN_CUDA(sim, cudaMemsetAsync(g.dev.counts, 0, 2 * g.numScenesUsed * sizeof(uint32_t), s));
   const bool prof = g.profiling;
+  GroupDev gd = g.dev;
+  gd.rewardOut = reward_out;
+  gd.maskOut = mask_out;
   const uint32_t seedLo = static_cast<uint32_t>(sim->cfg.seed);
   const uint32_t seedHi = static_cast<uint32_t>(sim->cfg.seed >> 32);
   if (prof) cudaEventRecord(g.prof[0], s);
-  k_pre<<<blocksFor(B, 256), 256, 0, s>>>(g.dev, sim->table, dAct, sim->turn, seedLo, seedHi);
+  k_pre<<<blocksFor(B, 256), 256, 0, s>>>(gd, sim->table, dAct, sim->turn, seedLo, seedHi);
   if (prof) cudaEventRecord(g.prof[1], s);
   if (g.warpGeo) {
     k_step_warp<<<dim3(g.geoGridX, g.numScenesUsed), g.warpsPerBlock * 32, g.geoSmem, s>>>(
-        g.dev, sim->table, g.pcap, g.slabOffset, g.fallbackScratch, seedLo, seedHi);
+        gd, sim->table, g.pcap, g.slabOffset, g.fallbackScratch, seedLo, seedHi);
   } else {
     k_step_thread<<<dim3(blocksFor(g.maxSceneEnvs, 128), g.numScenesUsed), 128, 0, s>>>(
-        g.dev, sim->table, g.scratch, seedLo, seedHi);
+        gd, sim->table, g.scratch, seedLo, seedHi);
   }
   if (prof) cudaEventRecord(g.prof[2], s);
   BPSN_CUDA(sim, cudaGetLastError());
@@ -775,12 +823,12 @@ int32_t bpsn_query_geodesic(bpsn_sim* sim, uint32_t scene, uint32_t n, const flo
 
 #if defined(BPSN_PHASE_TIMING)
 // developer builds only (see geo_warp.cuh)
-int32_t bpsn_debug_phase_cycles(unsigned long long* out16, int32_t reset) {
+int32_t bpsn_debug_phase_cycles(unsigned long long* out24, int32_t reset) {
   cudaDeviceSynchronize();
-  if (out16)
-    cudaMemcpyFromSymbol(out16, g_phaseCycles, sizeof(unsigned long long) * 16);
+  if (out24)
+    cudaMemcpyFromSymbol(out24, g_phaseCycles, sizeof(unsigned long long) * 24);
   if (reset) {
-    unsigned long long z[16] = {};
+    unsigned long long z[24] = {};
     cudaMemcpyToSymbol(g_phaseCycles, z, sizeof(z));
   }
   return 0;

@@ -49,13 +49,20 @@ namespace bpsn {
 // spent per phase of k_step_warp, summed over queries, and per-phase maxima.
 // [0] staging  [1] state load + forward move  [2] A*  [3] funnel  [4] finish
 // [5] queries  [6..10] per-phase max  [12] pop cycles [13] expand cycles [14] pops
-__device__ unsigned long long g_phaseCycles[16];
+__device__ unsigned long long g_phaseCycles[24];
 #define BPSN_TICK(var) const long long var = clock64()
-#define BPSN_PHASE_ADD(idx, cycles)                                              \
-  do {                                                                           \
-    atomicAdd(&g_phaseCycles[idx], static_cast<unsigned long long>(cycles));     \
-    atomicMax(&g_phaseCycles[6 + idx], static_cast<unsigned long long>(cycles)); \
-  } while (0)
+struct PhaseAcc {
+  unsigned long long sum[5];
+  unsigned long long mx[5];
+  unsigned long long queries, popCycles, expandCycles, pops;
+  unsigned long long exLoad, exMath, exBook;
+};
+__device__ __forceinline__ void phaseAdd(PhaseAcc* a, int idx, long long cycles) {
+  a->sum[idx] += static_cast<unsigned long long>(cycles);
+  if (static_cast<unsigned long long>(cycles) > a->mx[idx])
+    a->mx[idx] = static_cast<unsigned long long>(cycles);
+}
+#define BPSN_PHASE_ADD(idx, cycles) phaseAdd(pacc, idx, cycles)
 #else
 #define BPSN_TICK(var)
 #define BPSN_PHASE_ADD(idx, cycles)
@@ -115,14 +122,34 @@ __device__ __forceinline__ WarpSlab carveSlab(uint8_t* base, int pcap) {
   return s;
 }
 
-__device__ __forceinline__ float4 ldVert4(const NavScene& sc, uint32_t iv) {
-  return reinterpret_cast<const float4*>(sc.verts)[iv];
+// The staged tables as the search sees them.  Passed by value so that the
+// pointers live in registers: a NavScene whose address escapes to a called
+// function sits in local memory, and every shared-memory store could alias it.
+struct StagedView {
+  const NavPoly* polys;
+  const float4* verts;
+  const int32_t* island;
+  int32_t npolys;
+  uint32_t polyMask;
+  uint32_t refBase;
+};
+
+__device__ __forceinline__ float4 ldVert4(const StagedView& sc, uint32_t iv) {
+  return sc.verts[iv];
+}
+
+__device__ __forceinline__ bool validRef(const StagedView& sc, uint32_t ref) {
+  if (!ref)
+    return false;
+  if ((ref & ~sc.polyMask) != sc.refBase)
+    return false;
+  return (ref & sc.polyMask) < static_cast<uint32_t>(sc.npolys);
 }
 
 // closestPointOnPolyBoundary (DetourNavMeshQuery.cpp:538-586) for the first and
 // the last corridor polygon at once: lanes 0-5 take the edges of the first
 // polygon, lanes 8-13 those of the last.
-__device__ __forceinline__ void warpClosestOnBoundary(const NavScene& sc, int lane,
+__device__ __forceinline__ void warpClosestOnBoundary(const StagedView sc, int lane,
                                                       uint32_t polyA, const float* posA,
                                                       uint32_t polyB, const float* posB,
                                                       float* outA, float* outB) {
@@ -180,7 +207,7 @@ __device__ __forceinline__ void warpClosestOnBoundary(const NavScene& sc, int la
 // Portal end points of every corridor edge are extracted by all lanes first
 // (they only depend on the corridor) into the slab's node arrays, which the
 // finished search no longer needs; lane 0 then walks the funnel.
-__device__ __forceinline__ float warpFunnel(const NavScene& sc, const WarpSlab& w, int lane,
+__device__ __forceinline__ float warpFunnel(const StagedView sc, const WarpSlab w, int lane,
                                             const float* startPos, const float* endPos,
                                             int pathSize, uint32_t* status) {
   float closestStart[3], closestEnd[3];
@@ -333,10 +360,18 @@ __device__ __forceinline__ float warpFunnel(const NavScene& sc, const WarpSlab& 
 // Returns the distance in every lane.  *needFallback is set (uniformly) when
 // the fast path cannot decide the pop order (tie for the minimum) or the
 // register open list is full.
-__device__ __forceinline__ float warpGeodesic(const NavScene& sc, const WarpSlab& w, int lane,
-                                              const float* startPos, uint32_t startRef,
-                                              const float* endPos, uint32_t endRef,
-                                              uint32_t* status, bool* needFallback) {
+__device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSlab w, int lane,
+                                              const float* startPosIn, uint32_t startRef,
+                                              const float* endPosIn, uint32_t endRef,
+                                              uint32_t* status, bool* needFallback
+#if defined(BPSN_PHASE_TIMING)
+                                              , PhaseAcc* pacc
+#endif
+) {
+  // private copies: the caller's arrays are also handed to a non-inlined
+  // function and therefore live in local memory
+  const float startPos[3] = {startPosIn[0], startPosIn[1], startPosIn[2]};
+  const float endPos[3] = {endPosIn[0], endPosIn[1], endPosIn[2]};
   *needFallback = false;
   BPSN_TICK(tA0);
   // (i) trivial path: Eigen isApprox with precision 1e-5
@@ -468,6 +503,7 @@ __device__ __forceinline__ float warpGeodesic(const NavScene& sc, const WarpSlab
       const float4 V0 = ldVert4(sc, va);
       const float4 V1 = ldVert4(sc, vb);
 
+      BPSN_TICK(tE1);
       const bool isNew = act && nf == 0;
       const uint32_t newMask = __ballot_sync(0xffffffffu, isNew);
       if (nodeCount + __popc(newMask) > kMaxAStarNodes) {
@@ -503,6 +539,7 @@ __device__ __forceinline__ float warpGeodesic(const NavScene& sc, const WarpSlab
       const bool upd = act && (isNew || !(ntotal >= __uint_as_float(nB.x)));
       const bool wasOpen = (nf & 1) != 0;
 
+      BPSN_TICK(tE2);
       // ---- open-list bookkeeping
       uint32_t mySlot = (nB.y >> 16) & 0xffu;
       uint32_t am = __ballot_sync(0xffffffffu, upd && !wasOpen);
@@ -552,6 +589,7 @@ __device__ __forceinline__ float warpGeodesic(const NavScene& sc, const WarpSlab
             t0 = nt;
         }
       }
+      BPSN_TICK(tE3);
       if (upd) {
         w.nodeA[nei] = make_float4(nx, ny, nz, cost);
         w.nodeB[nei] = make_uint2(ntBits, best | (mySlot << 16));
@@ -561,11 +599,12 @@ __device__ __forceinline__ float warpGeodesic(const NavScene& sc, const WarpSlab
 #if defined(BPSN_PHASE_TIMING)
       {
         BPSN_TICK(tP2);
-        if (lane == 0) {
-          atomicAdd(&g_phaseCycles[12], static_cast<unsigned long long>(tP1 - tP0));
-          atomicAdd(&g_phaseCycles[13], static_cast<unsigned long long>(tP2 - tP1));
-          atomicAdd(&g_phaseCycles[14], 1ull);
-        }
+        pacc->popCycles += static_cast<unsigned long long>(tP1 - tP0);
+        pacc->expandCycles += static_cast<unsigned long long>(tP2 - tP1);
+        pacc->pops += 1;
+        pacc->exLoad += static_cast<unsigned long long>(tE1 - tP1);
+        pacc->exMath += static_cast<unsigned long long>(tE2 - tE1);
+        pacc->exBook += static_cast<unsigned long long>(tE3 - tE2);
       }
 #endif
     }
@@ -606,10 +645,8 @@ __device__ __forceinline__ float warpGeodesic(const NavScene& sc, const WarpSlab
   BPSN_TICK(tA1);
   const float dres = warpFunnel(sc, w, lane, startPos, endPos, pathSize, status);
   BPSN_TICK(tA2);
-  if (lane == 0) {
-    BPSN_PHASE_ADD(2, tA1 - tA0);
-    BPSN_PHASE_ADD(3, tA2 - tA1);
-  }
+  BPSN_PHASE_ADD(2, tA1 - tA0);
+  BPSN_PHASE_ADD(3, tA2 - tA1);
   return dres;
 }
 
@@ -636,54 +673,14 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
   NavScene sc = scGlobal;
   const StagedLayout lay = stagedLayout(sc.nverts, sc.npolys, sc.ndtris, sc.ndverts);
   {
-    float4* dv = reinterpret_cast<float4*>(smem + lay.verts);
-    for (int i = threadIdx.x; i < sc.nverts; i += blockDim.x) {
-      const float* v = scGlobal.verts + 3 * static_cast<size_t>(i);
-      dv[i] = make_float4(v[0], v[1], v[2], 0.f);
-    }
-    auto copy16 = [&](size_t dstOff, const void* srcPtr, size_t bytes) {
-      const uint4* src = reinterpret_cast<const uint4*>(srcPtr);
-      uint4* dst = reinterpret_cast<uint4*>(smem + dstOff);
-      const int n16 = static_cast<int>(pad16(bytes) / 16);
-      for (int i = threadIdx.x; i < n16; i += blockDim.x)
-        dst[i] = src[i];
-    };
-    // every source array is followed by at least 16 bytes of padding in the
-    // scene's device allocation, so the rounded-up 16-byte reads stay inside it
-    copy16(lay.polys, scGlobal.polys, static_cast<size_t>(sc.npolys) * sizeof(NavPoly));
-    copy16(lay.detail, scGlobal.detail, static_cast<size_t>(sc.npolys) * sizeof(NavDetail));
-    copy16(lay.dtris, scGlobal.dtris, static_cast<size_t>(sc.ndtris + 1) * 4);
-    copy16(lay.dverts, scGlobal.dverts, static_cast<size_t>(sc.ndverts) * 12);
-    copy16(lay.island, scGlobal.island, static_cast<size_t>(sc.npolys) * 4);
-  }
-  __syncthreads();
-  {
-    // drop links to neighbours the filter rejects; flag polygons that reach one
-    // neighbour through two edges (each thread edits only its own records'
-    // neis/pad and reads other records' flags)
-    NavPoly* sp = reinterpret_cast<NavPoly*>(smem + lay.polys);
-    for (int i = threadIdx.x; i < sc.npolys; i += blockDim.x) {
-      uint16_t ne[kVertsPerPoly];
-      const int nvp = sp[i].vertCount;
-#pragma unroll
-      for (int j = 0; j < kVertsPerPoly; ++j) {
-        uint16_t v = j < nvp ? sp[i].neis[j] : 0;
-        if (v && !(v & kExtLink) && (sp[v - 1].flags & kFlagWalk) == 0)
-          v = 0;
-        ne[j] = v;
-      }
-      bool dup = false;
-#pragma unroll
-      for (int j = 1; j < kVertsPerPoly; ++j)
-#pragma unroll
-        for (int k = 0; k < j; ++k)
-          if (ne[j] && !(ne[j] & kExtLink) && ne[j] == ne[k])
-            dup = true;
-#pragma unroll
-      for (int j = 0; j < kVertsPerPoly; ++j)
-        sp[i].neis[j] = ne[j];
-      sp[i].pad = dup ? 1 : 0;
-    }
+    // the image was laid out at set-up exactly as stagedLayout() describes:
+    // float4 vertices, polygons with filtered links and the duplicate-neighbour
+    // flag, detail bases / triangles / vertices, island ids
+    const uint4* src = reinterpret_cast<const uint4*>(scGlobal.staged);
+    uint4* dst = reinterpret_cast<uint4*>(smem);
+    const int n16 = static_cast<int>(scGlobal.stagedBytes / 16);
+    for (int i = threadIdx.x; i < n16; i += blockDim.x)
+      dst[i] = src[i];
   }
   __syncthreads();
   sc.verts = reinterpret_cast<const float*>(smem + lay.verts);
@@ -694,9 +691,19 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
   sc.dverts = reinterpret_cast<const float*>(smem + lay.dverts);
   sc.island = reinterpret_cast<const int32_t*>(smem + lay.island);
   BPSN_TICK(tS1);
-  if (threadIdx.x == 0)
-    BPSN_PHASE_ADD(0, tS1 - tS0);
+#if defined(BPSN_PHASE_TIMING)
+  PhaseAcc paccStore = {};
+  PhaseAcc* pacc = &paccStore;
+  BPSN_PHASE_ADD(0, tS1 - tS0);
+#endif
 
+  StagedView sv;
+  sv.polys = sc.polys;
+  sv.verts = reinterpret_cast<const float4*>(sc.verts);
+  sv.island = sc.island;
+  sv.npolys = sc.npolys;
+  sv.polyMask = sc.polyMask;
+  sv.refBase = sc.refBase;
   uint8_t* slabBase = smem + slabOffset + static_cast<size_t>(warp) * warpGeoSlabBytes(pcap);
   const WarpSlab w = carveSlab(slabBase, pcap);
 
@@ -726,7 +733,11 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
     uint32_t status = 0;
     bool fallback = false;
     BPSN_TICK(tQ1);
-    float d = warpGeodesic(sc, w, lane, b, bref, a, aref, &status, &fallback);
+#if defined(BPSN_PHASE_TIMING)
+    float d = warpGeodesic(sv, w, lane, b, bref, a, aref, &status, &fallback, pacc);
+#else
+    float d = warpGeodesic(sv, w, lane, b, bref, a, aref, &status, &fallback);
+#endif
     BPSN_TICK(tQ2);
     if (lane == 0) {
       if (fallback) {
@@ -743,11 +754,26 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
       BPSN_PHASE_ADD(1, tQ1 - tQ0);
       BPSN_PHASE_ADD(4, tQ3 - tQ2);
 #if defined(BPSN_PHASE_TIMING)
-      atomicAdd(&g_phaseCycles[5], 1ull);
+      pacc->queries += 1;
 #endif
     }
     __syncwarp();
   }
+#if defined(BPSN_PHASE_TIMING)
+  if (lane == 0) {
+    for (int k = 0; k < 5; ++k) {
+      atomicAdd(&g_phaseCycles[k], pacc->sum[k]);
+      atomicMax(&g_phaseCycles[6 + k], pacc->mx[k]);
+    }
+    atomicAdd(&g_phaseCycles[5], pacc->queries);
+    atomicAdd(&g_phaseCycles[12], pacc->popCycles);
+    atomicAdd(&g_phaseCycles[13], pacc->expandCycles);
+    atomicAdd(&g_phaseCycles[14], pacc->pops);
+    atomicAdd(&g_phaseCycles[11], pacc->exLoad);
+    atomicAdd(&g_phaseCycles[15], pacc->exMath);
+    atomicAdd(&g_phaseCycles[16], pacc->exBook);
+  }
+#endif
 }
 
 }  // namespace bpsn

@@ -69,6 +69,8 @@ struct NavScene {
   const uint8_t* dtris;     // 4 * ndtris
   const NavBVNode* bv;      // nbv (0 => linear scan)
   const int32_t* island;    // npolys, connected-component id per polygon
+  const uint8_t* staged;    // ready-to-copy shared-memory image of the tables (may be null)
+  uint32_t stagedBytes;
   int32_t npolys;
   int32_t nverts;
   int32_t nbv;

@@ -124,6 +124,8 @@ NavScene HostScene::view() const {
   s.dtris = dtris.data();
   s.bv = bv.data();
   s.island = island.data();
+  s.staged = nullptr;
+  s.stagedBytes = 0;
   s.npolys = static_cast<int32_t>(polys.size());
   s.nverts = static_cast<int32_t>(verts.size() / 3);
   s.nbv = static_cast<int32_t>(bv.size());

@@ -64,6 +64,10 @@ struct GroupDev {
   uint8_t* mask;  // [B]
   float* info;    // [B][3]
   float* polar;   // [B][2]
+  // optional second destination of this step's reward / mask (e.g. a row of
+  // rollout storage); null when unused
+  float* rewardOut;
+  uint8_t* maskOut;
   // geodesic work list, segmented by scene: scene s owns geoList[listBase[s] ...],
   // counts[s] entries are valid this step
   uint32_t* geoList;         // [B]
@@ -225,6 +229,10 @@ __device__ __forceinline__ void finishEnv(const GroupDev& g, const SceneTable& s
     reward += prev - d;
   g.reward[e] = reward;
   g.mask[e] = done ? 0 : 1;
+  if (g.rewardOut)
+    g.rewardOut[e] = reward;
+  if (g.maskOut)
+    g.maskOut[e] = done ? 0 : 1;
   g.info[3 * e + 0] = success;
   g.info[3 * e + 1] = spl;
   g.info[3 * e + 2] = d;

@@ -131,6 +131,13 @@ int32_t bpsn_reset(bpsn_sim* sim, uint32_t group, void* stream);
  * mirrors are enabled and otherwise only closes the start/end pairing. */
 int32_t bpsn_step_start(bpsn_sim* sim, uint32_t group, const int64_t* actions,
                         int32_t actions_mem, void* stream);
+/* As bpsn_step_start, and the step's reward (float32 [B]) and mask (uint8 [B])
+ * are also written to the given DEVICE arrays when non-NULL -- e.g. rows
+ * rewards[t] and masks[t+1] of rollout storage, which the reference fills with
+ * a separate copy (RolloutStorage.insert, bps_nav/common/rollout_storage.py:130-183). */
+int32_t bpsn_step_start_ex(bpsn_sim* sim, uint32_t group, const int64_t* actions,
+                           int32_t actions_mem, void* stream, float* reward_out,
+                           uint8_t* mask_out);
 int32_t bpsn_step_end(bpsn_sim* sim, uint32_t group);
 
 /* Pointer to a per-group array; mem selects device memory or (for the four
