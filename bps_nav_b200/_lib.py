@@ -25,6 +25,7 @@ ERR_NAMES = {
     5: "BPSN_ERR_BAD_ACTION", 6: "BPSN_ERR_IO", 7: "BPSN_ERR_NO_DEVICE",
 }
 FLAG_HOST_MIRRORS = 1
+FLAG_GENERIC_KERNEL = 2
 MEM_DEVICE, MEM_HOST = 0, 1
 (FIELD_REWARD, FIELD_MASK, FIELD_INFO, FIELD_POLAR, FIELD_POSITION, FIELD_ROTATION, FIELD_GOAL,
  FIELD_NAV_POSITION, FIELD_NAV_POLY, FIELD_GOAL_POLY, FIELD_STEP, FIELD_EPISODE, FIELD_RESET_COUNT,

@@ -89,17 +89,17 @@ class _RolloutGenerator:
     @classmethod
     def from_scenes(cls, scenes, num_environments, num_active_scenes=None, gpu_id=0,
                     render_resolution=(64, 64), color=False, depth=False, double_buffered=False,
-                    seed=0, host_mirrors=True):
+                    seed=0, host_mirrors=True, generic_kernel=False):
         """Builds a generator from in-memory ``dataset.Scene`` objects (no JSON involved)."""
         self = cls.__new__(cls)
         if num_active_scenes is None:
             num_active_scenes = len(scenes)
         self._setup(list(scenes), num_environments, num_active_scenes, gpu_id, render_resolution,
-                    color, depth, double_buffered, seed, host_mirrors)
+                    color, depth, double_buffered, seed, host_mirrors, generic_kernel)
         return self
 
     def _setup(self, scenes, num_environments, num_active_scenes, gpu_id, render_resolution, color,
-               depth, double_buffered, seed, host_mirrors):
+               depth, double_buffered, seed, host_mirrors, generic_kernel=False):
         if self._task != "pointnav":
             raise NotImplementedError(
                 f"{type(self).__name__}: only the PointGoal navigation task is implemented")
@@ -121,7 +121,8 @@ class _RolloutGenerator:
         self._host_mirrors = bool(host_mirrors)
         cfg = L.Config(gpu_id=self.gpu_id, num_envs=self.num_environments, num_groups=num_groups,
                        num_scenes=len(self._scenes), seed=int(seed) & (2**64 - 1),
-                       flags=L.FLAG_HOST_MIRRORS if host_mirrors else 0, reserved=0)
+                       flags=(L.FLAG_HOST_MIRRORS if host_mirrors else 0) |
+                       (L.FLAG_GENERIC_KERNEL if generic_kernel else 0), reserved=0)
         L.check(self._lib.bpsn_create(C.byref(cfg), C.byref(self._h)))
         try:
             for i, sc in enumerate(self._scenes):

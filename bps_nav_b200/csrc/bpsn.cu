@@ -291,7 +291,7 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
       wpb = static_cast<int>((kSmemMax - maxSceneBytes) / slab);
     if (wpb > 16)
       wpb = 16;
-    g.warpGeo = wpb >= 4;
+    g.warpGeo = wpb >= 4 && !(sim->cfg.flags & BPSN_FLAG_GENERIC_KERNEL);
     if (g.warpGeo) {
       g.warpsPerBlock = wpb;
       g.slabOffset = maxSceneBytes;

@@ -74,7 +74,11 @@ enum {
   /* keep pinned host copies of reward/mask/info/polar, refreshed by every
      step/reset and complete when bpsn_step_end returns (reference behaviour:
      the result arrays are host memory) */
-  BPSN_FLAG_HOST_MIRRORS = 1u << 0
+  BPSN_FLAG_HOST_MIRRORS = 1u << 0,
+  /* always use the generic one-thread-per-environment step kernel (tables and
+     A* scratch in global memory) instead of the shared-memory warp kernel;
+     it is otherwise chosen only for scenes too large for shared memory */
+  BPSN_FLAG_GENERIC_KERNEL = 1u << 1
 };
 
 /* Fields addressable through bpsn_get_ptr.  All arrays are indexed by the

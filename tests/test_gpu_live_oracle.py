@@ -1,0 +1,148 @@
+"""GPU parity against the oracle run live on the same box (the reference's compiled PathFinder
+under the simulator restatement).  Skipped when oracle/_ref is not present.
+
+Same tolerances as test_gpu_parity.py: integer outputs bit-exact, poses 1e-5 m, geodesic / reward
+1e-4 relative, polar 1e-5.
+"""
+import numpy as np
+import pytest
+
+from conftest import load_scene, scene_path
+
+from oracle import pyoracle
+
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(not pyoracle.available(), reason="oracle libraries not built")]
+
+torch = pytest.importorskip("torch")
+
+
+def _close(a, b, rel, abs_=0.0):
+    a = np.asarray(a, np.float64)
+    b = np.asarray(b, np.float64)
+    same = (a == b) | (np.isnan(a) & np.isnan(b))
+    with np.errstate(invalid="ignore"):
+        near = np.abs(a - b) <= abs_ + rel * np.abs(b)
+    return same | near
+
+
+def _compare_run(scene_names, n, steps, seed, mix, threads=8, check_state_every=16, **gen_kw):
+    from bps_nav_b200 import bps_sim
+    scenes = [load_scene(s) for s in scene_names]
+    gen = bps_sim.PointNavRolloutGenerator.from_scenes(scenes, n, seed=seed, **gen_kw)
+    osim = pyoracle.OracleSim([(scene_path(s), sc.episodes) for s, sc in zip(scene_names, scenes)],
+                              n, seed, threads=threads)
+    groups = gen.num_groups
+    B = gen.envs_per_group
+    for g in range(groups):
+        gen.reset(g)
+    osim.reset()
+    pol = np.concatenate([gen.get_polars(g) for g in range(groups)])
+    assert _close(pol, osim.polars, 0, 1e-5).all()
+    actions = pyoracle.philox_actions(steps, n, seed + 99, mix)
+    ties = 0
+    for t in range(steps):
+        for g in range(groups):
+            gen.step(g, actions[t, g * B:(g + 1) * B])
+        assert osim.step(actions[t]) == 0
+        mask = np.concatenate([gen.get_masks(g) for g in range(groups)])
+        info = np.concatenate([gen.get_infos(g) for g in range(groups)])
+        rew = np.concatenate([gen.get_rewards(g) for g in range(groups)])
+        pol = np.concatenate([gen.get_polars(g) for g in range(groups)])
+        assert np.array_equal(mask, osim.masks), f"mask, step {t}"
+        assert np.array_equal(info["success"], osim.infos[:, 0]), f"success, step {t}"
+        assert _close(info["spl"], osim.infos[:, 1], 1e-4, 1e-6).all(), f"spl, step {t}"
+        assert _close(info["distanceToGoal"], osim.infos[:, 2], 1e-4, 1e-6).all(), f"dist, step {t}"
+        assert _close(rew, osim.rewards, 1e-4, 1e-5).all(), f"reward, step {t}"
+        assert _close(pol, osim.polars, 0, 1e-5).all(), f"polar, step {t}"
+        if (t + 1) % check_state_every == 0 or t + 1 == steps:
+            torch.cuda.synchronize()
+            st = osim.state()
+            for name in ("nav_poly", "goal_poly", "step", "episode", "reset_count"):
+                got = np.concatenate([gen.tensor(g, name).cpu().numpy().view(np.uint32)
+                                      for g in range(groups)])
+                assert np.array_equal(got, st[name]), f"{name}, step {t}"
+            for name in ("position", "rotation", "nav_position"):
+                got = np.concatenate([gen.tensor(g, name).cpu().numpy().T for g in range(groups)])
+                assert _close(got, st[name], 0, 1e-5).all(), f"{name}, step {t}"
+    status = np.concatenate([gen.tensor(g, "status").cpu().numpy().view(np.uint32)
+                             for g in range(groups)])
+    ties = int(((status >> 8) & 1).sum())
+    assert int(np.bitwise_or.reduce(status) & 0xA0) == 0  # no iteration cap, no bad action
+    gen.close()
+    osim.close()
+    return ties
+
+
+def test_single_scene_large_batch_uniform_actions():
+    # benchmark config 1 shape; 4096 envs also exercise the exact-heap fallback on open-list ties
+    _compare_run(["c1"], 4096, 96, seed=321, mix="uniform")
+
+
+def test_single_scene_policy_like_actions_long_episodes():
+    _compare_run(["c1"], 1024, 600, seed=17, mix="policy", check_state_every=100)
+
+
+def test_mixed_scene_batch():
+    # benchmark config 3 shape, scaled: 16 scenes, envs split scene-major
+    names = [f"m{i:02d}" for i in range(16)]
+    _compare_run(names, 2048, 64, seed=5, mix="uniform")
+    _compare_run(names, 512, 300, seed=6, mix="policy", check_state_every=100)
+
+
+def test_generic_kernel_matches_oracle():
+    _compare_run(["c1"], 512, 64, seed=11, mix="uniform", generic_kernel=True)
+    _compare_run(["m01", "m04"], 256, 128, seed=12, mix="policy", generic_kernel=True)
+
+
+def test_double_buffered_groups():
+    _compare_run(["c0", "m15", "m13", "m14"], 256, 64, seed=3, mix="uniform", double_buffered=True)
+
+
+def test_step_protocol_errors():
+    from bps_nav_b200 import bps_sim
+    gen = bps_sim.PointNavRolloutGenerator.from_scenes([load_scene("c0")], 32, seed=1)
+    gen.reset(0)
+    acts = np.zeros(32, np.int64)
+    with pytest.raises(RuntimeError, match="Simulation already done"):
+        gen.step_end(0)
+    gen.step_start(0, acts)
+    with pytest.raises(RuntimeError, match="Not done with previous simulation"):
+        gen.step_start(0, acts)
+    gen.step_end(0)
+    bad = acts.copy()
+    bad[5] = 9
+    with pytest.raises(RuntimeError, match="Unknown action: 9"):
+        gen.step_start(0, bad)
+    # a rejected call steps nothing and leaves the generator usable
+    before = gen.tensor(0, "step").clone()
+    gen.step(0, np.full(32, 2, np.int64))
+    assert torch.equal(gen.tensor(0, "step"), before + 1)
+    # device-side actions out of range: flagged, pose untouched, no fault
+    dact = torch.full((32,), 2, dtype=torch.int64, device="cuda")
+    dact[7] = 77
+    rot = gen.tensor(0, "rotation").clone()
+    gen.step(0, dact)
+    torch.cuda.synchronize()
+    st = gen.tensor(0, "status").cpu().numpy().view(np.uint32)
+    assert st[7] & 0x80 and not (np.delete(st, 7) & 0x80).any()
+    assert torch.equal(gen.tensor(0, "rotation")[:, 7], rot[:, 7])
+    with pytest.raises(RuntimeError):
+        gen.step_start(3, acts)
+    gen.close()
+
+
+def test_rollout_rows_written_by_the_step():
+    from bps_nav_b200 import bps_sim
+    gen = bps_sim.PointNavRolloutGenerator.from_scenes([load_scene("c0")], 64, seed=2)
+    gen.reset(0)
+    T = 8
+    rewards = torch.zeros(T + 1, 64, 1, device="cuda")
+    masks = torch.ones(T + 1, 64, 1, dtype=torch.bool, device="cuda")
+    acts = pyoracle.philox_actions(T, 64, 4, "uniform")
+    for t in range(T):
+        gen.step_start(0, acts[t], reward_out=rewards[t], mask_out=masks[t + 1])
+        gen.step_end(0)
+        assert np.array_equal(rewards[t, :, 0].cpu().numpy(), gen.get_rewards(0))
+        assert np.array_equal(masks[t + 1, :, 0].cpu().numpy(), gen.get_masks(0) != 0)
+    gen.close()
