@@ -43,6 +43,9 @@ BYTES_PER_ENV_STEP = 177          # move + sensor + reward path, per environment
 BYTES_PER_GEO_QUERY = 44          # list entry 4, scene 4, two points 24, two refs 8 -> distance 4
 BYTES_PER_GAE_ELEM = 25.2         # scan 17.2 + normalise 8 per (t, env)
 L2_FLUSH_BYTES = 256 << 20
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu capture
+# (profiles/k_step_warp_config1_ncu_full.md); only meaningful for the default workload
+NCU_TRAFFIC_BYTES = {("c1", 4096, "uniform", "k_step"): 2.5e6}
 
 
 def parse_args():
@@ -319,7 +322,8 @@ def run_ours(args):
     step_ms = sum(kms.values())
     roofline = {
         "bound": "hbm", "kernel": top, "achieved": achieved, "peak": peak, "unit": "GB/s",
-        "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+        "frac": achieved / peak,
+        "traffic": NCU_TRAFFIC_BYTES.get((args.scene, N, args.mix, top)), "peak_source": peak_src,
         "ms_per_launch": kms[top],
         "note": "A* is latency/divergence-bound: its algorithmic HBM bytes are tiny by design "
                 "(scratch is L2-resident); see kernels{} for every launch",
