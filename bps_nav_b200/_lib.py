@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(HERE, "libbpsn.so")
 SYMBOLS = [
     "bpsn_create", "bpsn_destroy", "bpsn_set_navmesh_file", "bpsn_set_navmesh_blob",
     "bpsn_set_episodes", "bpsn_set_env_scenes", "bpsn_finalize", "bpsn_reset", "bpsn_step_start", "bpsn_step_start_ex",
-    "bpsn_step_end", "bpsn_get_ptr", "bpsn_profile_enable", "bpsn_profile_read", "bpsn_scene_info", "bpsn_query_snap", "bpsn_query_try_step",
+    "bpsn_step_end", "bpsn_get_ptr", "bpsn_device_error_flags", "bpsn_profile_enable", "bpsn_profile_read", "bpsn_scene_info", "bpsn_query_snap", "bpsn_query_try_step",
     "bpsn_query_geodesic", "bpsn_gae_workspace_bytes", "bpsn_gae", "bpsn_gae_static", "bpsn_last_error",
     "bpsn_version",
 ]
@@ -69,6 +69,7 @@ def load():
     lib.bpsn_step_start_ex.argtypes = [vp, u32, vp, i32, vp, vp, vp]
     lib.bpsn_step_end.argtypes = [vp, u32]
     lib.bpsn_get_ptr.argtypes = [vp, u32, i32, i32, C.POINTER(vp), C.POINTER(sz)]
+    lib.bpsn_device_error_flags.argtypes = [vp, u32, C.POINTER(C.c_uint32)]
     lib.bpsn_profile_enable.argtypes = [vp, u32, i32]
     lib.bpsn_profile_read.argtypes = [vp, u32, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]
     lib.bpsn_scene_info.argtypes = [vp, u32, C.POINTER(i32), C.POINTER(i32), C.POINTER(i32)]

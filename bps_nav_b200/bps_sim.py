@@ -291,6 +291,12 @@ class _RolloutGenerator:
         # groups as RolloutGenerator::swapStats does (simulator.cpp:1412-1424); no swapping here.
         return (0.0, float(len(self._scenes)), float(self.envs_per_scene * self.num_groups))
 
+    def device_errors(self, group_idx):
+        """Sticky device-side error flags of a group (0 in normal operation); synchronises."""
+        v = C.c_uint32()
+        L.check(self._lib.bpsn_device_error_flags(self._h, group_idx, C.byref(v)), self._h)
+        return int(v.value)
+
     KERNEL_NAMES = ("k_pre", "k_step")
 
     def profile(self, group_idx, enable=True):

@@ -268,7 +268,7 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
     g.numScenesUsed = ns;
     // Shared-memory plan: every scene used by the group must fit next to at
     // least four warp slabs in one CTA's 227 KB.
-    const size_t kSmemMax = 227 * 1024;
+    const size_t kSmemMax = 227 * 1024 - 64;  // 227 KB per CTA minus the kernel's static shared memory
     size_t maxSceneBytes = 0;
     int maxPolys = 0;
     bool anyUsed = false;
@@ -695,6 +695,16 @@ int32_t bpsn_step_end(bpsn_sim* sim, uint32_t group) {
     }
     g.profSteps++;
   }
+  return BPSN_OK;
+}
+
+int32_t bpsn_device_error_flags(bpsn_sim* sim, uint32_t group, uint32_t* flags) {
+  if (!sim || !sim->finalized || group >= sim->groups.size() || !flags)
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_device_error_flags: bad argument");
+  Group& g = sim->groups[group];
+  BPSN_CUDA(sim, cudaSetDevice(sim->cfg.gpu_id));
+  BPSN_CUDA(sim, cudaMemcpy(flags, g.dev.counts + 2 * g.numScenesUsed, sizeof(uint32_t),
+                            cudaMemcpyDeviceToHost));
   return BPSN_OK;
 }
 

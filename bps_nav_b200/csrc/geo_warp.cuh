@@ -433,6 +433,11 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
     bool reached = false;
     bool outOfNodes = false;
     int guard = 0;
+    // Edge j of the popped polygon is evaluated by lane (j + rot) & 31 and rot moves on
+    // after every pop, so that over a search every lane gets to evaluate neighbours: a
+    // new open node is kept in the *evaluating* lane's own registers, without any
+    // cross-lane traffic, and the entries spread over the warp.
+    int rot = 0;
 
     while (true) {
       if (++guard > 32 * kMaxAStarNodes) {
@@ -475,7 +480,8 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
       // ---- expand: one lane per edge of the popped polygon.  All loads of a
       // round are issued before any of them is used.
       const NavPoly* bp = &sc.polys[best];
-      const int li = lane < kVertsPerPoly ? lane : kVertsPerPoly - 1;
+      const int ej = (lane - rot) & 31;  // this lane's edge index (>= nv: none)
+      const int li = ej < kVertsPerPoly ? ej : kVertsPerPoly - 1;
       const int nv = bp->vertCount;
       const uint32_t dupFlag = bp->pad;
       const uint16_t ne = bp->neis[li];
@@ -487,13 +493,15 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
       const uint32_t bpar = w.nodeB[best].y & 0xffffu;
 
       const uint16_t vb = (li + 1 == nv) ? vbFirst : vbNext;
-      bool act = lane < nv && ne != 0 && !(ne & kExtLink) &&
+      bool act = ej < nv && ne != 0 && !(ne & kExtLink) &&
                  static_cast<uint32_t>(ne - 1) != bpar;
       uint32_t nei = act ? static_cast<uint32_t>(ne - 1) : best;
       if (dupFlag & 1) {  // polygon shares more than one edge with some neighbour (rare)
         const uint32_t grp = __match_any_sync(0xffffffffu, act ? nei : 0xffff0000u + lane);
-        if (act && (__ffs(grp) - 1) != lane) {
-          act = false;  // same neighbour through a lower edge: that lane acts
+        // bit k of the rotated mask = edge k; the lowest edge of the group acts
+        const uint32_t byEdge = __funnelshift_r(grp, grp, rot);
+        if (act && (__ffs(byEdge) - 1) != ej) {
+          act = false;
           nei = best;
         }
       }
@@ -542,39 +550,56 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
       BPSN_TICK(tE2);
       // ---- open-list bookkeeping
       uint32_t mySlot = (nB.y >> 16) & 0xffu;
-      uint32_t am = __ballot_sync(0xffffffffu, upd && !wasOpen);
-      uint32_t f0 = __ballot_sync(0xffffffffu, t0 == kInfBits);
-      uint32_t f1 = __ballot_sync(0xffffffffu, t1 == kInfBits);
-      if (__popc(am) > __popc(f0) + __popc(f1)) {
-        *needFallback = true;
-        return 0.f;
-      }
-      while (am) {
-        const int src = __ffs(am) - 1;
-        am &= am - 1;
-        int dst, reg;
-        if (f0) {
-          dst = __ffs(f0) - 1;
-          f0 &= f0 - 1;
-          reg = 0;
+      bool spill = false;
+      if (upd && !wasOpen) {
+        if (t0 == kInfBits) {
+          t0 = ntBits;
+          p0 = nei;
+          mySlot = static_cast<uint32_t>(lane);
+        } else if (t1 == kInfBits) {
+          t1 = ntBits;
+          p1 = nei;
+          mySlot = static_cast<uint32_t>(lane) | 32u;
         } else {
-          dst = __ffs(f1) - 1;
-          f1 &= f1 - 1;
-          reg = 1;
+          spill = true;  // both of this lane's entries are taken
         }
-        const uint32_t nt = __shfl_sync(0xffffffffu, ntBits, src);
-        const uint32_t np = __shfl_sync(0xffffffffu, nei, src);
-        if (lane == dst) {
-          if (reg == 0) {
-            t0 = nt;
-            p0 = np;
+      }
+      uint32_t am = __ballot_sync(0xffffffffu, spill);
+      if (am) {
+        // rare: hand the entry to any lane that has a free slot
+        uint32_t f0 = __ballot_sync(0xffffffffu, t0 == kInfBits);
+        uint32_t f1 = __ballot_sync(0xffffffffu, t1 == kInfBits);
+        if (__popc(am) > __popc(f0) + __popc(f1)) {
+          *needFallback = true;
+          return 0.f;
+        }
+        while (am) {
+          const int src = __ffs(am) - 1;
+          am &= am - 1;
+          int dst, reg;
+          if (f0) {
+            dst = __ffs(f0) - 1;
+            f0 &= f0 - 1;
+            reg = 0;
           } else {
-            t1 = nt;
-            p1 = np;
+            dst = __ffs(f1) - 1;
+            f1 &= f1 - 1;
+            reg = 1;
           }
+          const uint32_t nt = __shfl_sync(0xffffffffu, ntBits, src);
+          const uint32_t np = __shfl_sync(0xffffffffu, nei, src);
+          if (lane == dst) {
+            if (reg == 0) {
+              t0 = nt;
+              p0 = np;
+            } else {
+              t1 = nt;
+              p1 = np;
+            }
+          }
+          if (lane == src)
+            mySlot = static_cast<uint32_t>(dst) | (static_cast<uint32_t>(reg) << 5);
         }
-        if (lane == src)
-          mySlot = static_cast<uint32_t>(dst) | (static_cast<uint32_t>(reg) << 5);
       }
       uint32_t mm = __ballot_sync(0xffffffffu, upd && wasOpen);
       while (mm) {
@@ -595,6 +620,7 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
         w.nodeB[nei] = make_uint2(ntBits, best | (mySlot << 16));
         w.flags[nei] = 1;  // open (closed bit cleared)
       }
+      rot = (rot + 7) & 31;
       __syncwarp();
 #if defined(BPSN_PHASE_TIMING)
       {
@@ -673,16 +699,50 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
   NavScene sc = scGlobal;
   const StagedLayout lay = stagedLayout(sc.nverts, sc.npolys, sc.ndtris, sc.ndverts);
   {
-    // the image was laid out at set-up exactly as stagedLayout() describes:
-    // float4 vertices, polygons with filtered links and the duplicate-neighbour
-    // flag, detail bases / triangles / vertices, island ids
-    const uint4* src = reinterpret_cast<const uint4*>(scGlobal.staged);
-    uint4* dst = reinterpret_cast<uint4*>(smem);
-    const int n16 = static_cast<int>(scGlobal.stagedBytes / 16);
-    for (int i = threadIdx.x; i < n16; i += blockDim.x)
-      dst[i] = src[i];
+    // The image was laid out at set-up exactly as stagedLayout() describes (float4
+    // vertices, polygons with filtered links and the duplicate-neighbour flag, detail
+    // bases / triangles / vertices, island ids), 16-byte aligned and a multiple of 16
+    // bytes long: one bulk asynchronous copy (TMA, untiled, this CTA's own shared
+    // memory, no multicast) brings it in and signals an mbarrier.
+    __shared__ __align__(8) unsigned long long stageBar;
+    const uint32_t bar = static_cast<uint32_t>(__cvta_generic_to_shared(&stageBar));
+    const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    const uint32_t bytes = scGlobal.stagedBytes;
+    if (threadIdx.x == 0) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar) : "memory");
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                   : "memory");
+      asm volatile(
+          "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+          ::"r"(dst), "l"(scGlobal.staged), "r"(bytes), "r"(bar)
+          : "memory");
+    }
+    // bounded wait on phase 0 of the barrier; a copy of this size lands within
+    // microseconds, the bound is ~1 s of polling
+    bool landed = false;
+    for (int it = 0; it < (1 << 22) && !landed; ++it) {
+      uint32_t ok;
+      asm volatile(
+          "{\n\t.reg .pred p;\n\t"
+          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(ok)
+          : "r"(bar)
+          : "memory");
+      landed = ok != 0;
+    }
+    if (!__syncthreads_and(landed ? 1 : 0)) {
+      // never observed; leave without touching the half-filled tables (the step's
+      // listed envs keep their previous outputs) and make the failure visible
+      if (threadIdx.x == 0)
+        atomicOr(&g.counts[2 * gridDim.y], 1u);
+      return;
+    }
   }
-  __syncthreads();
   sc.verts = reinterpret_cast<const float*>(smem + lay.verts);
   sc.vstride = 4;
   sc.polys = reinterpret_cast<const NavPoly*>(smem + lay.polys);

@@ -316,10 +316,21 @@ k_pre(GroupDev g, SceneTable st, const int64_t* __restrict__ actions, TurnConsts
     writePolar(g, e, g.pos[e], g.pos[B + e], g.pos[2 * B + e], qx, qy, qz, qw, g.goal[e],
                g.goal[B + e], g.goal[2 * B + e]);
   }
-  if (done || moved) {
+  const bool listed = done || moved;
+  const unsigned running = __activemask();
+  const unsigned listedMask = __ballot_sync(running, listed);
+  if (listed) {
     g.flags[e] = (done ? 1u : 0u) | (moved ? 2u : 0u);
+    // one atomic per (warp, scene) instead of one per environment
     const uint32_t sceneIdx = g.scene[e];
-    const uint32_t slot = atomicAdd(&g.counts[sceneIdx], 1u);
+    const unsigned grp = __match_any_sync(listedMask, sceneIdx);
+    const int leader = __ffs(grp) - 1;
+    const int lane = threadIdx.x & 31;
+    uint32_t base = 0;
+    if (lane == leader)
+      base = atomicAdd(&g.counts[sceneIdx], static_cast<uint32_t>(__popc(grp)));
+    base = __shfl_sync(grp, base, leader);
+    const uint32_t slot = base + __popc(grp & ((1u << lane) - 1u));
     g.geoList[g.listBase[sceneIdx] + slot] = e;
   } else {
     finishEnv(g, st, e, false, false, 0.f, seedLo, seedHi);

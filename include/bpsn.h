@@ -150,6 +150,12 @@ int32_t bpsn_step_end(bpsn_sim* sim, uint32_t group);
 int32_t bpsn_get_ptr(bpsn_sim* sim, uint32_t group, int32_t field, int32_t mem, void** ptr,
                      size_t* bytes);
 
+/* Sticky device-side error word of a group (synchronous read; no counterpart
+ * in the reference, which aborts on inconsistencies).  Bit 0: a step kernel gave
+ * up waiting for its scene tables to arrive in shared memory and skipped its
+ * work.  Zero in normal operation. */
+int32_t bpsn_device_error_flags(bpsn_sim* sim, uint32_t group, uint32_t* flags);
+
 /* Per-kernel device timing of the step (no counterpart in the reference; its
  * Python side times phases with wall clocks, bps_nav/common/utils.py:387-436).
  * While enabled, bpsn_step_end waits for the step and adds the CUDA-event

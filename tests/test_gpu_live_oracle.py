@@ -69,6 +69,7 @@ def _compare_run(scene_names, n, steps, seed, mix, threads=8, check_state_every=
                              for g in range(groups)])
     ties = int(((status >> 8) & 1).sum())
     assert int(np.bitwise_or.reduce(status) & 0xA0) == 0  # no iteration cap, no bad action
+    assert all(gen.device_errors(g) == 0 for g in range(groups))
     gen.close()
     osim.close()
     return ties
