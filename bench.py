@@ -190,6 +190,7 @@ def run_reference(args):
         return
     t_start = time.perf_counter()
     per_window_budget = max(args.cpu_seconds, 5.0)
+    args.envs = args.envs * max(args.gpus, 1)  # the whole job's environments on the host cores
     rate, d = cpu_arm(args, per_window_budget, steps_cap=args.steps + args.warmup)
     ms = 1000.0 * d["seconds"] / max(d["windows"], 1)
     line = {

@@ -29,7 +29,8 @@ FLAG_GENERIC_KERNEL = 2
 MEM_DEVICE, MEM_HOST = 0, 1
 (FIELD_REWARD, FIELD_MASK, FIELD_INFO, FIELD_POLAR, FIELD_POSITION, FIELD_ROTATION, FIELD_GOAL,
  FIELD_NAV_POSITION, FIELD_NAV_POLY, FIELD_GOAL_POLY, FIELD_STEP, FIELD_EPISODE, FIELD_RESET_COUNT,
- FIELD_STATUS, FIELD_PREV_DIST, FIELD_CUM_TRAVEL, FIELD_INIT_DIST, FIELD_SCENE) = range(18)
+ FIELD_STATUS, FIELD_PREV_DIST, FIELD_CUM_TRAVEL, FIELD_INIT_DIST, FIELD_SCENE,
+ FIELD_EPISODE_REWARD, FIELD_EPISODE_STATS) = range(20)
 
 
 class Config(C.Structure):
@@ -66,7 +67,7 @@ def load():
     lib.bpsn_finalize.argtypes = [vp]
     lib.bpsn_reset.argtypes = [vp, u32, vp]
     lib.bpsn_step_start.argtypes = [vp, u32, vp, i32, vp]
-    lib.bpsn_step_start_ex.argtypes = [vp, u32, vp, i32, vp, vp, vp]
+    lib.bpsn_step_start_ex.argtypes = [vp, u32, vp, i32, vp, vp, vp, vp]
     lib.bpsn_step_end.argtypes = [vp, u32]
     lib.bpsn_get_ptr.argtypes = [vp, u32, i32, i32, C.POINTER(vp), C.POINTER(sz)]
     lib.bpsn_device_error_flags.argtypes = [vp, u32, C.POINTER(C.c_uint32)]

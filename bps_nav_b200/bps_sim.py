@@ -53,6 +53,8 @@ _FIELDS = {
     "cum_travel": (L.FIELD_CUM_TRAVEL, np.float32, lambda B: (B,)),
     "init_dist": (L.FIELD_INIT_DIST, np.float32, lambda B: (B,)),
     "scene": (L.FIELD_SCENE, np.uint32, lambda B: (B,)),
+    "episode_reward": (L.FIELD_EPISODE_REWARD, np.float32, lambda B: (B,)),
+    "episode_stats": (L.FIELD_EPISODE_STATS, np.float32, lambda B: (5, B)),
 }
 
 
@@ -165,13 +167,19 @@ class _RolloutGenerator:
     def reset(self, group_idx):
         L.check(self._lib.bpsn_reset(self._h, group_idx, self._stream()), self._h)
 
-    def step_start(self, group_idx, actions, reward_out=None, mask_out=None):
+    def step_start(self, group_idx, actions, reward_out=None, mask_out=None, polar_out=None):
         """``actions``: C-contiguous int64 numpy array of length ``envs_per_group`` (reference
         signature), or a CUDA int64 tensor of the same length (device-resident fast path).
 
         ``reward_out`` / ``mask_out`` (added): contiguous CUDA tensors of ``envs_per_group``
         float32 / 1-byte elements that also receive this step's reward and mask, e.g.
-        ``rollouts.rewards[t]`` and ``rollouts.masks[t + 1]``."""
+        ``rollouts.rewards[t]`` and ``rollouts.masks[t + 1]``; ``polar_out``: CUDA float32
+        ``[B, 2]`` that also receives the GPS/compass observation (``observations[t + 1]``)."""
+        po = polar_out.data_ptr() if polar_out is not None else None
+        if polar_out is not None and (polar_out.numel() != 2 * self.envs_per_group or
+                                      polar_out.element_size() != 4 or
+                                      not polar_out.is_contiguous() or not polar_out.is_cuda):
+            raise RuntimeError("polar_out must be a contiguous CUDA float32 tensor of B x 2")
         ro = reward_out.data_ptr() if reward_out is not None else None
         mo = mask_out.data_ptr() if mask_out is not None else None
         if reward_out is not None and (reward_out.numel() != self.envs_per_group or
@@ -187,9 +195,9 @@ class _RolloutGenerator:
                 actions = np.ascontiguousarray(actions, dtype=np.int64)
             if actions.shape[0] != self.envs_per_group:
                 raise RuntimeError("actions length must equal the number of envs in the group")
-            self._keepalive = [actions, reward_out, mask_out]
+            self._keepalive = [actions, reward_out, mask_out, polar_out]
             L.check(self._lib.bpsn_step_start_ex(self._h, group_idx, actions.ctypes.data,
-                                                 L.MEM_HOST, self._stream(), ro, mo), self._h)
+                                                 L.MEM_HOST, self._stream(), ro, mo, po), self._h)
         else:
             import torch
             if not (isinstance(actions, torch.Tensor) and actions.is_cuda and
@@ -200,7 +208,7 @@ class _RolloutGenerator:
                 raise RuntimeError("actions length must equal the number of envs in the group")
             self._keepalive = [actions]
             L.check(self._lib.bpsn_step_start_ex(self._h, group_idx, actions.data_ptr(),
-                                                 L.MEM_DEVICE, self._stream(), ro, mo), self._h)
+                                                 L.MEM_DEVICE, self._stream(), ro, mo, po), self._h)
         self._num_steps_taken += self.envs_per_group
 
     def step_end(self, group_idx):
@@ -249,7 +257,8 @@ class _RolloutGenerator:
     def tensor(self, group_idx, name):
         """Zero-copy CUDA tensor over a per-group array; names are the keys of ``_FIELDS``
         (``reward mask info polar position rotation goal nav_position nav_poly goal_poly step
-        episode reset_count status prev_dist cum_travel init_dist scene``).  uint32 arrays are
+        episode reset_count status prev_dist cum_travel init_dist scene episode_reward
+        episode_stats``).  uint32 arrays are
         exposed as int32 tensors (same bits)."""
         import torch
         key = (group_idx, name)

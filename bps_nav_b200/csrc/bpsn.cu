@@ -214,6 +214,7 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
   const size_t oReward = place(B * f), oMask = place(B), oInfo = place(3 * B * f),
                oPolar = place(2 * B * f);
   const uint32_t ns = sim->cfg.num_scenes;
+  const size_t oEpReward = place(B * f), oStats = place(5 * B * f);
   const size_t oGeoList = place(B * u), oCounts = place((2 * ns + 4) * u),
                oListBase = place((ns + 4) * u);
   g.stateBytes = off;
@@ -245,6 +246,8 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
   d.mask = reinterpret_cast<uint8_t*>(b + oMask);
   d.info = reinterpret_cast<float*>(b + oInfo);
   d.polar = reinterpret_cast<float*>(b + oPolar);
+  d.episodeReward = reinterpret_cast<float*>(b + oEpReward);
+  d.stats = reinterpret_cast<float*>(b + oStats);
   d.geoList = reinterpret_cast<uint32_t*>(b + oGeoList);
   d.counts = reinterpret_cast<uint32_t*>(b + oCounts);
   d.listBase = reinterpret_cast<const uint32_t*>(b + oListBase);
@@ -336,6 +339,8 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
   setField(BPSN_FIELD_CUM_TRAVEL, d.cumTravel, B * f);
   setField(BPSN_FIELD_INIT_DIST, d.initDist, B * f);
   setField(BPSN_FIELD_SCENE, d.scene, B * u);
+  setField(BPSN_FIELD_EPISODE_REWARD, d.episodeReward, B * f);
+  setField(BPSN_FIELD_EPISODE_STATS, d.stats, 5 * B * f);
 
   if (!g.warpGeo)  // per-slot A* scratch is only used by the generic (global-memory) kernel
     BPSN_CUDA(sim, cudaMalloc(&g.scratch, sizeof(AStarScratch) * static_cast<size_t>(B)));
@@ -617,12 +622,12 @@ int32_t bpsn_reset(bpsn_sim* sim, uint32_t group, void* stream) {
 
 int32_t bpsn_step_start(bpsn_sim* sim, uint32_t group, const int64_t* actions,
                         int32_t actions_mem, void* stream) {
-  return bpsn_step_start_ex(sim, group, actions, actions_mem, stream, nullptr, nullptr);
+  return bpsn_step_start_ex(sim, group, actions, actions_mem, stream, nullptr, nullptr, nullptr);
 }
 
 int32_t bpsn_step_start_ex(bpsn_sim* sim, uint32_t group, const int64_t* actions,
                            int32_t actions_mem, void* stream, float* reward_out,
-                           uint8_t* mask_out) {
+                           uint8_t* mask_out, float* polar_out) {
   if (!sim || !sim->finalized)
     return fail(sim, BPSN_ERR_STATE, "bpsn_step_start: handle not finalized");
   if (group >= sim->groups.size())
@@ -654,6 +659,7 @@ int32_t bpsn_step_start_ex(bpsn_sim* sim, uint32_t group, const int64_t* actions
   GroupDev gd = g.dev;
   gd.rewardOut = reward_out;
   gd.maskOut = mask_out;
+  gd.polarOut = polar_out;
   const uint32_t seedLo = static_cast<uint32_t>(sim->cfg.seed);
   const uint32_t seedHi = static_cast<uint32_t>(sim->cfg.seed >> 32);
   if (prof) cudaEventRecord(g.prof[0], s);

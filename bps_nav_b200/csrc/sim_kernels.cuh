@@ -64,10 +64,16 @@ struct GroupDev {
   uint8_t* mask;  // [B]
   float* info;    // [B][3]
   float* polar;   // [B][2]
-  // optional second destination of this step's reward / mask (e.g. a row of
-  // rollout storage); null when unused
+  // optional second destination of this step's reward / mask / polar (e.g. rows
+  // of rollout storage); null when unused
   float* rewardOut;
   uint8_t* maskOut;
+  float* polarOut;  // [B][2]
+  // running episode statistics, the device-side form of PPOTrainer._update_stats
+  // (bps_nav/rl/ppo/ppo_trainer.py:286-319)
+  float* episodeReward;  // [B]     reward accumulated in the current episode
+  float* stats;          // [5][B]  sums over finished episodes: reward, count, success,
+                         //         spl, distanceToGoal
   // geodesic work list, segmented by scene: scene s owns geoList[listBase[s] ...],
   // counts[s] entries are valid this step
   uint32_t* geoList;         // [B]
@@ -143,6 +149,8 @@ __device__ __forceinline__ void writePolar(const GroupDev& g, uint32_t e, float 
   const float rho = sqrtf(ax * ax + ay * ay);
   const float phi = atan2f(ay, ax);
   reinterpret_cast<float2*>(g.polar)[e] = make_float2(rho, -phi);
+  if (g.polarOut)
+    reinterpret_cast<float2*>(g.polarOut)[e] = make_float2(rho, -phi);
 }
 
 // BaseSimulator::reset + InfoFunctor::reset + RewardFunctor::reset for one env.
@@ -236,8 +244,21 @@ __device__ __forceinline__ void finishEnv(const GroupDev& g, const SceneTable& s
   g.info[3 * e + 0] = success;
   g.info[3 * e + 1] = spl;
   g.info[3 * e + 2] = d;
-  if (done)
+  // current_episode_reward += reward; on done the episode's totals go to the
+  // running sums and the accumulator restarts (same fp32 operations, in step
+  // order, as the trainer's tensor code)
+  const float epr = g.episodeReward[e] + reward;
+  if (done) {
+    g.stats[e] += epr;
+    g.stats[B + e] += 1.f;
+    g.stats[2 * B + e] += success;
+    g.stats[3 * B + e] += spl;
+    g.stats[4 * B + e] += d;
+    g.episodeReward[e] = 0.f;
     resetEnv(g, st, e, seedLo, seedHi);
+  } else {
+    g.episodeReward[e] = epr;
+  }
 }
 
 // MoveForward of handleMovement: target = position + rotation * (0, 0, -0.25),

@@ -102,7 +102,12 @@ enum {
   BPSN_FIELD_CUM_TRAVEL = 15,/* float32 [B]                               */
   BPSN_FIELD_INIT_DIST = 16, /* float32 [B]                               */
   BPSN_FIELD_SCENE = 17,     /* uint32  [B]   scene index of the env      */
-  BPSN_FIELD_COUNT = 18
+  BPSN_FIELD_EPISODE_REWARD = 18, /* float32 [B] reward accumulated in the running episode */
+  BPSN_FIELD_EPISODE_STATS = 19,  /* float32 [5,B] sums over finished episodes: reward | count |
+                                     success | spl | distanceToGoal (what PPOTrainer._update_stats
+                                     keeps, bps_nav/rl/ppo/ppo_trainer.py:286-319); zero them to
+                                     restart a window */
+  BPSN_FIELD_COUNT = 20
 };
 
 enum { BPSN_MEM_DEVICE = 0, BPSN_MEM_HOST = 1 };
@@ -135,13 +140,14 @@ int32_t bpsn_reset(bpsn_sim* sim, uint32_t group, void* stream);
  * mirrors are enabled and otherwise only closes the start/end pairing. */
 int32_t bpsn_step_start(bpsn_sim* sim, uint32_t group, const int64_t* actions,
                         int32_t actions_mem, void* stream);
-/* As bpsn_step_start, and the step's reward (float32 [B]) and mask (uint8 [B])
- * are also written to the given DEVICE arrays when non-NULL -- e.g. rows
- * rewards[t] and masks[t+1] of rollout storage, which the reference fills with
- * a separate copy (RolloutStorage.insert, bps_nav/common/rollout_storage.py:130-183). */
+/* As bpsn_step_start, and the step's reward (float32 [B]), mask (uint8 [B])
+ * and GPS/compass observation (float32 [B,2]) are also written to the given
+ * DEVICE arrays when non-NULL -- e.g. rows rewards[t], masks[t+1] and
+ * observations[t+1] of rollout storage, which the reference fills with separate
+ * copies (RolloutStorage.insert, bps_nav/common/rollout_storage.py:130-183). */
 int32_t bpsn_step_start_ex(bpsn_sim* sim, uint32_t group, const int64_t* actions,
                            int32_t actions_mem, void* stream, float* reward_out,
-                           uint8_t* mask_out);
+                           uint8_t* mask_out, float* polar_out);
 int32_t bpsn_step_end(bpsn_sim* sim, uint32_t group);
 
 /* Pointer to a per-group array; mem selects device memory or (for the four

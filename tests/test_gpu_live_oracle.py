@@ -140,10 +140,13 @@ def test_rollout_rows_written_by_the_step():
     T = 8
     rewards = torch.zeros(T + 1, 64, 1, device="cuda")
     masks = torch.ones(T + 1, 64, 1, dtype=torch.bool, device="cuda")
+    obs = torch.zeros(T + 1, 64, 2, device="cuda")
     acts = pyoracle.philox_actions(T, 64, 4, "uniform")
     for t in range(T):
-        gen.step_start(0, acts[t], reward_out=rewards[t], mask_out=masks[t + 1])
+        gen.step_start(0, acts[t], reward_out=rewards[t], mask_out=masks[t + 1],
+                       polar_out=obs[t + 1])
         gen.step_end(0)
         assert np.array_equal(rewards[t, :, 0].cpu().numpy(), gen.get_rewards(0))
         assert np.array_equal(masks[t + 1, :, 0].cpu().numpy(), gen.get_masks(0) != 0)
+        assert np.array_equal(obs[t + 1].cpu().numpy(), gen.get_polars(0))
     gen.close()

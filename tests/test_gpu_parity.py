@@ -101,6 +101,22 @@ def test_trajectory_matches_golden(fname, host_actions):
         if (t + 1) in snaps:
             check_state(t + 1)
     assert int(gen.tensor(0, "status").cpu().numpy().view(np.uint32).max() & 0xA0) == 0
+    # running episode statistics kept on the device == PPOTrainer._update_stats
+    # (bps_nav/rl/ppo/ppo_trainer.py:286-319) replayed in float32 on the golden outputs
+    cur = np.zeros(n, np.float32)
+    acc = np.zeros((5, n), np.float32)
+    for t in range(steps):
+        cur = cur + g["reward"][t]
+        done = g["mask"][t] == 0
+        acc[0] += np.where(done, cur, np.float32(0))
+        acc[1] += done.astype(np.float32)
+        for k in range(3):
+            acc[2 + k] += np.where(done, g["info"][t, :, k], np.float32(0))
+        cur = np.where(done, np.float32(0), cur)
+    got = gen.tensor(0, "episode_stats").cpu().numpy()
+    assert np.array_equal(got[1], acc[1]) and np.array_equal(got[2], acc[2])
+    assert _close(got, acc, 1e-4, 1e-5).all()
+    assert _close(gen.tensor(0, "episode_reward").cpu().numpy(), cur, 1e-4, 1e-5).all()
     gen.close()
 
 
