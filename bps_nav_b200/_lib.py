@@ -26,6 +26,7 @@ ERR_NAMES = {
 }
 FLAG_HOST_MIRRORS = 1
 FLAG_GENERIC_KERNEL = 2
+TASK_POINTNAV, TASK_FLEE, TASK_EXPLORATION = 0, 1, 2
 MEM_DEVICE, MEM_HOST = 0, 1
 (FIELD_REWARD, FIELD_MASK, FIELD_INFO, FIELD_POLAR, FIELD_POSITION, FIELD_ROTATION, FIELD_GOAL,
  FIELD_NAV_POSITION, FIELD_NAV_POLY, FIELD_GOAL_POLY, FIELD_STEP, FIELD_EPISODE, FIELD_RESET_COUNT,
@@ -36,7 +37,7 @@ MEM_DEVICE, MEM_HOST = 0, 1
 class Config(C.Structure):
     _fields_ = [("gpu_id", C.c_int32), ("num_envs", C.c_uint32), ("num_groups", C.c_uint32),
                 ("num_scenes", C.c_uint32), ("seed", C.c_uint64), ("flags", C.c_uint32),
-                ("reserved", C.c_uint32)]
+                ("task", C.c_uint32)]
 
 
 class Episode(C.Structure):

@@ -1,4 +1,5 @@
-"""Drop-in for the reference's ``bps_sim`` extension module (PointGoal navigation).
+"""Drop-in for the reference's ``bps_sim`` extension module (PointNav, Flee and Exploration
+generators).
 
 Class and method names, argument order and meaning follow the pybind11 bindings at
 ``simulator/simulator.cpp:1785-1823`` (``RolloutGenerator`` at ``:1332-1460``).  The work that the
@@ -32,6 +33,12 @@ from . import _lib as L
 from . import dataset as _dataset
 
 INFO_DTYPE = np.dtype([("success", "<f4"), ("spl", "<f4"), ("distanceToGoal", "<f4")])
+# StepInfo records of the three tasks (simulator/simulator.cpp:738-742, 834-836, 893-895, 1814-1821)
+_TASKS = {
+    "pointnav": (L.TASK_POINTNAV, INFO_DTYPE),
+    "flee": (L.TASK_FLEE, np.dtype([("distanceFromStart", "<f4")])),
+    "exploration": (L.TASK_EXPLORATION, np.dtype([("numVisited", "<f4")])),
+}
 
 _FIELDS = {
     # name: (field id, numpy dtype, shape as function of B)
@@ -102,9 +109,10 @@ class _RolloutGenerator:
 
     def _setup(self, scenes, num_environments, num_active_scenes, gpu_id, render_resolution, color,
                depth, double_buffered, seed, host_mirrors, generic_kernel=False):
-        if self._task != "pointnav":
-            raise NotImplementedError(
-                f"{type(self).__name__}: only the PointGoal navigation task is implemented")
+        if self._task not in _TASKS:
+            raise NotImplementedError(f"{type(self).__name__}: unknown task")
+        self._task_id, self._info_dtype = _TASKS[self._task]
+        self._info_width = len(self._info_dtype.names)
         self._lib = L.load()
         self._h = C.c_void_p()
         num_groups = 2 if double_buffered else 1
@@ -124,7 +132,8 @@ class _RolloutGenerator:
         cfg = L.Config(gpu_id=self.gpu_id, num_envs=self.num_environments, num_groups=num_groups,
                        num_scenes=len(self._scenes), seed=int(seed) & (2**64 - 1),
                        flags=(L.FLAG_HOST_MIRRORS if host_mirrors else 0) |
-                       (L.FLAG_GENERIC_KERNEL if generic_kernel else 0), reserved=0)
+                       (L.FLAG_GENERIC_KERNEL if generic_kernel else 0),
+                       task=self._task_id)
         L.check(self._lib.bpsn_create(C.byref(cfg), C.byref(self._h)))
         try:
             for i, sc in enumerate(self._scenes):
@@ -237,9 +246,14 @@ class _RolloutGenerator:
             L.check(self._lib.bpsn_get_ptr(self._h, group_idx, fid, L.MEM_HOST, C.byref(p),
                                            C.byref(n)), self._h)
             buf = (C.c_uint8 * n.value).from_address(p.value)
-            arr = np.frombuffer(buf, dtype=dt).reshape(shape(self.envs_per_group))
+            arr = np.frombuffer(buf, dtype=dt).reshape(self._shape(name, shape))
             self._host_views[key] = arr
         return self._host_views[key]
+
+    def _shape(self, name, shape):
+        if name == "info":  # [B, 3] for PointNav, [B, 1] for Flee / Exploration
+            return (self.envs_per_group, self._info_width)
+        return shape(self.envs_per_group)
 
     def get_rewards(self, group_idx):
         return self._host_array(group_idx, "reward")
@@ -248,7 +262,7 @@ class _RolloutGenerator:
         return self._host_array(group_idx, "mask")
 
     def get_infos(self, group_idx):
-        return self._host_array(group_idx, "info").view(INFO_DTYPE).reshape(-1)
+        return self._host_array(group_idx, "info").view(self._info_dtype).reshape(-1)
 
     def get_polars(self, group_idx):
         return self._host_array(group_idx, "polar")
@@ -269,7 +283,7 @@ class _RolloutGenerator:
                                            C.byref(n)), self._h)
             if dt == np.uint32:
                 dt = np.int32
-            carrier = _DeviceArray(p.value, shape(self.envs_per_group), dt)
+            carrier = _DeviceArray(p.value, self._shape(name, shape), dt)
             self._dev_tensors[key] = torch.as_tensor(carrier, device=f"cuda:{self.gpu_id}")
         return self._dev_tensors[key]
 
@@ -367,10 +381,12 @@ class PointNavRolloutGenerator(_RolloutGenerator):
 
 
 class FleeRolloutGenerator(_RolloutGenerator):
-    """Present in the reference module (``simulator/simulator.cpp:1818-1819``); not implemented."""
+    """Flee task (``simulator/simulator.cpp:830-887, 1818-1819``): info = geodesic distance from
+    the episode start, reward = its increase."""
     _task = "flee"
 
 
 class ExplorationRolloutGenerator(_RolloutGenerator):
-    """Present in the reference module (``simulator/simulator.cpp:1821-1822``); not implemented."""
+    """Exploration task (``simulator/simulator.cpp:889-999, 1821-1822``): info = visited 1 m cells
+    minus one, reward = 0.25 per new cell."""
     _task = "exploration"

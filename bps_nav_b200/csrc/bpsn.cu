@@ -215,6 +215,9 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
                oPolar = place(2 * B * f);
   const uint32_t ns = sim->cfg.num_scenes;
   const size_t oEpReward = place(B * f), oStats = place(5 * B * f);
+  const bool expl = sim->cfg.task == BPSN_TASK_EXPLORATION;
+  const size_t oExplInit = place(expl ? 7 * B * f : 16), oNumCells = place(expl ? B * u : 16),
+               oVisited = place(expl ? static_cast<size_t>(B) * kVisitedSlots * u : 16);
   const size_t oGeoList = place(B * u), oCounts = place((2 * ns + 4) * u),
                oListBase = place((ns + 4) * u);
   g.stateBytes = off;
@@ -224,6 +227,11 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
   GroupDev& d = g.dev;
   d.B = B;
   d.envBase = envBase;
+  d.task = sim->cfg.task;
+  d.infoWidth = sim->cfg.task == BPSN_TASK_POINTNAV ? 3u : 1u;
+  d.explInit = reinterpret_cast<float*>(b + oExplInit);
+  d.numCells = reinterpret_cast<uint32_t*>(b + oNumCells);
+  d.visited = reinterpret_cast<uint32_t*>(b + oVisited);
   d.pos = reinterpret_cast<float*>(b + oPos);
   d.rot = reinterpret_cast<float*>(b + oRot);
   d.goal = reinterpret_cast<float*>(b + oGoal);
@@ -323,7 +331,7 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
   };
   setField(BPSN_FIELD_REWARD, d.reward, B * f);
   setField(BPSN_FIELD_MASK, d.mask, B);
-  setField(BPSN_FIELD_INFO, d.info, 3 * B * f);
+  setField(BPSN_FIELD_INFO, d.info, d.infoWidth * B * f);
   setField(BPSN_FIELD_POLAR, d.polar, 2 * B * f);
   setField(BPSN_FIELD_POSITION, d.pos, 3 * B * f);
   setField(BPSN_FIELD_ROTATION, d.rot, 4 * B * f);
@@ -398,6 +406,8 @@ int32_t bpsn_create(const bpsn_config* cfg, bpsn_sim** out) {
   if (!cfg || !out)
     return fail(nullptr, BPSN_ERR_INVALID_ARG, "bpsn_create: null argument");
   *out = nullptr;
+  if (cfg->task > BPSN_TASK_EXPLORATION)
+    return fail(nullptr, BPSN_ERR_INVALID_ARG, "bpsn_create: unknown task");
   if (cfg->num_envs == 0 || cfg->num_scenes == 0 || cfg->num_groups == 0 || cfg->num_groups > 2)
     return fail(nullptr, BPSN_ERR_INVALID_ARG,
                 "bpsn_create: num_envs, num_scenes must be > 0 and num_groups 1 or 2");

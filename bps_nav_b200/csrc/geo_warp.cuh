@@ -792,12 +792,17 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
     const uint32_t bref = g.goalRef[e];
     uint32_t status = 0;
     bool fallback = false;
+    float d = 0.f;
+    // PointNav queries on every listed step, Flee only after a move, Exploration never
+    const bool needGeo = g.task == kTaskPointNav || (g.task == kTaskFlee && moved);
     BPSN_TICK(tQ1);
+    if (needGeo) {
 #if defined(BPSN_PHASE_TIMING)
-    float d = warpGeodesic(sv, w, lane, b, bref, a, aref, &status, &fallback, pacc);
+      d = warpGeodesic(sv, w, lane, b, bref, a, aref, &status, &fallback, pacc);
 #else
-    float d = warpGeodesic(sv, w, lane, b, bref, a, aref, &status, &fallback);
+      d = warpGeodesic(sv, w, lane, b, bref, a, aref, &status, &fallback);
 #endif
+    }
     BPSN_TICK(tQ2);
     if (lane == 0) {
       if (fallback) {
@@ -807,6 +812,8 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
         d = geodesic(scGlobal, fallbackScratch + slot, b, bref, a, aref, &status);
         status |= kStatTieFallback;
       }
+      if (g.task == kTaskExploration && moved)
+        explVisit(g, e, a[0], a[1], a[2]);
       if (status)
         g.status[e] |= status;
       finishEnv(g, st, e, done, moved, d, seedLo, seedHi);

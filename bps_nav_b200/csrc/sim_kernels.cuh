@@ -19,6 +19,14 @@
 //           finished, the reset (BaseSimulator::reset :601-618,
 //           InfoFunctor::reset :744-756, RewardFunctor::reset :801-806).
 //
+// Tasks.  PointNav is described above.  Flee (simulator.cpp:830-887): the info is the
+// geodesic distance from the episode's snapped start to the agent, refreshed only when
+// the agent moved, reward = its increase; the start point is kept in the navGoal /
+// goalRef columns so the same query code serves both tasks.  Exploration
+// (simulator.cpp:889-999): the info is the number of 1 m grid cells (in the frame of
+// the initial pose) visited so far minus one, reward = 0.25 per new cell; no
+// geodesic query at all.
+//
 // Everything reset() derives from the chosen episode alone -- the snapped
 // start point, the snapped goal and the initial geodesic distance agent ->
 // goal (:611-612, :747-752) -- is a pure function of the episode record, so it
@@ -37,9 +45,15 @@
 
 namespace bpsn {
 
+enum Task : uint32_t { kTaskPointNav = 0, kTaskFlee = 1, kTaskExploration = 2 };
+
+constexpr uint32_t kVisitedSlots = 1024;  // per-env open-addressing table of visited grid cells
+
 struct GroupDev {
-  uint32_t B;        // environments in this group
-  uint32_t envBase;  // global index of the group's first environment
+  uint32_t B;          // environments in this group
+  uint32_t envBase;    // global index of the group's first environment
+  uint32_t task;       // Task
+  uint32_t infoWidth;  // floats per env in `info`: 3 (PointNav) or 1 (Flee, Exploration)
   // pose / task state, each [B] (vectors are component-major: x[B] y[B] z[B])
   float* pos;      // [3][B]  position_
   float* rot;      // [4][B]  rotation_ (x y z w)
@@ -62,7 +76,7 @@ struct GroupDev {
   // outputs
   float* reward;  // [B]
   uint8_t* mask;  // [B]
-  float* info;    // [B][3]
+  float* info;    // [B][infoWidth]
   float* polar;   // [B][2]
   // optional second destination of this step's reward / mask / polar (e.g. rows
   // of rollout storage); null when unused
@@ -72,6 +86,10 @@ struct GroupDev {
   // running episode statistics, the device-side form of PPOTrainer._update_stats
   // (bps_nav/rl/ppo/ppo_trainer.py:286-319)
   float* episodeReward;  // [B]     reward accumulated in the current episode
+  // Exploration task only (simulator/simulator.cpp:889-999)
+  float* explInit;       // [7][B]  initial position xyz, inverse initial rotation xyzw
+  uint32_t* visited;     // [B][kVisitedSlots] visited cells (0 = empty slot)
+  uint32_t* numCells;    // [B]     cells in the set
   float* stats;          // [5][B]  sums over finished episodes: reward, count, success,
                          //         spl, distanceToGoal
   // geodesic work list, segmented by scene: scene s owns geoList[listBase[s] ...],
@@ -153,6 +171,47 @@ __device__ __forceinline__ void writePolar(const GroupDev& g, uint32_t e, float 
     reinterpret_cast<float2*>(g.polarOut)[e] = make_float2(rho, -phi);
 }
 
+// Exploration: cell of the current position in the initial pose's frame,
+// InfoFunctor::update (simulator.cpp:897-904).  Returns true if the cell is new.
+__device__ __forceinline__ bool explVisit(const GroupDev& g, uint32_t e, float px, float py,
+                                          float pz) {
+  const uint32_t B = g.B;
+  const float dx = px - g.explInit[e];
+  const float dy = py - g.explInit[B + e];
+  const float dz = pz - g.explInit[2 * B + e];
+  const float qx = g.explInit[3 * B + e], qy = g.explInit[4 * B + e];
+  const float qz = g.explInit[5 * B + e], qw = g.explInit[6 * B + e];
+  // q * v = v + 2 * (w * (q x v) + q x (q x v)), then / cell_size (1.0)
+  const float uvx = qy * dz - dy * qz;
+  const float uvy = qz * dx - dz * qx;
+  const float uvz = qx * dy - dx * qy;
+  const float uuvx = qy * uvz - uvy * qz;
+  const float uuvy = qz * uvx - uvz * qx;
+  const float uuvz = qx * uvy - uvx * qy;
+  const float gx = (dx + ((uvx * qw) + uuvx) * 2.f) / 1.0f;
+  const float gy = (dy + ((uvy * qw) + uuvy) * 2.f) / 1.0f;
+  const float gz = (dz + ((uvz * qw) + uuvz) * 2.f) / 1.0f;
+  const int ix = static_cast<int>(gx), iy = static_cast<int>(gy), iz = static_cast<int>(gz);
+  // an episode has at most 499 moves of 0.25 m: |cell| <= 125 fits 10 bits
+  const uint32_t key = 0x80000000u | ((static_cast<uint32_t>(ix) & 0x3ffu) << 20) |
+                       ((static_cast<uint32_t>(iy) & 0x3ffu) << 10) |
+                       (static_cast<uint32_t>(iz) & 0x3ffu);
+  uint32_t* tab = g.visited + static_cast<size_t>(e) * kVisitedSlots;
+  uint32_t h = (key * 2654435761u) >> 22;  // 10 bits
+  for (uint32_t probe = 0; probe < kVisitedSlots; ++probe) {
+    const uint32_t cur = tab[h];
+    if (cur == key)
+      return false;
+    if (cur == 0u) {
+      tab[h] = key;
+      g.numCells[e] += 1u;
+      return true;
+    }
+    h = (h + 1u) & (kVisitedSlots - 1u);
+  }
+  return false;  // table full: cannot happen within one episode (<= 500 cells)
+}
+
 // BaseSimulator::reset + InfoFunctor::reset + RewardFunctor::reset for one env.
 __device__ __forceinline__ void resetEnv(const GroupDev& g, const SceneTable& st, uint32_t e,
                                          uint32_t seedLo, uint32_t seedHi) {
@@ -200,50 +259,95 @@ __device__ __forceinline__ void resetEnv(const GroupDev& g, const SceneTable& st
   g.prevPos[B + e] = sy;
   g.prevPos[2 * B + e] = sz;
   writePolar(g, e, sx, sy, sz, qx, qy, qz, qw, gx, gy, gz);
+  if (g.task == kTaskFlee) {
+    // Flee::InfoFunctor::reset: the reference point of the distance is the snapped
+    // start; distance and the reward's previous distance start at 0
+    g.navGoal[e] = __uint_as_float(n0.x);
+    g.navGoal[B + e] = __uint_as_float(n0.y);
+    g.navGoal[2 * B + e] = __uint_as_float(n0.z);
+    g.goalRef[e] = n0.w;
+    g.initDist[e] = 0.f;
+    g.prevDist[e] = 0.f;
+  } else if (g.task == kTaskExploration) {
+    // Exploration::InfoFunctor::reset: empty set, remember the initial pose
+    // (glm::inverse(q) = conjugate(q) / dot(q, q)), visit the first cell
+    uint4* tab = reinterpret_cast<uint4*>(g.visited + static_cast<size_t>(e) * kVisitedSlots);
+    for (uint32_t i = 0; i < kVisitedSlots / 4; ++i)
+      tab[i] = make_uint4(0u, 0u, 0u, 0u);
+    g.numCells[e] = 0u;
+    const float nrm = qx * qx + qy * qy + qz * qz + qw * qw;
+    g.explInit[e] = sx;
+    g.explInit[B + e] = sy;
+    g.explInit[2 * B + e] = sz;
+    g.explInit[3 * B + e] = -qx / nrm;
+    g.explInit[4 * B + e] = -qy / nrm;
+    g.explInit[5 * B + e] = -qz / nrm;
+    g.explInit[6 * B + e] = qw / nrm;
+    explVisit(g, e, sx, sy, sz);
+    g.initDist[e] = 0.f;
+    g.prevDist[e] = 0.f;  // numVisited = size - 1 = 0
+  }
 }
 
 // InfoFunctor::step + RewardFunctor::step, then the in-loop reset when done.
-// `d` is the geodesic distance of this step (ignored when the env neither
-// moved nor finished).
+// `d` is the geodesic distance of this step (ignored when the task or the
+// action did not ask for one).
 __device__ __forceinline__ void finishEnv(const GroupDev& g, const SceneTable& st, uint32_t e,
                                           bool done, bool moved, float d, uint32_t seedLo,
                                           uint32_t seedHi) {
   const uint32_t B = g.B;
   const float prev = g.prevDist[e];
-  float success = 0, spl = 0;
-  if (done) {
-    success = d < kSuccessDistance ? 1.f : 0.f;
-    const float init = g.initDist[e];
-    const float cum = g.cumTravel[e];
-    const float mx = (init < cum) ? cum : init;  // std::max(init, cum)
-    spl = success * init / mx;
-  } else if (moved) {
-    const float px = g.pos[e], py = g.pos[B + e], pz = g.pos[2 * B + e];
-    const float dx = px - g.prevPos[e];
-    const float dy = py - g.prevPos[B + e];
-    const float dz = pz - g.prevPos[2 * B + e];
-    g.cumTravel[e] += sqrtf(dx * dx + dy * dy + dz * dz);
+  float success = 0, spl = 0, reward;
+  if (g.task == kTaskPointNav) {
+    if (done) {
+      success = d < kSuccessDistance ? 1.f : 0.f;
+      const float init = g.initDist[e];
+      const float cum = g.cumTravel[e];
+      const float mx = (init < cum) ? cum : init;  // std::max(init, cum)
+      spl = success * init / mx;
+    } else if (moved) {
+      const float px = g.pos[e], py = g.pos[B + e], pz = g.pos[2 * B + e];
+      const float dx = px - g.prevPos[e];
+      const float dy = py - g.prevPos[B + e];
+      const float dz = pz - g.prevPos[2 * B + e];
+      g.cumTravel[e] += sqrtf(dx * dx + dy * dy + dz * dz);
+      g.prevDist[e] = d;
+      g.prevPos[e] = px;
+      g.prevPos[B + e] = py;
+      g.prevPos[2 * B + e] = pz;
+    } else {
+      d = prev;
+    }
+    reward = -kSlackReward;
+    if (done)
+      reward += kSuccessReward * spl;
+    else
+      reward += prev - d;
+    g.info[3 * e + 0] = success;
+    g.info[3 * e + 1] = spl;
+    g.info[3 * e + 2] = d;
+  } else if (g.task == kTaskFlee) {
+    // Flee::InfoFunctor::step / RewardFunctor::step (simulator.cpp:846-880)
+    if (!moved)
+      d = prev;
+    reward = d - prev;
     g.prevDist[e] = d;
-    g.prevPos[e] = px;
-    g.prevPos[B + e] = py;
-    g.prevPos[2 * B + e] = pz;
+    g.info[e] = d;
+    success = d;  // first info column, for the running statistics below
   } else {
-    d = prev;
+    // Exploration (simulator.cpp:919-993); the set itself was updated by the caller
+    d = static_cast<float>(g.numCells[e] - 1u);
+    reward = 0.25f * (d - prev);
+    g.prevDist[e] = d;
+    g.info[e] = d;
+    success = d;
   }
-  float reward = -kSlackReward;
-  if (done)
-    reward += kSuccessReward * spl;
-  else
-    reward += prev - d;
   g.reward[e] = reward;
   g.mask[e] = done ? 0 : 1;
   if (g.rewardOut)
     g.rewardOut[e] = reward;
   if (g.maskOut)
     g.maskOut[e] = done ? 0 : 1;
-  g.info[3 * e + 0] = success;
-  g.info[3 * e + 1] = spl;
-  g.info[3 * e + 2] = d;
   // current_episode_reward += reward; on done the episode's totals go to the
   // running sums and the accumulator restarts (same fp32 operations, in step
   // order, as the trainer's tensor code)
@@ -379,12 +483,17 @@ k_step_thread(GroupDev g, SceneTable st, AStarScratch* __restrict__ scratch, uin
   const bool done = f & 1u, moved = f & 2u;
   if (moved)
     forwardMove(g, sc, e);
-  const float a[3] = {g.navPos[e], g.navPos[B + e], g.navPos[2 * B + e]};
-  const float b[3] = {g.navGoal[e], g.navGoal[B + e], g.navGoal[2 * B + e]};
-  uint32_t status = 0;
-  const float d = geodesic(sc, scratch + slot, b, g.goalRef[e], a, g.navRef[e], &status);
-  if (status)
-    g.status[e] |= status;
+  float d = 0.f;
+  if (g.task == kTaskPointNav || (g.task == kTaskFlee && moved)) {
+    const float a[3] = {g.navPos[e], g.navPos[B + e], g.navPos[2 * B + e]};
+    const float b[3] = {g.navGoal[e], g.navGoal[B + e], g.navGoal[2 * B + e]};
+    uint32_t status = 0;
+    d = geodesic(sc, scratch + slot, b, g.goalRef[e], a, g.navRef[e], &status);
+    if (status)
+      g.status[e] |= status;
+  } else if (g.task == kTaskExploration && moved) {
+    explVisit(g, e, g.pos[e], g.pos[B + e], g.pos[2 * B + e]);
+  }
   finishEnv(g, st, e, done, moved, d, seedLo, seedHi);
 }
 

@@ -67,8 +67,16 @@ typedef struct {
   uint32_t num_scenes;       /* scenes resident on the device */
   uint64_t seed;             /* seeds the episode-selection stream */
   uint32_t flags;            /* BPSN_FLAG_* */
-  uint32_t reserved;
+  uint32_t task;             /* BPSN_TASK_* */
 } bpsn_config;
+
+/* Tasks of the reference's three generators (simulator/simulator.cpp:734-999,
+ * 1812-1822).  They share motion, sensor, done rule and reset; they differ in
+ * the info record and the reward:
+ *   POINTNAV     info {success, spl, distanceToGoal}; reward -dGeodesic + 2.5*spl - 0.01
+ *   FLEE         info {distanceFromStart} (geodesic, refreshed on moves); reward = its increase
+ *   EXPLORATION  info {numVisited} 1 m cells visited - 1;               reward 0.25 per new cell */
+enum { BPSN_TASK_POINTNAV = 0, BPSN_TASK_FLEE = 1, BPSN_TASK_EXPLORATION = 2 };
 
 enum {
   /* keep pinned host copies of reward/mask/info/polar, refreshed by every
@@ -86,7 +94,8 @@ enum {
 enum {
   BPSN_FIELD_REWARD = 0,     /* float32 [B]                               */
   BPSN_FIELD_MASK = 1,       /* uint8   [B]   1 = episode continues       */
-  BPSN_FIELD_INFO = 2,       /* float32 [B,3] success, spl, distanceToGoal*/
+  BPSN_FIELD_INFO = 2,       /* float32 [B,3] success, spl, distanceToGoal (PointNav);
+                                float32 [B] distanceFromStart (Flee) / numVisited (Exploration) */
   BPSN_FIELD_POLAR = 3,      /* float32 [B,2] rho, -phi                   */
   BPSN_FIELD_POSITION = 4,   /* float32 [3,B] x | y | z                   */
   BPSN_FIELD_ROTATION = 5,   /* float32 [4,B] x | y | z | w               */

@@ -9,6 +9,10 @@
 //   * PointNav::RewardFunctor::reset / step      (:801-806, 808-822)
 //   * constants                                   (:46-61)
 //   * the batch loop with in-loop auto-reset      (:1619-1653)
+//   * Flee::InfoFunctor / RewardFunctor           (:830-887)
+//   * Exploration::InfoFunctor / RewardFunctor    (:889-999; the visited set is a
+//     std::set of integer cells -- only its size is observable, so the
+//     reference's hash function plays no role)
 // All navigation-mesh arithmetic (snapPoint, tryStep, findPath) is done by
 // the reference's own compiled PathFinder through oracle/_ref/libref_nav.so
 // (see ref_capi.cpp); this file only restates the control flow around it and
@@ -29,6 +33,8 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <set>
+#include <tuple>
 #include <string>
 #include <thread>
 #include <vector>
@@ -128,6 +134,10 @@ struct Env {
   uint64_t navGoalPoly = 0;
   // RewardFunctor
   float rewardPrevDist = 0;
+  // Exploration
+  Vec3 initialPosition{};
+  Quat inverseInitialRotation{};
+  std::set<std::tuple<int, int, int>> visited;
 };
 
 struct Sim {
@@ -135,12 +145,14 @@ struct Sim {
   std::vector<std::string> navPaths;
   std::vector<std::vector<Episode>> episodes;
   int nEnvs = 0;
+  int task = 0;  // 0 PointNav, 1 Flee, 2 Exploration
   uint64_t seed = 0;
   std::vector<Env> envs;
   // outputs (simulator/simulator.cpp:1194-1197)
   std::vector<float> rewards;
   std::vector<uint8_t> masks;
-  std::vector<float> infos;   // 3 per env: success, spl, distanceToGoal
+  int infoWidth = 3;
+  std::vector<float> infos;   // PointNav: 3 per env (success, spl, distanceToGoal); else 1
   std::vector<float> polars;  // 2 per env
   Quat leftRot{}, rightRot{};
 
@@ -190,6 +202,15 @@ void updateObservation(Sim& s, int e) {
   s.polars[2 * e + 1] = -phi;
 }
 
+// Exploration::InfoFunctor::update (:897-904)
+void explorationUpdate(Env& v) {
+  Vec3 d{v.position.x - v.initialPosition.x, v.position.y - v.initialPosition.y,
+         v.position.z - v.initialPosition.z};
+  Vec3 g = quatRotate(v.inverseInitialRotation, d);
+  const float cell = 1.0f;
+  v.visited.emplace(int(g.x / cell), int(g.y / cell), int(g.z / cell));
+}
+
 void resetEnv(Sim& s, int e, std::vector<void*>& pfs) {
   Env& v = s.envs[e];
   void* pf = pfs[v.scene];
@@ -209,6 +230,29 @@ void resetEnv(Sim& s, int e, std::vector<void*>& pfs) {
   refnav_snap(pf, ep.start, v.navPos, &v.navPoly);
 
   updateObservation(s, e);
+
+  if (s.task == 1) {
+    // Flee::InfoFunctor::reset / RewardFunctor::reset: reference point = snapped start
+    v.navGoal[0] = v.navPos[0];
+    v.navGoal[1] = v.navPos[1];
+    v.navGoal[2] = v.navPos[2];
+    v.navGoalPoly = v.navPoly;
+    v.prevDist = 0;
+    v.rewardPrevDist = 0;
+    return;
+  }
+  if (s.task == 2) {
+    // Exploration::InfoFunctor::reset; glm::inverse(q) = conjugate(q) / dot(q, q)
+    v.visited.clear();
+    v.initialPosition = v.position;
+    const Quat& q = v.rotation;
+    const float nrm = q.x * q.x + q.y * q.y + q.z * q.z + q.w * q.w;
+    v.inverseInitialRotation = Quat{-q.x / nrm, -q.y / nrm, -q.z / nrm, q.w / nrm};
+    explorationUpdate(v);
+    v.prevDist = float(v.visited.size() - 1);
+    v.rewardPrevDist = v.prevDist;
+    return;
+  }
 
   // InfoFunctor::reset
   refnav_snap(pf, ep.goal, v.navGoal, &v.navGoalPoly);
@@ -252,6 +296,29 @@ int stepEnv(Sim& s, int e, int64_t action, std::vector<void*>& pfs) {
       return -1;
     }
     updateObservation(s, e);
+  }
+
+  if (s.task != 0) {
+    float info;
+    float reward;
+    if (s.task == 1) {
+      // Flee::InfoFunctor::step / RewardFunctor::step
+      if (v.positionUpdated)
+        v.prevDist = geoDist(s, pf, v.navGoal, v.navGoalPoly, v.navPos, v.navPoly);
+      info = v.prevDist;
+      reward = info - v.rewardPrevDist;
+    } else {
+      // Exploration::InfoFunctor::step / RewardFunctor::step
+      if (v.positionUpdated)
+        explorationUpdate(v);
+      info = float(v.visited.size() - 1);
+      reward = static_cast<float>(0.25 * (info - v.rewardPrevDist));
+    }
+    v.rewardPrevDist = info;
+    s.rewards[e] = reward;
+    s.masks[e] = done ? 0 : 1;
+    s.infos[e] = info;
+    return done ? 1 : 0;
   }
 
   // InfoFunctor::step
@@ -355,8 +422,10 @@ extern "C" {
 // each environment's scene.
 void* osim_create(int n_scenes, const char** navmesh_paths, const float* episodes,
                   const int* ep_offsets, int n_envs, const int* env_scene, uint64_t seed,
-                  int n_threads) {
+                  int n_threads, int task) {
   Sim* s = new Sim();
+  s->task = task;
+  s->infoWidth = task == 0 ? 3 : 1;
   s->nScenes = n_scenes;
   s->seed = seed;
   s->nEnvs = n_envs;

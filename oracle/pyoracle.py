@@ -156,7 +156,7 @@ def sim_lib():
         lib = C.CDLL(SIM_LIB)
         lib.osim_create.restype = C.c_void_p
         lib.osim_create.argtypes = [C.c_int, C.POINTER(C.c_char_p), _fp, C.POINTER(C.c_int),
-                                    C.c_int, C.POINTER(C.c_int), C.c_uint64, C.c_int]
+                                    C.c_int, C.POINTER(C.c_int), C.c_uint64, C.c_int, C.c_int]
         lib.osim_destroy.argtypes = [C.c_void_p]
         lib.osim_reset.argtypes = [C.c_void_p, C.c_int, C.c_int]
         lib.osim_step.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_int64)]
@@ -184,7 +184,9 @@ _STATE_U = {"nav_poly": 0, "goal_poly": 1, "step": 2, "episode": 3, "reset_count
 class OracleSim:
     """CPU oracle over a list of (navmesh_path, episodes[n,10]) scenes."""
 
-    def __init__(self, scenes, num_envs, seed, env_scene=None, threads=1):
+    TASKS = {"pointnav": 0, "flee": 1, "exploration": 2}
+
+    def __init__(self, scenes, num_envs, seed, env_scene=None, threads=1, task="pointnav"):
         lib = sim_lib()
         self._lib = lib
         self.num_envs = num_envs
@@ -201,13 +203,14 @@ class OracleSim:
         self._h = C.c_void_p(lib.osim_create(ns, paths, _p(allep, _fp),
                                              offs.ctypes.data_as(C.POINTER(C.c_int)), num_envs,
                                              env_scene.ctypes.data_as(C.POINTER(C.c_int)),
-                                             C.c_uint64(seed), threads))
+                                             C.c_uint64(seed), threads, self.TASKS[task]))
         if not self._h.value:
             raise RuntimeError("oracle simulator creation failed")
         n = num_envs
         self.rewards = np.ctypeslib.as_array(lib.osim_rewards(self._h), (n,))
         self.masks = np.ctypeslib.as_array(lib.osim_masks(self._h), (n,))
-        self.infos = np.ctypeslib.as_array(lib.osim_infos(self._h), (n, 3))
+        self.infos = np.ctypeslib.as_array(lib.osim_infos(self._h),
+                                           (n, 3 if task == "pointnav" else 1))
         self.polars = np.ctypeslib.as_array(lib.osim_polars(self._h), (n, 2))
 
     def close(self):

@@ -201,12 +201,12 @@ def test_create_validates_arguments_and_needs_a_gpu():
     from bps_nav_b200 import _lib as L
     lib = L.load()
     h = C.c_void_p()
-    bad = L.Config(gpu_id=0, num_envs=10, num_groups=1, num_scenes=3, seed=0, flags=0, reserved=0)
+    bad = L.Config(gpu_id=0, num_envs=10, num_groups=1, num_scenes=3, seed=0, flags=0, task=0)
     assert lib.bpsn_create(C.byref(bad), C.byref(h)) == L.ERR_INVALID_ARG
     assert b"multiple" in lib.bpsn_last_error(None)
     assert lib.bpsn_create(None, C.byref(h)) == L.ERR_INVALID_ARG
     if not torch.cuda.is_available():
-        ok = L.Config(gpu_id=0, num_envs=8, num_groups=1, num_scenes=1, seed=0, flags=0, reserved=0)
+        ok = L.Config(gpu_id=0, num_envs=8, num_groups=1, num_scenes=1, seed=0, flags=0, task=0)
         assert lib.bpsn_create(C.byref(ok), C.byref(h)) == L.ERR_NO_DEVICE
         # the Python mirror surfaces it as an exception: no silent CPU fallback
         from bps_nav_b200 import bps_sim
@@ -221,12 +221,27 @@ def test_create_validates_arguments_and_needs_a_gpu():
                         None) == L.ERR_INVALID_ARG
 
 
-def test_unimplemented_tasks_raise():
-    from bps_nav_b200 import bps_sim
-    from conftest import load_scene
-    for cls in (bps_sim.FleeRolloutGenerator, bps_sim.ExplorationRolloutGenerator):
-        with pytest.raises(NotImplementedError):
-            cls.from_scenes([load_scene("c0")], 8)
+@needs_oracle
+def test_oracle_flee_and_exploration_invariants():
+    """Flee: info = geodesic distance from the start, reward = its change; Exploration: info =
+    visited cells - 1 (non-decreasing within an episode), reward = 0.25 per new cell."""
+    eps = np.load(os.path.join(SCENES, "c0.episodes.npy"))
+    acts = pyoracle.philox_actions(120, 32, 5, "policy")
+    for task in ("flee", "exploration"):
+        sim = pyoracle.OracleSim([(scene_path("c0"), eps)], 32, 9, task=task)
+        sim.reset()
+        prev = np.zeros(32, np.float32)
+        for t in range(120):
+            sim.step(acts[t])
+            info = sim.infos[:, 0].copy()
+            scale = np.float32(0.25) if task == "exploration" else np.float32(1)
+            assert np.array_equal(sim.rewards, scale * (info - prev))
+            if task == "exploration":
+                assert (info >= prev).all() and (info == np.round(info)).all()
+            done = sim.masks == 0
+            assert np.array_equal(done, (acts[t] == 0) | (sim.state()["step"] == 1))
+            prev = np.where(done, np.float32(0), info)
+        sim.close()
 
 
 # ------------------------------------------------------------------ dataset / host logic

@@ -100,6 +100,45 @@ def test_double_buffered_groups():
     _compare_run(["c0", "m15", "m13", "m14"], 256, 64, seed=3, mix="uniform", double_buffered=True)
 
 
+@pytest.mark.parametrize("task,cls_name", [("flee", "FleeRolloutGenerator"),
+                                           ("exploration", "ExplorationRolloutGenerator")])
+@pytest.mark.parametrize("generic", [False, True])
+def test_other_tasks_match_oracle(task, cls_name, generic):
+    """Flee and Exploration generators (simulator/simulator.cpp:830-999) on two scenes."""
+    from bps_nav_b200 import bps_sim
+    names = ["c1", "m10"]
+    n, steps, seed = 512, 200, 31
+    scenes = [load_scene(s) for s in names]
+    gen = getattr(bps_sim, cls_name).from_scenes(scenes, n, seed=seed, generic_kernel=generic)
+    osim = pyoracle.OracleSim([(scene_path(s), sc.episodes) for s, sc in zip(names, scenes)], n,
+                              seed, threads=8, task=task)
+    gen.reset(0)
+    osim.reset()
+    actions = pyoracle.philox_actions(steps, n, seed + 1, "policy")
+    actions[::7] = pyoracle.philox_actions(steps, n, seed + 2, "uniform")[::7]  # some resets
+    field = "distanceFromStart" if task == "flee" else "numVisited"
+    for t in range(steps):
+        gen.step(0, actions[t])
+        osim.step(actions[t])
+        assert np.array_equal(gen.get_masks(0), osim.masks), f"mask, step {t}"
+        info = gen.get_infos(0)
+        assert info.dtype.names == (field,)
+        if task == "exploration":
+            assert np.array_equal(info[field], osim.infos[:, 0]), f"info, step {t}"
+            assert np.array_equal(gen.get_rewards(0), osim.rewards), f"reward, step {t}"
+        else:
+            assert _close(info[field], osim.infos[:, 0], 1e-4, 1e-6).all(), f"info, step {t}"
+            assert _close(gen.get_rewards(0), osim.rewards, 1e-4, 1e-5).all(), f"reward, step {t}"
+        assert _close(gen.get_polars(0), osim.polars, 0, 1e-5).all(), f"polar, step {t}"
+    torch.cuda.synchronize()
+    st = osim.state()
+    for name in ("nav_poly", "step", "episode", "reset_count"):
+        assert np.array_equal(gen.tensor(0, name).cpu().numpy().view(np.uint32), st[name]), name
+    assert gen.device_errors(0) == 0
+    gen.close()
+    osim.close()
+
+
 def test_step_protocol_errors():
     from bps_nav_b200 import bps_sim
     gen = bps_sim.PointNavRolloutGenerator.from_scenes([load_scene("c0")], 32, seed=1)
