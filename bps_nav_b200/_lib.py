@@ -14,7 +14,7 @@ SYMBOLS = [
     "bpsn_create", "bpsn_destroy", "bpsn_set_navmesh_file", "bpsn_set_navmesh_blob",
     "bpsn_set_episodes", "bpsn_set_env_scenes", "bpsn_finalize", "bpsn_reset", "bpsn_step_start", "bpsn_step_start_ex",
     "bpsn_step_end", "bpsn_get_ptr", "bpsn_device_error_flags", "bpsn_profile_enable", "bpsn_profile_read", "bpsn_scene_info", "bpsn_query_snap", "bpsn_query_try_step",
-    "bpsn_query_geodesic", "bpsn_gae_workspace_bytes", "bpsn_gae", "bpsn_gae_static", "bpsn_last_error",
+    "bpsn_query_geodesic", "bpsn_gae_workspace_bytes", "bpsn_gae", "bpsn_gae_static", "bpsn_selftest_sqrt", "bpsn_last_error",
     "bpsn_version",
 ]
 
@@ -84,6 +84,7 @@ def load():
                              C.c_float, vp, vp]
     lib.bpsn_gae_static.argtypes = [vp, vp, vp, vp, vp, vp, u32, u32, C.c_double, C.c_double, i32,
                                     C.c_float, vp]
+    lib.bpsn_selftest_sqrt.argtypes = [i32, u32, u32, C.POINTER(C.c_uint64)]
     lib.bpsn_last_error.argtypes = [vp]
     lib.bpsn_last_error.restype = C.c_char_p
     lib.bpsn_version.restype = C.c_char_p

@@ -219,6 +219,7 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
   const size_t oExplInit = place(expl ? 7 * B * f : 16), oNumCells = place(expl ? B * u : 16),
                oVisited = place(expl ? static_cast<size_t>(B) * kVisitedSlots * u : 16);
   const size_t oGeoList = place(B * u), oCounts = place((2 * ns + 4) * u),
+               oCounts2 = place((2 * ns + 4) * u), oErr = place(4 * u),
                oListBase = place((ns + 4) * u);
   g.stateBytes = off;
   BPSN_CUDA(sim, cudaMalloc(&g.stateBlob, off));
@@ -258,6 +259,8 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
   d.stats = reinterpret_cast<float*>(b + oStats);
   d.geoList = reinterpret_cast<uint32_t*>(b + oGeoList);
   d.counts = reinterpret_cast<uint32_t*>(b + oCounts);
+  d.countsNext = reinterpret_cast<uint32_t*>(b + oCounts2);
+  d.errFlags = reinterpret_cast<uint32_t*>(b + oErr);
   d.listBase = reinterpret_cast<const uint32_t*>(b + oListBase);
   {
     // per-scene segments of the geodesic work list, sized by the number of
@@ -389,6 +392,21 @@ inline uint32_t blocksFor(uint32_t n, uint32_t bs) {
 }
 
 }  // namespace
+
+// sqrtExact(x) == sqrtf(x), bit for bit, for every operand in [lo, hi]?
+__global__ void __launch_bounds__(256)
+k_selftest_sqrt(uint32_t lo, uint32_t hi, unsigned long long* mismatches) {
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+  unsigned long long bad = 0;
+  for (uint64_t i = lo + static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i <= hi;
+       i += stride) {
+    const float x = __uint_as_float(static_cast<uint32_t>(i));
+    if (__float_as_uint(sqrtExact(x)) != __float_as_uint(sqrtf(x)))
+      bad++;
+  }
+  if (bad)
+    atomicAdd(mismatches, bad);
+}
 
 extern "C" {
 
@@ -664,7 +682,9 @@ int32_t bpsn_step_start_ex(bpsn_sim* sim, uint32_t group, const int64_t* actions
   } else if (actions_mem != BPSN_MEM_DEVICE) {
     return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_step_start: actions_mem must be host or device");
   }
-  BPSN_CUDA(sim, cudaMemsetAsync(g.dev.counts, 0, 2 * g.numScenesUsed * sizeof(uint32_t), s));
+  // The work-list counters alternate between two arrays: this step fills one and
+  // zeroes the other for the step after it (both start zeroed).
+  std::swap(g.dev.counts, g.dev.countsNext);
   const bool prof = g.profiling;
   GroupDev gd = g.dev;
   gd.rewardOut = reward_out;
@@ -672,15 +692,36 @@ int32_t bpsn_step_start_ex(bpsn_sim* sim, uint32_t group, const int64_t* actions
   gd.polarOut = polar_out;
   const uint32_t seedLo = static_cast<uint32_t>(sim->cfg.seed);
   const uint32_t seedHi = static_cast<uint32_t>(sim->cfg.seed >> 32);
+  // Both kernels are launched with programmatic stream serialization: each may
+  // become resident while its predecessor in the stream is still running and
+  // does its read-only prologue (the step kernel: the copy of the scene image
+  // into shared memory) before it waits for the predecessor to finish.  Not
+  // while per-launch times are being recorded.
+  cudaLaunchAttribute pdl[1];
+  pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  pdl[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t lc = {};
+  lc.stream = s;
+  lc.attrs = pdl;
+  lc.numAttrs = prof ? 0 : 1;
   if (prof) cudaEventRecord(g.prof[0], s);
-  k_pre<<<blocksFor(B, 256), 256, 0, s>>>(gd, sim->table, dAct, sim->turn, seedLo, seedHi);
+  lc.gridDim = dim3(blocksFor(B, 256));
+  lc.blockDim = dim3(256);
+  lc.dynamicSmemBytes = 0;
+  BPSN_CUDA(sim, cudaLaunchKernelEx(&lc, k_pre, gd, sim->table, dAct, sim->turn, seedLo, seedHi));
   if (prof) cudaEventRecord(g.prof[1], s);
   if (g.warpGeo) {
-    k_step_warp<<<dim3(g.geoGridX, g.numScenesUsed), g.warpsPerBlock * 32, g.geoSmem, s>>>(
-        gd, sim->table, g.pcap, g.slabOffset, g.fallbackScratch, seedLo, seedHi);
+    lc.gridDim = dim3(g.geoGridX, g.numScenesUsed);
+    lc.blockDim = dim3(g.warpsPerBlock * 32);
+    lc.dynamicSmemBytes = g.geoSmem;
+    BPSN_CUDA(sim, cudaLaunchKernelEx(&lc, k_step_warp, gd, sim->table, g.pcap, g.slabOffset,
+                                      g.fallbackScratch, seedLo, seedHi));
   } else {
-    k_step_thread<<<dim3(blocksFor(g.maxSceneEnvs, 128), g.numScenesUsed), 128, 0, s>>>(
-        gd, sim->table, g.scratch, seedLo, seedHi);
+    lc.gridDim = dim3(blocksFor(g.maxSceneEnvs, 128), g.numScenesUsed);
+    lc.blockDim = dim3(128);
+    lc.dynamicSmemBytes = 0;
+    BPSN_CUDA(sim, cudaLaunchKernelEx(&lc, k_step_thread, gd, sim->table, g.scratch, seedLo,
+                                      seedHi));
   }
   if (prof) cudaEventRecord(g.prof[2], s);
   BPSN_CUDA(sim, cudaGetLastError());
@@ -719,7 +760,7 @@ int32_t bpsn_device_error_flags(bpsn_sim* sim, uint32_t group, uint32_t* flags) 
     return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_device_error_flags: bad argument");
   Group& g = sim->groups[group];
   BPSN_CUDA(sim, cudaSetDevice(sim->cfg.gpu_id));
-  BPSN_CUDA(sim, cudaMemcpy(flags, g.dev.counts + 2 * g.numScenesUsed, sizeof(uint32_t),
+  BPSN_CUDA(sim, cudaMemcpy(flags, g.dev.errFlags, sizeof(uint32_t),
                             cudaMemcpyDeviceToHost));
   return BPSN_OK;
 }
@@ -972,6 +1013,34 @@ int32_t bpsn_gae_static(const float* rewards, float* values, const uint8_t* mask
   if (e != cudaSuccess)
     return fail(nullptr, BPSN_ERR_CUDA,
                 std::string("bpsn_gae_static launch: ") + cudaGetErrorString(e));
+  return BPSN_OK;
+}
+
+// Self-test of sqrtExact() against the compiler's IEEE sqrtf over every fp32
+// bit pattern in [first_bits, last_bits]; counts the operands whose results
+// differ in any bit.
+int32_t bpsn_selftest_sqrt(int32_t gpu_id, uint32_t first_bits, uint32_t last_bits,
+                           uint64_t* mismatches) {
+  if (!mismatches || first_bits > last_bits)
+    return fail(nullptr, BPSN_ERR_INVALID_ARG, "bpsn_selftest_sqrt: bad arguments");
+  if (cudaSetDevice(gpu_id) != cudaSuccess)
+    return fail(nullptr, BPSN_ERR_NO_DEVICE, "bpsn_selftest_sqrt: no such device");
+  unsigned long long* dCount = nullptr;
+  cudaError_t e = cudaMalloc(&dCount, sizeof(unsigned long long));
+  if (e == cudaSuccess)
+    e = cudaMemset(dCount, 0, sizeof(unsigned long long));
+  if (e == cudaSuccess) {
+    k_selftest_sqrt<<<148 * 8, 256>>>(first_bits, last_bits, dCount);
+    e = cudaGetLastError();
+  }
+  unsigned long long h = 0;
+  if (e == cudaSuccess)
+    e = cudaMemcpy(&h, dCount, sizeof(h), cudaMemcpyDeviceToHost);
+  cudaFree(dCount);
+  if (e != cudaSuccess)
+    return fail(nullptr, BPSN_ERR_CUDA,
+                std::string("bpsn_selftest_sqrt: ") + cudaGetErrorString(e));
+  *mismatches = h;
   return BPSN_OK;
 }
 

@@ -17,14 +17,17 @@
 //     search node per polygon: dtNavMeshQuery::findPath only creates extra
 //     nodes per polygon for tile-border links, DetourNavMeshQuery.cpp:1040-1045)
 //     in the warp's private shared-memory slab;
-//   * the open list lives in registers, two (total, polygon) entries per lane;
+//   * the open list lives in registers, three (total, polygon) entries per lane;
 //     "pop" is one hardware warp min-reduction.  A binary heap and an arg-min
 //     return the same node whenever the minimum `total` is unique.  When two
 //     open nodes tie for the minimum the result would depend on the reference
 //     heap's internal order (dtNodeQueue, Detour/Source/DetourNode.cpp:172-200),
 //     so the warp abandons the fast path and lane 0 reruns the query with the
 //     exact sequential emulation (geodesic()) on a global-memory scratch slab.
-//     The same fallback is taken if more than 64 nodes are open at once;
+//     An open node that gets a better total (dtNodeQueue::modify) is not
+//     updated in place: a second entry is added and the superseded one is
+//     discarded when it is popped (its total no longer matches the node's).
+//     The same fallback is taken if a lane runs out of entries (96 in all);
 //   * the up-to-six neighbours of the popped polygon are evaluated by six
 //     lanes at once (portal midpoint, cost, heuristic, skip test, node update).
 //     Two edges leading to the same neighbour produce bit-identical
@@ -69,6 +72,7 @@ __device__ __forceinline__ void phaseAdd(PhaseAcc* a, int idx, long long cycles)
 #endif
 
 constexpr uint32_t kInfBits = 0x7f800000u;
+constexpr uint32_t kNodeVisited = 0x10000u;  // in nodeB.y next to the 16-bit parent
 
 // Shared-memory layout of a staged scene (byte offsets, each 16-byte aligned).
 struct StagedLayout {
@@ -98,18 +102,16 @@ __host__ __device__ inline StagedLayout stagedLayout(int nverts, int npolys, int
 
 // Per-warp slab for node capacity pcap (a multiple of 16):
 //   nodeA  float4 {x, y, z, cost}                      16 B / polygon
-//   nodeB  uint2  {total bits, parent | slot << 16}      8 B / polygon
-//   flags  uint8  0 unseen, 1 open, 2 closed             1 B / polygon
+//   nodeB  uint2  {total bits, parent | visited << 16}   8 B / polygon
 //   path   uint16 corridor, at most 256 polygons       512 B
 // After the search the node arrays are reused for the corridor's portals.
 __host__ __device__ inline size_t warpGeoSlabBytes(int pcap) {
-  return static_cast<size_t>(pcap) * 25 + 512;
+  return static_cast<size_t>(pcap) * 24 + 512;
 }
 
 struct WarpSlab {
   float4* nodeA;
   uint2* nodeB;
-  uint8_t* flags;
   uint16_t* path;
 };
 
@@ -117,8 +119,7 @@ __device__ __forceinline__ WarpSlab carveSlab(uint8_t* base, int pcap) {
   WarpSlab s;
   s.nodeA = reinterpret_cast<float4*>(base);
   s.nodeB = reinterpret_cast<uint2*>(base + static_cast<size_t>(pcap) * 16);
-  s.flags = base + static_cast<size_t>(pcap) * 24;
-  s.path = reinterpret_cast<uint16_t*>(base + static_cast<size_t>(pcap) * 25);
+  s.path = reinterpret_cast<uint16_t*>(base + static_cast<size_t>(pcap) * 24);
   return s;
 }
 
@@ -363,7 +364,7 @@ __device__ __forceinline__ float warpFunnel(const StagedView sc, const WarpSlab 
 __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSlab w, int lane,
                                               const float* startPosIn, uint32_t startRef,
                                               const float* endPosIn, uint32_t endRef,
-                                              uint32_t* status, bool* needFallback
+                                              uint32_t* status, uint32_t* needFallback
 #if defined(BPSN_PHASE_TIMING)
                                               , PhaseAcc* pacc
 #endif
@@ -372,7 +373,7 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
   // function and therefore live in local memory
   const float startPos[3] = {startPosIn[0], startPosIn[1], startPosIn[2]};
   const float endPos[3] = {endPosIn[0], endPosIn[1], endPosIn[2]};
-  *needFallback = false;
+  *needFallback = 0u;
   BPSN_TICK(tA0);
   // (i) trivial path: Eigen isApprox with precision 1e-5
   {
@@ -410,71 +411,102 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
     __syncwarp();
   } else {
     const int P = sc.npolys;
-    {
-      uint32_t* f32 = reinterpret_cast<uint32_t*>(w.flags);
-      const int words = (P + 3) / 4;
-      for (int i = lane; i < words; i += 32)
-        f32[i] = 0u;
-    }
+    for (int i = lane; i < P; i += 32)
+      w.nodeB[i] = make_uint2(0u, 0u);  // nobody visited
     __syncwarp();
-    // open list: two register entries per lane, kInfBits = empty
-    uint32_t t0 = kInfBits, t1 = kInfBits;
-    uint32_t p0 = 0, p1 = 0;
+    // open list: three register entries per lane, kInfBits = empty
+    uint32_t t0 = kInfBits, t1 = kInfBits, t2 = kInfBits;
+    uint32_t p0 = 0, p1 = 0, p2 = 0;
+    int newNodes = 0;  // nodes this lane created (summed over the warp at the end)
     if (lane == 0) {
       const float tot = vdist(startPos, endPos) * 0.999f;
       w.nodeA[startIdx] = make_float4(startPos[0], startPos[1], startPos[2], 0.f);
-      w.nodeB[startIdx] = make_uint2(__float_as_uint(tot), 0xffffu);
-      w.flags[startIdx] = 1;
+      w.nodeB[startIdx] = make_uint2(__float_as_uint(tot), 0xffffu | kNodeVisited);
       t0 = __float_as_uint(tot);
       p0 = startIdx;
+      newNodes = 1;
     }
     __syncwarp();
-    int nodeCount = 1;
     bool reached = false;
-    bool outOfNodes = false;
+    bool overflow = false;  // this lane had to drop an entry: the query is redone exactly
     int guard = 0;
     // Edge j of the popped polygon is evaluated by lane (j + rot) & 31 and rot moves on
     // after every pop, so that over a search every lane gets to evaluate neighbours: a
-    // new open node is kept in the *evaluating* lane's own registers, without any
+    // new open entry is kept in the *evaluating* lane's own registers, without any
     // cross-lane traffic, and the entries spread over the warp.
     int rot = 0;
 
     while (true) {
-      if (++guard > 32 * kMaxAStarNodes) {
+      if (++guard > 64 * kMaxAStarNodes) {
         *status |= kStatIterCap;
         return BPSN_INF;
       }
       BPSN_TICK(tP0);
       // ---- pop: totals are non-negative floats, so their bit patterns order
-      // like unsigned integers and one warp reduction finds the minimum
-      const uint32_t lm = min(t0, t1);
+      // like unsigned integers and one warp reduction finds the minimum.  A lane
+      // that overflowed reports 0 so that the search stops at once.
+      const uint32_t lm = overflow ? 0u : min(min(t0, t1), t2);
       const uint32_t gm = __reduce_min_sync(0xffffffffu, lm);
-      if (gm == kInfBits)
-        break;  // open list empty: the end polygon was not reached
-      const uint32_t b0 = __ballot_sync(0xffffffffu, t0 == gm);
-      const uint32_t b1 = __ballot_sync(0xffffffffu, t1 == gm);
-      if (__popc(b0) + __popc(b1) != 1) {
-        *needFallback = true;
-        return 0.f;
+      const bool m0 = t0 == gm, m1 = t1 == gm, m2 = t2 == gm;
+      const int mc = (m0 ? 1 : 0) + (m1 ? 1 : 0) + (m2 ? 1 : 0);
+      const uint32_t holders = __ballot_sync(0xffffffffu, mc != 0);
+      const uint32_t mine = (m0 ? p0 : (m1 ? p1 : p2)) | (mc > 1 ? 0x80000000u : 0u);
+      uint32_t best = __shfl_sync(0xffffffffu, mine, (__ffs(holders) - 1) & 31);
+      // one branch for everything that is not "a unique minimum that is not the end"
+      if ((__popc(holders) != 1) | (best >= 0x80000000u) | (best == endIdx)) {
+        if (gm == kInfBits)
+          break;  // open list empty: the end polygon was not reached
+        if (__popc(holders) != 1 || best >= 0x80000000u) {
+          if (__any_sync(0xffffffffu, overflow)) {
+            *needFallback = kStatOpenOverflow;
+            return 0.f;
+          }
+          // Several entries share the minimum.  Superseded entries do not count: only
+          // those whose total is still their node's are in the reference's heap.
+          const bool l0 = m0 && w.nodeB[p0].x == gm;
+          const bool l1 = m1 && w.nodeB[p1].x == gm;
+          const bool l2 = m2 && w.nodeB[p2].x == gm;
+          const int lc = (l0 ? 1 : 0) + (l1 ? 1 : 0) + (l2 ? 1 : 0);
+          const uint32_t liveHolders = __ballot_sync(0xffffffffu, lc != 0);
+          const bool liveMulti = __any_sync(0xffffffffu, lc > 1);
+#if defined(BPSN_PHASE_TIMING)
+          if (lane == 0) {
+            atomicAdd(&g_phaseCycles[17], 1ull);
+            if (liveHolders == 0u) atomicAdd(&g_phaseCycles[18], 1ull);
+            if (__popc(liveHolders) == 1 && !liveMulti) atomicAdd(&g_phaseCycles[19], 1ull);
+            if (__popc(liveHolders) > 1 || liveMulti) {
+              atomicAdd(&g_phaseCycles[20], 1ull);
+              g_phaseCycles[21] = gm;
+            }
+          }
+          if ((__popc(liveHolders) > 1 || liveMulti) && lc != 0) {
+            // sample: which polygons tie
+            const uint32_t pp = l0 ? p0 : (l1 ? p1 : p2);
+            if (lane == __ffs(liveHolders) - 1) g_phaseCycles[22] = pp | (static_cast<unsigned long long>(w.nodeB[pp].y) << 32);
+            else g_phaseCycles[23] = pp | (static_cast<unsigned long long>(w.nodeB[pp].y) << 32);
+          }
+#endif
+          if (__popc(liveHolders) > 1 || liveMulti) {
+            *needFallback = kStatTieFallback;  // a real tie: the heap's order decides
+            return 0.f;
+          }
+          if (liveHolders == 0u) {  // only superseded entries surfaced: drop them
+            t0 = m0 ? kInfBits : t0;
+            t1 = m1 ? kInfBits : t1;
+            t2 = m2 ? kInfBits : t2;
+            continue;
+          }
+          best = __shfl_sync(0xffffffffu, l0 ? p0 : (l1 ? p1 : p2), __ffs(liveHolders) - 1);
+        }
+        if (best == endIdx) {
+          reached = true;
+          break;
+        }
       }
-      uint32_t best;
-      if (b0) {
-        const int wl = __ffs(b0) - 1;
-        best = __shfl_sync(0xffffffffu, p0, wl);
-        if (lane == wl)
-          t0 = kInfBits;
-      } else {
-        const int wl = __ffs(b1) - 1;
-        best = __shfl_sync(0xffffffffu, p1, wl);
-        if (lane == wl)
-          t1 = kInfBits;
-      }
-      if (best == endIdx) {
-        reached = true;
-        break;
-      }
-      if (lane == 0)
-        w.flags[best] = 2;  // closed
+      // the popped entry and, after a resolved tie, the superseded ones beside it
+      t0 = m0 ? kInfBits : t0;
+      t1 = m1 ? kInfBits : t1;
+      t2 = m2 ? kInfBits : t2;
       BPSN_TICK(tP1);
 
       // ---- expand: one lane per edge of the popped polygon.  All loads of a
@@ -490,13 +522,61 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
       const uint16_t vbNext = (&bp->verts[0])[li + 1];
       const uint16_t vbFirst = bp->verts[0];
       const float4 bA = w.nodeA[best];
-      const uint32_t bpar = w.nodeB[best].y & 0xffffu;
+      const uint2 bB = w.nodeB[best];
 
+      // While those loads are in flight: a lane whose three entries are all taken
+      // hands one to a lane with room (preferably one with two free pairs), so that
+      // it can accept a neighbour below.
+      // A lane evaluates a neighbour at most once in four consecutive pops (the windows
+      // of six lanes move on by seven), so looking every fourth pop is often enough.
+      if ((guard & 3) == 0) {
+        const bool f0 = t0 == kInfBits, f1 = t1 == kInfBits, f2 = t2 == kInfBits;
+        uint32_t fb = __ballot_sync(0xffffffffu, !f0 && !f1 && !f2);
+        if (fb) {
+          const int freeCnt = (f0 ? 1 : 0) + (f1 ? 1 : 0) + (f2 ? 1 : 0);
+          uint32_t rb = __ballot_sync(0xffffffffu, freeCnt >= 2);
+          const uint32_t rb1 = __ballot_sync(0xffffffffu, freeCnt >= 1);
+          if (!rb)
+            rb = rb1;
+          while (fb && rb) {
+            const int src = __ffs(fb) - 1, dst = __ffs(rb) - 1;
+            fb &= fb - 1;
+            rb &= rb - 1;
+            const uint32_t mt = __shfl_sync(0xffffffffu, t2, src);
+            const uint32_t mp = __shfl_sync(0xffffffffu, p2, src);
+            if (lane == dst) {  // into its first free pair
+              if (f0) {
+                t0 = mt;
+                p0 = mp;
+              } else if (f1) {
+                t1 = mt;
+                p1 = mp;
+              } else {
+                t2 = mt;
+                p2 = mp;
+              }
+            }
+            if (lane == src)
+              t2 = kInfBits;
+          }
+        }
+      }
+
+      const uint32_t bpar = bB.y & 0xffffu;
       const uint16_t vb = (li + 1 == nv) ? vbFirst : vbNext;
       bool act = ej < nv && ne != 0 && !(ne & kExtLink) &&
                  static_cast<uint32_t>(ne - 1) != bpar;
       uint32_t nei = act ? static_cast<uint32_t>(ne - 1) : best;
-      if (dupFlag & 1) {  // polygon shares more than one edge with some neighbour (rare)
+      if ((bB.x != gm) | (dupFlag & 1)) {  // one branch for the two uncommon cases
+        // Entries are never updated in place: a better total for an open node adds a
+        // second entry and the superseded one is dropped here, when it surfaces.  All
+        // entries of a node have different totals (each is strictly below the one
+        // before), so the live one is the one that matches the node's current total.
+        if (bB.x != gm) {
+          rot = (rot + 7) & 31;
+          continue;
+        }
+        // the polygon shares more than one edge with some neighbour
         const uint32_t grp = __match_any_sync(0xffffffffu, act ? nei : 0xffff0000u + lane);
         // bit k of the rotated mask = edge k; the lowest edge of the group acts
         const uint32_t byEdge = __funnelshift_r(grp, grp, rot);
@@ -507,118 +587,52 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
       }
       const float4 nA = w.nodeA[nei];
       const uint2 nB = w.nodeB[nei];
-      const uint8_t nf = w.flags[nei];
       const float4 V0 = ldVert4(sc, va);
       const float4 V1 = ldVert4(sc, vb);
 
       BPSN_TICK(tE1);
-      const bool isNew = act && nf == 0;
-      const uint32_t newMask = __ballot_sync(0xffffffffu, isNew);
-      if (nodeCount + __popc(newMask) > kMaxAStarNodes) {
-        outOfNodes = true;  // some getNode() would have failed: DT_OUT_OF_NODES
-        break;
-      }
-      nodeCount += __popc(newMask);
-
-      float nx, ny, nz;
-      if (isNew) {
-        nx = (V0.x + V1.x) * 0.5f;
-        ny = (V0.y + V1.y) * 0.5f;
-        nz = (V0.z + V1.z) * 0.5f;
-      } else {
-        nx = nA.x;
-        ny = nA.y;
-        nz = nA.z;
-      }
+      const bool isNew = act && !(nB.y & kNodeVisited);
+      newNodes += isNew ? 1 : 0;
+      const float nx = isNew ? (V0.x + V1.x) * 0.5f : nA.x;
+      const float ny = isNew ? (V0.y + V1.y) * 0.5f : nA.y;
+      const float nz = isNew ? (V0.z + V1.z) * 0.5f : nA.z;
       const float bpos[3] = {bA.x, bA.y, bA.z};
       const float npos[3] = {nx, ny, nz};
-      const float curCost = vdist(bpos, npos) * 1.0f;
-      const float toEnd = vdist(npos, endPos);
-      float cost, heuristic;
-      if (nei == endIdx) {
-        cost = bA.w + curCost + toEnd * 1.0f;
-        heuristic = 0.f;
-      } else {
-        cost = bA.w + curCost;
-        heuristic = toEnd * 0.999f;
-      }
+      // lanes without a neighbour take the root of 1: a zero operand would send the
+      // whole warp through the square root's slow path
+      const float c2 = act ? vdistSqr(bpos, npos) : 1.f;
+      const float e2 = act ? vdistSqr(npos, endPos) : 1.f;
+      float curCost, toEnd;  // vdist(bpos, npos) * 1.0f and vdist(npos, endPos)
+      sqrtExact2(c2, e2, curCost, toEnd);
+      const bool atEnd = nei == endIdx;
+      // end polygon: cost = g + step + distance to the end point, h = 0
+      const float base = bA.w + curCost;
+      const float cost = atEnd ? base + toEnd * 1.0f : base;
+      const float heuristic = atEnd ? 0.f : toEnd * 0.999f;
       const float ntotal = cost + heuristic;
       const uint32_t ntBits = __float_as_uint(ntotal);
+      // open or closed alike: skipped unless strictly better (DetourNavMeshQuery.cpp:1075-1080)
       const bool upd = act && (isNew || !(ntotal >= __uint_as_float(nB.x)));
-      const bool wasOpen = (nf & 1) != 0;
 
       BPSN_TICK(tE2);
-      // ---- open-list bookkeeping
-      uint32_t mySlot = (nB.y >> 16) & 0xffu;
-      bool spill = false;
-      if (upd && !wasOpen) {
-        if (t0 == kInfBits) {
-          t0 = ntBits;
-          p0 = nei;
-          mySlot = static_cast<uint32_t>(lane);
-        } else if (t1 == kInfBits) {
-          t1 = ntBits;
-          p1 = nei;
-          mySlot = static_cast<uint32_t>(lane) | 32u;
-        } else {
-          spill = true;  // both of this lane's entries are taken
-        }
-      }
-      uint32_t am = __ballot_sync(0xffffffffu, spill);
-      if (am) {
-        // rare: hand the entry to any lane that has a free slot
-        uint32_t f0 = __ballot_sync(0xffffffffu, t0 == kInfBits);
-        uint32_t f1 = __ballot_sync(0xffffffffu, t1 == kInfBits);
-        if (__popc(am) > __popc(f0) + __popc(f1)) {
-          *needFallback = true;
-          return 0.f;
-        }
-        while (am) {
-          const int src = __ffs(am) - 1;
-          am &= am - 1;
-          int dst, reg;
-          if (f0) {
-            dst = __ffs(f0) - 1;
-            f0 &= f0 - 1;
-            reg = 0;
-          } else {
-            dst = __ffs(f1) - 1;
-            f1 &= f1 - 1;
-            reg = 1;
-          }
-          const uint32_t nt = __shfl_sync(0xffffffffu, ntBits, src);
-          const uint32_t np = __shfl_sync(0xffffffffu, nei, src);
-          if (lane == dst) {
-            if (reg == 0) {
-              t0 = nt;
-              p0 = np;
-            } else {
-              t1 = nt;
-              p1 = np;
-            }
-          }
-          if (lane == src)
-            mySlot = static_cast<uint32_t>(dst) | (static_cast<uint32_t>(reg) << 5);
-        }
-      }
-      uint32_t mm = __ballot_sync(0xffffffffu, upd && wasOpen);
-      while (mm) {
-        const int src = __ffs(mm) - 1;
-        mm &= mm - 1;
-        const uint32_t sl = __shfl_sync(0xffffffffu, mySlot, src);
-        const uint32_t nt = __shfl_sync(0xffffffffu, ntBits, src);
-        if (lane == static_cast<int>(sl & 31u)) {
-          if (sl >> 5)
-            t1 = nt;
-          else
-            t0 = nt;
-        }
+      // ---- the new entry goes into this lane's first free register pair
+      {
+        const bool f0 = t0 == kInfBits, f1 = t1 == kInfBits, f2 = t2 == kInfBits;
+        const bool i0 = upd && f0;
+        const bool i1 = upd && !f0 && f1;
+        const bool i2 = upd && !f0 && !f1 && f2;
+        t0 = i0 ? ntBits : t0;
+        p0 = i0 ? nei : p0;
+        t1 = i1 ? ntBits : t1;
+        p1 = i1 ? nei : p1;
+        t2 = i2 ? ntBits : t2;
+        p2 = i2 ? nei : p2;
+        overflow = overflow || (upd && !f0 && !f1 && !f2);
       }
       BPSN_TICK(tE3);
       if (upd) {
         w.nodeA[nei] = make_float4(nx, ny, nz, cost);
-        w.nodeB[nei] = make_uint2(ntBits, best | (mySlot << 16));
-        w.flags[nei] = 1;  // open (closed bit cleared)
+        w.nodeB[nei] = make_uint2(ntBits, best | kNodeVisited);
       }
       rot = (rot + 7) & 31;
       __syncwarp();
@@ -635,6 +649,14 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
 #endif
     }
 
+    if (__any_sync(0xffffffffu, overflow)) {
+      *needFallback = kStatOpenOverflow;
+      return 0.f;
+    }
+    // dtNodePool hands out at most kMaxAStarNodes nodes; a search that asks for more
+    // ends with DT_OUT_OF_NODES in its status, which PathFinder turns into +inf
+    // whatever path was found (PathFinder.cpp:506).
+    const bool outOfNodes = __reduce_add_sync(0xffffffffu, newNodes) > kMaxAStarNodes;
     if (outOfNodes) {
       *status |= kStatOutOfNodes;
       return BPSN_INF;
@@ -686,15 +708,14 @@ __global__ void __launch_bounds__(512, 1)
 k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
             AStarScratch* __restrict__ fallbackScratch, uint32_t seedLo, uint32_t seedHi) {
   extern __shared__ __align__(16) uint8_t smem[];
+  launchDependents();
   const int sceneIdx = blockIdx.y;
-  const uint32_t n = g.counts[sceneIdx];
   const int warpsPerBlock = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  if (static_cast<uint32_t>(blockIdx.x) * warpsPerBlock >= n)
-    return;
 
   BPSN_TICK(tS0);
+  uint32_t n = 0;
   const NavScene scGlobal = st.scenes[sceneIdx];
   NavScene sc = scGlobal;
   const StagedLayout lay = stagedLayout(sc.nverts, sc.npolys, sc.ndtris, sc.ndverts);
@@ -721,6 +742,14 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
           ::"r"(dst), "l"(scGlobal.staged), "r"(bytes), "r"(bar)
           : "memory");
     }
+    // The scene image never changes, so the copy above may run while the kernel
+    // before this one is still at work; everything below reads what it wrote.
+    waitForPredecessor();
+    n = g.counts[sceneIdx];
+    if (blockIdx.x == 0 && threadIdx.x == 0) {  // the next step starts from empty lists
+      g.countsNext[sceneIdx] = 0u;
+      g.countsNext[gridDim.y + sceneIdx] = 0u;
+    }
     // bounded wait on phase 0 of the barrier; a copy of this size lands within
     // microseconds, the bound is ~1 s of polling
     bool landed = false;
@@ -739,10 +768,12 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
       // never observed; leave without touching the half-filled tables (the step's
       // listed envs keep their previous outputs) and make the failure visible
       if (threadIdx.x == 0)
-        atomicOr(&g.counts[2 * gridDim.y], 1u);
+        atomicOr(g.errFlags, 1u);
       return;
     }
   }
+  if (static_cast<uint32_t>(blockIdx.x) * warpsPerBlock >= n)
+    return;  // (only after the copy has landed: it targets this CTA's shared memory)
   sc.verts = reinterpret_cast<const float*>(smem + lay.verts);
   sc.vstride = 4;
   sc.polys = reinterpret_cast<const NavPoly*>(smem + lay.polys);
@@ -769,7 +800,7 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
 
   const uint32_t B = g.B;
   const uint32_t base = g.listBase[sceneIdx];
-  uint32_t* cursor = g.counts + gridDim.y + sceneIdx;  // zeroed with the counts every step
+  uint32_t* cursor = g.counts + gridDim.y + sceneIdx;  // zeroed by the step before
   while (true) {
     uint32_t q = 0;
     if (lane == 0)
@@ -791,7 +822,7 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
     const uint32_t aref = g.navRef[e];
     const uint32_t bref = g.goalRef[e];
     uint32_t status = 0;
-    bool fallback = false;
+    uint32_t fallback = 0u;
     float d = 0.f;
     // PointNav queries on every listed step, Flee only after a move, Exploration never
     const bool needGeo = g.task == kTaskPointNav || (g.task == kTaskFlee && moved);
@@ -810,7 +841,7 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
         const size_t slot = static_cast<size_t>(blockIdx.y) * gridDim.x * warpsPerBlock +
                             static_cast<size_t>(blockIdx.x) * warpsPerBlock + warp;
         d = geodesic(scGlobal, fallbackScratch + slot, b, bref, a, aref, &status);
-        status |= kStatTieFallback;
+        status |= fallback;
       }
       if (g.task == kTaskExploration && moved)
         explVisit(g, e, a[0], a[1], a[2]);

@@ -96,6 +96,9 @@ struct GroupDev {
   // counts[s] entries are valid this step
   uint32_t* geoList;         // [B]
   uint32_t* counts;          // [2 * numScenes]: list lengths, then work-queue cursors
+  uint32_t* countsNext;      // the next step's `counts`: the step kernel zeroes it, so that no
+                             // separate clearing pass sits between two steps
+  uint32_t* errFlags;        // [1] sticky device-side error bits (never cleared by kernels)
   const uint32_t* listBase;  // [numScenes]
 };
 
@@ -118,6 +121,17 @@ struct SceneTable {
   const uint32_t* epOffset;   // [numScenes]
   const uint32_t* epCount;    // [numScenes]
 };
+
+// Programmatic dependent launch: a kernel lets the next one in the stream start
+// its prologue early (launchDependents) and the next one waits for the whole of
+// its predecessor, memory included, before it touches anything the predecessor
+// writes (waitForPredecessor).  Both are no-ops for an ordinary launch.
+__device__ __forceinline__ void launchDependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void waitForPredecessor() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
 
 struct TurnConsts {  // +/-10 degrees about +Y, evaluated once on the host
   float lx, ly, lz, lw;
@@ -164,7 +178,7 @@ __device__ __forceinline__ void writePolar(const GroupDev& g, uint32_t e, float 
   const float vx = m00 * tx + m01 * ty + m02 * tz;
   const float vz = m20 * tx + m21 * ty + m22 * tz;
   const float ax = -vz, ay = vx;
-  const float rho = sqrtf(ax * ax + ay * ay);
+  const float rho = sqrtExact(ax * ax + ay * ay);
   const float phi = atan2f(ay, ax);
   reinterpret_cast<float2*>(g.polar)[e] = make_float2(rho, -phi);
   if (g.polarOut)
@@ -310,7 +324,7 @@ __device__ __forceinline__ void finishEnv(const GroupDev& g, const SceneTable& s
       const float dx = px - g.prevPos[e];
       const float dy = py - g.prevPos[B + e];
       const float dz = pz - g.prevPos[2 * B + e];
-      g.cumTravel[e] += sqrtf(dx * dx + dy * dy + dz * dz);
+      g.cumTravel[e] += sqrtExact(dx * dx + dy * dy + dz * dz);
       g.prevDist[e] = d;
       g.prevPos[e] = px;
       g.prevPos[B + e] = py;
@@ -401,6 +415,8 @@ __device__ __forceinline__ void forwardMove(const GroupDev& g, const NavScene& s
 __global__ void __launch_bounds__(256)
 k_pre(GroupDev g, SceneTable st, const int64_t* __restrict__ actions, TurnConsts tc,
       uint32_t seedLo, uint32_t seedHi) {
+  launchDependents();
+  waitForPredecessor();
   const uint32_t e = blockIdx.x * blockDim.x + threadIdx.x;
   if (e >= g.B)
     return;
@@ -468,9 +484,15 @@ k_pre(GroupDev g, SceneTable st, const int64_t* __restrict__ actions, TurnConsts
 __global__ void __launch_bounds__(128)
 k_step_thread(GroupDev g, SceneTable st, AStarScratch* __restrict__ scratch, uint32_t seedLo,
               uint32_t seedHi) {
+  launchDependents();
+  waitForPredecessor();
   const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
   const uint32_t sceneIdx = blockIdx.y;
   const uint32_t n = g.counts[sceneIdx];
+  if (t == 0) {  // the next step starts from empty lists
+    g.countsNext[sceneIdx] = 0u;
+    g.countsNext[gridDim.y + sceneIdx] = 0u;
+  }
   if (t >= n)
     return;
   const uint32_t slot = g.listBase[sceneIdx] + t;

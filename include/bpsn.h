@@ -241,6 +241,18 @@ int32_t bpsn_gae_static(const float* rewards, float* values, const uint8_t* mask
                         uint32_t N, double gamma, double tau, int32_t normalize, float eps,
                         void* stream);
 
+/* Self-test of the library's arithmetic contract.  Navigation-mesh queries take
+ * square roots with a hand-written estimate-and-correct sequence that must
+ * return exactly what IEEE sqrtf returns (results feed discrete decisions:
+ * A* pop order, funnel side tests).  This compares the two on the GPU for every
+ * fp32 bit pattern in [first_bits, last_bits] and returns the number of
+ * operands on which they differ (expected: 0 for any range, including zero,
+ * denormals, negatives, inf and NaN patterns).  The whole positive range
+ * 0x00000000..0x7f800000 takes about a second.  Allocates 8 bytes of device
+ * memory for the duration of the call. */
+int32_t bpsn_selftest_sqrt(int32_t gpu_id, uint32_t first_bits, uint32_t last_bits,
+                           uint64_t* mismatches);
+
 const char* bpsn_last_error(const bpsn_sim* sim);
 /* Library build identification, e.g. "bpsn sm_100a". */
 const char* bpsn_version(void);

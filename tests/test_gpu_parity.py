@@ -144,3 +144,14 @@ def test_gae_matches_reference_python(tag):
                             normalize=True)
     torch.cuda.synchronize()
     assert _close(adv.cpu().numpy(), g[f"{tag}_adv_norm"], 1e-5, 2e-6).all()
+
+
+def test_exact_sqrt_is_ieee_for_every_float():
+    """The hand-written square root of the navmesh queries returns sqrtf's bits for every
+    fp32 operand (all 2^32 bit patterns: zero, denormals, normals, inf, NaN, negatives)."""
+    import ctypes as C
+    from bps_nav_b200 import _lib as L
+    lib = L.load()
+    bad = C.c_uint64(1)
+    L.check(lib.bpsn_selftest_sqrt(0, 0x00000000, 0xFFFFFFFF, C.byref(bad)))
+    assert bad.value == 0
