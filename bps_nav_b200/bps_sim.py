@@ -98,17 +98,17 @@ class _RolloutGenerator:
     @classmethod
     def from_scenes(cls, scenes, num_environments, num_active_scenes=None, gpu_id=0,
                     render_resolution=(64, 64), color=False, depth=False, double_buffered=False,
-                    seed=0, host_mirrors=True, generic_kernel=False):
+                    seed=0, host_mirrors=True, generic_kernel=False, exact_heap=False):
         """Builds a generator from in-memory ``dataset.Scene`` objects (no JSON involved)."""
         self = cls.__new__(cls)
         if num_active_scenes is None:
             num_active_scenes = len(scenes)
         self._setup(list(scenes), num_environments, num_active_scenes, gpu_id, render_resolution,
-                    color, depth, double_buffered, seed, host_mirrors, generic_kernel)
+                    color, depth, double_buffered, seed, host_mirrors, generic_kernel, exact_heap)
         return self
 
     def _setup(self, scenes, num_environments, num_active_scenes, gpu_id, render_resolution, color,
-               depth, double_buffered, seed, host_mirrors, generic_kernel=False):
+               depth, double_buffered, seed, host_mirrors, generic_kernel=False, exact_heap=False):
         if self._task not in _TASKS:
             raise NotImplementedError(f"{type(self).__name__}: unknown task")
         self._task_id, self._info_dtype = _TASKS[self._task]
@@ -132,7 +132,8 @@ class _RolloutGenerator:
         cfg = L.Config(gpu_id=self.gpu_id, num_envs=self.num_environments, num_groups=num_groups,
                        num_scenes=len(self._scenes), seed=int(seed) & (2**64 - 1),
                        flags=(L.FLAG_HOST_MIRRORS if host_mirrors else 0) |
-                       (L.FLAG_GENERIC_KERNEL if generic_kernel else 0),
+                       (L.FLAG_GENERIC_KERNEL if generic_kernel else 0) |
+                       (L.FLAG_EXACT_HEAP if exact_heap else 0),
                        task=self._task_id)
         L.check(self._lib.bpsn_create(C.byref(cfg), C.byref(self._h)))
         try:

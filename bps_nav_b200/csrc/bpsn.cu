@@ -230,6 +230,7 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
   d.envBase = envBase;
   d.task = sim->cfg.task;
   d.infoWidth = sim->cfg.task == BPSN_TASK_POINTNAV ? 3u : 1u;
+  d.exactHeap = (sim->cfg.flags & BPSN_FLAG_EXACT_HEAP) ? 1u : 0u;
   d.explInit = reinterpret_cast<float*>(b + oExplInit);
   d.numCells = reinterpret_cast<uint32_t*>(b + oNumCells);
   d.visited = reinterpret_cast<uint32_t*>(b + oVisited);

@@ -357,6 +357,176 @@ __device__ __forceinline__ float warpFunnel(const StagedView sc, const WarpSlab 
   return result;
 }
 
+constexpr uint32_t kNodeOpen = 0x20000u;  // exact search only: the node is in the heap
+constexpr int kSlabHeapCap = kMaxPathPolys;  // the corridor array doubles as the heap
+
+// dtNodeQueue on the slab: the heap holds polygon indices (uint16) in w.path and
+// compares the nodes' current totals (nodeB.x), exactly like the reference's
+// heap of node pointers (Detour/Source/DetourNode.cpp:172-200).  Every lane runs
+// the same code on the same addresses and writes the same values, so each lane
+// reads back what it wrote itself and no synchronisation is needed in here.
+__device__ __forceinline__ float slabTotal(const WarpSlab& w, uint32_t node) {
+  return __uint_as_float(w.nodeB[node].x);
+}
+__device__ __forceinline__ void slabBubbleUp(const WarpSlab& w, int i, uint32_t node) {
+  const float tn = slabTotal(w, node);
+  int parent = (i - 1) / 2;
+  while (i > 0) {
+    const uint32_t pn = w.path[parent];
+    if (!(slabTotal(w, pn) > tn))
+      break;
+    w.path[i] = static_cast<uint16_t>(pn);
+    i = parent;
+    parent = (i - 1) / 2;
+  }
+  w.path[i] = static_cast<uint16_t>(node);
+}
+__device__ __forceinline__ void slabTrickleDown(const WarpSlab& w, int size, int i,
+                                                uint32_t node) {
+  int child = i * 2 + 1;
+  while (child < size) {
+    if ((child + 1) < size && slabTotal(w, w.path[child]) > slabTotal(w, w.path[child + 1]))
+      child++;
+    w.path[i] = w.path[child];
+    i = child;
+    child = i * 2 + 1;
+  }
+  slabBubbleUp(w, i, node);
+}
+
+enum AStarOutcome : int {
+  kAStarReached = 0,
+  kAStarExhausted = 1,  // open list ran empty before the end polygon was popped
+  kAStarIterCap = 2,
+  kAStarHeapFull = 3,   // exact slab search only: more than kSlabHeapCap open nodes
+};
+
+// dtNavMeshQuery::findPath (DetourNavMeshQuery.cpp:945-1137) with the reference's
+// own open list, a binary heap, kept in the slab: taken when the register open
+// list cannot decide the pop order (two live entries tie for the minimum) or is
+// full.  The neighbours of the popped polygon are still evaluated by one lane
+// each; their node updates and heap operations then happen one edge after the
+// other in edge order, as in the reference's loop, because a heap operation
+// compares against the totals the earlier edges have already written.
+__device__ __noinline__ int astarExactSlab(const StagedView sc, const WarpSlab w, int lane,
+                                           const float* startPosIn, const float* endPosIn,
+                                           uint32_t startIdx, uint32_t endIdx, int* nodesOut) {
+  const float startPos[3] = {startPosIn[0], startPosIn[1], startPosIn[2]};
+  const float endPos[3] = {endPosIn[0], endPosIn[1], endPosIn[2]};
+  const int P = sc.npolys;
+  __syncwarp();
+  for (int i = lane; i < P; i += 32)
+    w.nodeB[i] = make_uint2(0u, 0u);
+  __syncwarp();
+  if (lane == 0) {
+    const float tot = vdist(startPos, endPos) * 0.999f;
+    w.nodeA[startIdx] = make_float4(startPos[0], startPos[1], startPos[2], 0.f);
+    w.nodeB[startIdx] = make_uint2(__float_as_uint(tot), 0xffffu | kNodeVisited | kNodeOpen);
+  }
+  __syncwarp();
+  int heapSize = 1;
+  slabBubbleUp(w, 0, startIdx);
+  int nodes = 1;
+  int outcome = kAStarExhausted;
+  int guard = 0;
+  while (heapSize > 0) {
+    if (++guard > 32 * kMaxAStarNodes) {
+      outcome = kAStarIterCap;
+      break;
+    }
+    // pop
+    const uint32_t best = w.path[0];
+    heapSize--;
+    slabTrickleDown(w, heapSize, 0, w.path[heapSize]);
+    if (best == endIdx) {
+      outcome = kAStarReached;
+      break;
+    }
+    const NavPoly* bp = &sc.polys[best];
+    const int nv = bp->vertCount;
+    const float4 bA = w.nodeA[best];
+    const uint2 bB = w.nodeB[best];
+    __syncwarp();
+    if (lane == 0)
+      w.nodeB[best].y = bB.y & ~kNodeOpen;
+    const uint32_t bpar = bB.y & 0xffffu;
+    // evaluate: lane j takes edge j
+    const int li = lane < kVertsPerPoly ? lane : kVertsPerPoly - 1;
+    const uint16_t ne = bp->neis[li];
+    bool act = lane < nv && ne != 0 && !(ne & kExtLink) && static_cast<uint32_t>(ne - 1) != bpar;
+    uint32_t nei = act ? static_cast<uint32_t>(ne - 1) : best;
+    {
+      // two edges to the same neighbour: the second candidate is bit-identical to the
+      // first and fails the reference's `total >= node->total` test; the lowest edge acts
+      const uint32_t grp = __match_any_sync(0xffffffffu, act ? nei : 0xffff0000u + lane);
+      if (act && (__ffs(grp) - 1) != lane) {
+        act = false;
+        nei = best;
+      }
+    }
+    const float4 nA = w.nodeA[nei];
+    const uint2 nB = w.nodeB[nei];
+    const float4 V0 = ldVert4(sc, bp->verts[li]);
+    const float4 V1 = ldVert4(sc, bp->verts[(li + 1 == nv) ? 0 : li + 1]);
+    const bool isNew = act && !(nB.y & kNodeVisited);
+    const float nx = isNew ? (V0.x + V1.x) * 0.5f : nA.x;
+    const float ny = isNew ? (V0.y + V1.y) * 0.5f : nA.y;
+    const float nz = isNew ? (V0.z + V1.z) * 0.5f : nA.z;
+    const float bpos[3] = {bA.x, bA.y, bA.z};
+    const float npos[3] = {nx, ny, nz};
+    const float curCost = act ? vdist(bpos, npos) * 1.0f : 0.f;
+    const float toEnd = act ? vdist(npos, endPos) : 0.f;
+    const bool atEnd = nei == endIdx;
+    const float base = bA.w + curCost;
+    const float cost = atEnd ? base + toEnd * 1.0f : base;
+    const float heuristic = atEnd ? 0.f : toEnd * 0.999f;
+    const float ntotal = cost + heuristic;
+    const bool upd = act && (isNew || !(ntotal >= __uint_as_float(nB.x)));
+    const bool wasOpen = (nB.y & kNodeOpen) != 0;
+    nodes += __popc(__ballot_sync(0xffffffffu, isNew));
+    // commit edge by edge
+    const uint32_t updMask = __ballot_sync(0xffffffffu, upd);
+    const uint32_t openMask = __ballot_sync(0xffffffffu, upd && wasOpen);
+    bool full = false;
+    for (uint32_t m = updMask; m; m &= m - 1) {
+      const int j = __ffs(m) - 1;
+      const uint32_t node = __shfl_sync(0xffffffffu, nei, j);
+      if (lane == j) {
+        w.nodeA[nei] = make_float4(nx, ny, nz, cost);
+        w.nodeB[nei] = make_uint2(__float_as_uint(ntotal), best | kNodeVisited | kNodeOpen);
+      }
+      __syncwarp();
+      if ((openMask >> j) & 1u) {
+        // dtNodeQueue::modify: find the node, bubble it up from where it is
+        int at = -1;
+        for (int k0 = 0; k0 < heapSize && at < 0; k0 += 32) {
+          const int k = k0 + lane;
+          const uint32_t hit = __ballot_sync(0xffffffffu, k < heapSize && w.path[k] == node);
+          if (hit)
+            at = k0 + __ffs(hit) - 1;
+        }
+        if (at >= 0)
+          slabBubbleUp(w, at, node);
+      } else {
+        if (heapSize >= kSlabHeapCap) {
+          full = true;
+          break;
+        }
+        heapSize++;
+        slabBubbleUp(w, heapSize - 1, node);
+      }
+    }
+    if (full) {
+      outcome = kAStarHeapFull;
+      break;
+    }
+    __syncwarp();
+  }
+  __syncwarp();
+  *nodesOut = nodes;
+  return outcome;
+}
+
 // One query by one warp.  `sc` points at the staged (shared-memory) tables.
 // Returns the distance in every lane.  *needFallback is set (uniformly) when
 // the fast path cannot decide the pop order (tie for the minimum) or the
@@ -364,7 +534,8 @@ __device__ __forceinline__ float warpFunnel(const StagedView sc, const WarpSlab 
 __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSlab w, int lane,
                                               const float* startPosIn, uint32_t startRef,
                                               const float* endPosIn, uint32_t endRef,
-                                              uint32_t* status, uint32_t* needFallback
+                                              uint32_t* status, uint32_t* needFallback,
+                                              bool forceExact
 #if defined(BPSN_PHASE_TIMING)
                                               , PhaseAcc* pacc
 #endif
@@ -429,6 +600,8 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
     __syncwarp();
     bool reached = false;
     bool overflow = false;  // this lane had to drop an entry: the query is redone exactly
+    // why the search has to be (re)done with the reference's heap
+    uint32_t exactWhy = forceExact ? kStatTieFallback : 0u;
     int guard = 0;
     // Edge j of the popped polygon is evaluated by lane (j + rot) & 31 and rot moves on
     // after every pop, so that over a search every lane gets to evaluate neighbours: a
@@ -436,7 +609,7 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
     // cross-lane traffic, and the entries spread over the warp.
     int rot = 0;
 
-    while (true) {
+    while (!forceExact) {
       if (++guard > 64 * kMaxAStarNodes) {
         *status |= kStatIterCap;
         return BPSN_INF;
@@ -458,8 +631,8 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
           break;  // open list empty: the end polygon was not reached
         if (__popc(holders) != 1 || best >= 0x80000000u) {
           if (__any_sync(0xffffffffu, overflow)) {
-            *needFallback = kStatOpenOverflow;
-            return 0.f;
+            exactWhy = kStatOpenOverflow;
+            break;
           }
           // Several entries share the minimum.  Superseded entries do not count: only
           // those whose total is still their node's are in the reference's heap.
@@ -487,8 +660,8 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
           }
 #endif
           if (__popc(liveHolders) > 1 || liveMulti) {
-            *needFallback = kStatTieFallback;  // a real tie: the heap's order decides
-            return 0.f;
+            exactWhy = kStatTieFallback;  // a real tie: the heap's order decides
+            break;
           }
           if (liveHolders == 0u) {  // only superseded entries surfaced: drop them
             t0 = m0 ? kInfBits : t0;
@@ -649,14 +822,26 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
 #endif
     }
 
-    if (__any_sync(0xffffffffu, overflow)) {
-      *needFallback = kStatOpenOverflow;
-      return 0.f;
+    if (!exactWhy && __any_sync(0xffffffffu, overflow))
+      exactWhy = kStatOpenOverflow;
+    int nodeTotal = __reduce_add_sync(0xffffffffu, newNodes);
+    if (exactWhy) {
+      const int outcome = astarExactSlab(sc, w, lane, startPos, endPos, startIdx, endIdx, &nodeTotal);
+      if (outcome == kAStarHeapFull) {
+        *needFallback = exactWhy;  // hand the query to the global-memory emulation
+        return 0.f;
+      }
+      if (outcome == kAStarIterCap) {
+        *status |= kStatIterCap;
+        return BPSN_INF;
+      }
+      *status |= exactWhy;
+      reached = outcome == kAStarReached;
     }
     // dtNodePool hands out at most kMaxAStarNodes nodes; a search that asks for more
     // ends with DT_OUT_OF_NODES in its status, which PathFinder turns into +inf
     // whatever path was found (PathFinder.cpp:506).
-    const bool outOfNodes = __reduce_add_sync(0xffffffffu, newNodes) > kMaxAStarNodes;
+    const bool outOfNodes = nodeTotal > kMaxAStarNodes;
     if (outOfNodes) {
       *status |= kStatOutOfNodes;
       return BPSN_INF;
@@ -829,9 +1014,9 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
     BPSN_TICK(tQ1);
     if (needGeo) {
 #if defined(BPSN_PHASE_TIMING)
-      d = warpGeodesic(sv, w, lane, b, bref, a, aref, &status, &fallback, pacc);
+      d = warpGeodesic(sv, w, lane, b, bref, a, aref, &status, &fallback, g.exactHeap != 0, pacc);
 #else
-      d = warpGeodesic(sv, w, lane, b, bref, a, aref, &status, &fallback);
+      d = warpGeodesic(sv, w, lane, b, bref, a, aref, &status, &fallback, g.exactHeap != 0);
 #endif
     }
     BPSN_TICK(tQ2);

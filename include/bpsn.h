@@ -86,7 +86,11 @@ enum {
   /* always use the generic one-thread-per-environment step kernel (tables and
      A* scratch in global memory) instead of the shared-memory warp kernel;
      it is otherwise chosen only for scenes too large for shared memory */
-  BPSN_FLAG_GENERIC_KERNEL = 1u << 1
+  BPSN_FLAG_GENERIC_KERNEL = 1u << 1,
+  /* warp kernel only: run every A* search with the reference's binary heap kept
+     in shared memory, the path otherwise taken only when the register open list
+     cannot decide the pop order (a tie for the minimum) -- for testing that path */
+  BPSN_FLAG_EXACT_HEAP = 1u << 2
 };
 
 /* Fields addressable through bpsn_get_ptr.  All arrays are indexed by the

@@ -96,6 +96,12 @@ def test_generic_kernel_matches_oracle():
     _compare_run(["m01", "m04"], 256, 128, seed=12, mix="policy", generic_kernel=True)
 
 
+def test_exact_heap_search_matches_oracle():
+    # every A* search through the shared-memory binary heap (normally only after a tie)
+    assert _compare_run(["c1"], 2048, 64, seed=23, mix="uniform", exact_heap=True) > 0
+    _compare_run(["m03", "m07"], 512, 128, seed=24, mix="policy", exact_heap=True)
+
+
 def test_double_buffered_groups():
     _compare_run(["c0", "m15", "m13", "m14"], 256, 64, seed=3, mix="uniform", double_buffered=True)
 
