@@ -129,6 +129,9 @@ __device__ __forceinline__ WarpSlab carveSlab(uint8_t* base, int pcap) {
 struct StagedView {
   const NavPoly* polys;
   const float4* verts;
+  const NavDetail* detail;
+  const uint8_t* dtris;
+  const float* dverts;
   const int32_t* island;
   int32_t npolys;
   uint32_t polyMask;
@@ -355,6 +358,256 @@ __device__ __forceinline__ float warpFunnel(const StagedView sc, const WarpSlab 
   st = __shfl_sync(0xffffffffu, st, 0);
   *status |= st;
   return result;
+}
+
+// Vertex k of a detail triangle of polygon `p`: a polygon vertex or an extra detail vertex.
+__device__ __forceinline__ void stagedDetailVert(const StagedView& sc, const NavPoly* p, int nv,
+                                                 const NavDetail pd, uint32_t k, float* out) {
+  if (k < static_cast<uint32_t>(nv)) {
+    const float4 v = ldVert4(sc, p->verts[k]);
+    out[0] = v.x;
+    out[1] = v.y;
+    out[2] = v.z;
+  } else {
+    const float* v = sc.dverts + 3 * static_cast<size_t>(pd.vertBase + (k - nv));
+    out[0] = v[0];
+    out[1] = v[1];
+    out[2] = v[2];
+  }
+}
+
+// dtNavMesh::getPolyHeight (DetourNavMesh.cpp:677-726) by one warp: the point-in-
+// polygon test takes one lane per edge (the parity of crossings does not depend on
+// the order), the detail triangles are tested 32 at a time and the first triangle
+// (lowest index) that contains the point gives the height, as in the sequential
+// loop.  Returns false, *height untouched, when pos is outside the polygon in xz.
+// The result is the same in every lane.
+__device__ __forceinline__ bool warpPolyHeight(const StagedView sc, const NavScene& scFull,
+                                               int lane, uint32_t ip, const float* pos,
+                                               float* height) {
+  const NavPoly* p = &sc.polys[ip];
+  if ((p->areaAndType >> 6) == 1)  // off-mesh connection
+    return false;
+  const int nv = p->vertCount;
+  bool cross = false;
+  if (lane < nv) {
+    const float4 vi = ldVert4(sc, p->verts[lane]);
+    const float4 vj = ldVert4(sc, p->verts[(lane == 0) ? nv - 1 : lane - 1]);
+    cross = ((vi.z > pos[2]) != (vj.z > pos[2])) &&
+            (pos[0] < (vj.x - vi.x) * (pos[2] - vi.z) / (vj.z - vi.z) + vi.x);
+  }
+  if ((__popc(__ballot_sync(0xffffffffu, cross)) & 1) == 0)
+    return false;
+  const NavDetail pd = sc.detail[ip];
+  const int ntris = p->detailTriCount;
+  for (int base = 0; base < ntris; base += 32) {
+    const int t = base + lane;
+    bool hit = false;
+    float h = 0.f;
+    if (t < ntris) {
+      const uchar4 tq =
+          *reinterpret_cast<const uchar4*>(sc.dtris + 4 * static_cast<size_t>(pd.triBase + t));
+      float v[3][3];
+      stagedDetailVert(sc, p, nv, pd, tq.x, v[0]);
+      stagedDetailVert(sc, p, nv, pd, tq.y, v[1]);
+      stagedDetailVert(sc, p, nv, pd, tq.z, v[2]);
+      hit = closestHeightPointTriangle(pos, v[0], v[1], v[2], h);
+    }
+    const uint32_t hits = __ballot_sync(0xffffffffu, hit);
+    if (hits) {
+      *height = __shfl_sync(0xffffffffu, h, __ffs(hits) - 1);
+      return true;
+    }
+  }
+  // inside the polygon but in none of its detail triangles (numerical edge case)
+  float closest[3] = {0.f, 0.f, 0.f};
+  if (lane == 0) {
+    const NavPoly pc = loadPoly(scFull, ip);
+    closestOnDetailEdges(scFull, ip, pc, pos, false, closest);
+  }
+  *height = __shfl_sync(0xffffffffu, closest[1], 0);
+  return true;
+}
+
+// dtNavMeshQuery::moveAlongSurface as PathFinder::tryStep uses it (see
+// moveAlongSurface() in nav_query.cuh for the one-thread form, whose decisions
+// this reproduces): breadth-first over the polygons near the step, one lane per
+// edge of the polygon at the head of the queue.
+//   * end point inside the polygon: crossing parity over the edge lanes;
+//   * wall edges: the sequential loop keeps the first edge with the strictly
+//     smallest squared distance, i.e. the minimum with the lowest edge index;
+//   * neighbour edges: node allocation, the visited bit and the FIFO push depend
+//     on the order of the edges, so they are replayed edge by edge (the distance
+//     test of each was already evaluated by its lane).
+// The tiny node pool (64 ids) and the FIFO live in the warp's corridor array,
+// which nothing else uses during the move.  Results are the same in every lane.
+__device__ __forceinline__ bool warpMoveAlongSurface(const StagedView sc, const WarpSlab w,
+                                                     int lane, const float* navPos,
+                                                     uint32_t startRef, const float* endPos,
+                                                     float* bestPos, uint32_t* endIdxOut) {
+  if (!validRef(sc, startRef) || !finite3(navPos) || !finite3(endPos))
+    return false;
+  uint16_t* ids = w.path;           // [kMovePool]
+  uint16_t* queue = w.path + kMovePool;  // [kMovePool] each node enters once
+  int nnodes = 1, qhead = 0, qtail = 1;
+  unsigned long long closedBits = 1ull;
+  __syncwarp();
+  if (lane == 0) {
+    ids[0] = static_cast<uint16_t>(startRef & sc.polyMask);
+    queue[0] = 0;
+  }
+  __syncwarp();
+  vcopy(bestPos, navPos);
+  float bestDist = 3.402823466e+38f;
+  int bestNode = -1;
+  float searchPos[3];
+  vlerp(searchPos, navPos, endPos, 0.5f);
+  const float rad = vdist(navPos, endPos) / 2.0f + 0.001f;
+  const float searchRadSqr = rad * rad;
+
+  while (qhead < qtail) {
+    const int cur = queue[qhead++];
+    const uint32_t curIdx = ids[cur];
+    const NavPoly* poly = &sc.polys[curIdx];
+    const int nv = poly->vertCount;
+    // lane i: edge from vertex j = i - 1 (cyclic) to vertex i, neighbour code neis[j]
+    const bool act = lane < nv;
+    const int i = act ? lane : 0;
+    const int j = (i == 0) ? nv - 1 : i - 1;
+    const float4 vi4 = ldVert4(sc, poly->verts[i]);
+    const float4 vj4 = ldVert4(sc, poly->verts[j]);
+    const uint16_t ne = poly->neis[j];
+    const float vi[3] = {vi4.x, vi4.y, vi4.z};
+    const float vj[3] = {vj4.x, vj4.y, vj4.z};
+    const bool cross = act && ((vi[2] > endPos[2]) != (vj[2] > endPos[2])) &&
+                       (endPos[0] < (vj[0] - vi[0]) * (endPos[2] - vi[2]) / (vj[2] - vi[2]) + vi[0]);
+    if (__popc(__ballot_sync(0xffffffffu, cross)) & 1) {
+      bestNode = cur;
+      vcopy(bestPos, endPos);
+      break;
+    }
+    // links to polygons the filter rejects were cleared when the scene was staged
+    const bool isNei = act && ne != 0 && !(ne & kExtLink);
+    const bool isWall = act && !isNei;
+    float tseg = 0.f;
+    const float dq = distPtSegSqr2D(isWall ? endPos : searchPos, vj, vi, tseg);
+    // walls
+    const uint32_t key = isWall ? __float_as_uint(dq) : 0xffffffffu;
+    const uint32_t kmin = __reduce_min_sync(0xffffffffu, key);
+    if (kmin != 0xffffffffu && __uint_as_float(kmin) < bestDist) {
+      const int src = __ffs(__ballot_sync(0xffffffffu, key == kmin)) - 1;
+      float cand[3];
+      vlerp(cand, vj, vi, tseg);
+      bestPos[0] = __shfl_sync(0xffffffffu, cand[0], src);
+      bestPos[1] = __shfl_sync(0xffffffffu, cand[1], src);
+      bestPos[2] = __shfl_sync(0xffffffffu, cand[2], src);
+      bestDist = __uint_as_float(kmin);
+      bestNode = cur;
+    }
+    // neighbours, in edge order
+    const uint32_t neiMask = __ballot_sync(0xffffffffu, isNei);
+    const uint32_t nearMask = __ballot_sync(0xffffffffu, isNei && !(dq > searchRadSqr));
+    for (uint32_t m = neiMask; m; m &= m - 1) {
+      const int L = __ffs(m) - 1;
+      const uint32_t nei = __shfl_sync(0xffffffffu, static_cast<uint32_t>(ne) - 1u, L);
+      // getNode: find or allocate
+      const uint32_t lo = __ballot_sync(0xffffffffu, lane < nnodes && ids[lane] == nei);
+      const uint32_t hi = __ballot_sync(0xffffffffu, lane + 32 < nnodes && ids[lane + 32] == nei);
+      int node;
+      if (lo) {
+        node = __ffs(lo) - 1;
+      } else if (hi) {
+        node = 32 + __ffs(hi) - 1;
+      } else {
+        if (nnodes >= kMovePool)
+          continue;
+        node = nnodes++;
+        if (lane == 0)
+          ids[node] = static_cast<uint16_t>(nei);
+        __syncwarp();
+      }
+      if ((closedBits >> node) & 1ull)
+        continue;
+      if (!((nearMask >> L) & 1u))
+        continue;
+      if ((qtail - qhead) < kMoveStack) {
+        closedBits |= 1ull << node;
+        if (lane == 0)
+          queue[qtail] = static_cast<uint16_t>(node);
+        qtail++;
+      }
+    }
+    __syncwarp();
+  }
+  if (bestNode < 0)
+    return false;  // numPolys == 0
+  *endIdxOut = ids[bestNode];
+  return true;
+}
+
+// MoveForward of handleMovement for one environment by one warp (see forwardMove()
+// in sim_kernels.cuh for the one-thread form).  The new navmesh position and
+// polygon ref are returned in every lane; lane 0 writes pose and GPS/compass back.
+__device__ __forceinline__ void warpForwardMove(const GroupDev& g, const StagedView sv,
+                                                const NavScene& scFull, const WarpSlab w, int lane,
+                                                uint32_t e, float* navOut, uint32_t* refOut) {
+  const uint32_t B = g.B;
+  // every lane loads the pose (same addresses: one transaction each)
+  const float px = g.pos[e], py = g.pos[B + e], pz = g.pos[2 * B + e];
+  const float qx = g.rot[e], qy = g.rot[B + e], qz = g.rot[2 * B + e], qw = g.rot[3 * B + e];
+  float np[3] = {g.navPos[e], g.navPos[B + e], g.navPos[2 * B + e]};
+  uint32_t ref = g.navRef[e];
+  const float gx = g.goal[e], gy = g.goal[B + e], gz = g.goal[2 * B + e];
+  // delta = rot * v :  v + 2 * (w * (q x v) + q x (q x v))
+  const float vx = 0.f * kForwardStep, vy = 0.f * kForwardStep, vz = -1.f * kForwardStep;
+  const float uvx = qy * vz - vy * qz;
+  const float uvy = qz * vx - vz * qx;
+  const float uvz = qx * vy - vx * qy;
+  const float uuvx = qy * uvz - uvy * qz;
+  const float uuvy = qz * uvx - uvz * qx;
+  const float uuvz = qx * uvy - uvx * qy;
+  float endPos[3];
+  endPos[0] = px + (vx + ((uvx * qw) + uuvx) * 2.f);
+  endPos[1] = py + (vy + ((uvy * qw) + uuvy) * 2.f);
+  endPos[2] = pz + (vz + ((uvz * qw) + uuvz) * 2.f);
+  BPSN_TICK(tM1);
+  float best[3];
+  uint32_t endIdx = 0;
+  const bool ok = warpMoveAlongSurface(sv, w, lane, np, ref, endPos, best, &endIdx);
+  BPSN_TICK(tM2);
+  if (ok) {
+    float h = best[1];
+    if (finitef(best[0]) && finitef(best[2]))
+      warpPolyHeight(sv, scFull, lane, endIdx, best, &h);
+    np[0] = best[0];
+    np[1] = h;
+    np[2] = best[2];
+    ref = sv.refBase | endIdx;
+  }
+  BPSN_TICK(tM3);
+  if (lane == 0) {
+    g.navPos[e] = np[0];
+    g.navPos[B + e] = np[1];
+    g.navPos[2 * B + e] = np[2];
+    g.navRef[e] = ref;
+    g.pos[e] = np[0];
+    g.pos[B + e] = np[1];
+    g.pos[2 * B + e] = np[2];
+    writePolar(g, e, np[0], np[1], np[2], qx, qy, qz, qw, gx, gy, gz);
+  }
+#if defined(BPSN_PHASE_TIMING)
+  if (lane == 0) {
+    const long long tM4 = clock64();
+    atomicAdd(&g_phaseCycles[18], static_cast<unsigned long long>(tM2 - tM1));
+    atomicAdd(&g_phaseCycles[19], static_cast<unsigned long long>(tM3 - tM2));
+    atomicAdd(&g_phaseCycles[20], static_cast<unsigned long long>(tM4 - tM3));
+    atomicAdd(&g_phaseCycles[21], 1ull);
+  }
+#endif
+  navOut[0] = np[0];
+  navOut[1] = np[1];
+  navOut[2] = np[2];
+  *refOut = ref;
 }
 
 constexpr uint32_t kNodeOpen = 0x20000u;  // exact search only: the node is in the heap
@@ -642,23 +895,6 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
           const int lc = (l0 ? 1 : 0) + (l1 ? 1 : 0) + (l2 ? 1 : 0);
           const uint32_t liveHolders = __ballot_sync(0xffffffffu, lc != 0);
           const bool liveMulti = __any_sync(0xffffffffu, lc > 1);
-#if defined(BPSN_PHASE_TIMING)
-          if (lane == 0) {
-            atomicAdd(&g_phaseCycles[17], 1ull);
-            if (liveHolders == 0u) atomicAdd(&g_phaseCycles[18], 1ull);
-            if (__popc(liveHolders) == 1 && !liveMulti) atomicAdd(&g_phaseCycles[19], 1ull);
-            if (__popc(liveHolders) > 1 || liveMulti) {
-              atomicAdd(&g_phaseCycles[20], 1ull);
-              g_phaseCycles[21] = gm;
-            }
-          }
-          if ((__popc(liveHolders) > 1 || liveMulti) && lc != 0) {
-            // sample: which polygons tie
-            const uint32_t pp = l0 ? p0 : (l1 ? p1 : p2);
-            if (lane == __ffs(liveHolders) - 1) g_phaseCycles[22] = pp | (static_cast<unsigned long long>(w.nodeB[pp].y) << 32);
-            else g_phaseCycles[23] = pp | (static_cast<unsigned long long>(w.nodeB[pp].y) << 32);
-          }
-#endif
           if (__popc(liveHolders) > 1 || liveMulti) {
             exactWhy = kStatTieFallback;  // a real tie: the heap's order decides
             break;
@@ -976,6 +1212,9 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
   StagedView sv;
   sv.polys = sc.polys;
   sv.verts = reinterpret_cast<const float4*>(sc.verts);
+  sv.detail = sc.detail;
+  sv.dtris = sc.dtris;
+  sv.dverts = sc.dverts;
   sv.island = sc.island;
   sv.npolys = sc.npolys;
   sv.polyMask = sc.polyMask;
@@ -997,15 +1236,18 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
     const uint32_t e = g.geoList[base + q];
     const uint32_t f = g.flags[e];
     const bool done = f & 1u, moved = f & 2u;
-    if (moved) {
-      if (lane == 0)
-        forwardMove(g, sc, e);
-      __syncwarp();
-    }
-    const float a[3] = {g.navPos[e], g.navPos[B + e], g.navPos[2 * B + e]};
     const float b[3] = {g.navGoal[e], g.navGoal[B + e], g.navGoal[2 * B + e]};
-    const uint32_t aref = g.navRef[e];
     const uint32_t bref = g.goalRef[e];
+    float a[3];
+    uint32_t aref;
+    if (moved) {
+      warpForwardMove(g, sv, sc, w, lane, e, a, &aref);
+    } else {
+      a[0] = g.navPos[e];
+      a[1] = g.navPos[B + e];
+      a[2] = g.navPos[2 * B + e];
+      aref = g.navRef[e];
+    }
     uint32_t status = 0;
     uint32_t fallback = 0u;
     float d = 0.f;
