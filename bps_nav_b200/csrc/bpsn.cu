@@ -895,9 +895,12 @@ int32_t bpsn_debug_phase_cycles(unsigned long long* out24, int32_t reset) {
   cudaDeviceSynchronize();
   if (out24)
     cudaMemcpyFromSymbol(out24, g_phaseCycles, sizeof(unsigned long long) * 24);
-  if (reset) {
+  if (reset == 1) {
     unsigned long long z[24] = {};
     cudaMemcpyToSymbol(g_phaseCycles, z, sizeof(z));
+  } else if (reset == 2) {  // only the per-launch maximum
+    unsigned long long z = 0;
+    cudaMemcpyToSymbol(g_phaseCycles, &z, sizeof(z), 17 * sizeof(unsigned long long));
   }
   return 0;
 }

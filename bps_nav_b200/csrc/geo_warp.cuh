@@ -862,27 +862,38 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
     // cross-lane traffic, and the entries spread over the warp.
     int rot = 0;
 
-    while (!forceExact) {
-      if (++guard > 64 * kMaxAStarNodes) {
-        *status |= kStatIterCap;
-        return BPSN_INF;
-      }
+    // The loop body has one conditional branch on its common path besides the two
+    // uncommon-case tests after the loads (a branch costs about as much as a
+    // shared-memory load here): the iteration cap, the state of the open list, the end
+    // test and the request to rebalance all leave through the same test.
+    if (!forceExact) while (true) {
+      ++guard;
       BPSN_TICK(tP0);
       // ---- pop: totals are non-negative floats, so their bit patterns order
       // like unsigned integers and one warp reduction finds the minimum.  A lane
       // that overflowed reports 0 so that the search stops at once.
       const uint32_t lm = overflow ? 0u : min(min(t0, t1), t2);
       const uint32_t gm = __reduce_min_sync(0xffffffffu, lm);
-      const bool m0 = t0 == gm, m1 = t1 == gm, m2 = t2 == gm;
-      const int mc = (m0 ? 1 : 0) + (m1 ? 1 : 0) + (m2 ? 1 : 0);
-      const uint32_t holders = __ballot_sync(0xffffffffu, mc != 0);
-      const uint32_t mine = (m0 ? p0 : (m1 ? p1 : p2)) | (mc > 1 ? 0x80000000u : 0u);
-      uint32_t best = __shfl_sync(0xffffffffu, mine, (__ffs(holders) - 1) & 31);
+      bool m0 = t0 == gm, m1 = t1 == gm, m2 = t2 == gm;
+      const uint32_t mc = (m0 ? 1u : 0u) + (m1 ? 1u : 0u) + (m2 ? 1u : 0u);
+      // Two more reductions, side by side, instead of vote + find-first-set + shuffle
+      // (each of which costs about as much as a reduction): how many entries hold the
+      // minimum, and the polygon of the one that does when it is alone.
+      // (a lane whose three entries are all taken adds 65536: it asks for a rebalance)
+      const bool laneFull = t0 != kInfBits && t1 != kInfBits && t2 != kInfBits;
+      const uint32_t hsum = __reduce_add_sync(0xffffffffu, mc | (laneFull ? 0x10000u : 0u));
+      uint32_t best =
+          __reduce_min_sync(0xffffffffu, mc ? (m0 ? p0 : (m1 ? p1 : p2)) : 0xffffffffu);
       // one branch for everything that is not "a unique minimum that is not the end"
-      if ((__popc(holders) != 1) | (best >= 0x80000000u) | (best == endIdx)) {
+      if ((hsum != 1u) | (best == endIdx) | (guard > 64 * kMaxAStarNodes)) {
+        if (guard > 64 * kMaxAStarNodes) {
+          *status |= kStatIterCap;
+          return BPSN_INF;
+        }
         if (gm == kInfBits)
           break;  // open list empty: the end polygon was not reached
-        if (__popc(holders) != 1 || best >= 0x80000000u) {
+        const uint32_t holders = hsum & 0xffffu;
+        if (holders != 1u) {
           if (__any_sync(0xffffffffu, overflow)) {
             exactWhy = kStatOpenOverflow;
             break;
@@ -911,37 +922,15 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
           reached = true;
           break;
         }
-      }
-      // the popped entry and, after a resolved tie, the superseded ones beside it
-      t0 = m0 ? kInfBits : t0;
-      t1 = m1 ? kInfBits : t1;
-      t2 = m2 ? kInfBits : t2;
-      BPSN_TICK(tP1);
-
-      // ---- expand: one lane per edge of the popped polygon.  All loads of a
-      // round are issued before any of them is used.
-      const NavPoly* bp = &sc.polys[best];
-      const int ej = (lane - rot) & 31;  // this lane's edge index (>= nv: none)
-      const int li = ej < kVertsPerPoly ? ej : kVertsPerPoly - 1;
-      const int nv = bp->vertCount;
-      const uint32_t dupFlag = bp->pad;
-      const uint16_t ne = bp->neis[li];
-      const uint16_t va = bp->verts[li];
-      // verts[li + 1] stays inside the record (neis follows verts)
-      const uint16_t vbNext = (&bp->verts[0])[li + 1];
-      const uint16_t vbFirst = bp->verts[0];
-      const float4 bA = w.nodeA[best];
-      const uint2 bB = w.nodeB[best];
-
-      // While those loads are in flight: a lane whose three entries are all taken
-      // hands one to a lane with room (preferably one with two free pairs), so that
-      // it can accept a neighbour below.
-      // A lane evaluates a neighbour at most once in four consecutive pops (the windows
-      // of six lanes move on by seven), so looking every fourth pop is often enough.
-      if ((guard & 3) == 0) {
-        const bool f0 = t0 == kInfBits, f1 = t1 == kInfBits, f2 = t2 == kInfBits;
-        uint32_t fb = __ballot_sync(0xffffffffu, !f0 && !f1 && !f2);
-        if (fb) {
+        if (hsum >> 16) {
+          // A lane whose three entries are all taken hands one to a lane with room
+          // (preferably one with two free pairs), so that it can accept a neighbour below.
+          t0 = m0 ? kInfBits : t0;  // (the popped entry first)
+          t1 = m1 ? kInfBits : t1;
+          t2 = m2 ? kInfBits : t2;
+          m0 = m1 = m2 = false;  // done: the pairs may be refilled just below
+          const bool f0 = t0 == kInfBits, f1 = t1 == kInfBits, f2 = t2 == kInfBits;
+          uint32_t fb = __ballot_sync(0xffffffffu, !f0 && !f1 && !f2);
           const int freeCnt = (f0 ? 1 : 0) + (f1 ? 1 : 0) + (f2 ? 1 : 0);
           uint32_t rb = __ballot_sync(0xffffffffu, freeCnt >= 2);
           const uint32_t rb1 = __ballot_sync(0xffffffffu, freeCnt >= 1);
@@ -970,6 +959,26 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
           }
         }
       }
+      // the popped entry and, after a resolved tie, the superseded ones beside it
+      t0 = m0 ? kInfBits : t0;
+      t1 = m1 ? kInfBits : t1;
+      t2 = m2 ? kInfBits : t2;
+      BPSN_TICK(tP1);
+
+      // ---- expand: one lane per edge of the popped polygon.  All loads of a
+      // round are issued before any of them is used.
+      const NavPoly* bp = &sc.polys[best];
+      const int ej = (lane - rot) & 31;  // this lane's edge index (>= nv: none)
+      const int li = ej < kVertsPerPoly ? ej : kVertsPerPoly - 1;
+      const int nv = bp->vertCount;
+      const uint32_t dupFlag = bp->pad;
+      const uint16_t ne = bp->neis[li];
+      const uint16_t va = bp->verts[li];
+      // verts[li + 1] stays inside the record (neis follows verts)
+      const uint16_t vbNext = (&bp->verts[0])[li + 1];
+      const uint16_t vbFirst = bp->verts[0];
+      const float4 bA = w.nodeA[best];
+      const uint2 bB = w.nodeB[best];
 
       const uint32_t bpar = bB.y & 0xffffu;
       const uint16_t vb = (li + 1 == nv) ? vbFirst : vbNext;
@@ -1233,6 +1242,9 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
     if (q >= n)
       break;
     BPSN_TICK(tQ0);
+#if defined(BPSN_PHASE_TIMING)
+    const unsigned long long accA0 = pacc->sum[2], accF0 = pacc->sum[3];
+#endif
     const uint32_t e = g.geoList[base + q];
     const uint32_t f = g.flags[e];
     const bool done = f & 1u, moved = f & 2u;
@@ -1280,6 +1292,19 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
       BPSN_PHASE_ADD(4, tQ3 - tQ2);
 #if defined(BPSN_PHASE_TIMING)
       pacc->queries += 1;
+      {
+        // the query that ends last in the launch, with its own phase times (units of 128 cycles)
+        auto f = [](long long c, int bits) -> unsigned long long {
+          unsigned long long v = static_cast<unsigned long long>(c) >> 7;
+          const unsigned long long mx = (1ull << bits) - 1ull;
+          return v > mx ? mx : v;
+        };
+        const unsigned long long packed =
+            (f(tQ3 - tS0, 16) << 48) | (f(tQ0 - tS0, 12) << 36) | (f(tQ1 - tQ0, 8) << 28) |
+            (f(static_cast<long long>(pacc->sum[2] - accA0), 12) << 16) |
+            (f(static_cast<long long>(pacc->sum[3] - accF0), 8) << 8) | f(tQ3 - tQ2, 8);
+        atomicMax(&g_phaseCycles[17], packed);
+      }
 #endif
     }
     __syncwarp();
