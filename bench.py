@@ -351,13 +351,16 @@ def run_ours(args):
         h_info = gen2.get_infos(0)
         sink = 0.0
 
+        rew_rows = [rewards[t] for t in range(T)]      # row views of the rollout storage
+        mask_rows = [masks[t + 1] for t in range(T)]
+
         def window_e2e(k):
             nonlocal sink
             base = k * T
             for t in range(T):
                 # numpy actions in (H2D), numpy reward / mask / info / polar out (D2H) every
                 # step; the rollout rows are filled on the device by the same launch
-                gen2.step_start(0, hacts[base + t], reward_out=rewards[t], mask_out=masks[t + 1])
+                gen2.step_start(0, hacts[base + t], reward_out=rew_rows[t], mask_out=mask_rows[t])
                 gen2.step_end(0)
                 sink += (float(h_polar[0, 0]) + float(h_info["distanceToGoal"][0]) +
                          float(h_rew[0]) + float(h_mask[0]))
@@ -373,7 +376,7 @@ def run_ours(args):
             window_e2e(W + k)
         barrier()
         e2e_s = max_over_ranks(time.perf_counter() - t0)
-        h2d = T * (N * 8)                         # int64 actions
+        h2d = T * N                               # actions cross the bus as one byte each
         d2h = T * (N * 4 + N + N * 12 + N * 8) + 4  # reward, mask, info, polar (+ window result)
         e2e = {"value": world * N * T * K / e2e_s, "unit": "env-steps/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

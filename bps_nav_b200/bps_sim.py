@@ -172,6 +172,9 @@ class _RolloutGenerator:
     # ------------------------------------------------------------------ stepping
     def _stream(self):
         import torch
+        raw = getattr(torch._C, "_cuda_getCurrentRawStream", None)  # same value, less overhead
+        if raw is not None:
+            return C.c_void_p(raw(self.gpu_id))
         return C.c_void_p(torch.cuda.current_stream(self.gpu_id).cuda_stream)
 
     def reset(self, group_idx):
@@ -206,7 +209,8 @@ class _RolloutGenerator:
             if actions.shape[0] != self.envs_per_group:
                 raise RuntimeError("actions length must equal the number of envs in the group")
             self._keepalive = [actions, reward_out, mask_out, polar_out]
-            L.check(self._lib.bpsn_step_start_ex(self._h, group_idx, actions.ctypes.data,
+            L.check(self._lib.bpsn_step_start_ex(self._h, group_idx,
+                                                 actions.__array_interface__["data"][0],
                                                  L.MEM_HOST, self._stream(), ro, mo, po), self._h)
         else:
             import torch

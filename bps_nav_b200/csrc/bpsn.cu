@@ -44,8 +44,8 @@ struct Group {
   uint8_t* hMask = nullptr;
   float* hInfo = nullptr;
   float* hPolar = nullptr;
-  int64_t* hActions = nullptr;  // pinned staging
-  int64_t* dActions = nullptr;
+  uint8_t* hActions = nullptr;  // pinned, device-mapped staging of host-supplied actions
+  const uint8_t* dActions8 = nullptr;  // the same buffer as the device addresses it
   AStarScratch* scratch = nullptr;
   // launch plan of the geodesic phase
   uint32_t numScenesUsed = 0;   // grid.y
@@ -356,8 +356,12 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
 
   if (!g.warpGeo)  // per-slot A* scratch is only used by the generic (global-memory) kernel
     BPSN_CUDA(sim, cudaMalloc(&g.scratch, sizeof(AStarScratch) * static_cast<size_t>(B)));
-  BPSN_CUDA(sim, cudaMalloc(&g.dActions, sizeof(int64_t) * B));
-  BPSN_CUDA(sim, cudaMallocHost(&g.hActions, sizeof(int64_t) * B));
+  BPSN_CUDA(sim, cudaHostAlloc(&g.hActions, B, cudaHostAllocMapped));
+  {
+    void* dp = nullptr;
+    BPSN_CUDA(sim, cudaHostGetDevicePointer(&dp, g.hActions, 0));
+    g.dActions8 = static_cast<const uint8_t*>(dp);
+  }
   if (sim->cfg.flags & BPSN_FLAG_HOST_MIRRORS) {
     // the four result arrays are adjacent in the state block: one pinned
     // block with the same relative layout lets a step publish them in one copy
@@ -469,7 +473,6 @@ int32_t bpsn_destroy(bpsn_sim* sim) {
     cudaFree(g.stateBlob);
     cudaFree(g.scratch);
     cudaFree(g.fallbackScratch);
-    cudaFree(g.dActions);
     cudaFreeHost(g.hActions);
     cudaFreeHost(g.hOut);
     if (g.done)
@@ -670,16 +673,22 @@ int32_t bpsn_step_start_ex(bpsn_sim* sim, uint32_t group, const int64_t* actions
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const uint32_t B = g.dev.B;
   const int64_t* dAct = actions;
+  const uint8_t* dAct8 = nullptr;
   if (actions_mem == BPSN_MEM_HOST) {
     for (uint32_t i = 0; i < B; ++i) {
       const int64_t a = actions[i];
       if (a < 0 || a > 3)
         return fail(sim, BPSN_ERR_BAD_ACTION, "Unknown action: " + std::to_string(a));
-      g.hActions[i] = a;
     }
-    BPSN_CUDA(sim, cudaMemcpyAsync(g.dActions, g.hActions, sizeof(int64_t) * B,
-                                   cudaMemcpyHostToDevice, s));
-    dAct = g.dActions;
+    // The staging buffer is read in place by the kernel of this step; without host
+    // mirrors step_end does not wait for the device, so make sure the previous step
+    // is through with the buffer before overwriting it.
+    if (!(sim->cfg.flags & BPSN_FLAG_HOST_MIRRORS))
+      BPSN_CUDA(sim, cudaEventSynchronize(g.done));
+    for (uint32_t i = 0; i < B; ++i)
+      g.hActions[i] = static_cast<uint8_t>(actions[i]);
+    dAct = nullptr;
+    dAct8 = g.dActions8;
   } else if (actions_mem != BPSN_MEM_DEVICE) {
     return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_step_start: actions_mem must be host or device");
   }
@@ -709,7 +718,8 @@ int32_t bpsn_step_start_ex(bpsn_sim* sim, uint32_t group, const int64_t* actions
   lc.gridDim = dim3(blocksFor(B, 256));
   lc.blockDim = dim3(256);
   lc.dynamicSmemBytes = 0;
-  BPSN_CUDA(sim, cudaLaunchKernelEx(&lc, k_pre, gd, sim->table, dAct, sim->turn, seedLo, seedHi));
+  BPSN_CUDA(sim, cudaLaunchKernelEx(&lc, k_pre, gd, sim->table, dAct, dAct8, sim->turn, seedLo,
+                                    seedHi));
   if (prof) cudaEventRecord(g.prof[1], s);
   if (g.warpGeo) {
     lc.gridDim = dim3(g.geoGridX, g.numScenesUsed);

@@ -72,6 +72,7 @@ __device__ __forceinline__ void phaseAdd(PhaseAcc* a, int idx, long long cycles)
 #endif
 
 constexpr uint32_t kInfBits = 0x7f800000u;
+constexpr int kOpenSlots = 3;  // register open-list entries per lane (96 per warp)
 constexpr uint32_t kNodeVisited = 0x10000u;  // in nodeB.y next to the 16-bit parent
 
 // Shared-memory layout of a staged scene (byte offsets, each 16-byte aligned).
@@ -838,16 +839,21 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
     for (int i = lane; i < P; i += 32)
       w.nodeB[i] = make_uint2(0u, 0u);  // nobody visited
     __syncwarp();
-    // open list: three register entries per lane, kInfBits = empty
-    uint32_t t0 = kInfBits, t1 = kInfBits, t2 = kInfBits;
-    uint32_t p0 = 0, p1 = 0, p2 = 0;
+    // open list: kOpenSlots register entries (total, polygon) per lane, kInfBits = empty.
+    // All loops over the slots are unrolled, so the arrays live in registers.
+    uint32_t t[kOpenSlots], p[kOpenSlots];
+#pragma unroll
+    for (int k = 0; k < kOpenSlots; ++k) {
+      t[k] = kInfBits;
+      p[k] = 0;
+    }
     int newNodes = 0;  // nodes this lane created (summed over the warp at the end)
     if (lane == 0) {
       const float tot = vdist(startPos, endPos) * 0.999f;
       w.nodeA[startIdx] = make_float4(startPos[0], startPos[1], startPos[2], 0.f);
       w.nodeB[startIdx] = make_uint2(__float_as_uint(tot), 0xffffu | kNodeVisited);
-      t0 = __float_as_uint(tot);
-      p0 = startIdx;
+      t[0] = __float_as_uint(tot);
+      p[0] = startIdx;
       newNodes = 1;
     }
     __syncwarp();
@@ -872,18 +878,27 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
       // ---- pop: totals are non-negative floats, so their bit patterns order
       // like unsigned integers and one warp reduction finds the minimum.  A lane
       // that overflowed reports 0 so that the search stops at once.
-      const uint32_t lm = overflow ? 0u : min(min(t0, t1), t2);
-      const uint32_t gm = __reduce_min_sync(0xffffffffu, lm);
-      bool m0 = t0 == gm, m1 = t1 == gm, m2 = t2 == gm;
-      const uint32_t mc = (m0 ? 1u : 0u) + (m1 ? 1u : 0u) + (m2 ? 1u : 0u);
+      uint32_t lm = t[0];
+#pragma unroll
+      for (int k = 1; k < kOpenSlots; ++k)
+        lm = min(lm, t[k]);
+      const uint32_t gm = __reduce_min_sync(0xffffffffu, overflow ? 0u : lm);
+      bool m[kOpenSlots];
+      uint32_t mc = 0, cand = 0xffffffffu;
+      bool laneFull = true;
+#pragma unroll
+      for (int k = kOpenSlots - 1; k >= 0; --k) {
+        m[k] = t[k] == gm;
+        mc += m[k] ? 1u : 0u;
+        cand = m[k] ? p[k] : cand;
+        laneFull = laneFull && t[k] != kInfBits;
+      }
       // Two more reductions, side by side, instead of vote + find-first-set + shuffle
       // (each of which costs about as much as a reduction): how many entries hold the
       // minimum, and the polygon of the one that does when it is alone.
-      // (a lane whose three entries are all taken adds 65536: it asks for a rebalance)
-      const bool laneFull = t0 != kInfBits && t1 != kInfBits && t2 != kInfBits;
+      // (a lane whose entries are all taken adds 65536: it asks for a rebalance)
       const uint32_t hsum = __reduce_add_sync(0xffffffffu, mc | (laneFull ? 0x10000u : 0u));
-      uint32_t best =
-          __reduce_min_sync(0xffffffffu, mc ? (m0 ? p0 : (m1 ? p1 : p2)) : 0xffffffffu);
+      uint32_t best = __reduce_min_sync(0xffffffffu, cand);
       // one branch for everything that is not "a unique minimum that is not the end"
       if ((hsum != 1u) | (best == endIdx) | (guard > 64 * kMaxAStarNodes)) {
         if (guard > 64 * kMaxAStarNodes) {
@@ -900,10 +915,14 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
           }
           // Several entries share the minimum.  Superseded entries do not count: only
           // those whose total is still their node's are in the reference's heap.
-          const bool l0 = m0 && w.nodeB[p0].x == gm;
-          const bool l1 = m1 && w.nodeB[p1].x == gm;
-          const bool l2 = m2 && w.nodeB[p2].x == gm;
-          const int lc = (l0 ? 1 : 0) + (l1 ? 1 : 0) + (l2 ? 1 : 0);
+          int lc = 0;
+          uint32_t livePoly = 0;
+#pragma unroll
+          for (int k = kOpenSlots - 1; k >= 0; --k) {
+            const bool live = m[k] && w.nodeB[p[k]].x == gm;
+            lc += live ? 1 : 0;
+            livePoly = live ? p[k] : livePoly;
+          }
           const uint32_t liveHolders = __ballot_sync(0xffffffffu, lc != 0);
           const bool liveMulti = __any_sync(0xffffffffu, lc > 1);
           if (__popc(liveHolders) > 1 || liveMulti) {
@@ -911,27 +930,30 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
             break;
           }
           if (liveHolders == 0u) {  // only superseded entries surfaced: drop them
-            t0 = m0 ? kInfBits : t0;
-            t1 = m1 ? kInfBits : t1;
-            t2 = m2 ? kInfBits : t2;
+#pragma unroll
+            for (int k = 0; k < kOpenSlots; ++k)
+              t[k] = m[k] ? kInfBits : t[k];
             continue;
           }
-          best = __shfl_sync(0xffffffffu, l0 ? p0 : (l1 ? p1 : p2), __ffs(liveHolders) - 1);
+          best = __shfl_sync(0xffffffffu, livePoly, __ffs(liveHolders) - 1);
         }
         if (best == endIdx) {
           reached = true;
           break;
         }
         if (hsum >> 16) {
-          // A lane whose three entries are all taken hands one to a lane with room
+          // A lane whose entries are all taken hands its last one to a lane with room
           // (preferably one with two free pairs), so that it can accept a neighbour below.
-          t0 = m0 ? kInfBits : t0;  // (the popped entry first)
-          t1 = m1 ? kInfBits : t1;
-          t2 = m2 ? kInfBits : t2;
-          m0 = m1 = m2 = false;  // done: the pairs may be refilled just below
-          const bool f0 = t0 == kInfBits, f1 = t1 == kInfBits, f2 = t2 == kInfBits;
-          uint32_t fb = __ballot_sync(0xffffffffu, !f0 && !f1 && !f2);
-          const int freeCnt = (f0 ? 1 : 0) + (f1 ? 1 : 0) + (f2 ? 1 : 0);
+          bool f[kOpenSlots];
+          int freeCnt = 0;
+#pragma unroll
+          for (int k = 0; k < kOpenSlots; ++k) {
+            t[k] = m[k] ? kInfBits : t[k];  // (the popped entry first)
+            m[k] = false;                   // done: the pairs may be refilled just below
+            f[k] = t[k] == kInfBits;
+            freeCnt += f[k] ? 1 : 0;
+          }
+          uint32_t fb = __ballot_sync(0xffffffffu, freeCnt == 0);
           uint32_t rb = __ballot_sync(0xffffffffu, freeCnt >= 2);
           const uint32_t rb1 = __ballot_sync(0xffffffffu, freeCnt >= 1);
           if (!rb)
@@ -940,29 +962,25 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
             const int src = __ffs(fb) - 1, dst = __ffs(rb) - 1;
             fb &= fb - 1;
             rb &= rb - 1;
-            const uint32_t mt = __shfl_sync(0xffffffffu, t2, src);
-            const uint32_t mp = __shfl_sync(0xffffffffu, p2, src);
-            if (lane == dst) {  // into its first free pair
-              if (f0) {
-                t0 = mt;
-                p0 = mp;
-              } else if (f1) {
-                t1 = mt;
-                p1 = mp;
-              } else {
-                t2 = mt;
-                p2 = mp;
-              }
+            const uint32_t mt = __shfl_sync(0xffffffffu, t[kOpenSlots - 1], src);
+            const uint32_t mp = __shfl_sync(0xffffffffu, p[kOpenSlots - 1], src);
+            bool placed = lane != dst;  // into the receiver's first free pair
+#pragma unroll
+            for (int k = 0; k < kOpenSlots; ++k) {
+              const bool here = !placed && f[k];
+              t[k] = here ? mt : t[k];
+              p[k] = here ? mp : p[k];
+              placed = placed || here;
             }
             if (lane == src)
-              t2 = kInfBits;
+              t[kOpenSlots - 1] = kInfBits;
           }
         }
       }
       // the popped entry and, after a resolved tie, the superseded ones beside it
-      t0 = m0 ? kInfBits : t0;
-      t1 = m1 ? kInfBits : t1;
-      t2 = m2 ? kInfBits : t2;
+#pragma unroll
+      for (int k = 0; k < kOpenSlots; ++k)
+        t[k] = m[k] ? kInfBits : t[k];
       BPSN_TICK(tP1);
 
       // ---- expand: one lane per edge of the popped polygon.  All loads of a
@@ -1035,17 +1053,15 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
       BPSN_TICK(tE2);
       // ---- the new entry goes into this lane's first free register pair
       {
-        const bool f0 = t0 == kInfBits, f1 = t1 == kInfBits, f2 = t2 == kInfBits;
-        const bool i0 = upd && f0;
-        const bool i1 = upd && !f0 && f1;
-        const bool i2 = upd && !f0 && !f1 && f2;
-        t0 = i0 ? ntBits : t0;
-        p0 = i0 ? nei : p0;
-        t1 = i1 ? ntBits : t1;
-        p1 = i1 ? nei : p1;
-        t2 = i2 ? ntBits : t2;
-        p2 = i2 ? nei : p2;
-        overflow = overflow || (upd && !f0 && !f1 && !f2);
+        bool placed = !upd;
+#pragma unroll
+        for (int k = 0; k < kOpenSlots; ++k) {
+          const bool here = !placed && t[k] == kInfBits;
+          t[k] = here ? ntBits : t[k];
+          p[k] = here ? nei : p[k];
+          placed = placed || here;
+        }
+        overflow = overflow || !placed;
       }
       BPSN_TICK(tE3);
       if (upd) {
@@ -1243,7 +1259,7 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
       break;
     BPSN_TICK(tQ0);
 #if defined(BPSN_PHASE_TIMING)
-    const unsigned long long accA0 = pacc->sum[2], accF0 = pacc->sum[3];
+    const unsigned long long accA0 = pacc->sum[2], accF0 = pacc->sum[3], accP0 = pacc->pops;
 #endif
     const uint32_t e = g.geoList[base + q];
     const uint32_t f = g.flags[e];
@@ -1300,7 +1316,7 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
           return v > mx ? mx : v;
         };
         const unsigned long long packed =
-            (f(tQ3 - tS0, 16) << 48) | (f(tQ0 - tS0, 12) << 36) | (f(tQ1 - tQ0, 8) << 28) |
+            (f(tQ3 - tS0, 16) << 48) | (((pacc->pops - accP0) & 0xfffull) << 36) | (f(tQ1 - tQ0, 8) << 28) |
             (f(static_cast<long long>(pacc->sum[2] - accA0), 12) << 16) |
             (f(static_cast<long long>(pacc->sum[3] - accF0), 8) << 8) | f(tQ3 - tQ2, 8);
         atomicMax(&g_phaseCycles[17], packed);

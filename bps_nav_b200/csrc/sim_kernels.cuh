@@ -414,15 +414,17 @@ __device__ __forceinline__ void forwardMove(const GroupDev& g, const NavScene& s
 }
 
 __global__ void __launch_bounds__(256)
-k_pre(GroupDev g, SceneTable st, const int64_t* __restrict__ actions, TurnConsts tc,
-      uint32_t seedLo, uint32_t seedHi) {
+k_pre(GroupDev g, SceneTable st, const int64_t* __restrict__ actions,
+      const uint8_t* __restrict__ actions8, TurnConsts tc, uint32_t seedLo, uint32_t seedHi) {
   launchDependents();
   waitForPredecessor();
   const uint32_t e = blockIdx.x * blockDim.x + threadIdx.x;
   if (e >= g.B)
     return;
   const uint32_t B = g.B;
-  const int64_t action = actions[e];
+  // host-supplied actions arrive validated and narrowed to one byte each, in pinned
+  // host memory that the kernel reads in place (no staging copy in the stream)
+  const int64_t action = actions8 ? static_cast<int64_t>(actions8[e]) : actions[e];
   const uint32_t step = g.step[e] + 1;
   g.step[e] = step;
   bool done = static_cast<float>(step) >= kMaxSteps;
