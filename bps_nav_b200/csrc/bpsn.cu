@@ -210,7 +210,7 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
                oTmp = place(B * f);
   const size_t oNavRef = place(B * u), oGoalRef = place(B * u), oStep = place(B * u),
                oEpisode = place(B * u), oResetCount = place(B * u), oStatus = place(B * u),
-               oScene = place(B * u), oFlags = place(B * u);
+               oScene = place(B * u);
   const size_t oReward = place(B * f), oMask = place(B), oInfo = place(3 * B * f),
                oPolar = place(2 * B * f);
   const uint32_t ns = sim->cfg.num_scenes;
@@ -251,7 +251,6 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
   d.resetCount = reinterpret_cast<uint32_t*>(b + oResetCount);
   d.status = reinterpret_cast<uint32_t*>(b + oStatus);
   d.scene = reinterpret_cast<uint32_t*>(b + oScene);
-  d.flags = reinterpret_cast<uint32_t*>(b + oFlags);
   d.reward = reinterpret_cast<float*>(b + oReward);
   d.mask = reinterpret_cast<uint8_t*>(b + oMask);
   d.info = reinterpret_cast<float*>(b + oInfo);
@@ -435,6 +434,8 @@ int32_t bpsn_create(const bpsn_config* cfg, bpsn_sim** out) {
     return fail(nullptr, BPSN_ERR_INVALID_ARG,
                 "bpsn_create: num_envs, num_scenes must be > 0 and num_groups 1 or 2");
   // the reference aborts on these (simulator/simulator.cpp:1503-1508, 1536-1538)
+  if (cfg->num_envs > kListEnvMask)
+    return fail(nullptr, BPSN_ERR_INVALID_ARG, "bpsn_create: at most 2^30 - 1 environments");
   if (cfg->num_envs % cfg->num_scenes != 0)
     return fail(nullptr, BPSN_ERR_INVALID_ARG,
                 "Num environments is not a multiple of the number of active scenes");

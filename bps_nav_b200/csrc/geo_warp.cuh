@@ -216,8 +216,10 @@ __device__ __forceinline__ float warpFunnel(const StagedView sc, const WarpSlab 
                                             const float* startPos, const float* endPos,
                                             int pathSize, uint32_t* status) {
   float closestStart[3], closestEnd[3];
+  BPSN_TICK(tF0);
   warpClosestOnBoundary(sc, lane, w.path[0], startPos, w.path[pathSize - 1], endPos, closestStart,
                         closestEnd);
+  BPSN_TICK(tF1);
   bool bad = false;
   for (int i = lane; i + 1 < pathSize; i += 32) {
     const NavPoly* from = &sc.polys[w.path[i]];
@@ -246,9 +248,13 @@ __device__ __forceinline__ float warpFunnel(const StagedView sc, const WarpSlab 
     return BPSN_INF;
   }
   __syncwarp();
+  BPSN_TICK(tF2);
 
   float result = 0.f;
   uint32_t st = 0;
+#if defined(BPSN_PHASE_TIMING)
+  int scanIters = 0;
+#endif
   if (lane == 0) {
     PathAcc acc;
     acc.count = 0;
@@ -263,86 +269,116 @@ __device__ __forceinline__ float warpFunnel(const StagedView sc, const WarpSlab 
       vcopy(pr, apex);
       int apexIndex = 0, leftIndex = 0, rightIndex = 0;
       bool leftIsEnd = false, rightIsEnd = false;
+      // The scan is a chain of dependent decisions; a branch costs about as much here
+      // as a shared-memory load.  Per portal all five signed areas and the two
+      // coincidence tests are evaluated up front (they are independent) and the
+      // tightening of the funnel is done with selects, which leaves two rarely taken
+      // branches (a corner on the left, a corner on the right).  The float operations
+      // and comparisons are those of the sequential form in funnelLength().
       int guard = 0;
-      for (int i = 0; i < pathSize; ++i) {
-        if (++guard > 64 * kMaxPathPolys) {
-          st |= kStatIterCap;
-          result = BPSN_INF;
-          finished = true;
-          break;
+      const int lastPortal = pathSize - 2;  // portals are 0 .. pathSize - 2
+      float4 curA = w.nodeA[0];
+      uint2 curB = w.nodeB[0];
+      // The first portal is skipped when the start lies on it (DetourNavMeshQuery.cpp:
+      // 1858-1863).  The body only ever runs with i == 0 here, at the start: a restart
+      // resumes behind its apex.
+      int i = 0;
+      {
+        const float l0[3] = {curA.x, curA.y, curA.z};
+        const float r0[3] = {curA.w, __uint_as_float(curB.x), __uint_as_float(curB.y)};
+        float t;
+        if (distPtSegSqr2D(apex, l0, r0, t) < (0.001f * 0.001f)) {
+          i = 1;
+          const int ri = (1 <= lastPortal) ? 1 : lastPortal;
+          curA = w.nodeA[ri];
+          curB = w.nodeB[ri];
         }
-        float left[3], right[3];
+      }
+      constexpr int kFunnelCap = 64 * kMaxPathPolys;
+      for (; i < pathSize && guard < kFunnelCap; ++i) {
+        ++guard;
+#if defined(BPSN_PHASE_TIMING)
+        scanIters++;
+#endif
+        // portal i is in cur; fetch the next one now, it is needed a whole iteration later
+        const int ni = (i + 1 <= lastPortal) ? i + 1 : lastPortal;
+        const float4 nxtA = w.nodeA[ni];
+        const uint2 nxtB = w.nodeB[ni];
         const bool isPortal = i + 1 < pathSize;
-        if (isPortal) {
-          const float4 pa = w.nodeA[i];
-          const uint2 pb = w.nodeB[i];
-          left[0] = pa.x; left[1] = pa.y; left[2] = pa.z;
-          right[0] = pa.w; right[1] = __uint_as_float(pb.x); right[2] = __uint_as_float(pb.y);
-          if (i == 0) {
-            float t;
-            if (distPtSegSqr2D(apex, left, right, t) < (0.001f * 0.001f))
-              continue;
-          }
-        } else {
-          vcopy(left, closestEnd);
-          vcopy(right, closestEnd);
+        float left[3], right[3];
+        left[0] = isPortal ? curA.x : closestEnd[0];
+        left[1] = isPortal ? curA.y : closestEnd[1];
+        left[2] = isPortal ? curA.z : closestEnd[2];
+        right[0] = isPortal ? curA.w : closestEnd[0];
+        right[1] = isPortal ? __uint_as_float(curB.x) : closestEnd[1];
+        right[2] = isPortal ? __uint_as_float(curB.y) : closestEnd[2];
+        curA = nxtA;
+        curB = nxtB;
+        const float aR = triArea2D(apex, pr, right);
+        const float aRL = triArea2D(apex, pl, right);
+        const float aL = triArea2D(apex, pl, left);
+        const float aLRold = triArea2D(apex, pr, left);
+        const float aLRnew = triArea2D(apex, right, left);
+        const bool eqR = vequal(apex, pr);
+        const bool eqL = vequal(apex, pl);
+        const bool rHit = aR <= 0.0f;
+        const bool rTight = rHit && (eqR || aRL > 0.0f);
+        const bool cornerLeft = rHit && !rTight;  // the right side crossed over the left
+        // the left vertex is looked at only if the right one made no corner; its test uses
+        // the right point as just tightened: triArea2D(apex, pr, left) with the new pr
+        const float aLR = rTight ? aLRnew : aLRold;
+        const bool lHit = aL >= 0.0f;
+        const bool lTight = lHit && (eqL || aLR < 0.0f);
+        const bool cornerRight = !cornerLeft && lHit && !lTight;
+        if (!cornerLeft) {
+          pr[0] = rTight ? right[0] : pr[0];
+          pr[1] = rTight ? right[1] : pr[1];
+          pr[2] = rTight ? right[2] : pr[2];
+          rightIsEnd = rTight ? !isPortal : rightIsEnd;
+          rightIndex = rTight ? i : rightIndex;
         }
-        if (triArea2D(apex, pr, right) <= 0.0f) {
-          if (vequal(apex, pr) || triArea2D(apex, pl, right) > 0.0f) {
-            vcopy(pr, right);
-            rightIsEnd = !isPortal;
-            rightIndex = i;
-          } else {
+        if (cornerLeft || cornerRight) {
+          // a corner: the opposite side's point becomes the apex and the scan resumes there
+          if (cornerLeft) {
             vcopy(apex, pl);
             apexIndex = leftIndex;
             stat = appendVertex(acc, apex, leftIsEnd);
-            if (stat == 2) {
-              st |= kStatFunnelOverflow;
-              result = BPSN_INF;
-              finished = true;
-              break;
-            }
-            if (stat == 1) {
-              result = acc.length;
-              finished = true;
-              break;
-            }
-            vcopy(pl, apex);
-            vcopy(pr, apex);
-            leftIndex = apexIndex;
-            rightIndex = apexIndex;
-            i = apexIndex;
-            continue;
-          }
-        }
-        if (triArea2D(apex, pl, left) >= 0.0f) {
-          if (vequal(apex, pl) || triArea2D(apex, pr, left) < 0.0f) {
-            vcopy(pl, left);
-            leftIsEnd = !isPortal;
-            leftIndex = i;
           } else {
             vcopy(apex, pr);
             apexIndex = rightIndex;
             stat = appendVertex(acc, apex, rightIsEnd);
-            if (stat == 2) {
-              st |= kStatFunnelOverflow;
-              result = BPSN_INF;
-              finished = true;
-              break;
-            }
-            if (stat == 1) {
-              result = acc.length;
-              finished = true;
-              break;
-            }
-            vcopy(pl, apex);
-            vcopy(pr, apex);
-            leftIndex = apexIndex;
-            rightIndex = apexIndex;
-            i = apexIndex;
-            continue;
           }
+          if (stat == 2) {
+            st |= kStatFunnelOverflow;
+            result = BPSN_INF;
+            finished = true;
+            break;
+          }
+          if (stat == 1) {
+            result = acc.length;
+            finished = true;
+            break;
+          }
+          vcopy(pl, apex);
+          vcopy(pr, apex);
+          leftIndex = apexIndex;
+          rightIndex = apexIndex;
+          i = apexIndex;
+          const int ri = (i + 1 <= lastPortal) ? i + 1 : lastPortal;
+          curA = w.nodeA[ri];
+          curB = w.nodeB[ri];
+          continue;
         }
+        pl[0] = lTight ? left[0] : pl[0];
+        pl[1] = lTight ? left[1] : pl[1];
+        pl[2] = lTight ? left[2] : pl[2];
+        leftIsEnd = lTight ? !isPortal : leftIsEnd;
+        leftIndex = lTight ? i : leftIndex;
+      }
+      if (!finished && guard >= kFunnelCap && i < pathSize) {
+        st |= kStatIterCap;
+        result = BPSN_INF;
+        finished = true;
       }
     }
     if (!finished) {
@@ -355,6 +391,16 @@ __device__ __forceinline__ float warpFunnel(const StagedView sc, const WarpSlab 
       }
     }
   }
+#if defined(BPSN_PHASE_TIMING)
+  if (lane == 0) {
+    const long long tF3 = clock64();
+    atomicAdd(&g_phaseCycles[18], static_cast<unsigned long long>(tF1 - tF0));
+    atomicAdd(&g_phaseCycles[19], static_cast<unsigned long long>(tF2 - tF1));
+    atomicAdd(&g_phaseCycles[20], static_cast<unsigned long long>(tF3 - tF2));
+    atomicAdd(&g_phaseCycles[21], 1ull);
+    atomicAdd(&g_phaseCycles[23], static_cast<unsigned long long>(scanIters));
+  }
+#endif
   result = __shfl_sync(0xffffffffu, result, 0);
   st = __shfl_sync(0xffffffffu, st, 0);
   *status |= st;
@@ -599,10 +645,6 @@ __device__ __forceinline__ void warpForwardMove(const GroupDev& g, const StagedV
 #if defined(BPSN_PHASE_TIMING)
   if (lane == 0) {
     const long long tM4 = clock64();
-    atomicAdd(&g_phaseCycles[18], static_cast<unsigned long long>(tM2 - tM1));
-    atomicAdd(&g_phaseCycles[19], static_cast<unsigned long long>(tM3 - tM2));
-    atomicAdd(&g_phaseCycles[20], static_cast<unsigned long long>(tM4 - tM3));
-    atomicAdd(&g_phaseCycles[21], 1ull);
   }
 #endif
   navOut[0] = np[0];
@@ -901,6 +943,11 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
       uint32_t best = __reduce_min_sync(0xffffffffu, cand);
       // one branch for everything that is not "a unique minimum that is not the end"
       if ((hsum != 1u) | (best == endIdx) | (guard > 64 * kMaxAStarNodes)) {
+#if defined(BPSN_PHASE_TIMING)
+        if (lane == 0) {
+          atomicAdd(&g_phaseCycles[22], 1ull);
+        }
+#endif
         if (guard > 64 * kMaxAStarNodes) {
           *status |= kStatIterCap;
           return BPSN_INF;
@@ -1009,6 +1056,8 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
         // entries of a node have different totals (each is strictly below the one
         // before), so the live one is the one that matches the node's current total.
         if (bB.x != gm) {
+#if defined(BPSN_PHASE_TIMING)
+#endif
           rot = (rot + 7) & 31;
           continue;
         }
@@ -1250,20 +1299,25 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
   const uint32_t B = g.B;
   const uint32_t base = g.listBase[sceneIdx];
   uint32_t* cursor = g.counts + gridDim.y + sceneIdx;  // zeroed by the step before
-  while (true) {
-    uint32_t q = 0;
-    if (lane == 0)
-      q = atomicAdd(cursor, 1u);
-    q = __shfl_sync(0xffffffffu, q, 0);
+  // Every warp starts on the list slot of its own number; the slots beyond the number of
+  // warps in the grid are handed out through the cursor.
+  const uint32_t gridWarps = gridDim.x * static_cast<uint32_t>(warpsPerBlock);
+  uint32_t q = blockIdx.x * static_cast<uint32_t>(warpsPerBlock) + static_cast<uint32_t>(warp);
+  for (bool first = true;; first = false) {
+    if (!first) {
+      if (lane == 0)
+        q = gridWarps + atomicAdd(cursor, 1u);
+      q = __shfl_sync(0xffffffffu, q, 0);
+    }
     if (q >= n)
       break;
     BPSN_TICK(tQ0);
 #if defined(BPSN_PHASE_TIMING)
     const unsigned long long accA0 = pacc->sum[2], accF0 = pacc->sum[3], accP0 = pacc->pops;
 #endif
-    const uint32_t e = g.geoList[base + q];
-    const uint32_t f = g.flags[e];
-    const bool done = f & 1u, moved = f & 2u;
+    const uint32_t entry = g.geoList[base + q];
+    const uint32_t e = entry & kListEnvMask;
+    const bool done = entry & kListDone, moved = entry & kListMoved;
     const float b[3] = {g.navGoal[e], g.navGoal[B + e], g.navGoal[2 * B + e]};
     const uint32_t bref = g.goalRef[e];
     float a[3];

@@ -47,6 +47,11 @@ namespace bpsn {
 
 enum Task : uint32_t { kTaskPointNav = 0, kTaskFlee = 1, kTaskExploration = 2 };
 
+// work-list entries: environment index in the low 30 bits, the action's outcome above
+constexpr uint32_t kListEnvMask = 0x3fffffffu;
+constexpr uint32_t kListDone = 1u << 30;   // the episode ends with this step
+constexpr uint32_t kListMoved = 1u << 31;  // MoveForward
+
 constexpr uint32_t kVisitedSlots = 1024;  // per-env open-addressing table of visited grid cells
 
 struct GroupDev {
@@ -73,7 +78,6 @@ struct GroupDev {
   uint32_t* resetCount;
   uint32_t* status;
   uint32_t* scene;
-  uint32_t* flags;  // per-step: bit0 done, bit1 moved
   // outputs
   float* reward;  // [B]
   uint8_t* mask;  // [B]
@@ -464,7 +468,8 @@ k_pre(GroupDev g, SceneTable st, const int64_t* __restrict__ actions,
   const unsigned running = __activemask();
   const unsigned listedMask = __ballot_sync(running, listed);
   if (listed) {
-    g.flags[e] = (done ? 1u : 0u) | (moved ? 2u : 0u);
+    // the list entry carries what the step kernel has to know about the action
+    const uint32_t entry = e | (done ? kListDone : 0u) | (moved ? kListMoved : 0u);
     // one atomic per (warp, scene) instead of one per environment
     const uint32_t sceneIdx = g.scene[e];
     const unsigned grp = __match_any_sync(listedMask, sceneIdx);
@@ -475,7 +480,7 @@ k_pre(GroupDev g, SceneTable st, const int64_t* __restrict__ actions,
       base = atomicAdd(&g.counts[sceneIdx], static_cast<uint32_t>(__popc(grp)));
     base = __shfl_sync(grp, base, leader);
     const uint32_t slot = base + __popc(grp & ((1u << lane) - 1u));
-    g.geoList[g.listBase[sceneIdx] + slot] = e;
+    g.geoList[g.listBase[sceneIdx] + slot] = entry;
   } else {
     finishEnv(g, st, e, false, false, 0.f, seedLo, seedHi);
   }
@@ -501,11 +506,11 @@ k_step_thread(GroupDev g, SceneTable st, AStarScratch* __restrict__ scratch, uin
   const uint32_t slot = g.listBase[sceneIdx] + t;
   if (slot >= g.B)
     return;
-  const uint32_t e = g.geoList[slot];
+  const uint32_t entry = g.geoList[slot];
+  const uint32_t e = entry & kListEnvMask;
   const uint32_t B = g.B;
   const NavScene sc = st.scenes[sceneIdx];
-  const uint32_t f = g.flags[e];
-  const bool done = f & 1u, moved = f & 2u;
+  const bool done = entry & kListDone, moved = entry & kListMoved;
   if (moved)
     forwardMove(g, sc, e);
   float d = 0.f;
