@@ -45,7 +45,8 @@ BYTES_PER_GAE_ELEM = 25.2         # scan 17.2 + normalise 8 per (t, env)
 L2_FLUSH_BYTES = 256 << 20
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu capture
 # (profiles/k_step_warp_config1_ncu_full.md); only meaningful for the default workload
-NCU_TRAFFIC_BYTES = {("c1", 4096, "uniform", "k_step"): 2.5e6}
+LARGE_BATCH_ENVS = 32768
+NCU_TRAFFIC_BYTES = {("c1", 4096, "uniform", "k_step"): 0.89e6}
 
 
 def parse_args():
@@ -60,6 +61,7 @@ def parse_args():
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-large-batch", action="store_true")
     return ap.parse_args()
 
 
@@ -81,17 +83,57 @@ def draw_actions(shape, mix, seed):
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    """Samples SM clock and throttle reasons of one GPU while a region runs: NVML from a
+    thread every few milliseconds (reads only), or nvidia-smi when NVML is not importable."""
 
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NVML_REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+                    0x4: "sw_power_cap"}
 
     def __init__(self, gpu):
         self.gpu = gpu
         self.proc = None
+        self.thread = None
+        self.stop_flag = False
+        self.sm, self.mx, self.reasons = [], [], set()
+
+    def _nvml_index(self):
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [v.strip() for v in vis.split(",") if v.strip()]
+            if self.gpu < len(ids) and ids[self.gpu].isdigit():
+                return int(ids[self.gpu])
+        return self.gpu
+
+    def _poll(self, nv, handle):
+        reasons_fn = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons", None)
+        while not self.stop_flag:
+            try:
+                self.sm.append(float(nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)))
+                if reasons_fn is not None:
+                    bits = int(reasons_fn(handle))
+                    for bit, name in self.NVML_REASONS.items():
+                        if bits & bit:
+                            self.reasons.add(name)
+            except Exception:  # noqa: BLE001 - sampling must never take the bench down
+                break
+            time.sleep(0.002)
 
     def start(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            handle = nv.nvmlDeviceGetHandleByIndex(self._nvml_index())
+            self.mx.append(float(nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM)))
+            import threading
+            self.thread = threading.Thread(target=self._poll, args=(nv, handle), daemon=True)
+            self.thread.start()
+            return
+        except Exception:  # noqa: BLE001
+            self.thread = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.Q}",
@@ -101,6 +143,12 @@ class ClockSampler:
             self.proc = None
 
     def stop(self):
+        if self.thread is not None:
+            self.stop_flag = True
+            self.thread.join(timeout=2)
+            return {"sm_mhz": float(np.median(self.sm)) if self.sm else None,
+                    "sm_max_mhz": float(np.max(self.mx)) if self.mx else None,
+                    "samples": len(self.sm), "reasons": sorted(self.reasons), "source": "nvml"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -125,7 +173,7 @@ class ClockSampler:
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None,
                 "sm_max_mhz": float(np.max(mx)) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "reasons": sorted(reasons), "source": "nvidia-smi"}
 
 
 def measured_peak():
@@ -337,6 +385,45 @@ def run_ours(args):
                      "ms_per_step_all_launches": step_ms}
     gen.close()
 
+    # ---------------- the same device-resident window at the largest per-GPU batch the
+    # benchmark configurations name (32768 environments): reported beside the headline, it
+    # shows the throughput once every warp has several queries to work through
+    big = None
+    if not args.no_large_batch and N < LARGE_BATCH_ENVS:
+        NB, KB = LARGE_BATCH_ENVS, 3
+        genb = bps_sim.PointNavRolloutGenerator.from_scenes(
+            [scene], NB, gpu_id=local, seed=dist_utils.shard_seed(2000, rank, NB),
+            host_mirrors=False)
+        genb.reset(0)
+        actsb = torch.from_numpy(draw_actions(((1 + KB) * T, NB), args.mix, 11 + rank)).to(dev)
+        rb = torch.zeros(T + 1, NB, 1, device=dev)
+        vb = torch.randn(T + 1, NB, 1, device=dev)
+        nvb = torch.randn(NB, 1, device=dev)
+        mb = torch.ones(T + 1, NB, 1, dtype=torch.bool, device=dev)
+        retb = torch.zeros(T + 1, NB, 1, device=dev)
+        advb = torch.empty(T, NB, 1, device=dev)
+
+        def window_big(k):
+            for t in range(T):
+                genb.step_start(0, actsb[k * T + t], reward_out=rb[t], mask_out=mb[t + 1])
+                genb.step_end(0)
+            rollout.compute_returns(rb, vb, mb, retb, nvb, T, GAMMA, TAU, advantages=advb,
+                                    normalize=True)
+
+        window_big(0)
+        barrier()
+        b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        b0.record()
+        for k in range(KB):
+            window_big(1 + k)
+        b1.record()
+        barrier()
+        big_ms = max_over_ranks(b0.elapsed_time(b1))
+        big = {"envs_per_gpu": NB, "windows": KB, "value": world * NB * T * KB / (big_ms / 1000.0),
+               "unit": "env-steps/s", "note": "informational; not the headline workload"}
+        genb.close()
+        del actsb, rb, vb, nvb, mb, retb, advb
+
     # ---------------- end-to-end arm through the reference-shaped host API
     e2e = None
     if not args.no_e2e:
@@ -405,7 +492,7 @@ def run_ours(args):
                        "envs_per_gpu": N, "rollout_T": T, "polys": info["num_polys"],
                        "l2": f"flushed between timed windows ({L2_FLUSH_BYTES >> 20} MiB write)",
                        "timing": "CUDA events per window on the launch stream, summed, max over ranks"},
-            "clocks": clocks, "e2e": e2e, "roofline": roofline, "roofline_step": step_roofline,
+            "clocks": clocks, "e2e": e2e, "large_batch": big, "roofline": roofline, "roofline_step": step_roofline,
             "kernels": kernels, "cpu_baseline": cpu,
             "gpu_launches": K * (T * 2 + 2), "resets_per_step": resets_per_step,
             "mean_return": mean_return, "wall_s_device_arm": wall,
