@@ -232,6 +232,65 @@ def cpu_arm(args, seconds, steps_cap=None):
                             "PathFinder replica per thread"}
 
 
+def cpu_microbench(args, seconds=3.0):
+    """One-core rate of the same CPU simulator and microseconds per navmesh query of the
+    reference's compiled PathFinder (tryStep, findPath) on the bench scene's episodes."""
+    from oracle import pyoracle
+    nav, epf = scene_files(args.scene)
+    eps = np.load(epf)
+    n = min(args.envs, 1024)
+    sim = pyoracle.OracleSim([(nav, eps)], n, seed=1, threads=1)
+    sim.reset()
+    sim.run(draw_actions((4, n), args.mix, 99))
+    steps, busy, k = 0, 0.0, 0
+    while busy < seconds:
+        acts = draw_actions((16, n), args.mix, 500 + k)
+        ta = time.perf_counter()
+        sim.run(acts)
+        busy += time.perf_counter() - ta
+        steps += 16
+        k += 1
+    sim.close()
+    one_core = steps * n / busy
+    nq = min(len(eps), 4000)
+    start = np.ascontiguousarray(eps[:nq, 0:3], np.float32)   # record = start 3, rotation 4, goal 3
+    goal = np.ascontiguousarray(eps[:nq, 7:10], np.float32)
+    rn = pyoracle.RefNav(nav)
+    s_pos, s_ref = rn.snap(start)
+    g_pos, g_ref = rn.snap(goal)
+    d = g_pos - s_pos
+    d[:, 1] = 0
+    d /= np.maximum(np.linalg.norm(d, axis=1, keepdims=True), 1e-6)
+    end = (s_pos + 0.25 * d).astype(np.float32)
+    rn.try_step(s_pos, s_ref, end)
+    t0 = time.perf_counter()
+    for _ in range(5):
+        rn.try_step(s_pos, s_ref, end)
+    us_try = 1e6 * (time.perf_counter() - t0) / (5 * nq)
+    rn.geodesic(s_pos, s_ref, g_pos, g_ref)
+    t0 = time.perf_counter()
+    for _ in range(3):
+        rn.geodesic(s_pos, s_ref, g_pos, g_ref)
+    us_path = 1e6 * (time.perf_counter() - t0) / (3 * nq)
+    rn.close()
+    return {"one_core_env_steps_per_s": one_core, "one_core_envs": n,
+            "us_per_try_step": us_try, "us_per_find_path_start_to_goal": us_path,
+            "queries_timed": nq}
+
+
+def torch_gae_restatement(rewards, value_preds, masks, returns, next_value, T, gamma, tau):
+    """RolloutStorage.compute_returns (bps_nav/common/rollout_storage.py:203-219) restated with the
+    same tensor operations: the per-step Python loop whose launch overhead the fused kernel removes."""
+    value_preds[T] = next_value
+    gae = 0
+    for step in reversed(range(T)):
+        delta = rewards[step] + gamma * value_preds[step + 1] * masks[step + 1] - value_preds[step]
+        gae = delta + gamma * tau * masks[step + 1] * gae
+        returns[step] = gae + value_preds[step]
+    adv = returns[:T] - value_preds[:T]
+    return (adv - adv.mean()) / (adv.std() + 1e-5)
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -471,12 +530,41 @@ def run_ours(args):
                "how": "host wall clock, barrier + synchronize on both sides, max over ranks"}
         gen2.close()
 
+    # ---------------- the reference's GAE formulation (a Python loop of tensor ops) timed on
+    # this GPU and on the host, beside the fused kernels
+    gae_base = None
+    if rank == 0 and world == 1:
+        def med(fn, reps, sync):
+            ts = []
+            for _ in range(reps):
+                if sync:
+                    torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                fn()
+                if sync:
+                    torch.cuda.synchronize()
+                ts.append(time.perf_counter() - t0)
+            return 1000.0 * float(np.median(ts))
+        vals2, ret2 = values.clone(), returns.clone()
+        cuda_ms = med(lambda: torch_gae_restatement(rewards, vals2, masks, ret2, next_value, T,
+                                                    GAMMA, TAU), 30, True)
+        ours_ms = med(lambda: rollout.compute_returns(rewards, values, masks, returns, next_value, T,
+                                                      GAMMA, TAU, advantages=adv, normalize=True),
+                      30, True)
+        cr, cv, cm, cn = rewards.cpu(), values.cpu(), masks.cpu(), next_value.cpu()
+        cret = torch.zeros_like(cr)
+        cpu_ms = med(lambda: torch_gae_restatement(cr, cv, cm, cret, cn, T, GAMMA, TAU), 5, False)
+        gae_base = {"torch_loop_cuda_ms": cuda_ms, "torch_loop_cpu_ms": cpu_ms,
+                    "fused_kernels_ms": ours_ms, "T": T, "N": N,
+                    "how": "median wall time per call incl. launch and synchronize"}
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         try:
             rate, d = cpu_arm(args, args.cpu_seconds)
             cpu = {"value": rate, "unit": "env-steps/s", "cores": d["cores"], "kind": "reference",
                    "sample": d["sample"], "seconds": d["seconds"]}
+            cpu.update(cpu_microbench(args))
         except Exception as e:  # the baseline is a reported figure, not a dependency
             cpu = {"value": None, "unit": "env-steps/s", "cores": 0, "kind": "reference",
                    "sample": f"unavailable: {e}"}
@@ -493,7 +581,7 @@ def run_ours(args):
                        "l2": f"flushed between timed windows ({L2_FLUSH_BYTES >> 20} MiB write)",
                        "timing": "CUDA events per window on the launch stream, summed, max over ranks"},
             "clocks": clocks, "e2e": e2e, "large_batch": big, "roofline": roofline, "roofline_step": step_roofline,
-            "kernels": kernels, "cpu_baseline": cpu,
+            "kernels": kernels, "cpu_baseline": cpu, "gae_baseline": gae_base,
             "gpu_launches": K * (T * 2 + 2), "resets_per_step": resets_per_step,
             "mean_return": mean_return, "wall_s_device_arm": wall,
         }
