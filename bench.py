@@ -62,6 +62,7 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-large-batch", action="store_true")
+    ap.add_argument("--no-depth", action="store_true")
     return ap.parse_args()
 
 
@@ -483,6 +484,34 @@ def run_ours(args):
         genb.close()
         del actsb, rb, vb, nvb, mb, retb, advb
 
+    # ---------------- depth sensor (optional observation path; informational)
+    depth_info = None
+    if not args.no_depth and scene.floor is not None:
+        RW, RH = 64, 64
+        gend = bps_sim.PointNavRolloutGenerator.from_scenes(
+            [scene], N, gpu_id=local, seed=dist_utils.shard_seed(3000, rank, N),
+            host_mirrors=False, depth=True, render_resolution=(RW, RH))
+        gend.reset(0)
+        for t in range(8):
+            gend.step(0, acts[t])
+        torch.cuda.synchronize()
+        d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 20
+        d0.record()
+        for _ in range(reps):
+            gend.render(0)
+        d1.record()
+        torch.cuda.synchronize()
+        d_ms = max_over_ranks(d0.elapsed_time(d1)) / reps
+        nbox = len(scene.boxes)
+        depth_info = {"resolution": [RW, RH], "boxes": nbox, "ms_per_render": d_ms,
+                      "rays_per_s": world * N * RW * RH / (d_ms * 1e-3),
+                      "ray_box_tests_per_s": world * N * RW * RH * nbox / (d_ms * 1e-3),
+                      "image_write_gbs": N * RW * RH * 4 / (d_ms * 1e-3) / 1e9,
+                      "note": "k_depth: analytic ray / box sensor, fp32-pipe-bound; not part of "
+                              "the headline metric (the benchmark configuration disables rendering)"}
+        gend.close()
+
     # ---------------- end-to-end arm through the reference-shaped host API
     e2e = None
     if not args.no_e2e:
@@ -580,7 +609,7 @@ def run_ours(args):
                        "envs_per_gpu": N, "rollout_T": T, "polys": info["num_polys"],
                        "l2": f"flushed between timed windows ({L2_FLUSH_BYTES >> 20} MiB write)",
                        "timing": "CUDA events per window on the launch stream, summed, max over ranks"},
-            "clocks": clocks, "e2e": e2e, "large_batch": big, "roofline": roofline, "roofline_step": step_roofline,
+            "clocks": clocks, "e2e": e2e, "large_batch": big, "depth_sensor": depth_info, "roofline": roofline, "roofline_step": step_roofline,
             "kernels": kernels, "cpu_baseline": cpu, "gae_baseline": gae_base,
             "gpu_launches": K * (T * 2 + 2), "resets_per_step": resets_per_step,
             "mean_return": mean_return, "wall_s_device_arm": wall,

@@ -12,8 +12,8 @@ LIB_PATH = os.path.join(HERE, "libbpsn.so")
 # every symbol include/bpsn.h declares
 SYMBOLS = [
     "bpsn_create", "bpsn_destroy", "bpsn_set_navmesh_file", "bpsn_set_navmesh_blob",
-    "bpsn_set_episodes", "bpsn_set_env_scenes", "bpsn_finalize", "bpsn_reset", "bpsn_step_start", "bpsn_step_start_ex",
-    "bpsn_step_end", "bpsn_get_ptr", "bpsn_device_error_flags", "bpsn_profile_enable", "bpsn_profile_read", "bpsn_scene_info", "bpsn_query_snap", "bpsn_query_try_step",
+    "bpsn_set_episodes", "bpsn_set_env_scenes", "bpsn_set_scene_geometry", "bpsn_finalize", "bpsn_reset", "bpsn_step_start", "bpsn_step_start_ex",
+    "bpsn_step_end", "bpsn_render", "bpsn_get_ptr", "bpsn_device_error_flags", "bpsn_profile_enable", "bpsn_profile_read", "bpsn_scene_info", "bpsn_query_snap", "bpsn_query_try_step",
     "bpsn_query_geodesic", "bpsn_gae_workspace_bytes", "bpsn_gae", "bpsn_gae_static", "bpsn_selftest_sqrt", "bpsn_last_error",
     "bpsn_version",
 ]
@@ -32,13 +32,13 @@ MEM_DEVICE, MEM_HOST = 0, 1
 (FIELD_REWARD, FIELD_MASK, FIELD_INFO, FIELD_POLAR, FIELD_POSITION, FIELD_ROTATION, FIELD_GOAL,
  FIELD_NAV_POSITION, FIELD_NAV_POLY, FIELD_GOAL_POLY, FIELD_STEP, FIELD_EPISODE, FIELD_RESET_COUNT,
  FIELD_STATUS, FIELD_PREV_DIST, FIELD_CUM_TRAVEL, FIELD_INIT_DIST, FIELD_SCENE,
- FIELD_EPISODE_REWARD, FIELD_EPISODE_STATS) = range(20)
+ FIELD_EPISODE_REWARD, FIELD_EPISODE_STATS, FIELD_DEPTH) = range(21)
 
 
 class Config(C.Structure):
     _fields_ = [("gpu_id", C.c_int32), ("num_envs", C.c_uint32), ("num_groups", C.c_uint32),
                 ("num_scenes", C.c_uint32), ("seed", C.c_uint64), ("flags", C.c_uint32),
-                ("task", C.c_uint32)]
+                ("task", C.c_uint32), ("render_width", C.c_uint32), ("render_height", C.c_uint32)]
 
 
 class Episode(C.Structure):
@@ -66,6 +66,8 @@ def load():
     lib.bpsn_set_navmesh_blob.argtypes = [vp, u32, vp, sz]
     lib.bpsn_set_episodes.argtypes = [vp, u32, vp, u32]
     lib.bpsn_set_env_scenes.argtypes = [vp, vp, u32]
+    lib.bpsn_set_scene_geometry.argtypes = [vp, u32, vp, vp, u32]
+    lib.bpsn_render.argtypes = [vp, u32, vp]
     lib.bpsn_finalize.argtypes = [vp]
     lib.bpsn_reset.argtypes = [vp, u32, vp]
     lib.bpsn_step_start.argtypes = [vp, u32, vp, i32, vp]

@@ -134,7 +134,9 @@ class _RolloutGenerator:
                        flags=(L.FLAG_HOST_MIRRORS if host_mirrors else 0) |
                        (L.FLAG_GENERIC_KERNEL if generic_kernel else 0) |
                        (L.FLAG_EXACT_HEAP if exact_heap else 0),
-                       task=self._task_id)
+                       task=self._task_id,
+                       render_width=self._res[0] if self._depth else 0,
+                       render_height=self._res[1] if self._depth else 0)
         L.check(self._lib.bpsn_create(C.byref(cfg), C.byref(self._h)))
         try:
             for i, sc in enumerate(self._scenes):
@@ -143,6 +145,12 @@ class _RolloutGenerator:
                 eps = np.ascontiguousarray(sc.episodes)
                 L.check(self._lib.bpsn_set_episodes(self._h, i, eps.ctypes.data, len(eps)),
                         self._h)
+                if self._depth and getattr(sc, "floor", None) is not None:
+                    floor = np.asarray(sc.floor, np.float32)
+                    boxes = np.ascontiguousarray(sc.boxes, np.float32)
+                    L.check(self._lib.bpsn_set_scene_geometry(
+                        self._h, i, floor.ctypes.data, boxes.ctypes.data if len(boxes) else None,
+                        len(boxes)), self._h)
             L.check(self._lib.bpsn_finalize(self._h), self._h)
         except Exception:
             self._lib.bpsn_destroy(self._h)
@@ -229,8 +237,12 @@ class _RolloutGenerator:
         L.check(self._lib.bpsn_step_end(self._h, group_idx), self._h)
 
     def render(self, group_idx):
-        """No renderer on this path; kept so call sites need no change."""
-        del group_idx
+        """Renders the depth sensor of the group (when the generator was built with
+        ``depth=True``) from the current poses, asynchronously on the current stream;
+        otherwise a no-op kept so that call sites need no change.  There is no colour
+        renderer: ``rgba`` stays zero-filled."""
+        if self._depth:
+            L.check(self._lib.bpsn_render(self._h, group_idx, self._stream()), self._h)
 
     def step(self, group_idx, actions):
         self.step_start(group_idx, actions)
@@ -310,6 +322,11 @@ class _RolloutGenerator:
         return _new_capsule(self._render_buffer(group_idx, "rgba").data_ptr())
 
     def depth(self, group_idx):
+        if self._depth:  # the library's own float32 [B, H, W] image
+            p, n = C.c_void_p(), C.c_size_t()
+            L.check(self._lib.bpsn_get_ptr(self._h, group_idx, L.FIELD_DEPTH, L.MEM_DEVICE,
+                                           C.byref(p), C.byref(n)), self._h)
+            return _new_capsule(p.value)
         return _new_capsule(self._render_buffer(group_idx, "depth").data_ptr())
 
     # ------------------------------------------------------------------ misc

@@ -14,6 +14,7 @@
 #include <string>
 #include <vector>
 
+#include "depth_kernels.cuh"
 #include "gae_kernels.cuh"
 #include "geo_warp.cuh"
 #include "navmesh_host.h"
@@ -31,6 +32,9 @@ struct DeviceScene {
   void* blob = nullptr;  // one device allocation holding every array
   NavScene dev{};
   std::vector<bpsn_episode> episodes;
+  // render geometry (optional): floor rectangle and boxes
+  float floor[4] = {0.f, 0.f, 0.f, 0.f};
+  std::vector<float> boxes;
 };
 
 struct Group {
@@ -57,6 +61,7 @@ struct Group {
   size_t geoSmem = 0;
   size_t slabOffset = 0;
   AStarScratch* fallbackScratch = nullptr;
+  float* depth = nullptr;  // [B][H][W] when a render size was configured
   cudaEvent_t done = nullptr;
   bool inFlight = false;
   // optional per-kernel timing (bpsn_profile_enable)
@@ -85,6 +90,11 @@ struct bpsn_sim {
   uint32_t* dEpOffset = nullptr;
   uint32_t* dEpCount = nullptr;
   SceneTable table{};
+  RenderTable render{};
+  float* dBoxes = nullptr;
+  uint32_t* dBoxOffset = nullptr;
+  uint32_t* dBoxCount = nullptr;
+  float* dFloor = nullptr;
   TurnConsts turn{};
   // scratch for the bpsn_query_* entry points
   AStarScratch* queryScratch = nullptr;
@@ -352,6 +362,12 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
   setField(BPSN_FIELD_SCENE, d.scene, B * u);
   setField(BPSN_FIELD_EPISODE_REWARD, d.episodeReward, B * f);
   setField(BPSN_FIELD_EPISODE_STATS, d.stats, 5 * B * f);
+  if (sim->cfg.render_width && sim->cfg.render_height) {
+    const size_t bytes = static_cast<size_t>(B) * sim->cfg.render_width * sim->cfg.render_height * f;
+    BPSN_CUDA(sim, cudaMalloc(&g.depth, bytes));
+    BPSN_CUDA(sim, cudaMemset(g.depth, 0, bytes));
+    setField(BPSN_FIELD_DEPTH, g.depth, bytes);
+  }
 
   if (!g.warpGeo)  // per-slot A* scratch is only used by the generic (global-memory) kernel
     BPSN_CUDA(sim, cudaMalloc(&g.scratch, sizeof(AStarScratch) * static_cast<size_t>(B)));
@@ -434,6 +450,10 @@ int32_t bpsn_create(const bpsn_config* cfg, bpsn_sim** out) {
     return fail(nullptr, BPSN_ERR_INVALID_ARG,
                 "bpsn_create: num_envs, num_scenes must be > 0 and num_groups 1 or 2");
   // the reference aborts on these (simulator/simulator.cpp:1503-1508, 1536-1538)
+  if ((cfg->render_width == 0) != (cfg->render_height == 0) || cfg->render_width > 4096 ||
+      cfg->render_height > 4096)
+    return fail(nullptr, BPSN_ERR_INVALID_ARG,
+                "bpsn_create: render_width and render_height must both be 0 or both in 1..4096");
   if (cfg->num_envs > kListEnvMask)
     return fail(nullptr, BPSN_ERR_INVALID_ARG, "bpsn_create: at most 2^30 - 1 environments");
   if (cfg->num_envs % cfg->num_scenes != 0)
@@ -474,6 +494,7 @@ int32_t bpsn_destroy(bpsn_sim* sim) {
     cudaFree(g.stateBlob);
     cudaFree(g.scratch);
     cudaFree(g.fallbackScratch);
+    cudaFree(g.depth);
     cudaFreeHost(g.hActions);
     cudaFreeHost(g.hOut);
     if (g.done)
@@ -489,6 +510,10 @@ int32_t bpsn_destroy(bpsn_sim* sim) {
   cudaFree(sim->dEpNav);
   cudaFree(sim->dEpOffset);
   cudaFree(sim->dEpCount);
+  cudaFree(sim->dBoxes);
+  cudaFree(sim->dBoxOffset);
+  cudaFree(sim->dBoxCount);
+  cudaFree(sim->dFloor);
   cudaFree(sim->queryScratch);
   delete sim;
   return BPSN_OK;
@@ -618,6 +643,35 @@ int32_t bpsn_finalize(bpsn_sim* sim) {
   sim->table.epOffset = sim->dEpOffset;
   sim->table.epCount = sim->dEpCount;
 
+  if (sim->cfg.render_width && sim->cfg.render_height) {
+    std::vector<float> boxes, floors(4 * static_cast<size_t>(ns), 0.f);
+    std::vector<uint32_t> bOff(ns), bCnt(ns);
+    for (uint32_t i = 0; i < ns; ++i) {
+      bOff[i] = static_cast<uint32_t>(boxes.size() / 6);
+      bCnt[i] = static_cast<uint32_t>(sim->scenes[i].boxes.size() / 6);
+      boxes.insert(boxes.end(), sim->scenes[i].boxes.begin(), sim->scenes[i].boxes.end());
+      for (int k = 0; k < 4; ++k)
+        floors[4 * static_cast<size_t>(i) + k] = sim->scenes[i].floor[k];
+    }
+    BPSN_CUDA(sim, cudaMalloc(&sim->dBoxes, sizeof(float) * (boxes.size() + 6)));
+    if (!boxes.empty())
+      BPSN_CUDA(sim, cudaMemcpy(sim->dBoxes, boxes.data(), sizeof(float) * boxes.size(),
+                                cudaMemcpyHostToDevice));
+    BPSN_CUDA(sim, cudaMalloc(&sim->dBoxOffset, sizeof(uint32_t) * ns));
+    BPSN_CUDA(sim, cudaMemcpy(sim->dBoxOffset, bOff.data(), sizeof(uint32_t) * ns,
+                              cudaMemcpyHostToDevice));
+    BPSN_CUDA(sim, cudaMalloc(&sim->dBoxCount, sizeof(uint32_t) * ns));
+    BPSN_CUDA(sim, cudaMemcpy(sim->dBoxCount, bCnt.data(), sizeof(uint32_t) * ns,
+                              cudaMemcpyHostToDevice));
+    BPSN_CUDA(sim, cudaMalloc(&sim->dFloor, sizeof(float) * 4 * ns));
+    BPSN_CUDA(sim, cudaMemcpy(sim->dFloor, floors.data(), sizeof(float) * 4 * ns,
+                              cudaMemcpyHostToDevice));
+    sim->render.boxes = sim->dBoxes;
+    sim->render.boxOffset = sim->dBoxOffset;
+    sim->render.boxCount = sim->dBoxCount;
+    sim->render.floor = sim->dFloor;
+  }
+
   const uint32_t ng = sim->cfg.num_groups;
   const uint32_t B = sim->cfg.num_envs / ng;
   sim->groups.resize(ng);
@@ -741,6 +795,41 @@ int32_t bpsn_step_start_ex(bpsn_sim* sim, uint32_t group, const int64_t* actions
   if (rc)
     return rc;
   g.inFlight = true;
+  return BPSN_OK;
+}
+
+int32_t bpsn_set_scene_geometry(bpsn_sim* sim, uint32_t scene, const float* floor4,
+                                const float* boxes, uint32_t num_boxes) {
+  if (!sim || !floor4 || (num_boxes && !boxes))
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_set_scene_geometry: null argument");
+  if (sim->finalized)
+    return fail(sim, BPSN_ERR_STATE, "bpsn_set_scene_geometry: already finalized");
+  if (scene >= sim->scenes.size())
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_set_scene_geometry: scene index out of range");
+  DeviceScene& ds = sim->scenes[scene];
+  for (int k = 0; k < 4; ++k)
+    ds.floor[k] = floor4[k];
+  ds.boxes.assign(boxes, boxes + 6 * static_cast<size_t>(num_boxes));
+  for (uint32_t b = 0; b < num_boxes; ++b)
+    for (int k = 0; k < 3; ++k)
+      if (!(ds.boxes[6 * b + k] <= ds.boxes[6 * b + 3 + k]))
+        return fail(sim, BPSN_ERR_INVALID_ARG,
+                    "bpsn_set_scene_geometry: box " + std::to_string(b) + " has min > max");
+  return BPSN_OK;
+}
+
+int32_t bpsn_render(bpsn_sim* sim, uint32_t group, void* stream) {
+  if (!sim || !sim->finalized)
+    return fail(sim, BPSN_ERR_STATE, "bpsn_render: handle not finalized");
+  if (group >= sim->groups.size())
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_render: group out of range");
+  Group& g = sim->groups[group];
+  if (!g.depth)
+    return fail(sim, BPSN_ERR_STATE, "bpsn_render: the handle was created without a render size");
+  BPSN_CUDA(sim, cudaSetDevice(sim->cfg.gpu_id));
+  k_depth<<<g.dev.B, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      g.dev, sim->render, g.depth, sim->cfg.render_width, sim->cfg.render_height);
+  BPSN_CUDA(sim, cudaGetLastError());
   return BPSN_OK;
 }
 

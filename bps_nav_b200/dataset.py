@@ -19,9 +19,26 @@ EPISODE_DTYPE = np.dtype([("start_position", "<f4", 3), ("start_rotation", "<f4"
 
 
 class Scene:
-    def __init__(self, navmesh_path, episodes, scene_id=""):
+    """One scene: navmesh file, episode records and, optionally, the render geometry of the depth
+    sensor (``floor`` = (xmin, zmin, xmax, zmax) at y = 0, ``boxes`` = float32 [K, 6] min/max
+    corners).  When not given, geometry is read from ``<navmesh stem>.scene.json`` if that file
+    exists (keys ``size_x``, ``size_z``, ``boxes``), the sidecar the synthetic scene generator
+    writes; scenes without geometry render as empty space."""
+
+    def __init__(self, navmesh_path, episodes, scene_id="", floor=None, boxes=None):
         self.navmesh_path = navmesh_path
         self.scene_id = scene_id
+        if floor is None and boxes is None:
+            side = os.path.splitext(navmesh_path)[0] + ".scene.json"
+            if os.path.exists(side):
+                with open(side) as f:
+                    doc = json.load(f)
+                if "size_x" in doc and "size_z" in doc:
+                    floor = (0.0, 0.0, float(doc["size_x"]), float(doc["size_z"]))
+                    boxes = doc.get("boxes", [])
+        self.floor = None if floor is None else tuple(float(x) for x in floor)
+        self.boxes = (np.zeros((0, 6), np.float32) if boxes is None else
+                      np.ascontiguousarray(np.asarray(boxes, np.float32).reshape(-1, 6)))
         episodes = np.ascontiguousarray(episodes)
         if episodes.dtype != EPISODE_DTYPE:
             flat = np.asarray(episodes, dtype=np.float32).reshape(-1, 10)

@@ -68,6 +68,8 @@ typedef struct {
   uint64_t seed;             /* seeds the episode-selection stream */
   uint32_t flags;            /* BPSN_FLAG_* */
   uint32_t task;             /* BPSN_TASK_* */
+  uint32_t render_width;     /* depth sensor image width  (0 with render_height 0: no sensor) */
+  uint32_t render_height;    /* depth sensor image height                                    */
 } bpsn_config;
 
 /* Tasks of the reference's three generators (simulator/simulator.cpp:734-999,
@@ -120,7 +122,9 @@ enum {
                                      success | spl | distanceToGoal (what PPOTrainer._update_stats
                                      keeps, bps_nav/rl/ppo/ppo_trainer.py:286-319); zero them to
                                      restart a window */
-  BPSN_FIELD_COUNT = 20
+  BPSN_FIELD_DEPTH = 20,     /* float32 [B,H,W] depth sensor image of the last bpsn_render
+                                (only when the handle was created with a render size)    */
+  BPSN_FIELD_COUNT = 21
 };
 
 enum { BPSN_MEM_DEVICE = 0, BPSN_MEM_HOST = 1 };
@@ -139,6 +143,15 @@ int32_t bpsn_set_episodes(bpsn_sim* sim, uint32_t scene, const bpsn_episode* epi
  * simulator/simulator.cpp:1205-1221, 1581-1592). */
 int32_t bpsn_set_env_scenes(bpsn_sim* sim, const uint32_t* env_scene, uint32_t count);
 /* Uploads scenes and episodes, allocates state, outputs and query scratch. */
+/* Render geometry of a scene for the depth sensor: the floor rectangle at y = 0
+ * (floor4 = xmin, zmin, xmax, zmax) and `num_boxes` axis-aligned boxes of 6 floats
+ * each (min xyz, max xyz).  Stands in for the render asset the reference loads per
+ * scene (Dataset::getScenePath + AssetLoader::loadScene, simulator/simulator.cpp:
+ * 330-342, 1209-1210).  Optional; before bpsn_finalize.  Scenes without geometry
+ * render as empty space (every pixel at the far plane). */
+int32_t bpsn_set_scene_geometry(bpsn_sim* sim, uint32_t scene, const float* floor4,
+                                const float* boxes, uint32_t num_boxes);
+
 int32_t bpsn_finalize(bpsn_sim* sim);
 
 /* Starts a fresh episode in every environment of the group.  Asynchronous on
@@ -162,6 +175,16 @@ int32_t bpsn_step_start_ex(bpsn_sim* sim, uint32_t group, const int64_t* actions
                            int32_t actions_mem, void* stream, float* reward_out,
                            uint8_t* mask_out, float* polar_out);
 int32_t bpsn_step_end(bpsn_sim* sim, uint32_t group);
+
+/* RolloutGenerator::render (simulator/simulator.cpp:1400-1410): renders the depth
+ * image of every environment of the group from its current pose into
+ * BPSN_FIELD_DEPTH, asynchronously on `stream`.  Camera as the reference sets it
+ * up: eye = position + 1.25 * up, looking down -Z of the agent frame, 90 degree
+ * vertical field of view, near 0.1, far 1000 (simulator.cpp:651-663, 1216); pixel
+ * value = view-space depth in metres, 1000 where nothing is hit.  The geometry is
+ * what bpsn_set_scene_geometry gave (the reference rasterises a mesh with bps3D,
+ * which is not part of its tree).  BPSN_ERR_STATE without a render size. */
+int32_t bpsn_render(bpsn_sim* sim, uint32_t group, void* stream);
 
 /* Pointer to a per-group array; mem selects device memory or (for the four
  * result fields, when BPSN_FLAG_HOST_MIRRORS is set) the pinned host copy.

@@ -325,3 +325,52 @@ def gae_reference(rewards, values, masks, next_value, gamma, tau, normalize=Fals
         std = a64.std(ddof=1)
         adv = ((adv - np.float32(mean)) / (np.float32(std) + np.float32(eps))).astype(np.float32)
     return returns, adv, values
+
+
+# ----------------------------------------------------------------------------- depth sensor
+def depth_reference(position, rotation, floor, boxes, width, height):
+    """Depth image [H, W] float32 of one environment: CPU restatement, in fp32 numpy with the
+    same operation order, of the analytic box-world sensor (camera of simulator/simulator.cpp:
+    651-663 and :1216: eye = position + 1.25 up, looking down -Z of the agent frame, 90 degree
+    vertical field of view, near 0.1, far 1000; value = view-space depth, far where nothing is
+    hit).  Parity unpinned: the reference renders with bps3D, which is not in its tree, so there
+    is no reference image to pin this against; it checks the CUDA kernel against an independent
+    evaluation of the same geometry."""
+    f = np.float32
+    qx, qy, qz, qw = (f(x) for x in rotation)
+    ox, oy, oz = f(position[0]), f(position[1]) + f(1.25), f(position[2])
+    qxx, qyy, qzz = qx * qx, qy * qy, qz * qz
+    qxz, qxy, qyz = qx * qz, qx * qy, qy * qz
+    qwx, qwy, qwz = qw * qx, qw * qy, qw * qz
+    one, two = f(1), f(2)
+    m00, m01, m02 = one - two * (qyy + qzz), two * (qxy + qwz), two * (qxz - qwy)
+    m10, m11, m12 = two * (qxy - qwz), one - two * (qxx + qzz), two * (qyz + qwx)
+    m20, m21, m22 = two * (qxz + qwy), two * (qyz - qwx), one - two * (qxx + qyy)
+    aspect = f(width) / f(height)
+    px = np.arange(width, dtype=np.float32)
+    py = np.arange(height, dtype=np.float32)
+    u = ((px + f(0.5)) / f(width) * two - one) * aspect
+    v = one - (py + f(0.5)) / f(height) * two
+    U, V = np.meshgrid(u, v)  # [H, W]
+    dx = (m00 * U + m10 * V) - m20
+    dy = (m01 * U + m11 * V) - m21
+    dz = (m02 * U + m12 * V) - m22
+    near, far = f(0.1), f(1000.0)
+    t = np.full((height, width), far, np.float32)
+    with np.errstate(divide="ignore", invalid="ignore", over="ignore"):
+        tf = (f(0) - oy) / dy
+        hx, hz = ox + tf * dx, oz + tf * dz
+        fl = [f(x) for x in floor]
+        hit = ((dy < 0) & (tf >= near) & (tf < t) & (hx >= fl[0]) & (hx <= fl[2]) &
+               (hz >= fl[1]) & (hz <= fl[3]))
+        t = np.where(hit, tf, t).astype(np.float32)
+        ix, iy, iz = one / dx, one / dy, one / dz
+        for b in np.asarray(boxes, np.float32).reshape(-1, 6):
+            tx0, tx1 = (b[0] - ox) * ix, (b[3] - ox) * ix
+            ty0, ty1 = (b[1] - oy) * iy, (b[4] - oy) * iy
+            tz0, tz1 = (b[2] - oz) * iz, (b[5] - oz) * iz
+            tenter = np.fmax(np.fmax(np.fmin(tx0, tx1), np.fmin(ty0, ty1)), np.fmin(tz0, tz1))
+            texit = np.fmin(np.fmin(np.fmax(tx0, tx1), np.fmax(ty0, ty1)), np.fmax(tz0, tz1))
+            hit = (tenter <= texit) & (tenter >= near) & (tenter < t)
+            t = np.where(hit, tenter, t).astype(np.float32)
+    return t

@@ -339,3 +339,20 @@ def test_two_rank_sharding_gloo():
     assert [r[2] for r in res] == [8192.0, 8192.0]      # whole-job env count
     assert res[0][3] == 1000 and res[1][3] == 1000 + 4096
     assert res[0][4] != res[1][4]
+
+
+def test_depth_oracle_known_answers():
+    """The CPU restatement of the depth sensor on a scene whose image is known in closed form."""
+    from oracle import pyoracle
+    # agent at (5, 0, 5), identity rotation = looking down -Z; a 2 m high box face at z = 3
+    d = pyoracle.depth_reference([5, 0, 5], [0, 0, 0, 1], (0, 0, 10, 10), [[4, 0, 2, 6, 2, 3]],
+                                 64, 64)
+    assert d.shape == (64, 64) and d.dtype == np.float32
+    assert d[32, 32] == np.float32(2.0)              # optical axis hits the face 2 m ahead
+    assert d[0, 32] == np.float32(1000.0)            # 45 degrees up: over the box, nothing there
+    v = 1.0 - (63 + 0.5) / 64 * 2.0                  # bottom row: the floor, depth = 1.25 / |v|
+    assert abs(d[63, 32] - 1.25 / abs(v)) < 1e-5
+    # turned by 180 degrees about +Y the agent looks at the floor's far edge and then the void
+    d2 = pyoracle.depth_reference([5, 0, 5], [0, 1, 0, 0], (0, 0, 10, 10), [[4, 0, 2, 6, 2, 3]],
+                                  64, 64)
+    assert d2[32, 32] == np.float32(1000.0) and d2[63, 32] == d[63, 32]
