@@ -14,7 +14,8 @@ SYMBOLS = [
     "bpsn_create", "bpsn_destroy", "bpsn_set_navmesh_file", "bpsn_set_navmesh_blob",
     "bpsn_set_episodes", "bpsn_set_env_scenes", "bpsn_set_scene_geometry", "bpsn_finalize", "bpsn_reset", "bpsn_step_start", "bpsn_step_start_ex",
     "bpsn_step_end", "bpsn_render", "bpsn_get_ptr", "bpsn_device_error_flags", "bpsn_profile_enable", "bpsn_profile_read", "bpsn_scene_info", "bpsn_query_snap", "bpsn_query_try_step",
-    "bpsn_query_geodesic", "bpsn_gae_workspace_bytes", "bpsn_gae", "bpsn_gae_static", "bpsn_selftest_sqrt", "bpsn_last_error",
+    "bpsn_query_geodesic", "bpsn_gae_workspace_bytes", "bpsn_gae", "bpsn_gae_static", "bpsn_selftest_sqrt", "bpsn_dataset_open", "bpsn_dataset_num_scenes", "bpsn_dataset_scene",
+    "bpsn_dataset_close", "bpsn_last_error",
     "bpsn_version",
 ]
 
@@ -88,12 +89,20 @@ def load():
     lib.bpsn_gae_static.argtypes = [vp, vp, vp, vp, vp, vp, u32, u32, C.c_double, C.c_double, i32,
                                     C.c_float, vp]
     lib.bpsn_selftest_sqrt.argtypes = [i32, u32, u32, C.POINTER(C.c_uint64)]
+    lib.bpsn_dataset_open.argtypes = [C.c_char_p, C.c_char_p, u32, C.POINTER(vp)]
+    lib.bpsn_dataset_num_scenes.argtypes = [vp]
+    lib.bpsn_dataset_num_scenes.restype = u32
+    lib.bpsn_dataset_scene.argtypes = [vp, u32, C.POINTER(C.c_char_p), C.POINTER(C.c_char_p),
+                                       C.POINTER(vp), C.POINTER(u32)]
+    lib.bpsn_dataset_close.argtypes = [vp]
+    lib.bpsn_dataset_close.restype = None
     lib.bpsn_last_error.argtypes = [vp]
     lib.bpsn_last_error.restype = C.c_char_p
     lib.bpsn_version.restype = C.c_char_p
     for name in SYMBOLS:
         fn = getattr(lib, name)
-        if name not in ("bpsn_gae_workspace_bytes", "bpsn_last_error", "bpsn_version"):
+        if name not in ("bpsn_gae_workspace_bytes", "bpsn_last_error", "bpsn_version",
+                        "bpsn_dataset_num_scenes", "bpsn_dataset_close"):
             fn.restype = i32
     _lib = lib
     return lib

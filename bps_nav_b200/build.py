@@ -12,7 +12,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libbpsn.so")
-SOURCES = ["bpsn.cu", "navmesh_host.cpp"]
+SOURCES = ["bpsn.cu", "navmesh_host.cpp", "dataset_host.cpp"]
 
 
 def _nvcc():
@@ -41,7 +41,7 @@ def build(force=False, verbose=False):
     ]
     if verbose:
         cmd += ["-Xptxas", "-v"]
-    cmd += [os.path.join(CSRC, s) for s in SOURCES] + ["-o", LIB]
+    cmd += [os.path.join(CSRC, s) for s in SOURCES] + ["-lz", "-o", LIB]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if verbose:
         sys.stderr.write(res.stderr)

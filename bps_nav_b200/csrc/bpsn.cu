@@ -14,6 +14,7 @@
 #include <string>
 #include <vector>
 
+#include "dataset_host.h"
 #include "depth_kernels.cuh"
 #include "gae_kernels.cuh"
 #include "geo_warp.cuh"
@@ -75,6 +76,10 @@ struct Group {
 };
 
 }  // namespace
+
+struct bpsn_dataset {
+  std::vector<DatasetScene> scenes;
+};
 
 struct bpsn_sim {
   bpsn_config cfg{};
@@ -1146,6 +1151,45 @@ int32_t bpsn_selftest_sqrt(int32_t gpu_id, uint32_t first_bits, uint32_t last_bi
                 std::string("bpsn_selftest_sqrt: ") + cudaGetErrorString(e));
   *mismatches = h;
   return BPSN_OK;
+}
+
+int32_t bpsn_dataset_open(const char* dataset_path, const char* asset_path, uint32_t num_threads,
+                          bpsn_dataset** out) {
+  if (!dataset_path || !asset_path || !out)
+    return fail(nullptr, BPSN_ERR_INVALID_ARG, "bpsn_dataset_open: null argument");
+  bpsn_dataset* ds = new bpsn_dataset();
+  std::string err;
+  if (!loadDataset(dataset_path, asset_path, num_threads, &ds->scenes, &err)) {
+    delete ds;
+    return fail(nullptr, BPSN_ERR_IO, err);
+  }
+  *out = ds;
+  return BPSN_OK;
+}
+
+uint32_t bpsn_dataset_num_scenes(const bpsn_dataset* ds) {
+  return ds ? static_cast<uint32_t>(ds->scenes.size()) : 0u;
+}
+
+int32_t bpsn_dataset_scene(const bpsn_dataset* ds, uint32_t index, const char** scene_id,
+                           const char** navmesh_path, const bpsn_episode** episodes,
+                           uint32_t* num_episodes) {
+  if (!ds || index >= ds->scenes.size())
+    return fail(nullptr, BPSN_ERR_INVALID_ARG, "bpsn_dataset_scene: bad dataset or index");
+  const DatasetScene& s = ds->scenes[index];
+  if (scene_id)
+    *scene_id = s.sceneId.c_str();
+  if (navmesh_path)
+    *navmesh_path = s.navmeshPath.c_str();
+  if (episodes)
+    *episodes = s.episodes.data();
+  if (num_episodes)
+    *num_episodes = static_cast<uint32_t>(s.episodes.size());
+  return BPSN_OK;
+}
+
+void bpsn_dataset_close(bpsn_dataset* ds) {
+  delete ds;
 }
 
 }  // extern "C"

@@ -46,7 +46,35 @@ class Scene:
         self.episodes = episodes
 
 
-def load_dataset(dataset_path, asset_path):
+def load_dataset(dataset_path, asset_path, num_threads=None):
+    """Reads a directory of ``*.json.gz`` episode files with the library's native reader
+    (``bpsn_dataset_open``: zlib + its own JSON parser, one thread per file up to
+    ``num_threads``) and returns ``Scene`` objects in file-name order."""
+    import ctypes as C
+    from . import _lib as L
+    lib = L.load()
+    if num_threads is None:
+        num_threads = max(1, len(os.sched_getaffinity(0)))
+    h = C.c_void_p()
+    L.check(lib.bpsn_dataset_open(os.fsencode(dataset_path), os.fsencode(asset_path),
+                                  int(num_threads), C.byref(h)))
+    try:
+        scenes = []
+        for i in range(lib.bpsn_dataset_num_scenes(h)):
+            sid, nav, eps, n = C.c_char_p(), C.c_char_p(), C.c_void_p(), C.c_uint32()
+            L.check(lib.bpsn_dataset_scene(h, i, C.byref(sid), C.byref(nav), C.byref(eps),
+                                           C.byref(n)))
+            buf = (C.c_char * (n.value * EPISODE_DTYPE.itemsize)).from_address(eps.value)
+            arr = np.frombuffer(buf, dtype=EPISODE_DTYPE).copy()
+            scenes.append(Scene(nav.value.decode(), arr, sid.value.decode()))
+        return scenes
+    finally:
+        lib.bpsn_dataset_close(h)
+
+
+def load_dataset_py(dataset_path, asset_path):
+    """The same reader in plain Python (gzip + json modules); kept as the cross-check of the
+    native one."""
     files = sorted(glob.glob(os.path.join(dataset_path, "*.json.gz")))
     if not files:
         raise RuntimeError(f"no *.json.gz episode files under {dataset_path}")

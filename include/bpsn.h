@@ -280,6 +280,23 @@ int32_t bpsn_gae_static(const float* rewards, float* values, const uint8_t* mask
 int32_t bpsn_selftest_sqrt(int32_t gpu_id, uint32_t first_bits, uint32_t last_bits,
                            uint64_t* mismatches);
 
+/* Episode datasets on disk (Dataset, simulator/simulator.cpp:190-359): a directory of
+ * `*.json.gz` Habitat PointNav episode files, one scene per file.  bpsn_dataset_open
+ * reads them all on up to `num_threads` host threads; scenes come back in file-name
+ * order.  bpsn_dataset_scene returns pointers into the dataset object (valid until
+ * bpsn_dataset_close): the scene id as written in the file, the navmesh path derived
+ * from it (asset_path / scene id with its extension replaced by ".navmesh") and the
+ * episode records, ready for bpsn_set_navmesh_file / bpsn_set_episodes.  On failure
+ * the message is available from bpsn_last_error(NULL).  No GPU is involved. */
+typedef struct bpsn_dataset bpsn_dataset;
+int32_t bpsn_dataset_open(const char* dataset_path, const char* asset_path, uint32_t num_threads,
+                          bpsn_dataset** out);
+uint32_t bpsn_dataset_num_scenes(const bpsn_dataset* ds);
+int32_t bpsn_dataset_scene(const bpsn_dataset* ds, uint32_t index, const char** scene_id,
+                           const char** navmesh_path, const bpsn_episode** episodes,
+                           uint32_t* num_episodes);
+void bpsn_dataset_close(bpsn_dataset* ds);
+
 const char* bpsn_last_error(const bpsn_sim* sim);
 /* Library build identification, e.g. "bpsn sm_100a". */
 const char* bpsn_version(void);

@@ -261,6 +261,61 @@ def test_dataset_round_trip(tmp_path):
             assert np.array_equal(a.episodes[f], b.episodes[f])
     with pytest.raises(RuntimeError):
         dataset.load_dataset(str(tmp_path / "assets"), str(tmp_path / "assets"))
+    # the native reader and the plain-Python one agree record for record
+    py = dataset.load_dataset_py(str(tmp_path / "eps"), str(tmp_path / "assets"))
+    assert [s.scene_id for s in py] == [s.scene_id for s in back]
+    assert [s.navmesh_path for s in py] == [s.navmesh_path for s in back]
+    for a, b in zip(py, back):
+        assert a.episodes.tobytes() == b.episodes.tobytes()
+
+
+def test_native_dataset_reader_edge_cases(tmp_path):
+    """JSON the writer above never produces: escapes, exponents, nested extras, whitespace,
+    an empty file (skipped), two scenes in one file (rejected), malformed input (rejected)."""
+    import gzip
+    import json
+    from bps_nav_b200 import dataset
+    d = tmp_path / "eps"
+    d.mkdir()
+    doc = r'''{ "config" : {"a": [1, 2, {"b": null}], "s": "q\\\"\u00e9\n"},
+ "episodes":[
+ {"episode_id":"0","scene_id":"dir\/A.glb","start_position":[1e0,-2.5E-1,3],
+  "start_rotation":[0,0.70710678,0,0.70710678],"goals":[{"position":[4,5.25,6],"radius":null}],
+  "info":{"geodesic_distance":7.5},"shortest_paths":null},
+ {"scene_id":"dir/A.glb","goals":[{"radius":0.2,"position":[0.1,0.2,0.3]}],
+  "start_rotation":[0,0,0,1],"start_position":[7,8,9],"extra":[true,false]}
+]}'''
+    with gzip.open(d / "a.json.gz", "wt") as f:
+        f.write(doc)
+    with gzip.open(d / "b.json.gz", "wt") as f:
+        json.dump({"episodes": []}, f)
+    got = dataset.load_dataset(str(d), "/assets", num_threads=3)
+    assert len(got) == 1 and got[0].scene_id == "dir/A.glb"
+    assert got[0].navmesh_path == "/assets/dir/A.navmesh"
+    e = got[0].episodes
+    assert e["start_position"].tolist() == [[1.0, -0.25, 3.0], [7.0, 8.0, 9.0]]
+    assert np.array_equal(e["start_rotation"][0],
+                          np.array([0, 0.70710678, 0, 0.70710678], np.float32))
+    assert np.array_equal(e["goal"], np.array([[4, 5.25, 6], [0.1, 0.2, 0.3]], np.float32))
+    ref = dataset.load_dataset_py(str(d), "/assets")
+    assert ref[0].episodes.tobytes() == e.tobytes()
+    with gzip.open(d / "c.json.gz", "wt") as f:
+        json.dump({"episodes": [
+            {"scene_id": "X.glb", "start_position": [0, 0, 0], "start_rotation": [0, 0, 0, 1],
+             "goals": [{"position": [1, 1, 1]}]},
+            {"scene_id": "Y.glb", "start_position": [0, 0, 0], "start_rotation": [0, 0, 0, 1],
+             "goals": [{"position": [1, 1, 1]}]}]}, f)
+    with pytest.raises(RuntimeError, match="one scene"):
+        dataset.load_dataset(str(d), "/assets")
+    os.remove(d / "c.json.gz")
+    with gzip.open(d / "c.json.gz", "wt") as f:
+        f.write('{"episodes": [ {"scene_id": "X.glb", ')
+    with pytest.raises(RuntimeError):
+        dataset.load_dataset(str(d), "/assets")
+    os.remove(d / "c.json.gz")
+    (d / "c.json.gz").write_bytes(b"this is not gzip")  # zlib reads it as plain text: bad JSON
+    with pytest.raises(RuntimeError):
+        dataset.load_dataset(str(d), "/assets")
 
 
 def test_active_scene_selection_matches_std_mt19937(tmp_path):
