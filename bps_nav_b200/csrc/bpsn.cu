@@ -55,12 +55,13 @@ struct Group {
   // launch plan of the geodesic phase
   uint32_t numScenesUsed = 0;   // grid.y
   uint32_t maxSceneEnvs = 0;    // largest per-scene list
-  bool warpGeo = false;         // shared-memory warp kernel usable for every scene of the group
-  int warpsPerBlock = 0;
-  int pcap = 0;
-  uint32_t geoGridX = 0;
+  bool warpGeo = false;         // some scene of the group runs on the shared-memory warp kernel
+  bool anyWarpScene = false;
+  bool anyThreadScene = false;  // some scene needs the generic kernel
+  uint32_t numCtas = 0;         // grid of the warp kernel
   size_t geoSmem = 0;
-  size_t slabOffset = 0;
+  WarpPlan* dPlan = nullptr;    // [numScenes]
+  uint2* dCtaMap = nullptr;     // [numCtas] (scene, rank within the scene)
   AStarScratch* fallbackScratch = nullptr;
   float* depth = nullptr;  // [B][H][W] when a render size was configured
   cudaEvent_t done = nullptr;
@@ -246,6 +247,7 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
   d.task = sim->cfg.task;
   d.infoWidth = sim->cfg.task == BPSN_TASK_POINTNAV ? 3u : 1u;
   d.exactHeap = (sim->cfg.flags & BPSN_FLAG_EXACT_HEAP) ? 1u : 0u;
+  d.numScenes = sim->cfg.num_scenes;
   d.explInit = reinterpret_cast<float*>(b + oExplInit);
   d.numCells = reinterpret_cast<uint32_t*>(b + oNumCells);
   d.visited = reinterpret_cast<uint32_t*>(b + oVisited);
@@ -295,52 +297,72 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
                               cudaMemcpyHostToDevice));
     BPSN_CUDA(sim, cudaMemcpy(d.scene, envScene, sizeof(uint32_t) * B, cudaMemcpyHostToDevice));
     g.numScenesUsed = ns;
-    // Shared-memory plan: every scene used by the group must fit next to at
-    // least four warp slabs in one CTA's 227 KB.
-    const size_t kSmemMax = 227 * 1024 - 64;  // 227 KB per CTA minus the kernel's static shared memory
-    size_t maxSceneBytes = 0;
-    int maxPolys = 0;
-    bool anyUsed = false;
+    // Shared-memory plan, scene by scene: a CTA serves one scene with 227 KB of shared
+    // memory = the scene's staged image + as many warp slabs (24 B per polygon + 512 B) as
+    // fit, at most 16.  A scene that leaves no room for a slab goes to the generic kernel.
+    // CTAs are dealt to the scenes in proportion to environments / warps-per-CTA, so that
+    // every scene's list drains in about the same time.
+    const size_t kSmemMax = ((sim->cfg.flags & BPSN_FLAG_SMEM_96K) ? 96 : 227) * 1024 - 64;  // per CTA, minus the kernel's static shared memory
+    std::vector<WarpPlan> plan(ns, WarpPlan{16u, 0u, 0u, 0u});
+    const bool forceGeneric = (sim->cfg.flags & BPSN_FLAG_GENERIC_KERNEL) != 0;
+    double workSum = 0.0;
+    std::vector<double> work(ns, 0.0);
+    g.anyThreadScene = false;
+    g.anyWarpScene = false;
     for (uint32_t s2 = 0; s2 < ns; ++s2) {
       if (!perScene[s2])
         continue;
-      anyUsed = true;
       const HostScene& h = sim->scenes[s2].host;
       const NavScene hv = h.view();
       const size_t sb = stagedLayout(hv.nverts, hv.npolys, hv.ndtris, hv.ndverts).total;
-      if (sb > maxSceneBytes)
-        maxSceneBytes = sb;
-      if (static_cast<int>(h.polys.size()) > maxPolys)
-        maxPolys = static_cast<int>(h.polys.size());
+      const uint32_t pcap = (static_cast<uint32_t>(h.polys.size()) + 15u) / 16u * 16u;
+      const size_t slab = warpGeoSlabBytes(static_cast<int>(pcap));
+      uint32_t w = 0;
+      if (!forceGeneric && h.polys.size() < 65000 && sb + slab <= kSmemMax)
+        w = static_cast<uint32_t>((kSmemMax - sb) / slab);
+      if (w > 16)
+        w = 16;
+      plan[s2].pcap = pcap;
+      plan[s2].slabOffset = static_cast<uint32_t>(sb);
+      plan[s2].warps = w;
+      if (w) {
+        g.anyWarpScene = true;
+        work[s2] = static_cast<double>(perScene[s2]) / w;
+        workSum += work[s2];
+      } else {
+        g.anyThreadScene = true;
+      }
     }
-    g.pcap = (maxPolys + 15) / 16 * 16;
-    const size_t slab = warpGeoSlabBytes(g.pcap);
-    int wpb = 0;
-    if (anyUsed && maxPolys < 65000 && maxSceneBytes + 4 * slab <= kSmemMax)
-      wpb = static_cast<int>((kSmemMax - maxSceneBytes) / slab);
-    if (wpb > 16)
-      wpb = 16;
-    g.warpGeo = wpb >= 4 && !(sim->cfg.flags & BPSN_FLAG_GENERIC_KERNEL);
-    if (g.warpGeo) {
-      g.warpsPerBlock = wpb;
-      g.slabOffset = maxSceneBytes;
-      g.geoSmem = maxSceneBytes + static_cast<size_t>(wpb) * slab;
-      const int blocksPerSm = static_cast<int>(kSmemMax / g.geoSmem) > 0
-                                  ? static_cast<int>(kSmemMax / g.geoSmem) : 1;
+    g.warpGeo = g.anyWarpScene;
+    if (g.anyWarpScene) {
       int sms = 148;
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, sim->cfg.gpu_id);
-      uint32_t gx = (static_cast<uint32_t>(sms * blocksPerSm) + ns - 1) / ns;
-      const uint32_t need = (g.maxSceneEnvs + wpb - 1) / wpb;
-      if (gx > need)
-        gx = need;
-      if (gx == 0)
-        gx = 1;
-      g.geoGridX = gx;
+      std::vector<uint2> ctaMap;
+      for (uint32_t s2 = 0; s2 < ns; ++s2) {
+        if (!plan[s2].warps)
+          continue;
+        uint32_t c = static_cast<uint32_t>(sms * work[s2] / workSum + 0.5);
+        const uint32_t need = (perScene[s2] + plan[s2].warps - 1) / plan[s2].warps;
+        if (c > need)
+          c = need;  // never more warps than environments
+        if (c == 0)
+          c = 1;
+        plan[s2].ctas = c;
+        for (uint32_t r = 0; r < c; ++r)
+          ctaMap.push_back(make_uint2(s2, r));
+      }
+      g.numCtas = static_cast<uint32_t>(ctaMap.size());
+      BPSN_CUDA(sim, cudaMalloc(&g.dCtaMap, sizeof(uint2) * ctaMap.size()));
+      BPSN_CUDA(sim, cudaMemcpy(g.dCtaMap, ctaMap.data(), sizeof(uint2) * ctaMap.size(),
+                                cudaMemcpyHostToDevice));
       BPSN_CUDA(sim, cudaFuncSetAttribute(k_step_warp, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           static_cast<int>(kSmemMax)));
+      g.geoSmem = kSmemMax;
       BPSN_CUDA(sim, cudaMalloc(&g.fallbackScratch,
-                                sizeof(AStarScratch) * static_cast<size_t>(gx) * ns * wpb));
+                                sizeof(AStarScratch) * static_cast<size_t>(g.numCtas) * 16));
     }
+    BPSN_CUDA(sim, cudaMalloc(&g.dPlan, sizeof(WarpPlan) * ns));
+    BPSN_CUDA(sim, cudaMemcpy(g.dPlan, plan.data(), sizeof(WarpPlan) * ns, cudaMemcpyHostToDevice));
   }
 
   auto setField = [&](int id, void* p, size_t bytes) {
@@ -374,7 +396,7 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
     setField(BPSN_FIELD_DEPTH, g.depth, bytes);
   }
 
-  if (!g.warpGeo)  // per-slot A* scratch is only used by the generic (global-memory) kernel
+  if (g.anyThreadScene)  // per-slot A* scratch is only used by the generic (global-memory) kernel
     BPSN_CUDA(sim, cudaMalloc(&g.scratch, sizeof(AStarScratch) * static_cast<size_t>(B)));
   BPSN_CUDA(sim, cudaHostAlloc(&g.hActions, B, cudaHostAllocMapped));
   {
@@ -499,6 +521,8 @@ int32_t bpsn_destroy(bpsn_sim* sim) {
     cudaFree(g.stateBlob);
     cudaFree(g.scratch);
     cudaFree(g.fallbackScratch);
+    cudaFree(g.dPlan);
+    cudaFree(g.dCtaMap);
     cudaFree(g.depth);
     cudaFreeHost(g.hActions);
     cudaFreeHost(g.hOut);
@@ -781,17 +805,21 @@ int32_t bpsn_step_start_ex(bpsn_sim* sim, uint32_t group, const int64_t* actions
   BPSN_CUDA(sim, cudaLaunchKernelEx(&lc, k_pre, gd, sim->table, dAct, dAct8, sim->turn, seedLo,
                                     seedHi));
   if (prof) cudaEventRecord(g.prof[1], s);
-  if (g.warpGeo) {
-    lc.gridDim = dim3(g.geoGridX, g.numScenesUsed);
-    lc.blockDim = dim3(g.warpsPerBlock * 32);
+  if (g.anyWarpScene) {
+    lc.gridDim = dim3(g.numCtas);
+    lc.blockDim = dim3(512);
     lc.dynamicSmemBytes = g.geoSmem;
-    BPSN_CUDA(sim, cudaLaunchKernelEx(&lc, k_step_warp, gd, sim->table, g.pcap, g.slabOffset,
-                                      g.fallbackScratch, seedLo, seedHi));
-  } else {
+    BPSN_CUDA(sim, cudaLaunchKernelEx(&lc, k_step_warp, gd, sim->table,
+                                      static_cast<const WarpPlan*>(g.dPlan),
+                                      static_cast<const uint2*>(g.dCtaMap), g.fallbackScratch,
+                                      seedLo, seedHi));
+  }
+  if (g.anyThreadScene) {  // scenes too large for shared memory (it skips the others)
     lc.gridDim = dim3(blocksFor(g.maxSceneEnvs, 128), g.numScenesUsed);
     lc.blockDim = dim3(128);
     lc.dynamicSmemBytes = 0;
-    BPSN_CUDA(sim, cudaLaunchKernelEx(&lc, k_step_thread, gd, sim->table, g.scratch, seedLo,
+    BPSN_CUDA(sim, cudaLaunchKernelEx(&lc, k_step_thread, gd, sim->table,
+                                      static_cast<const WarpPlan*>(g.dPlan), g.scratch, seedLo,
                                       seedHi));
   }
   if (prof) cudaEventRecord(g.prof[2], s);

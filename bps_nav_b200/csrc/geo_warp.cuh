@@ -1196,16 +1196,22 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
 // One simulator step for the environments listed per scene (see sim_kernels.cuh
 // for the phase split): forward move, GPS/compass, geodesic goal -> agent,
 // info / reward / mask and the in-loop reset.
-//   grid  = (blocksPerScene, numScenes), block = warpsPerBlock * 32 threads
-//   smem  = staged tables of blockIdx.y's scene + warpsPerBlock slabs
+//   grid  = CTAs of all scenes (ctaMap says which scene a CTA serves), block = 512 threads
+//   smem  = staged tables of the CTA's scene + as many warp slabs as fit (plan[scene].warps)
 // Warps pull list slots from a per-scene cursor until the list is drained.
 __global__ void __launch_bounds__(512, 1)
-k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
-            AStarScratch* __restrict__ fallbackScratch, uint32_t seedLo, uint32_t seedHi) {
+k_step_warp(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
+            const uint2* __restrict__ ctaMap, AStarScratch* __restrict__ fallbackScratch,
+            uint32_t seedLo, uint32_t seedHi) {
   extern __shared__ __align__(16) uint8_t smem[];
   launchDependents();
-  const int sceneIdx = blockIdx.y;
-  const int warpsPerBlock = blockDim.x >> 5;
+  // which scene this CTA serves and its number among that scene's CTAs (set-up data)
+  const uint2 cm = ctaMap[blockIdx.x];
+  const int sceneIdx = static_cast<int>(cm.x);
+  const uint32_t rank = cm.y;
+  const WarpPlan pl = plan[sceneIdx];
+  const int pcap = static_cast<int>(pl.pcap);
+  const int warpsPerBlock = static_cast<int>(pl.warps);  // warps of this CTA that take queries
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
@@ -1241,9 +1247,9 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
     // before this one is still at work; everything below reads what it wrote.
     waitForPredecessor();
     n = g.counts[sceneIdx];
-    if (blockIdx.x == 0 && threadIdx.x == 0) {  // the next step starts from empty lists
+    if (rank == 0 && threadIdx.x == 0) {  // the next step starts from empty lists
       g.countsNext[sceneIdx] = 0u;
-      g.countsNext[gridDim.y + sceneIdx] = 0u;
+      g.countsNext[g.numScenes + sceneIdx] = 0u;
     }
     // bounded wait on phase 0 of the barrier; a copy of this size lands within
     // microseconds, the bound is ~1 s of polling
@@ -1267,7 +1273,7 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
       return;
     }
   }
-  if (static_cast<uint32_t>(blockIdx.x) * warpsPerBlock >= n)
+  if (rank * static_cast<uint32_t>(warpsPerBlock) >= n || warp >= warpsPerBlock)
     return;  // (only after the copy has landed: it targets this CTA's shared memory)
   sc.verts = reinterpret_cast<const float*>(smem + lay.verts);
   sc.vstride = 4;
@@ -1293,16 +1299,16 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
   sv.npolys = sc.npolys;
   sv.polyMask = sc.polyMask;
   sv.refBase = sc.refBase;
-  uint8_t* slabBase = smem + slabOffset + static_cast<size_t>(warp) * warpGeoSlabBytes(pcap);
+  uint8_t* slabBase = smem + pl.slabOffset + static_cast<size_t>(warp) * warpGeoSlabBytes(pcap);
   const WarpSlab w = carveSlab(slabBase, pcap);
 
   const uint32_t B = g.B;
   const uint32_t base = g.listBase[sceneIdx];
-  uint32_t* cursor = g.counts + gridDim.y + sceneIdx;  // zeroed by the step before
+  uint32_t* cursor = g.counts + g.numScenes + sceneIdx;  // zeroed by the step before
   // Every warp starts on the list slot of its own number; the slots beyond the number of
   // warps in the grid are handed out through the cursor.
-  const uint32_t gridWarps = gridDim.x * static_cast<uint32_t>(warpsPerBlock);
-  uint32_t q = blockIdx.x * static_cast<uint32_t>(warpsPerBlock) + static_cast<uint32_t>(warp);
+  const uint32_t gridWarps = pl.ctas * static_cast<uint32_t>(warpsPerBlock);
+  uint32_t q = rank * static_cast<uint32_t>(warpsPerBlock) + static_cast<uint32_t>(warp);
   for (bool first = true;; first = false) {
     if (!first) {
       if (lane == 0)
@@ -1347,8 +1353,7 @@ k_step_warp(GroupDev g, SceneTable st, int pcap, size_t slabOffset,
     if (lane == 0) {
       if (fallback) {
         status = 0;
-        const size_t slot = static_cast<size_t>(blockIdx.y) * gridDim.x * warpsPerBlock +
-                            static_cast<size_t>(blockIdx.x) * warpsPerBlock + warp;
+        const size_t slot = static_cast<size_t>(blockIdx.x) * (blockDim.x >> 5) + warp;
         d = geodesic(scGlobal, fallbackScratch + slot, b, bref, a, aref, &status);
         status |= fallback;
       }

@@ -60,6 +60,7 @@ struct GroupDev {
   uint32_t task;       // Task
   uint32_t infoWidth;  // floats per env in `info`: 3 (PointNav) or 1 (Flee, Exploration)
   uint32_t exactHeap;  // test switch: every warp search uses the slab heap (geo_warp.cuh)
+  uint32_t numScenes;  // scenes of the simulator (length of the per-scene tables)
   // pose / task state, each [B] (vectors are component-major: x[B] y[B] z[B])
   float* pos;      // [3][B]  position_
   float* rot;      // [4][B]  rotation_ (x y z w)
@@ -137,6 +138,17 @@ __device__ __forceinline__ void launchDependents() {
 __device__ __forceinline__ void waitForPredecessor() {
   asm volatile("griddepcontrol.wait;" ::: "memory");
 }
+
+// How the step kernels divide a group's scenes between them.  A scene whose staged
+// image leaves room for at least one warp slab in a CTA's shared memory is handled by
+// the warp kernel with `warps` active warps per CTA on `ctas` CTAs; warps == 0 sends the
+// scene's environments to the one-thread-per-environment kernel.
+struct WarpPlan {
+  uint32_t pcap;        // polygon capacity of a slab of this scene (multiple of 16)
+  uint32_t slabOffset;  // bytes from the start of dynamic shared memory to the first slab
+  uint32_t warps;
+  uint32_t ctas;
+};
 
 struct TurnConsts {  // +/-10 degrees about +Y, evaluated once on the host
   float lx, ly, lz, lw;
@@ -490,16 +502,18 @@ k_pre(GroupDev g, SceneTable st, const int64_t* __restrict__ actions,
 // memory (grid.y = scene).  Used when a scene does not fit the shared-memory
 // kernel of geo_warp.cuh.
 __global__ void __launch_bounds__(128)
-k_step_thread(GroupDev g, SceneTable st, AStarScratch* __restrict__ scratch, uint32_t seedLo,
-              uint32_t seedHi) {
+k_step_thread(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
+              AStarScratch* __restrict__ scratch, uint32_t seedLo, uint32_t seedHi) {
   launchDependents();
+  const uint32_t sceneIdx = blockIdx.y;
+  if (plan && plan[sceneIdx].warps != 0)
+    return;  // the warp kernel has this scene
   waitForPredecessor();
   const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
-  const uint32_t sceneIdx = blockIdx.y;
   const uint32_t n = g.counts[sceneIdx];
   if (t == 0) {  // the next step starts from empty lists
     g.countsNext[sceneIdx] = 0u;
-    g.countsNext[gridDim.y + sceneIdx] = 0u;
+    g.countsNext[g.numScenes + sceneIdx] = 0u;
   }
   if (t >= n)
     return;

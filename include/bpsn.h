@@ -92,7 +92,11 @@ enum {
   /* warp kernel only: run every A* search with the reference's binary heap kept
      in shared memory, the path otherwise taken only when the register open list
      cannot decide the pop order (a tie for the minimum) -- for testing that path */
-  BPSN_FLAG_EXACT_HEAP = 1u << 2
+  BPSN_FLAG_EXACT_HEAP = 1u << 2,
+  /* plan the step kernels as if a CTA had 96 KB of shared memory instead of 227 KB:
+     medium-sized scenes then go to the generic kernel while small ones stay on the
+     warp kernel -- for testing groups that need both kernels in one step */
+  BPSN_FLAG_SMEM_96K = 1u << 3
 };
 
 /* Fields addressable through bpsn_get_ptr.  All arrays are indexed by the

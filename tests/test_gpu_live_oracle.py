@@ -102,6 +102,13 @@ def test_exact_heap_search_matches_oracle():
     _compare_run(["m03", "m07"], 512, 128, seed=24, mix="policy", exact_heap=True)
 
 
+def test_warp_and_generic_kernels_in_one_step():
+    # with the shared-memory budget cut to 96 KB the larger scenes (m04: 1304 polygons, m07, m01)
+    # run on the generic kernel and the small ones on the warp kernel, in the same group and step
+    _compare_run(["m04", "m13", "m07", "m15", "m01", "c0"], 1536, 64, seed=41, mix="uniform",
+                 small_smem=True)
+
+
 def test_double_buffered_groups():
     _compare_run(["c0", "m15", "m13", "m14"], 256, 64, seed=3, mix="uniform", double_buffered=True)
 
