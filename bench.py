@@ -192,11 +192,10 @@ def cpu_arm(args, seconds, steps_cap=None):
     from oracle import pyoracle
     if not pyoracle.available():
         raise RuntimeError("oracle libraries missing (oracle/_ref, oracle/_build)")
-    nav, epf = scene_files(args.scene)
-    eps = np.load(epf)
+    scene_list = [(scene_files(nm)[0], np.load(scene_files(nm)[1])) for nm in args.scene.split(",")]
     cores = len(os.sched_getaffinity(0))
     n = args.envs
-    sim = pyoracle.OracleSim([(nav, eps)], n, seed=1, threads=cores)
+    sim = pyoracle.OracleSim(scene_list, n, seed=1, threads=cores)
     sim.reset()
     chunk = T_ROLLOUT
     rewards = np.zeros((T_ROLLOUT + 1, n), np.float32)
@@ -237,7 +236,7 @@ def cpu_microbench(args, seconds=3.0):
     """One-core rate of the same CPU simulator and microseconds per navmesh query of the
     reference's compiled PathFinder (tryStep, findPath) on the bench scene's episodes."""
     from oracle import pyoracle
-    nav, epf = scene_files(args.scene)
+    nav, epf = scene_files(args.scene.split(",")[0])
     eps = np.load(epf)
     n = min(args.envs, 1024)
     sim = pyoracle.OracleSim([(nav, eps)], n, seed=1, threads=1)
@@ -334,8 +333,11 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    nav, epf = scene_files(args.scene)
-    scene = Scene(nav, np.load(epf), f"{args.scene}.glb")
+    names = args.scene.split(",")
+    scenes = [Scene(scene_files(nm)[0], np.load(scene_files(nm)[1]), f"{nm}.glb") for nm in names]
+    scene = scenes[0]
+    if args.envs % len(scenes):
+        raise SystemExit("--envs must be a multiple of the number of scenes")
     N, T, K, W = args.envs, T_ROLLOUT, args.steps, max(args.warmup, 3)
 
     def barrier():
@@ -355,10 +357,11 @@ def run_ours(args):
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
 
     # ---------------- device-resident arm
-    gen = bps_sim.PointNavRolloutGenerator.from_scenes([scene], N, gpu_id=local,
+    gen = bps_sim.PointNavRolloutGenerator.from_scenes(scenes, N, gpu_id=local,
                                                        seed=dist_utils.shard_seed(1000, rank, N),
                                                        host_mirrors=False)
     info = gen.scene_info(0)
+    polys = [gen.scene_info(i)["num_polys"] for i in range(len(scenes))]
     gen.reset(0)
     acts = torch.from_numpy(draw_actions(((W + K) * T, N), args.mix, 7 + rank)).to(dev)
     r_view = gen.tensor(0, "reward")
@@ -452,7 +455,7 @@ def run_ours(args):
     if not args.no_large_batch and N < LARGE_BATCH_ENVS:
         NB, KB = LARGE_BATCH_ENVS, 3
         genb = bps_sim.PointNavRolloutGenerator.from_scenes(
-            [scene], NB, gpu_id=local, seed=dist_utils.shard_seed(2000, rank, NB),
+            scenes, NB, gpu_id=local, seed=dist_utils.shard_seed(2000, rank, NB),
             host_mirrors=False)
         genb.reset(0)
         actsb = torch.from_numpy(draw_actions(((1 + KB) * T, NB), args.mix, 11 + rank)).to(dev)
@@ -489,7 +492,7 @@ def run_ours(args):
     if not args.no_depth and scene.floor is not None:
         RW, RH = 64, 64
         gend = bps_sim.PointNavRolloutGenerator.from_scenes(
-            [scene], N, gpu_id=local, seed=dist_utils.shard_seed(3000, rank, N),
+            scenes, N, gpu_id=local, seed=dist_utils.shard_seed(3000, rank, N),
             host_mirrors=False, depth=True, render_resolution=(RW, RH))
         gend.reset(0)
         for t in range(8):
@@ -503,7 +506,7 @@ def run_ours(args):
         d1.record()
         torch.cuda.synchronize()
         d_ms = max_over_ranks(d0.elapsed_time(d1)) / reps
-        nbox = len(scene.boxes)
+        nbox = int(np.mean([len(sc.boxes) for sc in scenes]))
         depth_info = {"resolution": [RW, RH], "boxes": nbox, "ms_per_render": d_ms,
                       "rays_per_s": world * N * RW * RH / (d_ms * 1e-3),
                       "ray_box_tests_per_s": world * N * RW * RH * nbox / (d_ms * 1e-3),
@@ -515,7 +518,7 @@ def run_ours(args):
     # ---------------- end-to-end arm through the reference-shaped host API
     e2e = None
     if not args.no_e2e:
-        gen2 = bps_sim.PointNavRolloutGenerator.from_scenes([scene], N, gpu_id=local,
+        gen2 = bps_sim.PointNavRolloutGenerator.from_scenes(scenes, N, gpu_id=local,
                                                            seed=dist_utils.shard_seed(1000, rank, N),
                                                            host_mirrors=True)
         gen2.reset(0)
@@ -603,8 +606,11 @@ def run_ours(args):
             "metric": "env_steps_per_sec", "value": value, "unit": "env-steps/s", "n_gpus": world,
             "steps": K, "warmup": W, "ms_per_step": dev_ms / K, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"config1: scene {args.scene} ({info['num_polys']} polys, "
-                                   f"{info['num_islands']} islands), {N} envs/GPU, one step = "
+            "config": {"workload": (f"config1: scene {args.scene} ({info['num_polys']} polys, "
+                                    f"{info['num_islands']} islands)" if len(scenes) == 1 else
+                                    f"{len(scenes)} scenes {args.scene} "
+                                    f"({min(polys)}-{max(polys)} polys)") +
+                                   f", {N} envs/GPU, one step = "
                                    f"T={T} sim steps + fused GAE/normalise, {args.mix} actions",
                        "envs_per_gpu": N, "rollout_T": T, "polys": info["num_polys"],
                        "l2": f"flushed between timed windows ({L2_FLUSH_BYTES >> 20} MiB write)",
