@@ -200,21 +200,9 @@ class _RolloutGenerator:
         float32 / 1-byte elements that also receive this step's reward and mask, e.g.
         ``rollouts.rewards[t]`` and ``rollouts.masks[t + 1]``; ``polar_out``: CUDA float32
         ``[B, 2]`` that also receives the GPS/compass observation (``observations[t + 1]``)."""
-        po = polar_out.data_ptr() if polar_out is not None else None
-        if polar_out is not None and (polar_out.numel() != 2 * self.envs_per_group or
-                                      polar_out.element_size() != 4 or
-                                      not polar_out.is_contiguous() or not polar_out.is_cuda):
-            raise RuntimeError("polar_out must be a contiguous CUDA float32 tensor of B x 2")
-        ro = reward_out.data_ptr() if reward_out is not None else None
-        mo = mask_out.data_ptr() if mask_out is not None else None
-        if reward_out is not None and (reward_out.numel() != self.envs_per_group or
-                                       reward_out.element_size() != 4 or
-                                       not reward_out.is_contiguous() or not reward_out.is_cuda):
-            raise RuntimeError("reward_out must be a contiguous CUDA float32 tensor of B elements")
-        if mask_out is not None and (mask_out.numel() != self.envs_per_group or
-                                     mask_out.element_size() != 1 or
-                                     not mask_out.is_contiguous() or not mask_out.is_cuda):
-            raise RuntimeError("mask_out must be a contiguous CUDA 1-byte tensor of B elements")
+        ro = mo = po = None
+        if reward_out is not None or mask_out is not None or polar_out is not None:
+            ro, mo, po = self._out_ptrs(reward_out, mask_out, polar_out)
         if isinstance(actions, np.ndarray):
             if actions.dtype != np.int64 or not actions.flags.c_contiguous:
                 actions = np.ascontiguousarray(actions, dtype=np.int64)
@@ -232,10 +220,26 @@ class _RolloutGenerator:
                                    "int64 tensor")
             if actions.numel() != self.envs_per_group:
                 raise RuntimeError("actions length must equal the number of envs in the group")
-            self._keepalive = [actions]
+            self._keepalive = [actions, reward_out, mask_out, polar_out]
             L.check(self._lib.bpsn_step_start_ex(self._h, group_idx, actions.data_ptr(),
                                                  L.MEM_DEVICE, self._stream(), ro, mo, po), self._h)
         self._num_steps_taken += self.envs_per_group
+
+    def _out_ptrs(self, reward_out, mask_out, polar_out):
+        B = self.envs_per_group
+        po = polar_out.data_ptr() if polar_out is not None else None
+        if polar_out is not None and (polar_out.numel() != 2 * B or polar_out.element_size() != 4 or
+                                      not polar_out.is_contiguous() or not polar_out.is_cuda):
+            raise RuntimeError("polar_out must be a contiguous CUDA float32 tensor of B x 2")
+        ro = reward_out.data_ptr() if reward_out is not None else None
+        mo = mask_out.data_ptr() if mask_out is not None else None
+        if reward_out is not None and (reward_out.numel() != B or reward_out.element_size() != 4 or
+                                       not reward_out.is_contiguous() or not reward_out.is_cuda):
+            raise RuntimeError("reward_out must be a contiguous CUDA float32 tensor of B elements")
+        if mask_out is not None and (mask_out.numel() != B or mask_out.element_size() != 1 or
+                                     not mask_out.is_contiguous() or not mask_out.is_cuda):
+            raise RuntimeError("mask_out must be a contiguous CUDA 1-byte tensor of B elements")
+        return ro, mo, po
 
     def step_end(self, group_idx):
         L.check(self._lib.bpsn_step_end(self._h, group_idx), self._h)

@@ -759,18 +759,24 @@ int32_t bpsn_step_start_ex(bpsn_sim* sim, uint32_t group, const int64_t* actions
   const int64_t* dAct = actions;
   const uint8_t* dAct8 = nullptr;
   if (actions_mem == BPSN_MEM_HOST) {
-    for (uint32_t i = 0; i < B; ++i) {
-      const int64_t a = actions[i];
-      if (a < 0 || a > 3)
-        return fail(sim, BPSN_ERR_BAD_ACTION, "Unknown action: " + std::to_string(a));
-    }
     // The staging buffer is read in place by the kernel of this step; without host
     // mirrors step_end does not wait for the device, so make sure the previous step
     // is through with the buffer before overwriting it.
     if (!(sim->cfg.flags & BPSN_FLAG_HOST_MIRRORS))
       BPSN_CUDA(sim, cudaEventSynchronize(g.done));
-    for (uint32_t i = 0; i < B; ++i)
-      g.hActions[i] = static_cast<uint8_t>(actions[i]);
+    // one pass: narrow and validate (a bad action leaves the buffer half written, which
+    // is harmless: nothing is launched)
+    uint64_t bad = 0;
+    for (uint32_t i = 0; i < B; ++i) {
+      const uint64_t a = static_cast<uint64_t>(actions[i]);
+      bad |= a;
+      g.hActions[i] = static_cast<uint8_t>(a);
+    }
+    if (bad > 3) {
+      for (uint32_t i = 0; i < B; ++i)
+        if (actions[i] < 0 || actions[i] > 3)
+          return fail(sim, BPSN_ERR_BAD_ACTION, "Unknown action: " + std::to_string(actions[i]));
+    }
     dAct = nullptr;
     dAct8 = g.dActions8;
   } else if (actions_mem != BPSN_MEM_DEVICE) {
