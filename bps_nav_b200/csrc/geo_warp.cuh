@@ -8,26 +8,31 @@
 // over the 32 lanes and every table it touches held on chip:
 //
 //   * the scene's vertex (padded to 16 bytes each), polygon, detail-mesh and
-//     island tables are copied once per CTA into shared memory (plain loads and
-//     stores; no multicast).  In the staged polygon table links to neighbours
-//     the query filter rejects are cleared: for the search they do not exist
-//     and for moveAlongSurface they are walls either way
+//     island tables are copied once per CTA into shared memory with one bulk
+//     asynchronous copy of an image laid out for it at set-up (this CTA's own
+//     shared memory; no multicast).  In the staged polygon table links to
+//     neighbours the query filter rejects are cleared: for the search they do
+//     not exist and for moveAlongSurface they are walls either way
 //     (DetourNavMeshQuery.cpp:2118-2132);
+//   * the forward move (moveAlongSurface, getPolyHeight) takes one lane per edge
+//     of the polygon at the head of its queue and 32 detail triangles at a time;
 //   * A* nodes are direct-mapped, one slot per polygon (a single tile has one
 //     search node per polygon: dtNavMeshQuery::findPath only creates extra
 //     nodes per polygon for tile-border links, DetourNavMeshQuery.cpp:1040-1045)
 //     in the warp's private shared-memory slab;
 //   * the open list lives in registers, three (total, polygon) entries per lane;
-//     "pop" is one hardware warp min-reduction.  A binary heap and an arg-min
-//     return the same node whenever the minimum `total` is unique.  When two
-//     open nodes tie for the minimum the result would depend on the reference
-//     heap's internal order (dtNodeQueue, Detour/Source/DetourNode.cpp:172-200),
-//     so the warp abandons the fast path and lane 0 reruns the query with the
-//     exact sequential emulation (geodesic()) on a global-memory scratch slab.
+//     "pop" is three hardware warp reductions (minimum total, how many entries
+//     hold it, the holder's polygon).  A binary heap and an arg-min return the
+//     same node whenever the minimum `total` is unique.  When two live entries
+//     tie for the minimum the result depends on the reference heap's internal
+//     order (dtNodeQueue, Detour/Source/DetourNode.cpp:172-200), so the search
+//     is redone with that heap itself, kept in the slab (astarExactSlab); only
+//     if the heap outgrows the slab does lane 0 rerun the query with the
+//     one-thread emulation (geodesic()) on a global-memory scratch slab.
 //     An open node that gets a better total (dtNodeQueue::modify) is not
 //     updated in place: a second entry is added and the superseded one is
 //     discarded when it is popped (its total no longer matches the node's).
-//     The same fallback is taken if a lane runs out of entries (96 in all);
+//     The exact search is also taken if a lane runs out of entries (96 in all);
 //   * the up-to-six neighbours of the popped polygon are evaluated by six
 //     lanes at once (portal midpoint, cost, heuristic, skip test, node update).
 //     Two edges leading to the same neighbour produce bit-identical
