@@ -61,6 +61,8 @@ struct Group {
   uint32_t numCtas = 0;         // grid of the warp kernel
   size_t geoSmem = 0;
   WarpPlan* dPlan = nullptr;    // [numScenes]
+  uint8_t* globalSlabs = nullptr;  // warp slabs of the scenes that are worked on in global memory
+  size_t globalSlabStride = 0;     // bytes between consecutive slabs there (the largest scene's)
   uint2* dCtaMap = nullptr;     // [numCtas] (scene, rank within the scene)
   AStarScratch* fallbackScratch = nullptr;
   float* depth = nullptr;  // [B][H][W] when a render size was configured
@@ -304,6 +306,15 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
     // every scene's list drains in about the same time.
     const size_t kSmemMax = ((sim->cfg.flags & BPSN_FLAG_SMEM_96K) ? 96 : 227) * 1024 - 64;  // per CTA, minus the kernel's static shared memory
     std::vector<WarpPlan> plan(ns, WarpPlan{16u, 0u, 0u, 0u});
+    size_t maxGlobalSlab = 0;
+#ifndef BPSN_GLOBAL_WARP_SPEED
+#define BPSN_GLOBAL_WARP_SPEED 0.6
+#endif
+    const double kGlobalWarpSpeed = BPSN_GLOBAL_WARP_SPEED;  // queries per unit time of a warp in global memory
+                                          // relative to one in shared memory (measured)
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, sim->cfg.gpu_id);
+    const bool throughputBound = B / 2 > 2u * static_cast<uint32_t>(sms) * 16u;
     const bool forceGeneric = (sim->cfg.flags & BPSN_FLAG_GENERIC_KERNEL) != 0;
     double workSum = 0.0;
     std::vector<double> work(ns, 0.0);
@@ -324,10 +335,26 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
         w = 16;
       plan[s2].pcap = pcap;
       plan[s2].slabOffset = static_cast<uint32_t>(sb);
+      // A scene that leaves no room for a slab is worked on in global memory (tables and
+      // slabs L2-resident, all 16 warps of the CTA active).  So is one that leaves room for
+      // fewer than 8 slabs when the group has more queries per step than two rounds of
+      // every warp of the GPU: then throughput counts, and 16 warps at L2 latency get
+      // through more queries than a few warps at shared-memory latency (measured on 16
+      // scenes of 91-1304 polygons: 105 against 90 M env-steps/s at 16384 envs); with fewer
+      // queries the step lasts as long as its slowest query, which shared memory shortens.
+      const uint32_t kMinSmemWarps = throughputBound ? 8u : 1u;
+      if (!forceGeneric && h.polys.size() < 65000 && w < kMinSmemWarps) {
+        w = 16;
+        plan[s2].slabOffset = kSlabInGlobal;
+        if (slab > maxGlobalSlab)
+          maxGlobalSlab = slab;
+      }
       plan[s2].warps = w;
       if (w) {
         g.anyWarpScene = true;
-        work[s2] = static_cast<double>(perScene[s2]) / w;
+        // a warp working in global memory gets through its queries more slowly
+        const double speed = plan[s2].slabOffset == kSlabInGlobal ? kGlobalWarpSpeed : 1.0;
+        work[s2] = static_cast<double>(perScene[s2]) / (w * speed);
         workSum += work[s2];
       } else {
         g.anyThreadScene = true;
@@ -335,8 +362,6 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
     }
     g.warpGeo = g.anyWarpScene;
     if (g.anyWarpScene) {
-      int sms = 148;
-      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, sim->cfg.gpu_id);
       std::vector<uint2> ctaMap;
       for (uint32_t s2 = 0; s2 < ns; ++s2) {
         if (!plan[s2].warps)
@@ -360,6 +385,9 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
       g.geoSmem = kSmemMax;
       BPSN_CUDA(sim, cudaMalloc(&g.fallbackScratch,
                                 sizeof(AStarScratch) * static_cast<size_t>(g.numCtas) * 16));
+      g.globalSlabStride = maxGlobalSlab;
+      if (maxGlobalSlab)
+        BPSN_CUDA(sim, cudaMalloc(&g.globalSlabs, maxGlobalSlab * g.numCtas * 16));
     }
     BPSN_CUDA(sim, cudaMalloc(&g.dPlan, sizeof(WarpPlan) * ns));
     BPSN_CUDA(sim, cudaMemcpy(g.dPlan, plan.data(), sizeof(WarpPlan) * ns, cudaMemcpyHostToDevice));
@@ -522,6 +550,7 @@ int32_t bpsn_destroy(bpsn_sim* sim) {
     cudaFree(g.scratch);
     cudaFree(g.fallbackScratch);
     cudaFree(g.dPlan);
+    cudaFree(g.globalSlabs);
     cudaFree(g.dCtaMap);
     cudaFree(g.depth);
     cudaFreeHost(g.hActions);
@@ -818,7 +847,7 @@ int32_t bpsn_step_start_ex(bpsn_sim* sim, uint32_t group, const int64_t* actions
     BPSN_CUDA(sim, cudaLaunchKernelEx(&lc, k_step_warp, gd, sim->table,
                                       static_cast<const WarpPlan*>(g.dPlan),
                                       static_cast<const uint2*>(g.dCtaMap), g.fallbackScratch,
-                                      seedLo, seedHi));
+                                      g.globalSlabs, g.globalSlabStride, seedLo, seedHi));
   }
   if (g.anyThreadScene) {  // scenes too large for shared memory (it skips the others)
     lc.gridDim = dim3(blocksFor(g.maxSceneEnvs, 128), g.numScenesUsed);

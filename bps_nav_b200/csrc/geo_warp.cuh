@@ -1198,95 +1198,36 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
   return dres;
 }
 
-// One simulator step for the environments listed per scene (see sim_kernels.cuh
-// for the phase split): forward move, GPS/compass, geodesic goal -> agent,
-// info / reward / mask and the in-loop reset.
-//   grid  = CTAs of all scenes (ctaMap says which scene a CTA serves), block = 512 threads
-//   smem  = staged tables of the CTA's scene + as many warp slabs as fit (plan[scene].warps)
-// Warps pull list slots from a per-scene cursor until the list is drained.
-__global__ void __launch_bounds__(512, 1)
-k_step_warp(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
-            const uint2* __restrict__ ctaMap, AStarScratch* __restrict__ fallbackScratch,
-            uint32_t seedLo, uint32_t seedHi) {
+// The part of k_step_warp after the scene is in place: the warp's loop over list slots.
+// Two instances: tables and slabs in shared memory (the pointers are then known to be
+// shared-memory addresses and the accesses compile to shared-memory instructions) or in
+// global memory.
+template <bool kGlobal>
+__device__ __forceinline__ void stepWarpQueries(const GroupDev& g, const SceneTable& st,
+                                                const WarpPlan pl, int sceneIdx, uint32_t rank,
+                                                uint32_t n, const NavScene& scGlobal,
+                                                uint8_t* globalSlabs, size_t globalSlabStride,
+                                                AStarScratch* fallbackScratch, uint32_t seedLo,
+                                                uint32_t seedHi
+#if defined(BPSN_PHASE_TIMING)
+                                                , long long tS0
+#endif
+) {
   extern __shared__ __align__(16) uint8_t smem[];
-  launchDependents();
-  // which scene this CTA serves and its number among that scene's CTAs (set-up data)
-  const uint2 cm = ctaMap[blockIdx.x];
-  const int sceneIdx = static_cast<int>(cm.x);
-  const uint32_t rank = cm.y;
-  const WarpPlan pl = plan[sceneIdx];
   const int pcap = static_cast<int>(pl.pcap);
-  const int warpsPerBlock = static_cast<int>(pl.warps);  // warps of this CTA that take queries
+  const int warpsPerBlock = static_cast<int>(pl.warps);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-
-  BPSN_TICK(tS0);
-  uint32_t n = 0;
-  const NavScene scGlobal = st.scenes[sceneIdx];
   NavScene sc = scGlobal;
   const StagedLayout lay = stagedLayout(sc.nverts, sc.npolys, sc.ndtris, sc.ndverts);
-  {
-    // The image was laid out at set-up exactly as stagedLayout() describes (float4
-    // vertices, polygons with filtered links and the duplicate-neighbour flag, detail
-    // bases / triangles / vertices, island ids), 16-byte aligned and a multiple of 16
-    // bytes long: one bulk asynchronous copy (TMA, untiled, this CTA's own shared
-    // memory, no multicast) brings it in and signals an mbarrier.
-    __shared__ __align__(8) unsigned long long stageBar;
-    const uint32_t bar = static_cast<uint32_t>(__cvta_generic_to_shared(&stageBar));
-    const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
-    const uint32_t bytes = scGlobal.stagedBytes;
-    if (threadIdx.x == 0) {
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar) : "memory");
-      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-                   : "memory");
-      asm volatile(
-          "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-          ::"r"(dst), "l"(scGlobal.staged), "r"(bytes), "r"(bar)
-          : "memory");
-    }
-    // The scene image never changes, so the copy above may run while the kernel
-    // before this one is still at work; everything below reads what it wrote.
-    waitForPredecessor();
-    n = g.counts[sceneIdx];
-    if (rank == 0 && threadIdx.x == 0) {  // the next step starts from empty lists
-      g.countsNext[sceneIdx] = 0u;
-      g.countsNext[g.numScenes + sceneIdx] = 0u;
-    }
-    // bounded wait on phase 0 of the barrier; a copy of this size lands within
-    // microseconds, the bound is ~1 s of polling
-    bool landed = false;
-    for (int it = 0; it < (1 << 22) && !landed; ++it) {
-      uint32_t ok;
-      asm volatile(
-          "{\n\t.reg .pred p;\n\t"
-          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\t"
-          "selp.u32 %0, 1, 0, p;\n\t}"
-          : "=r"(ok)
-          : "r"(bar)
-          : "memory");
-      landed = ok != 0;
-    }
-    if (!__syncthreads_and(landed ? 1 : 0)) {
-      // never observed; leave without touching the half-filled tables (the step's
-      // listed envs keep their previous outputs) and make the failure visible
-      if (threadIdx.x == 0)
-        atomicOr(g.errFlags, 1u);
-      return;
-    }
-  }
-  if (rank * static_cast<uint32_t>(warpsPerBlock) >= n || warp >= warpsPerBlock)
-    return;  // (only after the copy has landed: it targets this CTA's shared memory)
-  sc.verts = reinterpret_cast<const float*>(smem + lay.verts);
+  const uint8_t* tables = kGlobal ? scGlobal.staged : smem;
+  sc.verts = reinterpret_cast<const float*>(tables + lay.verts);
   sc.vstride = 4;
-  sc.polys = reinterpret_cast<const NavPoly*>(smem + lay.polys);
-  sc.detail = reinterpret_cast<const NavDetail*>(smem + lay.detail);
-  sc.dtris = smem + lay.dtris;
-  sc.dverts = reinterpret_cast<const float*>(smem + lay.dverts);
-  sc.island = reinterpret_cast<const int32_t*>(smem + lay.island);
+  sc.polys = reinterpret_cast<const NavPoly*>(tables + lay.polys);
+  sc.detail = reinterpret_cast<const NavDetail*>(tables + lay.detail);
+  sc.dtris = tables + lay.dtris;
+  sc.dverts = reinterpret_cast<const float*>(tables + lay.dverts);
+  sc.island = reinterpret_cast<const int32_t*>(tables + lay.island);
   BPSN_TICK(tS1);
 #if defined(BPSN_PHASE_TIMING)
   PhaseAcc paccStore = {};
@@ -1304,7 +1245,11 @@ k_step_warp(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
   sv.npolys = sc.npolys;
   sv.polyMask = sc.polyMask;
   sv.refBase = sc.refBase;
-  uint8_t* slabBase = smem + pl.slabOffset + static_cast<size_t>(warp) * warpGeoSlabBytes(pcap);
+  // (global memory: one stride for all scenes, slabs of different sizes must not overlap)
+  uint8_t* slabBase =
+      kGlobal ? globalSlabs + (static_cast<size_t>(blockIdx.x) * (blockDim.x >> 5) + warp) *
+                                  globalSlabStride
+              : smem + pl.slabOffset + static_cast<size_t>(warp) * warpGeoSlabBytes(pcap);
   const WarpSlab w = carveSlab(slabBase, pcap);
 
   const uint32_t B = g.B;
@@ -1403,6 +1348,113 @@ k_step_warp(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
     atomicAdd(&g_phaseCycles[15], pacc->exMath);
     atomicAdd(&g_phaseCycles[16], pacc->exBook);
   }
+#endif
+}
+
+// One simulator step for the environments listed per scene (see sim_kernels.cuh
+// for the phase split): forward move, GPS/compass, geodesic goal -> agent,
+// info / reward / mask and the in-loop reset.
+//   grid  = CTAs of all scenes (ctaMap says which scene a CTA serves), block = 512 threads
+//   smem  = staged tables of the CTA's scene + as many warp slabs as fit (plan[scene].warps)
+// Warps pull list slots from a per-scene cursor until the list is drained.
+__global__ void __launch_bounds__(512, 1)
+k_step_warp(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
+            const uint2* __restrict__ ctaMap, AStarScratch* __restrict__ fallbackScratch,
+            uint8_t* __restrict__ globalSlabs, size_t globalSlabStride, uint32_t seedLo,
+            uint32_t seedHi) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  launchDependents();
+  // which scene this CTA serves and its number among that scene's CTAs (set-up data)
+  const uint2 cm = ctaMap[blockIdx.x];
+  const int sceneIdx = static_cast<int>(cm.x);
+  const uint32_t rank = cm.y;
+  const WarpPlan pl = plan[sceneIdx];
+  const int warpsPerBlock = static_cast<int>(pl.warps);  // warps of this CTA that take queries
+  const int warp = threadIdx.x >> 5;
+
+  BPSN_TICK(tS0);
+  uint32_t n = 0;
+  const NavScene scGlobal = st.scenes[sceneIdx];
+  // A scene too large to sit in shared memory next to at least one slab is worked on where
+  // it lies: the same image, in global memory (L2-resident), and slabs in a global
+  // scratch area.  The code below is the same either way; only the latency differs.
+  const bool inGlobal = pl.slabOffset == kSlabInGlobal;
+  if (inGlobal) {
+    waitForPredecessor();
+    n = g.counts[sceneIdx];
+    if (rank == 0 && threadIdx.x == 0) {  // the next step starts from empty lists
+      g.countsNext[sceneIdx] = 0u;
+      g.countsNext[g.numScenes + sceneIdx] = 0u;
+    }
+  } else {
+    // The image was laid out at set-up exactly as stagedLayout() describes (float4
+    // vertices, polygons with filtered links and the duplicate-neighbour flag, detail
+    // bases / triangles / vertices, island ids), 16-byte aligned and a multiple of 16
+    // bytes long: one bulk asynchronous copy (TMA, untiled, this CTA's own shared
+    // memory, no multicast) brings it in and signals an mbarrier.
+    __shared__ __align__(8) unsigned long long stageBar;
+    const uint32_t bar = static_cast<uint32_t>(__cvta_generic_to_shared(&stageBar));
+    const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    const uint32_t bytes = scGlobal.stagedBytes;
+    if (threadIdx.x == 0) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar) : "memory");
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                   : "memory");
+      asm volatile(
+          "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+          ::"r"(dst), "l"(scGlobal.staged), "r"(bytes), "r"(bar)
+          : "memory");
+    }
+    // The scene image never changes, so the copy above may run while the kernel
+    // before this one is still at work; everything below reads what it wrote.
+    waitForPredecessor();
+    n = g.counts[sceneIdx];
+    if (rank == 0 && threadIdx.x == 0) {  // the next step starts from empty lists
+      g.countsNext[sceneIdx] = 0u;
+      g.countsNext[g.numScenes + sceneIdx] = 0u;
+    }
+    // bounded wait on phase 0 of the barrier; a copy of this size lands within
+    // microseconds, the bound is ~1 s of polling
+    bool landed = false;
+    for (int it = 0; it < (1 << 22) && !landed; ++it) {
+      uint32_t ok;
+      asm volatile(
+          "{\n\t.reg .pred p;\n\t"
+          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(ok)
+          : "r"(bar)
+          : "memory");
+      landed = ok != 0;
+    }
+    if (!__syncthreads_and(landed ? 1 : 0)) {
+      // never observed; leave without touching the half-filled tables (the step's
+      // listed envs keep their previous outputs) and make the failure visible
+      if (threadIdx.x == 0)
+        atomicOr(g.errFlags, 1u);
+      return;
+    }
+  }
+  if (rank * static_cast<uint32_t>(warpsPerBlock) >= n || warp >= warpsPerBlock)
+    return;  // (only after the copy has landed: it targets this CTA's shared memory)
+#if defined(BPSN_PHASE_TIMING)
+  if (inGlobal)
+    stepWarpQueries<true>(g, st, pl, sceneIdx, rank, n, scGlobal, globalSlabs, globalSlabStride,
+                          fallbackScratch, seedLo, seedHi, tS0);
+  else
+    stepWarpQueries<false>(g, st, pl, sceneIdx, rank, n, scGlobal, globalSlabs, globalSlabStride,
+                           fallbackScratch, seedLo, seedHi, tS0);
+#else
+  if (inGlobal)
+    stepWarpQueries<true>(g, st, pl, sceneIdx, rank, n, scGlobal, globalSlabs, globalSlabStride,
+                          fallbackScratch, seedLo, seedHi);
+  else
+    stepWarpQueries<false>(g, st, pl, sceneIdx, rank, n, scGlobal, globalSlabs, globalSlabStride,
+                           fallbackScratch, seedLo, seedHi);
 #endif
 }
 

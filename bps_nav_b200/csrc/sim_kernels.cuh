@@ -145,10 +145,12 @@ __device__ __forceinline__ void waitForPredecessor() {
 // scene's environments to the one-thread-per-environment kernel.
 struct WarpPlan {
   uint32_t pcap;        // polygon capacity of a slab of this scene (multiple of 16)
-  uint32_t slabOffset;  // bytes from the start of dynamic shared memory to the first slab
+  uint32_t slabOffset;  // bytes from the start of dynamic shared memory to the first slab, or
+                        // kSlabInGlobal: tables and slabs of this scene stay in global memory
   uint32_t warps;
   uint32_t ctas;
 };
+constexpr uint32_t kSlabInGlobal = 0xffffffffu;
 
 struct TurnConsts {  // +/-10 degrees about +Y, evaluated once on the host
   float lx, ly, lz, lw;

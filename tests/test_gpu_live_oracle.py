@@ -102,11 +102,19 @@ def test_exact_heap_search_matches_oracle():
     _compare_run(["m03", "m07"], 512, 128, seed=24, mix="policy", exact_heap=True)
 
 
-def test_warp_and_generic_kernels_in_one_step():
+def test_scenes_in_shared_and_in_global_memory_in_one_step():
     # with the shared-memory budget cut to 96 KB the larger scenes (m04: 1304 polygons, m07, m01)
-    # run on the generic kernel and the small ones on the warp kernel, in the same group and step
+    # do not fit and are worked on in global memory (slabs of three different sizes side by
+    # side), the small ones in shared memory, in the same group and launch
     _compare_run(["m04", "m13", "m07", "m15", "m01", "c0"], 1536, 64, seed=41, mix="uniform",
                  small_smem=True)
+
+
+def test_mixed_scene_batch_large_enough_for_the_throughput_plan():
+    # benchmark config 3 at a batch where the planner moves every scene with room for fewer
+    # than 8 slabs (m01, m04, m06, m07) to global memory
+    names = [f"m{i:02d}" for i in range(16)]
+    _compare_run(names, 12288, 24, seed=9, mix="uniform", check_state_every=8)
 
 
 def test_double_buffered_groups():
