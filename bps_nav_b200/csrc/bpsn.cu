@@ -436,12 +436,20 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
     // the four result arrays are adjacent in the state block: one pinned
     // block with the same relative layout lets a step publish them in one copy
     g.outBytes = (oPolar + 2 * B * f) - oReward;
-    BPSN_CUDA(sim, cudaMallocHost(&g.hOut, g.outBytes));
+    // mapped: the kernels write the mirrors themselves (GroupDev::hReward ...)
+    BPSN_CUDA(sim, cudaHostAlloc(&g.hOut, g.outBytes, cudaHostAllocMapped));
     memset(g.hOut, 0, g.outBytes);
     g.hReward = reinterpret_cast<float*>(g.hOut);
     g.hMask = g.hOut + (oMask - oReward);
     g.hInfo = reinterpret_cast<float*>(g.hOut + (oInfo - oReward));
     g.hPolar = reinterpret_cast<float*>(g.hOut + (oPolar - oReward));
+    void* dOut = nullptr;
+    BPSN_CUDA(sim, cudaHostGetDevicePointer(&dOut, g.hOut, 0));
+    uint8_t* db = static_cast<uint8_t*>(dOut);
+    d.hReward = reinterpret_cast<float*>(db);
+    d.hMask = db + (oMask - oReward);
+    d.hInfo = reinterpret_cast<float*>(db + (oInfo - oReward));
+    d.hPolar = reinterpret_cast<float*>(db + (oPolar - oReward));
   }
   BPSN_CUDA(sim, cudaEventCreateWithFlags(&g.done, cudaEventDisableTiming));
   return BPSN_OK;
@@ -449,15 +457,9 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
 
 // D2H of the result arrays + completion event
 int32_t finishLaunch(bpsn_sim* sim, Group& g, cudaStream_t s, bool polarOnly) {
-  if (sim->cfg.flags & BPSN_FLAG_HOST_MIRRORS) {
-    const uint32_t B = g.dev.B;
-    if (!polarOnly) {
-      BPSN_CUDA(sim, cudaMemcpyAsync(g.hOut, g.dev.reward, g.outBytes, cudaMemcpyDeviceToHost, s));
-    } else {
-      BPSN_CUDA(sim, cudaMemcpyAsync(g.hPolar, g.dev.polar, 2 * B * sizeof(float),
-                                     cudaMemcpyDeviceToHost, s));
-    }
-  }
+  // host mirrors need no copy: the kernels have stored into them (mapped pinned memory);
+  // they are complete for the host once this event has been waited for
+  (void)polarOnly;
   BPSN_CUDA(sim, cudaEventRecord(g.done, s));
   return BPSN_OK;
 }

@@ -89,6 +89,13 @@ struct GroupDev {
   float* rewardOut;
   uint8_t* maskOut;
   float* polarOut;  // [B][2]
+  // host mirrors of reward / mask / info / polar in mapped pinned memory (null when the
+  // handle keeps none): the kernels store every result a second time there, which puts
+  // the transfer inside the step instead of a copy after it
+  float* hReward;
+  uint8_t* hMask;
+  float* hInfo;
+  float* hPolar;
   // running episode statistics, the device-side form of PPOTrainer._update_stats
   // (bps_nav/rl/ppo/ppo_trainer.py:286-319)
   float* episodeReward;  // [B]     reward accumulated in the current episode
@@ -202,6 +209,8 @@ __device__ __forceinline__ void writePolar(const GroupDev& g, uint32_t e, float 
   reinterpret_cast<float2*>(g.polar)[e] = make_float2(rho, -phi);
   if (g.polarOut)
     reinterpret_cast<float2*>(g.polarOut)[e] = make_float2(rho, -phi);
+  if (g.hPolar)
+    reinterpret_cast<float2*>(g.hPolar)[e] = make_float2(rho, -phi);
 }
 
 // Exploration: cell of the current position in the initial pose's frame,
@@ -359,6 +368,11 @@ __device__ __forceinline__ void finishEnv(const GroupDev& g, const SceneTable& s
     g.info[3 * e + 0] = success;
     g.info[3 * e + 1] = spl;
     g.info[3 * e + 2] = d;
+    if (g.hInfo) {
+      g.hInfo[3 * e + 0] = success;
+      g.hInfo[3 * e + 1] = spl;
+      g.hInfo[3 * e + 2] = d;
+    }
   } else if (g.task == kTaskFlee) {
     // Flee::InfoFunctor::step / RewardFunctor::step (simulator.cpp:846-880)
     if (!moved)
@@ -366,6 +380,8 @@ __device__ __forceinline__ void finishEnv(const GroupDev& g, const SceneTable& s
     reward = d - prev;
     g.prevDist[e] = d;
     g.info[e] = d;
+    if (g.hInfo)
+      g.hInfo[e] = d;
     success = d;  // first info column, for the running statistics below
   } else {
     // Exploration (simulator.cpp:919-993); the set itself was updated by the caller
@@ -373,6 +389,8 @@ __device__ __forceinline__ void finishEnv(const GroupDev& g, const SceneTable& s
     reward = 0.25f * (d - prev);
     g.prevDist[e] = d;
     g.info[e] = d;
+    if (g.hInfo)
+      g.hInfo[e] = d;
     success = d;
   }
   g.reward[e] = reward;
@@ -381,6 +399,10 @@ __device__ __forceinline__ void finishEnv(const GroupDev& g, const SceneTable& s
     g.rewardOut[e] = reward;
   if (g.maskOut)
     g.maskOut[e] = done ? 0 : 1;
+  if (g.hReward) {
+    g.hReward[e] = reward;
+    g.hMask[e] = done ? 0 : 1;
+  }
   // current_episode_reward += reward; on done the episode's totals go to the
   // running sums and the accumulator restarts (same fp32 operations, in step
   // order, as the trainer's tensor code)
