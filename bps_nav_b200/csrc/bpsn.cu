@@ -851,7 +851,9 @@ int32_t bpsn_step_start_ex(bpsn_sim* sim, uint32_t group, const int64_t* actions
                                       static_cast<const uint2*>(g.dCtaMap), g.fallbackScratch,
                                       g.globalSlabs, g.globalSlabStride, seedLo, seedHi));
   }
-  if (g.anyThreadScene) {  // scenes too large for shared memory (it skips the others)
+  if (g.anyThreadScene) {  // meshes the warp kernel cannot index (it skips the other scenes)
+    if (g.anyWarpScene)
+      lc.numAttrs = 0;  // behind the warp kernel: plain stream order, no early start
     lc.gridDim = dim3(blocksFor(g.maxSceneEnvs, 128), g.numScenesUsed);
     lc.blockDim = dim3(128);
     lc.dynamicSmemBytes = 0;

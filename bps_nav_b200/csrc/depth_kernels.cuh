@@ -8,7 +8,7 @@
 // :1216), image [H, W] float32 per environment (simulator/pytorch.cpp:36-44).
 // For scenes that are given as a floor rectangle plus axis-aligned boxes the same
 // camera is evaluated here analytically: one ray per pixel centre, ray / plane for
-// the floor, slab test for every box, nearest hit.  The value is the view-space
+// the floor, slab test for every box that reaches into the view frustum, nearest hit.  The value is the view-space
 // depth in metres (distance along the optical axis), `far` where nothing is hit;
 // hits in front of the near plane are clipped.
 //
@@ -60,14 +60,49 @@ k_depth(GroupDev g, RenderTable rt, float* __restrict__ out, uint32_t W, uint32_
   const uint32_t npix = W * H;
   float* img = out + static_cast<size_t>(e) * npix;
 
-  // the first kDepthBoxChunk boxes of the scene are staged in shared memory (every
-  // thread walks them in the same order: broadcast reads); any beyond that are read
-  // from global memory, equally in lock step
-  const uint32_t staged = nb < static_cast<uint32_t>(kDepthBoxChunk)
-                              ? nb : static_cast<uint32_t>(kDepthBoxChunk);
-  for (uint32_t i = threadIdx.x; i < staged * 6; i += blockDim.x)
-    sBox[i] = boxes[i];
+  // Of the scene's first kDepthBoxChunk boxes only those that reach into the view frustum
+  // are staged in shared memory (every thread then walks them in the same order: broadcast
+  // reads); any boxes beyond that number are read from global memory, unculled.  A box is
+  // dropped when all its corners lie outside one of the five planes through the eye that
+  // bound the image (behind the near plane, beyond the left / right / top / bottom edge,
+  // with a millimetre of slack: pixel centres stay half a pixel inside those edges), so
+  // no ray of the image can touch it and the image is the same as without culling.  The
+  // order of the survivors does not matter: the nearest hit is a minimum.
+  __shared__ uint32_t sCount;
+  const uint32_t first = nb < static_cast<uint32_t>(kDepthBoxChunk)
+                             ? nb : static_cast<uint32_t>(kDepthBoxChunk);
+  if (threadIdx.x == 0)
+    sCount = 0u;
   __syncthreads();
+  for (uint32_t b = threadIdx.x; b < first; b += blockDim.x) {
+    const float* bx = boxes + 6 * static_cast<size_t>(b);
+    const float mn[3] = {bx[0], bx[1], bx[2]}, mx[3] = {bx[3], bx[4], bx[5]};
+    bool allNear = true, allLeft = true, allRight = true, allUp = true, allDown = true;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const float px = ((c & 1) ? mx[0] : mn[0]) - ox;
+      const float py = ((c & 2) ? mx[1] : mn[1]) - oy;
+      const float pz = ((c & 4) ? mx[2] : mn[2]) - oz;
+      // camera space: x right, y up, depth along the optical axis (-z)
+      const float cx = m00 * px + m01 * py + m02 * pz;
+      const float cy = m10 * px + m11 * py + m12 * pz;
+      const float depth = -(m20 * px + m21 * py + m22 * pz);
+      const float slack = 1e-3f;
+      allNear = allNear && (kNearPlane - depth > slack);
+      allRight = allRight && (cx - aspect * depth > slack);
+      allLeft = allLeft && (-cx - aspect * depth > slack);
+      allUp = allUp && (cy - depth > slack);
+      allDown = allDown && (-cy - depth > slack);
+    }
+    if (!(allNear || allLeft || allRight || allUp || allDown)) {
+      const uint32_t slot = atomicAdd(&sCount, 1u);
+#pragma unroll
+      for (int k = 0; k < 6; ++k)
+        sBox[6 * slot + k] = bx[k];
+    }
+  }
+  __syncthreads();
+  const uint32_t staged = sCount;
   for (uint32_t pix = threadIdx.x; pix < npix; pix += blockDim.x) {
     const uint32_t px = pix % W, py = pix / W;
     // pixel centre -> camera-space direction with z = -1 (tan(45 deg) = 1)
@@ -85,8 +120,10 @@ k_depth(GroupDev g, RenderTable rt, float* __restrict__ out, uint32_t W, uint32_
         t = tf;
     }
     const float ix = 1.f / dx, iy = 1.f / dy, iz = 1.f / dz;
-    for (uint32_t b = 0; b < nb; ++b) {
-      const float* bx = b < staged ? &sBox[6 * b] : &boxes[6 * static_cast<size_t>(b)];
+    const uint32_t total = staged + (nb - first);  // survivors, then the unculled rest
+    for (uint32_t b = 0; b < total; ++b) {
+      const float* bx = b < staged ? &sBox[6 * b]
+                                   : &boxes[6 * static_cast<size_t>(first + (b - staged))];
       const float tx0 = (bx[0] - ox) * ix, tx1 = (bx[3] - ox) * ix;
       const float ty0 = (bx[1] - oy) * iy, ty1 = (bx[4] - oy) * iy;
       const float tz0 = (bx[2] - oz) * iz, tz1 = (bx[5] - oz) * iz;
