@@ -59,6 +59,7 @@ struct Group {
   bool anyWarpScene = false;
   bool anyThreadScene = false;  // some scene needs the generic kernel
   uint32_t numCtas = 0;         // grid of the warp kernel
+  int warpMode = 0;             // which instance of k_step_warp: 0 shared, 1 global, 2 both
   size_t geoSmem = 0;
   WarpPlan* dPlan = nullptr;    // [numScenes]
   uint8_t* globalSlabs = nullptr;  // warp slabs of the scenes that are worked on in global memory
@@ -320,6 +321,10 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
     std::vector<double> work(ns, 0.0);
     g.anyThreadScene = false;
     g.anyWarpScene = false;
+    // Pass 1: how many slabs fit next to each scene's image in shared memory.
+    std::vector<uint32_t> smemWarps(ns, 0u);
+    std::vector<size_t> slabBytes(ns, 0), sceneBytes(ns, 0);
+    bool anyCramped = false;  // some scene has room for fewer than 8 slabs
     for (uint32_t s2 = 0; s2 < ns; ++s2) {
       if (!perScene[s2])
         continue;
@@ -329,31 +334,52 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
       const uint32_t pcap = (static_cast<uint32_t>(h.polys.size()) + 15u) / 16u * 16u;
       const size_t slab = warpGeoSlabBytes(static_cast<int>(pcap));
       uint32_t w = 0;
-      if (!forceGeneric && h.polys.size() < 65000 && sb + slab <= kSmemMax)
+      if (sb + slab <= kSmemMax)
         w = static_cast<uint32_t>((kSmemMax - sb) / slab);
       if (w > 16)
         w = 16;
+      smemWarps[s2] = w;
+      slabBytes[s2] = slab;
+      sceneBytes[s2] = sb;
       plan[s2].pcap = pcap;
-      plan[s2].slabOffset = static_cast<uint32_t>(sb);
-      // A scene that leaves no room for a slab is worked on in global memory (tables and
-      // slabs L2-resident, all 16 warps of the CTA active).  So is one that leaves room for
-      // fewer than 8 slabs when the group has more queries per step than two rounds of
-      // every warp of the GPU: then throughput counts, and 16 warps at L2 latency get
-      // through more queries than a few warps at shared-memory latency (measured on 16
-      // scenes of 91-1304 polygons: 105 against 90 M env-steps/s at 16384 envs); with fewer
-      // queries the step lasts as long as its slowest query, which shared memory shortens.
-      const uint32_t kMinSmemWarps = throughputBound ? 8u : 1u;
-      if (!forceGeneric && h.polys.size() < 65000 && w < kMinSmemWarps) {
+      if (w < 8 && h.polys.size() < 65000)
+        anyCramped = true;
+    }
+    // Pass 2: where each scene is worked on.
+    //  * A scene that leaves no room for a slab is worked on in global memory (tables and
+    //    slabs L2-resident, all 16 warps of the CTA active).
+    //  * When the group has more queries per step than two rounds of every warp of the GPU,
+    //    throughput counts, and a scene with room for fewer than 8 slabs gets through more
+    //    queries with 16 warps at cache latency than with a few warps at shared-memory
+    //    latency.  Such a group is then put in global memory as a whole: a kernel that uses no
+    //    shared memory leaves the entire unified cache to L1, which is what makes global
+    //    memory competitive (16 scenes of 91-1304 polygons, 16384 envs: 105 M env-steps/s all
+    //    in global memory, 95 M mixed, 90 M all in shared memory).
+    //  * With fewer queries the step lasts as long as its slowest query, which shared
+    //    memory shortens: everything that fits stays there.
+    const bool allGlobal = throughputBound && anyCramped;
+    for (uint32_t s2 = 0; s2 < ns; ++s2) {
+      if (!perScene[s2])
+        continue;
+      const HostScene& h = sim->scenes[s2].host;
+      uint32_t w = smemWarps[s2];
+      plan[s2].slabOffset = static_cast<uint32_t>(sceneBytes[s2]);
+      const bool indexable = h.polys.size() < 65000;  // 16-bit polygon indices in the slabs
+      if (forceGeneric || !indexable) {
+        w = 0;
+      } else if (allGlobal || w == 0) {
         w = 16;
         plan[s2].slabOffset = kSlabInGlobal;
-        if (slab > maxGlobalSlab)
-          maxGlobalSlab = slab;
+        if (slabBytes[s2] > maxGlobalSlab)
+          maxGlobalSlab = slabBytes[s2];
       }
       plan[s2].warps = w;
       if (w) {
         g.anyWarpScene = true;
-        // a warp working in global memory gets through its queries more slowly
-        const double speed = plan[s2].slabOffset == kSlabInGlobal ? kGlobalWarpSpeed : 1.0;
+        // a warp working in global memory beside shared-memory CTAs (small L1) gets
+        // through its queries more slowly
+        const double speed =
+            (plan[s2].slabOffset == kSlabInGlobal && !allGlobal) ? kGlobalWarpSpeed : 1.0;
         work[s2] = static_cast<double>(perScene[s2]) / (w * speed);
         workSum += work[s2];
       } else {
@@ -380,9 +406,25 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
       BPSN_CUDA(sim, cudaMalloc(&g.dCtaMap, sizeof(uint2) * ctaMap.size()));
       BPSN_CUDA(sim, cudaMemcpy(g.dCtaMap, ctaMap.data(), sizeof(uint2) * ctaMap.size(),
                                 cudaMemcpyHostToDevice));
-      BPSN_CUDA(sim, cudaFuncSetAttribute(k_step_warp, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          static_cast<int>(kSmemMax)));
-      g.geoSmem = kSmemMax;
+      bool anyShared = false, anyGlobal = false;
+      for (uint32_t s2 = 0; s2 < ns; ++s2) {
+        if (!plan[s2].warps)
+          continue;
+        if (plan[s2].slabOffset == kSlabInGlobal)
+          anyGlobal = true;
+        else
+          anyShared = true;
+      }
+      g.warpMode = anyShared ? (anyGlobal ? 2 : 0) : 1;
+      g.geoSmem = g.warpMode == 1 ? 0 : kSmemMax;
+      if (g.warpMode == 0)
+        BPSN_CUDA(sim, cudaFuncSetAttribute(k_step_warp<0>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            static_cast<int>(kSmemMax)));
+      else if (g.warpMode == 2)
+        BPSN_CUDA(sim, cudaFuncSetAttribute(k_step_warp<2>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            static_cast<int>(kSmemMax)));
       BPSN_CUDA(sim, cudaMalloc(&g.fallbackScratch,
                                 sizeof(AStarScratch) * static_cast<size_t>(g.numCtas) * 16));
       g.globalSlabStride = maxGlobalSlab;
@@ -846,7 +888,8 @@ int32_t bpsn_step_start_ex(bpsn_sim* sim, uint32_t group, const int64_t* actions
     lc.gridDim = dim3(g.numCtas);
     lc.blockDim = dim3(512);
     lc.dynamicSmemBytes = g.geoSmem;
-    BPSN_CUDA(sim, cudaLaunchKernelEx(&lc, k_step_warp, gd, sim->table,
+    auto* kernel = g.warpMode == 0 ? k_step_warp<0> : g.warpMode == 1 ? k_step_warp<1> : k_step_warp<2>;
+    BPSN_CUDA(sim, cudaLaunchKernelEx(&lc, kernel, gd, sim->table,
                                       static_cast<const WarpPlan*>(g.dPlan),
                                       static_cast<const uint2*>(g.dCtaMap), g.fallbackScratch,
                                       g.globalSlabs, g.globalSlabStride, seedLo, seedHi));

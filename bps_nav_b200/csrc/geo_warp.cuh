@@ -1357,6 +1357,13 @@ __device__ __forceinline__ void stepWarpQueries(const GroupDev& g, const SceneTa
 //   grid  = CTAs of all scenes (ctaMap says which scene a CTA serves), block = 512 threads
 //   smem  = staged tables of the CTA's scene + as many warp slabs as fit (plan[scene].warps)
 // Warps pull list slots from a per-scene cursor until the list is drained.
+// Three instances, chosen by the host from the group's plan, so that a group whose scenes
+// all sit in shared memory (the usual case) does not carry the code of the other mode:
+//   kMode 0  every scene of the group is staged in shared memory
+//   kMode 1  every scene is worked on in global memory (launched without dynamic shared
+//            memory, which leaves the whole unified cache to L1)
+//   kMode 2  both kinds in one grid
+template <int kMode>
 __global__ void __launch_bounds__(512, 1)
 k_step_warp(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
             const uint2* __restrict__ ctaMap, AStarScratch* __restrict__ fallbackScratch,
@@ -1378,7 +1385,7 @@ k_step_warp(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
   // A scene too large to sit in shared memory next to at least one slab is worked on where
   // it lies: the same image, in global memory (L2-resident), and slabs in a global
   // scratch area.  The code below is the same either way; only the latency differs.
-  const bool inGlobal = pl.slabOffset == kSlabInGlobal;
+  const bool inGlobal = kMode == 1 || (kMode == 2 && pl.slabOffset == kSlabInGlobal);
   if (inGlobal) {
     waitForPredecessor();
     n = g.counts[sceneIdx];
@@ -1442,20 +1449,23 @@ k_step_warp(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
   if (rank * static_cast<uint32_t>(warpsPerBlock) >= n || warp >= warpsPerBlock)
     return;  // (only after the copy has landed: it targets this CTA's shared memory)
 #if defined(BPSN_PHASE_TIMING)
-  if (inGlobal)
-    stepWarpQueries<true>(g, st, pl, sceneIdx, rank, n, scGlobal, globalSlabs, globalSlabStride,
-                          fallbackScratch, seedLo, seedHi, tS0);
-  else
-    stepWarpQueries<false>(g, st, pl, sceneIdx, rank, n, scGlobal, globalSlabs, globalSlabStride,
-                           fallbackScratch, seedLo, seedHi, tS0);
+#define BPSN_STEP_ARGS g, st, pl, sceneIdx, rank, n, scGlobal, globalSlabs, globalSlabStride, \
+                       fallbackScratch, seedLo, seedHi, tS0
 #else
-  if (inGlobal)
-    stepWarpQueries<true>(g, st, pl, sceneIdx, rank, n, scGlobal, globalSlabs, globalSlabStride,
-                          fallbackScratch, seedLo, seedHi);
-  else
-    stepWarpQueries<false>(g, st, pl, sceneIdx, rank, n, scGlobal, globalSlabs, globalSlabStride,
-                           fallbackScratch, seedLo, seedHi);
+#define BPSN_STEP_ARGS g, st, pl, sceneIdx, rank, n, scGlobal, globalSlabs, globalSlabStride, \
+                       fallbackScratch, seedLo, seedHi
 #endif
+  if constexpr (kMode == 0) {
+    stepWarpQueries<false>(BPSN_STEP_ARGS);
+  } else if constexpr (kMode == 1) {
+    stepWarpQueries<true>(BPSN_STEP_ARGS);
+  } else {
+    if (inGlobal)
+      stepWarpQueries<true>(BPSN_STEP_ARGS);
+    else
+      stepWarpQueries<false>(BPSN_STEP_ARGS);
+  }
+#undef BPSN_STEP_ARGS
 }
 
 }  // namespace bpsn
