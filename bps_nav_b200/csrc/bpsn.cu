@@ -357,7 +357,8 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
     //    in global memory, 95 M mixed, 90 M all in shared memory).
     //  * With fewer queries the step lasts as long as its slowest query, which shared
     //    memory shortens: everything that fits stays there.
-    const bool allGlobal = throughputBound && anyCramped;
+    const bool allGlobal = (throughputBound && anyCramped) ||
+                           (sim->cfg.flags & BPSN_FLAG_GLOBAL_MEMORY) != 0;
     for (uint32_t s2 = 0; s2 < ns; ++s2) {
       if (!perScene[s2])
         continue;
@@ -388,11 +389,23 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
     }
     g.warpGeo = g.anyWarpScene;
     if (g.anyWarpScene) {
+      bool anyShared = false, anyGlobal = false;
+      for (uint32_t s2 = 0; s2 < ns; ++s2) {
+        if (!plan[s2].warps)
+          continue;
+        if (plan[s2].slabOffset == kSlabInGlobal)
+          anyGlobal = true;
+        else
+          anyShared = true;
+      }
+      g.warpMode = anyShared ? (anyGlobal ? 2 : 0) : 1;
+      // the global-only instance fits two CTAs on an SM (64 registers, no shared memory)
+      const int ctaBudget = sms * (g.warpMode == 1 ? 2 : 1);
       std::vector<uint2> ctaMap;
       for (uint32_t s2 = 0; s2 < ns; ++s2) {
         if (!plan[s2].warps)
           continue;
-        uint32_t c = static_cast<uint32_t>(sms * work[s2] / workSum + 0.5);
+        uint32_t c = static_cast<uint32_t>(ctaBudget * work[s2] / workSum + 0.5);
         const uint32_t need = (perScene[s2] + plan[s2].warps - 1) / plan[s2].warps;
         if (c > need)
           c = need;  // never more warps than environments
@@ -406,16 +419,6 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
       BPSN_CUDA(sim, cudaMalloc(&g.dCtaMap, sizeof(uint2) * ctaMap.size()));
       BPSN_CUDA(sim, cudaMemcpy(g.dCtaMap, ctaMap.data(), sizeof(uint2) * ctaMap.size(),
                                 cudaMemcpyHostToDevice));
-      bool anyShared = false, anyGlobal = false;
-      for (uint32_t s2 = 0; s2 < ns; ++s2) {
-        if (!plan[s2].warps)
-          continue;
-        if (plan[s2].slabOffset == kSlabInGlobal)
-          anyGlobal = true;
-        else
-          anyShared = true;
-      }
-      g.warpMode = anyShared ? (anyGlobal ? 2 : 0) : 1;
       g.geoSmem = g.warpMode == 1 ? 0 : kSmemMax;
       if (g.warpMode == 0)
         BPSN_CUDA(sim, cudaFuncSetAttribute(k_step_warp<0>,

@@ -1364,7 +1364,7 @@ __device__ __forceinline__ void stepWarpQueries(const GroupDev& g, const SceneTa
 //            memory, which leaves the whole unified cache to L1)
 //   kMode 2  both kinds in one grid
 template <int kMode>
-__global__ void __launch_bounds__(512, 1)
+__global__ void __launch_bounds__(512, kMode == 1 ? 2 : 1)
 k_step_warp(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
             const uint2* __restrict__ ctaMap, AStarScratch* __restrict__ fallbackScratch,
             uint8_t* __restrict__ globalSlabs, size_t globalSlabStride, uint32_t seedLo,

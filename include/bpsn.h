@@ -96,7 +96,11 @@ enum {
   /* plan the step kernels as if a CTA had 96 KB of shared memory instead of 227 KB:
      medium-sized scenes then go to the generic kernel while small ones stay on the
      warp kernel -- for testing groups that need both kernels in one step */
-  BPSN_FLAG_SMEM_96K = 1u << 3
+  BPSN_FLAG_SMEM_96K = 1u << 3,
+  /* work on every scene in global memory (tables and A* slabs L2 / L1 resident, two CTAs
+     per SM) whatever its size; the planner otherwise does this only for large batches
+     that contain a scene too big to share an SM's shared memory with 8 slabs */
+  BPSN_FLAG_GLOBAL_MEMORY = 1u << 4
 };
 
 /* Fields addressable through bpsn_get_ptr.  All arrays are indexed by the

@@ -110,6 +110,14 @@ def test_scenes_in_shared_and_in_global_memory_in_one_step():
                  small_smem=True)
 
 
+def test_everything_in_global_memory():
+    # the global-only instance of the step kernel (two CTAs per SM) on scenes that would fit
+    # shared memory
+    _compare_run(["c1"], 2048, 48, seed=31, mix="uniform", global_memory=True)
+    _compare_run(["m03", "m10", "c0", "m12"], 1024, 96, seed=32, mix="policy", global_memory=True,
+                 check_state_every=32)
+
+
 def test_mixed_scene_batch_large_enough_for_the_throughput_plan():
     # benchmark config 3 at a batch where the planner moves every scene with room for fewer
     # than 8 slabs (m01, m04, m06, m07) to global memory
