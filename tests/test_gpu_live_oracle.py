@@ -125,6 +125,13 @@ def test_mixed_scene_batch_large_enough_for_the_throughput_plan():
     _compare_run(names, 12288, 24, seed=9, mix="uniform", check_state_every=8)
 
 
+def test_odd_batch_sizes():
+    # partial warps in k_pre's warp-aggregated list appends, fewer environments than warps
+    for n, seed in ((1, 50), (7, 51), (33, 52), (100, 53)):
+        _compare_run(["c0"], n, 40, seed=seed, mix="uniform")
+    _compare_run(["m13", "m15", "c0"], 99, 40, seed=54, mix="policy")
+
+
 def test_double_buffered_groups():
     _compare_run(["c0", "m15", "m13", "m14"], 256, 64, seed=3, mix="uniform", double_buffered=True)
 
