@@ -15,6 +15,17 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
 
 
+def pytest_sessionstart(session):
+    """A fresh checkout has no built library: build it once (nvcc cross-compiles without a
+    GPU).  An existing library is left alone, whatever its age."""
+    from bps_nav_b200 import build as _build
+    if not os.path.exists(_build.LIB):
+        try:
+            _build.build(force=True)
+        except Exception as e:  # the tests that need the library will say so themselves
+            sys.stderr.write(f"could not build libbpsn.so: {e}\n")
+
+
 def scene_path(name):
     return os.path.join(SCENES, f"{name}.navmesh")
 
