@@ -523,8 +523,11 @@ k_selftest_sqrt(uint32_t lo, uint32_t hi, unsigned long long* mismatches) {
   for (uint64_t i = lo + static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i <= hi;
        i += stride) {
     const float x = __uint_as_float(static_cast<uint32_t>(i));
-    if (__float_as_uint(sqrtExact(x)) != __float_as_uint(sqrtf(x)))
+    const uint32_t want = __float_as_uint(sqrtf(x));
+    if (__float_as_uint(sqrtExact(x)) != want)
       bad++;
+    if (sqrtCoreValid(x) && __float_as_uint(sqrtCore(x)) != want)
+      bad++;  // the bare sequence on the range it claims
   }
   if (bad)
     atomicAdd(mismatches, bad);

@@ -905,7 +905,8 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
     }
     __syncwarp();
     bool reached = false;
-    bool overflow = false;  // this lane had to drop an entry: the query is redone exactly
+    bool overflow = false;  // this lane had to drop an entry, or met a distance outside the bare
+                            // square root's range: the query is redone exactly
     // why the search has to be (re)done with the reference's heap
     uint32_t exactWhy = forceExact ? kStatTieFallback : 0u;
     int guard = 0;
@@ -1088,12 +1089,15 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
       const float nz = isNew ? (V0.z + V1.z) * 0.5f : nA.z;
       const float bpos[3] = {bA.x, bA.y, bA.z};
       const float npos[3] = {nx, ny, nz};
-      // lanes without a neighbour take the root of 1: a zero operand would send the
-      // whole warp through the square root's slow path
-      const float c2 = act ? vdistSqr(bpos, npos) : 1.f;
-      const float e2 = act ? vdistSqr(npos, endPos) : 1.f;
-      float curCost, toEnd;  // vdist(bpos, npos) * 1.0f and vdist(npos, endPos)
-      sqrtExact2(c2, e2, curCost, toEnd);
+      // The two distances use the bare square-root sequence (exact for operands from
+      // 2^-100 up).  An operand outside that range in a lane that has a neighbour - a zero
+      // distance, in practice - marks the search for the exact redo, like a full open list;
+      // nothing of this search is kept then.  Lanes without a neighbour compute garbage.
+      const float c2 = vdistSqr(bpos, npos);
+      const float e2 = vdistSqr(npos, endPos);
+      const float curCost = sqrtCore(c2);  // vdist(bpos, npos) * 1.0f
+      const float toEnd = sqrtCore(e2);    // vdist(npos, endPos)
+      overflow = overflow || (act && !(sqrtCoreValid(c2) & sqrtCoreValid(e2)));
       const bool atEnd = nei == endIdx;
       // end polygon: cost = g + step + distance to the end point, h = 0
       const float base = bA.w + curCost;

@@ -133,7 +133,8 @@ enum QueryStatus : uint32_t {
   kStatNoIsland = 1u << 6,      // start/end on different components -> +inf
   kStatBadAction = 1u << 7,     // action outside {0,1,2,3}
   kStatTieFallback = 1u << 8,   // open-list tie: query rerun with the exact heap emulation
-  kStatOpenOverflow = 1u << 9,  // register open list full: query rerun the same way
+  kStatOpenOverflow = 1u << 9,  // register open list full, or a zero / out-of-range distance in the
+                                // fast search: query rerun the same way
 };
 
 }  // namespace bpsn
