@@ -46,6 +46,7 @@ L2_FLUSH_BYTES = 256 << 20
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu capture
 # (profiles/k_step_warp_config1_ncu_full.md); only meaningful for the default workload
 LARGE_BATCH_ENVS = 32768
+DENSE_SCENE = "d0"
 NCU_TRAFFIC_BYTES = {("c1", 4096, "uniform", "k_step"): 0.89e6}
 
 
@@ -451,11 +452,9 @@ def run_ours(args):
     # ---------------- the same device-resident window at the largest per-GPU batch the
     # benchmark configurations name (32768 environments): reported beside the headline, it
     # shows the throughput once every warp has several queries to work through
-    big = None
-    if not args.no_large_batch and N < LARGE_BATCH_ENVS:
-        NB, KB = LARGE_BATCH_ENVS, 3
+    def device_window_rate(scene_set, NB, KB, seed0):
         genb = bps_sim.PointNavRolloutGenerator.from_scenes(
-            scenes, NB, gpu_id=local, seed=dist_utils.shard_seed(2000, rank, NB),
+            scene_set, NB, gpu_id=local, seed=dist_utils.shard_seed(seed0, rank, NB),
             host_mirrors=False)
         genb.reset(0)
         actsb = torch.from_numpy(draw_actions(((1 + KB) * T, NB), args.mix, 11 + rank)).to(dev)
@@ -482,10 +481,29 @@ def run_ours(args):
         b1.record()
         barrier()
         big_ms = max_over_ranks(b0.elapsed_time(b1))
-        big = {"envs_per_gpu": NB, "windows": KB, "value": world * NB * T * KB / (big_ms / 1000.0),
-               "unit": "env-steps/s", "note": "informational; not the headline workload"}
         genb.close()
-        del actsb, rb, vb, nvb, mb, retb, advb
+        return world * NB * T * KB / (big_ms / 1000.0)
+
+    big = None
+    if not args.no_large_batch and N < LARGE_BATCH_ENVS:
+        KB = 3
+        big = {"envs_per_gpu": LARGE_BATCH_ENVS, "windows": KB,
+               "value": device_window_rate(scenes, LARGE_BATCH_ENVS, KB, 2000),
+               "unit": "env-steps/s", "note": "informational; not the headline workload"}
+
+    # ---------------- and on a dense floor plan with the polygon count the description of
+    # config 1 quotes (scene d0: 150 x 150 m, 2500 boxes, 16407 polygons; the tables do not fit
+    # shared memory, so every search runs against global memory)
+    dense = None
+    if not args.no_large_batch and args.scene == "c1" and os.path.exists(scene_files(DENSE_SCENE)[0]):
+        dn, de = scene_files(DENSE_SCENE)
+        dscene = [Scene(dn, np.load(de), f"{DENSE_SCENE}.glb")]
+        KB = 3
+        dense = {"scene": DENSE_SCENE, "polys": 16407, "windows": KB, "unit": "env-steps/s",
+                 "value": device_window_rate(dscene, N, KB, 3000), "envs_per_gpu": N,
+                 "value_large_batch": device_window_rate(dscene, LARGE_BATCH_ENVS, KB, 3001),
+                 "note": "informational: same device-resident window as the headline, on a "
+                         "16407-polygon scene (searched in global memory)"}
 
     # ---------------- depth sensor (optional observation path; informational)
     depth_info = None
@@ -616,7 +634,7 @@ def run_ours(args):
                        "envs_per_gpu": N, "rollout_T": T, "polys": info["num_polys"],
                        "l2": f"flushed between timed windows ({L2_FLUSH_BYTES >> 20} MiB write)",
                        "timing": "CUDA events per window on the launch stream, summed, max over ranks"},
-            "clocks": clocks, "e2e": e2e, "large_batch": big, "depth_sensor": depth_info, "roofline": roofline, "roofline_step": step_roofline,
+            "clocks": clocks, "e2e": e2e, "large_batch": big, "dense_scene": dense, "depth_sensor": depth_info, "roofline": roofline, "roofline_step": step_roofline,
             "kernels": kernels, "cpu_baseline": cpu, "gae_baseline": gae_base,
             "gpu_launches": K * (T * 2 + 2), "resets_per_step": resets_per_step,
             "mean_return": mean_return, "wall_s_device_arm": wall,

@@ -14,7 +14,7 @@ SYMBOLS = [
     "bpsn_create", "bpsn_destroy", "bpsn_set_navmesh_file", "bpsn_set_navmesh_blob",
     "bpsn_set_episodes", "bpsn_set_env_scenes", "bpsn_set_scene_geometry", "bpsn_finalize", "bpsn_reset", "bpsn_step_start", "bpsn_step_start_ex",
     "bpsn_step_end", "bpsn_render", "bpsn_get_ptr", "bpsn_device_error_flags", "bpsn_profile_enable", "bpsn_profile_read", "bpsn_scene_info", "bpsn_query_snap", "bpsn_query_try_step",
-    "bpsn_query_geodesic", "bpsn_gae_workspace_bytes", "bpsn_gae", "bpsn_gae_static", "bpsn_selftest_sqrt", "bpsn_dataset_open", "bpsn_dataset_num_scenes", "bpsn_dataset_scene",
+    "bpsn_query_geodesic", "bpsn_gae_workspace_bytes", "bpsn_gae", "bpsn_gae_static", "bpsn_selftest_sqrt", "bpsn_debug_set_search_count", "bpsn_dataset_open", "bpsn_dataset_num_scenes", "bpsn_dataset_scene",
     "bpsn_dataset_close", "bpsn_last_error",
     "bpsn_version",
 ]
@@ -91,6 +91,7 @@ def load():
     lib.bpsn_gae_static.argtypes = [vp, vp, vp, vp, vp, vp, u32, u32, C.c_double, C.c_double, i32,
                                     C.c_float, vp]
     lib.bpsn_selftest_sqrt.argtypes = [i32, u32, u32, C.POINTER(C.c_uint64)]
+    lib.bpsn_debug_set_search_count.argtypes = [C.c_void_p, u32, u32]
     lib.bpsn_dataset_open.argtypes = [C.c_char_p, C.c_char_p, u32, C.POINTER(vp)]
     lib.bpsn_dataset_num_scenes.argtypes = [vp]
     lib.bpsn_dataset_num_scenes.restype = u32

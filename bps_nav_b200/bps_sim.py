@@ -351,6 +351,11 @@ class _RolloutGenerator:
         L.check(self._lib.bpsn_device_error_flags(self._h, group_idx, C.byref(v)), self._h)
         return int(v.value)
 
+    def debug_set_search_count(self, group_idx, count):
+        """Diagnostic: presets the search numbering of the group's global-memory node arrays
+        (bpsn_debug_set_search_count), e.g. to just below the point where it wraps."""
+        L.check(self._lib.bpsn_debug_set_search_count(self._h, group_idx, int(count)), self._h)
+
     KERNEL_NAMES = ("k_pre", "k_step")
 
     def profile(self, group_idx, enable=True):

@@ -430,9 +430,13 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
                                             static_cast<int>(kSmemMax)));
       BPSN_CUDA(sim, cudaMalloc(&g.fallbackScratch,
                                 sizeof(AStarScratch) * static_cast<size_t>(g.numCtas) * 16));
-      g.globalSlabStride = maxGlobalSlab;
-      if (maxGlobalSlab)
-        BPSN_CUDA(sim, cudaMalloc(&g.globalSlabs, maxGlobalSlab * g.numCtas * 16));
+      g.globalSlabStride = maxGlobalSlab ? maxGlobalSlab + kGlobalSlabExtra : 0;
+      if (maxGlobalSlab) {
+        // zeroed: search counters at 0, no node carries a visit tag
+        const size_t bytes = g.globalSlabStride * g.numCtas * 16;
+        BPSN_CUDA(sim, cudaMalloc(&g.globalSlabs, bytes));
+        BPSN_CUDA(sim, cudaMemset(g.globalSlabs, 0, bytes));
+      }
     }
     BPSN_CUDA(sim, cudaMalloc(&g.dPlan, sizeof(WarpPlan) * ns));
     BPSN_CUDA(sim, cudaMemcpy(g.dPlan, plan.data(), sizeof(WarpPlan) * ns, cudaMemcpyHostToDevice));
@@ -1238,6 +1242,28 @@ int32_t bpsn_gae_static(const float* rewards, float* values, const uint8_t* mask
   if (e != cudaSuccess)
     return fail(nullptr, BPSN_ERR_CUDA,
                 std::string("bpsn_gae_static launch: ") + cudaGetErrorString(e));
+  return BPSN_OK;
+}
+
+// Presets the search counter of every global-memory slab of a group (diagnostic: lets a test
+// drive the counters across the point where the 15-bit visit tag wraps and the slabs are wiped).
+int32_t bpsn_debug_set_search_count(bpsn_sim* sim, uint32_t group, uint32_t count) {
+  if (!sim || !sim->finalized)
+    return fail(sim, BPSN_ERR_STATE, "bpsn_debug_set_search_count: handle not finalized");
+  if (group >= sim->groups.size())
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_debug_set_search_count: group out of range");
+  Group& g = sim->groups[group];
+  if (g.inFlight)
+    return fail(sim, BPSN_ERR_STATE, "bpsn_debug_set_search_count: a step is in flight");
+  if (!g.globalSlabs)
+    return BPSN_OK;  // every slab of this group lives in shared memory
+  BPSN_CUDA(sim, cudaSetDevice(sim->cfg.gpu_id));
+  BPSN_CUDA(sim, cudaDeviceSynchronize());
+  const size_t slabs = static_cast<size_t>(g.numCtas) * 16;
+  std::vector<uint32_t> h(slabs, count);
+  BPSN_CUDA(sim, cudaMemcpy2D(g.globalSlabs + g.globalSlabStride - kGlobalSlabExtra,
+                              g.globalSlabStride, h.data(), sizeof(uint32_t), sizeof(uint32_t),
+                              slabs, cudaMemcpyHostToDevice));
   return BPSN_OK;
 }
 

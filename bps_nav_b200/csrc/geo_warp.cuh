@@ -78,7 +78,13 @@ __device__ __forceinline__ void phaseAdd(PhaseAcc* a, int idx, long long cycles)
 
 constexpr uint32_t kInfBits = 0x7f800000u;
 constexpr int kOpenSlots = 3;  // register open-list entries per lane (96 per warp)
-constexpr uint32_t kNodeVisited = 0x10000u;  // in nodeB.y next to the 16-bit parent
+// nodeB.y = parent (16 bits) | kNodeOpen | visit tag (15 bits).  A node belongs to the running
+// search iff its tag is the search's; anything else (zero, or the tag of an earlier search on
+// the same slab) reads as "not visited yet".
+constexpr uint32_t kNodeOpen = 0x10000u;  // exact search only: the node is in the heap
+constexpr uint32_t kNodeTagMask = 0xfffe0000u;
+constexpr uint32_t kNodeTagOne = 0x20000u;
+constexpr uint32_t kNodeTagMax = 32767u;
 
 // Shared-memory layout of a staged scene (byte offsets, each 16-byte aligned).
 struct StagedLayout {
@@ -108,17 +114,24 @@ __host__ __device__ inline StagedLayout stagedLayout(int nverts, int npolys, int
 
 // Per-warp slab for node capacity pcap (a multiple of 16):
 //   nodeA  float4 {x, y, z, cost}                      16 B / polygon
-//   nodeB  uint2  {total bits, parent | visited << 16}   8 B / polygon
+//   nodeB  uint2  {total bits, parent | open | tag}      8 B / polygon
 //   path   uint16 corridor, at most 256 polygons       512 B
 // After the search the node arrays are reused for the corridor's portals.
+// A slab in global memory keeps its contents from one search (and launch) to the next and
+// carries, in the last 16 bytes of its stride, the number of searches it has seen: that number
+// is the visit tag, so a search does not have to wipe the node array first (on a
+// 16 000-polygon mesh wiping costs as much as the search).  Shared-memory slabs start every
+// search from a wiped array.
 __host__ __device__ inline size_t warpGeoSlabBytes(int pcap) {
   return static_cast<size_t>(pcap) * 24 + 512;
 }
+constexpr size_t kGlobalSlabExtra = 16;  // the search counter of a global-memory slab
 
 struct WarpSlab {
   float4* nodeA;
   uint2* nodeB;
   uint16_t* path;
+  uint32_t* searches;  // global-memory slabs only: the search counter
 };
 
 __device__ __forceinline__ WarpSlab carveSlab(uint8_t* base, int pcap) {
@@ -126,6 +139,7 @@ __device__ __forceinline__ WarpSlab carveSlab(uint8_t* base, int pcap) {
   s.nodeA = reinterpret_cast<float4*>(base);
   s.nodeB = reinterpret_cast<uint2*>(base + static_cast<size_t>(pcap) * 16);
   s.path = reinterpret_cast<uint16_t*>(base + static_cast<size_t>(pcap) * 24);
+  s.searches = nullptr;
   return s;
 }
 
@@ -658,8 +672,29 @@ __device__ __forceinline__ void warpForwardMove(const GroupDev& g, const StagedV
   *refOut = ref;
 }
 
-constexpr uint32_t kNodeOpen = 0x20000u;  // exact search only: the node is in the heap
 constexpr int kSlabHeapCap = kMaxPathPolys;  // the corridor array doubles as the heap
+
+// Start of a search on slab `w`: returns the tag that marks this search's nodes.
+template <bool kGlobal>
+__device__ __forceinline__ uint32_t beginSearch(const WarpSlab w, int P, int lane) {
+  uint32_t count = 1u;
+  bool wipe = true;
+  if (kGlobal) {
+    __syncwarp();
+    count = *w.searches + 1u;  // same address in every lane
+    wipe = count > kNodeTagMax;  // the 15-bit tag wraps: wipe once and start over
+    count = wipe ? 1u : count;
+    __syncwarp();
+    if (lane == 0)
+      *w.searches = count;
+  }
+  if (wipe) {
+    for (int i = lane; i < P; i += 32)
+      w.nodeB[i] = make_uint2(0u, 0u);
+  }
+  __syncwarp();
+  return count * kNodeTagOne;
+}
 
 // dtNodeQueue on the slab: the heap holds polygon indices (uint16) in w.path and
 // compares the nodes' current totals (nodeB.x), exactly like the reference's
@@ -711,18 +746,14 @@ enum AStarOutcome : int {
 // compares against the totals the earlier edges have already written.
 __device__ __noinline__ int astarExactSlab(const StagedView sc, const WarpSlab w, int lane,
                                            const float* startPosIn, const float* endPosIn,
-                                           uint32_t startIdx, uint32_t endIdx, int* nodesOut) {
+                                           uint32_t startIdx, uint32_t endIdx, uint32_t tag,
+                                           int* nodesOut) {
   const float startPos[3] = {startPosIn[0], startPosIn[1], startPosIn[2]};
   const float endPos[3] = {endPosIn[0], endPosIn[1], endPosIn[2]};
-  const int P = sc.npolys;
-  __syncwarp();
-  for (int i = lane; i < P; i += 32)
-    w.nodeB[i] = make_uint2(0u, 0u);
-  __syncwarp();
   if (lane == 0) {
     const float tot = vdist(startPos, endPos) * 0.999f;
     w.nodeA[startIdx] = make_float4(startPos[0], startPos[1], startPos[2], 0.f);
-    w.nodeB[startIdx] = make_uint2(__float_as_uint(tot), 0xffffu | kNodeVisited | kNodeOpen);
+    w.nodeB[startIdx] = make_uint2(__float_as_uint(tot), 0xffffu | tag | kNodeOpen);
   }
   __syncwarp();
   int heapSize = 1;
@@ -769,7 +800,7 @@ __device__ __noinline__ int astarExactSlab(const StagedView sc, const WarpSlab w
     const uint2 nB = w.nodeB[nei];
     const float4 V0 = ldVert4(sc, bp->verts[li]);
     const float4 V1 = ldVert4(sc, bp->verts[(li + 1 == nv) ? 0 : li + 1]);
-    const bool isNew = act && !(nB.y & kNodeVisited);
+    const bool isNew = act && (nB.y & kNodeTagMask) != tag;
     const float nx = isNew ? (V0.x + V1.x) * 0.5f : nA.x;
     const float ny = isNew ? (V0.y + V1.y) * 0.5f : nA.y;
     const float nz = isNew ? (V0.z + V1.z) * 0.5f : nA.z;
@@ -783,7 +814,7 @@ __device__ __noinline__ int astarExactSlab(const StagedView sc, const WarpSlab w
     const float heuristic = atEnd ? 0.f : toEnd * 0.999f;
     const float ntotal = cost + heuristic;
     const bool upd = act && (isNew || !(ntotal >= __uint_as_float(nB.x)));
-    const bool wasOpen = (nB.y & kNodeOpen) != 0;
+    const bool wasOpen = !isNew && (nB.y & kNodeOpen) != 0;
     nodes += __popc(__ballot_sync(0xffffffffu, isNew));
     // commit edge by edge
     const uint32_t updMask = __ballot_sync(0xffffffffu, upd);
@@ -794,7 +825,7 @@ __device__ __noinline__ int astarExactSlab(const StagedView sc, const WarpSlab w
       const uint32_t node = __shfl_sync(0xffffffffu, nei, j);
       if (lane == j) {
         w.nodeA[nei] = make_float4(nx, ny, nz, cost);
-        w.nodeB[nei] = make_uint2(__float_as_uint(ntotal), best | kNodeVisited | kNodeOpen);
+        w.nodeB[nei] = make_uint2(__float_as_uint(ntotal), best | tag | kNodeOpen);
       }
       __syncwarp();
       if ((openMask >> j) & 1u) {
@@ -832,6 +863,7 @@ __device__ __noinline__ int astarExactSlab(const StagedView sc, const WarpSlab w
 // Returns the distance in every lane.  *needFallback is set (uniformly) when
 // the fast path cannot decide the pop order (tie for the minimum) or the
 // register open list is full.
+template <bool kGlobal>
 __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSlab w, int lane,
                                               const float* startPosIn, uint32_t startRef,
                                               const float* endPosIn, uint32_t endRef,
@@ -882,10 +914,7 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
     pathSize = 1;
     __syncwarp();
   } else {
-    const int P = sc.npolys;
-    for (int i = lane; i < P; i += 32)
-      w.nodeB[i] = make_uint2(0u, 0u);  // nobody visited
-    __syncwarp();
+    const uint32_t tag = beginSearch<kGlobal>(w, sc.npolys, lane);
     // open list: kOpenSlots register entries (total, polygon) per lane, kInfBits = empty.
     // All loops over the slots are unrolled, so the arrays live in registers.
     uint32_t t[kOpenSlots], p[kOpenSlots];
@@ -898,7 +927,7 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
     if (lane == 0) {
       const float tot = vdist(startPos, endPos) * 0.999f;
       w.nodeA[startIdx] = make_float4(startPos[0], startPos[1], startPos[2], 0.f);
-      w.nodeB[startIdx] = make_uint2(__float_as_uint(tot), 0xffffu | kNodeVisited);
+      w.nodeB[startIdx] = make_uint2(__float_as_uint(tot), 0xffffu | tag);
       t[0] = __float_as_uint(tot);
       p[0] = startIdx;
       newNodes = 1;
@@ -1082,7 +1111,7 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
       const float4 V1 = ldVert4(sc, vb);
 
       BPSN_TICK(tE1);
-      const bool isNew = act && !(nB.y & kNodeVisited);
+      const bool isNew = act && (nB.y & kNodeTagMask) != tag;
       newNodes += isNew ? 1 : 0;
       const float nx = isNew ? (V0.x + V1.x) * 0.5f : nA.x;
       const float ny = isNew ? (V0.y + V1.y) * 0.5f : nA.y;
@@ -1124,7 +1153,7 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
       BPSN_TICK(tE3);
       if (upd) {
         w.nodeA[nei] = make_float4(nx, ny, nz, cost);
-        w.nodeB[nei] = make_uint2(ntBits, best | kNodeVisited);
+        w.nodeB[nei] = make_uint2(ntBits, best | tag);
       }
       rot = (rot + 7) & 31;
       __syncwarp();
@@ -1145,7 +1174,9 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
       exactWhy = kStatOpenOverflow;
     int nodeTotal = __reduce_add_sync(0xffffffffu, newNodes);
     if (exactWhy) {
-      const int outcome = astarExactSlab(sc, w, lane, startPos, endPos, startIdx, endIdx, &nodeTotal);
+      const uint32_t exactTag = beginSearch<kGlobal>(w, sc.npolys, lane);
+      const int outcome = astarExactSlab(sc, w, lane, startPos, endPos, startIdx, endIdx, exactTag,
+                                         &nodeTotal);
       if (outcome == kAStarHeapFull) {
         *needFallback = exactWhy;  // hand the query to the global-memory emulation
         return 0.f;
@@ -1196,6 +1227,13 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
 
   BPSN_TICK(tA1);
   const float dres = warpFunnel(sc, w, lane, startPos, endPos, pathSize, status);
+  if (kGlobal) {
+    // the portals sit in the first node slots; what they left in the tag field must not
+    // pass for a visit mark of a later search
+    __syncwarp();
+    for (int i = lane; i + 1 < pathSize; i += 32)
+      w.nodeB[i].y = 0u;
+  }
   BPSN_TICK(tA2);
   BPSN_PHASE_ADD(2, tA1 - tA0);
   BPSN_PHASE_ADD(3, tA2 - tA1);
@@ -1254,7 +1292,9 @@ __device__ __forceinline__ void stepWarpQueries(const GroupDev& g, const SceneTa
       kGlobal ? globalSlabs + (static_cast<size_t>(blockIdx.x) * (blockDim.x >> 5) + warp) *
                                   globalSlabStride
               : smem + pl.slabOffset + static_cast<size_t>(warp) * warpGeoSlabBytes(pcap);
-  const WarpSlab w = carveSlab(slabBase, pcap);
+  WarpSlab w = carveSlab(slabBase, pcap);
+  if (kGlobal)
+    w.searches = reinterpret_cast<uint32_t*>(slabBase + globalSlabStride - kGlobalSlabExtra);
 
   const uint32_t B = g.B;
   const uint32_t base = g.listBase[sceneIdx];
@@ -1298,9 +1338,9 @@ __device__ __forceinline__ void stepWarpQueries(const GroupDev& g, const SceneTa
     BPSN_TICK(tQ1);
     if (needGeo) {
 #if defined(BPSN_PHASE_TIMING)
-      d = warpGeodesic(sv, w, lane, b, bref, a, aref, &status, &fallback, g.exactHeap != 0, pacc);
+      d = warpGeodesic<kGlobal>(sv, w, lane, b, bref, a, aref, &status, &fallback, g.exactHeap != 0, pacc);
 #else
-      d = warpGeodesic(sv, w, lane, b, bref, a, aref, &status, &fallback, g.exactHeap != 0);
+      d = warpGeodesic<kGlobal>(sv, w, lane, b, bref, a, aref, &status, &fallback, g.exactHeap != 0);
 #endif
     }
     BPSN_TICK(tQ2);

@@ -288,6 +288,14 @@ int32_t bpsn_gae_static(const float* rewards, float* values, const uint8_t* mask
 int32_t bpsn_selftest_sqrt(int32_t gpu_id, uint32_t first_bits, uint32_t last_bits,
                            uint64_t* mismatches);
 
+/* Diagnostic.  Scenes that are searched in global memory keep, per warp, a node array that is
+ * not wiped between searches: a node counts as visited when it carries the number of the
+ * running search (15 bits; when the number wraps the array is wiped once).  This call sets
+ * that number for every such array of `group`, so that a test can cross the wrap after a few
+ * steps instead of after 32767 searches.  No step may be in flight.  Groups whose scenes all
+ * fit in shared memory have no such arrays; the call then does nothing. */
+int32_t bpsn_debug_set_search_count(bpsn_sim* sim, uint32_t group, uint32_t count);
+
 /* Episode datasets on disk (Dataset, simulator/simulator.cpp:190-359): a directory of
  * `*.json.gz` Habitat PointNav episode files, one scene per file.  bpsn_dataset_open
  * reads them all on up to `num_threads` host threads; scenes come back in file-name

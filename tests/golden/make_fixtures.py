@@ -21,7 +21,8 @@ What it writes
                                 file path) and of the get_advantages formula
 
 Scene list: c0 = benchmark config 0 (20x20 m, 12 boxes, seed 1000); c1 = config 1 (50x50 m, 60
-boxes, seed 1001); m00..m15 = config 3's mixed batch (sides U(10,80) m, 5..150 boxes, interior
+boxes, seed 1001); d0 = a dense plan with the polygon count that config 1's description quotes
+(150x150 m, 2500 boxes, seed 1002: 16407 polygons); m00..m15 = config 3's mixed batch (sides U(10,80) m, 5..150 boxes, interior
 walls with door gaps; seeds 2000+i).
 """
 import importlib.util
@@ -42,7 +43,8 @@ SCENES = os.path.join(GOLD, "scenes")
 
 def scene_specs():
     specs = [("c0", dict(size=20, boxes=12, walls=0, seed=1000), 256),
-             ("c1", dict(size=50, boxes=60, walls=0, seed=1001), 4096)]
+             ("c1", dict(size=50, boxes=60, walls=0, seed=1001), 4096),
+             ("d0", dict(size=150, boxes=2500, walls=0, seed=1002), 4096)]
     rng = np.random.default_rng(20240)
     for i in range(16):
         sx = float(np.round(rng.uniform(10, 80), 1))

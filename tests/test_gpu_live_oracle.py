@@ -26,10 +26,14 @@ def _close(a, b, rel, abs_=0.0):
     return same | near
 
 
-def _compare_run(scene_names, n, steps, seed, mix, threads=8, check_state_every=16, **gen_kw):
+def _compare_run(scene_names, n, steps, seed, mix, threads=8, check_state_every=16,
+                 search_count=None, **gen_kw):
     from bps_nav_b200 import bps_sim
     scenes = [load_scene(s) for s in scene_names]
     gen = bps_sim.PointNavRolloutGenerator.from_scenes(scenes, n, seed=seed, **gen_kw)
+    if search_count is not None:
+        for g in range(gen.num_groups):
+            gen.debug_set_search_count(g, search_count)
     osim = pyoracle.OracleSim([(scene_path(s), sc.episodes) for s, sc in zip(scene_names, scenes)],
                               n, seed, threads=threads)
     groups = gen.num_groups
@@ -116,6 +120,25 @@ def test_everything_in_global_memory():
     _compare_run(["c1"], 2048, 48, seed=31, mix="uniform", global_memory=True)
     _compare_run(["m03", "m10", "c0", "m12"], 1024, 96, seed=32, mix="policy", global_memory=True,
                  check_state_every=32)
+
+
+def test_dense_scene_16k_polygons():
+    # 16407 polygons: the tables (and 394 KB of nodes per warp) stay in global memory; paths
+    # of up to 30 m cross a few hundred polygons
+    _compare_run(["d0"], 1024, 48, seed=77, mix="uniform", threads=16)
+    _compare_run(["d0"], 256, 32, seed=78, mix="uniform", threads=16, generic_kernel=True)
+    _compare_run(["d0", "c0"], 512, 200, seed=79, mix="policy", threads=16, check_state_every=50)
+
+
+def test_global_memory_search_numbering_wraps():
+    # Node arrays in global memory are not wiped between searches: a node is "visited" when it
+    # carries the number of the running search.  Start every array's numbering just below the
+    # 15-bit limit, so that each wraps (and is wiped once) within a few steps; the arrays hold
+    # the marks of earlier searches at that point.
+    _compare_run(["c1"], 2048, 24, seed=33, mix="uniform", global_memory=True)  # fresh numbering
+    _compare_run(["c1"], 4096, 96, seed=34, mix="uniform", global_memory=True, search_count=32760)
+    _compare_run(["m04", "m13", "m07", "c0"], 2048, 96, seed=35, mix="uniform", small_smem=True,
+                 search_count=32764)
 
 
 def test_mixed_scene_batch_large_enough_for_the_throughput_plan():
