@@ -1080,36 +1080,33 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
       const float4 bA = w.nodeA[best];
       const uint2 bB = w.nodeB[best];
 
-      const uint32_t bpar = bB.y & 0xffffu;
       const uint16_t vb = (li + 1 == nv) ? vbFirst : vbNext;
-      bool act = ej < nv && ne != 0 && !(ne & kExtLink) &&
-                 static_cast<uint32_t>(ne - 1) != bpar;
-      uint32_t nei = act ? static_cast<uint32_t>(ne - 1) : best;
+      const bool hasEdge = ej < nv && ne != 0 && !(ne & kExtLink);
+      const uint32_t nei = hasEdge ? static_cast<uint32_t>(ne - 1) : best;
+      // The neighbour's node and the edge's end points are requested as soon as the polygon
+      // record is there: they do not wait for the popped node's own record (in global
+      // memory that is a second trip to L2, now overlapped with this one).
+      const float4 nA = w.nodeA[nei];
+      const uint2 nB = w.nodeB[nei];
+      const float4 V0 = ldVert4(sc, va);
+      const float4 V1 = ldVert4(sc, vb);
+      const uint32_t bpar = bB.y & 0xffffu;
+      bool act = hasEdge && nei != bpar;
       if ((bB.x != gm) | (dupFlag & 1)) {  // one branch for the two uncommon cases
         // Entries are never updated in place: a better total for an open node adds a
         // second entry and the superseded one is dropped here, when it surfaces.  All
         // entries of a node have different totals (each is strictly below the one
         // before), so the live one is the one that matches the node's current total.
         if (bB.x != gm) {
-#if defined(BPSN_PHASE_TIMING)
-#endif
           rot = (rot + 7) & 31;
           continue;
         }
         // the polygon shares more than one edge with some neighbour
-        const uint32_t grp = __match_any_sync(0xffffffffu, act ? nei : 0xffff0000u + lane);
+        const uint32_t grp = __match_any_sync(0xffffffffu, hasEdge ? nei : 0xffff0000u + lane);
         // bit k of the rotated mask = edge k; the lowest edge of the group acts
         const uint32_t byEdge = __funnelshift_r(grp, grp, rot);
-        if (act && (__ffs(byEdge) - 1) != ej) {
-          act = false;
-          nei = best;
-        }
+        act = act && (__ffs(byEdge) - 1) == ej;
       }
-      const float4 nA = w.nodeA[nei];
-      const uint2 nB = w.nodeB[nei];
-      const float4 V0 = ldVert4(sc, va);
-      const float4 V1 = ldVert4(sc, vb);
-
       BPSN_TICK(tE1);
       const bool isNew = act && (nB.y & kNodeTagMask) != tag;
       newNodes += isNew ? 1 : 0;
