@@ -255,11 +255,12 @@ __device__ __forceinline__ bool explVisit(const GroupDev& g, uint32_t e, float p
 }
 
 // BaseSimulator::reset + InfoFunctor::reset + RewardFunctor::reset for one env.
-__device__ __forceinline__ void resetEnv(const GroupDev& g, const SceneTable& st, uint32_t e,
-                                         uint32_t seedLo, uint32_t seedHi) {
+// (`sceneIdx` = g.scene[e] and `rc` = g.resetCount[e], read by the caller together with whatever
+// else it needs from the environment's columns, so that all of it is one trip to memory)
+__device__ __forceinline__ void resetEnvLoaded(const GroupDev& g, const SceneTable& st, uint32_t e,
+                                               uint32_t sceneIdx, uint32_t rc, uint32_t seedLo,
+                                               uint32_t seedHi) {
   const uint32_t B = g.B;
-  const uint32_t sceneIdx = g.scene[e];
-  const uint32_t rc = g.resetCount[e];
   const uint32_t r = philoxFirst(g.envBase + e, rc, 0u, 0u, seedLo, seedHi);
   const uint32_t nEp = st.epCount[sceneIdx];
   const uint32_t idx = __umulhi(r, nEp);
@@ -330,6 +331,10 @@ __device__ __forceinline__ void resetEnv(const GroupDev& g, const SceneTable& st
     g.prevDist[e] = 0.f;  // numVisited = size - 1 = 0
   }
 }
+__device__ __forceinline__ void resetEnv(const GroupDev& g, const SceneTable& st, uint32_t e,
+                                         uint32_t seedLo, uint32_t seedHi) {
+  resetEnvLoaded(g, st, e, g.scene[e], g.resetCount[e], seedLo, seedHi);
+}
 
 // InfoFunctor::step + RewardFunctor::step, then the in-loop reset when done.
 // `d` is the geodesic distance of this step (ignored when the task or the
@@ -338,21 +343,47 @@ __device__ __forceinline__ void finishEnv(const GroupDev& g, const SceneTable& s
                                           bool done, bool moved, float d, uint32_t seedLo,
                                           uint32_t seedHi) {
   const uint32_t B = g.B;
+  // Everything this function reads from the environment's columns is requested here, before
+  // the first store: the columns may alias as far as the compiler knows, so a load placed
+  // after a store waits for it, and each such wait is a trip to L2.
   const float prev = g.prevDist[e];
+  const float epr0 = g.episodeReward[e];
+  const bool pointNav = g.task == kTaskPointNav;
+  float init = 0.f, cum = 0.f, px = 0.f, py = 0.f, pz = 0.f, qx = 0.f, qy = 0.f, qz = 0.f;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f, s4 = 0.f;
+  uint32_t sceneIdx = 0u, rc = 0u;
+  if (done) {
+    s0 = g.stats[e];
+    s1 = g.stats[B + e];
+    s2 = g.stats[2 * B + e];
+    s3 = g.stats[3 * B + e];
+    s4 = g.stats[4 * B + e];
+    sceneIdx = g.scene[e];
+    rc = g.resetCount[e];
+    if (pointNav) {
+      init = g.initDist[e];
+      cum = g.cumTravel[e];
+    }
+  } else if (moved && pointNav) {
+    cum = g.cumTravel[e];
+    px = g.pos[e];
+    py = g.pos[B + e];
+    pz = g.pos[2 * B + e];
+    qx = g.prevPos[e];
+    qy = g.prevPos[B + e];
+    qz = g.prevPos[2 * B + e];
+  }
   float success = 0, spl = 0, reward;
-  if (g.task == kTaskPointNav) {
+  if (pointNav) {
     if (done) {
       success = d < kSuccessDistance ? 1.f : 0.f;
-      const float init = g.initDist[e];
-      const float cum = g.cumTravel[e];
       const float mx = (init < cum) ? cum : init;  // std::max(init, cum)
       spl = success * init / mx;
     } else if (moved) {
-      const float px = g.pos[e], py = g.pos[B + e], pz = g.pos[2 * B + e];
-      const float dx = px - g.prevPos[e];
-      const float dy = py - g.prevPos[B + e];
-      const float dz = pz - g.prevPos[2 * B + e];
-      g.cumTravel[e] += sqrtExact(dx * dx + dy * dy + dz * dz);
+      const float dx = px - qx;
+      const float dy = py - qy;
+      const float dz = pz - qz;
+      g.cumTravel[e] = cum + sqrtExact(dx * dx + dy * dy + dz * dz);
       g.prevDist[e] = d;
       g.prevPos[e] = px;
       g.prevPos[B + e] = py;
@@ -406,15 +437,15 @@ __device__ __forceinline__ void finishEnv(const GroupDev& g, const SceneTable& s
   // current_episode_reward += reward; on done the episode's totals go to the
   // running sums and the accumulator restarts (same fp32 operations, in step
   // order, as the trainer's tensor code)
-  const float epr = g.episodeReward[e] + reward;
+  const float epr = epr0 + reward;
   if (done) {
-    g.stats[e] += epr;
-    g.stats[B + e] += 1.f;
-    g.stats[2 * B + e] += success;
-    g.stats[3 * B + e] += spl;
-    g.stats[4 * B + e] += d;
+    g.stats[e] = s0 + epr;
+    g.stats[B + e] = s1 + 1.f;
+    g.stats[2 * B + e] = s2 + success;
+    g.stats[3 * B + e] = s3 + spl;
+    g.stats[4 * B + e] = s4 + d;
     g.episodeReward[e] = 0.f;
-    resetEnv(g, st, e, seedLo, seedHi);
+    resetEnvLoaded(g, st, e, sceneIdx, rc, seedLo, seedHi);
   } else {
     g.episodeReward[e] = epr;
   }
