@@ -47,7 +47,7 @@ L2_FLUSH_BYTES = 256 << 20
 # (profiles/k_step_warp_config1_ncu_full.md); only meaningful for the default workload
 LARGE_BATCH_ENVS = 32768
 DENSE_SCENE = "d0"
-NCU_TRAFFIC_BYTES = {("c1", 4096, "uniform", "k_step"): 0.89e6}
+NCU_TRAFFIC_BYTES = {("c1", 4096, "uniform", "k_step"): 0.87e6}
 
 
 def parse_args():
