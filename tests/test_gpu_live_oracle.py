@@ -122,6 +122,15 @@ def test_everything_in_global_memory():
                  check_state_every=32)
 
 
+def test_sixty_four_scene_slots():
+    # the widest configuration the benchmark names: 64 scene slots in one group (the 16 mixed
+    # floor plans, each loaded four times), first with every scene in shared memory, then at a
+    # batch that is large enough for the planner to move the group to global memory
+    names = [f"m{i:02d}" for i in range(16)] * 4
+    _compare_run(names, 4096, 24, seed=64, mix="uniform", threads=16, check_state_every=8)
+    _compare_run(names, 16384, 12, seed=65, mix="uniform", threads=16, check_state_every=6)
+
+
 def test_dense_scene_16k_polygons():
     # 16407 polygons: the tables (and 394 KB of nodes per warp) stay in global memory; paths
     # of up to 30 m cross a few hundred polygons
