@@ -64,6 +64,7 @@ struct Group {
   WarpPlan* dPlan = nullptr;    // [numScenes]
   uint8_t* globalSlabs = nullptr;  // warp slabs of the scenes that are worked on in global memory
   size_t globalSlabStride = 0;     // bytes between consecutive slabs there (the largest scene's)
+  size_t numGlobalSlabs = 0;       // one per warp of the grid, or one per environment
   uint2* dCtaMap = nullptr;     // [numCtas] (scene, rank within the scene)
   AStarScratch* fallbackScratch = nullptr;
   float* depth = nullptr;  // [B][H][W] when a render size was configured
@@ -305,6 +306,8 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
     // fit, at most 16.  A scene that leaves no room for a slab goes to the generic kernel.
     // CTAs are dealt to the scenes in proportion to environments / warps-per-CTA, so that
     // every scene's list drains in about the same time.
+    const size_t kSlabPerEnvAbove = size_t(512) << 20;  // bytes of per-warp slabs from which on ...
+    const size_t kSlabPerEnvBudget = size_t(32) << 30;  // ... and bytes of per-env slabs up to which
     const size_t kSmemMax = ((sim->cfg.flags & BPSN_FLAG_SMEM_96K) ? 96 : 227) * 1024 - 64;  // per CTA, minus the kernel's static shared memory
     std::vector<WarpPlan> plan(ns, WarpPlan{16u, 0u, 0u, 0u});
     size_t maxGlobalSlab = 0;
@@ -432,8 +435,15 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
                                 sizeof(AStarScratch) * static_cast<size_t>(g.numCtas) * 16));
       g.globalSlabStride = maxGlobalSlab ? maxGlobalSlab + kGlobalSlabExtra : 0;
       if (maxGlobalSlab) {
+        // One slab per warp of the grid; one per environment instead when the warps' slabs
+        // together would not stay in L2 anyway and the environments' fit a memory budget.
+        const size_t warpSlabs = static_cast<size_t>(g.numCtas) * 16;
+        const bool perEnv = warpSlabs * g.globalSlabStride > kSlabPerEnvAbove &&
+                            static_cast<size_t>(B) * g.globalSlabStride <= kSlabPerEnvBudget;
+        g.numGlobalSlabs = perEnv ? static_cast<size_t>(B) : warpSlabs;
+        d.slabPerEnv = perEnv ? 1u : 0u;
         // zeroed: search counters at 0, no node carries a visit tag
-        const size_t bytes = g.globalSlabStride * g.numCtas * 16;
+        const size_t bytes = g.globalSlabStride * g.numGlobalSlabs;
         BPSN_CUDA(sim, cudaMalloc(&g.globalSlabs, bytes));
         BPSN_CUDA(sim, cudaMemset(g.globalSlabs, 0, bytes));
       }
@@ -1259,7 +1269,7 @@ int32_t bpsn_debug_set_search_count(bpsn_sim* sim, uint32_t group, uint32_t coun
     return BPSN_OK;  // every slab of this group lives in shared memory
   BPSN_CUDA(sim, cudaSetDevice(sim->cfg.gpu_id));
   BPSN_CUDA(sim, cudaDeviceSynchronize());
-  const size_t slabs = static_cast<size_t>(g.numCtas) * 16;
+  const size_t slabs = g.numGlobalSlabs;
   std::vector<uint32_t> h(slabs, count);
   BPSN_CUDA(sim, cudaMemcpy2D(g.globalSlabs + g.globalSlabStride - kGlobalSlabExtra,
                               g.globalSlabStride, h.data(), sizeof(uint32_t), sizeof(uint32_t),

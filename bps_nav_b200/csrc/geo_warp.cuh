@@ -1285,13 +1285,15 @@ __device__ __forceinline__ void stepWarpQueries(const GroupDev& g, const SceneTa
   sv.polyMask = sc.polyMask;
   sv.refBase = sc.refBase;
   // (global memory: one stride for all scenes, slabs of different sizes must not overlap)
-  uint8_t* slabBase =
-      kGlobal ? globalSlabs + (static_cast<size_t>(blockIdx.x) * (blockDim.x >> 5) + warp) *
-                                  globalSlabStride
-              : smem + pl.slabOffset + static_cast<size_t>(warp) * warpGeoSlabBytes(pcap);
-  WarpSlab w = carveSlab(slabBase, pcap);
-  if (kGlobal)
-    w.searches = reinterpret_cast<uint32_t*>(slabBase + globalSlabStride - kGlobalSlabExtra);
+  // (global memory: carved per query below)
+  WarpSlab w = carveSlab(
+      kGlobal ? globalSlabs : smem + pl.slabOffset + static_cast<size_t>(warp) * warpGeoSlabBytes(pcap),
+      pcap);
+  // Large slabs (the group's slabs together exceed what L2 holds) belong to environments
+  // instead: an environment's searches start from the same goal step after step and touch
+  // nearly the same nodes, so its own slab is still warm in L2 from the step before, whereas
+  // a warp meets a different environment every step.
+  const bool slabPerEnv = kGlobal && g.slabPerEnv != 0u;
 
   const uint32_t B = g.B;
   const uint32_t base = g.listBase[sceneIdx];
@@ -1314,6 +1316,14 @@ __device__ __forceinline__ void stepWarpQueries(const GroupDev& g, const SceneTa
 #endif
     const uint32_t entry = g.geoList[base + q];
     const uint32_t e = entry & kListEnvMask;
+    if (kGlobal) {
+      const size_t slabIdx =
+          slabPerEnv ? static_cast<size_t>(e)
+                     : static_cast<size_t>(blockIdx.x) * (blockDim.x >> 5) + static_cast<size_t>(warp);
+      uint8_t* slab = globalSlabs + slabIdx * globalSlabStride;
+      w = carveSlab(slab, pcap);
+      w.searches = reinterpret_cast<uint32_t*>(slab + globalSlabStride - kGlobalSlabExtra);
+    }
     const bool done = entry & kListDone, moved = entry & kListMoved;
     const float b[3] = {g.navGoal[e], g.navGoal[B + e], g.navGoal[2 * B + e]};
     const uint32_t bref = g.goalRef[e];

@@ -61,6 +61,7 @@ struct GroupDev {
   uint32_t infoWidth;  // floats per env in `info`: 3 (PointNav) or 1 (Flee, Exploration)
   uint32_t exactHeap;  // test switch: every warp search uses the slab heap (geo_warp.cuh)
   uint32_t numScenes;  // scenes of the simulator (length of the per-scene tables)
+  uint32_t slabPerEnv;  // global-memory slabs are indexed by environment, not by warp (geo_warp.cuh)
   // pose / task state, each [B] (vectors are component-major: x[B] y[B] z[B])
   float* pos;      // [3][B]  position_
   float* rot;      // [4][B]  rotation_ (x y z w)
