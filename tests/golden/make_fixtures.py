@@ -1,5 +1,5 @@
-"""Generates every fixture under tests/golden/ (run from the repository root, in the container that
-has the reference tree mounted at /root/reference):
+"""Generates every fixture under tests/golden/ (run from the repository root, on a machine that
+has the reference tree where oracle/Makefile's REF variable points):
 
     make -C oracle ref sim && python tests/golden/make_fixtures.py
 
