@@ -340,15 +340,14 @@ __device__ __forceinline__ void resetEnv(const GroupDev& g, const SceneTable& st
 // InfoFunctor::step + RewardFunctor::step, then the in-loop reset when done.
 // `d` is the geodesic distance of this step (ignored when the task or the
 // action did not ask for one).
-__device__ __forceinline__ void finishEnv(const GroupDev& g, const SceneTable& st, uint32_t e,
-                                          bool done, bool moved, float d, uint32_t seedLo,
-                                          uint32_t seedHi) {
+// (`prev` = g.prevDist[e] and `epr0` = g.episodeReward[e], read by the caller)
+__device__ __forceinline__ void finishEnvLoaded(const GroupDev& g, const SceneTable& st, uint32_t e,
+                                                bool done, bool moved, float d, float prev,
+                                                float epr0, uint32_t seedLo, uint32_t seedHi) {
   const uint32_t B = g.B;
   // Everything this function reads from the environment's columns is requested here, before
   // the first store: the columns may alias as far as the compiler knows, so a load placed
   // after a store waits for it, and each such wait is a trip to L2.
-  const float prev = g.prevDist[e];
-  const float epr0 = g.episodeReward[e];
   const bool pointNav = g.task == kTaskPointNav;
   float init = 0.f, cum = 0.f, px = 0.f, py = 0.f, pz = 0.f, qx = 0.f, qy = 0.f, qz = 0.f;
   float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f, s4 = 0.f;
@@ -451,6 +450,11 @@ __device__ __forceinline__ void finishEnv(const GroupDev& g, const SceneTable& s
     g.episodeReward[e] = epr;
   }
 }
+__device__ __forceinline__ void finishEnv(const GroupDev& g, const SceneTable& st, uint32_t e,
+                                          bool done, bool moved, float d, uint32_t seedLo,
+                                          uint32_t seedHi) {
+  finishEnvLoaded(g, st, e, done, moved, d, g.prevDist[e], g.episodeReward[e], seedLo, seedHi);
+}
 
 // MoveForward of handleMovement: target = position + rotation * (0, 0, -0.25),
 // PathFinder::tryStep from the navmesh position, then position = result and the
@@ -497,7 +501,15 @@ k_pre(GroupDev g, SceneTable st, const int64_t* __restrict__ actions,
   // host-supplied actions arrive validated and narrowed to one byte each, in pinned
   // host memory that the kernel reads in place (no staging copy in the stream)
   const int64_t action = actions8 ? static_cast<int64_t>(actions8[e]) : actions[e];
+  // every column value any branch below needs is requested now, together with the action
+  // (which may come over the bus), so that the branches do not add trips to memory
   const uint32_t step = g.step[e] + 1;
+  float qx = g.rot[e], qy = g.rot[B + e], qz = g.rot[2 * B + e], qw = g.rot[3 * B + e];
+  const float px = g.pos[e], py = g.pos[B + e], pz = g.pos[2 * B + e];
+  const float gx = g.goal[e], gy = g.goal[B + e], gz = g.goal[2 * B + e];
+  const uint32_t sceneIdx = g.scene[e];
+  const float prev = g.prevDist[e];
+  const float epr0 = g.episodeReward[e];
   g.step[e] = step;
   bool done = static_cast<float>(step) >= kMaxSteps;
   bool moved = false;
@@ -506,7 +518,6 @@ k_pre(GroupDev g, SceneTable st, const int64_t* __restrict__ actions,
   } else if (action == 1) {
     moved = true;
   } else {
-    float qx = g.rot[e], qy = g.rot[B + e], qz = g.rot[2 * B + e], qw = g.rot[3 * B + e];
     if (action == 2 || action == 3) {
       const float ox = action == 2 ? tc.lx : tc.rx;
       const float oy = action == 2 ? tc.ly : tc.ry;
@@ -529,8 +540,7 @@ k_pre(GroupDev g, SceneTable st, const int64_t* __restrict__ actions,
       // environment and leaves its pose untouched.
       g.status[e] |= kStatBadAction;
     }
-    writePolar(g, e, g.pos[e], g.pos[B + e], g.pos[2 * B + e], qx, qy, qz, qw, g.goal[e],
-               g.goal[B + e], g.goal[2 * B + e]);
+    writePolar(g, e, px, py, pz, qx, qy, qz, qw, gx, gy, gz);
   }
   const bool listed = done || moved;
   const unsigned running = __activemask();
@@ -539,7 +549,6 @@ k_pre(GroupDev g, SceneTable st, const int64_t* __restrict__ actions,
     // the list entry carries what the step kernel has to know about the action
     const uint32_t entry = e | (done ? kListDone : 0u) | (moved ? kListMoved : 0u);
     // one atomic per (warp, scene) instead of one per environment
-    const uint32_t sceneIdx = g.scene[e];
     const unsigned grp = __match_any_sync(listedMask, sceneIdx);
     const int leader = __ffs(grp) - 1;
     const int lane = threadIdx.x & 31;
@@ -550,7 +559,7 @@ k_pre(GroupDev g, SceneTable st, const int64_t* __restrict__ actions,
     const uint32_t slot = base + __popc(grp & ((1u << lane) - 1u));
     g.geoList[g.listBase[sceneIdx] + slot] = entry;
   } else {
-    finishEnv(g, st, e, false, false, 0.f, seedLo, seedHi);
+    finishEnvLoaded(g, st, e, false, false, 0.f, prev, epr0, seedLo, seedHi);
   }
 }
 
