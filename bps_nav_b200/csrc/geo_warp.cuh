@@ -944,6 +944,10 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
     // new open entry is kept in the *evaluating* lane's own registers, without any
     // cross-lane traffic, and the entries spread over the warp.
     int rot = 0;
+    // a two-way tie that is being expanded in place: expansions still to check, the tied
+    // total, the polygon that goes second
+    int tiePending = 0;
+    uint32_t tieTotal = 0u, tieOther = 0u;
 
     // The loop body has one conditional branch on its common path besides the two
     // uncommon-case tests after the loads (a branch costs about as much as a
@@ -1008,16 +1012,62 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
           const uint32_t liveHolders = __ballot_sync(0xffffffffu, lc != 0);
           const bool liveMulti = __any_sync(0xffffffffu, lc > 1);
           if (__popc(liveHolders) > 1 || liveMulti) {
-            exactWhy = kStatTieFallback;  // a real tie: the heap's order decides
-            break;
-          }
-          if (liveHolders == 0u) {  // only superseded entries surfaced: drop them
+            // A real tie: the heap's order decides which is popped first.  When exactly two
+            // polygons tie, neither is the end polygon, they are not adjacent and share no
+            // neighbour, and (checked below, after each of the two expansions) neither
+            // expansion writes a total at or below the tied one, then both are popped before
+            // anything else in either order and the two orders leave the same nodes and the
+            // same open set behind: they are expanded one after the other here.  Anything
+            // else goes to the exact redo.
+            bool resolved = false;
+            if (__popc(liveHolders) == 2 && !liveMulti && tiePending == 0) {
+              const uint32_t p0 = __shfl_sync(0xffffffffu, livePoly, __ffs(liveHolders) - 1);
+              const uint32_t p1 = __shfl_sync(0xffffffffu, livePoly, 31 - __clz(liveHolders));
+              const uint32_t first = min(p0, p1), second = max(p0, p1);
+              if (first != endIdx && second != endIdx) {
+                // lanes 0..5: the neighbours of the first, lanes 6..11: of the second
+                uint32_t key = 0xffffffffu;
+                const bool sideB = lane >= kVertsPerPoly;
+                if (lane < 2 * kVertsPerPoly) {
+                  const NavPoly* q = &sc.polys[sideB ? second : first];
+                  const int jj = sideB ? lane - kVertsPerPoly : lane;
+                  const uint16_t qn = q->neis[jj];
+                  if (jj < q->vertCount && qn != 0 && !(qn & kExtLink))
+                    key = static_cast<uint32_t>(qn - 1);
+                }
+                bool touch = false;
 #pragma unroll
-            for (int k = 0; k < kOpenSlots; ++k)
-              t[k] = m[k] ? kInfBits : t[k];
-            continue;
+                for (int jj = 0; jj < kVertsPerPoly; ++jj) {
+                  const uint32_t other = __shfl_sync(0xffffffffu, key, jj);
+                  touch = touch || (sideB && key == other);
+                }
+                touch = key != 0xffffffffu && (touch || key == (sideB ? first : second));
+                if (!__any_sync(0xffffffffu, touch)) {
+                  resolved = true;
+                  best = first;
+                  tieOther = second;
+                  tieTotal = gm;
+                  tiePending = 2;
+                  // the second polygon keeps its entry: it is the minimum of the next pop
+#pragma unroll
+                  for (int k = 0; k < kOpenSlots; ++k)
+                    m[k] = m[k] && p[k] != second;
+                }
+              }
+            }
+            if (!resolved) {
+              exactWhy = kStatTieFallback;
+              break;
+            }
+          } else {
+            if (liveHolders == 0u) {  // only superseded entries surfaced: drop them
+#pragma unroll
+              for (int k = 0; k < kOpenSlots; ++k)
+                t[k] = m[k] ? kInfBits : t[k];
+              continue;
+            }
+            best = __shfl_sync(0xffffffffu, livePoly, __ffs(liveHolders) - 1);
           }
-          best = __shfl_sync(0xffffffffu, livePoly, __ffs(liveHolders) - 1);
         }
         if (best == endIdx) {
           reached = true;
@@ -1133,6 +1183,16 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
       const uint32_t ntBits = __float_as_uint(ntotal);
       // open or closed alike: skipped unless strictly better (DetourNavMeshQuery.cpp:1075-1080)
       const bool upd = act && (isNew || !(ntotal >= __uint_as_float(nB.x)));
+      if (tiePending) {
+        // one of the two expansions of a resolved tie (see the pop): it has to be the expected
+        // polygon and must not write a total that the other order would have popped first
+        if ((tiePending == 1 && best != tieOther) ||
+            __any_sync(0xffffffffu, upd && ntBits <= tieTotal)) {
+          exactWhy = kStatTieFallback;
+          break;
+        }
+        --tiePending;
+      }
 
       BPSN_TICK(tE2);
       // ---- the new entry goes into this lane's first free register pair
