@@ -1082,6 +1082,9 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
           for (int k = 0; k < kOpenSlots; ++k) {
             t[k] = m[k] ? kInfBits : t[k];  // (the popped entry first)
             m[k] = false;                   // done: the pairs may be refilled just below
+            // superseded entries (their total is no longer their node's) only take up room
+            const bool stale = t[k] != kInfBits && w.nodeB[p[k]].x != t[k];
+            t[k] = stale ? kInfBits : t[k];
             f[k] = t[k] == kInfBits;
             freeCnt += f[k] ? 1 : 0;
           }
