@@ -1044,6 +1044,7 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
                 touch = key != 0xffffffffu && (touch || key == (sideB ? first : second));
                 if (!__any_sync(0xffffffffu, touch)) {
                   resolved = true;
+                  *status |= kStatTieInPlace;
                   best = first;
                   tieOther = second;
                   tieTotal = gm;

@@ -135,6 +135,7 @@ enum QueryStatus : uint32_t {
   kStatTieFallback = 1u << 8,   // open-list tie: query rerun with the exact heap emulation
   kStatOpenOverflow = 1u << 9,  // register open list full, or a zero / out-of-range distance in the
                                 // fast search: query rerun the same way
+  kStatTieInPlace = 1u << 10,   // a two-way open-list tie whose order cannot matter was expanded in place
 };
 
 }  // namespace bpsn
