@@ -99,19 +99,19 @@ class _RolloutGenerator:
     def from_scenes(cls, scenes, num_environments, num_active_scenes=None, gpu_id=0,
                     render_resolution=(64, 64), color=False, depth=False, double_buffered=False,
                     seed=0, host_mirrors=True, generic_kernel=False, exact_heap=False,
-                    small_smem=False, global_memory=False):
+                    small_smem=False, global_memory=False, small_pool=False):
         """Builds a generator from in-memory ``dataset.Scene`` objects (no JSON involved)."""
         self = cls.__new__(cls)
         if num_active_scenes is None:
             num_active_scenes = len(scenes)
         self._setup(list(scenes), num_environments, num_active_scenes, gpu_id, render_resolution,
                     color, depth, double_buffered, seed, host_mirrors, generic_kernel, exact_heap,
-                    small_smem, global_memory)
+                    small_smem, global_memory, small_pool)
         return self
 
     def _setup(self, scenes, num_environments, num_active_scenes, gpu_id, render_resolution, color,
                depth, double_buffered, seed, host_mirrors, generic_kernel=False, exact_heap=False,
-               small_smem=False, global_memory=False):
+               small_smem=False, global_memory=False, small_pool=False):
         if self._task not in _TASKS:
             raise NotImplementedError(f"{type(self).__name__}: unknown task")
         self._task_id, self._info_dtype = _TASKS[self._task]
@@ -138,7 +138,8 @@ class _RolloutGenerator:
                        (L.FLAG_GENERIC_KERNEL if generic_kernel else 0) |
                        (L.FLAG_EXACT_HEAP if exact_heap else 0) |
                        (L.FLAG_SMEM_96K if small_smem else 0) |
-                       (L.FLAG_GLOBAL_MEMORY if global_memory else 0),
+                       (L.FLAG_GLOBAL_MEMORY if global_memory else 0) |
+                       (L.FLAG_SMALL_POOL if small_pool else 0),
                        task=self._task_id,
                        render_width=self._res[0] if self._depth else 0,
                        render_height=self._res[1] if self._depth else 0)

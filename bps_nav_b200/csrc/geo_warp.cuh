@@ -16,10 +16,13 @@
 //     (DetourNavMeshQuery.cpp:2118-2132);
 //   * the forward move (moveAlongSurface, getPolyHeight) takes one lane per edge
 //     of the polygon at the head of its queue and 32 detail triangles at a time;
-//   * A* nodes are direct-mapped, one slot per polygon (a single tile has one
-//     search node per polygon: dtNavMeshQuery::findPath only creates extra
-//     nodes per polygon for tile-border links, DetourNavMeshQuery.cpp:1040-1045)
-//     in the warp's private shared-memory slab;
+//   * A* nodes live in a small per-warp pool in order of first visit, found through
+//     a polygon -> slot table (a single tile has one search node per polygon:
+//     dtNavMeshQuery::findPath only creates extra nodes per polygon for tile-border
+//     links, DetourNavMeshQuery.cpp:1040-1045).  Table and pool are the warp's
+//     private slab; a search that visits more polygons than the pool holds is
+//     handed to the one-thread emulation (geodesic()) like a heap that outgrew its
+//     array.  Which slot a node gets does not influence any result;
 //   * the open list lives in registers, three (total, polygon) entries per lane;
 //     "pop" is three hardware warp reductions (minimum total, how many entries
 //     hold it, the holder's polygon).  A binary heap and an arg-min return the
@@ -52,39 +55,19 @@
 
 namespace bpsn {
 
-#if defined(BPSN_PHASE_TIMING)
-// Developer instrumentation (not compiled into the shipped library): cycles
-// spent per phase of k_step_warp, summed over queries, and per-phase maxima.
-// [0] staging  [1] state load + forward move  [2] A*  [3] funnel  [4] finish
-// [5] queries  [6..10] per-phase max  [12] pop cycles [13] expand cycles [14] pops
-__device__ unsigned long long g_phaseCycles[24];
-#define BPSN_TICK(var) const long long var = clock64()
-struct PhaseAcc {
-  unsigned long long sum[5];
-  unsigned long long mx[5];
-  unsigned long long queries, popCycles, expandCycles, pops;
-  unsigned long long exLoad, exMath, exBook;
-};
-__device__ __forceinline__ void phaseAdd(PhaseAcc* a, int idx, long long cycles) {
-  a->sum[idx] += static_cast<unsigned long long>(cycles);
-  if (static_cast<unsigned long long>(cycles) > a->mx[idx])
-    a->mx[idx] = static_cast<unsigned long long>(cycles);
-}
-#define BPSN_PHASE_ADD(idx, cycles) phaseAdd(pacc, idx, cycles)
-#else
-#define BPSN_TICK(var)
-#define BPSN_PHASE_ADD(idx, cycles)
-#endif
 
 constexpr uint32_t kInfBits = 0x7f800000u;
 constexpr int kOpenSlots = 3;  // register open-list entries per lane (96 per warp)
-// nodeB.y = parent (16 bits) | kNodeOpen | visit tag (15 bits).  A node belongs to the running
-// search iff its tag is the search's; anything else (zero, or the tag of an earlier search on
-// the same slab) reads as "not visited yet".
-constexpr uint32_t kNodeOpen = 0x10000u;  // exact search only: the node is in the heap
-constexpr uint32_t kNodeTagMask = 0xfffe0000u;
-constexpr uint32_t kNodeTagOne = 0x20000u;
-constexpr uint32_t kNodeTagMax = 32767u;
+// nodeB.y = polygon of the parent (16 bits) | slot of the parent (12 bits) | kNodeOpen.
+constexpr uint32_t kNodeOpen = 0x10000000u;  // exact search only: the node is in the heap
+constexpr uint32_t kNoSlot = 0xfffu;         // parent slot of the start node
+constexpr int kMaxPoolNodes = kMaxAStarNodes;  // dtNodePool never hands out more (PathFinder.cpp:247)
+// Polygon -> slot table of a slab in global memory: visit tag (20 bits) | slot (12 bits).  An
+// entry belongs to the running search iff its tag is the search's; anything else (zero, or the
+// tag of an earlier search on the same slab) reads as "not visited yet".
+constexpr uint32_t kTableSlotMask = 0xfffu;
+constexpr uint32_t kTableTagShift = 12;
+constexpr uint32_t kTableTagMax = (1u << 20) - 1u;
 
 // Shared-memory layout of a staged scene (byte offsets, each 16-byte aligned).
 struct StagedLayout {
@@ -112,35 +95,63 @@ __host__ __device__ inline StagedLayout stagedLayout(int nverts, int npolys, int
   return l;
 }
 
-// Per-warp slab for node capacity pcap (a multiple of 16):
-//   nodeA  float4 {x, y, z, cost}                      16 B / polygon
-//   nodeB  uint2  {total bits, parent | open | tag}      8 B / polygon
-//   path   uint16 corridor, at most 256 polygons       512 B
-// After the search the node arrays are reused for the corridor's portals.
+// Per-warp slab for a scene of pcap polygons (a multiple of 16) and a pool of K nodes (even):
+//   nodeA  float4 {x, y, z, cost}                              16 B / node
+//   nodeB  uint2  {total bits, parent polygon | parent slot}     8 B / node
+//   table  polygon -> slot: uint16 (slot + 1, 0 = not visited) per polygon in shared memory,
+//          uint32 (visit tag | slot) per polygon in global memory
+//   path   uint16 corridor, at most 256 polygons               512 B
+// After the search the first node slots are reused for the corridor's portals (a corridor is
+// never longer than the number of nodes the search created).
 // A slab in global memory keeps its contents from one search (and launch) to the next and
 // carries, in the last 16 bytes of its stride, the number of searches it has seen: that number
-// is the visit tag, so a search does not have to wipe the node array first (on a
-// 16 000-polygon mesh wiping costs as much as the search).  Shared-memory slabs start every
-// search from a wiped array.
-__host__ __device__ inline size_t warpGeoSlabBytes(int pcap) {
-  return static_cast<size_t>(pcap) * 24 + 512;
+// is the visit tag, so a search does not have to wipe the table first.  Shared-memory slabs
+// start every search from a wiped table (2 bytes per polygon).
+__host__ __device__ inline size_t warpGeoSlabBytes(int pcap, int nodeCap, bool inGlobal) {
+  return static_cast<size_t>(nodeCap) * 24 + static_cast<size_t>(pcap) * (inGlobal ? 4 : 2) + 512;
 }
 constexpr size_t kGlobalSlabExtra = 16;  // the search counter of a global-memory slab
 
 struct WarpSlab {
   float4* nodeA;
   uint2* nodeB;
+  void* table;         // uint16[pcap] (shared memory) or uint32[pcap] (global memory)
   uint16_t* path;
   uint32_t* searches;  // global-memory slabs only: the search counter
+  int nodeCap;         // nodes the pool holds
+  int tableLen;        // entries of the table (the scene's polygon capacity)
 };
 
-__device__ __forceinline__ WarpSlab carveSlab(uint8_t* base, int pcap) {
+__device__ __forceinline__ WarpSlab carveSlab(uint8_t* base, int pcap, int nodeCap, bool inGlobal) {
   WarpSlab s;
   s.nodeA = reinterpret_cast<float4*>(base);
-  s.nodeB = reinterpret_cast<uint2*>(base + static_cast<size_t>(pcap) * 16);
-  s.path = reinterpret_cast<uint16_t*>(base + static_cast<size_t>(pcap) * 24);
+  s.nodeB = reinterpret_cast<uint2*>(base + static_cast<size_t>(nodeCap) * 16);
+  s.table = base + static_cast<size_t>(nodeCap) * 24;
+  s.path = reinterpret_cast<uint16_t*>(base + static_cast<size_t>(nodeCap) * 24 +
+                                       static_cast<size_t>(pcap) * (inGlobal ? 4 : 2));
   s.searches = nullptr;
+  s.nodeCap = nodeCap;
+  s.tableLen = pcap;
   return s;
+}
+
+// Polygon -> slot.  `tag` is the running search's tag, already shifted (global memory only).
+// Returns the slot, or -1 when the polygon has no node in this search.
+template <bool kGlobal>
+__device__ __forceinline__ int tableLookup(const WarpSlab& w, uint32_t poly, uint32_t tag) {
+  if (kGlobal) {
+    const uint32_t v = static_cast<const uint32_t*>(w.table)[poly];
+    return (v & ~kTableSlotMask) == tag ? static_cast<int>(v & kTableSlotMask) : -1;
+  }
+  return static_cast<int>(static_cast<const uint16_t*>(w.table)[poly]) - 1;
+}
+template <bool kGlobal>
+__device__ __forceinline__ void tableInsert(const WarpSlab& w, uint32_t poly, uint32_t slot,
+                                            uint32_t tag) {
+  if (kGlobal)
+    static_cast<uint32_t*>(w.table)[poly] = tag | slot;
+  else
+    static_cast<uint16_t*>(w.table)[poly] = static_cast<uint16_t>(slot + 1u);
 }
 
 // The staged tables as the search sees them.  Passed by value so that the
@@ -235,10 +246,8 @@ __device__ __forceinline__ float warpFunnel(const StagedView sc, const WarpSlab 
                                             const float* startPos, const float* endPos,
                                             int pathSize, uint32_t* status) {
   float closestStart[3], closestEnd[3];
-  BPSN_TICK(tF0);
   warpClosestOnBoundary(sc, lane, w.path[0], startPos, w.path[pathSize - 1], endPos, closestStart,
                         closestEnd);
-  BPSN_TICK(tF1);
   bool bad = false;
   for (int i = lane; i + 1 < pathSize; i += 32) {
     const NavPoly* from = &sc.polys[w.path[i]];
@@ -267,13 +276,9 @@ __device__ __forceinline__ float warpFunnel(const StagedView sc, const WarpSlab 
     return BPSN_INF;
   }
   __syncwarp();
-  BPSN_TICK(tF2);
 
   float result = 0.f;
   uint32_t st = 0;
-#if defined(BPSN_PHASE_TIMING)
-  int scanIters = 0;
-#endif
   if (lane == 0) {
     PathAcc acc;
     acc.count = 0;
@@ -316,9 +321,6 @@ __device__ __forceinline__ float warpFunnel(const StagedView sc, const WarpSlab 
       constexpr int kFunnelCap = 64 * kMaxPathPolys;
       for (; i < pathSize && guard < kFunnelCap; ++i) {
         ++guard;
-#if defined(BPSN_PHASE_TIMING)
-        scanIters++;
-#endif
         // portal i is in cur; fetch the next one now, it is needed a whole iteration later
         const int ni = (i + 1 <= lastPortal) ? i + 1 : lastPortal;
         const float4 nxtA = w.nodeA[ni];
@@ -410,16 +412,6 @@ __device__ __forceinline__ float warpFunnel(const StagedView sc, const WarpSlab 
       }
     }
   }
-#if defined(BPSN_PHASE_TIMING)
-  if (lane == 0) {
-    const long long tF3 = clock64();
-    atomicAdd(&g_phaseCycles[18], static_cast<unsigned long long>(tF1 - tF0));
-    atomicAdd(&g_phaseCycles[19], static_cast<unsigned long long>(tF2 - tF1));
-    atomicAdd(&g_phaseCycles[20], static_cast<unsigned long long>(tF3 - tF2));
-    atomicAdd(&g_phaseCycles[21], 1ull);
-    atomicAdd(&g_phaseCycles[23], static_cast<unsigned long long>(scanIters));
-  }
-#endif
   result = __shfl_sync(0xffffffffu, result, 0);
   st = __shfl_sync(0xffffffffu, st, 0);
   *status |= st;
@@ -636,11 +628,9 @@ __device__ __forceinline__ void warpForwardMove(const GroupDev& g, const StagedV
   endPos[0] = px + (vx + ((uvx * qw) + uuvx) * 2.f);
   endPos[1] = py + (vy + ((uvy * qw) + uuvy) * 2.f);
   endPos[2] = pz + (vz + ((uvz * qw) + uuvz) * 2.f);
-  BPSN_TICK(tM1);
   float best[3];
   uint32_t endIdx = 0;
   const bool ok = warpMoveAlongSurface(sv, w, lane, np, ref, endPos, best, &endIdx);
-  BPSN_TICK(tM2);
   if (ok) {
     float h = best[1];
     if (finitef(best[0]) && finitef(best[2]))
@@ -650,7 +640,6 @@ __device__ __forceinline__ void warpForwardMove(const GroupDev& g, const StagedV
     np[2] = best[2];
     ref = sv.refBase | endIdx;
   }
-  BPSN_TICK(tM3);
   if (lane == 0) {
     g.navPos[e] = np[0];
     g.navPos[B + e] = np[1];
@@ -661,11 +650,6 @@ __device__ __forceinline__ void warpForwardMove(const GroupDev& g, const StagedV
     g.pos[2 * B + e] = np[2];
     writePolar(g, e, np[0], np[1], np[2], qx, qy, qz, qw, gx, gy, gz);
   }
-#if defined(BPSN_PHASE_TIMING)
-  if (lane == 0) {
-    const long long tM4 = clock64();
-  }
-#endif
   navOut[0] = np[0];
   navOut[1] = np[1];
   navOut[2] = np[2];
@@ -674,26 +658,32 @@ __device__ __forceinline__ void warpForwardMove(const GroupDev& g, const StagedV
 
 constexpr int kSlabHeapCap = kMaxPathPolys;  // the corridor array doubles as the heap
 
-// Start of a search on slab `w`: returns the tag that marks this search's nodes.
+// Start of a search on slab `w`: returns the tag that marks this search's table entries
+// (global memory; shared-memory slabs are wiped instead and use no tag).
 template <bool kGlobal>
-__device__ __forceinline__ uint32_t beginSearch(const WarpSlab w, int P, int lane) {
-  uint32_t count = 1u;
-  bool wipe = true;
+__device__ __forceinline__ uint32_t beginSearch(const WarpSlab w, int lane) {
   if (kGlobal) {
     __syncwarp();
-    count = *w.searches + 1u;  // same address in every lane
-    wipe = count > kNodeTagMax;  // the 15-bit tag wraps: wipe once and start over
+    uint32_t count = *w.searches + 1u;  // same address in every lane
+    const bool wipe = count > kTableTagMax;  // the 20-bit tag wraps: wipe once and start over
     count = wipe ? 1u : count;
     __syncwarp();
     if (lane == 0)
       *w.searches = count;
+    if (wipe) {
+      uint32_t* t = static_cast<uint32_t*>(w.table);
+      for (int i = lane; i < w.tableLen; i += 32)
+        t[i] = 0u;
+    }
+    __syncwarp();
+    return count << kTableTagShift;
   }
-  if (wipe) {
-    for (int i = lane; i < P; i += 32)
-      w.nodeB[i] = make_uint2(0u, 0u);
-  }
+  // 2 bytes per polygon, tableLen a multiple of 16: whole 16-byte stores
+  uint4* t = static_cast<uint4*>(w.table);
+  for (int i = lane; i < (w.tableLen >> 3); i += 32)
+    t[i] = make_uint4(0u, 0u, 0u, 0u);
   __syncwarp();
-  return count * kNodeTagOne;
+  return 0u;
 }
 
 // dtNodeQueue on the slab: the heap holds polygon indices (uint16) in w.path and
@@ -701,15 +691,18 @@ __device__ __forceinline__ uint32_t beginSearch(const WarpSlab w, int P, int lan
 // heap of node pointers (Detour/Source/DetourNode.cpp:172-200).  Every lane runs
 // the same code on the same addresses and writes the same values, so each lane
 // reads back what it wrote itself and no synchronisation is needed in here.
-__device__ __forceinline__ float slabTotal(const WarpSlab& w, uint32_t node) {
-  return __uint_as_float(w.nodeB[node].x);
+template <bool kGlobal>
+__device__ __forceinline__ float slabTotal(const WarpSlab& w, uint32_t poly, uint32_t tag) {
+  return __uint_as_float(w.nodeB[tableLookup<kGlobal>(w, poly, tag)].x);
 }
-__device__ __forceinline__ void slabBubbleUp(const WarpSlab& w, int i, uint32_t node) {
-  const float tn = slabTotal(w, node);
+template <bool kGlobal>
+__device__ __forceinline__ void slabBubbleUp(const WarpSlab& w, int i, uint32_t node,
+                                             uint32_t tag) {
+  const float tn = slabTotal<kGlobal>(w, node, tag);
   int parent = (i - 1) / 2;
   while (i > 0) {
     const uint32_t pn = w.path[parent];
-    if (!(slabTotal(w, pn) > tn))
+    if (!(slabTotal<kGlobal>(w, pn, tag) > tn))
       break;
     w.path[i] = static_cast<uint16_t>(pn);
     i = parent;
@@ -717,17 +710,19 @@ __device__ __forceinline__ void slabBubbleUp(const WarpSlab& w, int i, uint32_t 
   }
   w.path[i] = static_cast<uint16_t>(node);
 }
-__device__ __forceinline__ void slabTrickleDown(const WarpSlab& w, int size, int i,
-                                                uint32_t node) {
+template <bool kGlobal>
+__device__ __forceinline__ void slabTrickleDown(const WarpSlab& w, int size, int i, uint32_t node,
+                                                uint32_t tag) {
   int child = i * 2 + 1;
   while (child < size) {
-    if ((child + 1) < size && slabTotal(w, w.path[child]) > slabTotal(w, w.path[child + 1]))
+    if ((child + 1) < size && slabTotal<kGlobal>(w, w.path[child], tag) >
+                                  slabTotal<kGlobal>(w, w.path[child + 1], tag))
       child++;
     w.path[i] = w.path[child];
     i = child;
     child = i * 2 + 1;
   }
-  slabBubbleUp(w, i, node);
+  slabBubbleUp<kGlobal>(w, i, node, tag);
 }
 
 enum AStarOutcome : int {
@@ -735,6 +730,7 @@ enum AStarOutcome : int {
   kAStarExhausted = 1,  // open list ran empty before the end polygon was popped
   kAStarIterCap = 2,
   kAStarHeapFull = 3,   // exact slab search only: more than kSlabHeapCap open nodes
+  kAStarPoolFull = 4,   // the search visits more polygons than the slab's pool holds
 };
 
 // dtNavMeshQuery::findPath (DetourNavMeshQuery.cpp:945-1137) with the reference's
@@ -744,20 +740,22 @@ enum AStarOutcome : int {
 // each; their node updates and heap operations then happen one edge after the
 // other in edge order, as in the reference's loop, because a heap operation
 // compares against the totals the earlier edges have already written.
+template <bool kGlobal>
 __device__ __noinline__ int astarExactSlab(const StagedView sc, const WarpSlab w, int lane,
                                            const float* startPosIn, const float* endPosIn,
                                            uint32_t startIdx, uint32_t endIdx, uint32_t tag,
-                                           int* nodesOut) {
+                                           int* nodesOut, uint32_t* endSlotOut) {
   const float startPos[3] = {startPosIn[0], startPosIn[1], startPosIn[2]};
   const float endPos[3] = {endPosIn[0], endPosIn[1], endPosIn[2]};
   if (lane == 0) {
     const float tot = vdist(startPos, endPos) * 0.999f;
-    w.nodeA[startIdx] = make_float4(startPos[0], startPos[1], startPos[2], 0.f);
-    w.nodeB[startIdx] = make_uint2(__float_as_uint(tot), 0xffffu | tag | kNodeOpen);
+    w.nodeA[0] = make_float4(startPos[0], startPos[1], startPos[2], 0.f);
+    w.nodeB[0] = make_uint2(__float_as_uint(tot), 0xffffu | (kNoSlot << 16) | kNodeOpen);
+    tableInsert<kGlobal>(w, startIdx, 0u, tag);
   }
   __syncwarp();
   int heapSize = 1;
-  slabBubbleUp(w, 0, startIdx);
+  slabBubbleUp<kGlobal>(w, 0, startIdx, tag);
   int nodes = 1;
   int outcome = kAStarExhausted;
   int guard = 0;
@@ -769,18 +767,20 @@ __device__ __noinline__ int astarExactSlab(const StagedView sc, const WarpSlab w
     // pop
     const uint32_t best = w.path[0];
     heapSize--;
-    slabTrickleDown(w, heapSize, 0, w.path[heapSize]);
+    slabTrickleDown<kGlobal>(w, heapSize, 0, w.path[heapSize], tag);
+    const uint32_t bestSlot = static_cast<uint32_t>(tableLookup<kGlobal>(w, best, tag));
     if (best == endIdx) {
+      *endSlotOut = bestSlot;
       outcome = kAStarReached;
       break;
     }
     const NavPoly* bp = &sc.polys[best];
     const int nv = bp->vertCount;
-    const float4 bA = w.nodeA[best];
-    const uint2 bB = w.nodeB[best];
+    const float4 bA = w.nodeA[bestSlot];
+    const uint2 bB = w.nodeB[bestSlot];
     __syncwarp();
     if (lane == 0)
-      w.nodeB[best].y = bB.y & ~kNodeOpen;
+      w.nodeB[bestSlot].y = bB.y & ~kNodeOpen;
     const uint32_t bpar = bB.y & 0xffffu;
     // evaluate: lane j takes edge j
     const int li = lane < kVertsPerPoly ? lane : kVertsPerPoly - 1;
@@ -796,11 +796,13 @@ __device__ __noinline__ int astarExactSlab(const StagedView sc, const WarpSlab w
         nei = best;
       }
     }
-    const float4 nA = w.nodeA[nei];
-    const uint2 nB = w.nodeB[nei];
+    const int found = tableLookup<kGlobal>(w, nei, tag);
+    const bool isNew = act && found < 0;
+    const uint32_t oldSlot = found < 0 ? 0u : static_cast<uint32_t>(found);
+    const float4 nA = w.nodeA[oldSlot];
+    const uint2 nB = w.nodeB[oldSlot];
     const float4 V0 = ldVert4(sc, bp->verts[li]);
     const float4 V1 = ldVert4(sc, bp->verts[(li + 1 == nv) ? 0 : li + 1]);
-    const bool isNew = act && (nB.y & kNodeTagMask) != tag;
     const float nx = isNew ? (V0.x + V1.x) * 0.5f : nA.x;
     const float ny = isNew ? (V0.y + V1.y) * 0.5f : nA.y;
     const float nz = isNew ? (V0.z + V1.z) * 0.5f : nA.z;
@@ -815,7 +817,15 @@ __device__ __noinline__ int astarExactSlab(const StagedView sc, const WarpSlab w
     const float ntotal = cost + heuristic;
     const bool upd = act && (isNew || !(ntotal >= __uint_as_float(nB.x)));
     const bool wasOpen = !isNew && (nB.y & kNodeOpen) != 0;
-    nodes += __popc(__ballot_sync(0xffffffffu, isNew));
+    // new nodes take the next pool slots
+    const uint32_t newMask = __ballot_sync(0xffffffffu, isNew);
+    const uint32_t slot =
+        isNew ? static_cast<uint32_t>(nodes) + __popc(newMask & ((1u << lane) - 1u)) : oldSlot;
+    nodes += __popc(newMask);
+    if (nodes > w.nodeCap) {
+      outcome = kAStarPoolFull;
+      break;
+    }
     // commit edge by edge
     const uint32_t updMask = __ballot_sync(0xffffffffu, upd);
     const uint32_t openMask = __ballot_sync(0xffffffffu, upd && wasOpen);
@@ -824,8 +834,10 @@ __device__ __noinline__ int astarExactSlab(const StagedView sc, const WarpSlab w
       const int j = __ffs(m) - 1;
       const uint32_t node = __shfl_sync(0xffffffffu, nei, j);
       if (lane == j) {
-        w.nodeA[nei] = make_float4(nx, ny, nz, cost);
-        w.nodeB[nei] = make_uint2(__float_as_uint(ntotal), best | tag | kNodeOpen);
+        w.nodeA[slot] = make_float4(nx, ny, nz, cost);
+        w.nodeB[slot] = make_uint2(__float_as_uint(ntotal), best | (bestSlot << 16) | kNodeOpen);
+        if (isNew)
+          tableInsert<kGlobal>(w, nei, slot, tag);
       }
       __syncwarp();
       if ((openMask >> j) & 1u) {
@@ -838,14 +850,14 @@ __device__ __noinline__ int astarExactSlab(const StagedView sc, const WarpSlab w
             at = k0 + __ffs(hit) - 1;
         }
         if (at >= 0)
-          slabBubbleUp(w, at, node);
+          slabBubbleUp<kGlobal>(w, at, node, tag);
       } else {
         if (heapSize >= kSlabHeapCap) {
           full = true;
           break;
         }
         heapSize++;
-        slabBubbleUp(w, heapSize - 1, node);
+        slabBubbleUp<kGlobal>(w, heapSize - 1, node, tag);
       }
     }
     if (full) {
@@ -859,26 +871,21 @@ __device__ __noinline__ int astarExactSlab(const StagedView sc, const WarpSlab w
   return outcome;
 }
 
-// One query by one warp.  `sc` points at the staged (shared-memory) tables.
-// Returns the distance in every lane.  *needFallback is set (uniformly) when
-// the fast path cannot decide the pop order (tie for the minimum) or the
-// register open list is full.
+// One query by one warp.  `sc` points at the staged tables (shared or global memory).
+// Returns the distance in every lane.  *needFallback is set (uniformly) when the query has
+// to be handed to the one-thread emulation: the exact search's heap outgrew its array, or
+// the search visited more polygons than the slab's pool holds.
 template <bool kGlobal>
 __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSlab w, int lane,
                                               const float* startPosIn, uint32_t startRef,
                                               const float* endPosIn, uint32_t endRef,
                                               uint32_t* status, uint32_t* needFallback,
-                                              bool forceExact
-#if defined(BPSN_PHASE_TIMING)
-                                              , PhaseAcc* pacc
-#endif
-) {
+                                              bool forceExact) {
   // private copies: the caller's arrays are also handed to a non-inlined
   // function and therefore live in local memory
   const float startPos[3] = {startPosIn[0], startPosIn[1], startPosIn[2]};
   const float endPos[3] = {endPosIn[0], endPosIn[1], endPosIn[2]};
   *needFallback = 0u;
-  BPSN_TICK(tA0);
   // (i) trivial path: Eigen isApprox with precision 1e-5
   {
     const float dx = startPos[0] - endPos[0];
@@ -914,30 +921,33 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
     pathSize = 1;
     __syncwarp();
   } else {
-    const uint32_t tag = beginSearch<kGlobal>(w, sc.npolys, lane);
-    // open list: kOpenSlots register entries (total, polygon) per lane, kInfBits = empty.
-    // All loops over the slots are unrolled, so the arrays live in registers.
+    const uint32_t tag = beginSearch<kGlobal>(w, lane);
+    // open list: kOpenSlots register entries per lane: total, and polygon | slot << 16 of the
+    // node; kInfBits = empty.  All loops over the slots are unrolled, so the arrays live in
+    // registers.
     uint32_t t[kOpenSlots], p[kOpenSlots];
 #pragma unroll
     for (int k = 0; k < kOpenSlots; ++k) {
       t[k] = kInfBits;
       p[k] = 0;
     }
-    int newNodes = 0;  // nodes this lane created (summed over the warp at the end)
+    int nodeCount = 1;  // nodes of this search (the same in every lane)
     if (lane == 0) {
       const float tot = vdist(startPos, endPos) * 0.999f;
-      w.nodeA[startIdx] = make_float4(startPos[0], startPos[1], startPos[2], 0.f);
-      w.nodeB[startIdx] = make_uint2(__float_as_uint(tot), 0xffffu | tag);
+      w.nodeA[0] = make_float4(startPos[0], startPos[1], startPos[2], 0.f);
+      w.nodeB[0] = make_uint2(__float_as_uint(tot), 0xffffu | (kNoSlot << 16));
+      tableInsert<kGlobal>(w, startIdx, 0u, tag);
       t[0] = __float_as_uint(tot);
-      p[0] = startIdx;
-      newNodes = 1;
+      p[0] = startIdx;  // slot 0
     }
     __syncwarp();
     bool reached = false;
+    uint32_t endSlot = 0u;
     bool overflow = false;  // this lane had to drop an entry, or met a distance outside the bare
                             // square root's range: the query is redone exactly
     // why the search has to be (re)done with the reference's heap
     uint32_t exactWhy = forceExact ? kStatTieFallback : 0u;
+    bool poolFull = false;
     int guard = 0;
     // Edge j of the popped polygon is evaluated by lane (j + rot) & 31 and rot moves on
     // after every pop, so that over a search every lane gets to evaluate neighbours: a
@@ -945,7 +955,7 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
     // cross-lane traffic, and the entries spread over the warp.
     int rot = 0;
     // a two-way tie that is being expanded in place: expansions still to check, the tied
-    // total, the polygon that goes second
+    // total, the entry that goes second
     int tiePending = 0;
     uint32_t tieTotal = 0u, tieOther = 0u;
 
@@ -955,7 +965,6 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
     // test and the request to rebalance all leave through the same test.
     if (!forceExact) while (true) {
       ++guard;
-      BPSN_TICK(tP0);
       // ---- pop: totals are non-negative floats, so their bit patterns order
       // like unsigned integers and one warp reduction finds the minimum.  A lane
       // that overflowed reports 0 so that the search stops at once.
@@ -976,17 +985,12 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
       }
       // Two more reductions, side by side, instead of vote + find-first-set + shuffle
       // (each of which costs about as much as a reduction): how many entries hold the
-      // minimum, and the polygon of the one that does when it is alone.
+      // minimum, and the node of the one that does when it is alone.
       // (a lane whose entries are all taken adds 65536: it asks for a rebalance)
       const uint32_t hsum = __reduce_add_sync(0xffffffffu, mc | (laneFull ? 0x10000u : 0u));
-      uint32_t best = __reduce_min_sync(0xffffffffu, cand);
+      uint32_t best = __reduce_min_sync(0xffffffffu, cand);  // polygon | slot << 16
       // one branch for everything that is not "a unique minimum that is not the end"
-      if ((hsum != 1u) | (best == endIdx) | (guard > 64 * kMaxAStarNodes)) {
-#if defined(BPSN_PHASE_TIMING)
-        if (lane == 0) {
-          atomicAdd(&g_phaseCycles[22], 1ull);
-        }
-#endif
+      if ((hsum != 1u) | ((best & 0xffffu) == endIdx) | (guard > 64 * kMaxAStarNodes)) {
         if (guard > 64 * kMaxAStarNodes) {
           *status |= kStatIterCap;
           return BPSN_INF;
@@ -1002,12 +1006,12 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
           // Several entries share the minimum.  Superseded entries do not count: only
           // those whose total is still their node's are in the reference's heap.
           int lc = 0;
-          uint32_t livePoly = 0;
+          uint32_t liveNode = 0;
 #pragma unroll
           for (int k = kOpenSlots - 1; k >= 0; --k) {
-            const bool live = m[k] && w.nodeB[p[k]].x == gm;
+            const bool live = m[k] && w.nodeB[p[k] >> 16].x == gm;
             lc += live ? 1 : 0;
-            livePoly = live ? p[k] : livePoly;
+            liveNode = live ? p[k] : liveNode;
           }
           const uint32_t liveHolders = __ballot_sync(0xffffffffu, lc != 0);
           const bool liveMulti = __any_sync(0xffffffffu, lc > 1);
@@ -1021,15 +1025,18 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
             // else goes to the exact redo.
             bool resolved = false;
             if (__popc(liveHolders) == 2 && !liveMulti && tiePending == 0) {
-              const uint32_t p0 = __shfl_sync(0xffffffffu, livePoly, __ffs(liveHolders) - 1);
-              const uint32_t p1 = __shfl_sync(0xffffffffu, livePoly, 31 - __clz(liveHolders));
-              const uint32_t first = min(p0, p1), second = max(p0, p1);
-              if (first != endIdx && second != endIdx) {
+              const uint32_t p0 = __shfl_sync(0xffffffffu, liveNode, __ffs(liveHolders) - 1);
+              const uint32_t p1 = __shfl_sync(0xffffffffu, liveNode, 31 - __clz(liveHolders));
+              // (polygon in the low half: the order below is by polygon index, as before)
+              const bool swap = (p1 & 0xffffu) < (p0 & 0xffffu);
+              const uint32_t first = swap ? p1 : p0, second = swap ? p0 : p1;
+              const uint32_t firstPoly = first & 0xffffu, secondPoly = second & 0xffffu;
+              if (firstPoly != endIdx && secondPoly != endIdx) {
                 // lanes 0..5: the neighbours of the first, lanes 6..11: of the second
                 uint32_t key = 0xffffffffu;
                 const bool sideB = lane >= kVertsPerPoly;
                 if (lane < 2 * kVertsPerPoly) {
-                  const NavPoly* q = &sc.polys[sideB ? second : first];
+                  const NavPoly* q = &sc.polys[sideB ? secondPoly : firstPoly];
                   const int jj = sideB ? lane - kVertsPerPoly : lane;
                   const uint16_t qn = q->neis[jj];
                   if (jj < q->vertCount && qn != 0 && !(qn & kExtLink))
@@ -1041,7 +1048,7 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
                   const uint32_t other = __shfl_sync(0xffffffffu, key, jj);
                   touch = touch || (sideB && key == other);
                 }
-                touch = key != 0xffffffffu && (touch || key == (sideB ? first : second));
+                touch = key != 0xffffffffu && (touch || key == (sideB ? firstPoly : secondPoly));
                 if (!__any_sync(0xffffffffu, touch)) {
                   resolved = true;
                   *status |= kStatTieInPlace;
@@ -1067,11 +1074,12 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
                 t[k] = m[k] ? kInfBits : t[k];
               continue;
             }
-            best = __shfl_sync(0xffffffffu, livePoly, __ffs(liveHolders) - 1);
+            best = __shfl_sync(0xffffffffu, liveNode, __ffs(liveHolders) - 1);
           }
         }
-        if (best == endIdx) {
+        if ((best & 0xffffu) == endIdx) {
           reached = true;
+          endSlot = best >> 16;
           break;
         }
         if (hsum >> 16) {
@@ -1084,7 +1092,7 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
             t[k] = m[k] ? kInfBits : t[k];  // (the popped entry first)
             m[k] = false;                   // done: the pairs may be refilled just below
             // superseded entries (their total is no longer their node's) only take up room
-            const bool stale = t[k] != kInfBits && w.nodeB[p[k]].x != t[k];
+            const bool stale = t[k] != kInfBits && w.nodeB[p[k] >> 16].x != t[k];
             t[k] = stale ? kInfBits : t[k];
             f[k] = t[k] == kInfBits;
             freeCnt += f[k] ? 1 : 0;
@@ -1117,11 +1125,11 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
 #pragma unroll
       for (int k = 0; k < kOpenSlots; ++k)
         t[k] = m[k] ? kInfBits : t[k];
-      BPSN_TICK(tP1);
 
       // ---- expand: one lane per edge of the popped polygon.  All loads of a
       // round are issued before any of them is used.
-      const NavPoly* bp = &sc.polys[best];
+      const uint32_t bestPoly = best & 0xffffu, bestSlot = best >> 16;
+      const NavPoly* bp = &sc.polys[bestPoly];
       const int ej = (lane - rot) & 31;  // this lane's edge index (>= nv: none)
       const int li = ej < kVertsPerPoly ? ej : kVertsPerPoly - 1;
       const int nv = bp->vertCount;
@@ -1131,19 +1139,20 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
       // verts[li + 1] stays inside the record (neis follows verts)
       const uint16_t vbNext = (&bp->verts[0])[li + 1];
       const uint16_t vbFirst = bp->verts[0];
-      const float4 bA = w.nodeA[best];
-      const uint2 bB = w.nodeB[best];
+      const float4 bA = w.nodeA[bestSlot];
+      const uint2 bB = w.nodeB[bestSlot];
 
       const uint16_t vb = (li + 1 == nv) ? vbFirst : vbNext;
       const bool hasEdge = ej < nv && ne != 0 && !(ne & kExtLink);
-      const uint32_t nei = hasEdge ? static_cast<uint32_t>(ne - 1) : best;
-      // The neighbour's node and the edge's end points are requested as soon as the polygon
-      // record is there: they do not wait for the popped node's own record (in global
-      // memory that is a second trip to L2, now overlapped with this one).
-      const float4 nA = w.nodeA[nei];
-      const uint2 nB = w.nodeB[nei];
+      const uint32_t nei = hasEdge ? static_cast<uint32_t>(ne - 1) : bestPoly;
+      // The neighbour's table entry and the edge's end points are requested as soon as the
+      // polygon record is there: they do not wait for the popped node's own record.
+      const int found = tableLookup<kGlobal>(w, nei, tag);
       const float4 V0 = ldVert4(sc, va);
       const float4 V1 = ldVert4(sc, vb);
+      const uint32_t oldSlot = found < 0 ? 0u : static_cast<uint32_t>(found);
+      const float4 nA = w.nodeA[oldSlot];
+      const uint2 nB = w.nodeB[oldSlot];
       const uint32_t bpar = bB.y & 0xffffu;
       bool act = hasEdge && nei != bpar;
       if ((bB.x != gm) | (dupFlag & 1)) {  // one branch for the two uncommon cases
@@ -1161,9 +1170,12 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
         const uint32_t byEdge = __funnelshift_r(grp, grp, rot);
         act = act && (__ffs(byEdge) - 1) == ej;
       }
-      BPSN_TICK(tE1);
-      const bool isNew = act && (nB.y & kNodeTagMask) != tag;
-      newNodes += isNew ? 1 : 0;
+      const bool isNew = act && found < 0;
+      // new nodes take the next pool slots (which slot a node gets influences nothing)
+      const uint32_t newMask = __ballot_sync(0xffffffffu, isNew);
+      const uint32_t slot =
+          isNew ? static_cast<uint32_t>(nodeCount) + __popc(newMask & ((1u << lane) - 1u)) : oldSlot;
+      nodeCount += __popc(newMask);
       const float nx = isNew ? (V0.x + V1.x) * 0.5f : nA.x;
       const float ny = isNew ? (V0.y + V1.y) * 0.5f : nA.y;
       const float nz = isNew ? (V0.z + V1.z) * 0.5f : nA.z;
@@ -1187,7 +1199,11 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
       const uint32_t ntBits = __float_as_uint(ntotal);
       // open or closed alike: skipped unless strictly better (DetourNavMeshQuery.cpp:1075-1080)
       const bool upd = act && (isNew || !(ntotal >= __uint_as_float(nB.x)));
-      if (tiePending) {
+      if (tiePending | (nodeCount > w.nodeCap)) {  // one branch for the two uncommon cases
+        if (nodeCount > w.nodeCap) {
+          poolFull = true;  // nothing of this round has been stored
+          break;
+        }
         // one of the two expansions of a resolved tie (see the pop): it has to be the expected
         // polygon and must not write a total that the other order would have popped first
         if ((tiePending == 1 && best != tieOther) ||
@@ -1198,46 +1214,35 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
         --tiePending;
       }
 
-      BPSN_TICK(tE2);
       // ---- the new entry goes into this lane's first free register pair
       {
         bool placed = !upd;
+        const uint32_t entry = nei | (slot << 16);
 #pragma unroll
         for (int k = 0; k < kOpenSlots; ++k) {
           const bool here = !placed && t[k] == kInfBits;
           t[k] = here ? ntBits : t[k];
-          p[k] = here ? nei : p[k];
+          p[k] = here ? entry : p[k];
           placed = placed || here;
         }
         overflow = overflow || !placed;
       }
-      BPSN_TICK(tE3);
       if (upd) {
-        w.nodeA[nei] = make_float4(nx, ny, nz, cost);
-        w.nodeB[nei] = make_uint2(ntBits, best | tag);
+        w.nodeA[slot] = make_float4(nx, ny, nz, cost);
+        w.nodeB[slot] = make_uint2(ntBits, bestPoly | (bestSlot << 16));
+        if (isNew)
+          tableInsert<kGlobal>(w, nei, slot, tag);
       }
       rot = (rot + 7) & 31;
       __syncwarp();
-#if defined(BPSN_PHASE_TIMING)
-      {
-        BPSN_TICK(tP2);
-        pacc->popCycles += static_cast<unsigned long long>(tP1 - tP0);
-        pacc->expandCycles += static_cast<unsigned long long>(tP2 - tP1);
-        pacc->pops += 1;
-        pacc->exLoad += static_cast<unsigned long long>(tE1 - tP1);
-        pacc->exMath += static_cast<unsigned long long>(tE2 - tE1);
-        pacc->exBook += static_cast<unsigned long long>(tE3 - tE2);
-      }
-#endif
     }
 
-    if (!exactWhy && __any_sync(0xffffffffu, overflow))
+    if (!exactWhy && !poolFull && __any_sync(0xffffffffu, overflow))
       exactWhy = kStatOpenOverflow;
-    int nodeTotal = __reduce_add_sync(0xffffffffu, newNodes);
-    if (exactWhy) {
-      const uint32_t exactTag = beginSearch<kGlobal>(w, sc.npolys, lane);
-      const int outcome = astarExactSlab(sc, w, lane, startPos, endPos, startIdx, endIdx, exactTag,
-                                         &nodeTotal);
+    if (exactWhy && !poolFull) {
+      const uint32_t exactTag = beginSearch<kGlobal>(w, lane);
+      const int outcome = astarExactSlab<kGlobal>(sc, w, lane, startPos, endPos, startIdx, endIdx,
+                                                  exactTag, &nodeCount, &endSlot);
       if (outcome == kAStarHeapFull) {
         *needFallback = exactWhy;  // hand the query to the global-memory emulation
         return 0.f;
@@ -1246,16 +1251,21 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
         *status |= kStatIterCap;
         return BPSN_INF;
       }
+      poolFull = outcome == kAStarPoolFull;
       *status |= exactWhy;
       reached = outcome == kAStarReached;
     }
-    // dtNodePool hands out at most kMaxAStarNodes nodes; a search that asks for more
-    // ends with DT_OUT_OF_NODES in its status, which PathFinder turns into +inf
-    // whatever path was found (PathFinder.cpp:506).
-    const bool outOfNodes = nodeTotal > kMaxAStarNodes;
-    if (outOfNodes) {
-      *status |= kStatOutOfNodes;
-      return BPSN_INF;
+    if (poolFull) {
+      // dtNodePool hands out at most kMaxAStarNodes nodes; a search that asks for more
+      // ends with DT_OUT_OF_NODES in its status, which PathFinder turns into +inf
+      // whatever path was found (PathFinder.cpp:506).  A smaller pool only says that this
+      // slab cannot hold the search.
+      if (w.nodeCap >= kMaxPoolNodes) {
+        *status |= kStatOutOfNodes;
+        return BPSN_INF;
+      }
+      *needFallback = kStatPoolOverflow;
+      return 0.f;
     }
     if (!reached) {
       *status |= kStatPartial;
@@ -1264,16 +1274,19 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
     // corridor: walk parents from the end polygon, then reverse
     int length = 0;
     if (lane == 0) {
-      uint32_t cur = endIdx;
-      while (cur != 0xffffu && length <= kMaxAStarNodes) {
+      uint32_t cur = endSlot;
+      while (cur != kNoSlot && length <= kMaxAStarNodes) {
         length++;
-        cur = w.nodeB[cur].y & 0xffffu;
+        cur = (w.nodeB[cur].y >> 16) & kNoSlot;
       }
       if (length <= kMaxPathPolys) {
-        cur = endIdx;
+        cur = endSlot;
+        uint32_t poly = endIdx;
         for (int i = length - 1; i >= 0; --i) {
-          w.path[i] = static_cast<uint16_t>(cur);
-          cur = w.nodeB[cur].y & 0xffffu;
+          w.path[i] = static_cast<uint16_t>(poly);
+          const uint32_t y = w.nodeB[cur].y;
+          poly = y & 0xffffu;
+          cur = (y >> 16) & kNoSlot;
         }
       }
     }
@@ -1286,19 +1299,7 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
     pathSize = length;
   }
 
-  BPSN_TICK(tA1);
-  const float dres = warpFunnel(sc, w, lane, startPos, endPos, pathSize, status);
-  if (kGlobal) {
-    // the portals sit in the first node slots; what they left in the tag field must not
-    // pass for a visit mark of a later search
-    __syncwarp();
-    for (int i = lane; i + 1 < pathSize; i += 32)
-      w.nodeB[i].y = 0u;
-  }
-  BPSN_TICK(tA2);
-  BPSN_PHASE_ADD(2, tA1 - tA0);
-  BPSN_PHASE_ADD(3, tA2 - tA1);
-  return dres;
+  return warpFunnel(sc, w, lane, startPos, endPos, pathSize, status);
 }
 
 // The part of k_step_warp after the scene is in place: the warp's loop over list slots.
@@ -1312,9 +1313,6 @@ __device__ __forceinline__ void stepWarpQueries(const GroupDev& g, const SceneTa
                                                 uint8_t* globalSlabs, size_t globalSlabStride,
                                                 AStarScratch* fallbackScratch, uint32_t seedLo,
                                                 uint32_t seedHi
-#if defined(BPSN_PHASE_TIMING)
-                                                , long long tS0
-#endif
 ) {
   extern __shared__ __align__(16) uint8_t smem[];
   const int pcap = static_cast<int>(pl.pcap);
@@ -1331,12 +1329,6 @@ __device__ __forceinline__ void stepWarpQueries(const GroupDev& g, const SceneTa
   sc.dtris = tables + lay.dtris;
   sc.dverts = reinterpret_cast<const float*>(tables + lay.dverts);
   sc.island = reinterpret_cast<const int32_t*>(tables + lay.island);
-  BPSN_TICK(tS1);
-#if defined(BPSN_PHASE_TIMING)
-  PhaseAcc paccStore = {};
-  PhaseAcc* pacc = &paccStore;
-  BPSN_PHASE_ADD(0, tS1 - tS0);
-#endif
 
   StagedView sv;
   sv.polys = sc.polys;
@@ -1348,11 +1340,13 @@ __device__ __forceinline__ void stepWarpQueries(const GroupDev& g, const SceneTa
   sv.npolys = sc.npolys;
   sv.polyMask = sc.polyMask;
   sv.refBase = sc.refBase;
-  // (global memory: one stride for all scenes, slabs of different sizes must not overlap)
-  // (global memory: carved per query below)
+  // (global memory: one stride for all scenes; the slab is carved per query below)
+  const int nodeCap = static_cast<int>(pl.nodeCap);
   WarpSlab w = carveSlab(
-      kGlobal ? globalSlabs : smem + pl.slabOffset + static_cast<size_t>(warp) * warpGeoSlabBytes(pcap),
-      pcap);
+      kGlobal ? globalSlabs
+              : smem + pl.slabOffset +
+                    static_cast<size_t>(warp) * warpGeoSlabBytes(pcap, nodeCap, false),
+      pcap, nodeCap, kGlobal);
   // Large slabs (the group's slabs together exceed what L2 holds) belong to environments
   // instead: an environment's searches start from the same goal step after step and touch
   // nearly the same nodes, so its own slab is still warm in L2 from the step before, whereas
@@ -1374,10 +1368,6 @@ __device__ __forceinline__ void stepWarpQueries(const GroupDev& g, const SceneTa
     }
     if (q >= n)
       break;
-    BPSN_TICK(tQ0);
-#if defined(BPSN_PHASE_TIMING)
-    const unsigned long long accA0 = pacc->sum[2], accF0 = pacc->sum[3], accP0 = pacc->pops;
-#endif
     const uint32_t entry = g.geoList[base + q];
     const uint32_t e = entry & kListEnvMask;
     if (kGlobal) {
@@ -1385,7 +1375,7 @@ __device__ __forceinline__ void stepWarpQueries(const GroupDev& g, const SceneTa
           slabPerEnv ? static_cast<size_t>(e)
                      : static_cast<size_t>(blockIdx.x) * (blockDim.x >> 5) + static_cast<size_t>(warp);
       uint8_t* slab = globalSlabs + slabIdx * globalSlabStride;
-      w = carveSlab(slab, pcap);
+      w = carveSlab(slab, pcap, nodeCap, true);
       w.searches = reinterpret_cast<uint32_t*>(slab + globalSlabStride - kGlobalSlabExtra);
     }
     const bool done = entry & kListDone, moved = entry & kListMoved;
@@ -1406,15 +1396,9 @@ __device__ __forceinline__ void stepWarpQueries(const GroupDev& g, const SceneTa
     float d = 0.f;
     // PointNav queries on every listed step, Flee only after a move, Exploration never
     const bool needGeo = g.task == kTaskPointNav || (g.task == kTaskFlee && moved);
-    BPSN_TICK(tQ1);
     if (needGeo) {
-#if defined(BPSN_PHASE_TIMING)
-      d = warpGeodesic<kGlobal>(sv, w, lane, b, bref, a, aref, &status, &fallback, g.exactHeap != 0, pacc);
-#else
       d = warpGeodesic<kGlobal>(sv, w, lane, b, bref, a, aref, &status, &fallback, g.exactHeap != 0);
-#endif
     }
-    BPSN_TICK(tQ2);
     if (lane == 0) {
       if (fallback) {
         status = 0;
@@ -1427,43 +1411,9 @@ __device__ __forceinline__ void stepWarpQueries(const GroupDev& g, const SceneTa
       if (status)
         g.status[e] |= status;
       finishEnv(g, st, e, done, moved, d, seedLo, seedHi);
-      BPSN_TICK(tQ3);
-      BPSN_PHASE_ADD(1, tQ1 - tQ0);
-      BPSN_PHASE_ADD(4, tQ3 - tQ2);
-#if defined(BPSN_PHASE_TIMING)
-      pacc->queries += 1;
-      {
-        // the query that ends last in the launch, with its own phase times (units of 128 cycles)
-        auto f = [](long long c, int bits) -> unsigned long long {
-          unsigned long long v = static_cast<unsigned long long>(c) >> 7;
-          const unsigned long long mx = (1ull << bits) - 1ull;
-          return v > mx ? mx : v;
-        };
-        const unsigned long long packed =
-            (f(tQ3 - tS0, 16) << 48) | (((pacc->pops - accP0) & 0xfffull) << 36) | (f(tQ1 - tQ0, 8) << 28) |
-            (f(static_cast<long long>(pacc->sum[2] - accA0), 12) << 16) |
-            (f(static_cast<long long>(pacc->sum[3] - accF0), 8) << 8) | f(tQ3 - tQ2, 8);
-        atomicMax(&g_phaseCycles[17], packed);
-      }
-#endif
     }
     __syncwarp();
   }
-#if defined(BPSN_PHASE_TIMING)
-  if (lane == 0) {
-    for (int k = 0; k < 5; ++k) {
-      atomicAdd(&g_phaseCycles[k], pacc->sum[k]);
-      atomicMax(&g_phaseCycles[6 + k], pacc->mx[k]);
-    }
-    atomicAdd(&g_phaseCycles[5], pacc->queries);
-    atomicAdd(&g_phaseCycles[12], pacc->popCycles);
-    atomicAdd(&g_phaseCycles[13], pacc->expandCycles);
-    atomicAdd(&g_phaseCycles[14], pacc->pops);
-    atomicAdd(&g_phaseCycles[11], pacc->exLoad);
-    atomicAdd(&g_phaseCycles[15], pacc->exMath);
-    atomicAdd(&g_phaseCycles[16], pacc->exBook);
-  }
-#endif
 }
 
 // One simulator step for the environments listed per scene (see sim_kernels.cuh
@@ -1494,7 +1444,6 @@ k_step_warp(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
   const int warpsPerBlock = static_cast<int>(pl.warps);  // warps of this CTA that take queries
   const int warp = threadIdx.x >> 5;
 
-  BPSN_TICK(tS0);
   uint32_t n = 0;
   const NavScene scGlobal = st.scenes[sceneIdx];
   // A scene too large to sit in shared memory next to at least one slab is worked on where
@@ -1563,13 +1512,8 @@ k_step_warp(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
   }
   if (rank * static_cast<uint32_t>(warpsPerBlock) >= n || warp >= warpsPerBlock)
     return;  // (only after the copy has landed: it targets this CTA's shared memory)
-#if defined(BPSN_PHASE_TIMING)
-#define BPSN_STEP_ARGS g, st, pl, sceneIdx, rank, n, scGlobal, globalSlabs, globalSlabStride, \
-                       fallbackScratch, seedLo, seedHi, tS0
-#else
 #define BPSN_STEP_ARGS g, st, pl, sceneIdx, rank, n, scGlobal, globalSlabs, globalSlabStride, \
                        fallbackScratch, seedLo, seedHi
-#endif
   if constexpr (kMode == 0) {
     stepWarpQueries<false>(BPSN_STEP_ARGS);
   } else if constexpr (kMode == 1) {
