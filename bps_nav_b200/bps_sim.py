@@ -99,19 +99,19 @@ class _RolloutGenerator:
     def from_scenes(cls, scenes, num_environments, num_active_scenes=None, gpu_id=0,
                     render_resolution=(64, 64), color=False, depth=False, double_buffered=False,
                     seed=0, host_mirrors=True, generic_kernel=False, exact_heap=False,
-                    small_smem=False, global_memory=False, small_pool=False):
+                    small_smem=False, global_memory=False):
         """Builds a generator from in-memory ``dataset.Scene`` objects (no JSON involved)."""
         self = cls.__new__(cls)
         if num_active_scenes is None:
             num_active_scenes = len(scenes)
         self._setup(list(scenes), num_environments, num_active_scenes, gpu_id, render_resolution,
                     color, depth, double_buffered, seed, host_mirrors, generic_kernel, exact_heap,
-                    small_smem, global_memory, small_pool)
+                    small_smem, global_memory)
         return self
 
     def _setup(self, scenes, num_environments, num_active_scenes, gpu_id, render_resolution, color,
                depth, double_buffered, seed, host_mirrors, generic_kernel=False, exact_heap=False,
-               small_smem=False, global_memory=False, small_pool=False):
+               small_smem=False, global_memory=False):
         if self._task not in _TASKS:
             raise NotImplementedError(f"{type(self).__name__}: unknown task")
         self._task_id, self._info_dtype = _TASKS[self._task]
@@ -138,8 +138,7 @@ class _RolloutGenerator:
                        (L.FLAG_GENERIC_KERNEL if generic_kernel else 0) |
                        (L.FLAG_EXACT_HEAP if exact_heap else 0) |
                        (L.FLAG_SMEM_96K if small_smem else 0) |
-                       (L.FLAG_GLOBAL_MEMORY if global_memory else 0) |
-                       (L.FLAG_SMALL_POOL if small_pool else 0),
+                       (L.FLAG_GLOBAL_MEMORY if global_memory else 0),
                        task=self._task_id,
                        render_width=self._res[0] if self._depth else 0,
                        render_height=self._res[1] if self._depth else 0)
@@ -162,6 +161,11 @@ class _RolloutGenerator:
             self._lib.bpsn_destroy(self._h)
             self._h = C.c_void_p()
             raise
+        self._group_streams = None
+        if num_groups == 2 and host_mirrors:
+            import torch
+            with torch.cuda.device(self.gpu_id):
+                self._group_streams = [torch.cuda.Stream() for _ in range(num_groups)]
         self.envs_per_group = self.num_environments // num_groups
         self.envs_per_scene = self.num_environments // len(self._scenes)
         self._num_steps_taken = 0
@@ -184,7 +188,18 @@ class _RolloutGenerator:
             pass
 
     # ------------------------------------------------------------------ stepping
-    def _stream(self):
+    def _stream(self, group_idx=0):
+        """The CUDA stream a group's work is enqueued on.  A double-buffered generator with
+        host result arrays (the reference's way of use: ``step_end`` returns when the numpy
+        arrays are complete) gives each group a stream of its own, so that the two groups'
+        steps overlap on the GPU as the reference's two groups overlap on its worker threads
+        (simulator/simulator.cpp:1377-1399).  Otherwise work goes to torch's current stream and
+        is ordered with the caller's tensor operations."""
+        if self._group_streams is not None:
+            return C.c_void_p(self._group_streams[group_idx].cuda_stream)
+        return self._current_stream()
+
+    def _current_stream(self):
         import torch
         raw = getattr(torch._C, "_cuda_getCurrentRawStream", None)  # same value, less overhead
         if raw is not None:
@@ -192,7 +207,7 @@ class _RolloutGenerator:
         return C.c_void_p(torch.cuda.current_stream(self.gpu_id).cuda_stream)
 
     def reset(self, group_idx):
-        L.check(self._lib.bpsn_reset(self._h, group_idx, self._stream()), self._h)
+        L.check(self._lib.bpsn_reset(self._h, group_idx, self._stream(group_idx)), self._h)
 
     def step_start(self, group_idx, actions, reward_out=None, mask_out=None, polar_out=None):
         """``actions``: C-contiguous int64 numpy array of length ``envs_per_group`` (reference
@@ -213,7 +228,8 @@ class _RolloutGenerator:
             self._keepalive = [actions, reward_out, mask_out, polar_out]
             L.check(self._lib.bpsn_step_start_ex(self._h, group_idx,
                                                  actions.__array_interface__["data"][0],
-                                                 L.MEM_HOST, self._stream(), ro, mo, po), self._h)
+                                                 L.MEM_HOST, self._stream(group_idx), ro, mo, po),
+                    self._h)
         else:
             import torch
             if not (isinstance(actions, torch.Tensor) and actions.is_cuda and
@@ -224,7 +240,8 @@ class _RolloutGenerator:
                 raise RuntimeError("actions length must equal the number of envs in the group")
             self._keepalive = [actions, reward_out, mask_out, polar_out]
             L.check(self._lib.bpsn_step_start_ex(self._h, group_idx, actions.data_ptr(),
-                                                 L.MEM_DEVICE, self._stream(), ro, mo, po), self._h)
+                                                 L.MEM_DEVICE, self._stream(group_idx), ro, mo, po),
+                    self._h)
         self._num_steps_taken += self.envs_per_group
 
     def _out_ptrs(self, reward_out, mask_out, polar_out):
@@ -252,7 +269,7 @@ class _RolloutGenerator:
         otherwise a no-op kept so that call sites need no change.  There is no colour
         renderer: ``rgba`` stays zero-filled."""
         if self._depth:
-            L.check(self._lib.bpsn_render(self._h, group_idx, self._stream()), self._h)
+            L.check(self._lib.bpsn_render(self._h, group_idx, self._stream(group_idx)), self._h)
 
     def step(self, group_idx, actions):
         self.step_start(group_idx, actions)
@@ -261,8 +278,10 @@ class _RolloutGenerator:
 
     def wait_for_frame(self, group_idx):
         import torch
-        del group_idx
-        torch.cuda.current_stream(self.gpu_id).synchronize()
+        if self._group_streams is not None:
+            self._group_streams[group_idx].synchronize()
+        else:
+            torch.cuda.current_stream(self.gpu_id).synchronize()
 
     # ------------------------------------------------------------------ result views (host)
     def _host_array(self, group_idx, name):
@@ -384,7 +403,7 @@ class _RolloutGenerator:
         out = torch.empty_like(pts)
         refs = torch.empty(n, dtype=torch.int32, device=pts.device)
         L.check(self._lib.bpsn_query_snap(self._h, scene_idx, n, pts.data_ptr(), out.data_ptr(),
-                                          refs.data_ptr(), self._stream()), self._h)
+                                          refs.data_ptr(), self._current_stream()), self._h)
         return out, refs
 
     def query_try_step(self, scene_idx, start, start_refs, end):
@@ -396,7 +415,7 @@ class _RolloutGenerator:
         refs = torch.empty(n, dtype=torch.int32, device=s.device)
         L.check(self._lib.bpsn_query_try_step(self._h, scene_idx, n, s.data_ptr(), r.data_ptr(),
                                               e.data_ptr(), out.data_ptr(), refs.data_ptr(),
-                                              self._stream()), self._h)
+                                              self._current_stream()), self._h)
         return out, refs
 
     def query_geodesic(self, scene_idx, start, start_refs, end, end_refs):
@@ -409,7 +428,7 @@ class _RolloutGenerator:
         status = torch.empty(n, dtype=torch.int32, device=s.device)
         L.check(self._lib.bpsn_query_geodesic(self._h, scene_idx, n, s.data_ptr(), sr.data_ptr(),
                                               e.data_ptr(), er.data_ptr(), out.data_ptr(),
-                                              status.data_ptr(), self._stream()), self._h)
+                                              status.data_ptr(), self._current_stream()), self._h)
         return out, status
 
 

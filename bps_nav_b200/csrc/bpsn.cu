@@ -301,36 +301,29 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
                               cudaMemcpyHostToDevice));
     BPSN_CUDA(sim, cudaMemcpy(d.scene, envScene, sizeof(uint32_t) * B, cudaMemcpyHostToDevice));
     g.numScenesUsed = ns;
-    // Shared-memory plan, scene by scene: a CTA serves one scene; its shared memory holds
-    // the scene's staged image and one slab per warp (polygon -> slot table, 2 B per polygon,
-    // a pool of nodeCap A* nodes of 24 B, 512 B of corridor).  The pool is sized for the
-    // searches, not for the mesh: kPoolWanted nodes cover every search seen on the test
-    // scenes (episodes of at most 30 m: <= 152 nodes on a 446-polygon floor, <= 247 on a
-    // 16 000-polygon one); a search that outgrows its pool is redone by the one-thread
-    // emulation with the same result.  A scene that leaves no room for a slab is worked on
-    // in global memory.  CTAs are dealt to the scenes in proportion to environments /
-    // warps-per-CTA, so that every scene's list drains in about the same time.
+    // Shared-memory plan, scene by scene: a CTA serves one scene with 227 KB of shared
+    // memory = the scene's staged image + as many warp slabs (24 B per polygon + 512 B) as
+    // fit, at most 16.  A scene that leaves no room for a slab goes to the generic kernel.
+    // CTAs are dealt to the scenes in proportion to environments / warps-per-CTA, so that
+    // every scene's list drains in about the same time.
     const size_t kSlabPerEnvAbove = size_t(512) << 20;  // bytes of per-warp slabs from which on ...
     const size_t kSlabPerEnvBudget = size_t(32) << 30;  // ... and bytes of per-env slabs up to which
     const size_t kSmemMax = ((sim->cfg.flags & BPSN_FLAG_SMEM_96K) ? 96 : 227) * 1024 - 64;  // per CTA, minus the kernel's static shared memory
-    const uint32_t kPoolWanted = 256, kPoolMin = 160;
-    const uint32_t poolOverride = (sim->cfg.flags & BPSN_FLAG_SMALL_POOL) ? 32u : 0u;
-    std::vector<WarpPlan> plan(ns, WarpPlan{16u, 0u, 0u, 0u, 0u, 0u});
+    std::vector<WarpPlan> plan(ns, WarpPlan{16u, 0u, 0u, 0u});
     size_t maxGlobalSlab = 0;
     const double kGlobalWarpSpeed = 0.6;  // queries per unit time of a warp in global memory
                                           // relative to one in shared memory (measured)
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, sim->cfg.gpu_id);
-    const uint32_t kWarpsPerCta = 16;
-    const bool throughputBound = B / 2 > 2u * static_cast<uint32_t>(sms) * kWarpsPerCta;
+    const bool throughputBound = B / 2 > 2u * static_cast<uint32_t>(sms) * 16u;
     const bool forceGeneric = (sim->cfg.flags & BPSN_FLAG_GENERIC_KERNEL) != 0;
     double workSum = 0.0;
     std::vector<double> work(ns, 0.0);
     g.anyThreadScene = false;
     g.anyWarpScene = false;
     // Pass 1: how many slabs fit next to each scene's image in shared memory.
-    std::vector<uint32_t> smemWarps(ns, 0u), smemCap(ns, 0u), globalCap(ns, 0u);
-    std::vector<size_t> slabBytes(ns, 0), sceneBytes(ns, 0), globalSlabBytes(ns, 0);
+    std::vector<uint32_t> smemWarps(ns, 0u);
+    std::vector<size_t> slabBytes(ns, 0), sceneBytes(ns, 0);
     bool anyCramped = false;  // some scene has room for fewer than 8 slabs
     for (uint32_t s2 = 0; s2 < ns; ++s2) {
       if (!perScene[s2])
@@ -339,27 +332,15 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
       const NavScene hv = h.view();
       const size_t sb = stagedLayout(hv.nverts, hv.npolys, hv.ndtris, hv.ndverts).total;
       const uint32_t pcap = (static_cast<uint32_t>(h.polys.size()) + 15u) / 16u * 16u;
-      uint32_t w = 0, cap = 0;
-      size_t slab = 0;
-      for (uint32_t want : {kPoolWanted, kPoolMin}) {
-        cap = pcap < want ? pcap : want;
-        if (poolOverride && poolOverride < cap)
-          cap = poolOverride;
-        slab = warpGeoSlabBytes(static_cast<int>(pcap), static_cast<int>(cap), false);
-        w = sb + slab <= kSmemMax ? static_cast<uint32_t>((kSmemMax - sb) / slab) : 0u;
-        if (w >= kWarpsPerCta)
-          break;
-      }
-      if (w > kWarpsPerCta)
-        w = kWarpsPerCta;
+      const size_t slab = warpGeoSlabBytes(static_cast<int>(pcap));
+      uint32_t w = 0;
+      if (sb + slab <= kSmemMax)
+        w = static_cast<uint32_t>((kSmemMax - sb) / slab);
+      if (w > 16)
+        w = 16;
       smemWarps[s2] = w;
-      smemCap[s2] = cap;
       slabBytes[s2] = slab;
       sceneBytes[s2] = sb;
-      // in global memory the pool is the reference's own: it never overflows
-      globalCap[s2] = pcap < static_cast<uint32_t>(kMaxPoolNodes) ? pcap : kMaxPoolNodes;
-      globalSlabBytes[s2] =
-          warpGeoSlabBytes(static_cast<int>(pcap), static_cast<int>(globalCap[s2]), true);
       plan[s2].pcap = pcap;
       if (w < 8 && h.polys.size() < 65000)
         anyCramped = true;
@@ -385,15 +366,13 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
       uint32_t w = smemWarps[s2];
       plan[s2].slabOffset = static_cast<uint32_t>(sceneBytes[s2]);
       const bool indexable = h.polys.size() < 65000;  // 16-bit polygon indices in the slabs
-      plan[s2].nodeCap = smemCap[s2];
       if (forceGeneric || !indexable) {
         w = 0;
       } else if (allGlobal || w == 0) {
-        w = kWarpsPerCta;
+        w = 16;
         plan[s2].slabOffset = kSlabInGlobal;
-        plan[s2].nodeCap = globalCap[s2];
-        if (globalSlabBytes[s2] > maxGlobalSlab)
-          maxGlobalSlab = globalSlabBytes[s2];
+        if (slabBytes[s2] > maxGlobalSlab)
+          maxGlobalSlab = slabBytes[s2];
       }
       plan[s2].warps = w;
       if (w) {
@@ -421,7 +400,13 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
       }
       g.warpMode = anyShared ? (anyGlobal ? 2 : 0) : 1;
       // the global-only instance fits two CTAs on an SM (64 registers, no shared memory)
-      const int ctaBudget = sms * (g.warpMode == 1 ? 2 : 1);
+      // The steps of a double-buffered generator's two groups are in flight together
+      // (simulator/simulator.cpp:1377-1399; bps_nav/rl/ddppo/algo/ddppo_trainer.py:205-270).
+      // A small batch's step lasts as long as its slowest query whatever the number of CTAs,
+      // so each group gets half of the SMs and the two kernels run side by side instead of
+      // one waiting for the other's last warp.
+      const int groupsSharing = throughputBound ? 1 : static_cast<int>(sim->cfg.num_groups);
+      const int ctaBudget = sms * (g.warpMode == 1 ? 2 : 1) / groupsSharing;
       std::vector<uint2> ctaMap;
       for (uint32_t s2 = 0; s2 < ns; ++s2) {
         if (!plan[s2].warps)
@@ -441,7 +426,7 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
       BPSN_CUDA(sim, cudaMemcpy(g.dCtaMap, ctaMap.data(), sizeof(uint2) * ctaMap.size(),
                                 cudaMemcpyHostToDevice));
       // dynamic shared memory of a CTA: what the largest of the group's shared-memory scenes
-      // needs (not the whole SM: CTAs of another group's step can then share the SM)
+      // needs, not the whole SM
       g.geoSmem = 0;
       for (uint32_t s2 = 0; s2 < ns; ++s2)
         if (plan[s2].warps && plan[s2].slabOffset != kSlabInGlobal) {
@@ -451,8 +436,8 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
         }
       if (g.geoSmem > kSmemMax)
         return fail(sim, BPSN_ERR_INVALID_ARG, "step plan: shared memory of a CTA exceeds the limit");
-      // the function attribute is the hardware limit whatever this handle's plan asks for:
-      // it is shared by every handle of the process
+      // The function attribute is the hardware limit whatever this handle's plan asks for: it
+      // belongs to the function, so every handle of the process shares it.
       const int kSmemAttr = 227 * 1024 - 64;
       if (g.warpMode == 0)
         BPSN_CUDA(sim, cudaFuncSetAttribute(k_step_warp<0>,
@@ -607,7 +592,11 @@ int32_t bpsn_create(const bpsn_config* cfg, bpsn_sim** out) {
   if (cfg->num_envs % cfg->num_scenes != 0)
     return fail(nullptr, BPSN_ERR_INVALID_ARG,
                 "Num environments is not a multiple of the number of active scenes");
-  if (cfg->num_envs % cfg->num_groups != 0 || cfg->num_scenes % cfg->num_groups != 0)
+  // (the reference also wants num_scenes to be a multiple of num_groups, simulator.cpp:1536-1538,
+  // because each group renders its own scenes; here the groups share the scene tables, so a
+  // single scene may serve both groups: the Python constructor keeps the reference's rule)
+  if (cfg->num_envs % cfg->num_groups != 0 ||
+      (cfg->num_scenes % cfg->num_groups != 0 && cfg->num_scenes != 1))
     return fail(nullptr, BPSN_ERR_INVALID_ARG,
                 "num_envs and num_scenes must be multiples of num_groups");
   int ndev = 0;

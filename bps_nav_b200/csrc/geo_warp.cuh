@@ -16,13 +16,10 @@
 //     (DetourNavMeshQuery.cpp:2118-2132);
 //   * the forward move (moveAlongSurface, getPolyHeight) takes one lane per edge
 //     of the polygon at the head of its queue and 32 detail triangles at a time;
-//   * A* nodes live in a small per-warp pool in order of first visit, found through
-//     a polygon -> slot table (a single tile has one search node per polygon:
-//     dtNavMeshQuery::findPath only creates extra nodes per polygon for tile-border
-//     links, DetourNavMeshQuery.cpp:1040-1045).  Table and pool are the warp's
-//     private slab; a search that visits more polygons than the pool holds is
-//     handed to the one-thread emulation (geodesic()) like a heap that outgrew its
-//     array.  Which slot a node gets does not influence any result;
+//   * A* nodes are direct-mapped, one slot per polygon (a single tile has one
+//     search node per polygon: dtNavMeshQuery::findPath only creates extra
+//     nodes per polygon for tile-border links, DetourNavMeshQuery.cpp:1040-1045)
+//     in the warp's private shared-memory slab;
 //   * the open list lives in registers, three (total, polygon) entries per lane;
 //     "pop" is three hardware warp reductions (minimum total, how many entries
 //     hold it, the holder's polygon).  A binary heap and an arg-min return the
@@ -55,19 +52,15 @@
 
 namespace bpsn {
 
-
 constexpr uint32_t kInfBits = 0x7f800000u;
 constexpr int kOpenSlots = 3;  // register open-list entries per lane (96 per warp)
-// nodeB.y = polygon of the parent (16 bits) | slot of the parent (12 bits) | kNodeOpen.
-constexpr uint32_t kNodeOpen = 0x10000000u;  // exact search only: the node is in the heap
-constexpr uint32_t kNoSlot = 0xfffu;         // parent slot of the start node
-constexpr int kMaxPoolNodes = kMaxAStarNodes;  // dtNodePool never hands out more (PathFinder.cpp:247)
-// Polygon -> slot table of a slab in global memory: visit tag (20 bits) | slot (12 bits).  An
-// entry belongs to the running search iff its tag is the search's; anything else (zero, or the
-// tag of an earlier search on the same slab) reads as "not visited yet".
-constexpr uint32_t kTableSlotMask = 0xfffu;
-constexpr uint32_t kTableTagShift = 12;
-constexpr uint32_t kTableTagMax = (1u << 20) - 1u;
+// nodeB.y = parent (16 bits) | kNodeOpen | visit tag (15 bits).  A node belongs to the running
+// search iff its tag is the search's; anything else (zero, or the tag of an earlier search on
+// the same slab) reads as "not visited yet".
+constexpr uint32_t kNodeOpen = 0x10000u;  // exact search only: the node is in the heap
+constexpr uint32_t kNodeTagMask = 0xfffe0000u;
+constexpr uint32_t kNodeTagOne = 0x20000u;
+constexpr uint32_t kNodeTagMax = 32767u;
 
 // Shared-memory layout of a staged scene (byte offsets, each 16-byte aligned).
 struct StagedLayout {
@@ -95,63 +88,35 @@ __host__ __device__ inline StagedLayout stagedLayout(int nverts, int npolys, int
   return l;
 }
 
-// Per-warp slab for a scene of pcap polygons (a multiple of 16) and a pool of K nodes (even):
-//   nodeA  float4 {x, y, z, cost}                              16 B / node
-//   nodeB  uint2  {total bits, parent polygon | parent slot}     8 B / node
-//   table  polygon -> slot: uint16 (slot + 1, 0 = not visited) per polygon in shared memory,
-//          uint32 (visit tag | slot) per polygon in global memory
-//   path   uint16 corridor, at most 256 polygons               512 B
-// After the search the first node slots are reused for the corridor's portals (a corridor is
-// never longer than the number of nodes the search created).
+// Per-warp slab for node capacity pcap (a multiple of 16):
+//   nodeA  float4 {x, y, z, cost}                      16 B / polygon
+//   nodeB  uint2  {total bits, parent | open | tag}      8 B / polygon
+//   path   uint16 corridor, at most 256 polygons       512 B
+// After the search the node arrays are reused for the corridor's portals.
 // A slab in global memory keeps its contents from one search (and launch) to the next and
 // carries, in the last 16 bytes of its stride, the number of searches it has seen: that number
-// is the visit tag, so a search does not have to wipe the table first.  Shared-memory slabs
-// start every search from a wiped table (2 bytes per polygon).
-__host__ __device__ inline size_t warpGeoSlabBytes(int pcap, int nodeCap, bool inGlobal) {
-  return static_cast<size_t>(nodeCap) * 24 + static_cast<size_t>(pcap) * (inGlobal ? 4 : 2) + 512;
+// is the visit tag, so a search does not have to wipe the node array first (on a
+// 16 000-polygon mesh wiping costs as much as the search).  Shared-memory slabs start every
+// search from a wiped array.
+__host__ __device__ inline size_t warpGeoSlabBytes(int pcap) {
+  return static_cast<size_t>(pcap) * 24 + 512;
 }
 constexpr size_t kGlobalSlabExtra = 16;  // the search counter of a global-memory slab
 
 struct WarpSlab {
   float4* nodeA;
   uint2* nodeB;
-  void* table;         // uint16[pcap] (shared memory) or uint32[pcap] (global memory)
   uint16_t* path;
   uint32_t* searches;  // global-memory slabs only: the search counter
-  int nodeCap;         // nodes the pool holds
-  int tableLen;        // entries of the table (the scene's polygon capacity)
 };
 
-__device__ __forceinline__ WarpSlab carveSlab(uint8_t* base, int pcap, int nodeCap, bool inGlobal) {
+__device__ __forceinline__ WarpSlab carveSlab(uint8_t* base, int pcap) {
   WarpSlab s;
   s.nodeA = reinterpret_cast<float4*>(base);
-  s.nodeB = reinterpret_cast<uint2*>(base + static_cast<size_t>(nodeCap) * 16);
-  s.table = base + static_cast<size_t>(nodeCap) * 24;
-  s.path = reinterpret_cast<uint16_t*>(base + static_cast<size_t>(nodeCap) * 24 +
-                                       static_cast<size_t>(pcap) * (inGlobal ? 4 : 2));
+  s.nodeB = reinterpret_cast<uint2*>(base + static_cast<size_t>(pcap) * 16);
+  s.path = reinterpret_cast<uint16_t*>(base + static_cast<size_t>(pcap) * 24);
   s.searches = nullptr;
-  s.nodeCap = nodeCap;
-  s.tableLen = pcap;
   return s;
-}
-
-// Polygon -> slot.  `tag` is the running search's tag, already shifted (global memory only).
-// Returns the slot, or -1 when the polygon has no node in this search.
-template <bool kGlobal>
-__device__ __forceinline__ int tableLookup(const WarpSlab& w, uint32_t poly, uint32_t tag) {
-  if (kGlobal) {
-    const uint32_t v = static_cast<const uint32_t*>(w.table)[poly];
-    return (v & ~kTableSlotMask) == tag ? static_cast<int>(v & kTableSlotMask) : -1;
-  }
-  return static_cast<int>(static_cast<const uint16_t*>(w.table)[poly]) - 1;
-}
-template <bool kGlobal>
-__device__ __forceinline__ void tableInsert(const WarpSlab& w, uint32_t poly, uint32_t slot,
-                                            uint32_t tag) {
-  if (kGlobal)
-    static_cast<uint32_t*>(w.table)[poly] = tag | slot;
-  else
-    static_cast<uint16_t*>(w.table)[poly] = static_cast<uint16_t>(slot + 1u);
 }
 
 // The staged tables as the search sees them.  Passed by value so that the
@@ -658,32 +623,26 @@ __device__ __forceinline__ void warpForwardMove(const GroupDev& g, const StagedV
 
 constexpr int kSlabHeapCap = kMaxPathPolys;  // the corridor array doubles as the heap
 
-// Start of a search on slab `w`: returns the tag that marks this search's table entries
-// (global memory; shared-memory slabs are wiped instead and use no tag).
+// Start of a search on slab `w`: returns the tag that marks this search's nodes.
 template <bool kGlobal>
-__device__ __forceinline__ uint32_t beginSearch(const WarpSlab w, int lane) {
+__device__ __forceinline__ uint32_t beginSearch(const WarpSlab w, int P, int lane) {
+  uint32_t count = 1u;
+  bool wipe = true;
   if (kGlobal) {
     __syncwarp();
-    uint32_t count = *w.searches + 1u;  // same address in every lane
-    const bool wipe = count > kTableTagMax;  // the 20-bit tag wraps: wipe once and start over
+    count = *w.searches + 1u;  // same address in every lane
+    wipe = count > kNodeTagMax;  // the 15-bit tag wraps: wipe once and start over
     count = wipe ? 1u : count;
     __syncwarp();
     if (lane == 0)
       *w.searches = count;
-    if (wipe) {
-      uint32_t* t = static_cast<uint32_t*>(w.table);
-      for (int i = lane; i < w.tableLen; i += 32)
-        t[i] = 0u;
-    }
-    __syncwarp();
-    return count << kTableTagShift;
   }
-  // 2 bytes per polygon, tableLen a multiple of 16: whole 16-byte stores
-  uint4* t = static_cast<uint4*>(w.table);
-  for (int i = lane; i < (w.tableLen >> 3); i += 32)
-    t[i] = make_uint4(0u, 0u, 0u, 0u);
+  if (wipe) {
+    for (int i = lane; i < P; i += 32)
+      w.nodeB[i] = make_uint2(0u, 0u);
+  }
   __syncwarp();
-  return 0u;
+  return count * kNodeTagOne;
 }
 
 // dtNodeQueue on the slab: the heap holds polygon indices (uint16) in w.path and
@@ -691,18 +650,15 @@ __device__ __forceinline__ uint32_t beginSearch(const WarpSlab w, int lane) {
 // heap of node pointers (Detour/Source/DetourNode.cpp:172-200).  Every lane runs
 // the same code on the same addresses and writes the same values, so each lane
 // reads back what it wrote itself and no synchronisation is needed in here.
-template <bool kGlobal>
-__device__ __forceinline__ float slabTotal(const WarpSlab& w, uint32_t poly, uint32_t tag) {
-  return __uint_as_float(w.nodeB[tableLookup<kGlobal>(w, poly, tag)].x);
+__device__ __forceinline__ float slabTotal(const WarpSlab& w, uint32_t node) {
+  return __uint_as_float(w.nodeB[node].x);
 }
-template <bool kGlobal>
-__device__ __forceinline__ void slabBubbleUp(const WarpSlab& w, int i, uint32_t node,
-                                             uint32_t tag) {
-  const float tn = slabTotal<kGlobal>(w, node, tag);
+__device__ __forceinline__ void slabBubbleUp(const WarpSlab& w, int i, uint32_t node) {
+  const float tn = slabTotal(w, node);
   int parent = (i - 1) / 2;
   while (i > 0) {
     const uint32_t pn = w.path[parent];
-    if (!(slabTotal<kGlobal>(w, pn, tag) > tn))
+    if (!(slabTotal(w, pn) > tn))
       break;
     w.path[i] = static_cast<uint16_t>(pn);
     i = parent;
@@ -710,19 +666,17 @@ __device__ __forceinline__ void slabBubbleUp(const WarpSlab& w, int i, uint32_t 
   }
   w.path[i] = static_cast<uint16_t>(node);
 }
-template <bool kGlobal>
-__device__ __forceinline__ void slabTrickleDown(const WarpSlab& w, int size, int i, uint32_t node,
-                                                uint32_t tag) {
+__device__ __forceinline__ void slabTrickleDown(const WarpSlab& w, int size, int i,
+                                                uint32_t node) {
   int child = i * 2 + 1;
   while (child < size) {
-    if ((child + 1) < size && slabTotal<kGlobal>(w, w.path[child], tag) >
-                                  slabTotal<kGlobal>(w, w.path[child + 1], tag))
+    if ((child + 1) < size && slabTotal(w, w.path[child]) > slabTotal(w, w.path[child + 1]))
       child++;
     w.path[i] = w.path[child];
     i = child;
     child = i * 2 + 1;
   }
-  slabBubbleUp<kGlobal>(w, i, node, tag);
+  slabBubbleUp(w, i, node);
 }
 
 enum AStarOutcome : int {
@@ -730,7 +684,6 @@ enum AStarOutcome : int {
   kAStarExhausted = 1,  // open list ran empty before the end polygon was popped
   kAStarIterCap = 2,
   kAStarHeapFull = 3,   // exact slab search only: more than kSlabHeapCap open nodes
-  kAStarPoolFull = 4,   // the search visits more polygons than the slab's pool holds
 };
 
 // dtNavMeshQuery::findPath (DetourNavMeshQuery.cpp:945-1137) with the reference's
@@ -740,22 +693,20 @@ enum AStarOutcome : int {
 // each; their node updates and heap operations then happen one edge after the
 // other in edge order, as in the reference's loop, because a heap operation
 // compares against the totals the earlier edges have already written.
-template <bool kGlobal>
 __device__ __noinline__ int astarExactSlab(const StagedView sc, const WarpSlab w, int lane,
                                            const float* startPosIn, const float* endPosIn,
                                            uint32_t startIdx, uint32_t endIdx, uint32_t tag,
-                                           int* nodesOut, uint32_t* endSlotOut) {
+                                           int* nodesOut) {
   const float startPos[3] = {startPosIn[0], startPosIn[1], startPosIn[2]};
   const float endPos[3] = {endPosIn[0], endPosIn[1], endPosIn[2]};
   if (lane == 0) {
     const float tot = vdist(startPos, endPos) * 0.999f;
-    w.nodeA[0] = make_float4(startPos[0], startPos[1], startPos[2], 0.f);
-    w.nodeB[0] = make_uint2(__float_as_uint(tot), 0xffffu | (kNoSlot << 16) | kNodeOpen);
-    tableInsert<kGlobal>(w, startIdx, 0u, tag);
+    w.nodeA[startIdx] = make_float4(startPos[0], startPos[1], startPos[2], 0.f);
+    w.nodeB[startIdx] = make_uint2(__float_as_uint(tot), 0xffffu | tag | kNodeOpen);
   }
   __syncwarp();
   int heapSize = 1;
-  slabBubbleUp<kGlobal>(w, 0, startIdx, tag);
+  slabBubbleUp(w, 0, startIdx);
   int nodes = 1;
   int outcome = kAStarExhausted;
   int guard = 0;
@@ -767,20 +718,18 @@ __device__ __noinline__ int astarExactSlab(const StagedView sc, const WarpSlab w
     // pop
     const uint32_t best = w.path[0];
     heapSize--;
-    slabTrickleDown<kGlobal>(w, heapSize, 0, w.path[heapSize], tag);
-    const uint32_t bestSlot = static_cast<uint32_t>(tableLookup<kGlobal>(w, best, tag));
+    slabTrickleDown(w, heapSize, 0, w.path[heapSize]);
     if (best == endIdx) {
-      *endSlotOut = bestSlot;
       outcome = kAStarReached;
       break;
     }
     const NavPoly* bp = &sc.polys[best];
     const int nv = bp->vertCount;
-    const float4 bA = w.nodeA[bestSlot];
-    const uint2 bB = w.nodeB[bestSlot];
+    const float4 bA = w.nodeA[best];
+    const uint2 bB = w.nodeB[best];
     __syncwarp();
     if (lane == 0)
-      w.nodeB[bestSlot].y = bB.y & ~kNodeOpen;
+      w.nodeB[best].y = bB.y & ~kNodeOpen;
     const uint32_t bpar = bB.y & 0xffffu;
     // evaluate: lane j takes edge j
     const int li = lane < kVertsPerPoly ? lane : kVertsPerPoly - 1;
@@ -796,13 +745,11 @@ __device__ __noinline__ int astarExactSlab(const StagedView sc, const WarpSlab w
         nei = best;
       }
     }
-    const int found = tableLookup<kGlobal>(w, nei, tag);
-    const bool isNew = act && found < 0;
-    const uint32_t oldSlot = found < 0 ? 0u : static_cast<uint32_t>(found);
-    const float4 nA = w.nodeA[oldSlot];
-    const uint2 nB = w.nodeB[oldSlot];
+    const float4 nA = w.nodeA[nei];
+    const uint2 nB = w.nodeB[nei];
     const float4 V0 = ldVert4(sc, bp->verts[li]);
     const float4 V1 = ldVert4(sc, bp->verts[(li + 1 == nv) ? 0 : li + 1]);
+    const bool isNew = act && (nB.y & kNodeTagMask) != tag;
     const float nx = isNew ? (V0.x + V1.x) * 0.5f : nA.x;
     const float ny = isNew ? (V0.y + V1.y) * 0.5f : nA.y;
     const float nz = isNew ? (V0.z + V1.z) * 0.5f : nA.z;
@@ -817,15 +764,7 @@ __device__ __noinline__ int astarExactSlab(const StagedView sc, const WarpSlab w
     const float ntotal = cost + heuristic;
     const bool upd = act && (isNew || !(ntotal >= __uint_as_float(nB.x)));
     const bool wasOpen = !isNew && (nB.y & kNodeOpen) != 0;
-    // new nodes take the next pool slots
-    const uint32_t newMask = __ballot_sync(0xffffffffu, isNew);
-    const uint32_t slot =
-        isNew ? static_cast<uint32_t>(nodes) + __popc(newMask & ((1u << lane) - 1u)) : oldSlot;
-    nodes += __popc(newMask);
-    if (nodes > w.nodeCap) {
-      outcome = kAStarPoolFull;
-      break;
-    }
+    nodes += __popc(__ballot_sync(0xffffffffu, isNew));
     // commit edge by edge
     const uint32_t updMask = __ballot_sync(0xffffffffu, upd);
     const uint32_t openMask = __ballot_sync(0xffffffffu, upd && wasOpen);
@@ -834,10 +773,8 @@ __device__ __noinline__ int astarExactSlab(const StagedView sc, const WarpSlab w
       const int j = __ffs(m) - 1;
       const uint32_t node = __shfl_sync(0xffffffffu, nei, j);
       if (lane == j) {
-        w.nodeA[slot] = make_float4(nx, ny, nz, cost);
-        w.nodeB[slot] = make_uint2(__float_as_uint(ntotal), best | (bestSlot << 16) | kNodeOpen);
-        if (isNew)
-          tableInsert<kGlobal>(w, nei, slot, tag);
+        w.nodeA[nei] = make_float4(nx, ny, nz, cost);
+        w.nodeB[nei] = make_uint2(__float_as_uint(ntotal), best | tag | kNodeOpen);
       }
       __syncwarp();
       if ((openMask >> j) & 1u) {
@@ -850,14 +787,14 @@ __device__ __noinline__ int astarExactSlab(const StagedView sc, const WarpSlab w
             at = k0 + __ffs(hit) - 1;
         }
         if (at >= 0)
-          slabBubbleUp<kGlobal>(w, at, node, tag);
+          slabBubbleUp(w, at, node);
       } else {
         if (heapSize >= kSlabHeapCap) {
           full = true;
           break;
         }
         heapSize++;
-        slabBubbleUp<kGlobal>(w, heapSize - 1, node, tag);
+        slabBubbleUp(w, heapSize - 1, node);
       }
     }
     if (full) {
@@ -871,16 +808,17 @@ __device__ __noinline__ int astarExactSlab(const StagedView sc, const WarpSlab w
   return outcome;
 }
 
-// One query by one warp.  `sc` points at the staged tables (shared or global memory).
-// Returns the distance in every lane.  *needFallback is set (uniformly) when the query has
-// to be handed to the one-thread emulation: the exact search's heap outgrew its array, or
-// the search visited more polygons than the slab's pool holds.
+// One query by one warp.  `sc` points at the staged (shared-memory) tables.
+// Returns the distance in every lane.  *needFallback is set (uniformly) when
+// the fast path cannot decide the pop order (tie for the minimum) or the
+// register open list is full.
 template <bool kGlobal>
 __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSlab w, int lane,
                                               const float* startPosIn, uint32_t startRef,
                                               const float* endPosIn, uint32_t endRef,
                                               uint32_t* status, uint32_t* needFallback,
-                                              bool forceExact) {
+                                              bool forceExact
+) {
   // private copies: the caller's arrays are also handed to a non-inlined
   // function and therefore live in local memory
   const float startPos[3] = {startPosIn[0], startPosIn[1], startPosIn[2]};
@@ -921,33 +859,30 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
     pathSize = 1;
     __syncwarp();
   } else {
-    const uint32_t tag = beginSearch<kGlobal>(w, lane);
-    // open list: kOpenSlots register entries per lane: total, and polygon | slot << 16 of the
-    // node; kInfBits = empty.  All loops over the slots are unrolled, so the arrays live in
-    // registers.
+    const uint32_t tag = beginSearch<kGlobal>(w, sc.npolys, lane);
+    // open list: kOpenSlots register entries (total, polygon) per lane, kInfBits = empty.
+    // All loops over the slots are unrolled, so the arrays live in registers.
     uint32_t t[kOpenSlots], p[kOpenSlots];
 #pragma unroll
     for (int k = 0; k < kOpenSlots; ++k) {
       t[k] = kInfBits;
       p[k] = 0;
     }
-    int nodeCount = 1;  // nodes of this search (the same in every lane)
+    int newNodes = 0;  // nodes this lane created (summed over the warp at the end)
     if (lane == 0) {
       const float tot = vdist(startPos, endPos) * 0.999f;
-      w.nodeA[0] = make_float4(startPos[0], startPos[1], startPos[2], 0.f);
-      w.nodeB[0] = make_uint2(__float_as_uint(tot), 0xffffu | (kNoSlot << 16));
-      tableInsert<kGlobal>(w, startIdx, 0u, tag);
+      w.nodeA[startIdx] = make_float4(startPos[0], startPos[1], startPos[2], 0.f);
+      w.nodeB[startIdx] = make_uint2(__float_as_uint(tot), 0xffffu | tag);
       t[0] = __float_as_uint(tot);
-      p[0] = startIdx;  // slot 0
+      p[0] = startIdx;
+      newNodes = 1;
     }
     __syncwarp();
     bool reached = false;
-    uint32_t endSlot = 0u;
     bool overflow = false;  // this lane had to drop an entry, or met a distance outside the bare
                             // square root's range: the query is redone exactly
     // why the search has to be (re)done with the reference's heap
     uint32_t exactWhy = forceExact ? kStatTieFallback : 0u;
-    bool poolFull = false;
     int guard = 0;
     // Edge j of the popped polygon is evaluated by lane (j + rot) & 31 and rot moves on
     // after every pop, so that over a search every lane gets to evaluate neighbours: a
@@ -955,7 +890,7 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
     // cross-lane traffic, and the entries spread over the warp.
     int rot = 0;
     // a two-way tie that is being expanded in place: expansions still to check, the tied
-    // total, the entry that goes second
+    // total, the polygon that goes second
     int tiePending = 0;
     uint32_t tieTotal = 0u, tieOther = 0u;
 
@@ -985,12 +920,12 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
       }
       // Two more reductions, side by side, instead of vote + find-first-set + shuffle
       // (each of which costs about as much as a reduction): how many entries hold the
-      // minimum, and the node of the one that does when it is alone.
+      // minimum, and the polygon of the one that does when it is alone.
       // (a lane whose entries are all taken adds 65536: it asks for a rebalance)
       const uint32_t hsum = __reduce_add_sync(0xffffffffu, mc | (laneFull ? 0x10000u : 0u));
-      uint32_t best = __reduce_min_sync(0xffffffffu, cand);  // polygon | slot << 16
+      uint32_t best = __reduce_min_sync(0xffffffffu, cand);
       // one branch for everything that is not "a unique minimum that is not the end"
-      if ((hsum != 1u) | ((best & 0xffffu) == endIdx) | (guard > 64 * kMaxAStarNodes)) {
+      if ((hsum != 1u) | (best == endIdx) | (guard > 64 * kMaxAStarNodes)) {
         if (guard > 64 * kMaxAStarNodes) {
           *status |= kStatIterCap;
           return BPSN_INF;
@@ -1006,12 +941,12 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
           // Several entries share the minimum.  Superseded entries do not count: only
           // those whose total is still their node's are in the reference's heap.
           int lc = 0;
-          uint32_t liveNode = 0;
+          uint32_t livePoly = 0;
 #pragma unroll
           for (int k = kOpenSlots - 1; k >= 0; --k) {
-            const bool live = m[k] && w.nodeB[p[k] >> 16].x == gm;
+            const bool live = m[k] && w.nodeB[p[k]].x == gm;
             lc += live ? 1 : 0;
-            liveNode = live ? p[k] : liveNode;
+            livePoly = live ? p[k] : livePoly;
           }
           const uint32_t liveHolders = __ballot_sync(0xffffffffu, lc != 0);
           const bool liveMulti = __any_sync(0xffffffffu, lc > 1);
@@ -1025,18 +960,15 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
             // else goes to the exact redo.
             bool resolved = false;
             if (__popc(liveHolders) == 2 && !liveMulti && tiePending == 0) {
-              const uint32_t p0 = __shfl_sync(0xffffffffu, liveNode, __ffs(liveHolders) - 1);
-              const uint32_t p1 = __shfl_sync(0xffffffffu, liveNode, 31 - __clz(liveHolders));
-              // (polygon in the low half: the order below is by polygon index, as before)
-              const bool swap = (p1 & 0xffffu) < (p0 & 0xffffu);
-              const uint32_t first = swap ? p1 : p0, second = swap ? p0 : p1;
-              const uint32_t firstPoly = first & 0xffffu, secondPoly = second & 0xffffu;
-              if (firstPoly != endIdx && secondPoly != endIdx) {
+              const uint32_t p0 = __shfl_sync(0xffffffffu, livePoly, __ffs(liveHolders) - 1);
+              const uint32_t p1 = __shfl_sync(0xffffffffu, livePoly, 31 - __clz(liveHolders));
+              const uint32_t first = min(p0, p1), second = max(p0, p1);
+              if (first != endIdx && second != endIdx) {
                 // lanes 0..5: the neighbours of the first, lanes 6..11: of the second
                 uint32_t key = 0xffffffffu;
                 const bool sideB = lane >= kVertsPerPoly;
                 if (lane < 2 * kVertsPerPoly) {
-                  const NavPoly* q = &sc.polys[sideB ? secondPoly : firstPoly];
+                  const NavPoly* q = &sc.polys[sideB ? second : first];
                   const int jj = sideB ? lane - kVertsPerPoly : lane;
                   const uint16_t qn = q->neis[jj];
                   if (jj < q->vertCount && qn != 0 && !(qn & kExtLink))
@@ -1048,7 +980,7 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
                   const uint32_t other = __shfl_sync(0xffffffffu, key, jj);
                   touch = touch || (sideB && key == other);
                 }
-                touch = key != 0xffffffffu && (touch || key == (sideB ? firstPoly : secondPoly));
+                touch = key != 0xffffffffu && (touch || key == (sideB ? first : second));
                 if (!__any_sync(0xffffffffu, touch)) {
                   resolved = true;
                   *status |= kStatTieInPlace;
@@ -1074,12 +1006,11 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
                 t[k] = m[k] ? kInfBits : t[k];
               continue;
             }
-            best = __shfl_sync(0xffffffffu, liveNode, __ffs(liveHolders) - 1);
+            best = __shfl_sync(0xffffffffu, livePoly, __ffs(liveHolders) - 1);
           }
         }
-        if ((best & 0xffffu) == endIdx) {
+        if (best == endIdx) {
           reached = true;
-          endSlot = best >> 16;
           break;
         }
         if (hsum >> 16) {
@@ -1092,7 +1023,7 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
             t[k] = m[k] ? kInfBits : t[k];  // (the popped entry first)
             m[k] = false;                   // done: the pairs may be refilled just below
             // superseded entries (their total is no longer their node's) only take up room
-            const bool stale = t[k] != kInfBits && w.nodeB[p[k] >> 16].x != t[k];
+            const bool stale = t[k] != kInfBits && w.nodeB[p[k]].x != t[k];
             t[k] = stale ? kInfBits : t[k];
             f[k] = t[k] == kInfBits;
             freeCnt += f[k] ? 1 : 0;
@@ -1128,8 +1059,7 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
 
       // ---- expand: one lane per edge of the popped polygon.  All loads of a
       // round are issued before any of them is used.
-      const uint32_t bestPoly = best & 0xffffu, bestSlot = best >> 16;
-      const NavPoly* bp = &sc.polys[bestPoly];
+      const NavPoly* bp = &sc.polys[best];
       const int ej = (lane - rot) & 31;  // this lane's edge index (>= nv: none)
       const int li = ej < kVertsPerPoly ? ej : kVertsPerPoly - 1;
       const int nv = bp->vertCount;
@@ -1139,20 +1069,19 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
       // verts[li + 1] stays inside the record (neis follows verts)
       const uint16_t vbNext = (&bp->verts[0])[li + 1];
       const uint16_t vbFirst = bp->verts[0];
-      const float4 bA = w.nodeA[bestSlot];
-      const uint2 bB = w.nodeB[bestSlot];
+      const float4 bA = w.nodeA[best];
+      const uint2 bB = w.nodeB[best];
 
       const uint16_t vb = (li + 1 == nv) ? vbFirst : vbNext;
       const bool hasEdge = ej < nv && ne != 0 && !(ne & kExtLink);
-      const uint32_t nei = hasEdge ? static_cast<uint32_t>(ne - 1) : bestPoly;
-      // The neighbour's table entry and the edge's end points are requested as soon as the
-      // polygon record is there: they do not wait for the popped node's own record.
-      const int found = tableLookup<kGlobal>(w, nei, tag);
+      const uint32_t nei = hasEdge ? static_cast<uint32_t>(ne - 1) : best;
+      // The neighbour's node and the edge's end points are requested as soon as the polygon
+      // record is there: they do not wait for the popped node's own record (in global
+      // memory that is a second trip to L2, now overlapped with this one).
+      const float4 nA = w.nodeA[nei];
+      const uint2 nB = w.nodeB[nei];
       const float4 V0 = ldVert4(sc, va);
       const float4 V1 = ldVert4(sc, vb);
-      const uint32_t oldSlot = found < 0 ? 0u : static_cast<uint32_t>(found);
-      const float4 nA = w.nodeA[oldSlot];
-      const uint2 nB = w.nodeB[oldSlot];
       const uint32_t bpar = bB.y & 0xffffu;
       bool act = hasEdge && nei != bpar;
       if ((bB.x != gm) | (dupFlag & 1)) {  // one branch for the two uncommon cases
@@ -1170,12 +1099,8 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
         const uint32_t byEdge = __funnelshift_r(grp, grp, rot);
         act = act && (__ffs(byEdge) - 1) == ej;
       }
-      const bool isNew = act && found < 0;
-      // new nodes take the next pool slots (which slot a node gets influences nothing)
-      const uint32_t newMask = __ballot_sync(0xffffffffu, isNew);
-      const uint32_t slot =
-          isNew ? static_cast<uint32_t>(nodeCount) + __popc(newMask & ((1u << lane) - 1u)) : oldSlot;
-      nodeCount += __popc(newMask);
+      const bool isNew = act && (nB.y & kNodeTagMask) != tag;
+      newNodes += isNew ? 1 : 0;
       const float nx = isNew ? (V0.x + V1.x) * 0.5f : nA.x;
       const float ny = isNew ? (V0.y + V1.y) * 0.5f : nA.y;
       const float nz = isNew ? (V0.z + V1.z) * 0.5f : nA.z;
@@ -1199,11 +1124,7 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
       const uint32_t ntBits = __float_as_uint(ntotal);
       // open or closed alike: skipped unless strictly better (DetourNavMeshQuery.cpp:1075-1080)
       const bool upd = act && (isNew || !(ntotal >= __uint_as_float(nB.x)));
-      if (tiePending | (nodeCount > w.nodeCap)) {  // one branch for the two uncommon cases
-        if (nodeCount > w.nodeCap) {
-          poolFull = true;  // nothing of this round has been stored
-          break;
-        }
+      if (tiePending) {
         // one of the two expansions of a resolved tie (see the pop): it has to be the expected
         // polygon and must not write a total that the other order would have popped first
         if ((tiePending == 1 && best != tieOther) ||
@@ -1217,32 +1138,30 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
       // ---- the new entry goes into this lane's first free register pair
       {
         bool placed = !upd;
-        const uint32_t entry = nei | (slot << 16);
 #pragma unroll
         for (int k = 0; k < kOpenSlots; ++k) {
           const bool here = !placed && t[k] == kInfBits;
           t[k] = here ? ntBits : t[k];
-          p[k] = here ? entry : p[k];
+          p[k] = here ? nei : p[k];
           placed = placed || here;
         }
         overflow = overflow || !placed;
       }
       if (upd) {
-        w.nodeA[slot] = make_float4(nx, ny, nz, cost);
-        w.nodeB[slot] = make_uint2(ntBits, bestPoly | (bestSlot << 16));
-        if (isNew)
-          tableInsert<kGlobal>(w, nei, slot, tag);
+        w.nodeA[nei] = make_float4(nx, ny, nz, cost);
+        w.nodeB[nei] = make_uint2(ntBits, best | tag);
       }
       rot = (rot + 7) & 31;
       __syncwarp();
     }
 
-    if (!exactWhy && !poolFull && __any_sync(0xffffffffu, overflow))
+    if (!exactWhy && __any_sync(0xffffffffu, overflow))
       exactWhy = kStatOpenOverflow;
-    if (exactWhy && !poolFull) {
-      const uint32_t exactTag = beginSearch<kGlobal>(w, lane);
-      const int outcome = astarExactSlab<kGlobal>(sc, w, lane, startPos, endPos, startIdx, endIdx,
-                                                  exactTag, &nodeCount, &endSlot);
+    int nodeTotal = __reduce_add_sync(0xffffffffu, newNodes);
+    if (exactWhy) {
+      const uint32_t exactTag = beginSearch<kGlobal>(w, sc.npolys, lane);
+      const int outcome = astarExactSlab(sc, w, lane, startPos, endPos, startIdx, endIdx, exactTag,
+                                         &nodeTotal);
       if (outcome == kAStarHeapFull) {
         *needFallback = exactWhy;  // hand the query to the global-memory emulation
         return 0.f;
@@ -1251,21 +1170,16 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
         *status |= kStatIterCap;
         return BPSN_INF;
       }
-      poolFull = outcome == kAStarPoolFull;
       *status |= exactWhy;
       reached = outcome == kAStarReached;
     }
-    if (poolFull) {
-      // dtNodePool hands out at most kMaxAStarNodes nodes; a search that asks for more
-      // ends with DT_OUT_OF_NODES in its status, which PathFinder turns into +inf
-      // whatever path was found (PathFinder.cpp:506).  A smaller pool only says that this
-      // slab cannot hold the search.
-      if (w.nodeCap >= kMaxPoolNodes) {
-        *status |= kStatOutOfNodes;
-        return BPSN_INF;
-      }
-      *needFallback = kStatPoolOverflow;
-      return 0.f;
+    // dtNodePool hands out at most kMaxAStarNodes nodes; a search that asks for more
+    // ends with DT_OUT_OF_NODES in its status, which PathFinder turns into +inf
+    // whatever path was found (PathFinder.cpp:506).
+    const bool outOfNodes = nodeTotal > kMaxAStarNodes;
+    if (outOfNodes) {
+      *status |= kStatOutOfNodes;
+      return BPSN_INF;
     }
     if (!reached) {
       *status |= kStatPartial;
@@ -1274,19 +1188,16 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
     // corridor: walk parents from the end polygon, then reverse
     int length = 0;
     if (lane == 0) {
-      uint32_t cur = endSlot;
-      while (cur != kNoSlot && length <= kMaxAStarNodes) {
+      uint32_t cur = endIdx;
+      while (cur != 0xffffu && length <= kMaxAStarNodes) {
         length++;
-        cur = (w.nodeB[cur].y >> 16) & kNoSlot;
+        cur = w.nodeB[cur].y & 0xffffu;
       }
       if (length <= kMaxPathPolys) {
-        cur = endSlot;
-        uint32_t poly = endIdx;
+        cur = endIdx;
         for (int i = length - 1; i >= 0; --i) {
-          w.path[i] = static_cast<uint16_t>(poly);
-          const uint32_t y = w.nodeB[cur].y;
-          poly = y & 0xffffu;
-          cur = (y >> 16) & kNoSlot;
+          w.path[i] = static_cast<uint16_t>(cur);
+          cur = w.nodeB[cur].y & 0xffffu;
         }
       }
     }
@@ -1299,7 +1210,15 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
     pathSize = length;
   }
 
-  return warpFunnel(sc, w, lane, startPos, endPos, pathSize, status);
+  const float dres = warpFunnel(sc, w, lane, startPos, endPos, pathSize, status);
+  if (kGlobal) {
+    // the portals sit in the first node slots; what they left in the tag field must not
+    // pass for a visit mark of a later search
+    __syncwarp();
+    for (int i = lane; i + 1 < pathSize; i += 32)
+      w.nodeB[i].y = 0u;
+  }
+  return dres;
 }
 
 // The part of k_step_warp after the scene is in place: the warp's loop over list slots.
@@ -1340,13 +1259,11 @@ __device__ __forceinline__ void stepWarpQueries(const GroupDev& g, const SceneTa
   sv.npolys = sc.npolys;
   sv.polyMask = sc.polyMask;
   sv.refBase = sc.refBase;
-  // (global memory: one stride for all scenes; the slab is carved per query below)
-  const int nodeCap = static_cast<int>(pl.nodeCap);
+  // (global memory: one stride for all scenes, slabs of different sizes must not overlap)
+  // (global memory: carved per query below)
   WarpSlab w = carveSlab(
-      kGlobal ? globalSlabs
-              : smem + pl.slabOffset +
-                    static_cast<size_t>(warp) * warpGeoSlabBytes(pcap, nodeCap, false),
-      pcap, nodeCap, kGlobal);
+      kGlobal ? globalSlabs : smem + pl.slabOffset + static_cast<size_t>(warp) * warpGeoSlabBytes(pcap),
+      pcap);
   // Large slabs (the group's slabs together exceed what L2 holds) belong to environments
   // instead: an environment's searches start from the same goal step after step and touch
   // nearly the same nodes, so its own slab is still warm in L2 from the step before, whereas
@@ -1375,7 +1292,7 @@ __device__ __forceinline__ void stepWarpQueries(const GroupDev& g, const SceneTa
           slabPerEnv ? static_cast<size_t>(e)
                      : static_cast<size_t>(blockIdx.x) * (blockDim.x >> 5) + static_cast<size_t>(warp);
       uint8_t* slab = globalSlabs + slabIdx * globalSlabStride;
-      w = carveSlab(slab, pcap, nodeCap, true);
+      w = carveSlab(slab, pcap);
       w.searches = reinterpret_cast<uint32_t*>(slab + globalSlabStride - kGlobalSlabExtra);
     }
     const bool done = entry & kListDone, moved = entry & kListMoved;

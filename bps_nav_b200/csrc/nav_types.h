@@ -136,8 +136,6 @@ enum QueryStatus : uint32_t {
   kStatOpenOverflow = 1u << 9,  // register open list full, or a zero / out-of-range distance in the
                                 // fast search: query rerun the same way
   kStatTieInPlace = 1u << 10,   // a two-way open-list tie whose order cannot matter was expanded in place
-  kStatPoolOverflow = 1u << 11,  // the search visited more polygons than the warp's node pool holds:
-                                 // query rerun by the one-thread emulation (same result)
 };
 
 }  // namespace bpsn

@@ -157,8 +157,6 @@ struct WarpPlan {
                         // kSlabInGlobal: tables and slabs of this scene stay in global memory
   uint32_t warps;
   uint32_t ctas;
-  uint32_t nodeCap;     // A* nodes a slab's pool holds (even)
-  uint32_t pad;
 };
 constexpr uint32_t kSlabInGlobal = 0xffffffffu;
 

@@ -100,11 +100,7 @@ enum {
   /* work on every scene in global memory (tables and A* slabs L2 / L1 resident, two CTAs
      per SM) whatever its size; the planner otherwise does this only for large batches
      that contain a scene too big to share an SM's shared memory with 8 slabs */
-  BPSN_FLAG_GLOBAL_MEMORY = 1u << 4,
-  /* warp kernel, scenes in shared memory: give every warp a pool of only 32 A* nodes, so
-     that most searches outgrow it and are redone by the one-thread emulation -- for
-     testing that hand-over (results are the same either way) */
-  BPSN_FLAG_SMALL_POOL = 1u << 5
+  BPSN_FLAG_GLOBAL_MEMORY = 1u << 4
 };
 
 /* Fields addressable through bpsn_get_ptr.  All arrays are indexed by the
