@@ -14,7 +14,8 @@ SYMBOLS = [
     "bpsn_create", "bpsn_destroy", "bpsn_set_navmesh_file", "bpsn_set_navmesh_blob",
     "bpsn_set_episodes", "bpsn_set_env_scenes", "bpsn_set_scene_geometry", "bpsn_finalize", "bpsn_reset", "bpsn_step_start", "bpsn_step_start_ex",
     "bpsn_step_end", "bpsn_render", "bpsn_get_ptr", "bpsn_device_error_flags", "bpsn_profile_enable", "bpsn_profile_read", "bpsn_scene_info", "bpsn_query_snap", "bpsn_query_try_step",
-    "bpsn_query_geodesic", "bpsn_gae_workspace_bytes", "bpsn_gae", "bpsn_gae_static", "bpsn_selftest_sqrt", "bpsn_debug_set_search_count", "bpsn_dataset_open", "bpsn_dataset_num_scenes", "bpsn_dataset_scene",
+    "bpsn_query_geodesic", "bpsn_gae_workspace_bytes", "bpsn_gae", "bpsn_gae_static", "bpsn_adv_workspace_bytes",
+    "bpsn_adv_normalize", "bpsn_adv_mean", "bpsn_adv_ema_shift", "bpsn_selftest_sqrt", "bpsn_debug_set_search_count", "bpsn_dataset_open", "bpsn_dataset_num_scenes", "bpsn_dataset_scene",
     "bpsn_dataset_close", "bpsn_last_error",
     "bpsn_version",
 ]
@@ -42,6 +43,14 @@ class Config(C.Structure):
     _fields_ = [("gpu_id", C.c_int32), ("num_envs", C.c_uint32), ("num_groups", C.c_uint32),
                 ("num_scenes", C.c_uint32), ("seed", C.c_uint64), ("flags", C.c_uint32),
                 ("task", C.c_uint32), ("render_width", C.c_uint32), ("render_height", C.c_uint32)]
+
+
+class AdvSegment(C.Structure):
+    _fields_ = [("advantages", C.c_void_p), ("N", C.c_uint32), ("start", C.c_uint32),
+                ("end", C.c_uint32), ("group", C.c_uint32)]
+
+
+MAX_ADV_SEGMENTS = 64
 
 
 class Episode(C.Structure):
@@ -90,6 +99,11 @@ def load():
                              C.c_float, vp, vp]
     lib.bpsn_gae_static.argtypes = [vp, vp, vp, vp, vp, vp, u32, u32, C.c_double, C.c_double, i32,
                                     C.c_float, vp]
+    lib.bpsn_adv_workspace_bytes.argtypes = []
+    lib.bpsn_adv_workspace_bytes.restype = sz
+    lib.bpsn_adv_normalize.argtypes = [C.POINTER(AdvSegment), u32, u32, C.c_float, vp, vp]
+    lib.bpsn_adv_mean.argtypes = [C.POINTER(AdvSegment), u32, u32, vp, vp, vp]
+    lib.bpsn_adv_ema_shift.argtypes = [C.POINTER(AdvSegment), u32, u32, vp, vp, C.c_float, vp]
     lib.bpsn_selftest_sqrt.argtypes = [i32, u32, u32, C.POINTER(C.c_uint64)]
     lib.bpsn_debug_set_search_count.argtypes = [C.c_void_p, u32, u32]
     lib.bpsn_dataset_open.argtypes = [C.c_char_p, C.c_char_p, u32, C.POINTER(vp)]
@@ -104,7 +118,7 @@ def load():
     lib.bpsn_version.restype = C.c_char_p
     for name in SYMBOLS:
         fn = getattr(lib, name)
-        if name not in ("bpsn_gae_workspace_bytes", "bpsn_last_error", "bpsn_version",
+        if name not in ("bpsn_gae_workspace_bytes", "bpsn_adv_workspace_bytes", "bpsn_last_error", "bpsn_version",
                         "bpsn_dataset_num_scenes", "bpsn_dataset_close"):
             fn.restype = i32
     _lib = lib

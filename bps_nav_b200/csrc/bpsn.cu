@@ -1180,6 +1180,113 @@ int32_t bpsn_gae(const float* rewards, float* values, const uint8_t* masks,
 }
 
 // ---------------------------------------------------------------------------
+// Advantage normalisation over segments (see gae_kernels.cuh)
+
+namespace {
+constexpr uint32_t kAdvMaxBlocksPerSeg = 592;  // 4 x 148 SMs when a single segment is given
+
+int32_t buildAdvList(const char* who, const bpsn_adv_segment* segments, uint32_t num_segments,
+                     uint32_t T, AdvSegmentList* out) {
+  if (!segments || num_segments == 0 || num_segments > BPSN_MAX_ADV_SEGMENTS)
+    return fail(nullptr, BPSN_ERR_INVALID_ARG,
+                std::string(who) + ": between 1 and " + std::to_string(BPSN_MAX_ADV_SEGMENTS) +
+                    " segments");
+  if (T == 0)
+    return fail(nullptr, BPSN_ERR_INVALID_ARG, std::string(who) + ": T must be positive");
+  size_t largest = 0;
+  for (uint32_t i = 0; i < num_segments; ++i) {
+    const bpsn_adv_segment& sg = segments[i];
+    if (!sg.advantages || sg.start >= sg.end || sg.end > sg.N)
+      return fail(nullptr, BPSN_ERR_INVALID_ARG,
+                  std::string(who) + ": segment " + std::to_string(i) +
+                      " needs a tensor and 0 <= start < end <= N");
+    for (uint32_t j = 0; j < i; ++j)
+      if (segments[j].advantages == sg.advantages && segments[j].start < sg.end &&
+          sg.start < segments[j].end)
+        return fail(nullptr, BPSN_ERR_INVALID_ARG,
+                    std::string(who) + ": segments " + std::to_string(j) + " and " +
+                        std::to_string(i) + " overlap");
+    out->seg[i] = AdvSegment{sg.advantages, sg.N, sg.start, sg.end, sg.group};
+    const size_t elems = static_cast<size_t>(T) * (sg.end - sg.start);
+    if (elems > largest)
+      largest = elems;
+  }
+  out->count = num_segments;
+  out->T = T;
+  uint32_t bps = static_cast<uint32_t>((largest + 2047) / 2048);
+  const uint32_t cap = kAdvMaxBlocksPerSeg / num_segments ? kAdvMaxBlocksPerSeg / num_segments : 1u;
+  if (bps > cap)
+    bps = cap;
+  if (bps == 0)
+    bps = 1;
+  out->blocksPerSeg = bps;
+  return BPSN_OK;
+}
+}  // namespace
+
+size_t bpsn_adv_workspace_bytes(void) {
+  return sizeof(GaeStat) * static_cast<size_t>(kAdvMaxBlocksPerSeg + BPSN_MAX_ADV_SEGMENTS);
+}
+
+int32_t bpsn_adv_normalize(const bpsn_adv_segment* segments, uint32_t num_segments, uint32_t T,
+                           float eps, void* workspace, void* stream) {
+  if (!workspace)
+    return fail(nullptr, BPSN_ERR_INVALID_ARG, "bpsn_adv_normalize: null workspace");
+  AdvSegmentList list{};
+  int32_t rc = buildAdvList("bpsn_adv_normalize", segments, num_segments, T, &list);
+  if (rc)
+    return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  GaeStat* partials = static_cast<GaeStat*>(workspace);
+  const dim3 grid(list.blocksPerSeg, list.count);
+  k_adv_stats<<<grid, kAdvBlock, 0, s>>>(list, partials);
+  k_adv_normalize<<<grid, kAdvBlock, 0, s>>>(list, partials, eps);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess)
+    return fail(nullptr, BPSN_ERR_CUDA,
+                std::string("bpsn_adv_normalize launch: ") + cudaGetErrorString(e));
+  return BPSN_OK;
+}
+
+int32_t bpsn_adv_mean(const bpsn_adv_segment* segments, uint32_t num_segments, uint32_t T,
+                      float* mean_out, void* workspace, void* stream) {
+  if (!workspace || !mean_out)
+    return fail(nullptr, BPSN_ERR_INVALID_ARG, "bpsn_adv_mean: null workspace or output");
+  AdvSegmentList list{};
+  int32_t rc = buildAdvList("bpsn_adv_mean", segments, num_segments, T, &list);
+  if (rc)
+    return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  GaeStat* partials = static_cast<GaeStat*>(workspace);
+  k_adv_stats<<<dim3(list.blocksPerSeg, list.count), kAdvBlock, 0, s>>>(list, partials);
+  k_adv_mean<<<1, 32, 0, s>>>(list, partials, mean_out);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess)
+    return fail(nullptr, BPSN_ERR_CUDA, std::string("bpsn_adv_mean launch: ") + cudaGetErrorString(e));
+  return BPSN_OK;
+}
+
+int32_t bpsn_adv_ema_shift(const bpsn_adv_segment* segments, uint32_t num_segments, uint32_t T,
+                           float* ema_state, const float* mean, float beta, void* stream) {
+  if (!ema_state || !mean)
+    return fail(nullptr, BPSN_ERR_INVALID_ARG, "bpsn_adv_ema_shift: null state or mean");
+  if (!(beta >= 0.f && beta < 1.f))
+    return fail(nullptr, BPSN_ERR_INVALID_ARG, "bpsn_adv_ema_shift: beta must be in [0, 1)");
+  AdvSegmentList list{};
+  int32_t rc = buildAdvList("bpsn_adv_ema_shift", segments, num_segments, T, &list);
+  if (rc)
+    return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  k_adv_ema_update<<<1, 32, 0, s>>>(ema_state, mean, beta);
+  k_adv_shift<<<dim3(list.blocksPerSeg, list.count), kAdvBlock, 0, s>>>(list, ema_state);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess)
+    return fail(nullptr, BPSN_ERR_CUDA,
+                std::string("bpsn_adv_ema_shift launch: ") + cudaGetErrorString(e));
+  return BPSN_OK;
+}
+
+// ---------------------------------------------------------------------------
 // bpsn_gae_static: the same two GAE launches as bpsn_gae, for callers that are
 // not able to provide a device workspace.  The per-block advantage statistics
 // go to a fixed array that is part of the library image, so the call performs

@@ -169,4 +169,154 @@ k_gae_normalize(float* __restrict__ adv, size_t total, const GaeStat* __restrict
     adv[i] = (adv[i] - mean) / denom;
 }
 
+// ---------------------------------------------------------------------------
+// Advantage normalisation over segments.  A segment is a range of environment
+// columns [start, end) of one [T, N] advantage tensor; segments that carry the
+// same group number are normalised together, over all of their elements:
+//   * one segment covering the batch      -> PPO.get_advantages (ppo.py:190-201);
+//   * the two halves of a double-buffered rollout in one group -> the same call
+//     on the concatenation the reference builds with torch.cat(advantages, 1);
+//   * one group per range of environments -> per-minibatch statistics.
+// Passed to the kernels by value (no device copy of the list).
+constexpr int kMaxAdvSegments = 64;
+constexpr int kAdvBlock = 256;
+
+struct AdvSegment {
+  float* adv;       // [T, N] row-major
+  uint32_t N;       // row length of that tensor
+  uint32_t start;   // first environment column
+  uint32_t end;     // one past the last
+  uint32_t group;   // segments with equal numbers share mean and std
+};
+struct AdvSegmentList {
+  AdvSegment seg[kMaxAdvSegments];
+  uint32_t count;
+  uint32_t blocksPerSeg;
+  uint32_t T;
+};
+
+// element i of a segment: row i / width, column start + i % width
+__device__ __forceinline__ size_t advIndex(const AdvSegment& sg, uint32_t width, size_t i) {
+  const size_t row = i / width;
+  return row * sg.N + sg.start + (i - row * width);
+}
+
+// grid (blocksPerSeg, count): partials[seg * blocksPerSeg + block] <- (n, mean, M2) of the
+// block's share of the segment
+__global__ void __launch_bounds__(kAdvBlock)
+k_adv_stats(const AdvSegmentList L, GaeStat* __restrict__ partials) {
+  const AdvSegment sg = L.seg[blockIdx.y];
+  const uint32_t width = sg.end - sg.start;
+  const size_t total = static_cast<size_t>(L.T) * width;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  double sum = 0.0, sumSq = 0.0;
+  unsigned long long count = 0;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += stride) {
+    const double a = static_cast<double>(sg.adv[advIndex(sg, width, i)]);
+    sum += a;
+    sumSq += a * a;
+    ++count;
+  }
+  GaeStat st;
+  st.n = static_cast<double>(count);
+  st.mean = count ? sum / st.n : 0.0;
+  const double m2 = count ? sumSq - sum * st.mean : 0.0;
+  st.m2 = m2 > 0.0 ? m2 : 0.0;
+  __shared__ GaeStat sh[kAdvBlock / 32];
+  st = gaeWarpReduce(st);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0)
+    sh[warp] = st;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    GaeStat acc = sh[0];
+    for (int w = 1; w < kAdvBlock / 32; ++w)
+      acc = gaeMerge(acc, sh[w]);
+    partials[blockIdx.y * gridDim.x + blockIdx.x] = acc;
+  }
+}
+
+// statistics of the group the block's segment belongs to (first warp; result in lane 0)
+__device__ __forceinline__ GaeStat advGroupStat(const AdvSegmentList& L, uint32_t group,
+                                                const GaeStat* __restrict__ partials) {
+  GaeStat st;
+  st.n = 0.0;
+  st.mean = 0.0;
+  st.m2 = 0.0;
+  for (uint32_t s = 0; s < L.count; ++s) {
+    if (L.seg[s].group != group)
+      continue;
+    for (uint32_t b = threadIdx.x; b < L.blocksPerSeg; b += 32)
+      st = gaeMerge(st, partials[s * L.blocksPerSeg + b]);
+  }
+  return gaeWarpReduce(st);
+}
+
+// mode 0: (a - mean) / (std + eps), unbiased std, per group
+__global__ void __launch_bounds__(kAdvBlock)
+k_adv_normalize(const AdvSegmentList L, const GaeStat* __restrict__ partials, float eps) {
+  const AdvSegment sg = L.seg[blockIdx.y];
+  __shared__ float sMean, sDenom;
+  if (threadIdx.x < 32) {
+    const GaeStat st = advGroupStat(L, sg.group, partials);
+    if (threadIdx.x == 0) {
+      const double var =
+          st.n > 1.0 ? st.m2 / (st.n - 1.0) : __longlong_as_double(0x7ff8000000000000ll);
+      sMean = static_cast<float>(st.mean);
+      sDenom = static_cast<float>(sqrt(var)) + eps;
+    }
+  }
+  __syncthreads();
+  const float mean = sMean, denom = sDenom;
+  const uint32_t width = sg.end - sg.start;
+  const size_t total = static_cast<size_t>(L.T) * width;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += stride) {
+    const size_t at = advIndex(sg, width, i);
+    sg.adv[at] = (sg.adv[at] - mean) / denom;
+  }
+}
+
+// mean over every element of every segment -> *meanOut (one block)
+__global__ void __launch_bounds__(32)
+k_adv_mean(const AdvSegmentList L, const GaeStat* __restrict__ partials, float* meanOut) {
+  GaeStat st;
+  st.n = 0.0;
+  st.mean = 0.0;
+  st.m2 = 0.0;
+  for (uint32_t i = threadIdx.x; i < L.count * L.blocksPerSeg; i += 32)
+    st = gaeMerge(st, partials[i]);
+  st = gaeWarpReduce(st);
+  if (threadIdx.x == 0)
+    *meanOut = static_cast<float>(st.mean);
+}
+
+// The running mean DD-PPO subtracts (DecentralizedDistributedMixin._get_advantages_distributed,
+// bps_nav/rl/ddppo/algo/ddppo.py:46-64): biased = beta * biased + (1 - beta) * mean,
+// unbias = beta * unbias + (1 - beta), shift = biased / unbias.  state = {biased, unbias, shift}.
+__global__ void k_adv_ema_update(float* state, const float* mean, float beta) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    const float biased = state[0] * beta + (1.f - beta) * *mean;
+    const float unbias = state[1] * beta + (1.f - beta);
+    state[0] = biased;
+    state[1] = unbias;
+    state[2] = biased / unbias;
+  }
+}
+__global__ void __launch_bounds__(kAdvBlock)
+k_adv_shift(const AdvSegmentList L, const float* __restrict__ state) {
+  const AdvSegment sg = L.seg[blockIdx.y];
+  const float shift = state[2];
+  const uint32_t width = sg.end - sg.start;
+  const size_t total = static_cast<size_t>(L.T) * width;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += stride) {
+    const size_t at = advIndex(sg, width, i);
+    sg.adv[at] = sg.adv[at] - shift;
+  }
+}
+
 }  // namespace bpsn

@@ -29,6 +29,11 @@
  *   bpsn_gae
  *       RolloutStorage.compute_returns          bps_nav/common/rollout_storage.py:203-219
  *       PPO.get_advantages                      bps_nav/rl/ppo/ppo.py:190-201
+ *   bpsn_adv_normalize
+ *       PPO.get_advantages over concatenated buffers or per range of environments
+ *   bpsn_adv_mean / bpsn_adv_ema_shift
+ *       DecentralizedDistributedMixin._get_advantages_distributed
+ *                                               bps_nav/rl/ddppo/algo/ddppo.py:18-64
  */
 #ifndef BPSN_H
 #define BPSN_H
@@ -249,6 +254,48 @@ int32_t bpsn_gae(const float* rewards, float* values, const uint8_t* masks,
                  const float* next_value, float* returns, float* advantages, uint32_t T,
                  uint32_t N, double gamma, double tau, int32_t normalize, float eps,
                  void* workspace, void* stream);
+
+/* Advantage normalisation over segments of environments; every tensor pointer is a DEVICE
+ * pointer, the segment list itself is HOST memory (read during the call).
+ *
+ * A segment is a range of environment columns [start, end) of one float32 [T, N] advantage
+ * tensor (row-major; rows of N).  Segments with the same `group` number are normalised
+ * together, over all T * (end - start) elements of all of them:
+ *   - one segment {adv, N, 0, N, 0}: the whole batch, PPO.get_advantages
+ *     (bps_nav/rl/ppo/ppo.py:190-201): (a - mean) / (std + eps), unbiased std;
+ *   - the two halves of a double-buffered rollout as two segments of one group: what the
+ *     reference computes on torch.cat(advantages, 1) (ppo.py:191-198);
+ *   - k ranges of environments with k different group numbers: each range on its own
+ *     statistics (per-minibatch normalisation; the reference's minibatches are sets of
+ *     environments, bps_nav/common/rollout_storage.py:228-238).
+ * Segments must not overlap.  At most BPSN_MAX_ADV_SEGMENTS per call.  `workspace`: device
+ * scratch of at least bpsn_adv_workspace_bytes() bytes. */
+#define BPSN_MAX_ADV_SEGMENTS 64
+typedef struct {
+  float* advantages; /* device, [T, N] */
+  uint32_t N;        /* row length of that tensor */
+  uint32_t start;    /* first environment column of the segment */
+  uint32_t end;      /* one past the last */
+  uint32_t group;    /* segments with equal group numbers share mean and std */
+} bpsn_adv_segment;
+size_t bpsn_adv_workspace_bytes(void);
+int32_t bpsn_adv_normalize(const bpsn_adv_segment* segments, uint32_t num_segments, uint32_t T,
+                           float eps, void* workspace, void* stream);
+
+/* The advantage baseline DD-PPO installs instead (DecentralizedDistributedMixin.
+ * _get_advantages_distributed, bps_nav/rl/ddppo/algo/ddppo.py:46-64): advantages minus the
+ * bias-corrected exponential moving average of their mean; no division by the std.
+ *   bpsn_adv_mean       *mean_out (device float) <- mean over every element of every segment.
+ *                       With several workers the caller all-reduces it and divides by the
+ *                       world size, as distributed_mean_and_var does (ddppo.py:18-42).
+ *   bpsn_adv_ema_shift  ema_state (device float[3]: biased, unbias, last shift; start at 0):
+ *                       biased = beta * biased + (1 - beta) * mean; unbias = beta * unbias +
+ *                       (1 - beta); every element of every segment -= biased / unbias.
+ *                       The reference uses beta = 0.8. */
+int32_t bpsn_adv_mean(const bpsn_adv_segment* segments, uint32_t num_segments, uint32_t T,
+                      float* mean_out, void* workspace, void* stream);
+int32_t bpsn_adv_ema_shift(const bpsn_adv_segment* segments, uint32_t num_segments, uint32_t T,
+                           float* ema_state, const float* mean, float beta, void* stream);
 
 /* bpsn_gae without any allocation.  No counterpart in the reference.
  *

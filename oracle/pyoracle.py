@@ -31,11 +31,21 @@ def available():
     return os.path.exists(REF_LIB) and os.path.exists(SIM_LIB)
 
 
-def build(reference_root="/root/reference"):
+def reference_root():
+    """Root of the bps-nav tree on this machine: $BPS_NAV_REFERENCE, else a directory named
+    ``reference`` beside the repository; None when neither exists."""
+    cand = os.environ.get("BPS_NAV_REFERENCE")
+    if not cand:
+        cand = os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+    return cand if os.path.isdir(os.path.join(cand, "simulator")) else None
+
+
+def build(root=None):
     """Builds oracle/_ref (needs the reference sources) and oracle/_build.  Returns True when both
     libraries exist afterwards."""
-    if os.path.isdir(reference_root):
-        subprocess.run(["make", "-C", HERE, "ref", f"REF={reference_root}"], check=True,
+    root = root or reference_root()
+    if root:
+        subprocess.run(["make", "-C", HERE, "ref", f"REF={root}"], check=True,
                        capture_output=True)
     if os.path.exists(REF_LIB):
         subprocess.run(["make", "-C", HERE, "sim"], check=True, capture_output=True)

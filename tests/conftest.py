@@ -16,14 +16,13 @@ def pytest_configure(config):
 
 
 def pytest_sessionstart(session):
-    """A fresh checkout has no built library: build it once (nvcc cross-compiles without a
-    GPU).  An existing library is left alone, whatever its age."""
+    """Builds the library when it is missing or older than one of its sources (nvcc
+    cross-compiles without a GPU), so that no test runs against a stale binary."""
     from bps_nav_b200 import build as _build
-    if not os.path.exists(_build.LIB):
-        try:
-            _build.build(force=True)
-        except Exception as e:  # the tests that need the library will say so themselves
-            sys.stderr.write(f"could not build libbpsn.so: {e}\n")
+    try:
+        _build.build()
+    except Exception as e:  # the tests that need the library will say so themselves
+        sys.stderr.write(f"could not build libbpsn.so: {e}\n")
 
 
 def scene_path(name):

@@ -1,6 +1,7 @@
 """Generates every fixture under tests/golden/ (run from the repository root, on a machine that
-has the reference tree where oracle/Makefile's REF variable points):
+has the bps-nav tree; BPS_NAV_REFERENCE names its root):
 
+    export BPS_NAV_REFERENCE=/path/to/bps-nav
     make -C oracle ref sim && python tests/golden/make_fixtures.py
 
 What it writes
@@ -19,6 +20,11 @@ What it writes
   gae_ref.npz                   inputs and outputs of the reference's own Python
                                 RolloutStorage.compute_returns (loaded from the reference tree by
                                 file path) and of the get_advantages formula
+  gae_c2_16384.npz              the same at benchmark config 2's full size (T = 32, N = 16384):
+                                the inputs come from a seeded numpy generator that the tests
+                                re-run (gae_c2_inputs below), the file holds the reference's
+                                outputs for every 16th environment, CRC-32 of the full returns /
+                                advantages arrays and their sums
 
 Scene list: c0 = benchmark config 0 (20x20 m, 12 boxes, seed 1000); c1 = config 1 (50x50 m, 60
 boxes, seed 1001); d0 = a dense plan with the polygon count that config 1's description quotes
@@ -30,6 +36,7 @@ import os
 import subprocess
 import sys
 import types
+import zlib
 
 import numpy as np
 
@@ -195,6 +202,48 @@ def make_gae(reference_root):
     np.savez_compressed(os.path.join(GOLD, "gae_ref.npz"), **out)
     print("   gae_ref.npz written from the reference's RolloutStorage.compute_returns")
 
+    # benchmark config 2 at its full size
+    T, N = 32, 16384
+    r, v, m, nv = gae_c2_inputs(T, N)
+    rs = RS(T, N, _Space(), None, 8, 1)
+    sb = rs.storage_buffers
+    sb["rewards"].copy_(torch.from_numpy(r)[..., None])
+    sb["value_preds"].copy_(torch.from_numpy(v)[..., None])
+    sb["masks"].copy_(torch.from_numpy(m)[..., None])
+    rs.step = T
+    rs.compute_returns(torch.from_numpy(nv)[:, None], True, 0.99, 0.95)
+    ret = sb["returns"][:T, :, 0]
+    adv = ret - sb["value_preds"][:T, :, 0]                     # ppo.py:193-195
+    advn = (adv - adv.mean()) / (adv.std() + 1e-5)               # ppo.py:201
+    # per range of 4096 environments (the reference's minibatches are sets of environments,
+    # rollout_storage.py:228-238); the same formula on each range
+    advr = torch.cat([(adv[:, s:s + 4096] - adv[:, s:s + 4096].mean()) /
+                      (adv[:, s:s + 4096].std() + 1e-5) for s in range(0, N, 4096)], 1)
+    cols = np.arange(0, N, 16)
+    np.savez_compressed(
+        os.path.join(GOLD, "gae_c2_16384.npz"), cols=cols.astype(np.int32),
+        returns_cols=ret.numpy()[:, cols].copy(), adv_cols=adv.numpy()[:, cols].copy(),
+        adv_norm_cols=advn.numpy()[:, cols].copy(), adv_range_norm_cols=advr.numpy()[:, cols].copy(),
+        returns_crc=np.uint32(zlib.crc32(np.ascontiguousarray(ret.numpy()).tobytes())),
+        adv_crc=np.uint32(zlib.crc32(np.ascontiguousarray(adv.numpy()).tobytes())),
+        returns_sum=np.float64(ret.double().sum().item()),
+        adv_mean=np.float64(adv.double().mean().item()),
+        adv_std=np.float64(adv.double().std().item()),
+        adv_mean_f32=np.float32(adv.mean().item()), adv_std_f32=np.float32(adv.std().item()))
+    print("   gae_c2_16384.npz written (T = 32, N = 16384)")
+
+
+def gae_c2_inputs(T=32, N=16384, seed=20250):
+    """Benchmark config 2's inputs: rewards, values ~ N(0, 1) float32 [T+1, N], masks = not
+    Bernoulli(0.002) bool [T+1, N], next_value float32 [N], from numpy's PCG64 (the same arrays on
+    every machine)."""
+    rng = np.random.default_rng(seed)
+    r = rng.standard_normal((T + 1, N), dtype=np.float32)
+    v = rng.standard_normal((T + 1, N), dtype=np.float32)
+    m = rng.random((T + 1, N)) >= 0.002
+    nv = rng.standard_normal(N, dtype=np.float32)
+    return r, v, m, nv
+
 
 def main():
     if not pyoracle.available():
@@ -217,8 +266,12 @@ def main():
         eps = np.load(os.path.join(SCENES, "c0.episodes.npy"))
         make_traj(c0, eps, "c0_traj.npz", 64, 500, seed=12345, act_seed=777, mix="uniform")
         make_traj(c0, eps, "c0_policy_traj.npz", 64, 500, seed=12345, act_seed=778, mix="policy")
-    if (not only or "gae" in only) and os.path.isdir("/root/reference"):
-        make_gae("/root/reference")
+    if not only or "gae" in only:
+        ref = pyoracle.reference_root()
+        if ref:
+            make_gae(ref)
+        else:
+            print("   GAE fixtures skipped: set BPS_NAV_REFERENCE to the root of the bps-nav tree")
 
 
 if __name__ == "__main__":

@@ -110,6 +110,35 @@ def test_gae_restatement_matches_reference_python_fixture():
         assert np.allclose(advn, g[f"{tag}_adv_norm"][..., 0], rtol=1e-5, atol=2e-6)
 
 
+def _c2_inputs():
+    """The C2 inputs of tests/golden/make_fixtures.py::gae_c2_inputs (seeded numpy PCG64)."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("make_fixtures",
+                                                  os.path.join(GOLD, "make_fixtures.py"))
+    mf = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mf)
+    return mf.gae_c2_inputs()
+
+
+def test_gae_restatement_at_config2_size_matches_reference_python():
+    # T = 32, N = 16384: the reference's RolloutStorage.compute_returns wrote the fixture; the
+    # numpy restatement must reproduce the whole arrays bit for bit (CRC-32 of the bytes)
+    import zlib
+    g = np.load(os.path.join(GOLD, "gae_c2_16384.npz"))
+    r, v, m, nv = _c2_inputs()
+    T = 32
+    ret, adv, _ = pyoracle.gae_reference(r, v, m, nv, 0.99, 0.95)
+    assert zlib.crc32(np.ascontiguousarray(ret[:T]).tobytes()) == int(g["returns_crc"])
+    assert zlib.crc32(np.ascontiguousarray(adv).tobytes()) == int(g["adv_crc"])
+    cols = g["cols"]
+    assert np.array_equal(ret[:T][:, cols], g["returns_cols"])
+    assert np.array_equal(adv[:, cols], g["adv_cols"])
+    _, advn, _ = pyoracle.gae_reference(r, v, m, nv, 0.99, 0.95, normalize=True)
+    assert np.allclose(advn[:, cols], g["adv_norm_cols"], rtol=1e-5, atol=2e-6)
+    assert abs(float(adv.astype(np.float64).mean()) - float(g["adv_mean"])) < 1e-9
+    assert abs(float(adv.astype(np.float64).std(ddof=1)) - float(g["adv_std"])) < 1e-9
+
+
 def test_philox_known_answers():
     # Random123 known-answer vectors for philox4x32-10
     out = pyoracle._philox4x32(0, 0, 0, 0, 0, 0)

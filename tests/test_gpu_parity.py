@@ -146,6 +146,147 @@ def test_gae_matches_reference_python(tag):
     assert _close(adv.cpu().numpy(), g[f"{tag}_adv_norm"], 1e-5, 2e-6).all()
 
 
+def _c2():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("make_fixtures",
+                                                  os.path.join(GOLD, "make_fixtures.py"))
+    mf = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mf)
+    r, v, m, nv = mf.gae_c2_inputs()
+    return r, v, m, nv, np.load(os.path.join(GOLD, "gae_c2_16384.npz"))
+
+
+def _c2_device(r, v, m, nv):
+    rewards = torch.from_numpy(r)[..., None].cuda()
+    values = torch.from_numpy(v)[..., None].cuda()
+    masks = torch.from_numpy(m)[..., None].cuda()
+    next_value = torch.from_numpy(nv)[:, None].cuda()
+    return rewards, values, masks, next_value
+
+
+def test_gae_config2_full_size_matches_reference_python():
+    """Benchmark config 2 (T = 32, N = 16384): every element against the oracle restatement
+    (itself pinned to the reference's output bit for bit, CRC-32 over the whole arrays), the
+    reference's own values on every 16th environment, and the CRC of the whole returns array."""
+    import zlib
+    from bps_nav_b200 import rollout
+    from oracle import pyoracle
+    r, v, m, nv, g = _c2()
+    T, N = 32, 16384
+    rewards, values, masks, next_value = _c2_device(r, v, m, nv)
+    returns = torch.zeros_like(rewards)
+    adv = torch.empty(T, N, 1, device="cuda")
+    rollout.compute_returns(rewards, values, masks, returns, next_value, T, 0.99, 0.95,
+                            advantages=adv, normalize=False)
+    torch.cuda.synchronize()
+    ref_ret, ref_adv, _ = pyoracle.gae_reference(r, v, m, nv, 0.99, 0.95)
+    got = returns[:T, :, 0].cpu().numpy()
+    assert _close(got, ref_ret[:T], 1e-5, 1e-6).all()
+    assert zlib.crc32(np.ascontiguousarray(got).tobytes()) == int(g["returns_crc"])  # bit-exact
+    cols = g["cols"]
+    assert np.array_equal(got[:, cols], g["returns_cols"])
+    got_adv = adv[..., 0].cpu().numpy()
+    assert _close(got_adv, ref_adv, 1e-5, 1e-6).all()
+    assert zlib.crc32(np.ascontiguousarray(got_adv).tobytes()) == int(g["adv_crc"])
+    rollout.compute_returns(rewards, values, masks, returns, next_value, T, 0.99, 0.95,
+                            advantages=adv, normalize=True)
+    torch.cuda.synchronize()
+    _, ref_advn, _ = pyoracle.gae_reference(r, v, m, nv, 0.99, 0.95, normalize=True)
+    got_advn = adv[..., 0].cpu().numpy()
+    assert _close(got_advn, ref_advn, 1e-5, 2e-6).all()
+    assert _close(got_advn[:, cols], g["adv_norm_cols"], 1e-5, 2e-6).all()
+
+
+def test_advantage_normalisation_over_ranges_and_buffers():
+    """bpsn_adv_normalize against the torch formula of PPO.get_advantages
+    (bps_nav/rl/ppo/ppo.py:190-201): (a) per range of 4096 environments -- also against the
+    values the fixture script computed beside the reference's own returns --, (b) the two halves
+    of a double-buffered rollout normalised together, as torch.cat(advantages, 1) is, (c) ragged
+    ranges that do not cover the batch."""
+    from bps_nav_b200 import rollout
+    from oracle import pyoracle
+    r, v, m, nv, g = _c2()
+    T, N = 32, 16384
+    _, ref_adv, _ = pyoracle.gae_reference(r, v, m, nv, 0.99, 0.95)
+    base = torch.from_numpy(ref_adv)  # float32 [T, N], CPU
+
+    def torch_norm(a):
+        return (a - a.mean()) / (a.std() + 1e-5)
+
+    # (a)
+    adv = base.clone()[..., None].cuda()
+    ranges = [(s, s + 4096) for s in range(0, N, 4096)]
+    rollout.normalize_advantages(adv, ranges=ranges)
+    want = torch.cat([torch_norm(base[:, s:e]) for s, e in ranges], 1).numpy()
+    got = adv[..., 0].cpu().numpy()
+    assert _close(got, want, 1e-5, 2e-6).all()
+    assert _close(got[:, g["cols"]], g["adv_range_norm_cols"], 1e-5, 2e-6).all()
+    # (b)
+    a0 = base[:, :N // 2].contiguous().cuda()
+    a1 = base[:, N // 2:].contiguous().cuda()
+    rollout.normalize_advantages([a0, a1])
+    want = torch_norm(base).numpy()
+    assert _close(a0.cpu().numpy(), want[:, :N // 2], 1e-5, 2e-6).all()
+    assert _close(a1.cpu().numpy(), want[:, N // 2:], 1e-5, 2e-6).all()
+    assert _close(a0.cpu().numpy()[:, g["cols"][g["cols"] < N // 2]],
+                  g["adv_norm_cols"][:, g["cols"] < N // 2], 1e-5, 2e-6).all()
+    # (c) ragged ranges; columns outside every range stay as they were
+    adv = base.clone().cuda()
+    ragged = [(0, 1), (5, 1000), (1000, 1003), (9000, 16384)]
+    rollout.normalize_advantages(adv, ranges=ragged)
+    got = adv.cpu().numpy()
+    want = base.clone()
+    for s, e in ragged:
+        if e - s > 1:
+            want[:, s:e] = torch_norm(base[:, s:e])
+    for s, e in ragged:
+        if e - s > 1:
+            assert _close(got[:, s:e], want[:, s:e].numpy(), 1e-5, 2e-6).all(), (s, e)
+    assert np.array_equal(got[:, 1:5], base[:, 1:5].numpy())
+    assert np.array_equal(got[:, 1003:9000], base[:, 1003:9000].numpy())
+    # argument checking: overlapping ranges, empty range, CPU tensor
+    with pytest.raises(RuntimeError, match="overlap"):
+        rollout.normalize_advantages(adv, ranges=[(0, 10), (5, 20)])
+    with pytest.raises(RuntimeError, match="start < end"):
+        rollout.normalize_advantages(adv, ranges=[(7, 7)])
+    with pytest.raises(RuntimeError, match="CUDA"):
+        rollout.normalize_advantages(base.clone())
+
+
+def test_ema_mean_baseline_matches_ddppo_formula():
+    """bpsn_adv_mean + bpsn_adv_ema_shift against the recurrences of
+    DecentralizedDistributedMixin._get_advantages_distributed (bps_nav/rl/ddppo/algo/ddppo.py:
+    46-64) evaluated with torch on the CPU over three successive updates, single worker and
+    with a stand-in for the all-reduce over two workers."""
+    from bps_nav_b200 import rollout
+    rng = np.random.default_rng(5)
+    T, N = 32, 2048
+    updates = [torch.from_numpy((rng.standard_normal((T, N)) * (k + 1) + 0.3 * k).astype(np.float32))
+               for k in range(3)]
+    for workers in (1, 2):
+        ema = rollout.EmaMeanBaseline("cuda", beta=0.8)
+        biased = torch.tensor(0.0)
+        unbias = torch.tensor(0.0)
+        for a in updates:
+            other = torch.tensor(0.25)  # the second worker's mean
+
+            def all_reduce(mean_dev):
+                mean_dev.add_(other.item()).div_(2)
+
+            halves = [a[:, :N // 2].contiguous().cuda(), a[:, N // 2:].contiguous().cuda()]
+            ema(halves, all_reduce=all_reduce if workers == 2 else None)
+            mean = a.mean()
+            if workers == 2:
+                mean = (mean + other) / 2
+            biased = biased * 0.8 + (1 - 0.8) * mean
+            unbias = unbias * 0.8 + (1 - 0.8)
+            want = (a - biased / unbias).numpy()
+            got = np.concatenate([h.cpu().numpy() for h in halves], 1)
+            assert _close(got, want, 1e-5, 2e-6).all()
+        st = ema.state.cpu().numpy()
+        assert abs(st[0] - float(biased)) < 1e-6 and abs(st[1] - float(unbias)) < 1e-6
+
+
 def test_exact_sqrt_is_ieee_for_every_float():
     """The hand-written square root of the navmesh queries returns sqrtf's bits for every
     fp32 operand (all 2^32 bit patterns: zero, denormals, normals, inf, NaN, negatives)."""

@@ -61,6 +61,44 @@ def test_static_gae_matches_workspace_gae_twice():
                 assert np.allclose(a[:T], b[:T], rtol=1e-5, atol=2e-6), \
                     f"call {call}, normalize={normalize}: {name} differ"
             assert np.array_equal(got[0][:T], ref[0][:T])
+            if call == 0:
+                # and against the CPU oracle, not only against the sibling entry point
+                from oracle import pyoracle
+                o_ret, o_adv, _ = pyoracle.gae_reference(
+                    rewards[..., 0].cpu().numpy(), values[..., 0].cpu().numpy(),
+                    masks[..., 0].cpu().numpy(), nv[:, 0].cpu().numpy(), 0.99, 0.95,
+                    normalize=normalize)
+                assert np.allclose(got[0][:T, :, 0], o_ret[:T], rtol=1e-5, atol=1e-6)
+                assert np.allclose(got[1][..., 0], o_adv, rtol=1e-5, atol=2e-6)
+
+
+def test_static_gae_leaves_device_memory_alone():
+    """The point of the entry point: the call itself must not take or return device memory.
+    Free memory as the driver reports it is the same before and after."""
+    from bps_nav_b200 import _lib as L
+    lib = L.load()
+    T, N = 32, 16384
+    rewards, values, masks, nv = _inputs(T, N, 21, 0.002)
+    returns = torch.zeros_like(rewards)
+    adv = torch.empty(T, N, 1, device="cuda")
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def call():
+        L.check(lib.bpsn_gae_static(rewards.data_ptr(), values.data_ptr(), masks.data_ptr(),
+                                    nv.data_ptr(), returns.data_ptr(), adv.data_ptr(), T, N,
+                                    0.99, 0.95, 1, 1e-5, stream))
+
+    # The set-up call comes first (documented: the first call on a device resolves the array's
+    # address; the CUDA runtime also loads the two kernels' code at their first launch, which
+    # is the runtime's memory, not this library's).
+    call()
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0
 
 
 def test_static_gae_rejects_oversize_batch():
