@@ -12,13 +12,16 @@ LIB_PATH = os.path.join(HERE, "libbpsn.so")
 # every symbol include/bpsn.h declares
 SYMBOLS = [
     "bpsn_create", "bpsn_destroy", "bpsn_set_navmesh_file", "bpsn_set_navmesh_blob",
-    "bpsn_set_episodes", "bpsn_set_env_scenes", "bpsn_set_scene_geometry", "bpsn_finalize", "bpsn_reset", "bpsn_step_start", "bpsn_step_start_ex",
+    "bpsn_set_episodes", "bpsn_set_active_scenes", "bpsn_swap_stats", "bpsn_set_env_scenes", "bpsn_set_scene_geometry", "bpsn_finalize", "bpsn_reset", "bpsn_step_start", "bpsn_step_start_ex",
     "bpsn_step_end", "bpsn_render", "bpsn_get_ptr", "bpsn_device_error_flags", "bpsn_profile_enable", "bpsn_profile_read", "bpsn_scene_info", "bpsn_query_snap", "bpsn_query_try_step",
     "bpsn_query_geodesic", "bpsn_gae_workspace_bytes", "bpsn_gae", "bpsn_gae_static", "bpsn_adv_workspace_bytes",
-    "bpsn_adv_normalize", "bpsn_adv_mean", "bpsn_adv_ema_shift", "bpsn_selftest_sqrt", "bpsn_debug_set_search_count", "bpsn_dataset_open", "bpsn_dataset_num_scenes", "bpsn_dataset_scene",
+    "bpsn_adv_normalize", "bpsn_adv_mean", "bpsn_adv_ema_shift", "bpsn_selftest_sqrt", "bpsn_dataset_open", "bpsn_dataset_num_scenes", "bpsn_dataset_scene",
     "bpsn_dataset_close", "bpsn_last_error",
     "bpsn_version",
 ]
+
+# exports for the tests only (bps_nav_b200/csrc/bpsn_test_hooks.h)
+TEST_HOOKS = ["bpsn_debug_set_search_count"]
 
 OK = 0
 ERR_INVALID_ARG, ERR_BAD_NAVMESH, ERR_CUDA, ERR_STATE, ERR_BAD_ACTION, ERR_IO, ERR_NO_DEVICE = range(1, 8)
@@ -42,7 +45,8 @@ MEM_DEVICE, MEM_HOST = 0, 1
 class Config(C.Structure):
     _fields_ = [("gpu_id", C.c_int32), ("num_envs", C.c_uint32), ("num_groups", C.c_uint32),
                 ("num_scenes", C.c_uint32), ("seed", C.c_uint64), ("flags", C.c_uint32),
-                ("task", C.c_uint32), ("render_width", C.c_uint32), ("render_height", C.c_uint32)]
+                ("task", C.c_uint32), ("render_width", C.c_uint32), ("render_height", C.c_uint32),
+                ("num_active_scenes", C.c_uint32)]
 
 
 class AdvSegment(C.Structure):
@@ -78,6 +82,9 @@ def load():
     lib.bpsn_set_navmesh_blob.argtypes = [vp, u32, vp, sz]
     lib.bpsn_set_episodes.argtypes = [vp, u32, vp, u32]
     lib.bpsn_set_env_scenes.argtypes = [vp, vp, u32]
+    lib.bpsn_set_active_scenes.argtypes = [vp, vp, u32]
+    lib.bpsn_swap_stats.argtypes = [vp, C.POINTER(C.c_uint64), C.POINTER(C.c_float),
+                                    C.POINTER(C.c_float)]
     lib.bpsn_set_scene_geometry.argtypes = [vp, u32, vp, vp, u32]
     lib.bpsn_render.argtypes = [vp, u32, vp]
     lib.bpsn_finalize.argtypes = [vp]
@@ -116,7 +123,7 @@ def load():
     lib.bpsn_last_error.argtypes = [vp]
     lib.bpsn_last_error.restype = C.c_char_p
     lib.bpsn_version.restype = C.c_char_p
-    for name in SYMBOLS:
+    for name in SYMBOLS + TEST_HOOKS:
         fn = getattr(lib, name)
         if name not in ("bpsn_gae_workspace_bytes", "bpsn_adv_workspace_bytes", "bpsn_last_error", "bpsn_version",
                         "bpsn_dataset_num_scenes", "bpsn_dataset_close"):

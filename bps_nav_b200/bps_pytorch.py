@@ -30,13 +30,19 @@ def _wrap(capsule, dev_id, shape, dtype):
 
 
 def make_color_tensor(ptr_capsule, dev_id, batch_size, resolution):
-    """uint8 CUDA tensor ``[batch, H, W, 4]`` (``pytorch.cpp:13-27``); resolution = [W, H]."""
-    return _wrap(ptr_capsule, dev_id, (batch_size, resolution[1], resolution[0], 4), np.uint8)
+    """uint8 CUDA tensor ``[batch, resolution[0], resolution[1], 4]`` -- the dimensions in the
+    order ``pytorch.cpp:13-27`` gives them.  ``resolution`` is what the generator was built
+    with, ``[width, height]`` (``simulator/simulator.cpp:381-383``), while the memory holds
+    ``height`` rows of ``width`` pixels per image: for square images the two readings agree, for
+    any other shape the reference's tensor has its two image dimensions labelled the wrong way
+    round and ``t.view(batch, resolution[1], resolution[0], 4)`` is the image."""
+    return _wrap(ptr_capsule, dev_id, (batch_size, resolution[0], resolution[1], 4), np.uint8)
 
 
 def make_depth_tensor(ptr_capsule, dev_id, batch_size, resolution):
-    """float32 CUDA tensor ``[batch, H, W]`` (``pytorch.cpp:31-45``)."""
-    return _wrap(ptr_capsule, dev_id, (batch_size, resolution[1], resolution[0]), np.float32)
+    """float32 CUDA tensor ``[batch, resolution[0], resolution[1]]`` (``pytorch.cpp:31-45``); see
+    ``make_color_tensor`` for what that means for images that are not square."""
+    return _wrap(ptr_capsule, dev_id, (batch_size, resolution[0], resolution[1]), np.float32)
 
 
 def make_fcout_tensor(ptr_capsule, dev_id, batch_size, num_features):

@@ -21,9 +21,10 @@ Added (not in the reference): device-resident views of every result and state ar
 (``tensor(group, name)``), and ``step_start`` accepting a CUDA int64 tensor of actions, so a
 trainer can keep the whole rollout on the GPU.
 
-Not reproduced: rendering (``render`` / ``wait_for_frame`` only order the stream; ``rgba`` /
-``depth`` expose zero-filled device buffers) and active-scene swapping (``swap_stats`` reports no
-swaps).
+Not reproduced: the colour renderer (``rgba`` exposes a zero-filled device buffer; ``depth`` is
+the analytic sensor of box-world scenes).  Scenes rotate through the active slots as in the
+reference, with one deterministic rule in place of its background loader's timing (see
+``include/bpsn.h``, ``num_active_scenes``).
 """
 import ctypes as C
 
@@ -99,19 +100,21 @@ class _RolloutGenerator:
     def from_scenes(cls, scenes, num_environments, num_active_scenes=None, gpu_id=0,
                     render_resolution=(64, 64), color=False, depth=False, double_buffered=False,
                     seed=0, host_mirrors=True, generic_kernel=False, exact_heap=False,
-                    small_smem=False, global_memory=False):
-        """Builds a generator from in-memory ``dataset.Scene`` objects (no JSON involved)."""
+                    small_smem=False, global_memory=False, env_scene=None):
+        """Builds a generator from in-memory ``dataset.Scene`` objects (no JSON involved).
+        ``env_scene``: optional explicit scene (index into ``scenes``) of every environment, for
+        layouts other than equal consecutive blocks; only with every scene active."""
         self = cls.__new__(cls)
         if num_active_scenes is None:
             num_active_scenes = len(scenes)
         self._setup(list(scenes), num_environments, num_active_scenes, gpu_id, render_resolution,
                     color, depth, double_buffered, seed, host_mirrors, generic_kernel, exact_heap,
-                    small_smem, global_memory)
+                    small_smem, global_memory, env_scene)
         return self
 
     def _setup(self, scenes, num_environments, num_active_scenes, gpu_id, render_resolution, color,
                depth, double_buffered, seed, host_mirrors, generic_kernel=False, exact_heap=False,
-               small_smem=False, global_memory=False):
+               small_smem=False, global_memory=False, env_scene=None):
         if self._task not in _TASKS:
             raise NotImplementedError(f"{type(self).__name__}: unknown task")
         self._task_id, self._info_dtype = _TASKS[self._task]
@@ -121,10 +124,16 @@ class _RolloutGenerator:
         num_groups = 2 if double_buffered else 1
         if num_active_scenes > len(scenes):
             raise RuntimeError("num_active_scenes exceeds the number of scenes in the dataset")
+        # Every scene of the dataset is uploaded (navigation meshes are small); the ones drawn
+        # here are in use first and the others rotate in as episodes end (SceneSwapper,
+        # simulator/simulator.cpp:1063-1154).  (The reference's assert that the dataset has more
+        # scenes than are active, :1516, is compiled out of its RelWithDebInfo build; with equal
+        # counts nothing ever rotates, there as here.)
         active, inactive = _dataset.select_active_scenes(len(scenes), num_active_scenes, seed)
         self._active_scenes = active
         self._inactive_scenes = inactive
-        self._scenes = [scenes[i] for i in active]
+        self._scenes = list(scenes)
+        self.num_active_scenes = int(num_active_scenes)
         self.num_environments = int(num_environments)
         self.num_groups = num_groups
         self.gpu_id = int(gpu_id)
@@ -141,9 +150,15 @@ class _RolloutGenerator:
                        (L.FLAG_GLOBAL_MEMORY if global_memory else 0),
                        task=self._task_id,
                        render_width=self._res[0] if self._depth else 0,
-                       render_height=self._res[1] if self._depth else 0)
+                       render_height=self._res[1] if self._depth else 0,
+                       num_active_scenes=self.num_active_scenes)
         L.check(self._lib.bpsn_create(C.byref(cfg), C.byref(self._h)))
         try:
+            act = np.ascontiguousarray(active, np.uint32)
+            L.check(self._lib.bpsn_set_active_scenes(self._h, act.ctypes.data, len(act)), self._h)
+            if env_scene is not None:
+                es = np.ascontiguousarray(env_scene, np.uint32)
+                L.check(self._lib.bpsn_set_env_scenes(self._h, es.ctypes.data, len(es)), self._h)
             for i, sc in enumerate(self._scenes):
                 L.check(self._lib.bpsn_set_navmesh_file(self._h, i, sc.navmesh_path.encode()),
                         self._h)
@@ -167,7 +182,7 @@ class _RolloutGenerator:
             with torch.cuda.device(self.gpu_id):
                 self._group_streams = [torch.cuda.Stream() for _ in range(num_groups)]
         self.envs_per_group = self.num_environments // num_groups
-        self.envs_per_scene = self.num_environments // len(self._scenes)
+        self.envs_per_scene = self.num_environments // self.num_active_scenes
         self._num_steps_taken = 0
         self._host_views = {}
         self._dev_tensors = {}
@@ -361,9 +376,13 @@ class _RolloutGenerator:
     # ------------------------------------------------------------------ misc
     @property
     def swap_stats(self):
-        # (% of steps that swapped a scene, scenes in use, mean envs per scene) summed over
-        # groups as RolloutGenerator::swapStats does (simulator.cpp:1412-1424); no swapping here.
-        return (0.0, float(len(self._scenes)), float(self.envs_per_scene * self.num_groups))
+        # (scene swaps per 100 environment steps, scenes in use, mean envs per scene), the last
+        # two summed over the groups, as RolloutGenerator::swapStats (simulator.cpp:1412-1424)
+        n, scenes, per = C.c_uint64(), C.c_float(), C.c_float()
+        L.check(self._lib.bpsn_swap_stats(self._h, C.byref(n), C.byref(scenes), C.byref(per)),
+                self._h)
+        steps = max(self._num_steps_taken, 1)
+        return (100.0 * n.value / steps, float(scenes.value), float(per.value))
 
     def device_errors(self, group_idx):
         """Sticky device-side error flags of a group (0 in normal operation); synchronises."""

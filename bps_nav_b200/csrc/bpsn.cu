@@ -4,6 +4,7 @@
 // execution path: every compute entry point launches CUDA kernels or fails.
 
 #include "../../include/bpsn.h"
+#include "bpsn_test_hooks.h"
 
 #include <cuda_runtime.h>
 #include <math.h>
@@ -49,12 +50,12 @@ struct Group {
   uint8_t* hMask = nullptr;
   float* hInfo = nullptr;
   float* hPolar = nullptr;
+  volatile uint32_t* hErr = nullptr;  // host view of the device error word (with mirrors)
   uint8_t* hActions = nullptr;  // pinned, device-mapped staging of host-supplied actions
   const uint8_t* dActions8 = nullptr;  // the same buffer as the device addresses it
   AStarScratch* scratch = nullptr;
   // launch plan of the geodesic phase
-  uint32_t numScenesUsed = 0;   // grid.y
-  uint32_t maxSceneEnvs = 0;    // largest per-scene list
+  uint32_t maxListLen = 0;      // longest work list (environments of the largest slot)
   bool warpGeo = false;         // some scene of the group runs on the shared-memory warp kernel
   bool anyWarpScene = false;
   bool anyThreadScene = false;  // some scene needs the generic kernel
@@ -65,7 +66,7 @@ struct Group {
   uint8_t* globalSlabs = nullptr;  // warp slabs of the scenes that are worked on in global memory
   size_t globalSlabStride = 0;     // bytes between consecutive slabs there (the largest scene's)
   size_t numGlobalSlabs = 0;       // one per warp of the grid, or one per environment
-  uint2* dCtaMap = nullptr;     // [numCtas] (scene, rank within the scene)
+  uint4* dCtaMap = nullptr;     // [numCtas] (slot, number among the slot's CTAs, their count)
   AStarScratch* fallbackScratch = nullptr;
   float* depth = nullptr;  // [B][H][W] when a render size was configured
   cudaEvent_t done = nullptr;
@@ -90,6 +91,12 @@ struct bpsn_sim {
   bpsn_config cfg{};
   std::vector<DeviceScene> scenes;
   std::vector<uint32_t> envScene;
+  bool envSceneExplicit = false;
+  // scene rotation (num_active_scenes < num_scenes)
+  uint32_t numActive = 0;
+  bool rotation = false;
+  std::vector<uint32_t> activeScenes;       // [numActive] scene of every slot at the start
+  std::vector<std::vector<uint32_t>> pools;  // per group: scenes waiting for a slot
   std::vector<Group> groups;
   bool finalized = false;
   std::string lastError;
@@ -214,8 +221,33 @@ int32_t uploadScene(bpsn_sim* sim, DeviceScene& ds) {
   return BPSN_OK;
 }
 
-int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
-                   const uint32_t* envScene) {
+int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase, uint32_t groupIdx) {
+  const uint32_t ns = sim->cfg.num_scenes;
+  const uint32_t* envScene = sim->envScene.data() + envBase;
+  const bool rotation = sim->rotation;
+  // ---- slots (see GroupDev::slot): one per scene when the scenes are fixed, else
+  // `active scenes / groups` slots of equal size
+  const uint32_t numSlots = rotation ? sim->numActive / sim->cfg.num_groups : ns;
+  const uint32_t slotBase = groupIdx * numSlots;
+  std::vector<uint32_t> envSlot(B), slotSize(numSlots, 0u), slotScene(numSlots, 0u);
+  if (rotation) {
+    const uint32_t perSlot = B / numSlots;
+    for (uint32_t e = 0; e < B; ++e)
+      envSlot[e] = e / perSlot;
+    for (uint32_t s2 = 0; s2 < numSlots; ++s2)
+      slotScene[s2] = sim->activeScenes[slotBase + s2];
+  } else {
+    for (uint32_t e = 0; e < B; ++e)
+      envSlot[e] = envScene[e];
+    for (uint32_t s2 = 0; s2 < numSlots; ++s2)
+      slotScene[s2] = s2;
+  }
+  for (uint32_t e = 0; e < B; ++e)
+    slotSize[envSlot[e]]++;
+  const std::vector<uint32_t>& pool = sim->pools[groupIdx];
+  const uint32_t poolSize = static_cast<uint32_t>(pool.size());
+  const uint32_t numLists = 2u * numSlots;
+
   size_t off = 0;
   auto place = [&](size_t bytes) {
     size_t o = off;
@@ -233,14 +265,18 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
                oScene = place(B * u);
   const size_t oReward = place(B * f), oMask = place(B), oInfo = place(3 * B * f),
                oPolar = place(2 * B * f);
-  const uint32_t ns = sim->cfg.num_scenes;
   const size_t oEpReward = place(B * f), oStats = place(5 * B * f);
   const bool expl = sim->cfg.task == BPSN_TASK_EXPLORATION;
   const size_t oExplInit = place(expl ? 7 * B * f : 16), oNumCells = place(expl ? B * u : 16),
                oVisited = place(expl ? static_cast<size_t>(B) * kVisitedSlots * u : 16);
-  const size_t oGeoList = place(B * u), oCounts = place((2 * ns + 4) * u),
-               oCounts2 = place((2 * ns + 4) * u), oErr = place(4 * u),
-               oListBase = place((ns + 4) * u);
+  const size_t oGeoList = place(2 * static_cast<size_t>(B) * u),
+               oCounts = place((2 * numLists + 4) * u), oCounts2 = place((2 * numLists + 4) * u),
+               oErr = place(4 * u), oListBase = place((numLists + 4) * u);
+  const size_t oSlot = place(B * u), oEnvEpoch = place(B * u);
+  const size_t oSlotScene = place(numSlots * u), oSlotPrev = place(numSlots * u),
+               oSlotEpoch = place(numSlots * u), oSlotRemaining = place(numSlots * u),
+               oSlotSize = place(numSlots * u), oPool = place((poolSize + 4) * u),
+               oSwapCount = place(4 * u);
   g.stateBytes = off;
   BPSN_CUDA(sim, cudaMalloc(&g.stateBlob, off));
   BPSN_CUDA(sim, cudaMemset(g.stateBlob, 0, off));
@@ -251,7 +287,12 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
   d.task = sim->cfg.task;
   d.infoWidth = sim->cfg.task == BPSN_TASK_POINTNAV ? 3u : 1u;
   d.exactHeap = (sim->cfg.flags & BPSN_FLAG_EXACT_HEAP) ? 1u : 0u;
-  d.numScenes = sim->cfg.num_scenes;
+  d.numScenes = ns;
+  d.numLists = numLists;
+  d.rotation = rotation ? 1u : 0u;
+  d.numSlots = numSlots;
+  d.poolSize = poolSize;
+  d.slotBase = slotBase;
   d.explInit = reinterpret_cast<float*>(b + oExplInit);
   d.numCells = reinterpret_cast<uint32_t*>(b + oNumCells);
   d.visited = reinterpret_cast<uint32_t*>(b + oVisited);
@@ -283,42 +324,69 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
   d.countsNext = reinterpret_cast<uint32_t*>(b + oCounts2);
   d.errFlags = reinterpret_cast<uint32_t*>(b + oErr);
   d.listBase = reinterpret_cast<const uint32_t*>(b + oListBase);
+  d.slot = reinterpret_cast<uint32_t*>(b + oSlot);
+  d.envEpoch = reinterpret_cast<uint32_t*>(b + oEnvEpoch);
+  d.slotScene = reinterpret_cast<uint32_t*>(b + oSlotScene);
+  d.slotPrev = reinterpret_cast<uint32_t*>(b + oSlotPrev);
+  d.slotEpoch = reinterpret_cast<uint32_t*>(b + oSlotEpoch);
+  d.slotRemaining = reinterpret_cast<uint32_t*>(b + oSlotRemaining);
+  d.slotSize = reinterpret_cast<uint32_t*>(b + oSlotSize);
+  d.pool = reinterpret_cast<uint32_t*>(b + oPool);
+  d.swapCount = reinterpret_cast<uint32_t*>(b + oSwapCount);
   {
-    // per-scene segments of the geodesic work list, sized by the number of
-    // environments of this group that live in each scene
-    std::vector<uint32_t> perScene(ns, 0), base(ns + 4, 0);
-    for (uint32_t e = 0; e < B; ++e)
-      perScene[envScene[e]]++;
+    // two work lists per slot, each as long as the slot has environments
+    std::vector<uint32_t> base(numLists + 4, 0u), initScene(B);
     uint32_t acc = 0;
-    g.maxSceneEnvs = 0;
-    for (uint32_t s2 = 0; s2 < ns; ++s2) {
-      base[s2] = acc;
-      acc += perScene[s2];
-      if (perScene[s2] > g.maxSceneEnvs)
-        g.maxSceneEnvs = perScene[s2];
+    g.maxListLen = 0;
+    for (uint32_t s2 = 0; s2 < numSlots; ++s2) {
+      base[2 * s2] = acc;
+      base[2 * s2 + 1] = acc + slotSize[s2];
+      acc += 2 * slotSize[s2];
+      if (slotSize[s2] > g.maxListLen)
+        g.maxListLen = slotSize[s2];
     }
-    BPSN_CUDA(sim, cudaMemcpy(b + oListBase, base.data(), sizeof(uint32_t) * (ns + 4),
-                              cudaMemcpyHostToDevice));
-    BPSN_CUDA(sim, cudaMemcpy(d.scene, envScene, sizeof(uint32_t) * B, cudaMemcpyHostToDevice));
-    g.numScenesUsed = ns;
-    // Shared-memory plan, scene by scene: a CTA serves one scene with 227 KB of shared
-    // memory = the scene's staged image + as many warp slabs (24 B per polygon + 512 B) as
-    // fit, at most 16.  A scene that leaves no room for a slab goes to the generic kernel.
-    // CTAs are dealt to the scenes in proportion to environments / warps-per-CTA, so that
-    // every scene's list drains in about the same time.
+    for (uint32_t e = 0; e < B; ++e)
+      initScene[e] = slotScene[envSlot[e]];
+    auto up = [&](size_t o, const void* src, size_t bytes) {
+      return bytes ? cudaMemcpy(b + o, src, bytes, cudaMemcpyHostToDevice) : cudaSuccess;
+    };
+    BPSN_CUDA(sim, up(oListBase, base.data(), u * (numLists + 4)));
+    BPSN_CUDA(sim, up(oScene, initScene.data(), u * B));
+    BPSN_CUDA(sim, up(oSlot, envSlot.data(), u * B));
+    // every environment is in its slot's scene, no move under way (the first is started by
+    // bpsn_finalize); slotRemaining and slotEpoch start at 0 (memset above)
+    BPSN_CUDA(sim, up(oSlotScene, slotScene.data(), u * numSlots));
+    BPSN_CUDA(sim, up(oSlotPrev, slotScene.data(), u * numSlots));
+    BPSN_CUDA(sim, up(oSlotSize, slotSize.data(), u * numSlots));
+    BPSN_CUDA(sim, up(oPool, pool.data(), u * poolSize));
+  }
+  {
+    // Scenes this group can ever work on: those of its slots and, when scenes rotate, the
+    // ones waiting in its pool.
+    std::vector<uint8_t> used(ns, 0);
+    for (uint32_t s2 = 0; s2 < numSlots; ++s2)
+      if (slotSize[s2])
+        used[slotScene[s2]] = 1;
+    for (uint32_t sc : pool)
+      used[sc] = 1;
+    // Shared-memory plan, scene by scene: a CTA works on one scene at a time with 227 KB of
+    // shared memory = the scene's staged image + as many warp slabs (24 B per polygon +
+    // 512 B) as fit, at most 16.  A scene that leaves no room for a slab goes to global memory.
+    // CTAs are dealt to the slots in proportion to environments / warps-per-CTA of the slot's
+    // first scene, so that every slot's list drains in about the same time.
     const size_t kSlabPerEnvAbove = size_t(512) << 20;  // bytes of per-warp slabs from which on ...
     const size_t kSlabPerEnvBudget = size_t(32) << 30;  // ... and bytes of per-env slabs up to which
     const size_t kSmemMax = ((sim->cfg.flags & BPSN_FLAG_SMEM_96K) ? 96 : 227) * 1024 - 64;  // per CTA, minus the kernel's static shared memory
+    const uint32_t kBlockWarps = 16;
     std::vector<WarpPlan> plan(ns, WarpPlan{16u, 0u, 0u, 0u});
     size_t maxGlobalSlab = 0;
+    uint32_t maxGlobalPcap = 16;
     const double kGlobalWarpSpeed = 0.6;  // queries per unit time of a warp in global memory
                                           // relative to one in shared memory (measured)
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, sim->cfg.gpu_id);
-    const bool throughputBound = B / 2 > 2u * static_cast<uint32_t>(sms) * 16u;
+    const bool throughputBound = B / 2 > 2u * static_cast<uint32_t>(sms) * kBlockWarps;
     const bool forceGeneric = (sim->cfg.flags & BPSN_FLAG_GENERIC_KERNEL) != 0;
-    double workSum = 0.0;
-    std::vector<double> work(ns, 0.0);
     g.anyThreadScene = false;
     g.anyWarpScene = false;
     // Pass 1: how many slabs fit next to each scene's image in shared memory.
@@ -326,7 +394,7 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
     std::vector<size_t> slabBytes(ns, 0), sceneBytes(ns, 0);
     bool anyCramped = false;  // some scene has room for fewer than 8 slabs
     for (uint32_t s2 = 0; s2 < ns; ++s2) {
-      if (!perScene[s2])
+      if (!used[s2])
         continue;
       const HostScene& h = sim->scenes[s2].host;
       const NavScene hv = h.view();
@@ -336,8 +404,8 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
       uint32_t w = 0;
       if (sb + slab <= kSmemMax)
         w = static_cast<uint32_t>((kSmemMax - sb) / slab);
-      if (w > 16)
-        w = 16;
+      if (w > kBlockWarps)
+        w = kBlockWarps;
       smemWarps[s2] = w;
       slabBytes[s2] = slab;
       sceneBytes[s2] = sb;
@@ -359,8 +427,10 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
     //    memory shortens: everything that fits stays there.
     const bool allGlobal = (throughputBound && anyCramped) ||
                            (sim->cfg.flags & BPSN_FLAG_GLOBAL_MEMORY) != 0;
+    std::vector<double> speedOf(ns, 1.0);
+    bool anyShared = false, anyGlobal = false;
     for (uint32_t s2 = 0; s2 < ns; ++s2) {
-      if (!perScene[s2])
+      if (!used[s2])
         continue;
       const HostScene& h = sim->scenes[s2].host;
       uint32_t w = smemWarps[s2];
@@ -369,67 +439,78 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
       if (forceGeneric || !indexable) {
         w = 0;
       } else if (allGlobal || w == 0) {
-        w = 16;
+        w = kBlockWarps;
         plan[s2].slabOffset = kSlabInGlobal;
         if (slabBytes[s2] > maxGlobalSlab)
           maxGlobalSlab = slabBytes[s2];
+        if (plan[s2].pcap > maxGlobalPcap)
+          maxGlobalPcap = plan[s2].pcap;
       }
       plan[s2].warps = w;
       if (w) {
         g.anyWarpScene = true;
+        if (plan[s2].slabOffset == kSlabInGlobal)
+          anyGlobal = true;
+        else
+          anyShared = true;
         // a warp working in global memory beside shared-memory CTAs (small L1) gets
         // through its queries more slowly
-        const double speed =
-            (plan[s2].slabOffset == kSlabInGlobal && !allGlobal) ? kGlobalWarpSpeed : 1.0;
-        work[s2] = static_cast<double>(perScene[s2]) / (w * speed);
-        workSum += work[s2];
+        speedOf[s2] = (plan[s2].slabOffset == kSlabInGlobal && !allGlobal) ? kGlobalWarpSpeed : 1.0;
       } else {
         g.anyThreadScene = true;
       }
     }
     g.warpGeo = g.anyWarpScene;
+    d.globalPcap = maxGlobalPcap;
     if (g.anyWarpScene) {
-      bool anyShared = false, anyGlobal = false;
-      for (uint32_t s2 = 0; s2 < ns; ++s2) {
-        if (!plan[s2].warps)
-          continue;
-        if (plan[s2].slabOffset == kSlabInGlobal)
-          anyGlobal = true;
-        else
-          anyShared = true;
-      }
       g.warpMode = anyShared ? (anyGlobal ? 2 : 0) : 1;
-      // the global-only instance fits two CTAs on an SM (64 registers, no shared memory)
       // The steps of a double-buffered generator's two groups are in flight together
       // (simulator/simulator.cpp:1377-1399; bps_nav/rl/ddppo/algo/ddppo_trainer.py:205-270).
       // A small batch's step lasts as long as its slowest query whatever the number of CTAs,
       // so each group gets half of the SMs and the two kernels run side by side instead of
       // one waiting for the other's last warp.
       const int groupsSharing = throughputBound ? 1 : static_cast<int>(sim->cfg.num_groups);
+      // the global-only instance fits two CTAs on an SM (64 registers, no shared memory)
       const int ctaBudget = sms * (g.warpMode == 1 ? 2 : 1) / groupsSharing;
-      std::vector<uint2> ctaMap;
-      for (uint32_t s2 = 0; s2 < ns; ++s2) {
-        if (!plan[s2].warps)
+      double workSum = 0.0;
+      std::vector<double> work(numSlots, 0.0);
+      for (uint32_t s2 = 0; s2 < numSlots; ++s2) {
+        const WarpPlan& pl = plan[slotScene[s2]];
+        if (!slotSize[s2] || !pl.warps)
           continue;
-        uint32_t c = static_cast<uint32_t>(ctaBudget * work[s2] / workSum + 0.5);
-        const uint32_t need = (perScene[s2] + plan[s2].warps - 1) / plan[s2].warps;
-        if (c > need)
-          c = need;  // never more warps than environments
+        work[s2] = static_cast<double>(slotSize[s2]) / (pl.warps * speedOf[slotScene[s2]]);
+        workSum += work[s2];
+      }
+      std::vector<uint4> ctaMap;
+      for (uint32_t s2 = 0; s2 < numSlots; ++s2) {
+        if (!slotSize[s2])
+          continue;
+        const WarpPlan& pl = plan[slotScene[s2]];
+        uint32_t c = 1;
+        if (pl.warps && workSum > 0.0) {
+          c = static_cast<uint32_t>(ctaBudget * work[s2] / workSum + 0.5);
+          const uint32_t need = (slotSize[s2] + pl.warps - 1) / pl.warps;
+          if (c > need)
+            c = need;  // never more warps than environments
+        } else if (!rotation) {
+          continue;  // a fixed scene of the generic kernel: no CTA of this one
+        }
         if (c == 0)
           c = 1;
-        plan[s2].ctas = c;
         for (uint32_t r = 0; r < c; ++r)
-          ctaMap.push_back(make_uint2(s2, r));
+          ctaMap.push_back(make_uint4(s2, r, c, 0u));
       }
+      if (ctaMap.empty())
+        ctaMap.push_back(make_uint4(0u, 0u, 1u, 0u));
       g.numCtas = static_cast<uint32_t>(ctaMap.size());
-      BPSN_CUDA(sim, cudaMalloc(&g.dCtaMap, sizeof(uint2) * ctaMap.size()));
-      BPSN_CUDA(sim, cudaMemcpy(g.dCtaMap, ctaMap.data(), sizeof(uint2) * ctaMap.size(),
+      BPSN_CUDA(sim, cudaMalloc(&g.dCtaMap, sizeof(uint4) * ctaMap.size()));
+      BPSN_CUDA(sim, cudaMemcpy(g.dCtaMap, ctaMap.data(), sizeof(uint4) * ctaMap.size(),
                                 cudaMemcpyHostToDevice));
       // dynamic shared memory of a CTA: what the largest of the group's shared-memory scenes
       // needs, not the whole SM
       g.geoSmem = 0;
       for (uint32_t s2 = 0; s2 < ns; ++s2)
-        if (plan[s2].warps && plan[s2].slabOffset != kSlabInGlobal) {
+        if (used[s2] && plan[s2].warps && plan[s2].slabOffset != kSlabInGlobal) {
           const size_t need = sceneBytes[s2] + plan[s2].warps * slabBytes[s2];
           if (need > g.geoSmem)
             g.geoSmem = need;
@@ -440,18 +521,18 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
       // belongs to the function, so every handle of the process shares it.
       const int kSmemAttr = 227 * 1024 - 64;
       if (g.warpMode == 0)
-        BPSN_CUDA(sim, cudaFuncSetAttribute(k_step_warp<0>,
+        BPSN_CUDA(sim, cudaFuncSetAttribute(rotation ? k_step_warp<0, true> : k_step_warp<0, false>,
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAttr));
       else if (g.warpMode == 2)
-        BPSN_CUDA(sim, cudaFuncSetAttribute(k_step_warp<2>,
+        BPSN_CUDA(sim, cudaFuncSetAttribute(rotation ? k_step_warp<2, true> : k_step_warp<2, false>,
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAttr));
-      BPSN_CUDA(sim, cudaMalloc(&g.fallbackScratch,
-                                sizeof(AStarScratch) * static_cast<size_t>(g.numCtas) * 16));
+      BPSN_CUDA(sim, cudaMalloc(&g.fallbackScratch, sizeof(AStarScratch) *
+                                                        static_cast<size_t>(g.numCtas) * kBlockWarps));
       g.globalSlabStride = maxGlobalSlab ? maxGlobalSlab + kGlobalSlabExtra : 0;
       if (maxGlobalSlab) {
         // One slab per warp of the grid; one per environment instead when the warps' slabs
         // together would not stay in L2 anyway and the environments' fit a memory budget.
-        const size_t warpSlabs = static_cast<size_t>(g.numCtas) * 16;
+        const size_t warpSlabs = static_cast<size_t>(g.numCtas) * kBlockWarps;
         const bool perEnv = warpSlabs * g.globalSlabStride > kSlabPerEnvAbove &&
                             static_cast<size_t>(B) * g.globalSlabStride <= kSlabPerEnvBudget;
         g.numGlobalSlabs = perEnv ? static_cast<size_t>(B) : warpSlabs;
@@ -461,6 +542,34 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
         BPSN_CUDA(sim, cudaMalloc(&g.globalSlabs, bytes));
         BPSN_CUDA(sim, cudaMemset(g.globalSlabs, 0, bytes));
       }
+    }
+    // Every index the step kernels form from this plan, checked against what was allocated
+    // above (a plan that fails here would make a kernel read or write past an allocation;
+    // nothing is launched with it):
+    //   shared memory  slabOffset + warps * slab  <=  the CTA's dynamic shared memory
+    //   global slabs   (CTA * 16 + warp) or env   <   numGlobalSlabs, slab + counter <= stride
+    //   fallback       CTA * 16 + warp            <   numCtas * 16 scratch blocks
+    //   work lists     two per slot, each as long as the slot: 2 * B entries in all
+    for (uint32_t s2 = 0; s2 < ns; ++s2) {
+      const WarpPlan& pl = plan[s2];
+      if (!used[s2] || !pl.warps)
+        continue;
+      std::string bad;
+      if (pl.warps > kBlockWarps)
+        bad = "more query warps than the block has";
+      else if (pl.slabOffset == kSlabInGlobal) {
+        if (warpGeoSlabBytes(static_cast<int>(maxGlobalPcap)) + kGlobalSlabExtra >
+            g.globalSlabStride)
+          bad = "global slab larger than the slab stride";
+        else if (g.numGlobalSlabs < (d.slabPerEnv ? static_cast<size_t>(B)
+                                                  : static_cast<size_t>(g.numCtas) * kBlockWarps))
+          bad = "fewer global slabs than warps (or environments)";
+      } else if (pl.slabOffset + static_cast<size_t>(pl.warps) * slabBytes[s2] > g.geoSmem) {
+        bad = "slabs run past the CTA's shared memory";
+      }
+      if (!bad.empty())
+        return fail(sim, BPSN_ERR_INVALID_ARG,
+                    "step plan of scene " + std::to_string(s2) + ": " + bad);
     }
     BPSN_CUDA(sim, cudaMalloc(&g.dPlan, sizeof(WarpPlan) * ns));
     BPSN_CUDA(sim, cudaMemcpy(g.dPlan, plan.data(), sizeof(WarpPlan) * ns, cudaMemcpyHostToDevice));
@@ -510,8 +619,10 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
     // block with the same relative layout lets a step publish them in one copy
     g.outBytes = (oPolar + 2 * B * f) - oReward;
     // mapped: the kernels write the mirrors themselves (GroupDev::hReward ...)
-    BPSN_CUDA(sim, cudaHostAlloc(&g.hOut, g.outBytes, cudaHostAllocMapped));
-    memset(g.hOut, 0, g.outBytes);
+    // (+ one word behind the arrays: the host-visible copy of the device error flags)
+    BPSN_CUDA(sim, cudaHostAlloc(&g.hOut, g.outBytes + 16, cudaHostAllocMapped));
+    memset(g.hOut, 0, g.outBytes + 16);
+    g.hErr = reinterpret_cast<volatile uint32_t*>(g.hOut + g.outBytes);
     g.hReward = reinterpret_cast<float*>(g.hOut);
     g.hMask = g.hOut + (oMask - oReward);
     g.hInfo = reinterpret_cast<float*>(g.hOut + (oInfo - oReward));
@@ -523,6 +634,7 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase,
     d.hMask = db + (oMask - oReward);
     d.hInfo = reinterpret_cast<float*>(db + (oInfo - oReward));
     d.hPolar = reinterpret_cast<float*>(db + (oPolar - oReward));
+    d.hErr = reinterpret_cast<uint32_t*>(db + g.outBytes);
   }
   BPSN_CUDA(sim, cudaEventCreateWithFlags(&g.done, cudaEventDisableTiming));
   return BPSN_OK;
@@ -589,16 +701,22 @@ int32_t bpsn_create(const bpsn_config* cfg, bpsn_sim** out) {
                 "bpsn_create: render_width and render_height must both be 0 or both in 1..4096");
   if (cfg->num_envs > kListEnvMask)
     return fail(nullptr, BPSN_ERR_INVALID_ARG, "bpsn_create: at most 2^30 - 1 environments");
-  if (cfg->num_envs % cfg->num_scenes != 0)
+  const uint32_t numActive = cfg->num_active_scenes ? cfg->num_active_scenes : cfg->num_scenes;
+  if (numActive > cfg->num_scenes)
+    return fail(nullptr, BPSN_ERR_INVALID_ARG,
+                "bpsn_create: more active scenes than scenes");
+  if (cfg->num_envs % numActive != 0)
     return fail(nullptr, BPSN_ERR_INVALID_ARG,
                 "Num environments is not a multiple of the number of active scenes");
-  // (the reference also wants num_scenes to be a multiple of num_groups, simulator.cpp:1536-1538,
-  // because each group renders its own scenes; here the groups share the scene tables, so a
-  // single scene may serve both groups: the Python constructor keeps the reference's rule)
+  // (the reference also wants the active scenes to be a multiple of num_groups,
+  // simulator.cpp:1536-1538, because each group renders its own scenes; here the groups share
+  // the scene tables, so a single fixed scene may serve both groups: the Python constructor
+  // keeps the reference's rule)
+  const bool rotating = numActive < cfg->num_scenes;
   if (cfg->num_envs % cfg->num_groups != 0 ||
-      (cfg->num_scenes % cfg->num_groups != 0 && cfg->num_scenes != 1))
+      (numActive % cfg->num_groups != 0 && (rotating || numActive != 1)))
     return fail(nullptr, BPSN_ERR_INVALID_ARG,
-                "num_envs and num_scenes must be multiples of num_groups");
+                "num_envs and the number of active scenes must be multiples of num_groups");
   int ndev = 0;
   if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0)
     return fail(nullptr, BPSN_ERR_NO_DEVICE, "bpsn_create: no CUDA device available");
@@ -608,9 +726,11 @@ int32_t bpsn_create(const bpsn_config* cfg, bpsn_sim** out) {
   sim->cfg = *cfg;
   sim->scenes.resize(cfg->num_scenes);
   sim->envScene.resize(cfg->num_envs);
-  const uint32_t perScene = cfg->num_envs / cfg->num_scenes;
-  for (uint32_t e = 0; e < cfg->num_envs; ++e)
-    sim->envScene[e] = e / perScene;
+  sim->numActive = numActive;
+  sim->rotation = rotating;
+  sim->activeScenes.resize(numActive);
+  for (uint32_t i = 0; i < numActive; ++i)
+    sim->activeScenes[i] = i;
   // glm::angleAxis(radians(+/-10), +Y) = (sin(a/2) * axis, cos(a/2)), on the
   // host libm as the reference does at static-init time (simulator.cpp:52-60)
   const float a = 10.f * 0.01745329251994329576923690768489f;
@@ -719,7 +839,29 @@ int32_t bpsn_set_env_scenes(bpsn_sim* sim, const uint32_t* env_scene, uint32_t c
   for (uint32_t e = 0; e < count; ++e)
     if (env_scene[e] >= sim->cfg.num_scenes)
       return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_set_env_scenes: scene index out of range");
+  if (sim->rotation)
+    return fail(sim, BPSN_ERR_STATE,
+                "bpsn_set_env_scenes: environments follow their slot's scene when scenes rotate");
   sim->envScene.assign(env_scene, env_scene + count);
+  sim->envSceneExplicit = true;
+  return BPSN_OK;
+}
+
+int32_t bpsn_set_active_scenes(bpsn_sim* sim, const uint32_t* scenes, uint32_t count) {
+  if (!sim || !scenes)
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_set_active_scenes: null argument");
+  if (sim->finalized)
+    return fail(sim, BPSN_ERR_STATE, "bpsn_set_active_scenes: already finalized");
+  if (count != sim->numActive)
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_set_active_scenes: count != num_active_scenes");
+  for (uint32_t i = 0; i < count; ++i) {
+    if (scenes[i] >= sim->cfg.num_scenes)
+      return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_set_active_scenes: scene index out of range");
+    for (uint32_t j = 0; j < i; ++j)
+      if (scenes[j] == scenes[i])
+        return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_set_active_scenes: a scene is listed twice");
+  }
+  sim->activeScenes.assign(scenes, scenes + count);
   return BPSN_OK;
 }
 
@@ -815,12 +957,80 @@ int32_t bpsn_finalize(bpsn_sim* sim) {
   const uint32_t ng = sim->cfg.num_groups;
   const uint32_t B = sim->cfg.num_envs / ng;
   sim->groups.resize(ng);
+  if (!sim->envSceneExplicit) {
+    // num_envs / num_active_scenes consecutive environments per slot, group-major then
+    // slot-major (simulator/simulator.cpp:1205-1221, 1581-1592)
+    const uint32_t perSlot = sim->cfg.num_envs / sim->numActive;
+    for (uint32_t e = 0; e < sim->cfg.num_envs; ++e)
+      sim->envScene[e] = sim->activeScenes[e / perSlot];
+  }
+  // The scenes that wait for a slot, in ascending order (the reference's inactive_scenes_,
+  // simulator.cpp:1518-1534), dealt to the groups in turn: each group then rotates through
+  // its own share, whatever the other group is doing at the time (the groups' steps may
+  // overlap on the GPU).  The reference has one list for all groups.
+  sim->pools.assign(ng, std::vector<uint32_t>());
+  if (sim->rotation) {
+    std::vector<uint8_t> active(ns, 0);
+    for (uint32_t sc : sim->activeScenes)
+      active[sc] = 1;
+    uint32_t k = 0;
+    for (uint32_t sc = 0; sc < ns; ++sc)
+      if (!active[sc])
+        sim->pools[k++ % ng].push_back(sc);
+  }
   for (uint32_t gi = 0; gi < ng; ++gi) {
-    int32_t rc = allocGroup(sim, sim->groups[gi], B, gi * B, sim->envScene.data() + gi * B);
+    int32_t rc = allocGroup(sim, sim->groups[gi], B, gi * B, gi);
     if (rc)
       return rc;
   }
+  if (sim->rotation) {
+    // Every slot starts its first move right away (RolloutGenerator's constructor calls
+    // startSceneSwap on every swapper, simulator.cpp:1594): the environments begin in the
+    // first scenes and follow at the end of their first episodes.
+    for (uint32_t gi = 0; gi < ng; ++gi)
+      k_swap<<<1, 32>>>(sim->groups[gi].dev, static_cast<uint32_t>(sim->cfg.seed),
+                        static_cast<uint32_t>(sim->cfg.seed >> 32));
+    BPSN_CUDA(sim, cudaGetLastError());
+    BPSN_CUDA(sim, cudaDeviceSynchronize());
+  }
   sim->finalized = true;
+  return BPSN_OK;
+}
+
+int32_t bpsn_swap_stats(bpsn_sim* sim, uint64_t* num_swaps, float* scenes_in_use,
+                        float* envs_per_scene) {
+  if (!sim || !sim->finalized)
+    return fail(sim, BPSN_ERR_STATE, "bpsn_swap_stats: handle not finalized");
+  BPSN_CUDA(sim, cudaSetDevice(sim->cfg.gpu_id));
+  BPSN_CUDA(sim, cudaDeviceSynchronize());
+  uint64_t swaps = 0;
+  float scenes = 0.f, perScene = 0.f;
+  std::vector<uint32_t> envScene;
+  for (Group& g : sim->groups) {
+    uint32_t c = 0;
+    BPSN_CUDA(sim, cudaMemcpy(&c, g.dev.swapCount, sizeof(c), cudaMemcpyDeviceToHost));
+    // (the first move of every slot is started at set-up and not counted, as in the reference)
+    const uint32_t atSetup = g.dev.poolSize ? g.dev.numSlots : 0u;
+    swaps += c > atSetup ? c - atSetup : 0u;
+    envScene.resize(g.dev.B);
+    BPSN_CUDA(sim, cudaMemcpy(envScene.data(), g.dev.scene, sizeof(uint32_t) * g.dev.B,
+                              cudaMemcpyDeviceToHost));
+    // EnvironmentGroup::sceneStats (simulator.cpp:1212-1227)
+    std::vector<uint32_t> count(sim->cfg.num_scenes, 0u);
+    for (uint32_t sc : envScene)
+      count[sc]++;
+    uint32_t distinct = 0;
+    for (uint32_t c2 : count)
+      distinct += c2 ? 1u : 0u;
+    scenes += static_cast<float>(distinct);
+    perScene += distinct ? static_cast<float>(g.dev.B) / static_cast<float>(distinct) : 0.f;
+  }
+  if (num_swaps)
+    *num_swaps = swaps;
+  if (scenes_in_use)
+    *scenes_in_use = scenes;
+  if (envs_per_scene)
+    *envs_per_scene = perScene;
   return BPSN_OK;
 }
 
@@ -926,16 +1136,19 @@ int32_t bpsn_step_start_ex(bpsn_sim* sim, uint32_t group, const int64_t* actions
     lc.gridDim = dim3(g.numCtas);
     lc.blockDim = dim3(512);
     lc.dynamicSmemBytes = g.geoSmem;
-    auto* kernel = g.warpMode == 0 ? k_step_warp<0> : g.warpMode == 1 ? k_step_warp<1> : k_step_warp<2>;
+    const bool rot = g.dev.rotation != 0u;
+    auto* kernel = g.warpMode == 0   ? (rot ? k_step_warp<0, true> : k_step_warp<0, false>)
+                   : g.warpMode == 1 ? (rot ? k_step_warp<1, true> : k_step_warp<1, false>)
+                                     : (rot ? k_step_warp<2, true> : k_step_warp<2, false>);
     BPSN_CUDA(sim, cudaLaunchKernelEx(&lc, kernel, gd, sim->table,
                                       static_cast<const WarpPlan*>(g.dPlan),
-                                      static_cast<const uint2*>(g.dCtaMap), g.fallbackScratch,
+                                      static_cast<const uint4*>(g.dCtaMap), g.fallbackScratch,
                                       g.globalSlabs, g.globalSlabStride, seedLo, seedHi));
   }
   if (g.anyThreadScene) {  // meshes the warp kernel cannot index (it skips the other scenes)
     if (g.anyWarpScene)
       lc.numAttrs = 0;  // behind the warp kernel: plain stream order, no early start
-    lc.gridDim = dim3(blocksFor(g.maxSceneEnvs, 128), g.numScenesUsed);
+    lc.gridDim = dim3(blocksFor(g.maxListLen, 128), g.dev.numLists);
     lc.blockDim = dim3(128);
     lc.dynamicSmemBytes = 0;
     BPSN_CUDA(sim, cudaLaunchKernelEx(&lc, k_step_thread, gd, sim->table,
@@ -943,6 +1156,13 @@ int32_t bpsn_step_start_ex(bpsn_sim* sim, uint32_t group, const int64_t* actions
                                       seedHi));
   }
   if (prof) cudaEventRecord(g.prof[2], s);
+  if (g.dev.rotation && g.dev.poolSize) {  // slots that are complete start their next move
+    lc.numAttrs = prof ? 0 : 1;
+    lc.gridDim = dim3(1);
+    lc.blockDim = dim3(32);
+    lc.dynamicSmemBytes = 0;
+    BPSN_CUDA(sim, cudaLaunchKernelEx(&lc, k_swap, gd, seedLo, seedHi));
+  }
   BPSN_CUDA(sim, cudaGetLastError());
   int32_t rc = finishLaunch(sim, g, s, /*polarOnly=*/false);
   if (rc)
@@ -995,8 +1215,14 @@ int32_t bpsn_step_end(bpsn_sim* sim, uint32_t group) {
   if (!g.inFlight)
     return fail(sim, BPSN_ERR_STATE, "Simulation already done");
   g.inFlight = false;
-  if (sim->cfg.flags & BPSN_FLAG_HOST_MIRRORS)
+  if (sim->cfg.flags & BPSN_FLAG_HOST_MIRRORS) {
     BPSN_CUDA(sim, cudaEventSynchronize(g.done));
+    if (g.hErr && *g.hErr)
+      return fail(sim, BPSN_ERR_CUDA,
+                  "bpsn_step_end: a step kernel gave up waiting for its scene tables; the "
+                  "environments it served keep the outputs of the step before "
+                  "(bpsn_device_error_flags)");
+  }
   if (g.profiling) {
     BPSN_CUDA(sim, cudaEventSynchronize(g.prof[2]));
     for (int k = 0; k < 2; ++k) {

@@ -108,6 +108,7 @@ struct WarpSlab {
   uint2* nodeB;
   uint16_t* path;
   uint32_t* searches;  // global-memory slabs only: the search counter
+  int cap;             // node slots of the slab (what carveSlab was given)
 };
 
 __device__ __forceinline__ WarpSlab carveSlab(uint8_t* base, int pcap) {
@@ -116,6 +117,7 @@ __device__ __forceinline__ WarpSlab carveSlab(uint8_t* base, int pcap) {
   s.nodeB = reinterpret_cast<uint2*>(base + static_cast<size_t>(pcap) * 16);
   s.path = reinterpret_cast<uint16_t*>(base + static_cast<size_t>(pcap) * 24);
   s.searches = nullptr;
+  s.cap = pcap;
   return s;
 }
 
@@ -638,7 +640,10 @@ __device__ __forceinline__ uint32_t beginSearch(const WarpSlab w, int P, int lan
       *w.searches = count;
   }
   if (wipe) {
-    for (int i = lane; i < P; i += 32)
+    // (a global-memory slab serves scenes of different sizes over time and keeps their marks:
+    // when its numbering starts over, all of it is wiped, not just this scene's share)
+    const int len = kGlobal ? w.cap : P;
+    for (int i = lane; i < len; i += 32)
       w.nodeB[i] = make_uint2(0u, 0u);
   }
   __syncwarp();
@@ -1227,14 +1232,18 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
 // global memory.
 template <bool kGlobal>
 __device__ __forceinline__ void stepWarpQueries(const GroupDev& g, const SceneTable& st,
-                                                const WarpPlan pl, int sceneIdx, uint32_t rank,
-                                                uint32_t n, const NavScene& scGlobal,
+                                                const WarpPlan pl, uint32_t listIdx,
+                                                uint32_t rank, uint32_t slotCtas, uint32_t n,
+                                                const NavScene& scGlobal,
                                                 uint8_t* globalSlabs, size_t globalSlabStride,
                                                 AStarScratch* fallbackScratch, uint32_t seedLo,
                                                 uint32_t seedHi
 ) {
   extern __shared__ __align__(16) uint8_t smem[];
-  const int pcap = static_cast<int>(pl.pcap);
+  // Slabs in global memory are laid out for the largest scene of the group whatever scene
+  // is being worked on: a slab outlives searches, launches and (when scenes rotate) scenes,
+  // and its visit marks only mean something if they always sit in the same place.
+  const int pcap = static_cast<int>(kGlobal ? g.globalPcap : pl.pcap);
   const int warpsPerBlock = static_cast<int>(pl.warps);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -1271,11 +1280,11 @@ __device__ __forceinline__ void stepWarpQueries(const GroupDev& g, const SceneTa
   const bool slabPerEnv = kGlobal && g.slabPerEnv != 0u;
 
   const uint32_t B = g.B;
-  const uint32_t base = g.listBase[sceneIdx];
-  uint32_t* cursor = g.counts + g.numScenes + sceneIdx;  // zeroed by the step before
+  const uint32_t base = g.listBase[listIdx];
+  uint32_t* cursor = g.counts + g.numLists + listIdx;  // zeroed by the step before
   // Every warp starts on the list slot of its own number; the slots beyond the number of
-  // warps in the grid are handed out through the cursor.
-  const uint32_t gridWarps = pl.ctas * static_cast<uint32_t>(warpsPerBlock);
+  // warps the slot's CTAs have are handed out through the cursor.
+  const uint32_t gridWarps = slotCtas * static_cast<uint32_t>(warpsPerBlock);
   uint32_t q = rank * static_cast<uint32_t>(warpsPerBlock) + static_cast<uint32_t>(warp);
   for (bool first = true;; first = false) {
     if (!first) {
@@ -1333,115 +1342,175 @@ __device__ __forceinline__ void stepWarpQueries(const GroupDev& g, const SceneTa
   }
 }
 
-// One simulator step for the environments listed per scene (see sim_kernels.cuh
-// for the phase split): forward move, GPS/compass, geodesic goal -> agent,
-// info / reward / mask and the in-loop reset.
-//   grid  = CTAs of all scenes (ctaMap says which scene a CTA serves), block = 512 threads
-//   smem  = staged tables of the CTA's scene + as many warp slabs as fit (plan[scene].warps)
-// Warps pull list slots from a per-scene cursor until the list is drained.
+// One simulator step for the listed environments (see sim_kernels.cuh for the phase split):
+// forward move, GPS/compass, geodesic goal -> agent, info / reward / mask and the in-loop
+// reset.
+//   grid  = CTAs of all slots (ctaMap: slot, number among the slot's CTAs, their count),
+//           block = 512 threads
+//   smem  = staged tables of the scene being worked on + as many warp slabs as fit
+//           (plan[scene].warps)
+// A CTA drains the slot's two work lists one after the other: environments in the slot's
+// scene, then (only while the slot is moving to another scene) those still in the previous
+// one, whose tables are staged in between.  Warps pull list slots from a per-list cursor
+// until the list is drained.
 // Three instances, chosen by the host from the group's plan, so that a group whose scenes
 // all sit in shared memory (the usual case) does not carry the code of the other mode:
 //   kMode 0  every scene of the group is staged in shared memory
 //   kMode 1  every scene is worked on in global memory (launched without dynamic shared
 //            memory, which leaves the whole unified cache to L1)
 //   kMode 2  both kinds in one grid
-template <int kMode>
+// and each of them for fixed scenes (kRotate false: one list per slot, and which scene the
+// slot has is known before the kernel has to wait for its predecessor) and for rotating ones.
+template <int kMode, bool kRotate>
 __global__ void __launch_bounds__(512, kMode == 1 ? 2 : 1)
 k_step_warp(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
-            const uint2* __restrict__ ctaMap, AStarScratch* __restrict__ fallbackScratch,
+            const uint4* __restrict__ ctaMap, AStarScratch* __restrict__ fallbackScratch,
             uint8_t* __restrict__ globalSlabs, size_t globalSlabStride, uint32_t seedLo,
             uint32_t seedHi) {
   extern __shared__ __align__(16) uint8_t smem[];
   launchDependents();
-  // which scene this CTA serves and its number among that scene's CTAs (set-up data)
-  const uint2 cm = ctaMap[blockIdx.x];
-  const int sceneIdx = static_cast<int>(cm.x);
-  const uint32_t rank = cm.y;
-  const WarpPlan pl = plan[sceneIdx];
-  const int warpsPerBlock = static_cast<int>(pl.warps);  // warps of this CTA that take queries
+  // which slot this CTA serves, its number among that slot's CTAs and how many they are
+  // (set-up data)
+  const uint4 cm = ctaMap[blockIdx.x];
+  const uint32_t slot = cm.x, rank = cm.y, slotCtas = cm.z;
   const int warp = threadIdx.x >> 5;
 
-  uint32_t n = 0;
-  const NavScene scGlobal = st.scenes[sceneIdx];
-  // A scene too large to sit in shared memory next to at least one slab is worked on where
-  // it lies: the same image, in global memory (L2-resident), and slabs in a global
-  // scratch area.  The code below is the same either way; only the latency differs.
-  const bool inGlobal = kMode == 1 || (kMode == 2 && pl.slabOffset == kSlabInGlobal);
-  if (inGlobal) {
-    waitForPredecessor();
-    n = g.counts[sceneIdx];
-    if (rank == 0 && threadIdx.x == 0) {  // the next step starts from empty lists
-      g.countsNext[sceneIdx] = 0u;
-      g.countsNext[g.numScenes + sceneIdx] = 0u;
+  // The staged image of a scene was laid out at set-up exactly as stagedLayout() describes
+  // (float4 vertices, polygons with filtered links and the duplicate-neighbour flag, detail
+  // bases / triangles / vertices, island ids), 16-byte aligned and a multiple of 16 bytes
+  // long: one bulk asynchronous copy (TMA, untiled, this CTA's own shared memory, no
+  // multicast) brings it in and signals an mbarrier, whose phase alternates from one copy
+  // to the next.
+  __shared__ __align__(8) unsigned long long stageBar;
+  const uint32_t bar = static_cast<uint32_t>(__cvta_generic_to_shared(&stageBar));
+  const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  uint32_t phase = 0u;
+  bool inFlight = false, failed = false;
+  uint32_t stagedScene = 0xffffffffu;
+  auto stage = [&](const NavScene& scn) {
+    if (threadIdx.x == 0) {
+      const uint32_t bytes = scn.stagedBytes;
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                   : "memory");
+      asm volatile(
+          "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+          ::"r"(dst), "l"(scn.staged), "r"(bytes), "r"(bar)
+          : "memory");
     }
-  } else {
-    // The image was laid out at set-up exactly as stagedLayout() describes (float4
-    // vertices, polygons with filtered links and the duplicate-neighbour flag, detail
-    // bases / triangles / vertices, island ids), 16-byte aligned and a multiple of 16
-    // bytes long: one bulk asynchronous copy (TMA, untiled, this CTA's own shared
-    // memory, no multicast) brings it in and signals an mbarrier.
-    __shared__ __align__(8) unsigned long long stageBar;
-    const uint32_t bar = static_cast<uint32_t>(__cvta_generic_to_shared(&stageBar));
-    const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
-    const uint32_t bytes = scGlobal.stagedBytes;
+    inFlight = true;
+  };
+  // bounded wait for the copy in flight (a copy of this size lands within microseconds, the
+  // bound is ~1 s of polling); false when it did not arrive
+  auto landed = [&]() -> bool {
+    bool ok = false;
+    for (int it = 0; it < (1 << 22) && !ok; ++it) {
+      uint32_t r;
+      asm volatile(
+          "{\n\t.reg .pred p;\n\t"
+          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(r)
+          : "r"(bar), "r"(phase)
+          : "memory");
+      ok = r != 0;
+    }
+    const bool all = __syncthreads_and(ok ? 1 : 0) != 0;
+    if (all) {
+      phase ^= 1u;
+      inFlight = false;
+    }
+    return all;
+  };
+  if (kMode != 1) {
     if (threadIdx.x == 0) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar) : "memory");
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-                   : "memory");
-      asm volatile(
-          "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-          ::"r"(dst), "l"(scGlobal.staged), "r"(bytes), "r"(bar)
-          : "memory");
+  }
+  // Fixed scenes: which scene the slot has is set-up data and its image never changes, so
+  // all of it is fetched, and the copy started, while the kernel before this one is still at
+  // work.
+  uint32_t sc0 = 0u;
+  WarpPlan pl0{};
+  NavScene scn0{};
+  if (!kRotate) {
+    sc0 = g.slotScene[slot];
+    pl0 = plan[sc0];
+    scn0 = st.scenes[sc0];
+    if (kMode != 1 && pl0.warps != 0 && pl0.slabOffset != kSlabInGlobal) {
+      stage(scn0);
+      stagedScene = sc0;
     }
-    // The scene image never changes, so the copy above may run while the kernel
-    // before this one is still at work; everything below reads what it wrote.
-    waitForPredecessor();
-    n = g.counts[sceneIdx];
+  }
+  // everything below reads what the kernels before this one wrote
+  waitForPredecessor();
+
+  constexpr uint32_t kRoles = kRotate ? 2u : 1u;
+#pragma unroll 1
+  for (uint32_t role = 0; role < kRoles; ++role) {
+    const uint32_t listIdx = 2u * slot + role;
+    const uint32_t n = g.counts[listIdx];
     if (rank == 0 && threadIdx.x == 0) {  // the next step starts from empty lists
-      g.countsNext[sceneIdx] = 0u;
-      g.countsNext[g.numScenes + sceneIdx] = 0u;
+      g.countsNext[listIdx] = 0u;
+      g.countsNext[g.numLists + listIdx] = 0u;
     }
-    // bounded wait on phase 0 of the barrier; a copy of this size lands within
-    // microseconds, the bound is ~1 s of polling
-    bool landed = false;
-    for (int it = 0; it < (1 << 22) && !landed; ++it) {
-      uint32_t ok;
-      asm volatile(
-          "{\n\t.reg .pred p;\n\t"
-          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\t"
-          "selp.u32 %0, 1, 0, p;\n\t}"
-          : "=r"(ok)
-          : "r"(bar)
-          : "memory");
-      landed = ok != 0;
+    if (n == 0)
+      continue;
+    const uint32_t sceneIdx = !kRotate ? sc0 : (role ? g.slotPrev[slot] : g.slotScene[slot]);
+    const WarpPlan pl = !kRotate ? pl0 : plan[sceneIdx];
+    if (pl.warps == 0)
+      continue;  // a scene of the one-thread-per-environment kernel
+    const NavScene scGlobal = !kRotate ? scn0 : st.scenes[sceneIdx];
+    // A scene too large to sit in shared memory next to at least one slab is worked on where
+    // it lies: the same image, in global memory (L2-resident), and slabs in a global
+    // scratch area.  The code is the same either way; only the latency differs.
+    const bool inGlobal = kMode == 1 || (kMode == 2 && pl.slabOffset == kSlabInGlobal);
+    if (kMode != 1 && !inGlobal) {
+      if (stagedScene != sceneIdx) {
+        if (inFlight && !landed()) {
+          failed = true;
+          break;
+        }
+        __syncthreads();  // every warp is through with the image that is being replaced
+        stage(scGlobal);
+        stagedScene = sceneIdx;
+      }
+      if (inFlight && !landed()) {
+        failed = true;
+        break;
+      }
     }
-    if (!__syncthreads_and(landed ? 1 : 0)) {
-      // never observed; leave without touching the half-filled tables (the step's
-      // listed envs keep their previous outputs) and make the failure visible
-      if (threadIdx.x == 0)
-        atomicOr(g.errFlags, 1u);
-      return;
-    }
-  }
-  if (rank * static_cast<uint32_t>(warpsPerBlock) >= n || warp >= warpsPerBlock)
-    return;  // (only after the copy has landed: it targets this CTA's shared memory)
-#define BPSN_STEP_ARGS g, st, pl, sceneIdx, rank, n, scGlobal, globalSlabs, globalSlabStride, \
-                       fallbackScratch, seedLo, seedHi
-  if constexpr (kMode == 0) {
-    stepWarpQueries<false>(BPSN_STEP_ARGS);
-  } else if constexpr (kMode == 1) {
-    stepWarpQueries<true>(BPSN_STEP_ARGS);
-  } else {
-    if (inGlobal)
-      stepWarpQueries<true>(BPSN_STEP_ARGS);
-    else
+    const int warpsPerBlock = static_cast<int>(pl.warps);  // warps of this CTA that take queries
+    if (rank * static_cast<uint32_t>(warpsPerBlock) >= n || warp >= warpsPerBlock)
+      continue;
+#define BPSN_STEP_ARGS g, st, pl, listIdx, rank, slotCtas, n, scGlobal, globalSlabs, \
+                       globalSlabStride, fallbackScratch, seedLo, seedHi
+    if constexpr (kMode == 0) {
       stepWarpQueries<false>(BPSN_STEP_ARGS);
-  }
+    } else if constexpr (kMode == 1) {
+      stepWarpQueries<true>(BPSN_STEP_ARGS);
+    } else {
+      if (inGlobal)
+        stepWarpQueries<true>(BPSN_STEP_ARGS);
+      else
+        stepWarpQueries<false>(BPSN_STEP_ARGS);
+    }
 #undef BPSN_STEP_ARGS
+  }
+  if (kMode != 1) {
+    // A copy whose list turned out empty, or one that did not arrive in time (never observed):
+    // the CTA does not exit under a copy into its own shared memory, it waits once more.  A
+    // copy that was late is made visible (bpsn_step_end reports it): the environments this CTA
+    // would have served keep the outputs of the step before.
+    if (inFlight)
+      landed();
+    if (failed && threadIdx.x == 0) {
+      atomicOr(g.errFlags, 1u);
+      if (g.hErr)
+        *g.hErr = 1u;
+    }
+  }
 }
 
 }  // namespace bpsn

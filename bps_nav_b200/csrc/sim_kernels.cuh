@@ -61,7 +61,10 @@ struct GroupDev {
   uint32_t infoWidth;  // floats per env in `info`: 3 (PointNav) or 1 (Flee, Exploration)
   uint32_t exactHeap;  // test switch: every warp search uses the slab heap (geo_warp.cuh)
   uint32_t numScenes;  // scenes of the simulator (length of the per-scene tables)
+  uint32_t numLists;   // work lists of the group: two per slot (see `slot` below)
+  uint32_t rotation;   // scenes rotate through the slots (more scenes than slots)
   uint32_t slabPerEnv;  // global-memory slabs are indexed by environment, not by warp (geo_warp.cuh)
+  uint32_t globalPcap;  // node capacity every global-memory slab is laid out for
   // pose / task state, each [B] (vectors are component-major: x[B] y[B] z[B])
   float* pos;      // [3][B]  position_
   float* rot;      // [4][B]  rotation_ (x y z w)
@@ -97,6 +100,7 @@ struct GroupDev {
   uint8_t* hMask;
   float* hInfo;
   float* hPolar;
+  uint32_t* hErr;  // host-visible copy of errFlags[0] (same mapped block), null without mirrors
   // running episode statistics, the device-side form of PPOTrainer._update_stats
   // (bps_nav/rl/ppo/ppo_trainer.py:286-319)
   float* episodeReward;  // [B]     reward accumulated in the current episode
@@ -106,14 +110,35 @@ struct GroupDev {
   uint32_t* numCells;    // [B]     cells in the set
   float* stats;          // [5][B]  sums over finished episodes: reward, count, success,
                          //         spl, distanceToGoal
-  // geodesic work list, segmented by scene: scene s owns geoList[listBase[s] ...],
-  // counts[s] entries are valid this step
-  uint32_t* geoList;         // [B]
-  uint32_t* counts;          // [2 * numScenes]: list lengths, then work-queue cursors
+  // Slots.  A slot is a fixed set of environments that share a scene: one per scene of the
+  // group when the scenes are fixed; `environments / active scenes` consecutive environments
+  // when the dataset has more scenes than are active at a time
+  // (simulator/simulator.cpp:1205-1221).  Then a slot moves on to another scene whenever all
+  // of its environments have reached the current one: every environment follows at the end of
+  // its running episode (EnvironmentGroup::swapReady / swapScene, :1284-1308, called from the
+  // work loop :1636-1640), so a slot's environments are in at most two scenes at a time, the
+  // one it is moving to (`slotScene`) and the one before (`slotPrev`).
+  uint32_t* slot;           // [B] slot of each environment (fixed)
+  uint32_t* envEpoch;       // [B] number of the slot's move this environment has caught up with
+  uint32_t* slotScene;      // [slots] scene the slot's environments are in, or moving to
+  uint32_t* slotPrev;       // [slots] scene of those that have not moved yet
+  uint32_t* slotEpoch;      // [slots] moves started so far
+  uint32_t* slotRemaining;  // [slots] environments that still have to follow the current move
+  uint32_t* slotSize;       // [slots] environments of the slot
+  uint32_t* pool;           // [poolSize] scenes waiting for a slot
+  uint32_t* swapCount;      // [1] moves completed (RolloutGenerator::swapStats, :1412-1424)
+  uint32_t numSlots;
+  uint32_t poolSize;
+  uint32_t slotBase;        // number of the group's first slot among all slots
+  // geodesic work lists, two per slot: list 2 * s holds the slot's listed environments that are
+  // in slotScene[s], list 2 * s + 1 those still in slotPrev[s]; list l owns
+  // geoList[listBase[l] ...], counts[l] entries are valid this step
+  uint32_t* geoList;         // [2 * B]
+  uint32_t* counts;          // [2 * numLists]: list lengths, then work-queue cursors
   uint32_t* countsNext;      // the next step's `counts`: the step kernel zeroes it, so that no
                              // separate clearing pass sits between two steps
   uint32_t* errFlags;        // [1] sticky device-side error bits (never cleared by kernels)
-  const uint32_t* listBase;  // [numScenes]
+  const uint32_t* listBase;  // [numLists]
 };
 
 // Per-episode results of reset()'s navmesh queries.
@@ -172,13 +197,16 @@ constexpr float kMaxSteps = 500.f;        // :50
 constexpr float kForwardStep = 0.25f;     // :51
 
 // Philox-4x32-10 (Salmon et al., SC'11): the episode-selection stream.
-__device__ __forceinline__ uint32_t philoxFirst(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
-                                                uint32_t k0, uint32_t k1) {
+__host__ __device__ __forceinline__ uint32_t mulHi32(uint32_t a, uint32_t b) {
+  return static_cast<uint32_t>((static_cast<uint64_t>(a) * b) >> 32);
+}
+__host__ __device__ __forceinline__ uint32_t philoxFirst(uint32_t c0, uint32_t c1, uint32_t c2,
+                                                         uint32_t c3, uint32_t k0, uint32_t k1) {
 #pragma unroll
   for (int r = 0; r < 10; ++r) {
-    const uint32_t hi0 = __umulhi(0xD2511F53u, c0);
+    const uint32_t hi0 = mulHi32(0xD2511F53u, c0);
     const uint32_t lo0 = 0xD2511F53u * c0;
-    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2);
+    const uint32_t hi1 = mulHi32(0xCD9E8D57u, c2);
     const uint32_t lo1 = 0xCD9E8D57u * c2;
     const uint32_t n0 = hi1 ^ c1 ^ k0;
     const uint32_t n2 = hi0 ^ c3 ^ k1;
@@ -351,7 +379,7 @@ __device__ __forceinline__ void finishEnvLoaded(const GroupDev& g, const SceneTa
   const bool pointNav = g.task == kTaskPointNav;
   float init = 0.f, cum = 0.f, px = 0.f, py = 0.f, pz = 0.f, qx = 0.f, qy = 0.f, qz = 0.f;
   float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f, s4 = 0.f;
-  uint32_t sceneIdx = 0u, rc = 0u;
+  uint32_t sceneIdx = 0u, rc = 0u, slotIdx = 0u, myEpoch = 0u, slotEpoch = 0u, slotScene = 0u;
   if (done) {
     s0 = g.stats[e];
     s1 = g.stats[B + e];
@@ -363,6 +391,12 @@ __device__ __forceinline__ void finishEnvLoaded(const GroupDev& g, const SceneTa
     if (pointNav) {
       init = g.initDist[e];
       cum = g.cumTravel[e];
+    }
+    if (g.rotation) {
+      slotIdx = g.slot[e];
+      myEpoch = g.envEpoch[e];
+      slotEpoch = g.slotEpoch[slotIdx];
+      slotScene = g.slotScene[slotIdx];
     }
   } else if (moved && pointNav) {
     cum = g.cumTravel[e];
@@ -445,6 +479,14 @@ __device__ __forceinline__ void finishEnvLoaded(const GroupDev& g, const SceneTa
     g.stats[3 * B + e] = s3 + spl;
     g.stats[4 * B + e] = s4 + d;
     g.episodeReward[e] = 0.f;
+    if (myEpoch != slotEpoch) {
+      // the slot has moved on: this environment follows now, at the end of its episode, and
+      // starts its next one in the new scene (swapScene, simulator.cpp:1292-1308)
+      sceneIdx = slotScene;
+      g.scene[e] = slotScene;
+      g.envEpoch[e] = slotEpoch;
+      atomicSub(&g.slotRemaining[slotIdx], 1u);
+    }
     resetEnvLoaded(g, st, e, sceneIdx, rc, seedLo, seedHi);
   } else {
     g.episodeReward[e] = epr;
@@ -507,7 +549,10 @@ k_pre(GroupDev g, SceneTable st, const int64_t* __restrict__ actions,
   float qx = g.rot[e], qy = g.rot[B + e], qz = g.rot[2 * B + e], qw = g.rot[3 * B + e];
   const float px = g.pos[e], py = g.pos[B + e], pz = g.pos[2 * B + e];
   const float gx = g.goal[e], gy = g.goal[B + e], gz = g.goal[2 * B + e];
-  const uint32_t sceneIdx = g.scene[e];
+  const uint32_t slotIdx = g.slot[e];
+  uint32_t listIdx = 2u * slotIdx;
+  if (g.rotation)  // still in the scene the slot is leaving?
+    listIdx += g.envEpoch[e] != g.slotEpoch[slotIdx] ? 1u : 0u;
   const float prev = g.prevDist[e];
   const float epr0 = g.episodeReward[e];
   g.step[e] = step;
@@ -548,16 +593,16 @@ k_pre(GroupDev g, SceneTable st, const int64_t* __restrict__ actions,
   if (listed) {
     // the list entry carries what the step kernel has to know about the action
     const uint32_t entry = e | (done ? kListDone : 0u) | (moved ? kListMoved : 0u);
-    // one atomic per (warp, scene) instead of one per environment
-    const unsigned grp = __match_any_sync(listedMask, sceneIdx);
+    // one atomic per (warp, list) instead of one per environment
+    const unsigned grp = __match_any_sync(listedMask, listIdx);
     const int leader = __ffs(grp) - 1;
     const int lane = threadIdx.x & 31;
     uint32_t base = 0;
     if (lane == leader)
-      base = atomicAdd(&g.counts[sceneIdx], static_cast<uint32_t>(__popc(grp)));
+      base = atomicAdd(&g.counts[listIdx], static_cast<uint32_t>(__popc(grp)));
     base = __shfl_sync(grp, base, leader);
-    const uint32_t slot = base + __popc(grp & ((1u << lane) - 1u));
-    g.geoList[g.listBase[sceneIdx] + slot] = entry;
+    const uint32_t at = base + __popc(grp & ((1u << lane) - 1u));
+    g.geoList[g.listBase[listIdx] + at] = entry;
   } else {
     finishEnvLoaded(g, st, e, false, false, 0.f, prev, epr0, seedLo, seedHi);
   }
@@ -570,22 +615,24 @@ __global__ void __launch_bounds__(128)
 k_step_thread(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
               AStarScratch* __restrict__ scratch, uint32_t seedLo, uint32_t seedHi) {
   launchDependents();
-  const uint32_t sceneIdx = blockIdx.y;
+  const uint32_t listIdx = blockIdx.y;
+  waitForPredecessor();
+  const uint32_t sceneIdx =
+      (listIdx & 1u) ? g.slotPrev[listIdx >> 1] : g.slotScene[listIdx >> 1];
   if (plan && plan[sceneIdx].warps != 0)
     return;  // the warp kernel has this scene
-  waitForPredecessor();
   const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
-  const uint32_t n = g.counts[sceneIdx];
+  const uint32_t n = g.counts[listIdx];
   if (t == 0) {  // the next step starts from empty lists
-    g.countsNext[sceneIdx] = 0u;
-    g.countsNext[g.numScenes + sceneIdx] = 0u;
+    g.countsNext[listIdx] = 0u;
+    g.countsNext[g.numLists + listIdx] = 0u;
   }
   if (t >= n)
     return;
-  const uint32_t slot = g.listBase[sceneIdx] + t;
-  if (slot >= g.B)
+  const uint32_t at = g.listBase[listIdx] + t;
+  if (at >= 2u * g.B)
     return;
-  const uint32_t entry = g.geoList[slot];
+  const uint32_t entry = g.geoList[at];
   const uint32_t e = entry & kListEnvMask;
   const uint32_t B = g.B;
   const NavScene sc = st.scenes[sceneIdx];
@@ -597,13 +644,48 @@ k_step_thread(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
     const float a[3] = {g.navPos[e], g.navPos[B + e], g.navPos[2 * B + e]};
     const float b[3] = {g.navGoal[e], g.navGoal[B + e], g.navGoal[2 * B + e]};
     uint32_t status = 0;
-    d = geodesic(sc, scratch + slot, b, g.goalRef[e], a, g.navRef[e], &status);
+    d = geodesic(sc, scratch + e, b, g.goalRef[e], a, g.navRef[e], &status);
     if (status)
       g.status[e] |= status;
   } else if (g.task == kTaskExploration && moved) {
     explVisit(g, e, g.pos[e], g.pos[B + e], g.pos[2 * B + e]);
   }
   finishEnv(g, st, e, done, moved, d, seedLo, seedHi);
+}
+
+// After a step of a group whose scenes rotate: every slot whose environments have all reached
+// the slot's scene starts its next move (SceneSwapper::postStep / startSceneSwap,
+// simulator/simulator.cpp:1094-1129): a scene is drawn from the pool of waiting scenes and
+// trades places with the slot's scene, which can be drawn again at once, also while some
+// other slot's environments are still leaving it.  Slots are visited in order by one thread,
+// as the reference visits its swappers in order at the end of a step.  The reference draws
+// from the generator's std::mt19937, whose state at that point depends on how its worker
+// threads were scheduled, and makes the new scene available when a background thread has
+// loaded it; here the draw is Philox-4x32-10 keyed by the seed with counter (slot, move
+// number, 1, 0), index = mulhi32(r, pool size), and the new scene is available from the
+// next step on (every scene's navigation mesh is resident).
+__global__ void k_swap(GroupDev g, uint32_t seedLo, uint32_t seedHi) {
+  launchDependents();
+  waitForPredecessor();
+  if (blockIdx.x != 0 || threadIdx.x != 0 || g.poolSize == 0)
+    return;
+  uint32_t swaps = 0;
+  for (uint32_t s = 0; s < g.numSlots; ++s) {
+    if (g.slotRemaining[s] != 0u)
+      continue;
+    const uint32_t epoch = g.slotEpoch[s] + 1u;
+    const uint32_t r = philoxFirst(g.slotBase + s, epoch, 1u, 0u, seedLo, seedHi);
+    const uint32_t at = mulHi32(r, g.poolSize);
+    const uint32_t cur = g.slotScene[s];
+    g.slotPrev[s] = cur;
+    g.slotScene[s] = g.pool[at];
+    g.pool[at] = cur;
+    g.slotEpoch[s] = epoch;
+    g.slotRemaining[s] = g.slotSize[s];
+    ++swaps;
+  }
+  if (swaps)
+    *g.swapCount += swaps;
 }
 
 __global__ void __launch_bounds__(256)

@@ -75,6 +75,15 @@ typedef struct {
   uint32_t task;             /* BPSN_TASK_* */
   uint32_t render_width;     /* depth sensor image width  (0 with render_height 0: no sensor) */
   uint32_t render_height;    /* depth sensor image height                                    */
+  uint32_t num_active_scenes; /* scenes in use at a time; 0 = all of them.  With fewer than
+                                 num_scenes the others wait in a pool and the environments move
+                                 through the whole dataset, num_envs / num_active_scenes
+                                 consecutive environments (a "slot") at a time: when all
+                                 environments of a slot have reached its scene the slot draws
+                                 another one from the pool, and each environment follows at the
+                                 end of its running episode (SceneSwapper / EnvironmentGroup::
+                                 swapScene, simulator/simulator.cpp:1063-1154, 1284-1308,
+                                 1636-1640).  Every scene's navigation mesh stays resident. */
 } bpsn_config;
 
 /* Tasks of the reference's three generators (simulator/simulator.cpp:734-999,
@@ -151,9 +160,19 @@ int32_t bpsn_set_navmesh_blob(bpsn_sim* sim, uint32_t scene, const void* data, s
 /* Episode list of a scene (copied). */
 int32_t bpsn_set_episodes(bpsn_sim* sim, uint32_t scene, const bpsn_episode* episodes,
                           uint32_t count);
+/* Optional: the scenes that are in use first, one per slot (count = num_active_scenes;
+ * default 0 .. num_active_scenes - 1).  The reference draws them with std::mt19937(seed)
+ * (simulator/simulator.cpp:1518-1534). */
+int32_t bpsn_set_active_scenes(bpsn_sim* sim, const uint32_t* scenes, uint32_t count);
+/* Scene rotation so far (RolloutGenerator::swapStats, simulator/simulator.cpp:1412-1424):
+ * moves of a slot to another scene started since creation, the number of different scenes
+ * the environments are in right now and the mean number of environments per such scene, both
+ * summed over the groups as the reference does.  Waits for the steps in flight. */
+int32_t bpsn_swap_stats(bpsn_sim* sim, uint64_t* num_swaps, float* scenes_in_use,
+                        float* envs_per_scene);
 /* Optional: explicit scene per environment (default: num_envs / num_scenes
  * consecutive environments per scene, group-major then scene-major, as in
- * simulator/simulator.cpp:1205-1221, 1581-1592). */
+ * simulator/simulator.cpp:1205-1221, 1581-1592).  Only with every scene active. */
 int32_t bpsn_set_env_scenes(bpsn_sim* sim, const uint32_t* env_scene, uint32_t count);
 /* Uploads scenes and episodes, allocates state, outputs and query scratch. */
 /* Render geometry of a scene for the depth sensor: the floor rectangle at y = 0
@@ -208,7 +227,8 @@ int32_t bpsn_get_ptr(bpsn_sim* sim, uint32_t group, int32_t field, int32_t mem, 
 /* Sticky device-side error word of a group (synchronous read; no counterpart
  * in the reference, which aborts on inconsistencies).  Bit 0: a step kernel gave
  * up waiting for its scene tables to arrive in shared memory and skipped its
- * work.  Zero in normal operation. */
+ * work.  Zero in normal operation.  With host mirrors bpsn_step_end also checks the word
+ * and returns BPSN_ERR_CUDA once it is set. */
 int32_t bpsn_device_error_flags(bpsn_sim* sim, uint32_t group, uint32_t* flags);
 
 /* Per-kernel device timing of the step (no counterpart in the reference; its
@@ -334,14 +354,6 @@ int32_t bpsn_gae_static(const float* rewards, float* values, const uint8_t* mask
  * memory for the duration of the call. */
 int32_t bpsn_selftest_sqrt(int32_t gpu_id, uint32_t first_bits, uint32_t last_bits,
                            uint64_t* mismatches);
-
-/* Diagnostic.  Scenes that are searched in global memory keep, per warp, a node array that is
- * not wiped between searches: a node counts as visited when it carries the number of the
- * running search (15 bits; when the number wraps the array is wiped once).  This call sets
- * that number for every such array of `group`, so that a test can cross the wrap after a few
- * steps instead of after 32767 searches.  No step may be in flight.  Groups whose scenes all
- * fit in shared memory have no such arrays; the call then does nothing. */
-int32_t bpsn_debug_set_search_count(bpsn_sim* sim, uint32_t group, uint32_t count);
 
 /* Episode datasets on disk (Dataset, simulator/simulator.cpp:190-359): a directory of
  * `*.json.gz` Habitat PointNav episode files, one scene per file.  bpsn_dataset_open

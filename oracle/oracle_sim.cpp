@@ -19,12 +19,20 @@
 // the glm quaternion/matrix formulas the reference pulls from an un-vendored
 // submodule (angleAxis, quat*quat, quat*vec3, mat3_cast, transpose, length).
 //
+//   * scene rotation: SceneSwapper, EnvironmentGroup::swapReady / swapScene and their
+//     call sites (:1063-1154, 1284-1308, 1385, 1397-1398, 1594, 1636-1640)
 // One deliberate difference, shared with the CUDA implementation: the
 // reference draws the episode index from the *calling worker thread's*
 // std::mt19937 (:605-607, :1736), which makes the sequence depend on thread
 // scheduling.  Here the index is a pure function of (seed, env id, number of
 // resets that env has had): Philox-4x32-10 with key = (seed_lo, seed_hi),
 // counter = (env, reset_count, 0, 0); index = mulhi32(out[0], num_episodes).
+// The same holds for scene rotation: the reference picks the next scene of a slot with that
+// generator too and makes it available when a background thread has loaded it.  Here the
+// pick is Philox with counter = (slot, move number, 1, 0), index = mulhi32(out[0], pool
+// size); the new scene is available from the next step on; and every group draws from its
+// own share of the waiting scenes (dealt in turn, ascending), so that the order in which the
+// groups are stepped plays no role.
 
 #include <atomic>
 #include <cmath>
@@ -118,6 +126,8 @@ struct Episode {  // simulator/simulator.cpp:83-87, rotation stored x,y,z,w
 
 struct Env {
   int scene = 0;
+  int slot = 0;        // scene rotation: the slot this environment belongs to
+  uint32_t epoch = 0;  // ... and the number of the slot's move it has caught up with
   uint32_t resetCount = 0;
   uint32_t episodeIdx = 0;
   Vec3 position{};
@@ -171,7 +181,42 @@ struct Sim {
   bool triggerReset = false;
   // instrumentation
   std::atomic<uint64_t> nTryStep{0}, nFindPath{0}, nSnap{0};
+  // scene rotation (off unless osim_enable_rotation was called)
+  bool rotation = false;
+  int numSlots = 0, numGroups = 1, perSlot = 0;
+  std::vector<int> slotScene, slotPrev;
+  std::vector<uint32_t> slotEpoch;
+  std::vector<std::atomic<int>> slotRemaining;
+  std::vector<std::vector<int>> pools;  // per group
+  uint64_t numSwaps = 0;
 };
+
+// SceneSwapper::postStep + startSceneSwap (simulator.cpp:1094-1129) for the slots that lie
+// inside [first, first + count), in slot order: a slot all of whose environments have reached
+// its scene draws the next one from its group's pool; the scene it leaves goes into the pool.
+void swapPass(Sim& s, int first, int count) {
+  const int slotsPerGroup = s.numSlots / s.numGroups;
+  for (int sl = 0; sl < s.numSlots; ++sl) {
+    if (sl * s.perSlot < first || (sl + 1) * s.perSlot > first + count)
+      continue;
+    std::vector<int>& pool = s.pools[sl / slotsPerGroup];
+    if (pool.empty() || s.slotRemaining[sl].load() != 0)
+      continue;
+    const uint32_t epoch = s.slotEpoch[sl] + 1;
+    uint32_t r[4];
+    philox4x32(static_cast<uint32_t>(sl), epoch, 1u, 0u, static_cast<uint32_t>(s.seed),
+               static_cast<uint32_t>(s.seed >> 32), r);
+    const uint32_t at =
+        static_cast<uint32_t>((static_cast<uint64_t>(r[0]) * pool.size()) >> 32);
+    const int cur = s.slotScene[sl];
+    s.slotPrev[sl] = cur;
+    s.slotScene[sl] = pool[at];
+    pool[at] = cur;
+    s.slotEpoch[sl] = epoch;
+    s.slotRemaining[sl].store(s.perSlot);
+    s.numSwaps++;
+  }
+}
 
 inline float geoDist(Sim& s, void* pf, const float* a, uint64_t ap, const float* b, uint64_t bp) {
   s.nFindPath.fetch_add(1, std::memory_order_relaxed);
@@ -367,8 +412,19 @@ void simulate(Sim& s, int tid) {
       int done = stepEnv(s, e, s.actions[i], pfs);
       if (done < 0)
         g_badAction.store(1);
-      else if (done)
+      else if (done) {
+        if (s.rotation) {
+          // swapReady / swapScene (simulator.cpp:1284-1308): the slot has moved on and
+          // this environment follows now; its next episode is one of the new scene's
+          Env& v = s.envs[e];
+          if (v.epoch != s.slotEpoch[v.slot]) {
+            v.scene = s.slotScene[v.slot];
+            v.epoch = s.slotEpoch[v.slot];
+            s.slotRemaining[v.slot].fetch_sub(1);
+          }
+        }
         resetEnv(s, e, pfs);
+      }
     }
   }
 }
@@ -495,8 +551,54 @@ void osim_reset(void* h, int first, int count) {
 // action was outside {0,1,2,3}.
 int osim_step(void* h, int first, int count, const int64_t* actions) {
   g_badAction.store(0);
-  runRange(*static_cast<Sim*>(h), first, count, actions, false);
+  Sim& s = *static_cast<Sim*>(h);
+  runRange(s, first, count, actions, false);
+  if (s.rotation)
+    swapPass(s, first, count);
   return g_badAction.load() ? -1 : 0;
+}
+
+// Turns scene rotation on: num_active slots of n_envs / num_active consecutive environments,
+// slot i starting in scene active_scenes[i]; the other scenes wait in the groups' pools.
+// Every slot starts its first move at once (simulator.cpp:1594).  Call before the first reset.
+int osim_enable_rotation(void* h, int num_active, int num_groups, const int* active_scenes) {
+  Sim& s = *static_cast<Sim*>(h);
+  if (num_active <= 0 || num_groups <= 0 || s.nEnvs % num_active || num_active % num_groups)
+    return -1;
+  s.rotation = true;
+  s.numSlots = num_active;
+  s.numGroups = num_groups;
+  s.perSlot = s.nEnvs / num_active;
+  s.slotScene.assign(active_scenes, active_scenes + num_active);
+  s.slotPrev = s.slotScene;
+  s.slotEpoch.assign(num_active, 0u);
+  s.slotRemaining = std::vector<std::atomic<int>>(num_active);
+  for (auto& r : s.slotRemaining)
+    r.store(0);
+  std::vector<char> active(s.nScenes, 0);
+  for (int sc : s.slotScene)
+    active[sc] = 1;
+  s.pools.assign(num_groups, std::vector<int>());
+  int k = 0;
+  for (int sc = 0; sc < s.nScenes; ++sc)
+    if (!active[sc])
+      s.pools[k++ % num_groups].push_back(sc);
+  for (int e = 0; e < s.nEnvs; ++e) {
+    s.envs[e].slot = e / s.perSlot;
+    s.envs[e].scene = s.slotScene[s.envs[e].slot];
+    s.envs[e].epoch = 0;
+  }
+  swapPass(s, 0, s.nEnvs);
+  s.numSwaps = 0;
+  return 0;
+}
+
+// scene of every environment right now, and the moves started since set-up
+uint64_t osim_scenes(void* h, int* env_scene) {
+  Sim& s = *static_cast<Sim*>(h);
+  for (int e = 0; e < s.nEnvs; ++e)
+    env_scene[e] = s.envs[e].scene;
+  return s.numSwaps;
 }
 
 float* osim_rewards(void* h) { return static_cast<Sim*>(h)->rewards.data(); }

@@ -176,6 +176,9 @@ def sim_lib():
             getattr(lib, name).argtypes = [C.c_void_p]
         lib.osim_masks.restype = C.POINTER(C.c_uint8)
         lib.osim_masks.argtypes = [C.c_void_p]
+        lib.osim_enable_rotation.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_int)]
+        lib.osim_scenes.restype = C.c_uint64
+        lib.osim_scenes.argtypes = [C.c_void_p, C.POINTER(C.c_int)]
         lib.osim_get_state.argtypes = [C.c_void_p, _fp, _u32p]
         lib.osim_counters.argtypes = [C.c_void_p, _u64p]
         lib.osim_philox.argtypes = [C.c_uint32] * 6 + [_u32p]
@@ -196,7 +199,10 @@ class OracleSim:
 
     TASKS = {"pointnav": 0, "flee": 1, "exploration": 2}
 
-    def __init__(self, scenes, num_envs, seed, env_scene=None, threads=1, task="pointnav"):
+    def __init__(self, scenes, num_envs, seed, env_scene=None, threads=1, task="pointnav",
+                 active_scenes=None, num_groups=1):
+        """``active_scenes``: turns scene rotation on -- the scenes in use first, one per slot of
+        ``num_envs / len(active_scenes)`` consecutive environments; the others rotate in."""
         lib = sim_lib()
         self._lib = lib
         self.num_envs = num_envs
@@ -216,6 +222,11 @@ class OracleSim:
                                              C.c_uint64(seed), threads, self.TASKS[task]))
         if not self._h.value:
             raise RuntimeError("oracle simulator creation failed")
+        if active_scenes is not None:
+            act = np.ascontiguousarray(active_scenes, np.int32)
+            if lib.osim_enable_rotation(self._h, len(act), num_groups,
+                                        act.ctypes.data_as(C.POINTER(C.c_int))) != 0:
+                raise RuntimeError("oracle: bad scene rotation parameters")
         n = num_envs
         self.rewards = np.ctypeslib.as_array(lib.osim_rewards(self._h), (n,))
         self.masks = np.ctypeslib.as_array(lib.osim_masks(self._h), (n,))
@@ -254,6 +265,12 @@ class OracleSim:
                for k, (a, b) in _STATE_F_SLICES.items()}
         out.update({k: u[:, i].copy() for k, i in _STATE_U.items()})
         return out
+
+    def scenes(self):
+        """(scene of every environment, scene moves started since set-up)."""
+        out = np.zeros(self.num_envs, np.int32)
+        n = self._lib.osim_scenes(self._h, out.ctypes.data_as(C.POINTER(C.c_int)))
+        return out, int(n)
 
     def counters(self):
         c = np.zeros(3, np.uint64)

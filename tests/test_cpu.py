@@ -425,6 +425,30 @@ def test_two_rank_sharding_gloo():
     assert res[0][4] != res[1][4]
 
 
+def test_shard_plan_partitions_a_fixed_global_batch():
+    from bps_nav_b200 import dist_utils
+    # benchmark config 3: 16384 environments over 16 scenes, on 1 / 2 / 4 / 8 ranks
+    for world in (1, 2, 4, 8):
+        seen_envs, seen_scenes = [], set()
+        for rank in range(world):
+            first, count, scene_ids, env_scene = dist_utils.shard_plan(16384, 16, rank, world)
+            assert count == 16384 // world and first == rank * count
+            assert len(scene_ids) == 16 // world and len(env_scene) == count
+            # every environment keeps the scene it has in the global batch
+            assert all(scene_ids[env_scene[i]] == (first + i) // 1024 for i in range(0, count, 97))
+            seen_envs.extend(range(first, first + count))
+            seen_scenes.update(scene_ids)
+        assert seen_envs == list(range(16384)) and seen_scenes == set(range(16))
+    # more ranks than scenes: ranks share a scene, each with its part of the environments
+    first, count, scene_ids, env_scene = dist_utils.shard_plan(4096, 2, 3, 8)
+    assert (first, count, scene_ids) == (1536, 512, [0]) and set(env_scene) == {0}
+    # a block that straddles two scenes
+    first, count, scene_ids, env_scene = dist_utils.shard_plan(600, 3, 1, 2)
+    assert scene_ids == [1, 2] and env_scene.count(0) == 100 and env_scene.count(1) == 200
+    with pytest.raises(ValueError):
+        dist_utils.shard_plan(1000, 16, 0, 3)
+
+
 def test_depth_oracle_known_answers():
     """The CPU restatement of the depth sensor on a scene whose image is known in closed form."""
     from oracle import pyoracle

@@ -27,15 +27,21 @@ def _close(a, b, rel, abs_=0.0):
 
 
 def _compare_run(scene_names, n, steps, seed, mix, threads=8, check_state_every=16,
-                 search_count=None, want_status=0, **gen_kw):
+                 search_count=None, want_status=0, num_active=None, visited=None, **gen_kw):
+    """Steps the CUDA generator and the CPU oracle side by side and compares every output of
+    every step.  ``num_active``: fewer scenes in use than the list has, the others rotate in;
+    ``visited`` (a set) then collects the scenes the environments were seen in."""
     from bps_nav_b200 import bps_sim
     scenes = [load_scene(s) for s in scene_names]
-    gen = bps_sim.PointNavRolloutGenerator.from_scenes(scenes, n, seed=seed, **gen_kw)
+    gen = bps_sim.PointNavRolloutGenerator.from_scenes(scenes, n, seed=seed,
+                                                       num_active_scenes=num_active, **gen_kw)
     if search_count is not None:
         for g in range(gen.num_groups):
             gen.debug_set_search_count(g, search_count)
     osim = pyoracle.OracleSim([(scene_path(s), sc.episodes) for s, sc in zip(scene_names, scenes)],
-                              n, seed, threads=threads)
+                              n, seed, threads=threads,
+                              active_scenes=gen._active_scenes if num_active else None,
+                              num_groups=gen.num_groups)
     groups = gen.num_groups
     B = gen.envs_per_group
     for g in range(groups):
@@ -69,6 +75,18 @@ def _compare_run(scene_names, n, steps, seed, mix, threads=8, check_state_every=
             for name in ("position", "rotation", "nav_position"):
                 got = np.concatenate([gen.tensor(g, name).cpu().numpy().T for g in range(groups)])
                 assert _close(got, st[name], 0, 1e-5).all(), f"{name}, step {t}"
+            if num_active:
+                want_scene, want_swaps = osim.scenes()
+                got_scene = np.concatenate([gen.tensor(g, "scene").cpu().numpy()
+                                            for g in range(groups)])
+                assert np.array_equal(got_scene, want_scene), f"scene of the envs, step {t}"
+                rate, in_use, per_scene = gen.swap_stats
+                assert abs(rate - 100.0 * want_swaps / ((t + 1) * n)) < 1e-9
+                per_group = [len(set(want_scene[g * B:(g + 1) * B])) for g in range(groups)]
+                assert in_use == sum(per_group)
+                assert abs(per_scene - sum(B / k for k in per_group)) < 1e-3
+                if visited is not None:
+                    visited.update(int(x) for x in want_scene)
     status = np.concatenate([gen.tensor(g, "status").cpu().numpy().view(np.uint32)
                              for g in range(groups)])
     ties = int(((status >> 8) & 1).sum())
@@ -166,6 +184,32 @@ def test_mixed_scene_batch_large_enough_for_the_throughput_plan():
     # than 8 slabs (m01, m04, m06, m07) to global memory
     names = [f"m{i:02d}" for i in range(16)]
     _compare_run(names, 12288, 24, seed=9, mix="uniform", check_state_every=8)
+
+
+def test_scenes_rotate_through_the_whole_dataset():
+    """32 scenes, 8 in use at a time: every slot of 64 environments moves on to a waiting scene
+    whenever all of its environments have arrived, each environment following at the end of
+    its episode (simulator/simulator.cpp:1063-1154, 1284-1308, 1636-1640).  Every step is
+    compared with the oracle, the environments' scenes too, and every scene must get its turn."""
+    names = [f"m{i:02d}" for i in range(16)] * 2
+    seen = set()
+    _compare_run(names, 512, 400, seed=71, mix="uniform", threads=16, check_state_every=8,
+                 num_active=8, visited=seen)
+    assert seen == set(range(32)), sorted(set(range(32)) - seen)
+
+
+def test_scenes_rotate_with_two_groups_and_mixed_memory():
+    # two groups, each rotating through its own share of the waiting scenes; a 96 KB
+    # shared-memory budget puts the larger scenes in global memory, so slots change between
+    # shared and global memory as they move from scene to scene
+    names = ["c0", "m04", "m13", "c1", "m15", "m07", "m02", "m10", "m01", "m14"]
+    seen = set()
+    _compare_run(names, 256, 300, seed=72, mix="uniform", threads=16, check_state_every=10,
+                 num_active=4, visited=seen, double_buffered=True, small_smem=True)
+    assert len(seen) == len(names)
+    # long episodes: slots stay between two scenes for many steps
+    _compare_run(names, 128, 400, seed=73, mix="policy", threads=16, check_state_every=20,
+                 num_active=2, global_memory=True)
 
 
 def test_odd_batch_sizes():
@@ -283,8 +327,11 @@ def test_depth_sensor_matches_cpu_restatement():
         for t in range(40):
             gen.step(0, actions[t])  # step() renders, like the reference's
         gen.wait_for_frame(0)
-        img = bps_pytorch.make_depth_tensor(gen.depth(0), 0, n, res).cpu().numpy()
-        assert img.shape == (n, res[1], res[0])
+        t = bps_pytorch.make_depth_tensor(gen.depth(0), 0, n, res)
+        # the reference's order of dimensions (simulator/pytorch.cpp:36): [B, res[0], res[1]]
+        # with res = [width, height]; the memory is `height` rows of `width` pixels
+        assert tuple(t.shape) == (n, res[0], res[1])
+        img = t.reshape(n, res[1], res[0]).cpu().numpy()
         pos = gen.tensor(0, "position").cpu().numpy().T
         rot = gen.tensor(0, "rotation").cpu().numpy().T
         scn = gen.tensor(0, "scene").cpu().numpy().view(np.uint32)
