@@ -186,6 +186,25 @@ def test_mixed_scene_batch_large_enough_for_the_throughput_plan():
     _compare_run(names, 12288, 24, seed=9, mix="uniform", check_state_every=8)
 
 
+def test_benchmark_config1_at_full_length():
+    # config 1 as the benchmark states it: scene c1, 4096 environments, 1000 steps, uniform
+    # actions, every step of every environment compared; then the policy-like mix (long episodes)
+    _compare_run(["c1"], 4096, 1000, seed=101, mix="uniform", threads=16, check_state_every=100)
+    _compare_run(["c1"], 4096, 500, seed=102, mix="policy", threads=16, check_state_every=100)
+
+
+def test_benchmark_config3_at_full_length():
+    # config 3: 16 mixed floor plans, 16384 environments, 2000 steps
+    names = [f"m{i:02d}" for i in range(16)]
+    _compare_run(names, 16384, 2000, seed=103, mix="uniform", threads=16, check_state_every=250)
+
+
+def test_dense_scene_at_benchmark_batch():
+    # the 16 407-polygon plan at the headline batch size
+    _compare_run(["d0"], 4096, 150, seed=104, mix="uniform", threads=16, check_state_every=50)
+    _compare_run(["d0"], 4096, 100, seed=105, mix="policy", threads=16, check_state_every=50)
+
+
 def test_scenes_rotate_through_the_whole_dataset():
     """32 scenes, 8 in use at a time: every slot of 64 environments moves on to a waiting scene
     whenever all of its environments have arrived, each environment following at the end of
