@@ -11,17 +11,24 @@ Default workload: benchmark config 1 -- one 50x50 m synthetic floor plan with 60
 (Recast single-tile build: 446 polygons), 4096 environments per GPU, i.i.d. uniform actions over
 {stop, forward, left, right}.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload c4]
 
-Lines printed (rank 0, one JSON object):
-  value     device-resident arm: actions already in HBM, results stay in HBM, CUDA-event timed
-  e2e       same metric through the reference-shaped host API: numpy actions in, numpy
-            reward / mask / info / polar out every step (pinned-memory H2D + D2H inside the timed
-            region)
-  roofline  for the kernel with the largest share of step time, from CUDA events recorded around
-            every launch in a separate pass
-  cpu_baseline  the CPU oracle (the reference's compiled PathFinder driven by the simulator
-            restatement, all host cores) on a bounded sample of the same workload
+Keys of the line printed by rank 0 (one JSON object):
+  value          device-resident arm: actions already in HBM, results stay in HBM, CUDA-event timed
+  e2e            the same metric through the reference-shaped host API: numpy actions in, numpy
+                 reward / mask / info / polar out every step (host <-> device traffic inside the
+                 timed region).  Measured twice -- one group, and the two groups of a
+                 double-buffered generator stepped alternately as the reference's trainer drives
+                 it -- and the faster one is reported (e2e.variants holds both)
+  roofline       for the kernel with the largest share of step time
+  cpu_baseline   the CPU oracle (the reference's compiled PathFinder driven by the simulator
+                 restatement, all host cores) on a bounded sample of the same workload
+  dense_scene    config 1 read with the polygon count its description quotes (16 407 polygons)
+  large_batch    the headline window at 32768 environments per GPU
+  c2             benchmark config 2: GAE at T = 32, N = 16384
+  shard          benchmark config 3: a fixed global batch (16 scenes, 16384 environments) block-
+                 partitioned over the ranks, each rank loading only the scenes of its block
+  double_buffered  the headline window with the environments in two groups on two streams
 """
 import argparse
 import json
@@ -40,14 +47,15 @@ T_ROLLOUT = 32
 GAMMA, TAU = 0.99, 0.95
 # algorithmic bytes (state columns read + written, outputs written) per unit of each launch
 BYTES_PER_ENV_STEP = 177          # move + sensor + reward path, per environment step
-BYTES_PER_GEO_QUERY = 44          # list entry 4, scene 4, two points 24, two refs 8 -> distance 4
 BYTES_PER_GAE_ELEM = 25.2         # scan 17.2 + normalise 8 per (t, env)
 L2_FLUSH_BYTES = 256 << 20
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu capture
-# (profiles/k_step_warp_config1_ncu_full.md); only meaningful for the default workload
 LARGE_BATCH_ENVS = 32768
 DENSE_SCENE = "d0"
-NCU_TRAFFIC_BYTES = {("c1", 4096, "uniform", "k_step"): 0.87e6}
+C2_T, C2_N = 32, 16384
+C3_ENVS, C3_SCENES = 16384, [f"m{i:02d}" for i in range(16)]
+# dram__bytes_read.sum + dram__bytes_write.sum of one k_step launch, from an ncu capture of this
+# script's default workload (one kernel, three launches); other workloads report null
+NCU_TRAFFIC_BYTES = {("c1", 4096, "uniform"): 0.87e6}
 
 
 def parse_args():
@@ -56,7 +64,9 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--envs", type=int, default=4096, help="environments per GPU")
+    ap.add_argument("--workload", default="c1", choices=["c1", "c4"],
+                    help="c1: the headline (config 1); c4: full-box DD-PPO step harness")
+    ap.add_argument("--envs", type=int, default=None, help="environments per GPU")
     ap.add_argument("--scene", default="c1")
     ap.add_argument("--mix", default="uniform", choices=["uniform", "policy"])
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
@@ -64,7 +74,27 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-large-batch", action="store_true")
     ap.add_argument("--no-depth", action="store_true")
-    return ap.parse_args()
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the c2 / shard / double-buffered blocks")
+    args = ap.parse_args()
+    if args.envs is None:
+        args.envs = 32768 if args.workload == "c4" else 4096
+    return args
+
+
+def scene_polys(name):
+    with open(scene_files(name)[0].replace(".navmesh", ".scene.json")) as fh:
+        return int(json.load(fh)["num_polys"])
+
+
+def workload_string(args):
+    """The same words in both arms (the reference arm has no GPU to ask about the scene)."""
+    names = args.scene.split(",")
+    polys = [scene_polys(nm) for nm in names]
+    what = (f"config1: scene {names[0]} ({polys[0]} polys)" if len(names) == 1 else
+            f"{len(names)} scenes {args.scene} ({min(polys)}-{max(polys)} polys)")
+    return (f"{what}, {args.envs} envs/GPU, one step = T={T_ROLLOUT} sim steps + GAE/normalise, "
+            f"{args.mix} actions")
 
 
 def scene_files(name):
@@ -188,49 +218,49 @@ def measured_peak():
 
 # ------------------------------------------------------------------------------------ CPU arm
 
-def cpu_arm(args, seconds, steps_cap=None):
-    """Times the CPU oracle on the bench workload; returns (env_steps_per_s, details)."""
+def cpu_arm(scene_names, n, mix, seconds=None, windows=None, warmup=0):
+    """Times the CPU oracle on rollout windows of the bench workload (T steps over n
+    environments + numpy GAE per window): `windows` windows after `warmup` untimed ones, or as
+    many as fit into `seconds`.  Returns (env_steps_per_s, details)."""
     from oracle import pyoracle
     if not pyoracle.available():
         raise RuntimeError("oracle libraries missing (oracle/_ref, oracle/_build)")
-    scene_list = [(scene_files(nm)[0], np.load(scene_files(nm)[1])) for nm in args.scene.split(",")]
+    scene_list = [(scene_files(nm)[0], np.load(scene_files(nm)[1])) for nm in scene_names]
     cores = len(os.sched_getaffinity(0))
-    n = args.envs
     sim = pyoracle.OracleSim(scene_list, n, seed=1, threads=cores)
     sim.reset()
-    chunk = T_ROLLOUT
-    rewards = np.zeros((T_ROLLOUT + 1, n), np.float32)
-    masks = np.ones((T_ROLLOUT + 1, n), bool)
-    values = np.random.default_rng(0).standard_normal((T_ROLLOUT + 1, n)).astype(np.float32)
-    sim.run(draw_actions((8, n), args.mix, 99))  # warm-up
-    done_steps = 0
-    t0 = time.perf_counter()
-    k = 0
-    while True:
-        acts = draw_actions((chunk, n), args.mix, 1000 + k)
+    T = T_ROLLOUT
+    rewards = np.zeros((T + 1, n), np.float32)
+    masks = np.ones((T + 1, n), bool)
+    values = np.random.default_rng(0).standard_normal((T + 1, n)).astype(np.float32)
+
+    def window(k):
+        acts = draw_actions((T, n), mix, 1000 + k)
         ta = time.perf_counter()
-        for t in range(chunk):
+        for t in range(T):
             sim.step(acts[t])
             rewards[t] = sim.rewards
             masks[t + 1] = sim.masks != 0
-        pyoracle.gae_reference(rewards, values, masks, values[T_ROLLOUT], GAMMA, TAU, normalize=True)
-        tb = time.perf_counter()
+        pyoracle.gae_reference(rewards, values, masks, values[T], GAMMA, TAU, normalize=True)
+        return time.perf_counter() - ta
+
+    sim.run(draw_actions((8, n), mix, 99))
+    for k in range(warmup):
+        window(k)
+    busy, k = 0.0, 0
+    while True:
+        busy += window(warmup + k)
         k += 1
-        done_steps += chunk
-        if k == 1:
-            t0 = ta  # exclude the first action draw
-            busy = 0.0
-        busy += tb - ta
-        if busy >= seconds or (steps_cap and k >= steps_cap):
+        if (windows is not None and k >= windows) or (windows is None and busy >= seconds):
             break
     sim.close()
-    rate = done_steps * n / busy
+    rate = k * T * n / busy
     return rate, {"cores": cores, "windows": k, "seconds": busy,
-                  "sample": f"{k} windows of {T_ROLLOUT} steps x {n} envs on scene {args.scene} "
-                            f"({args.mix} actions) + numpy GAE per window; simulator control flow = "
-                            "oracle/oracle_sim.cpp restatement, every navmesh query = the "
-                            "reference's compiled PathFinder (oracle/_ref/libref_nav.so), one "
-                            "PathFinder replica per thread"}
+                  "sample": f"{k} windows of {T} steps x {n} envs on scene "
+                            f"{','.join(scene_names)} ({mix} actions) + numpy GAE per window; "
+                            "simulator control flow = oracle/oracle_sim.cpp restatement, every "
+                            "navmesh query = the reference's compiled PathFinder "
+                            "(oracle/_ref/libref_nav.so), one PathFinder replica per thread"}
 
 
 def cpu_microbench(args, seconds=3.0):
@@ -292,22 +322,54 @@ def torch_gae_restatement(rewards, value_preds, masks, returns, next_value, T, g
     return (adv - adv.mean()) / (adv.std() + 1e-5)
 
 
+def reference_compute_returns():
+    """The reference's own RolloutStorage class (bps_nav/common/rollout_storage.py), loaded by
+    file path when the bps-nav tree is on this machine; None otherwise."""
+    from oracle import pyoracle
+    root = pyoracle.reference_root()
+    if not root:
+        return None
+    import importlib.util
+    import types
+    common = os.path.join(root, "bps_nav", "common")
+    for pkg in ("bps_nav", "bps_nav.common"):
+        if pkg not in sys.modules:
+            sys.modules[pkg] = types.ModuleType(pkg)
+            sys.modules[pkg].__path__ = []
+    for mod in ("tree_utils", "rollout_storage"):
+        spec = importlib.util.spec_from_file_location(f"bps_nav.common.{mod}",
+                                                      os.path.join(common, f"{mod}.py"))
+        m = importlib.util.module_from_spec(spec)
+        sys.modules[f"bps_nav.common.{mod}"] = m
+        spec.loader.exec_module(m)
+    return sys.modules["bps_nav.common.rollout_storage"].RolloutStorage
+
+
 def run_reference(args):
+    """The reference arm: the same workload on the host cores.  Under torchrun only rank 0 works
+    (the whole job's environments), the other ranks leave at once."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     t_start = time.perf_counter()
-    per_window_budget = max(args.cpu_seconds, 5.0)
-    args.envs = args.envs * max(args.gpus, 1)  # the whole job's environments on the host cores
-    rate, d = cpu_arm(args, per_window_budget, steps_cap=args.steps + args.warmup)
+    if args.workload == "c4":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "config 4 needs the reference's renderer (bps3D / Vulkan): unavailable "
+                          "on this box"}), flush=True)
+        return
+    K, W = args.steps, max(args.warmup, 0)
+    n_job = args.envs * max(args.gpus, 1)  # the whole job's environments on the host cores
+    rate, d = cpu_arm(args.scene.split(","), n_job, args.mix, windows=K, warmup=W)
     ms = 1000.0 * d["seconds"] / max(d["windows"], 1)
     line = {
         "impl": "reference", "metric": "env_steps_per_sec", "value": rate, "unit": "env-steps/s",
-        "n_gpus": args.gpus, "steps": d["windows"], "warmup": 0, "ms_per_step": ms,
+        "n_gpus": args.gpus, "steps": K, "warmup": W, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": f"config1: scene {args.scene}, {args.envs} envs, T={T_ROLLOUT} "
-                               f"rollout + GAE, {args.mix} actions", "l2": "n/a (CPU)"},
+        "config": {"workload": workload_string(args), "envs_per_gpu": args.envs,
+                   "rollout_T": T_ROLLOUT},
+        "measurement": {"l2": "n/a (CPU)",
+                        "timing": "host wall clock around each window, summed"},
         "cpu_baseline": {"value": rate, "unit": "env-steps/s", "cores": d["cores"],
                          "kind": "reference", "sample": d["sample"]},
         "e2e": {"value": rate, "unit": "env-steps/s", "h2d_bytes_per_step": 0,
@@ -334,12 +396,16 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
+    def load(nm):
+        return Scene(scene_files(nm)[0], np.load(scene_files(nm)[1]), f"{nm}.glb")
+
     names = args.scene.split(",")
-    scenes = [Scene(scene_files(nm)[0], np.load(scene_files(nm)[1]), f"{nm}.glb") for nm in names]
+    scenes = [load(nm) for nm in names]
     scene = scenes[0]
     if args.envs % len(scenes):
         raise SystemExit("--envs must be a multiple of the number of scenes")
     N, T, K, W = args.envs, T_ROLLOUT, args.steps, max(args.warmup, 3)
+    peak, peak_src = measured_peak()
 
     def barrier():
         if world > 1:
@@ -349,164 +415,266 @@ def run_ours(args):
     def max_over_ranks(x):
         return dist_utils.max_over_ranks(x, dev)
 
-    rewards = torch.zeros(T + 1, N, 1, device=dev)
-    values = torch.randn(T + 1, N, 1, device=dev)
-    next_value = torch.randn(N, 1, device=dev)
-    masks = torch.ones(T + 1, N, 1, dtype=torch.bool, device=dev)
-    returns = torch.zeros(T + 1, N, 1, device=dev)
-    adv = torch.empty(T, N, 1, device=dev)
-    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+    class Storage:
+        """Rollout tensors of one group, laid out as the reference's storage lays them out."""
 
-    # ---------------- device-resident arm
-    gen = bps_sim.PointNavRolloutGenerator.from_scenes(scenes, N, gpu_id=local,
-                                                       seed=dist_utils.shard_seed(1000, rank, N),
-                                                       host_mirrors=False)
-    info = gen.scene_info(0)
-    polys = [gen.scene_info(i)["num_polys"] for i in range(len(scenes))]
-    gen.reset(0)
-    acts = torch.from_numpy(draw_actions(((W + K) * T, N), args.mix, 7 + rank)).to(dev)
-    r_view = gen.tensor(0, "reward")
-    m_view = gen.tensor(0, "mask")
+        def __init__(self, n):
+            self.n = n
+            self.rewards = torch.zeros(T + 1, n, 1, device=dev)
+            self.values = torch.randn(T + 1, n, 1, device=dev)
+            self.next_value = torch.randn(n, 1, device=dev)
+            self.masks = torch.ones(T + 1, n, 1, dtype=torch.bool, device=dev)
+            self.returns = torch.zeros(T + 1, n, 1, device=dev)
+            self.adv = torch.empty(T, n, 1, device=dev)
+            self.rew_rows = [self.rewards[t] for t in range(T)]
+            self.mask_rows = [self.masks[t + 1] for t in range(T)]
 
-    def window(k):
-        base = k * T
-        for t in range(T):
-            # reward / mask of step t land directly in rows t / t+1 of the rollout tensors
-            gen.step_start(0, acts[base + t], reward_out=rewards[t], mask_out=masks[t + 1])
-            gen.step_end(0)
-        rollout.compute_returns(rewards, values, masks, returns, next_value, T, GAMMA, TAU,
-                                advantages=adv, normalize=True)
+        def returns_only(self):
+            rollout.compute_returns(self.rewards, self.values, self.masks, self.returns,
+                                    self.next_value, T, GAMMA, TAU, advantages=self.adv,
+                                    normalize=False)
 
-    for k in range(W):
-        window(k)
-    barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-          for _ in range(K)]
-    t_wall0 = time.perf_counter()
-    for k in range(K):
-        flush.fill_(k & 0xFF)  # evict L2 between timed windows (untimed)
-        ev[k][0].record()
-        window(W + k)
-        ev[k][1].record()
-    barrier()
-    wall = time.perf_counter() - t_wall0
-    clocks = sampler.stop() if rank == 0 else None
-    dev_ms = sum(a.elapsed_time(b) for a, b in ev)
-    dev_ms = max_over_ranks(dev_ms)
-    value = world * N * T * K / (dev_ms / 1000.0)
-    mean_return = float(returns[:T].mean().item())
-
-    # ---------------- per-kernel pass (roofline): CUDA events around every launch
-    gen.profile(0, True)
-    P = min(K, 5)
-    nres = 0.0
-    for k in range(P):
-        for t in range(T):
-            gen.step_start(0, acts[k * T + t])
-            gen.step_end(0)
-            nres += float((m_view == 0).sum().item())
-    kms, ksteps = gen.profile_read(0)
-    gen.profile(0, False)
-    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    g0.record()
-    for _ in range(20):
-        rollout.compute_returns(rewards, values, masks, returns, next_value, T, GAMMA, TAU,
-                                advantages=adv, normalize=True)
-    g1.record()
-    torch.cuda.synchronize()
-    gae_ms = g0.elapsed_time(g1) / 20
-    kms = {k: v / max(ksteps, 1) for k, v in kms.items()}  # ms per launch
-    peak, peak_src = measured_peak()
-    top = max(kms, key=kms.get)
-    resets_per_step = nres / max(ksteps, 1)
-    if args.mix == "uniform":
-        q_step = N * 0.5  # moved (1/4) or stopped (1/4) -> one geodesic query
-    else:
-        q_step = N * 0.61
-    # k_pre touches action 8 + step 8 + rot 32 + pos 12 + goal 12 + polar 8 + outputs/state of
-    # the envs it finishes (~25 + 8); k_step is the per-env step path for listed envs
-    units = {"k_pre": N, "k_step": q_step}
-    per_unit = {"k_pre": 113, "k_step": BYTES_PER_ENV_STEP}
-    alg_bytes = units[top] * per_unit[top]
-    achieved = alg_bytes / (kms[top] * 1e-3) / 1e9
-    step_ms = sum(kms.values())
-    roofline = {
-        "bound": "hbm", "kernel": top, "achieved": achieved, "peak": peak, "unit": "GB/s",
-        "frac": achieved / peak,
-        "traffic": NCU_TRAFFIC_BYTES.get((args.scene, N, args.mix, top)), "peak_source": peak_src,
-        "ms_per_launch": kms[top],
-        "note": "A* is latency/divergence-bound: its algorithmic HBM bytes are tiny by design "
-                "(scratch is L2-resident); see kernels{} for every launch",
-    }
-    kernels = {k: {"ms_per_launch": v, "share": v / step_ms} for k, v in kms.items()}
-    kernels["gae(scan+normalise)"] = {"ms_per_launch": gae_ms,
-                                      "achieved_gbs": T * N * BYTES_PER_GAE_ELEM / (gae_ms * 1e-3) / 1e9}
-    step_roofline = {"achieved": N * BYTES_PER_ENV_STEP / (step_ms * 1e-3) / 1e9, "unit": "GB/s",
-                     "frac": N * BYTES_PER_ENV_STEP / (step_ms * 1e-3) / 1e9 / peak,
-                     "ms_per_step_all_launches": step_ms}
-    gen.close()
-
-    # ---------------- the same device-resident window at the largest per-GPU batch the
-    # benchmark configurations name (32768 environments): reported beside the headline, it
-    # shows the throughput once every warp has several queries to work through
-    def device_window_rate(scene_set, NB, KB, seed0):
-        genb = bps_sim.PointNavRolloutGenerator.from_scenes(
-            scene_set, NB, gpu_id=local, seed=dist_utils.shard_seed(seed0, rank, NB),
-            host_mirrors=False)
-        genb.reset(0)
-        actsb = torch.from_numpy(draw_actions(((1 + KB) * T, NB), args.mix, 11 + rank)).to(dev)
-        rb = torch.zeros(T + 1, NB, 1, device=dev)
-        vb = torch.randn(T + 1, NB, 1, device=dev)
-        nvb = torch.randn(NB, 1, device=dev)
-        mb = torch.ones(T + 1, NB, 1, dtype=torch.bool, device=dev)
-        retb = torch.zeros(T + 1, NB, 1, device=dev)
-        advb = torch.empty(T, NB, 1, device=dev)
-
-        def window_big(k):
-            for t in range(T):
-                genb.step_start(0, actsb[k * T + t], reward_out=rb[t], mask_out=mb[t + 1])
-                genb.step_end(0)
-            rollout.compute_returns(rb, vb, mb, retb, nvb, T, GAMMA, TAU, advantages=advb,
+        def returns_and_normalise(self):
+            rollout.compute_returns(self.rewards, self.values, self.masks, self.returns,
+                                    self.next_value, T, GAMMA, TAU, advantages=self.adv,
                                     normalize=True)
 
-        window_big(0)
-        barrier()
-        b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        b0.record()
-        for k in range(KB):
-            window_big(1 + k)
-        b1.record()
-        barrier()
-        big_ms = max_over_ranks(b0.elapsed_time(b1))
-        genb.close()
-        return world * NB * T * KB / (big_ms / 1000.0)
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
 
+    def device_windows(scene_set, n, windows, warm, seed0, groups=1, sample_clocks=False,
+                       env_scene=None):
+        """The device-resident window (T steps with the step's reward / mask landing in the
+        rollout rows, then GAE + normalisation) timed with CUDA events per window on the launch
+        stream(s), L2 flushed between windows.  With two groups the environments are split
+        between them, each group steps on its own stream and the advantages of the two halves
+        are normalised together.  Returns (env_steps_per_s of the whole job, ms per window,
+        clocks, generator facts)."""
+        gen = bps_sim.PointNavRolloutGenerator.from_scenes(
+            scene_set, n, gpu_id=local, seed=dist_utils.shard_seed(seed0, rank, n),
+            host_mirrors=False, double_buffered=groups == 2, env_scene=env_scene)
+        B = n // groups
+        store = [Storage(B) for _ in range(groups)]
+        streams = [torch.cuda.current_stream()] if groups == 1 else \
+            [torch.cuda.Stream() for _ in range(groups)]
+        for g in range(groups):
+            gen.reset(g)
+        acts = torch.from_numpy(draw_actions(((warm + windows) * T, n), args.mix, 7 + rank)).to(dev)
+        torch.cuda.synchronize()
+
+        def window(k):
+            base = k * T
+            if groups == 1:
+                st = store[0]
+                for t in range(T):
+                    gen.step_start(0, acts[base + t], reward_out=st.rew_rows[t],
+                                   mask_out=st.mask_rows[t])
+                    gen.step_end(0)
+                st.returns_and_normalise()
+                return
+            main = torch.cuda.current_stream()
+            for g in range(groups):
+                streams[g].wait_stream(main)
+            for t in range(T):
+                for g in range(groups):
+                    with torch.cuda.stream(streams[g]):
+                        gen.step_start(g, acts[base + t, g * B:(g + 1) * B],
+                                       reward_out=store[g].rew_rows[t],
+                                       mask_out=store[g].mask_rows[t])
+                        gen.step_end(g)
+            for g in range(groups):
+                with torch.cuda.stream(streams[g]):
+                    store[g].returns_only()
+                main.wait_stream(streams[g])
+            rollout.normalize_advantages([st.adv for st in store])  # torch.cat(advantages, 1)
+
+        for k in range(warm):
+            window(k)
+        barrier()
+        sampler = ClockSampler(local) if sample_clocks and rank == 0 else None
+        if sampler:
+            sampler.start()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+              for _ in range(windows)]
+        t0 = time.perf_counter()
+        for k in range(windows):
+            flush.fill_(k & 0xFF)  # evict L2 between timed windows (untimed)
+            ev[k][0].record()
+            window(warm + k)
+            ev[k][1].record()
+        barrier()
+        wall = time.perf_counter() - t0
+        clocks = sampler.stop() if sampler else None
+        ms = max_over_ranks(sum(a.elapsed_time(b) for a, b in ev))
+        facts = {"wall_s": wall, "mean_return": float(store[0].returns[:T].mean().item()),
+                 "gen": gen, "store": store, "acts": acts}
+        return world * n * T * windows / (ms / 1000.0), ms / windows, clocks, facts
+
+    def kernel_pass(gen, acts, n, windows):
+        """CUDA events around every launch of the step (programmatic dependent launch is off
+        while they are recorded, so the launches do not overlap): ms per launch of each kernel
+        and episode ends per step."""
+        gen.profile(0, True)
+        m_view = gen.tensor(0, "mask")
+        nres = 0.0
+        for k in range(windows):
+            for t in range(T):
+                gen.step_start(0, acts[k * T + t])
+                gen.step_end(0)
+                nres += float((m_view == 0).sum().item())
+        kms, ksteps = gen.profile_read(0)
+        gen.profile(0, False)
+        return {k: v / max(ksteps, 1) for k, v in kms.items()}, nres / max(ksteps, 1)
+
+    def gae_ms(st, reps=20):
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        st.returns_and_normalise()
+        g0.record()
+        for _ in range(reps):
+            st.returns_and_normalise()
+        g1.record()
+        torch.cuda.synchronize()
+        return g0.elapsed_time(g1) / reps
+
+    def step_roofline(kms, ms_window, ms_gae, n, scene_key):
+        """Roofline object of the step kernel.  Its duration is taken from the timed windows:
+        with programmatic dependent launch on, the step kernel is resident from the moment the
+        kernel before it starts (it stages its scene, then waits) until the step is complete, so
+        one launch lasts (window - GAE) / T.  Units: the environments listed for a navmesh
+        query that step (moved or finished: half of them under uniform actions)."""
+        q_step = n * (0.5 if args.mix == "uniform" else 0.61)
+        ms_launch = (ms_window - ms_gae) / T
+        achieved = q_step * BYTES_PER_ENV_STEP / (ms_launch * 1e-3) / 1e9
+        share = kms["k_step"] / max(sum(kms.values()), 1e-9)
+        return {"bound": "hbm", "kernel": "k_step", "achieved": achieved, "peak": peak,
+                "unit": "GB/s", "frac": achieved / peak,
+                "traffic": NCU_TRAFFIC_BYTES.get(scene_key), "peak_source": peak_src,
+                "ms_per_launch": ms_launch, "units_per_launch": q_step,
+                "bytes_per_unit": BYTES_PER_ENV_STEP,
+                "share_of_step_launches_unoverlapped": share,
+                "note": "A* is latency/divergence-bound: its algorithmic HBM bytes are tiny by "
+                        "design (tables and scratch stay on chip or in L2); ms_per_launch = "
+                        "(timed window - GAE) / T, the step kernel's residency with dependent "
+                        "launch on; kernels{} has each launch timed alone"}
+
+    # ---------------- headline: device-resident arm
+    value, ms_window, clocks, facts = device_windows(scenes, N, K, W, 1000, sample_clocks=True)
+    gen, acts, st0 = facts["gen"], facts["acts"], facts["store"][0]
+    info = gen.scene_info(0)
+    kms, resets_per_step = kernel_pass(gen, acts, N, min(K, 5))
+    ms_gae = gae_ms(st0)
+    roofline = step_roofline(kms, ms_window, ms_gae, N, (args.scene, N, args.mix))
+    step_ms = sum(kms.values())
+    kernels = {k: {"ms_per_launch": v, "share": v / step_ms} for k, v in kms.items()}
+    kernels["gae(scan+normalise)"] = {
+        "ms_per_launch": ms_gae, "achieved_gbs": T * N * BYTES_PER_GAE_ELEM / (ms_gae * 1e-3) / 1e9}
+    whole_step = {"achieved": N * BYTES_PER_ENV_STEP / ((ms_window - ms_gae) / T * 1e-3) / 1e9,
+                  "unit": "GB/s"}
+    whole_step["frac"] = whole_step["achieved"] / peak
+    gen.close()
+    mean_return, wall = facts["mean_return"], facts["wall_s"]
+    del facts
+
+    # ---------------- the same window at the largest per-GPU batch the benchmark
+    # configurations name (32768 environments): the throughput once every warp has several
+    # queries to work through
     big = None
     if not args.no_large_batch and N < LARGE_BATCH_ENVS:
-        KB = 3
-        big = {"envs_per_gpu": LARGE_BATCH_ENVS, "windows": KB,
-               "value": device_window_rate(scenes, LARGE_BATCH_ENVS, KB, 2000),
-               "unit": "env-steps/s", "note": "informational; not the headline workload"}
+        v, _, _, f = device_windows(scenes, LARGE_BATCH_ENVS, 3, 1, 2000)
+        f["gen"].close()
+        big = {"envs_per_gpu": LARGE_BATCH_ENVS, "windows": 3, "value": v, "unit": "env-steps/s",
+               "note": "informational; not the headline workload"}
 
-    # ---------------- and on a dense floor plan with the polygon count the description of
-    # config 1 quotes (scene d0: 150 x 150 m, 2500 boxes, 16407 polygons; the tables do not fit
-    # shared memory, so every search runs against global memory)
+    # ---------------- config 1 read with the polygon count its description quotes: scene d0
+    # (150 x 150 m, 2500 boxes, 16407 polygons; the tables do not fit shared memory, so every
+    # search runs against global memory), with its own roofline and its own CPU figure
     dense = None
     if not args.no_large_batch and args.scene == "c1" and os.path.exists(scene_files(DENSE_SCENE)[0]):
-        dn, de = scene_files(DENSE_SCENE)
-        dscene = [Scene(dn, np.load(de), f"{DENSE_SCENE}.glb")]
-        KB = 3
-        with open(dn.replace(".navmesh", ".scene.json")) as fh:
-            dpolys = json.load(fh)["num_polys"]
-        dense = {"scene": DENSE_SCENE, "polys": dpolys, "windows": KB, "unit": "env-steps/s",
-                 "value": device_window_rate(dscene, N, KB, 3000), "envs_per_gpu": N,
-                 "value_large_batch": device_window_rate(dscene, LARGE_BATCH_ENVS, KB, 3001),
-                 "note": "informational: same device-resident window as the headline, on a dense "
-                         "scene with the polygon count config 1's description quotes "
-                         "(searched in global memory)"}
+        dscene = [load(DENSE_SCENE)]
+        dv, dms, _, f = device_windows(dscene, N, 3, 1, 3000)
+        dkms, _ = kernel_pass(f["gen"], f["acts"], N, 2)
+        dgae = gae_ms(f["store"][0])
+        droof = step_roofline(dkms, dms, dgae, N, (DENSE_SCENE, N, args.mix))
+        f["gen"].close()
+        dbig, _, _, f2 = device_windows(dscene, LARGE_BATCH_ENVS, 3, 1, 3001)
+        f2["gen"].close()
+        dense = {"scene": DENSE_SCENE, "polys": scene_polys(DENSE_SCENE), "windows": 3,
+                 "unit": "env-steps/s", "value": dv, "envs_per_gpu": N, "ms_per_step": dms,
+                 "value_large_batch": dbig, "roofline": droof,
+                 "kernels": {k: {"ms_per_launch": x} for k, x in dkms.items()},
+                 "note": "the '~20k polygons' reading of config 1: same device-resident window "
+                         "as the headline on a dense scene (searched in global memory)"}
+        if rank == 0 and world == 1 and not args.no_cpu_baseline:
+            try:
+                r, d = cpu_arm([DENSE_SCENE], N, args.mix, seconds=min(args.cpu_seconds, 4.0))
+                dense["cpu_baseline"] = {"value": r, "unit": "env-steps/s", "cores": d["cores"],
+                                         "kind": "reference", "sample": d["sample"]}
+                dense["vs_cpu"] = dv / r
+            except Exception as e:  # noqa: BLE001 - a reported figure, not a dependency
+                dense["cpu_baseline"] = {"value": None, "sample": f"unavailable: {e}"}
+
+    # ---------------- the environments in the two groups of a double-buffered generator
+    # (simulator/simulator.cpp:1377-1399), each group on its own stream and half of the SMs
+    dbuf = None
+    if not args.no_extras and N % 2 == 0:
+        v2, ms2, _, f = device_windows(scenes, N, min(K, 10), 2, 1000, groups=2)
+        f["gen"].close()
+        dbuf = {"groups": 2, "envs_per_group": N // 2, "value": v2, "unit": "env-steps/s",
+                "ms_per_step": ms2,
+                "note": "same workload and metric as `value`, environments split over two "
+                        "groups whose steps overlap on the GPU; advantages of the two halves "
+                        "normalised together"}
+
+    # ---------------- benchmark config 2: GAE at T = 32, N = 16384
+    c2 = None
+    if not args.no_extras and rank == 0:
+        st = Storage(C2_N)
+        st.masks.copy_(torch.rand(C2_T + 1, C2_N, 1, device=dev) >= 0.002)
+        st.rewards.normal_()
+        ms = gae_ms(st, reps=50)
+        gbs = C2_T * C2_N * BYTES_PER_GAE_ELEM / (ms * 1e-3) / 1e9
+        c2 = {"T": C2_T, "N": C2_N, "fused_ms": ms, "achieved_gbs": gbs, "frac_of_hbm": gbs / peak,
+              "algorithmic_bytes": C2_T * C2_N * BYTES_PER_GAE_ELEM,
+              "note": "two launches (reverse scan, normalise); launch-latency-bound at this size"}
+        if world == 1:
+            c2.update(gae_reference_times(st, torch))
+
+    # ---------------- benchmark config 3: a fixed global batch block-partitioned over the ranks
+    shard = None
+    if not args.no_extras and all(os.path.exists(scene_files(nm)[0]) for nm in C3_SCENES) and \
+            C3_ENVS % world == 0:
+        first, count, scene_ids, env_scene = dist_utils.shard_plan(C3_ENVS, len(C3_SCENES), rank,
+                                                                   world)
+        sub = [load(C3_SCENES[i]) for i in scene_ids]
+        gen3 = bps_sim.PointNavRolloutGenerator.from_scenes(
+            sub, count, gpu_id=local, seed=dist_utils.shard_seed(4000, rank, count),
+            host_mirrors=False, env_scene=env_scene)
+        st = Storage(count)
+        gen3.reset(0)
+        a3 = torch.from_numpy(draw_actions((4 * T, count), args.mix, 31 + rank)).to(dev)
+
+        def window3(k):
+            for t in range(T):
+                gen3.step_start(0, a3[k * T + t], reward_out=st.rew_rows[t],
+                                mask_out=st.mask_rows[t])
+                gen3.step_end(0)
+            st.returns_and_normalise()
+
+        window3(0)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for k in range(3):
+            window3(1 + k)
+        e1.record()
+        barrier()
+        ms3 = max_over_ranks(e0.elapsed_time(e1))
+        gen3.close()
+        shard = {"global_envs": C3_ENVS, "scenes": len(C3_SCENES), "envs_per_rank": count,
+                 "scenes_per_rank": len(scene_ids), "windows": 3, "scaling": "strong",
+                 "value": C3_ENVS * T * 3 / (ms3 / 1000.0), "unit": "env-steps/s",
+                 "note": "config 3: rank r owns environments [r N/G, (r+1) N/G) of the global "
+                         "batch and loads only the scenes that block touches "
+                         "(dist_utils.shard_plan); no collective on the data path"}
 
     # ---------------- depth sensor (optional observation path; informational)
     depth_info = None
@@ -530,92 +698,94 @@ def run_ours(args):
         nbox = int(np.mean([len(sc.boxes) for sc in scenes]))
         depth_info = {"resolution": [RW, RH], "boxes": nbox, "ms_per_render": d_ms,
                       "rays_per_s": world * N * RW * RH / (d_ms * 1e-3),
-                      "nominal_ray_box_pairs_per_s": world * N * RW * RH * nbox / (d_ms * 1e-3),
                       "image_write_gbs": N * RW * RH * 4 / (d_ms * 1e-3) / 1e9,
-                      "note": "k_depth: analytic ray / box sensor (boxes outside the view frustum are culled per "
-                              "environment, so fewer pairs than nominal are tested), fp32-pipe-bound; not part of "
+                      "note": "k_depth: analytic ray / box sensor, fp32-pipe-bound; not part of "
                               "the headline metric (the benchmark configuration disables rendering)"}
         gend.close()
 
-    # ---------------- end-to-end arm through the reference-shaped host API
+    # ---------------- end-to-end through the reference-shaped host API: numpy actions in (H2D),
+    # numpy reward / mask / info / polar out (D2H) every step; the rollout rows are filled on
+    # the device by the same launch; one device -> host read of the window's result
     e2e = None
     if not args.no_e2e:
-        gen2 = bps_sim.PointNavRolloutGenerator.from_scenes(scenes, N, gpu_id=local,
-                                                           seed=dist_utils.shard_seed(1000, rank, N),
-                                                           host_mirrors=True)
-        gen2.reset(0)
         hacts = draw_actions(((W + K) * T, N), args.mix, 7 + rank)
-        h_rew = gen2.get_rewards(0)
-        h_mask = gen2.get_masks(0)
-        h_polar = gen2.get_polars(0)
-        h_info = gen2.get_infos(0)
-        sink = 0.0
 
-        rew_rows = [rewards[t] for t in range(T)]      # row views of the rollout storage
-        mask_rows = [masks[t + 1] for t in range(T)]
+        def e2e_run(groups):
+            gen2 = bps_sim.PointNavRolloutGenerator.from_scenes(
+                scenes, N, gpu_id=local, seed=dist_utils.shard_seed(1000, rank, N),
+                host_mirrors=True, double_buffered=groups == 2)
+            B = N // groups
+            store = [Storage(B) for _ in range(groups)]
+            views = [(gen2.get_rewards(g), gen2.get_masks(g), gen2.get_infos(g), gen2.get_polars(g))
+                     for g in range(groups)]
+            for g in range(groups):
+                gen2.reset(g)
+            sink = [0.0]
 
-        def window_e2e(k):
-            nonlocal sink
-            base = k * T
-            for t in range(T):
-                # numpy actions in (H2D), numpy reward / mask / info / polar out (D2H) every
-                # step; the rollout rows are filled on the device by the same launch
-                gen2.step_start(0, hacts[base + t], reward_out=rew_rows[t], mask_out=mask_rows[t])
-                gen2.step_end(0)
-                sink += (float(h_polar[0, 0]) + float(h_info["distanceToGoal"][0]) +
-                         float(h_rew[0]) + float(h_mask[0]))
-            rollout.compute_returns(rewards, values, masks, returns, next_value, T, GAMMA, TAU,
-                                    advantages=adv, normalize=True)
-            return float(adv.mean().item())  # device -> host read of the window's result
+            def read(g):
+                r, m, i, p = views[g]
+                sink[0] += (float(p[0, 0]) + float(i["distanceToGoal"][0]) + float(r[0]) +
+                            float(m[0]))
 
-        for k in range(W):
-            window_e2e(k)
-        barrier()
-        t0 = time.perf_counter()
-        for k in range(K):
-            window_e2e(W + k)
-        barrier()
-        e2e_s = max_over_ranks(time.perf_counter() - t0)
+            def window(k):
+                base = k * T
+                if groups == 1:
+                    st = store[0]
+                    for t in range(T):
+                        gen2.step_start(0, hacts[base + t], reward_out=st.rew_rows[t],
+                                        mask_out=st.mask_rows[t])
+                        gen2.step_end(0)
+                        read(0)
+                    st.returns_and_normalise()
+                    return float(st.adv.mean().item())
+                # the trainer's alternation (bps_nav/rl/ppo/ppo_trainer.py:245-275): while one
+                # group's step runs on the GPU the host collects the other group's results and
+                # starts its next step
+                for g in range(groups):
+                    gen2.step_start(g, hacts[base, g * B:(g + 1) * B],
+                                    reward_out=store[g].rew_rows[0], mask_out=store[g].mask_rows[0])
+                for t in range(1, T + 1):
+                    for g in range(groups):
+                        gen2.step_end(g)
+                        read(g)
+                        if t < T:
+                            gen2.step_start(g, hacts[base + t, g * B:(g + 1) * B],
+                                            reward_out=store[g].rew_rows[t],
+                                            mask_out=store[g].mask_rows[t])
+                for st in store:
+                    st.returns_only()
+                rollout.normalize_advantages([st.adv for st in store])
+                return float(store[0].adv.mean().item())
+
+            for k in range(W):
+                window(k)
+            barrier()
+            t0 = time.perf_counter()
+            for k in range(K):
+                window(W + k)
+            barrier()
+            secs = max_over_ranks(time.perf_counter() - t0)
+            gen2.close()
+            return {"value": world * N * T * K / secs, "ms_per_step": 1000 * secs / K}
+
+        variants = {"one_group": e2e_run(1)}
+        if N % 2 == 0:
+            variants["double_buffered"] = e2e_run(2)
+        best = max(variants, key=lambda k: variants[k]["value"])
         h2d = T * N                               # actions cross the bus as one byte each
         d2h = T * (N * 4 + N + N * 12 + N * 8) + 4  # reward, mask, info, polar (+ window result)
-        e2e = {"value": world * N * T * K / e2e_s, "unit": "env-steps/s",
+        e2e = {"value": variants[best]["value"], "unit": "env-steps/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-               "ms_per_step": 1000 * e2e_s / K,
-               "how": "host wall clock, barrier + synchronize on both sides, max over ranks"}
-        gen2.close()
-
-    # ---------------- the reference's GAE formulation (a Python loop of tensor ops) timed on
-    # this GPU and on the host, beside the fused kernels
-    gae_base = None
-    if rank == 0 and world == 1:
-        def med(fn, reps, sync):
-            ts = []
-            for _ in range(reps):
-                if sync:
-                    torch.cuda.synchronize()
-                t0 = time.perf_counter()
-                fn()
-                if sync:
-                    torch.cuda.synchronize()
-                ts.append(time.perf_counter() - t0)
-            return 1000.0 * float(np.median(ts))
-        vals2, ret2 = values.clone(), returns.clone()
-        cuda_ms = med(lambda: torch_gae_restatement(rewards, vals2, masks, ret2, next_value, T,
-                                                    GAMMA, TAU), 30, True)
-        ours_ms = med(lambda: rollout.compute_returns(rewards, values, masks, returns, next_value, T,
-                                                      GAMMA, TAU, advantages=adv, normalize=True),
-                      30, True)
-        cr, cv, cm, cn = rewards.cpu(), values.cpu(), masks.cpu(), next_value.cpu()
-        cret = torch.zeros_like(cr)
-        cpu_ms = med(lambda: torch_gae_restatement(cr, cv, cm, cret, cn, T, GAMMA, TAU), 5, False)
-        gae_base = {"torch_loop_cuda_ms": cuda_ms, "torch_loop_cpu_ms": cpu_ms,
-                    "fused_kernels_ms": ours_ms, "T": T, "N": N,
-                    "how": "median wall time per call incl. launch and synchronize"}
+               "ms_per_step": variants[best]["ms_per_step"], "variant": best,
+               "variants": variants,
+               "how": "host wall clock, barrier + synchronize on both sides, max over ranks; "
+                      "variant = how the host API was driven (one group, or the two groups of a "
+                      "double-buffered generator alternately, the reference trainer's way)"}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         try:
-            rate, d = cpu_arm(args, args.cpu_seconds)
+            rate, d = cpu_arm(names, N, args.mix, seconds=args.cpu_seconds)
             cpu = {"value": rate, "unit": "env-steps/s", "cores": d["cores"], "kind": "reference",
                    "sample": d["sample"], "seconds": d["seconds"]}
             cpu.update(cpu_microbench(args))
@@ -624,23 +794,310 @@ def run_ours(args):
                    "sample": f"unavailable: {e}"}
 
     if rank == 0:
+        launches_per_step = 2
         line = {
             "metric": "env_steps_per_sec", "value": value, "unit": "env-steps/s", "n_gpus": world,
-            "steps": K, "warmup": W, "ms_per_step": dev_ms / K, "higher_is_better": True,
+            "steps": K, "warmup": W, "ms_per_step": ms_window, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": (f"config1: scene {args.scene} ({info['num_polys']} polys, "
-                                    f"{info['num_islands']} islands)" if len(scenes) == 1 else
-                                    f"{len(scenes)} scenes {args.scene} "
-                                    f"({min(polys)}-{max(polys)} polys)") +
-                                   f", {N} envs/GPU, one step = "
-                                   f"T={T} sim steps + fused GAE/normalise, {args.mix} actions",
-                       "envs_per_gpu": N, "rollout_T": T, "polys": info["num_polys"],
-                       "l2": f"flushed between timed windows ({L2_FLUSH_BYTES >> 20} MiB write)",
-                       "timing": "CUDA events per window on the launch stream, summed, max over ranks"},
-            "clocks": clocks, "e2e": e2e, "large_batch": big, "dense_scene": dense, "depth_sensor": depth_info, "roofline": roofline, "roofline_step": step_roofline,
-            "kernels": kernels, "cpu_baseline": cpu, "gae_baseline": gae_base,
-            "gpu_launches": K * (T * 2 + 2), "resets_per_step": resets_per_step,
+            "config": {"workload": workload_string(args), "envs_per_gpu": N, "rollout_T": T},
+            "measurement": {"l2": f"flushed between timed windows ({L2_FLUSH_BYTES >> 20} MiB write)",
+                            "timing": "CUDA events per window on the launch stream, summed, max "
+                                      "over ranks",
+                            "polys": info["num_polys"], "islands": info["num_islands"]},
+            "clocks": clocks, "e2e": e2e, "roofline": roofline, "roofline_whole_step": whole_step,
+            "kernels": kernels, "cpu_baseline": cpu, "dense_scene": dense, "large_batch": big,
+            "double_buffered": dbuf, "c2": c2, "shard": shard, "depth_sensor": depth_info,
+            "gpu_launches": K * (T * launches_per_step + 2), "resets_per_step": resets_per_step,
             "mean_return": mean_return, "wall_s_device_arm": wall,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def gae_reference_times(st, torch):
+    """Config 2 beside the reference: RolloutStorage.compute_returns + the get_advantages
+    formula on CUDA tensors (what the reference's trainer runs) and on CPU tensors -- the
+    reference's own class when the bps-nav tree is on this machine, otherwise the restatement of
+    its loop (labelled).  Median wall time per call including launches and a synchronize."""
+    T, N = C2_T, C2_N
+
+    def med(fn, reps, sync):
+        ts = []
+        for _ in range(reps):
+            if sync:
+                torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            fn()
+            if sync:
+                torch.cuda.synchronize()
+            ts.append(time.perf_counter() - t0)
+        return 1000.0 * float(np.median(ts))
+
+    RS = None
+    try:
+        RS = reference_compute_returns()
+    except Exception:  # noqa: BLE001 - fall back to the restatement
+        RS = None
+    out = {}
+    for where in ("cuda", "cpu"):
+        r, v, m = st.rewards.to(where), st.values.to(where), st.masks.to(where)
+        nv = st.next_value.to(where)
+        if RS is not None:
+            class _Space:
+                spaces = {}
+            rs = RS(T, N, _Space(), None, 8, 1)
+            rs.to(where)
+            sb = rs.storage_buffers
+            sb["rewards"].copy_(r)
+            sb["value_preds"].copy_(v)
+            sb["masks"].copy_(m)
+            rs.step = T
+
+            def fn():
+                rs.compute_returns(nv, True, GAMMA, TAU)
+                a = sb["returns"][:-1] - sb["value_preds"][:-1]
+                return (a - a.mean()) / (a.std() + 1e-5)
+        else:
+            ret = torch.zeros_like(r)
+
+            def fn():
+                return torch_gae_restatement(r, v, m, ret, nv, T, GAMMA, TAU)
+        out[f"reference_loop_{where}_ms"] = med(fn, 20 if where == "cuda" else 5, where == "cuda")
+    out["reference_loop_is"] = ("the reference's RolloutStorage.compute_returns (loaded by path)"
+                                if RS is not None else
+                                "restatement of its per-step tensor-op loop (bps-nav tree absent)")
+    return out
+
+
+def run_c4(args):
+    """Benchmark config 4, a load generator around the simulator path: per GPU 32768
+    environments over 64 scene slots, double-buffered; every step = simulator step + 64 x 64
+    depth render + policy inference on the observations; after T = 32 steps GAE and one PPO
+    epoch (clipped surrogate, value and entropy terms, two minibatches of environments, BPTT
+    through the LSTM) with the gradients all-reduced over NCCL by DistributedDataParallel.
+    The policy is a plain-torch stand-in of the architecture the configuration names -- a
+    ResNet-18 at half width (32 base planes, GroupNorm) on the depth image, the GPS/compass and
+    previous-action embeddings, a 2-layer LSTM of 512 units, actor and critic heads -- with
+    random weights, run in fp16 autocast.  It is not an optimisation target: the figures of
+    interest are the simulator path's rate and its share of the step time
+    (bps_nav/rl/ppo/ppo_trainer.py:200-284 keeps the same split)."""
+    import torch
+    import torch.distributed as dist
+    import torch.nn as nn
+    import torch.nn.functional as F
+
+    from bps_nav_b200 import bps_pytorch, bps_sim, dist_utils, rollout
+    from bps_nav_b200.dataset import Scene
+
+    rank, world, local = dist_utils.rank_info()
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    N, T, K, W = args.envs, T_ROLLOUT, max(1, min(args.steps, 3)), 1
+    SLOTS, RES, MB = 64, (64, 64), 8
+    names = [C3_SCENES[i % len(C3_SCENES)] for i in range(SLOTS)]
+    scenes = [Scene(scene_files(nm)[0], np.load(scene_files(nm)[1]), f"{nm}_{i}.glb")
+              for i, nm in enumerate(names)]
+    gen = bps_sim.PointNavRolloutGenerator.from_scenes(
+        scenes, N, gpu_id=local, seed=dist_utils.shard_seed(5000, rank, N), host_mirrors=False,
+        depth=True, render_resolution=RES, double_buffered=True)
+    B = N // 2
+
+    def block(cin, cout, stride):
+        return nn.ModuleDict({
+            "c1": nn.Conv2d(cin, cout, 3, stride, 1, bias=False), "n1": nn.GroupNorm(16, cout),
+            "c2": nn.Conv2d(cout, cout, 3, 1, 1, bias=False), "n2": nn.GroupNorm(16, cout),
+            "sc": nn.Sequential(nn.Conv2d(cin, cout, 1, stride, bias=False), nn.GroupNorm(16, cout))
+            if stride != 1 or cin != cout else nn.Identity()})
+
+    class Policy(nn.Module):
+        def __init__(self, base=32, hidden=512):
+            super().__init__()
+            self.stem = nn.Sequential(nn.Conv2d(1, base, 7, 2, 3, bias=False), nn.GroupNorm(16, base),
+                                      nn.ReLU(True), nn.MaxPool2d(3, 2, 1))
+            cfg = [(base, base, 1), (base, base, 1), (base, 2 * base, 2), (2 * base, 2 * base, 1),
+                   (2 * base, 4 * base, 2), (4 * base, 4 * base, 1), (4 * base, 8 * base, 2),
+                   (8 * base, 8 * base, 1)]
+            self.blocks = nn.ModuleList([block(*c) for c in cfg])
+            self.compress = nn.Sequential(nn.Conv2d(8 * base, 64, 3, 1, 1, bias=False),
+                                          nn.GroupNorm(1, 64), nn.ReLU(True))
+            self.fc = nn.Sequential(nn.Flatten(), nn.Linear(64 * 2 * 2, hidden), nn.ReLU(True))
+            self.goal = nn.Linear(3, 32)
+            self.prev_action = nn.Embedding(5, 32)
+            self.rnn = nn.LSTM(hidden + 64, hidden, num_layers=2)
+            self.actor = nn.Linear(hidden, 4)
+            self.critic = nn.Linear(hidden, 1)
+
+        def encode(self, depth, polar, prev_a):
+            x = self.stem(depth)
+            for b in self.blocks:
+                y = F.relu(b["n1"](b["c1"](x)))
+                y = b["n2"](b["c2"](y))
+                x = F.relu(y + b["sc"](x))
+            x = self.fc(self.compress(x))
+            g = torch.stack([polar[:, 0], torch.cos(-polar[:, 1]), torch.sin(-polar[:, 1])], -1)
+            return torch.cat([x, self.goal(g.to(x.dtype)), self.prev_action(prev_a)], -1)
+
+        def forward(self, depth, polar, prev_a, hc, masks, steps=1):
+            """depth [steps * n, 1, H, W] ...; hc = (h, c) each [2, n, hidden]; masks [steps * n]
+            (0 where an episode began: the state is reset there)."""
+            f = self.encode(depth, polar, prev_a).view(steps, -1, 512 + 64)
+            m = masks.view(steps, 1, -1, 1).to(f.dtype)
+            outs = []
+            h, c = hc
+            for t in range(steps):
+                o, (h, c) = self.rnn(f[t:t + 1], (h * m[t], c * m[t]))
+                outs.append(o)
+            o = torch.cat(outs, 0).view(-1, 512)
+            return self.actor(o), self.critic(o), (h, c)
+
+    torch.manual_seed(1 + rank)
+    policy = Policy().to(dev)
+    ddp = nn.parallel.DistributedDataParallel(policy, device_ids=[local]) if world > 1 else policy
+    opt = torch.optim.Adam(policy.parameters(), lr=5e-4, eps=1e-5)
+
+    class Buf:
+        def __init__(self):
+            self.depth = torch.zeros(T + 1, B, 1, RES[1], RES[0], dtype=torch.float16, device=dev)
+            self.polar = torch.zeros(T + 1, B, 2, device=dev)
+            self.prev_a = torch.zeros(T + 1, B, dtype=torch.long, device=dev)
+            self.actions = torch.zeros(T, B, dtype=torch.long, device=dev)
+            self.logp = torch.zeros(T, B, device=dev)
+            self.rewards = torch.zeros(T + 1, B, 1, device=dev)
+            self.values = torch.zeros(T + 1, B, 1, device=dev)
+            self.masks = torch.ones(T + 1, B, 1, dtype=torch.bool, device=dev)
+            self.returns = torch.zeros(T + 1, B, 1, device=dev)
+            self.adv = torch.zeros(T, B, 1, device=dev)
+            self.h0 = torch.zeros(2, B, 512, device=dev, dtype=torch.float16)
+            self.c0 = torch.zeros(2, B, 512, device=dev, dtype=torch.float16)
+            self.hc = (self.h0.clone(), self.c0.clone())
+
+    bufs = [Buf(), Buf()]
+    depth_view = [bps_pytorch.make_depth_tensor(gen.depth(g), local, B, RES) for g in range(2)]
+    polar_view = [gen.tensor(g, "polar") for g in range(2)]
+    for g in range(2):
+        gen.reset(g)
+        gen.render(g)
+        bufs[g].depth[0, :, 0] = depth_view[g].clamp(max=10.0) / 10.0
+        bufs[g].polar[0] = polar_view[g]
+    ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
+
+    def rollout_and_learn(timed):
+        t_sim = t_pol = t_learn = 0.0
+        marks = []
+        for g in range(2):
+            b = bufs[g]
+            b.h0.copy_(b.hc[0])
+            b.c0.copy_(b.hc[1])
+        for t in range(T):
+            for g in range(2):
+                b = bufs[g]
+                e0, e1, e2 = ev(), ev(), ev()
+                e0.record()
+                with torch.no_grad(), torch.autocast("cuda", dtype=torch.float16):
+                    logits, value, b.hc = policy(b.depth[t], b.polar[t], b.prev_a[t], b.hc,
+                                                 b.masks[t, :, 0])
+                    dist_ = torch.distributions.Categorical(logits=logits.float())
+                    a = dist_.sample()
+                    b.actions[t] = a
+                    b.logp[t] = dist_.log_prob(a)
+                    b.values[t] = value.float()
+                e1.record()
+                gen.step_start(g, a, reward_out=b.rewards[t], mask_out=b.masks[t + 1],
+                               polar_out=b.polar[t + 1])
+                gen.step_end(g)
+                gen.render(g)
+                e2.record()
+                b.depth[t + 1, :, 0] = depth_view[g].clamp(max=10.0) / 10.0
+                b.prev_a[t + 1] = (a + 1) * b.masks[t + 1, :, 0]
+                marks.append((e0, e1, e2))
+        l0, l1, l2 = ev(), ev(), ev()
+        l0.record()
+        for g in range(2):
+            b = bufs[g]
+            with torch.no_grad(), torch.autocast("cuda", dtype=torch.float16):
+                _, nv, _ = policy(b.depth[T], b.polar[T], b.prev_a[T], b.hc, b.masks[T, :, 0])
+            rollout.compute_returns(b.rewards, b.values, b.masks, b.returns, nv.float(), T, GAMMA,
+                                    TAU, advantages=b.adv, normalize=False)
+        rollout.normalize_advantages([bufs[0].adv, bufs[1].adv])
+        l1.record()
+        per = B // (MB // 2)
+        for g in range(2):
+            b = bufs[g]
+            for s in range(0, B, per):
+                sl = slice(s, s + per)
+                with torch.autocast("cuda", dtype=torch.float16):
+                    logits, value, _ = ddp(
+                        b.depth[:T, sl].reshape(-1, 1, RES[1], RES[0]), b.polar[:T, sl].reshape(-1, 2),
+                        b.prev_a[:T, sl].reshape(-1), (b.h0[:, sl], b.c0[:, sl]),
+                        b.masks[:T, sl, 0].reshape(-1), steps=T)
+                d = torch.distributions.Categorical(logits=logits.float())
+                ratio = torch.exp(d.log_prob(b.actions[:, sl].reshape(-1)) - b.logp[:, sl].reshape(-1))
+                adv = b.adv[:, sl, 0].reshape(-1)
+                act_loss = -torch.min(ratio * adv, ratio.clamp(0.8, 1.2) * adv).mean()
+                v_loss = 0.5 * (b.returns[:T, sl, 0].reshape(-1) - value.float().view(-1)).pow(2).mean()
+                loss = act_loss + 0.5 * v_loss - 0.01 * d.entropy().mean()
+                opt.zero_grad(set_to_none=True)
+                loss.backward()   # DDP all-reduces the gradients over NCCL here
+                nn.utils.clip_grad_norm_(policy.parameters(), 0.25)
+                opt.step()
+        l2.record()
+        for g in range(2):
+            b = bufs[g]
+            b.depth[0].copy_(b.depth[T])
+            b.polar[0].copy_(b.polar[T])
+            b.prev_a[0].copy_(b.prev_a[T])
+            b.masks[0].copy_(b.masks[T])
+        torch.cuda.synchronize()
+        if timed:
+            for e0, e1, e2 in marks:
+                t_pol += e0.elapsed_time(e1)
+                t_sim += e1.elapsed_time(e2)
+            t_learn = l1.elapsed_time(l2)
+            return t_sim, t_pol, l0.elapsed_time(l1), t_learn
+        return None
+
+    for _ in range(W):
+        rollout_and_learn(False)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    tot = np.zeros(4)
+    w0 = time.perf_counter()
+    for _ in range(K):
+        tot += np.array(rollout_and_learn(True))
+    if world > 1:
+        dist.barrier()
+    wall = time.perf_counter() - w0
+    sim_ms, pol_ms, gae_ms_, learn_ms = [dist_utils.max_over_ranks(x, dev) / K for x in tot]
+    wall = dist_utils.max_over_ranks(wall, dev) / K
+    gen.close()
+    if rank == 0:
+        sim_path_ms = sim_ms + gae_ms_
+        step_ms = sim_ms + pol_ms + gae_ms_ + learn_ms
+        line = {
+            "metric": "env_steps_per_sec", "workload": "c4",
+            "value": world * N * T / (sim_path_ms / 1000.0), "unit": "env-steps/s",
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": step_ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": f"config4: {N} envs/GPU over {SLOTS} scene slots (two groups), "
+                                   f"T={T} sim steps + 64x64 depth + GAE feeding a random-init "
+                                   "ResNet-18-half + 2-layer LSTM-512 policy, one PPO epoch of "
+                                   f"{MB} minibatches, DDP gradient all-reduce over NCCL",
+                       "envs_per_gpu": N, "rollout_T": T},
+            "sim_path": {"ms_per_window": sim_path_ms, "share_of_step_time": sim_path_ms / step_ms,
+                         "step_and_render_ms": sim_ms, "gae_and_next_value_ms": gae_ms_,
+                         "what": "simulator steps + depth renders of both groups over T steps "
+                                 "(CUDA events around them) + GAE / advantage normalisation"},
+            "policy_inference_ms": pol_ms, "learner_ms": learn_ms,
+            "whole_window_env_steps_per_s": world * N * T / wall,
+            "wall_ms_per_window": 1000 * wall,
+            "note": "value = the simulator path's own rate (environment steps of the window / "
+                    "time spent in step + render + GAE); the policy and learner are plain "
+                    "PyTorch load, not an optimisation target",
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -651,6 +1108,8 @@ def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "c4":
+        run_c4(args)
     else:
         run_ours(args)
 
