@@ -34,6 +34,7 @@ FLAG_GENERIC_KERNEL = 2
 FLAG_EXACT_HEAP = 4
 FLAG_SMEM_96K = 8
 FLAG_GLOBAL_MEMORY = 16
+FLAG_TWO_LAUNCHES = 32
 TASK_POINTNAV, TASK_FLEE, TASK_EXPLORATION = 0, 1, 2
 MEM_DEVICE, MEM_HOST = 0, 1
 (FIELD_REWARD, FIELD_MASK, FIELD_INFO, FIELD_POLAR, FIELD_POSITION, FIELD_ROTATION, FIELD_GOAL,

@@ -33,6 +33,11 @@ import numpy as np
 from . import _lib as L
 from . import dataset as _dataset
 
+try:  # compiled binding of the per-step calls (csrc/pyext.c); ctypes does the same, slower
+    from . import _bpsn_fast as _fast
+except ImportError:
+    _fast = None
+
 INFO_DTYPE = np.dtype([("success", "<f4"), ("spl", "<f4"), ("distanceToGoal", "<f4")])
 # StepInfo records of the three tasks (simulator/simulator.cpp:738-742, 834-836, 893-895, 1814-1821)
 _TASKS = {
@@ -100,7 +105,7 @@ class _RolloutGenerator:
     def from_scenes(cls, scenes, num_environments, num_active_scenes=None, gpu_id=0,
                     render_resolution=(64, 64), color=False, depth=False, double_buffered=False,
                     seed=0, host_mirrors=True, generic_kernel=False, exact_heap=False,
-                    small_smem=False, global_memory=False, env_scene=None):
+                    small_smem=False, global_memory=False, env_scene=None, two_launches=False):
         """Builds a generator from in-memory ``dataset.Scene`` objects (no JSON involved).
         ``env_scene``: optional explicit scene (index into ``scenes``) of every environment, for
         layouts other than equal consecutive blocks; only with every scene active."""
@@ -109,12 +114,12 @@ class _RolloutGenerator:
             num_active_scenes = len(scenes)
         self._setup(list(scenes), num_environments, num_active_scenes, gpu_id, render_resolution,
                     color, depth, double_buffered, seed, host_mirrors, generic_kernel, exact_heap,
-                    small_smem, global_memory, env_scene)
+                    small_smem, global_memory, env_scene, two_launches)
         return self
 
     def _setup(self, scenes, num_environments, num_active_scenes, gpu_id, render_resolution, color,
                depth, double_buffered, seed, host_mirrors, generic_kernel=False, exact_heap=False,
-               small_smem=False, global_memory=False, env_scene=None):
+               small_smem=False, global_memory=False, env_scene=None, two_launches=False):
         if self._task not in _TASKS:
             raise NotImplementedError(f"{type(self).__name__}: unknown task")
         self._task_id, self._info_dtype = _TASKS[self._task]
@@ -147,7 +152,8 @@ class _RolloutGenerator:
                        (L.FLAG_GENERIC_KERNEL if generic_kernel else 0) |
                        (L.FLAG_EXACT_HEAP if exact_heap else 0) |
                        (L.FLAG_SMEM_96K if small_smem else 0) |
-                       (L.FLAG_GLOBAL_MEMORY if global_memory else 0),
+                       (L.FLAG_GLOBAL_MEMORY if global_memory else 0) |
+                       (L.FLAG_TWO_LAUNCHES if two_launches else 0),
                        task=self._task_id,
                        render_width=self._res[0] if self._depth else 0,
                        render_height=self._res[1] if self._depth else 0,
@@ -176,11 +182,16 @@ class _RolloutGenerator:
             self._lib.bpsn_destroy(self._h)
             self._h = C.c_void_p()
             raise
+        import torch
+        self._hv = self._h.value
+        self._out_cache = {}
+        self._raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None) or (
+            lambda dev: torch.cuda.current_stream(dev).cuda_stream)
         self._group_streams = None
         if num_groups == 2 and host_mirrors:
-            import torch
             with torch.cuda.device(self.gpu_id):
                 self._group_streams = [torch.cuda.Stream() for _ in range(num_groups)]
+            self._group_stream_ptrs = [st.cuda_stream for st in self._group_streams]
         self.envs_per_group = self.num_environments // num_groups
         self.envs_per_scene = self.num_environments // self.num_active_scenes
         self._num_steps_taken = 0
@@ -195,6 +206,7 @@ class _RolloutGenerator:
         if h is not None and h.value:
             self._lib.bpsn_destroy(h)
             self._h = C.c_void_p()
+            self._hv = 0
 
     def __del__(self):
         try:
@@ -234,17 +246,36 @@ class _RolloutGenerator:
         ``[B, 2]`` that also receives the GPS/compass observation (``observations[t + 1]``)."""
         ro = mo = po = None
         if reward_out is not None or mask_out is not None or polar_out is not None:
-            ro, mo, po = self._out_ptrs(reward_out, mask_out, polar_out)
-        if isinstance(actions, np.ndarray):
-            if actions.dtype != np.int64 or not actions.flags.c_contiguous:
-                actions = np.ascontiguousarray(actions, dtype=np.int64)
-            if actions.shape[0] != self.envs_per_group:
-                raise RuntimeError("actions length must equal the number of envs in the group")
-            self._keepalive = [actions, reward_out, mask_out, polar_out]
-            L.check(self._lib.bpsn_step_start_ex(self._h, group_idx,
-                                                 actions.__array_interface__["data"][0],
-                                                 L.MEM_HOST, self._stream(group_idx), ro, mo, po),
-                    self._h)
+            # validated once per set of tensor objects (a trainer passes the same row views
+            # window after window); the entry keeps them alive, so the ids stay theirs
+            key = (id(reward_out), id(mask_out), id(polar_out))
+            hit = self._out_cache.get(key)
+            if hit is None:
+                if len(self._out_cache) > 4096:
+                    self._out_cache.clear()
+                hit = self._out_ptrs(reward_out, mask_out, polar_out) + (
+                    (reward_out, mask_out, polar_out),)
+                self._out_cache[key] = hit
+            ro, mo, po = hit[0], hit[1], hit[2]
+        streams = self._group_streams
+        if streams is not None:
+            stream = self._group_stream_ptrs[group_idx]
+        else:
+            stream = self._raw_stream(self.gpu_id)
+        if type(actions) is np.ndarray:
+            self._keepalive = actions
+            if _fast is not None:
+                rc = _fast.step_start(self._hv, group_idx, actions, self.envs_per_group, stream,
+                                      ro, mo, po)
+            else:
+                if actions.dtype != np.int64 or not actions.flags.c_contiguous:
+                    actions = np.ascontiguousarray(actions, dtype=np.int64)
+                if actions.shape[0] != self.envs_per_group:
+                    raise RuntimeError("actions length must equal the number of envs in the group")
+                self._keepalive = actions
+                rc = self._lib.bpsn_step_start_ex(self._h, group_idx,
+                                                  actions.__array_interface__["data"][0],
+                                                  L.MEM_HOST, stream, ro, mo, po)
         else:
             import torch
             if not (isinstance(actions, torch.Tensor) and actions.is_cuda and
@@ -253,10 +284,15 @@ class _RolloutGenerator:
                                    "int64 tensor")
             if actions.numel() != self.envs_per_group:
                 raise RuntimeError("actions length must equal the number of envs in the group")
-            self._keepalive = [actions, reward_out, mask_out, polar_out]
-            L.check(self._lib.bpsn_step_start_ex(self._h, group_idx, actions.data_ptr(),
-                                                 L.MEM_DEVICE, self._stream(group_idx), ro, mo, po),
-                    self._h)
+            self._keepalive = actions
+            if _fast is not None:
+                rc = _fast.step_start_device(self._hv, group_idx, actions.data_ptr(), stream,
+                                             ro, mo, po)
+            else:
+                rc = self._lib.bpsn_step_start_ex(self._h, group_idx, actions.data_ptr(),
+                                                  L.MEM_DEVICE, stream, ro, mo, po)
+        if rc:
+            L.check(rc, self._h)
         self._num_steps_taken += self.envs_per_group
 
     def _out_ptrs(self, reward_out, mask_out, polar_out):
@@ -276,7 +312,12 @@ class _RolloutGenerator:
         return ro, mo, po
 
     def step_end(self, group_idx):
-        L.check(self._lib.bpsn_step_end(self._h, group_idx), self._h)
+        if _fast is not None:
+            rc = _fast.step_end(self._hv, group_idx)
+        else:
+            rc = self._lib.bpsn_step_end(self._h, group_idx)
+        if rc:
+            L.check(rc, self._h)
 
     def render(self, group_idx):
         """Renders the depth sensor of the group (when the generator was built with

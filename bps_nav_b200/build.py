@@ -32,7 +32,42 @@ def needs_build():
     return any(os.path.getmtime(d) > t for d in deps)
 
 
+def _ext_path():
+    import sysconfig
+    return os.path.join(HERE, "_bpsn_fast" + sysconfig.get_config_var("EXT_SUFFIX"))
+
+
+def build_pyext(force=False):
+    """The CPython binding of the per-step calls (csrc/pyext.c), linked against libbpsn.so in
+    this directory.  Optional: without Python's headers or a C compiler the package uses ctypes
+    for those calls too.  Returns the module's path or None."""
+    import sysconfig
+    out = _ext_path()
+    src = os.path.join(CSRC, "pyext.c")
+    inc = sysconfig.get_paths()["include"]
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if not cc or not os.path.exists(os.path.join(inc, "Python.h")):
+        return None
+    if not force and os.path.exists(out) and os.path.getmtime(out) >= max(
+            os.path.getmtime(src), os.path.getmtime(LIB)):
+        return out
+    cmd = [cc, "-O2", "-fPIC", "-shared", f"-I{inc}", src, f"-L{HERE}", "-l:libbpsn.so",
+           "-Wl,-rpath,$ORIGIN", "-o", out]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        sys.stderr.write("could not build the _bpsn_fast module (ctypes will be used):\n" +
+                         res.stderr)
+        return None
+    return out
+
+
 def build(force=False, verbose=False):
+    lib = _build_lib(force, verbose)
+    build_pyext(force)
+    return lib
+
+
+def _build_lib(force=False, verbose=False):
     if not force and not needs_build():
         return LIB
     cmd = [

@@ -51,6 +51,13 @@ struct Group {
   float* hInfo = nullptr;
   float* hPolar = nullptr;
   volatile uint32_t* hErr = nullptr;  // host view of the device error word (with mirrors)
+  volatile uint32_t* hStepFlag = nullptr;  // host view of the published-step counter
+  bool publish = false;   // the step kernel's last CTA copies the results to the mirrors
+  bool fused = false;     // one launch per step: the step kernel does k_pre's part itself
+  uint32_t stepCounter = 0;
+  uint32_t* dDoneCount = nullptr;
+  uint32_t* dOvList = nullptr;   // one-launch step: per-CTA overflow segments and their headers
+  uint32_t* dOvMeta = nullptr;
   uint8_t* hActions = nullptr;  // pinned, device-mapped staging of host-supplied actions
   const uint8_t* dActions8 = nullptr;  // the same buffer as the device addresses it
   AStarScratch* scratch = nullptr;
@@ -276,7 +283,8 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase, uint32
   const size_t oSlotScene = place(numSlots * u), oSlotPrev = place(numSlots * u),
                oSlotEpoch = place(numSlots * u), oSlotRemaining = place(numSlots * u),
                oSlotSize = place(numSlots * u), oPool = place((poolSize + 4) * u),
-               oSwapCount = place(4 * u);
+               oSwapCount = place(4 * u), oSlotEnvs = place(B * u),
+               oSlotEnvBase = place(numSlots * u);
   g.stateBytes = off;
   BPSN_CUDA(sim, cudaMalloc(&g.stateBlob, off));
   BPSN_CUDA(sim, cudaMemset(g.stateBlob, 0, off));
@@ -333,6 +341,8 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase, uint32
   d.slotSize = reinterpret_cast<uint32_t*>(b + oSlotSize);
   d.pool = reinterpret_cast<uint32_t*>(b + oPool);
   d.swapCount = reinterpret_cast<uint32_t*>(b + oSwapCount);
+  d.slotEnvs = reinterpret_cast<uint32_t*>(b + oSlotEnvs);
+  d.slotEnvBase = reinterpret_cast<uint32_t*>(b + oSlotEnvBase);
   {
     // two work lists per slot, each as long as the slot has environments
     std::vector<uint32_t> base(numLists + 4, 0u), initScene(B);
@@ -359,6 +369,14 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase, uint32
     BPSN_CUDA(sim, up(oSlotPrev, slotScene.data(), u * numSlots));
     BPSN_CUDA(sim, up(oSlotSize, slotSize.data(), u * numSlots));
     BPSN_CUDA(sim, up(oPool, pool.data(), u * poolSize));
+    // the environments ordered by slot (for the step kernel that serves a share of a slot)
+    std::vector<uint32_t> envBase(numSlots, 0u), fill(numSlots, 0u), bySlot(B);
+    for (uint32_t s2 = 1; s2 < numSlots; ++s2)
+      envBase[s2] = envBase[s2 - 1] + slotSize[s2 - 1];
+    for (uint32_t e = 0; e < B; ++e)
+      bySlot[envBase[envSlot[e]] + fill[envSlot[e]]++] = e;
+    BPSN_CUDA(sim, up(oSlotEnvs, bySlot.data(), u * B));
+    BPSN_CUDA(sim, up(oSlotEnvBase, envBase.data(), u * numSlots));
   }
   {
     // Scenes this group can ever work on: those of its slots and, when scenes rotate, the
@@ -376,7 +394,7 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase, uint32
     // first scene, so that every slot's list drains in about the same time.
     const size_t kSlabPerEnvAbove = size_t(512) << 20;  // bytes of per-warp slabs from which on ...
     const size_t kSlabPerEnvBudget = size_t(32) << 30;  // ... and bytes of per-env slabs up to which
-    const size_t kSmemMax = ((sim->cfg.flags & BPSN_FLAG_SMEM_96K) ? 96 : 227) * 1024 - 64;  // per CTA, minus the kernel's static shared memory
+    const size_t kSmemMax = ((sim->cfg.flags & BPSN_FLAG_SMEM_96K) ? 96 : 227) * 1024 - 512;  // per CTA, minus the kernel's static shared memory
     const uint32_t kBlockWarps = 16;
     std::vector<WarpPlan> plan(ns, WarpPlan{16u, 0u, 0u, 0u});
     size_t maxGlobalSlab = 0;
@@ -503,6 +521,26 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase, uint32
       if (ctaMap.empty())
         ctaMap.push_back(make_uint4(0u, 0u, 1u, 0u));
       g.numCtas = static_cast<uint32_t>(ctaMap.size());
+      // One launch per step (k_step_warp<.., kFused>) when every CTA's share of its slot is
+      // small enough for its warps to take about one query each (about half of the
+      // environments need one); larger batches drain a slot's list with all of its CTAs.
+      {
+        uint32_t maxShare = 0;
+        for (const uint4& cm : ctaMap) {
+          const uint32_t share = (slotSize[cm.x] + cm.z - 1) / cm.z;
+          if (share > maxShare)
+            maxShare = share;
+        }
+        g.fused = !rotation && g.warpMode == 0 && !g.anyThreadScene && maxShare <= 2 * kBlockWarps &&
+                  maxShare <= kFusedMaxShare && !(sim->cfg.flags & BPSN_FLAG_TWO_LAUNCHES);
+        if (g.fused) {
+          BPSN_CUDA(sim, cudaMalloc(&g.dOvList, sizeof(uint32_t) * kFusedMaxShare * g.numCtas));
+          BPSN_CUDA(sim, cudaMalloc(&g.dOvMeta, sizeof(uint32_t) * 4 * g.numCtas));
+          BPSN_CUDA(sim, cudaMemset(g.dOvMeta, 0, sizeof(uint32_t) * 4 * g.numCtas));
+          d.ovList = g.dOvList;
+          d.ovMeta = g.dOvMeta;
+        }
+      }
       BPSN_CUDA(sim, cudaMalloc(&g.dCtaMap, sizeof(uint4) * ctaMap.size()));
       BPSN_CUDA(sim, cudaMemcpy(g.dCtaMap, ctaMap.data(), sizeof(uint4) * ctaMap.size(),
                                 cudaMemcpyHostToDevice));
@@ -519,9 +557,11 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase, uint32
         return fail(sim, BPSN_ERR_INVALID_ARG, "step plan: shared memory of a CTA exceeds the limit");
       // The function attribute is the hardware limit whatever this handle's plan asks for: it
       // belongs to the function, so every handle of the process shares it.
-      const int kSmemAttr = 227 * 1024 - 64;
+      const int kSmemAttr = 227 * 1024 - 512;
       if (g.warpMode == 0)
-        BPSN_CUDA(sim, cudaFuncSetAttribute(rotation ? k_step_warp<0, true> : k_step_warp<0, false>,
+        BPSN_CUDA(sim, cudaFuncSetAttribute(rotation   ? k_step_warp<0, true>
+                                            : g.fused  ? k_step_warp<0, false, true>
+                                                       : k_step_warp<0, false>,
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAttr));
       else if (g.warpMode == 2)
         BPSN_CUDA(sim, cudaFuncSetAttribute(rotation ? k_step_warp<2, true> : k_step_warp<2, false>,
@@ -619,10 +659,13 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase, uint32
     // block with the same relative layout lets a step publish them in one copy
     g.outBytes = (oPolar + 2 * B * f) - oReward;
     // mapped: the kernels write the mirrors themselves (GroupDev::hReward ...)
-    // (+ one word behind the arrays: the host-visible copy of the device error flags)
-    BPSN_CUDA(sim, cudaHostAlloc(&g.hOut, g.outBytes + 16, cudaHostAllocMapped));
-    memset(g.hOut, 0, g.outBytes + 16);
-    g.hErr = reinterpret_cast<volatile uint32_t*>(g.hOut + g.outBytes);
+    // (+ two words behind the arrays: the host-visible copy of the device error flags and the
+    // number of the last step whose results were published)
+    const size_t outPadded = alignUp(g.outBytes, 16);
+    BPSN_CUDA(sim, cudaHostAlloc(&g.hOut, outPadded + 32, cudaHostAllocMapped));
+    memset(g.hOut, 0, outPadded + 32);
+    g.hErr = reinterpret_cast<volatile uint32_t*>(g.hOut + outPadded);
+    g.hStepFlag = reinterpret_cast<volatile uint32_t*>(g.hOut + outPadded + 16);
     g.hReward = reinterpret_cast<float*>(g.hOut);
     g.hMask = g.hOut + (oMask - oReward);
     g.hInfo = reinterpret_cast<float*>(g.hOut + (oInfo - oReward));
@@ -634,7 +677,18 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase, uint32
     d.hMask = db + (oMask - oReward);
     d.hInfo = reinterpret_cast<float*>(db + (oInfo - oReward));
     d.hPolar = reinterpret_cast<float*>(db + (oPolar - oReward));
-    d.hErr = reinterpret_cast<uint32_t*>(db + g.outBytes);
+    d.hErr = reinterpret_cast<uint32_t*>(db + outPadded);
+    // one-piece publishing needs the warp step kernel to be the last writer of results
+    g.publish = g.anyWarpScene && !g.anyThreadScene;
+    if (g.publish) {
+      BPSN_CUDA(sim, cudaMalloc(&g.dDoneCount, sizeof(uint32_t)));
+      BPSN_CUDA(sim, cudaMemset(g.dDoneCount, 0, sizeof(uint32_t)));
+      d.pubSrc = reinterpret_cast<const uint4*>(b + oReward);
+      d.pubDst = reinterpret_cast<uint4*>(db);
+      d.pubVec = static_cast<uint32_t>(outPadded / 16);
+      d.doneCount = g.dDoneCount;
+      d.hStepFlag = reinterpret_cast<uint32_t*>(db + outPadded + 16);
+    }
   }
   BPSN_CUDA(sim, cudaEventCreateWithFlags(&g.done, cudaEventDisableTiming));
   return BPSN_OK;
@@ -754,6 +808,9 @@ int32_t bpsn_destroy(bpsn_sim* sim) {
     cudaFree(g.dPlan);
     cudaFree(g.globalSlabs);
     cudaFree(g.dCtaMap);
+    cudaFree(g.dDoneCount);
+    cudaFree(g.dOvList);
+    cudaFree(g.dOvMeta);
     cudaFree(g.depth);
     cudaFreeHost(g.hActions);
     cudaFreeHost(g.hOut);
@@ -1108,6 +1165,14 @@ int32_t bpsn_step_start_ex(bpsn_sim* sim, uint32_t group, const int64_t* actions
   std::swap(g.dev.counts, g.dev.countsNext);
   const bool prof = g.profiling;
   GroupDev gd = g.dev;
+  gd.stepId = ++g.stepCounter;  // (never 0: the headers of the overflow segments start zeroed)
+  if (g.publish) {
+    // the step kernels write device memory only; the last CTA publishes (GroupDev::pubDst)
+    gd.hReward = nullptr;
+    gd.hMask = nullptr;
+    gd.hInfo = nullptr;
+    gd.hPolar = nullptr;
+  }
   gd.rewardOut = reward_out;
   gd.maskOut = mask_out;
   gd.polarOut = polar_out;
@@ -1129,21 +1194,24 @@ int32_t bpsn_step_start_ex(bpsn_sim* sim, uint32_t group, const int64_t* actions
   lc.gridDim = dim3(blocksFor(B, 256));
   lc.blockDim = dim3(256);
   lc.dynamicSmemBytes = 0;
-  BPSN_CUDA(sim, cudaLaunchKernelEx(&lc, k_pre, gd, sim->table, dAct, dAct8, sim->turn, seedLo,
-                                    seedHi));
+  if (!g.fused)
+    BPSN_CUDA(sim, cudaLaunchKernelEx(&lc, k_pre, gd, sim->table, dAct, dAct8, sim->turn, seedLo,
+                                      seedHi));
   if (prof) cudaEventRecord(g.prof[1], s);
   if (g.anyWarpScene) {
     lc.gridDim = dim3(g.numCtas);
     lc.blockDim = dim3(512);
     lc.dynamicSmemBytes = g.geoSmem;
     const bool rot = g.dev.rotation != 0u;
-    auto* kernel = g.warpMode == 0   ? (rot ? k_step_warp<0, true> : k_step_warp<0, false>)
+    auto* kernel = g.fused           ? k_step_warp<0, false, true>
+                   : g.warpMode == 0 ? (rot ? k_step_warp<0, true> : k_step_warp<0, false>)
                    : g.warpMode == 1 ? (rot ? k_step_warp<1, true> : k_step_warp<1, false>)
                                      : (rot ? k_step_warp<2, true> : k_step_warp<2, false>);
     BPSN_CUDA(sim, cudaLaunchKernelEx(&lc, kernel, gd, sim->table,
                                       static_cast<const WarpPlan*>(g.dPlan),
                                       static_cast<const uint4*>(g.dCtaMap), g.fallbackScratch,
-                                      g.globalSlabs, g.globalSlabStride, seedLo, seedHi));
+                                      g.globalSlabs, g.globalSlabStride, seedLo, seedHi, dAct,
+                                      dAct8, sim->turn));
   }
   if (g.anyThreadScene) {  // meshes the warp kernel cannot index (it skips the other scenes)
     if (g.anyWarpScene)
@@ -1216,7 +1284,20 @@ int32_t bpsn_step_end(bpsn_sim* sim, uint32_t group) {
     return fail(sim, BPSN_ERR_STATE, "Simulation already done");
   g.inFlight = false;
   if (sim->cfg.flags & BPSN_FLAG_HOST_MIRRORS) {
-    BPSN_CUDA(sim, cudaEventSynchronize(g.done));
+    bool out = false;
+    if (g.publish) {
+      // The results are complete on the host once the flag shows this step's number (written
+      // behind them, with a system-wide fence in between): poll it for a while before falling
+      // back to the event, which also covers a step that could not publish.
+      const uint32_t want = g.stepCounter;
+      for (int spin = 0; spin < 200000 && !out; ++spin) {
+        out = *g.hStepFlag == want;
+        if (!out)
+          __builtin_ia32_pause();
+      }
+    }
+    if (!out)
+      BPSN_CUDA(sim, cudaEventSynchronize(g.done));
     if (g.hErr && *g.hErr)
       return fail(sim, BPSN_ERR_CUDA,
                   "bpsn_step_end: a step kernel gave up waiting for its scene tables; the "

@@ -32,7 +32,7 @@
 //     An open node that gets a better total (dtNodeQueue::modify) is not
 //     updated in place: a second entry is added and the superseded one is
 //     discarded when it is popped (its total no longer matches the node's).
-//     The exact search is also taken if a lane runs out of entries (96 in all);
+//     The exact search is also taken if a lane runs out of entries (128 in all);
 //   * the up-to-six neighbours of the popped polygon are evaluated by six
 //     lanes at once (portal midpoint, cost, heuristic, skip test, node update).
 //     Two edges leading to the same neighbour produce bit-identical
@@ -53,7 +53,10 @@
 namespace bpsn {
 
 constexpr uint32_t kInfBits = 0x7f800000u;
-constexpr int kOpenSlots = 3;  // register open-list entries per lane (96 per warp)
+#ifndef BPSN_OPEN_SLOTS
+#define BPSN_OPEN_SLOTS 4
+#endif
+constexpr int kOpenSlots = BPSN_OPEN_SLOTS;  // register open-list entries per lane (128 per warp)
 // nodeB.y = parent (16 bits) | kNodeOpen | visit tag (15 bits).  A node belongs to the running
 // search iff its tag is the search's; anything else (zero, or the tag of an earlier search on
 // the same slab) reads as "not visited yet".
@@ -1226,14 +1229,98 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
   return dres;
 }
 
-// The part of k_step_warp after the scene is in place: the warp's loop over list slots.
-// Two instances: tables and slabs in shared memory (the pointers are then known to be
-// shared-memory addresses and the accesses compile to shared-memory instructions) or in
+// Where a warp gets its work-list entries from.  operator() returns false (in every lane)
+// when there is nothing left for this warp.
+//
+// ListSource: a work list in global memory shared by all CTAs of a slot.  Every warp starts on
+// the list slot of its own number; the slots beyond the number of warps that share the list
+// are handed out through a cursor that starts at zero.
+struct ListSource {
+  const uint32_t* list;
+  uint32_t* cursor;
+  uint32_t q;          // first slot of this warp
+  uint32_t gridWarps;  // warps that share the list
+  uint32_t n;
+  bool first;
+  __device__ __forceinline__ bool operator()(int lane, uint32_t* entry) {
+    if (!first) {
+      if (lane == 0)
+        q = gridWarps + atomicAdd(cursor, 1u);
+      q = __shfl_sync(0xffffffffu, q, 0);
+    }
+    first = false;
+    if (q >= n)
+      return false;
+    *entry = list[q];
+    return true;
+  }
+};
+
+// FusedSource: the CTA made its own list (see kFused).  Its first entries, one per warp, stay
+// in shared memory; the ones beyond sit in the CTA's segment of a global array, with a count,
+// a cursor and the number of the step they belong to, and are claimed through the cursor by
+// whichever warp has nothing else to do -- one of the CTA's own or one of a CTA that serves the
+// same slot (the next few in the slot's ring are looked at).  Nobody waits for anybody: a
+// segment that is not marked with this step's number yet is passed over, and its owner's
+// warps drain it themselves at the latest.
+constexpr uint32_t kFusedMaxShare = 64;  // environments per CTA at most
+constexpr uint32_t kStealReach = 8;      // neighbours in the slot's ring a warp looks at
+struct FusedSource {
+  const uint32_t* local;  // shared memory
+  uint32_t nLocal;
+  uint32_t* ovList;       // [CTA][kFusedMaxShare]
+  uint32_t* ovMeta;       // [CTA][4]: count, cursor, step number, -
+  uint32_t ctaBase, rank, slotCtas, stepId;
+  int warp;
+  uint32_t stage;         // 0: own first entry, 1: own segment, 2...: neighbours
+  __device__ __forceinline__ bool operator()(int lane, uint32_t* entry) {
+    if (stage == 0) {
+      stage = 1;
+      if (static_cast<uint32_t>(warp) < nLocal) {
+        *entry = local[warp];
+        return true;
+      }
+    }
+    // One look at the own segment and the next few of the slot's ring, a lane each (one trip
+    // to memory); the first that shows unclaimed entries of this step is tried.  A claim that
+    // loses the race for the last entry sends the warp round once more.
+    for (int tries = 0; tries < 4; ++tries) {
+      const uint32_t k = static_cast<uint32_t>(lane);
+      const bool looks = k <= kStealReach && k < slotCtas;
+      const uint32_t cta = ctaBase + (rank + (looks ? k : 0u)) % slotCtas;
+      uint4 m = make_uint4(0u, 0u, 0u, 0u);
+      if (looks)
+        m = __ldcg(reinterpret_cast<const uint4*>(ovMeta) + cta);
+      const uint32_t has = __ballot_sync(0xffffffffu, looks && m.z == stepId && m.y < m.x);
+      if (!has)
+        return false;
+      const int src = __ffs(has) - 1;
+      uint32_t got = 0xffffffffu;
+      if (lane == src) {
+        volatile uint32_t* meta = ovMeta + 4u * cta;
+        __threadfence();  // the step number was seen: the count and the entries are out
+        const uint32_t count = meta[0];
+        const uint32_t q = atomicAdd(ovMeta + 4u * cta + 1u, 1u);
+        if (q < count)
+          got = *(volatile uint32_t*)(ovList + static_cast<size_t>(cta) * kFusedMaxShare + q);
+      }
+      got = __shfl_sync(0xffffffffu, got, src);
+      if (got != 0xffffffffu) {
+        *entry = got;
+        return true;
+      }
+    }
+    return false;
+  }
+};
+
+// The part of k_step_warp after the scene is in place: the warp's loop over work-list
+// entries.  Two instances: tables and slabs in shared memory (the pointers are then known to
+// be shared-memory addresses and the accesses compile to shared-memory instructions) or in
 // global memory.
-template <bool kGlobal>
+template <bool kGlobal, class Source>
 __device__ __forceinline__ void stepWarpQueries(const GroupDev& g, const SceneTable& st,
-                                                const WarpPlan pl, uint32_t listIdx,
-                                                uint32_t rank, uint32_t slotCtas, uint32_t n,
+                                                const WarpPlan pl, Source next,
                                                 const NavScene& scGlobal,
                                                 uint8_t* globalSlabs, size_t globalSlabStride,
                                                 AStarScratch* fallbackScratch, uint32_t seedLo,
@@ -1280,21 +1367,11 @@ __device__ __forceinline__ void stepWarpQueries(const GroupDev& g, const SceneTa
   const bool slabPerEnv = kGlobal && g.slabPerEnv != 0u;
 
   const uint32_t B = g.B;
-  const uint32_t base = g.listBase[listIdx];
-  uint32_t* cursor = g.counts + g.numLists + listIdx;  // zeroed by the step before
-  // Every warp starts on the list slot of its own number; the slots beyond the number of
-  // warps the slot's CTAs have are handed out through the cursor.
-  const uint32_t gridWarps = slotCtas * static_cast<uint32_t>(warpsPerBlock);
-  uint32_t q = rank * static_cast<uint32_t>(warpsPerBlock) + static_cast<uint32_t>(warp);
-  for (bool first = true;; first = false) {
-    if (!first) {
-      if (lane == 0)
-        q = gridWarps + atomicAdd(cursor, 1u);
-      q = __shfl_sync(0xffffffffu, q, 0);
-    }
-    if (q >= n)
+  (void)warpsPerBlock;
+  for (;;) {
+    uint32_t entry = 0u;
+    if (!next(lane, &entry))
       break;
-    const uint32_t entry = g.geoList[base + q];
     const uint32_t e = entry & kListEnvMask;
     if (kGlobal) {
       const size_t slabIdx =
@@ -1361,13 +1438,23 @@ __device__ __forceinline__ void stepWarpQueries(const GroupDev& g, const SceneTa
 //   kMode 2  both kinds in one grid
 // and each of them for fixed scenes (kRotate false: one list per slot, and which scene the
 // slot has is known before the kernel has to wait for its predecessor) and for rotating ones.
-template <int kMode, bool kRotate>
+// kFused (fixed scenes in shared memory only): the kernel also does the part of the step that
+// needs no navmesh query (preEnv, otherwise the kernel k_pre before this one) for a share of
+// its slot's environments and works off the list of those it has to query itself, from
+// shared memory: one launch per step and no work list in global memory.  For batches in which
+// a CTA's share is small enough for its warps to take one query each; with more, the
+// lists of all CTAs of a slot are better drained together (k_pre + global lists).
+template <int kMode, bool kRotate, bool kFused = false>
 __global__ void __launch_bounds__(512, kMode == 1 ? 2 : 1)
 k_step_warp(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
             const uint4* __restrict__ ctaMap, AStarScratch* __restrict__ fallbackScratch,
             uint8_t* __restrict__ globalSlabs, size_t globalSlabStride, uint32_t seedLo,
-            uint32_t seedHi) {
+            uint32_t seedHi, const int64_t* __restrict__ actions,
+            const uint8_t* __restrict__ actions8, TurnConsts tc) {
+  static_assert(!kFused || (kMode == 0 && !kRotate), "fused: fixed scenes in shared memory");
   extern __shared__ __align__(16) uint8_t smem[];
+  __shared__ uint32_t fusedList[kFused ? kFusedMaxShare : 1];
+  __shared__ uint32_t fusedCount;
   launchDependents();
   // which slot this CTA serves, its number among that slot's CTAs and how many they are
   // (set-up data)
@@ -1443,15 +1530,52 @@ k_step_warp(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
       stagedScene = sc0;
     }
   }
+  // fused: this CTA's share of the slot's environments (set-up data)
+  uint32_t myEnv = 0xffffffffu;
+  if (kFused) {
+    const uint32_t size = g.slotSize[slot];
+    const uint32_t share = (size + slotCtas - 1u) / slotCtas;
+    const uint32_t at = rank * share + threadIdx.x;
+    if (threadIdx.x < share && at < size)
+      myEnv = g.slotEnvs[g.slotEnvBase[slot] + at];
+    if (threadIdx.x == 0)
+      fusedCount = 0u;
+    __syncthreads();
+  }
   // everything below reads what the kernels before this one wrote
   waitForPredecessor();
+  if (kFused) {
+    if (myEnv != 0xffffffffu) {
+      uint32_t entry = 0u, listIdx = 0u;
+      if (preEnv(g, st, myEnv, actions, actions8, tc, seedLo, seedHi, &entry, &listIdx))
+        fusedList[atomicAdd(&fusedCount, 1u)] = entry;
+    }
+    __syncthreads();
+    // entries beyond one per query warp go to this CTA's segment in global memory, where
+    // any warp of the slot's CTAs can claim them (FusedSource)
+    const uint32_t nLocal = min(fusedCount, pl0.warps);
+    const uint32_t nOver = fusedCount - nLocal;
+    if (threadIdx.x < nOver)
+      g.ovList[static_cast<size_t>(blockIdx.x) * kFusedMaxShare + threadIdx.x] =
+          fusedList[nLocal + threadIdx.x];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      volatile uint32_t* meta = g.ovMeta + 4u * blockIdx.x;
+      meta[0] = nOver;
+      meta[1] = 0u;
+      __threadfence();
+      meta[2] = g.stepId;
+    }
+    __syncthreads();  // the CTA's own warps see their segment as published
+  }
 
   constexpr uint32_t kRoles = kRotate ? 2u : 1u;
 #pragma unroll 1
   for (uint32_t role = 0; role < kRoles; ++role) {
     const uint32_t listIdx = 2u * slot + role;
-    const uint32_t n = g.counts[listIdx];
-    if (rank == 0 && threadIdx.x == 0) {  // the next step starts from empty lists
+    // (fused: a CTA without entries of its own may still find some to take over)
+    const uint32_t n = kFused ? 1u : g.counts[listIdx];
+    if (!kFused && rank == 0 && threadIdx.x == 0) {  // the next step starts from empty lists
       g.countsNext[listIdx] = 0u;
       g.countsNext[g.numLists + listIdx] = 0u;
     }
@@ -1482,19 +1606,30 @@ k_step_warp(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
       }
     }
     const int warpsPerBlock = static_cast<int>(pl.warps);  // warps of this CTA that take queries
-    if (rank * static_cast<uint32_t>(warpsPerBlock) >= n || warp >= warpsPerBlock)
+    if (warp >= warpsPerBlock)
       continue;
-#define BPSN_STEP_ARGS g, st, pl, listIdx, rank, slotCtas, n, scGlobal, globalSlabs, \
-                       globalSlabStride, fallbackScratch, seedLo, seedHi
-    if constexpr (kMode == 0) {
-      stepWarpQueries<false>(BPSN_STEP_ARGS);
-    } else if constexpr (kMode == 1) {
-      stepWarpQueries<true>(BPSN_STEP_ARGS);
+#define BPSN_STEP_ARGS scGlobal, globalSlabs, globalSlabStride, fallbackScratch, seedLo, seedHi
+    if constexpr (kFused) {
+      FusedSource src{fusedList, min(fusedCount, pl.warps), g.ovList, g.ovMeta,
+                      blockIdx.x - rank, rank, slotCtas, g.stepId, warp, 0u};
+      stepWarpQueries<false>(g, st, pl, src, BPSN_STEP_ARGS);
     } else {
-      if (inGlobal)
-        stepWarpQueries<true>(BPSN_STEP_ARGS);
-      else
-        stepWarpQueries<false>(BPSN_STEP_ARGS);
+      const uint32_t firstQ =
+          rank * static_cast<uint32_t>(warpsPerBlock) + static_cast<uint32_t>(warp);
+      if (firstQ - static_cast<uint32_t>(warp) >= n)
+        continue;
+      ListSource src{g.geoList + g.listBase[listIdx], g.counts + g.numLists + listIdx, firstQ,
+                     slotCtas * static_cast<uint32_t>(warpsPerBlock), n, true};
+      if constexpr (kMode == 0) {
+        stepWarpQueries<false>(g, st, pl, src, BPSN_STEP_ARGS);
+      } else if constexpr (kMode == 1) {
+        stepWarpQueries<true>(g, st, pl, src, BPSN_STEP_ARGS);
+      } else {
+        if (inGlobal)
+          stepWarpQueries<true>(g, st, pl, src, BPSN_STEP_ARGS);
+        else
+          stepWarpQueries<false>(g, st, pl, src, BPSN_STEP_ARGS);
+      }
     }
 #undef BPSN_STEP_ARGS
   }
@@ -1509,6 +1644,31 @@ k_step_warp(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
       atomicOr(g.errFlags, 1u);
       if (g.hErr)
         *g.hErr = 1u;
+    }
+  }
+  if (g.pubDst) {
+    // The CTA that is through last publishes the step's results (see GroupDev::pubDst).  Every
+    // CTA's stores are fenced before it counts itself, the last one fences again before it
+    // reads them; the results of the environments that needed no query were written by the
+    // kernel before this one.
+    __shared__ uint32_t lastCta;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      const uint32_t before = atomicAdd(g.doneCount, 1u);
+      lastCta = before == gridDim.x - 1u ? 1u : 0u;
+      if (lastCta)
+        *g.doneCount = 0u;  // for the next step
+    }
+    __syncthreads();
+    if (lastCta) {
+      __threadfence();
+      for (uint32_t i = threadIdx.x; i < g.pubVec; i += blockDim.x)
+        g.pubDst[i] = __ldcg(g.pubSrc + i);
+      __threadfence_system();
+      __syncthreads();
+      if (threadIdx.x == 0)
+        *reinterpret_cast<volatile uint32_t*>(g.hStepFlag) = g.stepId;
     }
   }
 }

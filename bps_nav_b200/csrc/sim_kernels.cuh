@@ -101,6 +101,18 @@ struct GroupDev {
   float* hInfo;
   float* hPolar;
   uint32_t* hErr;  // host-visible copy of errFlags[0] (same mapped block), null without mirrors
+  // Publishing the results to the host in one piece: when pubDst is set the step kernels leave
+  // the four mirrors above alone (they are null in the copy of this struct those kernels get);
+  // the CTA of the step kernel that finishes last copies the device block [reward | mask |
+  // info | polar] to its pinned twin with 16-byte stores and then raises *hStepFlag to stepId.
+  // (Thousands of 4-byte stores from single lanes cross the bus as one packet each and cost
+  // the step ~10 us; the same bytes in 128-byte packets take ~2 us.)
+  const uint4* pubSrc;
+  uint4* pubDst;
+  uint32_t pubVec;       // 16-byte pieces to copy
+  uint32_t* doneCount;   // [1] CTAs of the running step kernel that are through (device)
+  uint32_t* hStepFlag;   // mapped host word: number of the last step whose results are out
+  uint32_t stepId;
   // running episode statistics, the device-side form of PPOTrainer._update_stats
   // (bps_nav/rl/ppo/ppo_trainer.py:286-319)
   float* episodeReward;  // [B]     reward accumulated in the current episode
@@ -125,6 +137,10 @@ struct GroupDev {
   uint32_t* slotEpoch;      // [slots] moves started so far
   uint32_t* slotRemaining;  // [slots] environments that still have to follow the current move
   uint32_t* slotSize;       // [slots] environments of the slot
+  uint32_t* slotEnvs;       // [B] the environments ordered by slot (fixed)
+  uint32_t* slotEnvBase;    // [slots] where each slot's environments start in slotEnvs
+  uint32_t* ovList;         // one-launch step: per CTA, the list entries beyond one per warp
+  uint32_t* ovMeta;         // ... and per CTA {count, cursor, step number, -} (geo_warp.cuh)
   uint32_t* pool;           // [poolSize] scenes waiting for a slot
   uint32_t* swapCount;      // [1] moves completed (RolloutGenerator::swapStats, :1412-1424)
   uint32_t numSlots;
@@ -531,14 +547,15 @@ __device__ __forceinline__ void forwardMove(const GroupDev& g, const NavScene& s
              g.goal[2 * B + e]);
 }
 
-__global__ void __launch_bounds__(256)
-k_pre(GroupDev g, SceneTable st, const int64_t* __restrict__ actions,
-      const uint8_t* __restrict__ actions8, TurnConsts tc, uint32_t seedLo, uint32_t seedHi) {
-  launchDependents();
-  waitForPredecessor();
-  const uint32_t e = blockIdx.x * blockDim.x + threadIdx.x;
-  if (e >= g.B)
-    return;
+// The part of a step that needs no navmesh query, for one environment: decode the action,
+// advance the step counter, apply a turn and refresh the GPS/compass.  An environment that
+// neither moved nor finished is complete after this (info / reward / mask written here);
+// otherwise *entry receives its work-list entry and *listIdx its list, and true is returned.
+__device__ __forceinline__ bool preEnv(const GroupDev& g, const SceneTable& st, uint32_t e,
+                                       const int64_t* __restrict__ actions,
+                                       const uint8_t* __restrict__ actions8, const TurnConsts& tc,
+                                       uint32_t seedLo, uint32_t seedHi, uint32_t* entry,
+                                       uint32_t* listIdxOut) {
   const uint32_t B = g.B;
   // host-supplied actions arrive validated and narrowed to one byte each, in pinned
   // host memory that the kernel reads in place (no staging copy in the stream)
@@ -587,12 +604,29 @@ k_pre(GroupDev g, SceneTable st, const int64_t* __restrict__ actions,
     }
     writePolar(g, e, px, py, pz, qx, qy, qz, qw, gx, gy, gz);
   }
-  const bool listed = done || moved;
+  if (done || moved) {
+    // the list entry carries what the step kernel has to know about the action
+    *entry = e | (done ? kListDone : 0u) | (moved ? kListMoved : 0u);
+    *listIdxOut = listIdx;
+    return true;
+  }
+  finishEnvLoaded(g, st, e, false, false, 0.f, prev, epr0, seedLo, seedHi);
+  return false;
+}
+
+__global__ void __launch_bounds__(256)
+k_pre(GroupDev g, SceneTable st, const int64_t* __restrict__ actions,
+      const uint8_t* __restrict__ actions8, TurnConsts tc, uint32_t seedLo, uint32_t seedHi) {
+  launchDependents();
+  waitForPredecessor();
+  const uint32_t e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= g.B)
+    return;
+  uint32_t entry = 0u, listIdx = 0u;
+  const bool listed = preEnv(g, st, e, actions, actions8, tc, seedLo, seedHi, &entry, &listIdx);
   const unsigned running = __activemask();
   const unsigned listedMask = __ballot_sync(running, listed);
   if (listed) {
-    // the list entry carries what the step kernel has to know about the action
-    const uint32_t entry = e | (done ? kListDone : 0u) | (moved ? kListMoved : 0u);
     // one atomic per (warp, list) instead of one per environment
     const unsigned grp = __match_any_sync(listedMask, listIdx);
     const int leader = __ffs(grp) - 1;
@@ -603,8 +637,6 @@ k_pre(GroupDev g, SceneTable st, const int64_t* __restrict__ actions,
     base = __shfl_sync(grp, base, leader);
     const uint32_t at = base + __popc(grp & ((1u << lane) - 1u));
     g.geoList[g.listBase[listIdx] + at] = entry;
-  } else {
-    finishEnvLoaded(g, st, e, false, false, 0.f, prev, epr0, seedLo, seedHi);
   }
 }
 

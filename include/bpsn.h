@@ -114,7 +114,11 @@ enum {
   /* work on every scene in global memory (tables and A* slabs L2 / L1 resident, two CTAs
      per SM) whatever its size; the planner otherwise does this only for large batches
      that contain a scene too big to share an SM's shared memory with 8 slabs */
-  BPSN_FLAG_GLOBAL_MEMORY = 1u << 4
+  BPSN_FLAG_GLOBAL_MEMORY = 1u << 4,
+  /* always run a step as two launches (k_pre, then the step kernel on work lists in global
+     memory); small batches of fixed scenes otherwise use one launch that does both -- for
+     testing the two-launch form on batches of any size */
+  BPSN_FLAG_TWO_LAUNCHES = 1u << 5
 };
 
 /* Fields addressable through bpsn_get_ptr.  All arrays are indexed by the

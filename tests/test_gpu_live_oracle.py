@@ -231,6 +231,13 @@ def test_scenes_rotate_with_two_groups_and_mixed_memory():
                  num_active=2, global_memory=True)
 
 
+def test_two_launch_step_on_small_batches():
+    # small batches of fixed scenes run a step as one launch; the two-launch form (k_pre, then
+    # the step kernel on work lists in global memory) must give the same results on them
+    _compare_run(["c1"], 4096, 64, seed=111, mix="uniform", threads=16, two_launches=True)
+    _compare_run(["c0", "m13", "m15"], 96, 64, seed=112, mix="policy", two_launches=True)
+
+
 def test_odd_batch_sizes():
     # partial warps in k_pre's warp-aggregated list appends, fewer environments than warps
     for n, seed in ((1, 50), (7, 51), (33, 52), (100, 53)):
