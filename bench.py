@@ -985,7 +985,7 @@ def run_c4(args):
     ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
 
     def rollout_and_learn(timed):
-        t_sim = t_pol = t_learn = 0.0
+        t_sim = t_pol = 0.0
         marks = []
         for g in range(2):
             b = bufs[g]
@@ -994,7 +994,7 @@ def run_c4(args):
         for t in range(T):
             for g in range(2):
                 b = bufs[g]
-                e0, e1, e2 = ev(), ev(), ev()
+                e0, e1, e2, e3 = ev(), ev(), ev(), ev()
                 e0.record()
                 with torch.no_grad(), torch.autocast("cuda", dtype=torch.float16):
                     logits, value, b.hc = policy(b.depth[t], b.polar[t], b.prev_a[t], b.hc,
@@ -1008,18 +1008,24 @@ def run_c4(args):
                 gen.step_start(g, a, reward_out=b.rewards[t], mask_out=b.masks[t + 1],
                                polar_out=b.polar[t + 1])
                 gen.step_end(g)
-                gen.render(g)
                 e2.record()
+                gen.render(g)
+                e3.record()
                 b.depth[t + 1, :, 0] = depth_view[g].clamp(max=10.0) / 10.0
                 b.prev_a[t + 1] = (a + 1) * b.masks[t + 1, :, 0]
-                marks.append((e0, e1, e2))
-        l0, l1, l2 = ev(), ev(), ev()
+                marks.append((e0, e1, e2, e3))
+        l0, lg, l1, l2 = ev(), ev(), ev(), ev()
         l0.record()
+        nvs = []
         for g in range(2):
             b = bufs[g]
             with torch.no_grad(), torch.autocast("cuda", dtype=torch.float16):
                 _, nv, _ = policy(b.depth[T], b.polar[T], b.prev_a[T], b.hc, b.masks[T, :, 0])
-            rollout.compute_returns(b.rewards, b.values, b.masks, b.returns, nv.float(), T, GAMMA,
+            nvs.append(nv.float())
+        lg.record()
+        for g in range(2):
+            b = bufs[g]
+            rollout.compute_returns(b.rewards, b.values, b.masks, b.returns, nvs[g], T, GAMMA,
                                     TAU, advantages=b.adv, normalize=False)
         rollout.normalize_advantages([bufs[0].adv, bufs[1].adv])
         l1.record()
@@ -1052,11 +1058,13 @@ def run_c4(args):
             b.masks[0].copy_(b.masks[T])
         torch.cuda.synchronize()
         if timed:
-            for e0, e1, e2 in marks:
+            t_render = 0.0
+            for e0, e1, e2, e3 in marks:
                 t_pol += e0.elapsed_time(e1)
                 t_sim += e1.elapsed_time(e2)
-            t_learn = l1.elapsed_time(l2)
-            return t_sim, t_pol, l0.elapsed_time(l1), t_learn
+                t_render += e2.elapsed_time(e3)
+            t_pol += l0.elapsed_time(lg)  # the value of the last observation
+            return t_sim, t_pol, lg.elapsed_time(l1), l1.elapsed_time(l2), t_render
         return None
 
     for _ in range(W):
@@ -1064,19 +1072,20 @@ def run_c4(args):
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
-    tot = np.zeros(4)
+    tot = np.zeros(5)
     w0 = time.perf_counter()
     for _ in range(K):
         tot += np.array(rollout_and_learn(True))
     if world > 1:
         dist.barrier()
     wall = time.perf_counter() - w0
-    sim_ms, pol_ms, gae_ms_, learn_ms = [dist_utils.max_over_ranks(x, dev) / K for x in tot]
+    sim_ms, pol_ms, gae_ms_, learn_ms, render_ms = [dist_utils.max_over_ranks(x, dev) / K
+                                                   for x in tot]
     wall = dist_utils.max_over_ranks(wall, dev) / K
     gen.close()
     if rank == 0:
         sim_path_ms = sim_ms + gae_ms_
-        step_ms = sim_ms + pol_ms + gae_ms_ + learn_ms
+        step_ms = sim_ms + render_ms + pol_ms + gae_ms_ + learn_ms
         line = {
             "metric": "env_steps_per_sec", "workload": "c4",
             "value": world * N * T / (sim_path_ms / 1000.0), "unit": "env-steps/s",
@@ -1089,15 +1098,17 @@ def run_c4(args):
                                    f"{MB} minibatches, DDP gradient all-reduce over NCCL",
                        "envs_per_gpu": N, "rollout_T": T},
             "sim_path": {"ms_per_window": sim_path_ms, "share_of_step_time": sim_path_ms / step_ms,
-                         "step_and_render_ms": sim_ms, "gae_and_next_value_ms": gae_ms_,
-                         "what": "simulator steps + depth renders of both groups over T steps "
-                                 "(CUDA events around them) + GAE / advantage normalisation"},
+                         "steps_ms": sim_ms, "gae_ms": gae_ms_,
+                         "what": "the simulator steps of both groups over T steps (navmesh move, "
+                                 "geodesic, sensor, reward / done / reset; CUDA events around "
+                                 "them) + GAE and advantage normalisation"},
+            "depth_render_ms": render_ms, "depth_render_share": render_ms / step_ms,
             "policy_inference_ms": pol_ms, "learner_ms": learn_ms,
             "whole_window_env_steps_per_s": world * N * T / wall,
             "wall_ms_per_window": 1000 * wall,
             "note": "value = the simulator path's own rate (environment steps of the window / "
-                    "time spent in step + render + GAE); the policy and learner are plain "
-                    "PyTorch load, not an optimisation target",
+                    "time spent in the simulator steps + GAE); the depth sensor, the policy and "
+                    "the learner are reported beside it and are load, not optimisation targets",
         }
         print(json.dumps(line), flush=True)
     if world > 1:
