@@ -53,10 +53,7 @@
 namespace bpsn {
 
 constexpr uint32_t kInfBits = 0x7f800000u;
-#ifndef BPSN_OPEN_SLOTS
-#define BPSN_OPEN_SLOTS 4
-#endif
-constexpr int kOpenSlots = BPSN_OPEN_SLOTS;  // register open-list entries per lane (128 per warp)
+constexpr int kOpenSlots = 4;  // register open-list entries per lane (128 per warp)
 // nodeB.y = parent (16 bits) | kNodeOpen | visit tag (15 bits).  A node belongs to the running
 // search iff its tag is the search's; anything else (zero, or the tag of an earlier search on
 // the same slab) reads as "not visited yet".
@@ -816,17 +813,20 @@ __device__ __noinline__ int astarExactSlab(const StagedView sc, const WarpSlab w
   return outcome;
 }
 
-// One query by one warp.  `sc` points at the staged (shared-memory) tables.
-// Returns the distance in every lane.  *needFallback is set (uniformly) when
-// the fast path cannot decide the pop order (tie for the minimum) or the
-// register open list is full.
+// The search part of one query by one warp: everything of findPathInternal
+// (PathFinder.cpp:485-526) up to the corridor.  `sc` points at the staged tables (shared or
+// global memory).  Returns the corridor's length, the corridor itself being in w.path[0 ..
+// length); or 0 when the distance is already known without a funnel -- *early (0 for coincident
+// end points, +inf for every failure) -- or when the query has to be redone by the one-thread
+// emulation (*needFallback set, uniformly: the register open list could not decide the pop
+// order and the slab heap outgrew its array).  The same in every lane.
 template <bool kGlobal>
-__device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSlab w, int lane,
-                                              const float* startPosIn, uint32_t startRef,
-                                              const float* endPosIn, uint32_t endRef,
-                                              uint32_t* status, uint32_t* needFallback,
-                                              bool forceExact
-) {
+__device__ __forceinline__ int warpSearch(const StagedView sc, const WarpSlab w, int lane,
+                                          const float* startPosIn, uint32_t startRef,
+                                          const float* endPosIn, uint32_t endRef,
+                                          uint32_t* status, uint32_t* needFallback,
+                                          bool forceExact, float* early) {
+
   // private copies: the caller's arrays are also handed to a non-inlined
   // function and therefore live in local memory
   const float startPos[3] = {startPosIn[0], startPosIn[1], startPosIn[2]};
@@ -844,21 +844,21 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
     const float prec = 1e-5f;
     const float mn = n2 < n1 ? n2 : n1;
     if (d2 <= prec * prec * mn)
-      return 0.0f;
+      { *early = 0.0f; return 0; }
   }
   // (ii) island check
   if (!validRef(sc, startRef) || !validRef(sc, endRef)) {
     *status |= kStatNoIsland;
-    return BPSN_INF;
+    { *early = BPSN_INF; return 0; }
   }
   const uint32_t startIdx = startRef & sc.polyMask;
   const uint32_t endIdx = endRef & sc.polyMask;
   if (sc.island[startIdx] != sc.island[endIdx]) {
     *status |= kStatNoIsland;
-    return BPSN_INF;
+    { *early = BPSN_INF; return 0; }
   }
   if (!finite3(startPos) || !finite3(endPos))
-    return BPSN_INF;
+    { *early = BPSN_INF; return 0; }
 
   int pathSize = 0;
   if (startIdx == endIdx) {
@@ -936,7 +936,7 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
       if ((hsum != 1u) | (best == endIdx) | (guard > 64 * kMaxAStarNodes)) {
         if (guard > 64 * kMaxAStarNodes) {
           *status |= kStatIterCap;
-          return BPSN_INF;
+          { *early = BPSN_INF; return 0; }
         }
         if (gm == kInfBits)
           break;  // open list empty: the end polygon was not reached
@@ -1172,11 +1172,11 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
                                          &nodeTotal);
       if (outcome == kAStarHeapFull) {
         *needFallback = exactWhy;  // hand the query to the global-memory emulation
-        return 0.f;
+        { *early = 0.f; return 0; }
       }
       if (outcome == kAStarIterCap) {
         *status |= kStatIterCap;
-        return BPSN_INF;
+        { *early = BPSN_INF; return 0; }
       }
       *status |= exactWhy;
       reached = outcome == kAStarReached;
@@ -1187,11 +1187,11 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
     const bool outOfNodes = nodeTotal > kMaxAStarNodes;
     if (outOfNodes) {
       *status |= kStatOutOfNodes;
-      return BPSN_INF;
+      { *early = BPSN_INF; return 0; }
     }
     if (!reached) {
       *status |= kStatPartial;
-      return BPSN_INF;
+      { *early = BPSN_INF; return 0; }
     }
     // corridor: walk parents from the end polygon, then reverse
     int length = 0;
@@ -1213,11 +1213,27 @@ __device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSla
     __syncwarp();
     if (length > kMaxPathPolys) {
       *status |= kStatPathTooLong;
-      return BPSN_INF;
+      { *early = BPSN_INF; return 0; }
     }
     pathSize = length;
   }
 
+  return pathSize;
+}
+
+// One query by one warp: search, then the funnel over the corridor.  Returns the distance in
+// every lane; *needFallback as in warpSearch.
+template <bool kGlobal>
+__device__ __forceinline__ float warpGeodesic(const StagedView sc, const WarpSlab w, int lane,
+                                              const float* startPos, uint32_t startRef,
+                                              const float* endPos, uint32_t endRef,
+                                              uint32_t* status, uint32_t* needFallback,
+                                              bool forceExact) {
+  float early = 0.f;
+  const int pathSize = warpSearch<kGlobal>(sc, w, lane, startPos, startRef, endPos, endRef, status,
+                                           needFallback, forceExact, &early);
+  if (pathSize == 0)
+    return early;
   const float dres = warpFunnel(sc, w, lane, startPos, endPos, pathSize, status);
   if (kGlobal) {
     // the portals sit in the first node slots; what they left in the tag field must not
@@ -1318,7 +1334,12 @@ struct FusedSource {
 // entries.  Two instances: tables and slabs in shared memory (the pointers are then known to
 // be shared-memory addresses and the accesses compile to shared-memory instructions) or in
 // global memory.
-template <bool kGlobal, class Source>
+// kBatched (batches that give every warp many entries): the funnel and everything after it --
+// which are one thread's work -- are not done entry by entry on lane 0 with 31 lanes waiting,
+// but for up to 32 entries at a time, one per lane: the warp searches 32 entries one after the
+// other, keeping each corridor in a staging row, then every lane pulls the string through its
+// own corridor (funnelLength(), the one-thread form) and finishes its own environment.
+template <bool kGlobal, bool kBatched, class Source>
 __device__ __forceinline__ void stepWarpQueries(const GroupDev& g, const SceneTable& st,
                                                 const WarpPlan pl, Source next,
                                                 const NavScene& scGlobal,
@@ -1368,6 +1389,94 @@ __device__ __forceinline__ void stepWarpQueries(const GroupDev& g, const SceneTa
 
   const uint32_t B = g.B;
   (void)warpsPerBlock;
+  if constexpr (kBatched) {
+    uint16_t* stage = g.batchStage +
+                      (static_cast<size_t>(blockIdx.x) * (blockDim.x >> 5) + warp) * 32u * kMaxPathPolys;
+    for (;;) {
+      int cnt = 0;
+      uint32_t myEntry = 0u, myStatus = 0u;
+      int myLen = 0;
+      float myD = 0.f, myA[3] = {0.f, 0.f, 0.f}, myB[3] = {0.f, 0.f, 0.f};
+      while (cnt < 32) {
+        uint32_t entry = 0u;
+        if (!next(lane, &entry))
+          break;
+        const uint32_t e = entry & kListEnvMask;
+        if (kGlobal) {
+          const size_t slabIdx =
+              slabPerEnv ? static_cast<size_t>(e)
+                         : static_cast<size_t>(blockIdx.x) * (blockDim.x >> 5) + static_cast<size_t>(warp);
+          uint8_t* slab = globalSlabs + slabIdx * globalSlabStride;
+          w = carveSlab(slab, pcap);
+          w.searches = reinterpret_cast<uint32_t*>(slab + globalSlabStride - kGlobalSlabExtra);
+        }
+        const bool moved = entry & kListMoved;
+        const float b[3] = {g.navGoal[e], g.navGoal[B + e], g.navGoal[2 * B + e]};
+        const uint32_t bref = g.goalRef[e];
+        float a[3];
+        uint32_t aref;
+        if (moved) {
+          warpForwardMove(g, sv, sc, w, lane, e, a, &aref);
+        } else {
+          a[0] = g.navPos[e];
+          a[1] = g.navPos[B + e];
+          a[2] = g.navPos[2 * B + e];
+          aref = g.navRef[e];
+        }
+        uint32_t status = 0u, fallback = 0u;
+        float d = 0.f;
+        int len = 0;
+        const bool needGeo = g.task == kTaskPointNav || (g.task == kTaskFlee && moved);
+        if (needGeo) {
+          len = warpSearch<kGlobal>(sv, w, lane, b, bref, a, aref, &status, &fallback,
+                                    g.exactHeap != 0, &d);
+          if (fallback) {  // (rare) the one-thread emulation, at once
+            if (lane == 0) {
+              status = 0u;
+              const size_t slot = static_cast<size_t>(blockIdx.x) * (blockDim.x >> 5) + warp;
+              d = geodesic(scGlobal, fallbackScratch + slot, b, bref, a, aref, &status);
+              status |= fallback;
+            }
+            d = __shfl_sync(0xffffffffu, d, 0);
+            status = __shfl_sync(0xffffffffu, status, 0);
+            len = 0;
+          }
+          for (int i = lane; i < len; i += 32)
+            stage[cnt * kMaxPathPolys + i] = w.path[i];
+        }
+        if (lane == cnt) {
+          myEntry = entry;
+          myStatus = status;
+          myLen = len;
+          myD = d;
+          myA[0] = a[0]; myA[1] = a[1]; myA[2] = a[2];
+          myB[0] = b[0]; myB[1] = b[1]; myB[2] = b[2];
+        }
+        ++cnt;
+        __syncwarp();
+      }
+      if (cnt == 0)
+        break;
+      if (lane < cnt) {
+        const uint32_t e = myEntry & kListEnvMask;
+        const bool done = myEntry & kListDone, moved = myEntry & kListMoved;
+        if (myLen > 0) {
+          uint32_t st2 = 0u;
+          myD = funnelLength(sc, myB, myA, stage + lane * kMaxPathPolys, myLen, &st2);
+          myStatus |= st2;
+        }
+        if (g.task == kTaskExploration && moved)
+          explVisit(g, e, myA[0], myA[1], myA[2]);
+        if (myStatus)
+          g.status[e] |= myStatus;
+        finishEnv(g, st, e, done, moved, myD, seedLo, seedHi);
+      }
+      __syncwarp();
+      if (cnt < 32)
+        break;
+    }
+    return;
+  }
   for (;;) {
     uint32_t entry = 0u;
     if (!next(lane, &entry))
@@ -1444,7 +1553,7 @@ __device__ __forceinline__ void stepWarpQueries(const GroupDev& g, const SceneTa
 // shared memory: one launch per step and no work list in global memory.  For batches in which
 // a CTA's share is small enough for its warps to take one query each; with more, the
 // lists of all CTAs of a slot are better drained together (k_pre + global lists).
-template <int kMode, bool kRotate, bool kFused = false>
+template <int kMode, bool kRotate, bool kFused = false, bool kBatched = false>
 __global__ void __launch_bounds__(512, kMode == 1 ? 2 : 1)
 k_step_warp(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
             const uint4* __restrict__ ctaMap, AStarScratch* __restrict__ fallbackScratch,
@@ -1452,6 +1561,7 @@ k_step_warp(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
             uint32_t seedHi, const int64_t* __restrict__ actions,
             const uint8_t* __restrict__ actions8, TurnConsts tc) {
   static_assert(!kFused || (kMode == 0 && !kRotate), "fused: fixed scenes in shared memory");
+  static_assert(!kBatched || (kMode != 2 && !kRotate && !kFused), "batched: large fixed batches");
   extern __shared__ __align__(16) uint8_t smem[];
   __shared__ uint32_t fusedList[kFused ? kFusedMaxShare : 1];
   __shared__ uint32_t fusedCount;
@@ -1612,7 +1722,7 @@ k_step_warp(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
     if constexpr (kFused) {
       FusedSource src{fusedList, min(fusedCount, pl.warps), g.ovList, g.ovMeta,
                       blockIdx.x - rank, rank, slotCtas, g.stepId, warp, 0u};
-      stepWarpQueries<false>(g, st, pl, src, BPSN_STEP_ARGS);
+      stepWarpQueries<false, false>(g, st, pl, src, BPSN_STEP_ARGS);
     } else {
       const uint32_t firstQ =
           rank * static_cast<uint32_t>(warpsPerBlock) + static_cast<uint32_t>(warp);
@@ -1621,14 +1731,14 @@ k_step_warp(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
       ListSource src{g.geoList + g.listBase[listIdx], g.counts + g.numLists + listIdx, firstQ,
                      slotCtas * static_cast<uint32_t>(warpsPerBlock), n, true};
       if constexpr (kMode == 0) {
-        stepWarpQueries<false>(g, st, pl, src, BPSN_STEP_ARGS);
+        stepWarpQueries<false, kBatched>(g, st, pl, src, BPSN_STEP_ARGS);
       } else if constexpr (kMode == 1) {
-        stepWarpQueries<true>(g, st, pl, src, BPSN_STEP_ARGS);
+        stepWarpQueries<true, kBatched>(g, st, pl, src, BPSN_STEP_ARGS);
       } else {
         if (inGlobal)
-          stepWarpQueries<true>(g, st, pl, src, BPSN_STEP_ARGS);
+          stepWarpQueries<true, false>(g, st, pl, src, BPSN_STEP_ARGS);
         else
-          stepWarpQueries<false>(g, st, pl, src, BPSN_STEP_ARGS);
+          stepWarpQueries<false, false>(g, st, pl, src, BPSN_STEP_ARGS);
       }
     }
 #undef BPSN_STEP_ARGS

@@ -231,6 +231,17 @@ def test_scenes_rotate_with_two_groups_and_mixed_memory():
                  num_active=2, global_memory=True)
 
 
+def test_large_batch_finishes_thirty_two_entries_at_a_time():
+    # batches that give every warp several entries per step: the warp searches 32 entries,
+    # then every lane pulls the string through one corridor and finishes one environment --
+    # in shared memory (c1), in global memory (the 16 mixed scenes, d0), and with Flee's rule
+    # that only moves need a query
+    _compare_run(["c1"], 32768, 24, seed=121, mix="uniform", threads=16, check_state_every=12)
+    _compare_run(["c1"], 20480, 40, seed=122, mix="policy", threads=16, check_state_every=20)
+    names = [f"m{i:02d}" for i in range(16)]
+    _compare_run(names, 65536, 16, seed=123, mix="uniform", threads=16, check_state_every=8)
+
+
 def test_two_launch_step_on_small_batches():
     # small batches of fixed scenes run a step as one launch; the two-launch form (k_pre, then
     # the step kernel on work lists in global memory) must give the same results on them
