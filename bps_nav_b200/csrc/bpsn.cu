@@ -11,8 +11,10 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <algorithm>
 #include <mutex>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "dataset_host.h"
@@ -125,6 +127,7 @@ struct bpsn_sim {
   // scratch for the bpsn_query_* entry points
   AStarScratch* queryScratch = nullptr;
   uint32_t querySlots = 0;
+  std::vector<double> queryCost;  // per scene: work of one query, in opened nodes (bpsn_finalize)
 };
 
 namespace {
@@ -499,27 +502,55 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase, uint32
         if (!slotSize[s2] || !pl.warps)
           continue;
         work[s2] = static_cast<double>(slotSize[s2]) / (pl.warps * speedOf[slotScene[s2]]);
+        // Fixed scenes differ in work per query (a search on a scene of long corridors opens
+        // several times the nodes of one on a small room): CTAs in proportion to work, not to
+        // environments (16 scenes of 91-1304 polygons: 16384 envs 114 -> 121 M env-steps/s,
+        // 65536 envs 165 -> 195 M).  A rotating slot meets every scene in turn.
+        if (!rotation)
+          work[s2] *= sim->queryCost[slotScene[s2]];
         workSum += work[s2];
       }
-      std::vector<uint4> ctaMap;
-      for (uint32_t s2 = 0; s2 < numSlots; ++s2) {
-        if (!slotSize[s2])
-          continue;
-        const WarpPlan& pl = plan[slotScene[s2]];
-        uint32_t c = 1;
-        if (pl.warps && workSum > 0.0) {
-          c = static_cast<uint32_t>(ctaBudget * work[s2] / workSum + 0.5);
-          const uint32_t need = (slotSize[s2] + pl.warps - 1) / pl.warps;
-          if (c > need)
-            c = need;  // never more warps than environments
-        } else if (!rotation) {
-          continue;  // a fixed scene of the generic kernel: no CTA of this one
+      // Shares of the budget: whole CTAs by largest remainder, so that the grid does not
+      // exceed what is resident at once (a CTA that has to wait for another one to finish
+      // starts its first queries when the others are nearly through); at least one per slot.
+      std::vector<uint32_t> ctas(numSlots, 0u);
+      {
+        std::vector<std::pair<double, uint32_t>> rest;
+        int dealt = 0;
+        for (uint32_t s2 = 0; s2 < numSlots; ++s2) {
+          if (!slotSize[s2])
+            continue;
+          const WarpPlan& pl = plan[slotScene[s2]];
+          if (pl.warps && workSum > 0.0) {
+            const double share = ctaBudget * work[s2] / workSum;
+            const uint32_t need = (slotSize[s2] + pl.warps - 1) / pl.warps;
+            uint32_t c = static_cast<uint32_t>(share);
+            if (c >= need) {
+              c = need;  // never more warps than environments
+            } else {
+              rest.push_back({share - c, s2});
+            }
+            if (c == 0) {
+              c = 1;
+              if (!rest.empty() && rest.back().second == s2)
+                rest.pop_back();
+            }
+            ctas[s2] = c;
+          } else if (rotation) {
+            ctas[s2] = 1;
+          }  // else: a fixed scene of the generic kernel, no CTA of this one
+          dealt += static_cast<int>(ctas[s2]);
         }
-        if (c == 0)
-          c = 1;
-        for (uint32_t r = 0; r < c; ++r)
-          ctaMap.push_back(make_uint4(s2, r, c, 0u));
+        std::sort(rest.begin(), rest.end(), [](const auto& a, const auto& b2) {
+          return a.first > b2.first || (a.first == b2.first && a.second < b2.second);
+        });
+        for (size_t i = 0; i < rest.size() && dealt < ctaBudget; ++i, ++dealt)
+          ctas[rest[i].second]++;
       }
+      std::vector<uint4> ctaMap;
+      for (uint32_t s2 = 0; s2 < numSlots; ++s2)
+        for (uint32_t r = 0; r < ctas[s2]; ++r)
+          ctaMap.push_back(make_uint4(s2, r, ctas[s2], 0u));
       if (ctaMap.empty())
         ctaMap.push_back(make_uint4(0u, 0u, 1u, 0u));
       g.numCtas = static_cast<uint32_t>(ctaMap.size());
@@ -982,15 +1013,31 @@ int32_t bpsn_finalize(bpsn_sim* sim) {
   BPSN_CUDA(sim, cudaMalloc(&sim->queryScratch, sizeof(AStarScratch) * sim->querySlots));
   const size_t totalEps = eps.size() / 10;
   BPSN_CUDA(sim, cudaMalloc(&sim->dEpNav, sizeof(EpisodeNav) * totalEps));
+  unsigned long long* dSearchWork = nullptr;
+  BPSN_CUDA(sim, cudaMalloc(&dSearchWork, sizeof(unsigned long long) * 2 * ns));
+  BPSN_CUDA(sim, cudaMemset(dSearchWork, 0, sizeof(unsigned long long) * 2 * ns));
   for (uint32_t i = 0; i < ns; ++i) {
     const uint32_t slots = epCnt[i] < sim->querySlots ? epCnt[i] : sim->querySlots;
     k_episode_table<<<blocksFor(slots, 128), 128>>>(sim->dScenes + i,
                                                     sim->dEpisodes + 10 * static_cast<size_t>(epOff[i]),
                                                     epCnt[i], sim->queryScratch, slots,
-                                                    sim->dEpNav + epOff[i]);
+                                                    sim->dEpNav + epOff[i], dSearchWork + 2 * i);
   }
   BPSN_CUDA(sim, cudaGetLastError());
   BPSN_CUDA(sim, cudaDeviceSynchronize());
+  {
+    // Work of one query per scene, in opened nodes: what the episodes' own searches (start ->
+    // goal, the same pairs the steps will search between) needed on average, plus the part
+    // of a query that does not depend on the search (move, funnel, finish: about six nodes'
+    // worth of instructions).
+    std::vector<unsigned long long> w(2 * ns);
+    BPSN_CUDA(sim, cudaMemcpy(w.data(), dSearchWork, sizeof(unsigned long long) * 2 * ns,
+                              cudaMemcpyDeviceToHost));
+    BPSN_CUDA(sim, cudaFree(dSearchWork));
+    sim->queryCost.assign(ns, 1.0);
+    for (uint32_t i = 0; i < ns; ++i)
+      sim->queryCost[i] = 6.0 + (w[2 * i + 1] ? static_cast<double>(w[2 * i]) / w[2 * i + 1] : 10.0);
+  }
   sim->table.scenes = sim->dScenes;
   sim->table.episodes = sim->dEpisodes;
   sim->table.epNav = sim->dEpNav;
@@ -1326,6 +1373,7 @@ int32_t bpsn_step_end(bpsn_sim* sim, uint32_t group) {
     for (int k = 0; k < 2; ++k) {
       float ms = 0.f;
       BPSN_CUDA(sim, cudaEventElapsedTime(&ms, g.prof[k], g.prof[k + 1]));
+      if (k == 0 && g.fused) ms = 0.f;  // one launch per step: no k_pre between the two events
       g.profMs[k] += ms;
     }
     g.profSteps++;

@@ -734,11 +734,15 @@ k_reset_all(GroupDev g, SceneTable st, uint32_t seedLo, uint32_t seedHi) {
 // navmesh (simulator.cpp:611-612, 747-752).
 __global__ void __launch_bounds__(128)
 k_episode_table(const NavScene* scene, const float* __restrict__ episodes, uint32_t count,
-                AStarScratch* __restrict__ scratch, uint32_t nslots, EpisodeNav* out) {
+                AStarScratch* __restrict__ scratch, uint32_t nslots, EpisodeNav* out,
+                unsigned long long* searchWork) {
   const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= nslots)
     return;
   const NavScene sc = *scene;
+  // nodes opened by the episodes' searches and how many searches there were: how much work a
+  // query on this scene is (the step kernel's CTAs are dealt to the scenes by it)
+  unsigned long long nodesSum = 0ull, searches = 0ull;
   for (uint32_t i = t; i < count; i += nslots) {
     const float* ep = episodes + 10 * static_cast<size_t>(i);
     const float start[3] = {ep[0], ep[1], ep[2]};
@@ -749,10 +753,20 @@ k_episode_table(const NavScene* scene, const float* __restrict__ episodes, uint3
     uint32_t status = 0;
     if (r.startRef == 0 || r.goalRef == 0)
       status |= kStatSnapFailed;
-    r.initDist = geodesic(sc, scratch + t, r.navStart, r.startRef, r.navGoal, r.goalRef, &status);
+    uint32_t opened = 0u;
+    r.initDist = geodesic(sc, scratch + t, r.navStart, r.startRef, r.navGoal, r.goalRef, &status,
+                          &opened);
+    if (opened) {
+      nodesSum += opened;
+      searches++;
+    }
     r.status = status;
     r.pad[0] = r.pad[1] = 0;
     out[i] = r;
+  }
+  if (searches) {
+    atomicAdd(searchWork, nodesSum);
+    atomicAdd(searchWork + 1, searches);
   }
 }
 
