@@ -1475,8 +1475,7 @@ __device__ __forceinline__ void stepWarpQueries(const GroupDev& g, const SceneTa
       if (cnt < 32)
         break;
     }
-    return;
-  }
+  } else {
   for (;;) {
     uint32_t entry = 0u;
     if (!next(lane, &entry))
@@ -1525,6 +1524,7 @@ __device__ __forceinline__ void stepWarpQueries(const GroupDev& g, const SceneTa
       finishEnv(g, st, e, done, moved, d, seedLo, seedHi);
     }
     __syncwarp();
+  }
   }
 }
 
@@ -1773,8 +1773,18 @@ k_step_warp(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
     __syncthreads();
     if (lastCta) {
       __threadfence();
-      for (uint32_t i = threadIdx.x; i < g.pubVec; i += blockDim.x)
-        g.pubDst[i] = __ldcg(g.pubSrc + i);
+      // (four loads in flight per thread before the first store)
+      for (uint32_t base = threadIdx.x; base < g.pubVec; base += 4u * blockDim.x) {
+        uint4 v[4];
+#pragma unroll
+        for (uint32_t k = 0; k < 4u; ++k)
+          if (base + k * blockDim.x < g.pubVec)
+            v[k] = __ldcg(g.pubSrc + base + k * blockDim.x);
+#pragma unroll
+        for (uint32_t k = 0; k < 4u; ++k)
+          if (base + k * blockDim.x < g.pubVec)
+            g.pubDst[base + k * blockDim.x] = v[k];
+      }
       __threadfence_system();
       __syncthreads();
       if (threadIdx.x == 0)
