@@ -179,6 +179,7 @@ class ClockSampler:
             self.stop_flag = True
             self.thread.join(timeout=2)
             return {"sm_mhz": float(np.median(self.sm)) if self.sm else None,
+                    "sm_min_mhz": float(np.min(self.sm)) if self.sm else None,
                     "sm_max_mhz": float(np.max(self.mx)) if self.mx else None,
                     "samples": len(self.sm), "reasons": sorted(self.reasons), "source": "nvml"}
         if self.proc is None:
@@ -985,6 +986,8 @@ def run_c4(args):
         bufs[g].polar[0] = polar_view[g]
     ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
 
+    rollout_clocks = []
+
     def rollout_and_learn(timed):
         t_sim = t_pol = 0.0
         marks = []
@@ -992,6 +995,12 @@ def run_c4(args):
             b = bufs[g]
             b.h0.copy_(b.hc[0])
             b.c0.copy_(b.hc[1])
+        # the SM clock while the rollout (policy inference + simulator + depth) runs: the
+        # simulator's steps are latency-bound and follow it
+        sampler = ClockSampler(local) if timed and rank == 0 else None
+        if sampler:
+            torch.cuda.synchronize()
+            sampler.start()
         for t in range(T):
             for g in range(2):
                 b = bufs[g]
@@ -1015,6 +1024,9 @@ def run_c4(args):
                 b.depth[t + 1, :, 0] = depth_view[g].clamp(max=10.0) / 10.0
                 b.prev_a[t + 1] = (a + 1) * b.masks[t + 1, :, 0]
                 marks.append((e0, e1, e2, e3))
+        if sampler:
+            torch.cuda.synchronize()
+            rollout_clocks.append(sampler.stop())
         l0, lg, l1, l2 = ev(), ev(), ev(), ev()
         l0.record()
         nvs = []
@@ -1103,6 +1115,7 @@ def run_c4(args):
                          "what": "the simulator steps of both groups over T steps (navmesh move, "
                                  "geodesic, sensor, reward / done / reset; CUDA events around "
                                  "them) + GAE and advantage normalisation"},
+            "clocks_during_rollout": rollout_clocks[-1] if rollout_clocks else None,
             "depth_render_ms": render_ms, "depth_render_share": render_ms / step_ms,
             "policy_inference_ms": pol_ms, "learner_ms": learn_ms,
             "whole_window_env_steps_per_s": world * N * T / wall,
