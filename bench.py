@@ -541,8 +541,8 @@ def run_ours(args):
         with programmatic dependent launch on, the step kernel is resident from the moment the
         kernel before it starts (it stages its scene, then waits) until the step is complete, so
         one launch lasts (window - GAE) / T.  Units: the environments listed for a navmesh
-        query that step (moved or finished: half of them under uniform actions)."""
-        q_step = n * (0.5 if args.mix == "uniform" else 0.61)
+        query that step (those that moved: a quarter of them under uniform actions)."""
+        q_step = n * (0.25 if args.mix == "uniform" else 0.60)
         ms_launch = (ms_window - ms_gae) / T
         achieved = q_step * BYTES_PER_ENV_STEP / (ms_launch * 1e-3) / 1e9
         share = kms["k_step"] / max(sum(kms.values()), 1e-9)

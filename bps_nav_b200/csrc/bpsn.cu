@@ -318,7 +318,7 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase, uint32
   d.prevDist = reinterpret_cast<float*>(b + oPrevDist);
   d.cumTravel = reinterpret_cast<float*>(b + oCum);
   d.initDist = reinterpret_cast<float*>(b + oInit);
-  d.tmpDist = reinterpret_cast<float*>(b + oTmp);
+  d.doneDist = reinterpret_cast<float*>(b + oTmp);
   d.navRef = reinterpret_cast<uint32_t*>(b + oNavRef);
   d.goalRef = reinterpret_cast<uint32_t*>(b + oGoalRef);
   d.step = reinterpret_cast<uint32_t*>(b + oStep);

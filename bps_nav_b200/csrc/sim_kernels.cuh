@@ -75,7 +75,11 @@ struct GroupDev {
   float* prevDist;
   float* cumTravel;
   float* initDist;
-  float* tmpDist;  // geodesic result of the current step
+  // What InfoFunctor::step would find if the episode ended now without a move (it searches
+  // goal -> agent on every `done`, simulator.cpp:763-767): the distance of the last move's
+  // search -- the agent has not left that spot -- or, before the first move, the episode
+  // table's goal -> start distance.  An episode that ends on a stop or a turn needs no search.
+  float* doneDist;
   uint32_t* navRef;
   uint32_t* goalRef;
   uint32_t* step;
@@ -164,9 +168,10 @@ struct alignas(16) EpisodeNav {
   uint32_t startRef;
   float navGoal[3];
   uint32_t goalRef;
-  float initDist;
+  float initDist;      // start -> goal (InfoFunctor::reset)
   uint32_t status;
-  uint32_t pad[2];
+  float initDistRev;   // goal -> start: what a `done` before the first move reports
+  uint32_t statusRev;
 };
 static_assert(sizeof(EpisodeNav) == 48, "EpisodeNav is 48 bytes");
 
@@ -341,8 +346,9 @@ __device__ __forceinline__ void resetEnvLoaded(const GroupDev& g, const SceneTab
   const float init = __uint_as_float(n2.x);
   g.initDist[e] = init;
   g.prevDist[e] = init;
-  if (n2.y)
-    g.status[e] |= n2.y;
+  g.doneDist[e] = __uint_as_float(n2.z);
+  if (n2.y | n2.w)
+    g.status[e] |= n2.y | n2.w;
   g.cumTravel[e] = 0.f;
   g.prevPos[e] = sx;
   g.prevPos[B + e] = sy;
@@ -436,6 +442,7 @@ __device__ __forceinline__ void finishEnvLoaded(const GroupDev& g, const SceneTa
       const float dz = pz - qz;
       g.cumTravel[e] = cum + sqrtExact(dx * dx + dy * dy + dz * dz);
       g.prevDist[e] = d;
+      g.doneDist[e] = d;
       g.prevPos[e] = px;
       g.prevPos[B + e] = py;
       g.prevPos[2 * B + e] = pz;
@@ -605,13 +612,17 @@ __device__ __forceinline__ bool preEnv(const GroupDev& g, const SceneTable& st, 
     }
     writePolar(g, e, px, py, pz, qx, qy, qz, qw, gx, gy, gz);
   }
-  if (done || moved) {
+  if (moved) {
     // the list entry carries what the step kernel has to know about the action
-    *entry = e | (done ? kListDone : 0u) | (moved ? kListMoved : 0u);
+    *entry = e | (done ? kListDone : 0u) | kListMoved;
     *listIdxOut = listIdx;
     return true;
   }
-  finishEnvLoaded(g, st, e, false, false, 0.f, prev, epr0, seedLo, seedHi);
+  // No move, no navmesh query: a step that goes on reports the distance of the step before
+  // (:783-785), one that ends the episode the distance kept for that (GroupDev::doneDist);
+  // the in-loop reset is a table lookup.
+  const float dEnd = (done && g.task == kTaskPointNav) ? g.doneDist[e] : 0.f;
+  finishEnvLoaded(g, st, e, done, false, dEnd, prev, epr0, seedLo, seedHi);
   return false;
 }
 
@@ -761,7 +772,10 @@ k_episode_table(const NavScene* scene, const float* __restrict__ episodes, uint3
       searches++;
     }
     r.status = status;
-    r.pad[0] = r.pad[1] = 0;
+    uint32_t statusRev = 0;
+    r.initDistRev = geodesic(sc, scratch + t, r.navGoal, r.goalRef, r.navStart, r.startRef,
+                             &statusRev);
+    r.statusRev = statusRev;
     out[i] = r;
   }
   if (searches) {
