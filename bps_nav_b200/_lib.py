@@ -21,7 +21,7 @@ SYMBOLS = [
 ]
 
 # exports for the tests only (bps_nav_b200/csrc/bpsn_test_hooks.h)
-TEST_HOOKS = ["bpsn_debug_set_search_count"]
+TEST_HOOKS = ["bpsn_debug_set_search_count", "bpsn_debug_force_batched"]
 
 OK = 0
 ERR_INVALID_ARG, ERR_BAD_NAVMESH, ERR_CUDA, ERR_STATE, ERR_BAD_ACTION, ERR_IO, ERR_NO_DEVICE = range(1, 8)
@@ -114,6 +114,7 @@ def load():
     lib.bpsn_adv_ema_shift.argtypes = [C.POINTER(AdvSegment), u32, u32, vp, vp, C.c_float, vp]
     lib.bpsn_selftest_sqrt.argtypes = [i32, u32, u32, C.POINTER(C.c_uint64)]
     lib.bpsn_debug_set_search_count.argtypes = [C.c_void_p, u32, u32]
+    lib.bpsn_debug_force_batched.argtypes = [C.c_void_p, u32, C.c_int32]
     lib.bpsn_dataset_open.argtypes = [C.c_char_p, C.c_char_p, u32, C.POINTER(vp)]
     lib.bpsn_dataset_num_scenes.argtypes = [vp]
     lib.bpsn_dataset_num_scenes.restype = u32

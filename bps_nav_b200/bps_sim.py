@@ -436,6 +436,12 @@ class _RolloutGenerator:
         (bpsn_debug_set_search_count), e.g. to just below the point where it wraps."""
         L.check(self._lib.bpsn_debug_set_search_count(self._h, group_idx, int(count)), self._h)
 
+    def debug_force_batched(self, group_idx, mode):
+        """Diagnostic: form of the step kernel on large batches (bpsn_debug_force_batched):
+        1 always 32 entries at a time where the group has that form, 2 never, 0 chosen step
+        by step."""
+        L.check(self._lib.bpsn_debug_force_batched(self._h, group_idx, int(mode)), self._h)
+
     KERNEL_NAMES = ("k_pre", "k_step")
 
     def profile(self, group_idx, enable=True):

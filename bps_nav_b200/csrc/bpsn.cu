@@ -58,6 +58,9 @@ struct Group {
   bool fused = false;     // one launch per step: the step kernel does k_pre's part itself
   bool batched = false;   // funnel and finish for 32 entries at a time, one per lane
   uint16_t* dBatchStage = nullptr;
+  volatile uint32_t* hListed = nullptr;  // host view of the last step's number of list entries
+  uint32_t batchMinListed = 0;           // the batched form pays from this many entries on
+  int batchForce = 0;                    // test hook: 1 always batched, 2 never
   uint32_t stepCounter = 0;
   uint32_t* dDoneCount = nullptr;
   uint32_t* dOvList = nullptr;   // one-launch step: per-CTA overflow segments and their headers
@@ -295,6 +298,15 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase, uint32
   BPSN_CUDA(sim, cudaMemset(g.stateBlob, 0, off));
   uint8_t* b = static_cast<uint8_t*>(g.stateBlob);
   GroupDev& d = g.dev;
+  {
+    uint32_t* hl = nullptr;
+    BPSN_CUDA(sim, cudaHostAlloc(&hl, 64, cudaHostAllocMapped));
+    *hl = 0u;
+    g.hListed = hl;
+    void* dp = nullptr;
+    BPSN_CUDA(sim, cudaHostGetDevicePointer(&dp, hl, 0));
+    d.hListed = static_cast<uint32_t*>(dp);
+  }
   d.B = B;
   d.envBase = envBase;
   d.task = sim->cfg.task;
@@ -564,14 +576,18 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase, uint32
           if (share > maxShare)
             maxShare = share;
         }
-        g.fused = !rotation && g.warpMode == 0 && !g.anyThreadScene && maxShare <= 2 * kBlockWarps &&
+        g.fused = !rotation && g.warpMode == 0 && !g.anyThreadScene &&
                   maxShare <= kFusedMaxShare && !(sim->cfg.flags & BPSN_FLAG_TWO_LAUNCHES);
-        // Batches that give every warp several entries per step: funnel and finish 32 at a time.
-        // (measured: with 7 entries per warp and step +15 % in shared memory, +3 % in global
-        // memory; with 3.5 it costs 3-10 %: lanes beyond the batch's entries idle)
-        const uint32_t kBatchMinPerWarp = 4;
-        g.batched = !rotation && g.warpMode != 2 && !g.anyThreadScene &&
-                    B / 2 >= kBatchMinPerWarp * g.numCtas * kBlockWarps;
+        // Steps that give every warp several entries: funnel and finish 32 at a time.  How
+        // many entries a step lists depends on the actions (a quarter of the environments
+        // under uniform actions, 60 % under a trained policy's), so the form is chosen step by
+        // step from the number the step before listed (GroupDev::hListed).  Measured, entries
+        // per warp -> batched against entry by entry: shared memory 1.7 -> -16 %, 3.5 -> -1 %,
+        // 4.2 -> -1 %, 6.9 -> +13 %, 8.3 -> +14 %; global memory 3.5 -> -11 %, 8.3 -> +5 %.
+        const uint32_t kBatchMinPerWarp = g.warpMode == 0 ? 5 : 6;
+        g.batched = !rotation && g.warpMode != 2 && !g.anyThreadScene && !g.fused &&
+                    B >= kBatchMinPerWarp * g.numCtas * kBlockWarps;
+        g.batchMinListed = kBatchMinPerWarp * g.numCtas * kBlockWarps;
         if (g.batched) {
           const size_t bytes = sizeof(uint16_t) * 32 * kMaxPathPolys * g.numCtas * kBlockWarps;
           BPSN_CUDA(sim, cudaMalloc(&g.dBatchStage, bytes));
@@ -602,12 +618,16 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase, uint32
       // The function attribute is the hardware limit whatever this handle's plan asks for: it
       // belongs to the function, so every handle of the process shares it.
       const int kSmemAttr = 227 * 1024 - 512;
-      if (g.warpMode == 0)
-        BPSN_CUDA(sim, cudaFuncSetAttribute(rotation    ? k_step_warp<0, true>
-                                            : g.fused   ? k_step_warp<0, false, true>
-                                            : g.batched ? k_step_warp<0, false, false, true>
-                                                        : k_step_warp<0, false>,
+      if (g.warpMode == 0) {
+        BPSN_CUDA(sim, cudaFuncSetAttribute(rotation  ? k_step_warp<0, true>
+                                            : g.fused ? k_step_warp<0, false, true>
+                                                      : k_step_warp<0, false>,
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAttr));
+        if (g.batched)
+          BPSN_CUDA(sim, cudaFuncSetAttribute(k_step_warp<0, false, false, true>,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              kSmemAttr));
+      }
       else if (g.warpMode == 2)
         BPSN_CUDA(sim, cudaFuncSetAttribute(rotation ? k_step_warp<2, true> : k_step_warp<2, false>,
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAttr));
@@ -855,6 +875,7 @@ int32_t bpsn_destroy(bpsn_sim* sim) {
     cudaFree(g.dCtaMap);
     cudaFree(g.dDoneCount);
     cudaFree(g.dBatchStage);
+    cudaFreeHost(const_cast<uint32_t*>(g.hListed));
     cudaFree(g.dOvList);
     cudaFree(g.dOvMeta);
     cudaFree(g.depth);
@@ -1265,8 +1286,10 @@ int32_t bpsn_step_start_ex(bpsn_sim* sim, uint32_t group, const int64_t* actions
     lc.blockDim = dim3(512);
     lc.dynamicSmemBytes = g.geoSmem;
     const bool rot = g.dev.rotation != 0u;
+    const bool batchedNow = g.batched && g.batchForce != 2 &&
+                            (g.batchForce == 1 || *g.hListed >= g.batchMinListed);
     auto* kernel = g.fused           ? k_step_warp<0, false, true>
-                   : g.batched       ? (g.warpMode == 0 ? k_step_warp<0, false, false, true>
+                   : batchedNow      ? (g.warpMode == 0 ? k_step_warp<0, false, false, true>
                                                         : k_step_warp<1, false, false, true>)
                    : g.warpMode == 0 ? (rot ? k_step_warp<0, true> : k_step_warp<0, false>)
                    : g.warpMode == 1 ? (rot ? k_step_warp<1, true> : k_step_warp<1, false>)
@@ -1733,6 +1756,15 @@ int32_t bpsn_gae_static(const float* rewards, float* values, const uint8_t* mask
   if (e != cudaSuccess)
     return fail(nullptr, BPSN_ERR_CUDA,
                 std::string("bpsn_gae_static launch: ") + cudaGetErrorString(e));
+  return BPSN_OK;
+}
+
+// Step form of large batches (diagnostic): 0 chosen step by step, 1 always 32 entries at a
+// time where the group allows it, 2 always entry by entry.
+int32_t bpsn_debug_force_batched(bpsn_sim* sim, uint32_t group, int32_t mode) {
+  if (!sim || !sim->finalized || group >= sim->groups.size() || mode < 0 || mode > 2)
+    return fail(sim, BPSN_ERR_INVALID_ARG, "bpsn_debug_force_batched: bad argument");
+  sim->groups[group].batchForce = mode;
   return BPSN_OK;
 }
 

@@ -17,6 +17,12 @@ extern "C" {
  * fit in shared memory have no such arrays; the call then does nothing. */
 int32_t bpsn_debug_set_search_count(bpsn_sim* sim, uint32_t group, uint32_t count);
 
+/* Diagnostic.  Large batches of fixed scenes have two forms of the step kernel (entry by entry,
+ * or 32 entries searched and then finished one per lane) and choose between them step by step
+ * from the number of entries the step before listed.  mode 1: always the second form where the
+ * group has it, 2: never, 0: back to the choice. */
+int32_t bpsn_debug_force_batched(bpsn_sim* sim, uint32_t group, int32_t mode);
+
 #ifdef __cplusplus
 }
 #endif

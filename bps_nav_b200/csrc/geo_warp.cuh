@@ -1679,6 +1679,15 @@ k_step_warp(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
     __syncthreads();  // the CTA's own warps see their segment as published
   }
 
+  if (!kFused && blockIdx.x == 0 && warp == 0) {
+    // how many entries this step lists, for the host (GroupDev::hListed)
+    uint32_t listed = 0u;
+    for (uint32_t l = threadIdx.x; l < g.numLists; l += 32u)
+      listed += g.counts[l];
+    listed = __reduce_add_sync(0xffffffffu, listed);
+    if (threadIdx.x == 0)
+      *reinterpret_cast<volatile uint32_t*>(g.hListed) = listed;
+  }
   constexpr uint32_t kRoles = kRotate ? 2u : 1u;
 #pragma unroll 1
   for (uint32_t role = 0; role < kRoles; ++role) {

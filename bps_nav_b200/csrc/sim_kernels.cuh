@@ -146,6 +146,8 @@ struct GroupDev {
   uint32_t* ovList;         // one-launch step: per CTA, the list entries beyond one per warp
   uint32_t* ovMeta;         // ... and per CTA {count, cursor, step number, -} (geo_warp.cuh)
   uint16_t* batchStage;     // batched step: per warp 32 corridors of up to 256 polygons
+  uint32_t* hListed;        // mapped host word: list entries of the last step (the host picks
+                            // the next step's form by it)
   uint32_t* pool;           // [poolSize] scenes waiting for a slot
   uint32_t* swapCount;      // [1] moves completed (RolloutGenerator::swapStats, :1412-1424)
   uint32_t numSlots;

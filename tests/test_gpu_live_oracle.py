@@ -27,7 +27,8 @@ def _close(a, b, rel, abs_=0.0):
 
 
 def _compare_run(scene_names, n, steps, seed, mix, threads=8, check_state_every=16,
-                 search_count=None, want_status=0, num_active=None, visited=None, **gen_kw):
+                 search_count=None, want_status=0, num_active=None, visited=None,
+                 force_batched=None, **gen_kw):
     """Steps the CUDA generator and the CPU oracle side by side and compares every output of
     every step.  ``num_active``: fewer scenes in use than the list has, the others rotate in;
     ``visited`` (a set) then collects the scenes the environments were seen in."""
@@ -38,6 +39,9 @@ def _compare_run(scene_names, n, steps, seed, mix, threads=8, check_state_every=
     if search_count is not None:
         for g in range(gen.num_groups):
             gen.debug_set_search_count(g, search_count)
+    if force_batched is not None:
+        for g in range(gen.num_groups):
+            gen.debug_force_batched(g, force_batched)
     osim = pyoracle.OracleSim([(scene_path(s), sc.episodes) for s, sc in zip(scene_names, scenes)],
                               n, seed, threads=threads,
                               active_scenes=gen._active_scenes if num_active else None,
@@ -236,10 +240,15 @@ def test_large_batch_finishes_thirty_two_entries_at_a_time():
     # then every lane pulls the string through one corridor and finishes one environment --
     # in shared memory (c1), in global memory (the 16 mixed scenes, d0), and with Flee's rule
     # that only moves need a query
-    _compare_run(["c1"], 32768, 24, seed=121, mix="uniform", threads=16, check_state_every=12)
+    # (the form is chosen step by step from the number of entries the step before listed;
+    # forced here, then left to the choice: the policy-like mix lists enough entries at this
+    # size for the choice to switch forms after the first step)
+    _compare_run(["c1"], 32768, 24, seed=121, mix="uniform", threads=16, check_state_every=12,
+                 force_batched=1)
     _compare_run(["c1"], 20480, 40, seed=122, mix="policy", threads=16, check_state_every=20)
     names = [f"m{i:02d}" for i in range(16)]
-    _compare_run(names, 65536, 16, seed=123, mix="uniform", threads=16, check_state_every=8)
+    _compare_run(names, 65536, 16, seed=123, mix="uniform", threads=16, check_state_every=8,
+                 force_batched=1)
 
 
 def test_two_launch_step_on_small_batches():
