@@ -1645,8 +1645,12 @@ k_step_warp(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
   if (kFused) {
     const uint32_t size = g.slotSize[slot];
     const uint32_t share = (size + slotCtas - 1u) / slotCtas;
-    const uint32_t at = rank * share + threadIdx.x;
-    if (threadIdx.x < share && at < size)
+    // spread over the warps (lane l of warp w takes the share's environment 16 l + w): the
+    // three kinds of step -- a turn, a move, the end of an episode with its reset -- then run
+    // side by side in different warps instead of one after the other in one
+    const uint32_t mine = (threadIdx.x & 31u) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const uint32_t at = rank * share + mine;
+    if (mine < share && at < size)
       myEnv = g.slotEnvs[g.slotEnvBase[slot] + at];
     if (threadIdx.x == 0)
       fusedCount = 0u;
