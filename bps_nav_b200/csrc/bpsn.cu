@@ -1566,7 +1566,21 @@ int32_t bpsn_gae(const float* rewards, float* values, const uint8_t* masks,
       nb = 148 * 8;
     if (nb == 0)
       nb = 1;
-    k_gae_normalize<<<nb, 256, 0, s>>>(advantages, total, partials, blocks, eps);
+    // resident and waiting when the scan ends (gaeWaitForPredecessor)
+    cudaLaunchAttribute pdl[1];
+    pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    pdl[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(nb);
+    lc.blockDim = dim3(256);
+    lc.stream = s;
+    lc.attrs = pdl;
+    lc.numAttrs = 1;
+    const GaeStat* cpartials = partials;
+    cudaError_t le = cudaLaunchKernelEx(&lc, k_gae_normalize, advantages, total, cpartials, blocks,
+                                        eps);
+    if (le != cudaSuccess)
+      return fail(nullptr, BPSN_ERR_CUDA, std::string("bpsn_gae launch: ") + cudaGetErrorString(le));
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess)

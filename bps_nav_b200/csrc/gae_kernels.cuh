@@ -54,6 +54,16 @@ __device__ __forceinline__ GaeStat gaeWarpReduce(GaeStat s) {
 
 constexpr int kGaeBlock = 128;
 
+// Programmatic dependent launch of the normalisation behind the scan: the scan lets its
+// dependent become resident at once, the normalisation waits for the whole of the scan (and
+// its stores) before it reads anything.  Both instructions are no-ops for an ordinary launch.
+__device__ __forceinline__ void gaeLaunchDependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void gaeWaitForPredecessor() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // One thread per environment column.  partials[blockIdx.x] receives the
 // block's advantage statistics when `partials` is non-null.
 __global__ void __launch_bounds__(kGaeBlock)
@@ -61,6 +71,7 @@ k_gae_scan(const float* __restrict__ rewards, float* __restrict__ values,
            const uint8_t* __restrict__ masks, const float* __restrict__ nextValue,
            float* __restrict__ returns, float* __restrict__ adv, uint32_t T, uint32_t N,
            float gamma, float gammaTau, GaeStat* __restrict__ partials) {
+  gaeLaunchDependents();
   const uint32_t n = blockIdx.x * blockDim.x + threadIdx.x;
   GaeStat st;
   st.n = 0.0;
@@ -145,6 +156,7 @@ __global__ void __launch_bounds__(256)
 k_gae_normalize(float* __restrict__ adv, size_t total, const GaeStat* __restrict__ partials,
                 uint32_t numPartials, float eps) {
   __shared__ float sMean, sInv;
+  gaeWaitForPredecessor();
   if (threadIdx.x < 32) {
     GaeStat st;
     st.n = 0.0;
