@@ -540,9 +540,12 @@ def run_ours(args):
         """Roofline object of the step kernel.  Its duration is taken from the timed windows:
         with programmatic dependent launch on, the step kernel is resident from the moment the
         kernel before it starts (it stages its scene, then waits) until the step is complete, so
-        one launch lasts (window - GAE) / T.  Units: the environments listed for a navmesh
-        query that step (those that moved: a quarter of them under uniform actions)."""
-        q_step = n * (0.25 if args.mix == "uniform" else 0.60)
+        one launch lasts (window - GAE) / T.  Units: when the step is one launch (no k_pre) the
+        kernel does the whole step of every environment, 177 B each; when k_pre does the
+        query-free part, the environments listed for the step kernel (those that moved: a
+        quarter of them under uniform actions)."""
+        one_launch = kms.get("k_pre", 0.0) == 0.0
+        q_step = n * (1.0 if one_launch else 0.25 if args.mix == "uniform" else 0.60)
         ms_launch = (ms_window - ms_gae) / T
         achieved = q_step * BYTES_PER_ENV_STEP / (ms_launch * 1e-3) / 1e9
         share = kms["k_step"] / max(sum(kms.values()), 1e-9)
@@ -550,6 +553,8 @@ def run_ours(args):
                 "unit": "GB/s", "frac": achieved / peak,
                 "traffic": NCU_TRAFFIC_BYTES.get(scene_key), "peak_source": peak_src,
                 "ms_per_launch": ms_launch, "units_per_launch": q_step,
+                "units": "env-steps (whole step in one launch)" if one_launch
+                         else "environments listed for the step kernel",
                 "bytes_per_unit": BYTES_PER_ENV_STEP,
                 "share_of_step_launches_unoverlapped": share,
                 "note": "A* is latency/divergence-bound: its algorithmic HBM bytes are tiny by "
