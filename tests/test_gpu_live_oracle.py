@@ -28,7 +28,7 @@ def _close(a, b, rel, abs_=0.0):
 
 def _compare_run(scene_names, n, steps, seed, mix, threads=8, check_state_every=16,
                  search_count=None, want_status=0, num_active=None, visited=None,
-                 force_batched=None, **gen_kw):
+                 force_batched=None, actions=None, exact_done=None, **gen_kw):
     """Steps the CUDA generator and the CPU oracle side by side and compares every output of
     every step.  ``num_active``: fewer scenes in use than the list has, the others rotate in;
     ``visited`` (a set) then collects the scenes the environments were seen in."""
@@ -53,7 +53,8 @@ def _compare_run(scene_names, n, steps, seed, mix, threads=8, check_state_every=
     osim.reset()
     pol = np.concatenate([gen.get_polars(g) for g in range(groups)])
     assert _close(pol, osim.polars, 0, 1e-5).all()
-    actions = pyoracle.philox_actions(steps, n, seed + 99, mix)
+    if actions is None:
+        actions = pyoracle.philox_actions(steps, n, seed + 99, mix)
     ties = 0
     for t in range(steps):
         for g in range(groups):
@@ -67,6 +68,11 @@ def _compare_run(scene_names, n, steps, seed, mix, threads=8, check_state_every=
         assert np.array_equal(info["success"], osim.infos[:, 0]), f"success, step {t}"
         assert _close(info["spl"], osim.infos[:, 1], 1e-4, 1e-6).all(), f"spl, step {t}"
         assert _close(info["distanceToGoal"], osim.infos[:, 2], 1e-4, 1e-6).all(), f"dist, step {t}"
+        if exact_done is not None:  # [episode ends, of which the distance matches bit for bit]
+            ended = mask == 0
+            exact_done[0] += int(ended.sum())
+            exact_done[1] += int((info["distanceToGoal"][ended].view(np.uint32) ==
+                                  osim.infos[ended, 2].astype(np.float32).view(np.uint32)).sum())
         assert _close(rew, osim.rewards, 1e-4, 1e-5).all(), f"reward, step {t}"
         assert _close(pol, osim.polars, 0, 1e-5).all(), f"polar, step {t}"
         if (t + 1) % check_state_every == 0 or t + 1 == steps:
@@ -249,6 +255,27 @@ def test_large_batch_finishes_thirty_two_entries_at_a_time():
     names = [f"m{i:02d}" for i in range(16)]
     _compare_run(names, 65536, 16, seed=123, mix="uniform", threads=16, check_state_every=8,
                  force_batched=1)
+
+
+def test_episodes_that_end_without_a_move():
+    # An episode that ends on a stop (or on the step limit during a turn) reports the distance
+    # goal -> agent from where the agent stands: the last move's search, or, before the first
+    # move, the episode table's goal -> start distance -- no search at that step.  Patterns
+    # that end episodes at once, after turns only, right after a move and after a move and
+    # turns, in shared memory (one launch and two), in global memory and with rotating scenes.
+    pattern = np.array([0, 2, 0, 1, 0, 1, 3, 0, 1, 1, 2, 2, 0, 3, 3, 0, 1, 2, 1, 0], np.int64)
+    steps = 60
+    for names, n, kw in ((["c1"], 2048, {}), (["c1"], 2048, {"two_launches": True}),
+                         (["m03", "m11"], 1024, {"global_memory": True}),
+                         (["m00", "m03", "m07", "m12"], 1024, {"num_active": 2})):
+        t = np.arange(steps)[:, None]
+        e = np.arange(n)[None, :]
+        actions = pattern[(t + 7 * e) % len(pattern)]
+        counts = [0, 0]
+        _compare_run(names, n, steps, seed=131, mix="uniform", actions=actions,
+                     check_state_every=20, exact_done=counts, **kw)
+        assert counts[0] > n * steps // 8
+        assert counts[1] >= 0.999 * counts[0], counts
 
 
 def test_two_launch_step_on_small_batches():
