@@ -499,6 +499,13 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase, uint32
     d.globalPcap = maxGlobalPcap;
     if (g.anyWarpScene) {
       g.warpMode = anyShared ? (anyGlobal ? 2 : 0) : 1;
+      // A group whose scenes are all searched in global memory and whose step lasts as long as
+      // its slowest query runs on the instance without the 64-register cap (one CTA per SM: the
+      // cap buys a second CTA, which such a step has no use for, and costs each query 10-20 %):
+      // 16 407 polygons, 4096 envs: 204 -> 169 us per step.  (Global memory by request keeps
+      // the capped instance, so that tests reach it with small batches.)
+      if (g.warpMode == 1 && !throughputBound && !(sim->cfg.flags & BPSN_FLAG_GLOBAL_MEMORY))
+        g.warpMode = 2;
       // The steps of a double-buffered generator's two groups are in flight together
       // (simulator/simulator.cpp:1377-1399; bps_nav/rl/ddppo/algo/ddppo_trainer.py:205-270).
       // A small batch's step lasts as long as its slowest query whatever the number of CTAs,
