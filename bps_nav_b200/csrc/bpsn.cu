@@ -574,8 +574,8 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase, uint32
         ctaMap.push_back(make_uint4(0u, 0u, 1u, 0u));
       g.numCtas = static_cast<uint32_t>(ctaMap.size());
       // One launch per step (k_step_warp<.., kFused>) when every CTA's share of its slot is
-      // small enough for its warps to take about one query each (about half of the
-      // environments need one); larger batches drain a slot's list with all of its CTAs.
+      // small enough for its warps to take about one query each (the environments that
+      // moved need one); larger batches drain a slot's list with all of its CTAs.
       {
         uint32_t maxShare = 0;
         for (const uint4& cm : ctaMap) {

@@ -6,10 +6,12 @@
 //
 //   k_pre   one thread per env: decode the action, advance the step counter,
 //           apply a turn (handleMovement :696-703) and refresh the GPS/compass
-//           (updateObservationState :651-677).  An env that neither moved nor
-//           finished needs no navmesh query (InfoFunctor::step :784-786): its
-//           info / reward / mask are written here.  Envs that moved forward,
-//           stopped or timed out are appended to their scene's work list.
+//           (updateObservationState :651-677).  An env that did not move needs
+//           no navmesh query: on a turn it reports the distance of the step
+//           before (InfoFunctor::step :784-786); when its episode ends it
+//           reports the distance kept for that (GroupDev::doneDist) and is
+//           reset by table lookup.  Its info / reward / mask are written here.
+//           Envs that moved forward are appended to their slot's work list.
 //   k_step_warp / k_step_thread
 //           one warp (scene tables in shared memory, geo_warp.cuh) or one
 //           thread (tables in global memory) per listed env: forward move
@@ -18,6 +20,7 @@
 //           reward / mask (RewardFunctor::step :808-822) and, when the episode
 //           finished, the reset (BaseSimulator::reset :601-618,
 //           InfoFunctor::reset :744-756, RewardFunctor::reset :801-806).
+// (Small batches of fixed scenes run both parts in one launch, geo_warp.cuh.)
 //
 // Tasks.  PointNav is described above.  Flee (simulator.cpp:830-887): the info is the
 // geodesic distance from the episode's snapped start to the agent, refreshed only when
@@ -558,9 +561,10 @@ __device__ __forceinline__ void forwardMove(const GroupDev& g, const NavScene& s
 }
 
 // The part of a step that needs no navmesh query, for one environment: decode the action,
-// advance the step counter, apply a turn and refresh the GPS/compass.  An environment that
-// neither moved nor finished is complete after this (info / reward / mask written here);
-// otherwise *entry receives its work-list entry and *listIdx its list, and true is returned.
+// advance the step counter, apply a turn and refresh the GPS/compass.  An environment that did
+// not move is complete after this (info / reward / mask written here, the reset included when
+// its episode ended); one that moved gets its work-list entry in *entry and its list in
+// *listIdx, and true is returned.
 __device__ __forceinline__ bool preEnv(const GroupDev& g, const SceneTable& st, uint32_t e,
                                        const int64_t* __restrict__ actions,
                                        const uint8_t* __restrict__ actions8, const TurnConsts& tc,
