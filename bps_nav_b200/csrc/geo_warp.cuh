@@ -1693,6 +1693,18 @@ k_step_warp(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
       *reinterpret_cast<volatile uint32_t*>(g.hListed) = listed;
   }
   constexpr uint32_t kRoles = kRotate ? 2u : 1u;
+  // A slot that is between two scenes has entries in both of its lists.  Its CTAs then divide
+  // into two parties in proportion to the lists' lengths, one per list, so that the two scenes
+  // are worked on side by side and the step lasts as long as the slower of the two, not as
+  // their sum (a single CTA, or a slot with one list empty, takes them one after the other).
+  uint32_t firstParty = 0u;  // CTAs of the party of list 0; 0: no division
+  if (kRotate && slotCtas > 1u) {
+    const uint32_t n0 = g.counts[2u * slot], n1 = g.counts[2u * slot + 1u];
+    if (n0 != 0u && n1 != 0u) {
+      const uint32_t c0 = (slotCtas * n0 + (n0 + n1) / 2u) / (n0 + n1);
+      firstParty = min(max(c0, 1u), slotCtas - 1u);
+    }
+  }
 #pragma unroll 1
   for (uint32_t role = 0; role < kRoles; ++role) {
     const uint32_t listIdx = 2u * slot + role;
@@ -1704,6 +1716,13 @@ k_step_warp(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
     }
     if (n == 0)
       continue;
+    uint32_t partyRank = rank, partyCtas = slotCtas;
+    if (kRotate && firstParty != 0u) {
+      if ((role == 0u) != (rank < firstParty))
+        continue;  // the other party's list
+      partyRank = role == 0u ? rank : rank - firstParty;
+      partyCtas = role == 0u ? firstParty : slotCtas - firstParty;
+    }
     const uint32_t sceneIdx = !kRotate ? sc0 : (role ? g.slotPrev[slot] : g.slotScene[slot]);
     const WarpPlan pl = !kRotate ? pl0 : plan[sceneIdx];
     if (pl.warps == 0)
@@ -1738,11 +1757,11 @@ k_step_warp(GroupDev g, SceneTable st, const WarpPlan* __restrict__ plan,
       stepWarpQueries<false, false>(g, st, pl, src, BPSN_STEP_ARGS);
     } else {
       const uint32_t firstQ =
-          rank * static_cast<uint32_t>(warpsPerBlock) + static_cast<uint32_t>(warp);
+          partyRank * static_cast<uint32_t>(warpsPerBlock) + static_cast<uint32_t>(warp);
       if (firstQ - static_cast<uint32_t>(warp) >= n)
         continue;
       ListSource src{g.geoList + g.listBase[listIdx], g.counts + g.numLists + listIdx, firstQ,
-                     slotCtas * static_cast<uint32_t>(warpsPerBlock), n, true};
+                     partyCtas * static_cast<uint32_t>(warpsPerBlock), n, true};
       if constexpr (kMode == 0) {
         stepWarpQueries<false, kBatched>(g, st, pl, src, BPSN_STEP_ARGS);
       } else if constexpr (kMode == 1) {
