@@ -238,7 +238,11 @@ class _RolloutGenerator:
 
     def step_start(self, group_idx, actions, reward_out=None, mask_out=None, polar_out=None):
         """``actions``: C-contiguous int64 numpy array of length ``envs_per_group`` (reference
-        signature), or a CUDA int64 tensor of the same length (device-resident fast path).
+        signature: validated and staged by the call), or an int64 tensor of the same length
+        that the device can read where it lies -- a CUDA tensor, or a CPU tensor in page-locked
+        memory (``pin_memory()``), which the kernels then read over the bus.  A tensor is not
+        validated (an out-of-range value marks the environment, which does not move) and must
+        stay unchanged until the step has run.
 
         ``reward_out`` / ``mask_out`` (added): contiguous CUDA tensors of ``envs_per_group``
         float32 / 1-byte elements that also receive this step's reward and mask, e.g.
@@ -278,10 +282,10 @@ class _RolloutGenerator:
                                                   L.MEM_HOST, stream, ro, mo, po)
         else:
             import torch
-            if not (isinstance(actions, torch.Tensor) and actions.is_cuda and
-                    actions.dtype == torch.int64 and actions.is_contiguous()):
-                raise RuntimeError("actions must be an int64 numpy array or a contiguous CUDA "
-                                   "int64 tensor")
+            if not (isinstance(actions, torch.Tensor) and actions.dtype == torch.int64 and
+                    actions.is_contiguous() and (actions.is_cuda or actions.is_pinned())):
+                raise RuntimeError("actions must be an int64 numpy array, a contiguous CUDA "
+                                   "int64 tensor or a contiguous int64 tensor in pinned memory")
             if actions.numel() != self.envs_per_group:
                 raise RuntimeError("actions length must equal the number of envs in the group")
             self._keepalive = actions

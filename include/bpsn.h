@@ -197,7 +197,10 @@ int32_t bpsn_reset(bpsn_sim* sim, uint32_t group, void* stream);
 /* actions: int64 [B], one of {0 stop, 1 forward, 2 left, 3 right}.
  * actions_mem = BPSN_MEM_HOST: validated, staged and copied by the call;
  * BPSN_MEM_DEVICE: read by the kernels as is (an out-of-range value sets the
- * environment's BAD_ACTION status bit and that environment does not move).
+ * environment's BAD_ACTION status bit and that environment does not move); any
+ * address the device can read will do, page-locked host memory included (the
+ * kernels then read the actions over the bus; they must stay unchanged until
+ * the step has run).
  * The step is enqueued on `stream`; bpsn_step_end waits for it when host
  * mirrors are enabled and otherwise only closes the start/end pairing. */
 int32_t bpsn_step_start(bpsn_sim* sim, uint32_t group, const int64_t* actions,

@@ -59,8 +59,11 @@ def test_queries_match_golden(name):
     gen.close()
 
 
-@pytest.mark.parametrize("fname,host_actions", [("c0_traj.npz", True), ("c0_policy_traj.npz", False)])
+@pytest.mark.parametrize("fname,host_actions", [("c0_traj.npz", True), ("c0_policy_traj.npz", False),
+                                                ("c0_traj.npz", "pinned")])
 def test_trajectory_matches_golden(fname, host_actions):
+    # actions as numpy rows (validated and staged by the call), as rows of a CUDA tensor, or as
+    # rows of a tensor in page-locked host memory that the kernels read in place
     g = np.load(os.path.join(GOLD, fname))
     actions = g["actions"].astype(np.int64)
     steps, n = actions.shape
@@ -86,8 +89,11 @@ def test_trajectory_matches_golden(fname, host_actions):
 
     check_state(0)
     dact = torch.from_numpy(actions).cuda()
+    pact = torch.from_numpy(actions).pin_memory()
     for t in range(steps):
-        if host_actions:
+        if host_actions == "pinned":
+            gen.step(0, pact[t])
+        elif host_actions:
             gen.step(0, actions[t])
         else:
             gen.step(0, dact[t])
