@@ -641,6 +641,16 @@ def run_ours(args):
         c2 = {"T": C2_T, "N": C2_N, "fused_ms": ms, "achieved_gbs": gbs, "frac_of_hbm": gbs / peak,
               "algorithmic_bytes": C2_T * C2_N * BYTES_PER_GAE_ELEM,
               "note": "two launches (reverse scan, normalise); launch-latency-bound at this size"}
+        # the same kernels where the arrays are large enough for bandwidth to count
+        big_n = 16 * C2_N
+        stb = Storage(big_n)
+        stb.masks.copy_(torch.rand(C2_T + 1, big_n, 1, device=dev) >= 0.002)
+        stb.rewards.normal_()
+        msb = gae_ms(stb, reps=20)
+        gbsb = C2_T * big_n * BYTES_PER_GAE_ELEM / (msb * 1e-3) / 1e9
+        c2["at_16x_N"] = {"N": big_n, "fused_ms": msb, "achieved_gbs": gbsb,
+                          "frac_of_hbm": gbsb / peak}
+        del stb
         if world == 1:
             c2.update(gae_reference_times(st, torch))
 

@@ -156,16 +156,24 @@ __global__ void __launch_bounds__(256)
 k_gae_normalize(float* __restrict__ adv, size_t total, const GaeStat* __restrict__ partials,
                 uint32_t numPartials, float eps) {
   __shared__ float sMean, sInv;
+  __shared__ GaeStat sWarp[8];
   gaeWaitForPredecessor();
-  if (threadIdx.x < 32) {
+  {
+    // every thread merges a share of the block partials, the warps' results are merged by
+    // thread 0 (a chain of numPartials / 256 + 5 + 8 merges instead of numPartials / 32 + 5)
     GaeStat st;
     st.n = 0.0;
     st.mean = 0.0;
     st.m2 = 0.0;
-    for (uint32_t i = threadIdx.x; i < numPartials; i += 32)
+    for (uint32_t i = threadIdx.x; i < numPartials; i += blockDim.x)
       st = gaeMerge(st, partials[i]);
     st = gaeWarpReduce(st);
+    if ((threadIdx.x & 31u) == 0u)
+      sWarp[threadIdx.x >> 5] = st;
+    __syncthreads();
     if (threadIdx.x == 0) {
+      for (uint32_t w = 1; w < (blockDim.x >> 5); ++w)
+        st = gaeMerge(st, sWarp[w]);
       const double var = st.n > 1.0 ? st.m2 / (st.n - 1.0) : __longlong_as_double(0x7ff8000000000000ll);
       const float mean = static_cast<float>(st.mean);
       const float sd = static_cast<float>(sqrt(var));
@@ -176,9 +184,35 @@ k_gae_normalize(float* __restrict__ adv, size_t total, const GaeStat* __restrict
   __syncthreads();
   const float mean = sMean, denom = sInv;
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
-  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-       i += stride)
-    adv[i] = (adv[i] - mean) / denom;
+  const size_t first = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if ((reinterpret_cast<uintptr_t>(adv) & 15u) == 0u) {
+    // 16 bytes per access and four independent accesses in flight per thread: a plain
+    // element-by-element loop waits for each load before it issues the next (the store to the
+    // same array in between keeps the compiler from moving loads up)
+    float4* a4 = reinterpret_cast<float4*>(adv);
+    const size_t nvec = total / 4;
+    for (size_t i = first; i < nvec; i += 4 * stride) {
+      float4 v[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (i + k * stride < nvec)
+          v[k] = a4[i + k * stride];
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (i + k * stride < nvec) {
+          v[k].x = (v[k].x - mean) / denom;
+          v[k].y = (v[k].y - mean) / denom;
+          v[k].z = (v[k].z - mean) / denom;
+          v[k].w = (v[k].w - mean) / denom;
+          a4[i + k * stride] = v[k];
+        }
+    }
+    for (size_t i = nvec * 4 + first; i < total; i += stride)
+      adv[i] = (adv[i] - mean) / denom;
+  } else {
+    for (size_t i = first; i < total; i += stride)
+      adv[i] = (adv[i] - mean) / denom;
+  }
 }
 
 // ---------------------------------------------------------------------------
