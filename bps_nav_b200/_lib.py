@@ -47,7 +47,8 @@ class Config(C.Structure):
     _fields_ = [("gpu_id", C.c_int32), ("num_envs", C.c_uint32), ("num_groups", C.c_uint32),
                 ("num_scenes", C.c_uint32), ("seed", C.c_uint64), ("flags", C.c_uint32),
                 ("task", C.c_uint32), ("render_width", C.c_uint32), ("render_height", C.c_uint32),
-                ("num_active_scenes", C.c_uint32)]
+                ("num_active_scenes", C.c_uint32),
+                ("swap_interval", C.c_uint32)]
 
 
 class AdvSegment(C.Structure):

@@ -93,33 +93,38 @@ class _RolloutGenerator:
 
     def __init__(self, dataset_path, asset_path, num_environments, num_active_scenes, num_workers,
                  gpu_id, render_resolution, color, depth, double_buffered, seed,
-                 should_set_affinity=True):
+                 should_set_affinity=True, *, swap_interval=0):
         # num_workers / should_set_affinity configure the reference's CPU worker pool; a kernel
-        # launch replaces that pool, so they are accepted and ignored.
+        # launch replaces that pool, so they are accepted and ignored.  swap_interval (added,
+        # keyword only): see from_scenes.
         del num_workers, should_set_affinity
         scenes = _dataset.load_dataset(dataset_path, asset_path)
         self._setup(scenes, num_environments, num_active_scenes, gpu_id, render_resolution, color,
-                    depth, double_buffered, seed, host_mirrors=True)
+                    depth, double_buffered, seed, host_mirrors=True, swap_interval=swap_interval)
 
     @classmethod
     def from_scenes(cls, scenes, num_environments, num_active_scenes=None, gpu_id=0,
                     render_resolution=(64, 64), color=False, depth=False, double_buffered=False,
                     seed=0, host_mirrors=True, generic_kernel=False, exact_heap=False,
-                    small_smem=False, global_memory=False, env_scene=None, two_launches=False):
+                    small_smem=False, global_memory=False, env_scene=None, two_launches=False,
+                    swap_interval=0):
         """Builds a generator from in-memory ``dataset.Scene`` objects (no JSON involved).
         ``env_scene``: optional explicit scene (index into ``scenes``) of every environment, for
-        layouts other than equal consecutive blocks; only with every scene active."""
+        layouts other than equal consecutive blocks; only with every scene active.
+        ``swap_interval``: with fewer active scenes than scenes, steps of a group between two
+        scene changes at least (0: a slot changes scene as soon as it is whole again)."""
         self = cls.__new__(cls)
         if num_active_scenes is None:
             num_active_scenes = len(scenes)
         self._setup(list(scenes), num_environments, num_active_scenes, gpu_id, render_resolution,
                     color, depth, double_buffered, seed, host_mirrors, generic_kernel, exact_heap,
-                    small_smem, global_memory, env_scene, two_launches)
+                    small_smem, global_memory, env_scene, two_launches, swap_interval)
         return self
 
     def _setup(self, scenes, num_environments, num_active_scenes, gpu_id, render_resolution, color,
                depth, double_buffered, seed, host_mirrors, generic_kernel=False, exact_heap=False,
-               small_smem=False, global_memory=False, env_scene=None, two_launches=False):
+               small_smem=False, global_memory=False, env_scene=None, two_launches=False,
+               swap_interval=0):
         if self._task not in _TASKS:
             raise NotImplementedError(f"{type(self).__name__}: unknown task")
         self._task_id, self._info_dtype = _TASKS[self._task]
@@ -157,7 +162,8 @@ class _RolloutGenerator:
                        task=self._task_id,
                        render_width=self._res[0] if self._depth else 0,
                        render_height=self._res[1] if self._depth else 0,
-                       num_active_scenes=self.num_active_scenes)
+                       num_active_scenes=self.num_active_scenes,
+                       swap_interval=int(swap_interval))
         L.check(self._lib.bpsn_create(C.byref(cfg), C.byref(self._h)))
         try:
             act = np.ascontiguousarray(active, np.uint32)

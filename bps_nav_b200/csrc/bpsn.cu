@@ -358,6 +358,7 @@ int32_t allocGroup(bpsn_sim* sim, Group& g, uint32_t B, uint32_t envBase, uint32
   d.slotSize = reinterpret_cast<uint32_t*>(b + oSlotSize);
   d.pool = reinterpret_cast<uint32_t*>(b + oPool);
   d.swapCount = reinterpret_cast<uint32_t*>(b + oSwapCount);
+  d.swapInterval = rotation ? sim->cfg.swap_interval : 0u;
   d.slotEnvs = reinterpret_cast<uint32_t*>(b + oSlotEnvs);
   d.slotEnvBase = reinterpret_cast<uint32_t*>(b + oSlotEnvBase);
   {
@@ -1134,9 +1135,13 @@ int32_t bpsn_finalize(bpsn_sim* sim) {
     // Every slot starts its first move right away (RolloutGenerator's constructor calls
     // startSceneSwap on every swapper, simulator.cpp:1594): the environments begin in the
     // first scenes and follow at the end of their first episodes.
-    for (uint32_t gi = 0; gi < ng; ++gi)
-      k_swap<<<1, 32>>>(sim->groups[gi].dev, static_cast<uint32_t>(sim->cfg.seed),
+    for (uint32_t gi = 0; gi < ng; ++gi) {
+      GroupDev first = sim->groups[gi].dev;
+      first.swapInterval = 0u;  // all slots, whatever the pace of the later moves
+      first.stepId = 0u;
+      k_swap<<<1, 32>>>(first, static_cast<uint32_t>(sim->cfg.seed),
                         static_cast<uint32_t>(sim->cfg.seed >> 32));
+    }
     BPSN_CUDA(sim, cudaGetLastError());
     BPSN_CUDA(sim, cudaDeviceSynchronize());
   }

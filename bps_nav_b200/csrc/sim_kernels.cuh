@@ -152,7 +152,9 @@ struct GroupDev {
   uint32_t* hListed;        // mapped host word: list entries of the last step (the host picks
                             // the next step's form by it)
   uint32_t* pool;           // [poolSize] scenes waiting for a slot
-  uint32_t* swapCount;      // [1] moves completed (RolloutGenerator::swapStats, :1412-1424)
+  uint32_t* swapCount;      // [2] moves started (RolloutGenerator::swapStats, :1412-1424); the
+                            // step at which the group started its last one
+  uint32_t swapInterval;    // steps of the group between two moves at least (0: no limit)
   uint32_t numSlots;
   uint32_t poolSize;
   uint32_t slotBase;        // number of the group's first slot among all slots
@@ -719,10 +721,15 @@ __global__ void k_swap(GroupDev g, uint32_t seedLo, uint32_t seedHi) {
   waitForPredecessor();
   if (blockIdx.x != 0 || threadIdx.x != 0 || g.poolSize == 0)
     return;
+  // (with an interval: one move at a time, and only so many steps after the last one)
+  if (g.swapInterval != 0u && g.stepId - g.swapCount[1] < g.swapInterval)
+    return;
   uint32_t swaps = 0;
   for (uint32_t s = 0; s < g.numSlots; ++s) {
     if (g.slotRemaining[s] != 0u)
       continue;
+    if (g.swapInterval != 0u && swaps != 0u)
+      break;
     const uint32_t epoch = g.slotEpoch[s] + 1u;
     const uint32_t r = philoxFirst(g.slotBase + s, epoch, 1u, 0u, seedLo, seedHi);
     const uint32_t at = mulHi32(r, g.poolSize);
@@ -734,8 +741,10 @@ __global__ void k_swap(GroupDev g, uint32_t seedLo, uint32_t seedHi) {
     g.slotRemaining[s] = g.slotSize[s];
     ++swaps;
   }
-  if (swaps)
-    *g.swapCount += swaps;
+  if (swaps) {
+    g.swapCount[0] += swaps;
+    g.swapCount[1] = g.stepId;
+  }
 }
 
 __global__ void __launch_bounds__(256)

@@ -84,6 +84,11 @@ typedef struct {
                                  end of its running episode (SceneSwapper / EnvironmentGroup::
                                  swapScene, simulator/simulator.cpp:1063-1154, 1284-1308,
                                  1636-1640).  Every scene's navigation mesh stays resident. */
+  uint32_t swap_interval;    /* 0: a slot draws its next scene as soon as all of its
+                                 environments have arrived.  k > 0: a group starts at most one
+                                 such move every k of its steps -- the pace of the reference's
+                                 single background loader, which hands over one scene at a time
+                                 (BackgroundSceneLoader, simulator/simulator.cpp:462-550). */
 } bpsn_config;
 
 /* Tasks of the reference's three generators (simulator/simulator.cpp:734-999,

@@ -188,20 +188,42 @@ struct Sim {
   std::vector<uint32_t> slotEpoch;
   std::vector<std::atomic<int>> slotRemaining;
   std::vector<std::vector<int>> pools;  // per group
+  uint32_t swapInterval = 0;            // steps of a group between two of its moves (0: no limit)
+  std::vector<uint32_t> groupSteps, groupLastSwap;
   uint64_t numSwaps = 0;
 };
 
 // SceneSwapper::postStep + startSceneSwap (simulator.cpp:1094-1129) for the slots that lie
 // inside [first, first + count), in slot order: a slot all of whose environments have reached
 // its scene draws the next one from its group's pool; the scene it leaves goes into the pool.
-void swapPass(Sim& s, int first, int count) {
+void swapPass(Sim& s, int first, int count, bool atSetup = false) {
   const int slotsPerGroup = s.numSlots / s.numGroups;
+  // with an interval: every group whose environments were stepped counts a step, and starts
+  // at most one move, and only so many of its steps after its last one
+  std::vector<char> mayStart(s.numGroups, 1);
+  if (!atSetup) {
+    const int perGroup = s.nEnvs / s.numGroups;
+    for (int g = 0; g < s.numGroups; ++g) {
+      if (g * perGroup < first || (g + 1) * perGroup > first + count)
+        continue;
+      s.groupSteps[g]++;
+      if (s.swapInterval != 0u && s.groupSteps[g] - s.groupLastSwap[g] < s.swapInterval)
+        mayStart[g] = 0;
+    }
+  }
   for (int sl = 0; sl < s.numSlots; ++sl) {
     if (sl * s.perSlot < first || (sl + 1) * s.perSlot > first + count)
       continue;
-    std::vector<int>& pool = s.pools[sl / slotsPerGroup];
+    const int grp = sl / slotsPerGroup;
+    std::vector<int>& pool = s.pools[grp];
     if (pool.empty() || s.slotRemaining[sl].load() != 0)
       continue;
+    if (!atSetup && !mayStart[grp])
+      continue;
+    if (!atSetup && s.swapInterval != 0u) {
+      mayStart[grp] = 0;  // one move at a time
+      s.groupLastSwap[grp] = s.groupSteps[grp];
+    }
     const uint32_t epoch = s.slotEpoch[sl] + 1;
     uint32_t r[4];
     philox4x32(static_cast<uint32_t>(sl), epoch, 1u, 0u, static_cast<uint32_t>(s.seed),
@@ -588,9 +610,16 @@ int osim_enable_rotation(void* h, int num_active, int num_groups, const int* act
     s.envs[e].scene = s.slotScene[s.envs[e].slot];
     s.envs[e].epoch = 0;
   }
-  swapPass(s, 0, s.nEnvs);
+  s.groupSteps.assign(num_groups, 0u);
+  s.groupLastSwap.assign(num_groups, 0u);
+  swapPass(s, 0, s.nEnvs, /*atSetup=*/true);
   s.numSwaps = 0;
   return 0;
+}
+
+// Pace of the rotation: steps of a group between two of its moves at least (0: no limit).
+void osim_set_swap_interval(void* h, uint32_t interval) {
+  static_cast<Sim*>(h)->swapInterval = interval;
 }
 
 // scene of every environment right now, and the moves started since set-up

@@ -177,6 +177,7 @@ def sim_lib():
         lib.osim_masks.restype = C.POINTER(C.c_uint8)
         lib.osim_masks.argtypes = [C.c_void_p]
         lib.osim_enable_rotation.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_int)]
+        lib.osim_set_swap_interval.argtypes = [C.c_void_p, C.c_uint32]
         lib.osim_scenes.restype = C.c_uint64
         lib.osim_scenes.argtypes = [C.c_void_p, C.POINTER(C.c_int)]
         lib.osim_get_state.argtypes = [C.c_void_p, _fp, _u32p]
@@ -200,9 +201,10 @@ class OracleSim:
     TASKS = {"pointnav": 0, "flee": 1, "exploration": 2}
 
     def __init__(self, scenes, num_envs, seed, env_scene=None, threads=1, task="pointnav",
-                 active_scenes=None, num_groups=1):
+                 active_scenes=None, num_groups=1, swap_interval=0):
         """``active_scenes``: turns scene rotation on -- the scenes in use first, one per slot of
-        ``num_envs / len(active_scenes)`` consecutive environments; the others rotate in."""
+        ``num_envs / len(active_scenes)`` consecutive environments; the others rotate in,
+        at most one per group every ``swap_interval`` steps (0: as soon as a slot is whole)."""
         lib = sim_lib()
         self._lib = lib
         self.num_envs = num_envs
@@ -227,6 +229,7 @@ class OracleSim:
             if lib.osim_enable_rotation(self._h, len(act), num_groups,
                                         act.ctypes.data_as(C.POINTER(C.c_int))) != 0:
                 raise RuntimeError("oracle: bad scene rotation parameters")
+            lib.osim_set_swap_interval(self._h, int(swap_interval))
         n = num_envs
         self.rewards = np.ctypeslib.as_array(lib.osim_rewards(self._h), (n,))
         self.masks = np.ctypeslib.as_array(lib.osim_masks(self._h), (n,))

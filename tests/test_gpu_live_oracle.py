@@ -45,7 +45,8 @@ def _compare_run(scene_names, n, steps, seed, mix, threads=8, check_state_every=
     osim = pyoracle.OracleSim([(scene_path(s), sc.episodes) for s, sc in zip(scene_names, scenes)],
                               n, seed, threads=threads,
                               active_scenes=gen._active_scenes if num_active else None,
-                              num_groups=gen.num_groups)
+                              num_groups=gen.num_groups,
+                              swap_interval=gen_kw.get("swap_interval", 0))
     groups = gen.num_groups
     B = gen.envs_per_group
     for g in range(groups):
@@ -239,6 +240,31 @@ def test_scenes_rotate_with_two_groups_and_mixed_memory():
     # long episodes: slots stay between two scenes for many steps
     _compare_run(names, 128, 400, seed=73, mix="policy", threads=16, check_state_every=20,
                  num_active=2, global_memory=True)
+
+
+def test_scenes_rotate_at_a_set_pace():
+    # swap_interval: a group starts at most one move every so many of its steps (the pace of
+    # the reference's single background loader) instead of one per slot as soon as the slot is
+    # whole; one and two groups, compared with the oracle step by step, scenes and swap
+    # statistics included
+    names = [f"m{i:02d}" for i in range(12)]
+    _compare_run(names, 512, 300, seed=74, mix="uniform", threads=16, check_state_every=10,
+                 num_active=4, swap_interval=16)
+    _compare_run(names, 512, 300, seed=75, mix="uniform", threads=16, check_state_every=10,
+                 num_active=4, swap_interval=5, double_buffered=True)
+    from bps_nav_b200 import bps_sim
+    scenes = [load_scene(s) for s in names]
+    rates = []
+    for interval in (0, 16):
+        gen = bps_sim.PointNavRolloutGenerator.from_scenes(scenes, 512, seed=74, num_active_scenes=4,
+                                                           swap_interval=interval)
+        gen.reset(0)
+        acts = pyoracle.philox_actions(200, 512, 173, "uniform")
+        for t in range(200):
+            gen.step(0, acts[t])
+        rates.append(gen.swap_stats[0])
+        gen.close()
+    assert rates[1] < rates[0] and rates[1] <= 100.0 * (200 // 16 + 1) / (200 * 512) + 1e-9
 
 
 def test_large_batch_finishes_thirty_two_entries_at_a_time():
