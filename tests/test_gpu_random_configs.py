@@ -38,6 +38,8 @@ def _draw(rng):
     if k >= 4 and rng.random() < 0.3:
         half = k // 2
         kw["num_active"] = (half - half % groups) or groups
+        if rng.random() < 0.5:
+            kw["swap_interval"] = rng.choice([3, 16])
     form = rng.choice([None, None, 1, 2])
     if form is not None:
         kw["force_batched"] = form
